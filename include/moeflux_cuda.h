@@ -1,0 +1,234 @@
+/*
+ * moeflux_cuda.h - C ABI of the B200 (sm_100a) attention backend for moeflux.
+ *
+ * The library replaces the attention sub-block of moeflux's per-layer forward:
+ * what `full_attn_layer_forward` does between "q/k/v projections are ready"
+ * and "o_proj input is ready" (crates/moeflux/src/riir/full_attn_forward.rs:
+ * 278-389: RoPE, KV append, SDPA, sigmoid gate) and what
+ * `linear_attn_layer_forward` does with its five GatedDeltaNet kernels
+ * (crates/moeflux/src/riir/linear_attn_forward.rs:607-664: conv1d_step,
+ * rms_norm_qk, compute_decay_beta, gated_delta_net_step, gated_rms_norm),
+ * together with the per-layer state those steps own and the state calls of the
+ * public surface (crates/moeflux-sys/metal_infer/moeflux.h:88-104, 627-639).
+ *
+ * Conventions follow moeflux.h: opaque context, NULL on construction failure;
+ * `int` results are 0 on success and -1 on error unless stated; every buffer is
+ * caller-allocated and caller-owned; outputs are fully overwritten.  All
+ * pointers are HOST pointers unless the function name ends in `_dev`, in which
+ * case they are device pointers on the context's device and the call is
+ * asynchronous on the context's stream.  One thread per context at a time;
+ * several contexts may be used from different threads.
+ *
+ * There is no CPU fallback: every entry point that computes runs CUDA kernels
+ * and fails (-1, message in mfc_last_error) when no sm_100 device is usable.
+ */
+#ifndef MOEFLUX_CUDA_H
+#define MOEFLUX_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mfc_ctx mfc_ctx;
+
+enum { MFC_KV_F32 = 0, MFC_KV_BF16 = 1 };
+
+/* Geometry and placement.  The geometry fields mirror `Variant`
+ * (crates/moeflux/src/riir/variants.rs:132-250); mfc_default_config() fills
+ * them with the Qwen3.5-397B-A17B values (variants.rs:383-423). */
+typedef struct mfc_config {
+    int32_t num_layers;          /* 60 */
+    int32_t full_attn_interval;  /* 4: layer i is full attention iff (i+1) % interval == 0 */
+    int32_t num_attn_heads;      /* 32 */
+    int32_t num_kv_heads;        /* 2;  num_attn_heads / num_kv_heads must be <= 16 */
+    int32_t head_dim;            /* 256 (the only supported value) */
+    int32_t rotary_dim;          /* 64 (multiple of 4, <= head_dim) */
+    float   rope_theta;          /* 1e7 */
+    int32_t linear_num_v_heads;  /* 64 */
+    int32_t linear_num_k_heads;  /* 16 */
+    int32_t linear_key_dim;      /* 128 (only) */
+    int32_t linear_value_dim;    /* 128 (only) */
+    int32_t conv_kernel_size;    /* 4 (only) */
+    float   rms_norm_eps;        /* 1e-6 */
+    int32_t kv_dtype;            /* MFC_KV_F32 | MFC_KV_BF16: storage type of the KV cache */
+    int32_t max_seq;             /* positions per sequence (whole sequence, before any split) */
+    int32_t n_seqs;              /* independent sequences (seq_id in [0, n_seqs)) */
+    int32_t device;              /* CUDA device ordinal */
+    /* KV-sequence split across contexts (one per GPU): this context stores the
+     * positions p with (p / kv_block) % kv_world == kv_rank.  kv_world = 1
+     * keeps everything here. */
+    int32_t kv_rank;
+    int32_t kv_world;
+    int32_t kv_block;            /* positions per block of the cyclic split (multiple of 32) */
+    int32_t max_batch;           /* most (layer, sequence) items one batched call may carry */
+    int32_t snapshot_version;    /* 1 (C engine's header, 8 words) or 2 (Rust port's, 10 words) */
+} mfc_config;
+
+/* Fills *cfg with the A17B geometry, bf16 KV off (fp32), max_seq 8192,
+ * n_seqs 1, device 0, no KV split, max_batch = num_layers * n_seqs. */
+void mfc_default_config(mfc_config *cfg);
+
+/* Replaces mf_init_model / RsCtx::open for this path (moeflux.h:55,
+ * crates/moeflux/src/riir/mod.rs:270).  Allocates the KV caches, the
+ * GatedDeltaNet states (zeroed) and all working memory up front; no other entry
+ * point allocates device memory.  NULL on failure (mfc_last_error(NULL)). */
+mfc_ctx *mfc_open(const mfc_config *cfg);
+/* mf_free_model (moeflux.h:66).  No-op on NULL. */
+void mfc_free(mfc_ctx *ctx);
+/* Message of the last failure on this context (or of mfc_open when ctx is
+ * NULL).  Points to storage owned by the library. */
+const char *mfc_last_error(const mfc_ctx *ctx);
+/* The geometry the context was opened with. */
+int mfc_get_config(const mfc_ctx *ctx, mfc_config *out);
+/* cudaStream_t of the context, as void*; `_dev` calls are ordered on it. */
+void *mfc_stream(mfc_ctx *ctx);
+/* Blocks until the context's stream is idle; -1 if a kernel reported a fault
+ * (bounded wait expired) since the last call. */
+int mfc_synchronize(mfc_ctx *ctx);
+
+/* Per-layer constant tensors of a GatedDeltaNet layer, read where the reference
+ * reads them from the weight file (linear_attn_forward.rs:507-510):
+ * conv1d.weight bf16 [conv_dim][4], A_log f32 [v_heads], dt_bias bf16 [v_heads],
+ * norm.weight bf16 [value_dim] (may be NULL when the gated norm is never used). */
+int mfc_set_linear_weights(mfc_ctx *ctx, int32_t layer, const uint16_t *conv_w_bf16,
+                           const float *a_log, const uint16_t *dt_bias_bf16,
+                           const uint16_t *norm_w_bf16);
+/* ------------------------------------------------------------------------
+ * The hot path, one (layer, sequence) item per call.
+ * ---------------------------------------------------------------------- */
+
+/* Full-attention decode step of layer `layer` for sequence `seq_id` at absolute
+ * position `pos`: RoPE(q,k) -> append k,v -> SDPA over the pos+1 cached rows ->
+ * sigmoid gate.  Replaces full_attn_forward.rs:278-389 (apply_rotary_emb, the
+ * KV append, encode_attn_scores/softmax/values_batched + encode_sigmoid_gate of
+ * crates/moeflux/src/riir/gpu_attn.rs:119-235, and the sdpa_cpu fallback).
+ *   q, gate, out: [num_attn_heads * head_dim];  k, v: [num_kv_heads * head_dim].
+ * `pos` must equal the layer's current length (full_attn_forward.rs:73-78);
+ * -1 on mismatch, on overflow of max_seq, on a linear layer index, NULL args. */
+int mfc_full_attn_step(mfc_ctx *ctx, int32_t layer, int32_t seq_id, int32_t pos, const float *q,
+                       const float *gate, const float *k, const float *v, float *out);
+
+/* GatedDeltaNet decode step of layer `layer` for sequence `seq_id`:
+ * conv1d+SiLU (history advanced) -> q/k norm -> decay/beta -> delta-rule state
+ * update and read-out -> gated RMSNorm when z != NULL.  Replaces the five
+ * encoders of crates/moeflux/src/riir/gpu_linear_attn.rs:54-202 as sequenced at
+ * linear_attn_forward.rs:607-664.
+ *   qkv: [conv_dim] (q | k | v);  z: [v_heads*value_dim] or NULL;
+ *   alpha, beta: [v_heads];  out: [v_heads*value_dim]. */
+int mfc_linear_attn_step(mfc_ctx *ctx, int32_t layer, int32_t seq_id, const float *qkv,
+                         const float *z, const float *alpha, const float *beta, float *out);
+
+/* ------------------------------------------------------------------------
+ * Batched forms: n items, item i = (layers[i], seq_ids[i]); inputs and outputs
+ * are packed [n][...] in item order.  An item pair may appear once per call.
+ * The reference runs one sequence (seq_id ignored, moeflux.h:15-17); these are
+ * the same step applied to n independent (layer, sequence) states in one
+ * launch.  n <= max_batch.
+ * ---------------------------------------------------------------------- */
+int mfc_full_attn_step_batched(mfc_ctx *ctx, int32_t n, const int32_t *layers,
+                               const int32_t *seq_ids, const int32_t *pos, const float *q,
+                               const float *gate, const float *k, const float *v, float *out);
+int mfc_linear_attn_step_batched(mfc_ctx *ctx, int32_t n, const int32_t *layers,
+                                 const int32_t *seq_ids, const float *qkv, const float *z,
+                                 const float *alpha, const float *beta, float *out);
+
+/* Device-pointer forms: same meaning, q/gate/k/v/out (qkv/z/alpha/beta/out) are
+ * device pointers, layers/seq_ids/pos stay host arrays.  Asynchronous on
+ * mfc_stream(ctx); the per-sequence lengths advance at call time. */
+int mfc_full_attn_step_batched_dev(mfc_ctx *ctx, int32_t n, const int32_t *layers,
+                                   const int32_t *seq_ids, const int32_t *pos, const float *q,
+                                   const float *gate, const float *k, const float *v, float *out);
+int mfc_linear_attn_step_batched_dev(mfc_ctx *ctx, int32_t n, const int32_t *layers,
+                                     const int32_t *seq_ids, const float *qkv, const float *z,
+                                     const float *alpha, const float *beta, float *out);
+
+/* KV-sequence split (kv_world > 1): same as mfc_full_attn_step_batched_dev but
+ * the context attends over the positions it stores only and writes, per item,
+ * the un-normalised partial of every head: o_part [n][heads][head_dim],
+ * m_part [n][heads] (max scaled score, -inf if no row), l_part [n][heads]
+ * (sum of exp(s - m)).  The row at `pos` is appended by the context that owns
+ * it.  Gather the partials of all contexts (NCCL all-gather) and finish with
+ * mfc_lse_merge_gate_dev. */
+int mfc_full_attn_partial_batched_dev(mfc_ctx *ctx, int32_t n, const int32_t *layers,
+                                      const int32_t *seq_ids, const int32_t *pos, const float *q,
+                                      const float *k, const float *v, float *o_part,
+                                      float *m_part, float *l_part);
+/* out[i,h,:] = (sum_r e^{m_r-M} o_r / sum_r e^{m_r-M} l_r) * sigmoid(gate[i,h,:]),
+ * partials laid out [n_parts][n][heads][...]; gate may be NULL (no gate). */
+int mfc_lse_merge_gate_dev(mfc_ctx *ctx, int32_t n_parts, int32_t n, const float *o_parts,
+                           const float *m_parts, const float *l_parts, const float *gate,
+                           float *out);
+
+/* ------------------------------------------------------------------------
+ * Sequence state: mf_memory_clear / mf_memory_seq_rm / mf_memory_seq_pos_max
+ * (moeflux.h:88-104; crates/moeflux/src/riir/state.rs:417-473) with seq_id
+ * honoured.  seq_id = -1 applies to every sequence.
+ * ---------------------------------------------------------------------- */
+void mfc_memory_clear(mfc_ctx *ctx, int32_t seq_id);
+/* Truncate to [0, p0); GatedDeltaNet layers are reset to the empty state.
+ * p0 < 0 is 0; p1 < 0 or beyond the length means "to end".  Returns NONZERO on
+ * success, 0 on failure (moeflux.h:98). */
+int mfc_memory_seq_rm(mfc_ctx *ctx, int32_t seq_id, int32_t p0, int32_t p1);
+/* Largest length over the sequence's full-attention layers (state.rs:460-473:
+ * the reference returns the length, not length-1); -1 on NULL/bad seq_id. */
+int mfc_memory_seq_pos_max(mfc_ctx *ctx, int32_t seq_id);
+
+/* mf_state_size / mf_state_save / mf_state_load (moeflux.h:627-639;
+ * crates/moeflux/src/riir/state_snapshot.rs:195-663), per sequence, in the
+ * 'MFLX' wire format: KV rows fp32 [pos][kv_head][d], conv state [3][conv_dim],
+ * ssm state [v_head][value][key].  A bf16 cache is widened on save and rounded
+ * on load.  Only valid on a context with kv_world == 1.
+ * size: 0 on NULL.  save: bytes written or -1.  load: 0 or -1, and on -1 the
+ * state is unchanged (the buffer is validated before anything is written). */
+size_t mfc_state_size(const mfc_ctx *ctx, int32_t seq_id);
+long long mfc_state_save(mfc_ctx *ctx, int32_t seq_id, void *buf, size_t buf_len);
+int mfc_state_load(mfc_ctx *ctx, int32_t seq_id, const void *buf, size_t buf_len);
+
+/* Host-only helpers (no GPU needed).
+ * Block-cyclic KV split: rows of a sequence of whole length `len` that rank
+ * `rank` of `world` stores, and the local row of position `pos` (-1 when
+ * another rank owns it).  -1 on bad arguments. */
+int mfc_kv_local_len(int32_t len, int32_t rank, int32_t world, int32_t block);
+int mfc_kv_local_row(int32_t pos, int32_t rank, int32_t world, int32_t block);
+/* The checks mfc_state_load runs before it writes anything (header fields, per
+ * layer lengths, truncation; state_snapshot.rs:377-507) against a geometry.
+ * Returns the snapshot's size in bytes, or -1 (reason in mfc_last_error(NULL)). */
+long long mfc_snapshot_validate(const mfc_config *cfg, const void *buf, size_t buf_len);
+
+/* ------------------------------------------------------------------------
+ * Stateless parity hooks, GPU twins of the reference's diff-oracle hooks with
+ * the same argument meaning.  Each stages its host arguments on the device,
+ * runs the production kernel, and copies the result back.
+ * ---------------------------------------------------------------------- */
+
+/* mf_apply_rotary_emb (moeflux.h:151): q, k rotated in place at `pos`. */
+int mfc_apply_rotary_emb(mfc_ctx *ctx, int32_t pos, float *q, float *k);
+/* mf_sdpa_cpu (moeflux.h:179-182) on the GPU decode kernel: caches are
+ * [kv_len][num_kv_heads*head_dim] fp32 host rows (post-RoPE K). Stored in the
+ * context's kv_dtype before the kernel runs. */
+int mfc_sdpa(mfc_ctx *ctx, int32_t kv_len, const float *q, const float *q_gate,
+             const float *k_cache, const float *v_cache, float *out);
+/* One GatedDeltaNet step on caller-held state: conv_state [3][conv_dim] and
+ * ssm_state [v_heads][value_dim][key_dim] are read, advanced and written back
+ * (mf_conv1d_step_cpu + state shift, mf_gated_delta_recurrence_cpu,
+ * mf_rms_norm_gated_cpu in one call; moeflux.h:224-272). Uses the weights set
+ * for `layer`. */
+int mfc_linear_attn_step_stateless(mfc_ctx *ctx, int32_t layer, const float *qkv, const float *z,
+                                   const float *alpha, const float *beta, float *conv_state,
+                                   float *ssm_state, float *out);
+
+/* Tuning knobs (tests and sweeps): "gdn_rows" in {32,64,128} state rows per
+ * CTA; "gqa_target_ctas" CTAs a launch aims for when it picks the KV chunk
+ * length; "gqa_chunk" forces the chunk length (0 = automatic). */
+int mfc_set_tuning(mfc_ctx *ctx, const char *key, int value);
+
+/* Number of kernels this library has launched on the context so far. */
+long long mfc_launch_count(const mfc_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOEFLUX_CUDA_H */

@@ -1,0 +1,1164 @@
+// Context, state layer and C ABI of the attention backend.
+//
+// Owns what the reference keeps in `KvCache` / `LinearAttnState`
+// (crates/moeflux/src/riir/state.rs:37-74, 336-362) and in the GPU mirrors of
+// `LayerForwardBuffers` (crates/moeflux/src/riir/linear_attn_forward.rs:180-304),
+// laid out for the sm_100a kernels:
+//
+//   K, V cache   [kv slot = full layer * n_seqs + seq][kv head][row][256]  bf16 or fp32
+//                a (slot, head) is one contiguous run of rows, so a KV tile is a
+//                2-D TMA box and a chunk of a head is a plain row range;
+//   ssm state    [state slot = linear layer * n_seqs + seq][v head][128][128] fp32
+//                (the reference's own order, value-major, key fastest);
+//   conv ring    [state slot][4][conv_dim] fp32 (4-slot ring instead of a shifted
+//                3-row history, see gdn_decode.cu).
+//
+// One extra slot of each kind at the end serves the stateless parity hooks.
+// Lengths and ring positions live on the host; kernels receive them per item.
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/moeflux_cuda.h"
+#include "kernels.h"
+
+using namespace mfc;
+
+namespace {
+
+thread_local std::string g_open_error;
+
+constexpr uint32_t SNAPSHOT_MAGIC = 0x4D464C58u;  // 'MFLX', state_snapshot.rs:55-57
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace
+
+struct mfc_ctx {
+    mfc_config cfg;
+    int n_full = 0, n_lin = 0;
+    std::vector<int> layer_to_full, layer_to_lin;
+    int group = 0;
+    int cap_rows = 0;  // rows per (kv slot, kv head)
+    int conv_dim = 0;
+    int n_kv_slots = 0, n_state_slots = 0;
+    size_t kv_esize = 4;
+    cudaStream_t stream = nullptr;
+
+    void *k_cache = nullptr, *v_cache = nullptr;
+    CUtensorMap kmap, vmap;
+    float *ssm = nullptr, *conv = nullptr;
+    uint16_t *conv_w = nullptr, *dt_bias = nullptr, *norm_w = nullptr;
+    float *a_log = nullptr;
+    float *inv_freq = nullptr;
+
+    std::vector<int32_t> kv_len;     // [n_full * n_seqs + 1] whole-sequence lengths
+    std::vector<int64_t> conv_step;  // [n_state_slots]
+    std::vector<uint8_t> lin_weights_set;
+
+    GqaItem *d_gqa_items = nullptr;
+    GdnItem *d_gdn_items = nullptr;
+    std::vector<GqaItem> h_gqa_items;
+    std::vector<GdnItem> h_gdn_items;
+    float *sc_o = nullptr, *sc_m = nullptr, *sc_l = nullptr;
+    unsigned *tickets = nullptr, *status = nullptr;
+    int max_parts = 0;
+
+    // device staging for the host-pointer entry points (max_batch items)
+    float *st_q = nullptr, *st_gate = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
+    float *st_qkv = nullptr, *st_z = nullptr, *st_alpha = nullptr, *st_beta = nullptr, *st_gout = nullptr;
+    float *st_rows = nullptr;  // snapshot / hook staging, SNAP_ROWS wire rows
+    static constexpr int SNAP_ROWS = 4096;
+
+    int gdn_rows = 32;
+    int gqa_target_ctas = 148 * 2 * 4;
+    int gqa_forced_chunk = 0;
+    long long launches = 0;
+    std::string err;
+};
+
+namespace {
+
+bool fail(mfc_ctx *c, const std::string &msg) {
+    if (c) c->err = msg;
+    else g_open_error = msg;
+    return false;
+}
+#define CK(call)                                                                          \
+    do {                                                                                  \
+        cudaError_t e_ = (call);                                                          \
+        if (e_ != cudaSuccess) {                                                          \
+            fail(c, std::string(#call) + ": " + cudaGetErrorString(e_));                  \
+            return -1;                                                                    \
+        }                                                                                 \
+    } while (0)
+
+inline bool is_full_layer(const mfc_config &g, int i) { return (i + 1) % g.full_attn_interval == 0; }
+
+// rows of a sequence of whole length `len` stored by rank r of a block-cyclic split
+int local_len_of(int len, int r, int W, int B) {
+    if (W <= 1) return len;
+    const int full_blocks = len / B, rem = len % B;
+    int cnt = (full_blocks / W) * B;
+    const int part = full_blocks % W;
+    if (part > r) cnt += B;
+    else if (part == r) cnt += rem;
+    return cnt;
+}
+// local row of whole-sequence position p, or -1 when another rank owns it
+int local_row_of(int p, int r, int W, int B) {
+    if (W <= 1) return p;
+    const int blk = p / B;
+    if (blk % W != r) return -1;
+    return (blk / W) * B + p % B;
+}
+
+template <typename T>
+bool dalloc(mfc_ctx *c, T **p, size_t n, bool zero) {
+    if (n == 0) n = 1;
+    cudaError_t e = cudaMalloc((void **)p, n * sizeof(T));
+    if (e != cudaSuccess) return fail(c, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+    if (zero) {
+        e = cudaMemset(*p, 0, n * sizeof(T));
+        if (e != cudaSuccess) return fail(c, std::string("cudaMemset: ") + cudaGetErrorString(e));
+    }
+    return true;
+}
+
+bool make_tensor_map(mfc_ctx *c, CUtensorMap *map, void *base, uint64_t rows) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || !fn || qres != cudaDriverEntryPointSuccess)
+        return fail(c, "cuTensorMapEncodeTiled is not available from the driver");
+    const bool bf16 = c->cfg.kv_dtype == MFC_KV_BF16;
+    cuuint64_t dims[2] = {(cuuint64_t)HEAD_DIM, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(HEAD_DIM * c->kv_esize)};
+    cuuint32_t box[2] = {(cuuint32_t)(bf16 ? 64 : 32), (cuuint32_t)(bf16 ? KV_TILE : KV_TILE_F32)};  // 128-byte inner extent
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = ((EncodeTiledFn)fn)(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                     2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(c, "cuTensorMapEncodeTiled failed, code " + std::to_string((int)r));
+    return true;
+}
+
+void free_all(mfc_ctx *c) {
+    void *ptrs[] = {c->k_cache, c->v_cache, c->ssm, c->conv, c->conv_w, c->dt_bias, c->norm_w, c->a_log,
+                    c->inv_freq, c->d_gqa_items, c->d_gdn_items, c->sc_o, c->sc_m, c->sc_l, c->tickets,
+                    c->status, c->st_q, c->st_gate, c->st_k, c->st_v, c->st_out, c->st_qkv, c->st_z,
+                    c->st_alpha, c->st_beta, c->st_gout, c->st_rows};
+    for (void *p : ptrs)
+        if (p) cudaFree(p);
+    if (c->stream) cudaStreamDestroy(c->stream);
+}
+
+int check_status(mfc_ctx *c) {
+    unsigned st = 0;
+    CK(cudaMemcpyAsync(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    if (st) {
+        fail(c, "a kernel gave up on a bounded wait (device status " + std::to_string(st) +
+                    "); results of this context are no longer valid");
+        return -1;
+    }
+    return 0;
+}
+
+// ---- item list construction ---------------------------------------------------------
+
+// Chunk length for one launch: enough CTAs to fill the GPU several times over,
+// at most MAX_SPLITS chunks per (item, kv head).
+int plan_chunk(const mfc_ctx *c, long long total_rows, int max_len) {
+    if (c->gqa_forced_chunk > 0) {
+        int ch = (c->gqa_forced_chunk + KV_TILE - 1) / KV_TILE * KV_TILE;
+        const int min_ch = ((max_len + MAX_SPLITS - 1) / MAX_SPLITS + KV_TILE - 1) / KV_TILE * KV_TILE;
+        return ch > min_ch ? ch : min_ch;
+    }
+    long long ch = (total_rows + c->gqa_target_ctas - 1) / c->gqa_target_ctas;
+    if (ch < 256) ch = 256;
+    const long long min_ch = (max_len + MAX_SPLITS - 1) / MAX_SPLITS;
+    if (ch < min_ch) ch = min_ch;
+    ch = (ch + KV_TILE - 1) / KV_TILE * KV_TILE;
+    return (int)ch;
+}
+
+// Validates the items, advances the lengths and fills c->h_gqa_items.
+// kv_slot_override >= 0 selects the hook slot (no append, explicit length).
+int build_gqa_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq_ids,
+                    const int32_t *pos, int *total_ctas) {
+    const mfc_config &g = c->cfg;
+    if (n <= 0 || n > g.max_batch) {
+        fail(c, "item count must be in [1, max_batch]");
+        return -1;
+    }
+    if (!layers || !seq_ids || !pos) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    for (int i = 0; i < n; i++) {
+        const int l = layers[i], s = seq_ids[i];
+        if (l < 0 || l >= g.num_layers || !is_full_layer(g, l)) {
+            fail(c, "layer " + std::to_string(l) + " is not a full-attention layer");
+            return -1;
+        }
+        if (s < 0 || s >= g.n_seqs) {
+            fail(c, "seq_id out of range");
+            return -1;
+        }
+        const int slot = c->layer_to_full[l] * g.n_seqs + s;
+        if (pos[i] < 0 || pos[i] != c->kv_len[slot]) {
+            fail(c, "pos " + std::to_string(pos[i]) + " != current length " +
+                        std::to_string(c->kv_len[slot]) + " of layer " + std::to_string(l));
+            return -1;
+        }
+        if (pos[i] + 1 > g.max_seq) {
+            fail(c, "kv cache overflow");
+            return -1;
+        }
+    }
+    c->h_gqa_items.resize(n);
+    long long total_rows = 0;
+    int max_len = 0;
+    for (int i = 0; i < n; i++) {
+        GqaItem &it = c->h_gqa_items[i];
+        const int slot = c->layer_to_full[layers[i]] * g.n_seqs + seq_ids[i];
+        it.kv_slot = slot;
+        it.pos = pos[i];
+        it.local_len = local_len_of(pos[i] + 1, g.kv_rank, g.kv_world, g.kv_block);
+        it.append_row = local_row_of(pos[i], g.kv_rank, g.kv_world, g.kv_block);
+        it.in_idx = i;
+        total_rows += (long long)it.local_len * g.num_kv_heads;
+        if (it.local_len > max_len) max_len = it.local_len;
+    }
+    const int chunk = plan_chunk(c, total_rows, max_len);
+    int cta = 0;
+    for (int i = 0; i < n; i++) {
+        GqaItem &it = c->h_gqa_items[i];
+        it.chunk_len = chunk;
+        it.n_chunks = it.local_len > 0 ? (it.local_len + chunk - 1) / chunk : 1;
+        it.cta_begin = cta;
+        cta += it.n_chunks * g.num_kv_heads;
+    }
+    if (cta > c->max_parts) {
+        fail(c, "internal: split plan exceeds the scratch reserved at open");
+        return -1;
+    }
+    for (int i = 0; i < n; i++) c->kv_len[c->layer_to_full[layers[i]] * g.n_seqs + seq_ids[i]] += 1;
+    *total_ctas = cta;
+    return 0;
+}
+
+void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
+    const mfc_config &g = c->cfg;
+    memset(&p, 0, sizeof(p));
+    p.k_base = c->k_cache;
+    p.v_base = c->v_cache;
+    p.items = c->d_gqa_items;
+    p.n_items = n;
+    p.total_ctas = total_ctas;
+    p.sc_o = c->sc_o;
+    p.sc_m = c->sc_m;
+    p.sc_l = c->sc_l;
+    p.tickets = c->tickets;
+    p.inv_freq = c->inv_freq;
+    p.status = c->status;
+    p.H = g.num_attn_heads;
+    p.Hkv = g.num_kv_heads;
+    p.group = c->group;
+    p.rotary_dim = g.rotary_dim;
+    p.cap_rows = c->cap_rows;
+    p.scale = 1.0f / sqrtf((float)g.head_dim);
+}
+
+int launch_gqa(mfc_ctx *c, const GqaParams &p) {
+    CK(cudaMemcpyAsync(c->d_gqa_items, c->h_gqa_items.data(), sizeof(GqaItem) * p.n_items,
+                       cudaMemcpyHostToDevice, c->stream));
+    if (c->cfg.kv_dtype == MFC_KV_BF16) CK(launch_gqa_decode_bf16(c->kmap, c->vmap, p, c->stream));
+    else CK(launch_gqa_decode_f32(c->kmap, c->vmap, p, c->stream));
+    c->launches += 1;
+    return 0;
+}
+
+int build_gdn_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq_ids) {
+    const mfc_config &g = c->cfg;
+    if (n <= 0 || n > g.max_batch) {
+        fail(c, "item count must be in [1, max_batch]");
+        return -1;
+    }
+    if (!layers || !seq_ids) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    for (int i = 0; i < n; i++) {
+        const int l = layers[i], s = seq_ids[i];
+        if (l < 0 || l >= g.num_layers || is_full_layer(g, l)) {
+            fail(c, "layer " + std::to_string(l) + " is not a linear-attention layer");
+            return -1;
+        }
+        if (s < 0 || s >= g.n_seqs) {
+            fail(c, "seq_id out of range");
+            return -1;
+        }
+        if (!c->lin_weights_set[c->layer_to_lin[l]]) {
+            fail(c, "mfc_set_linear_weights was not called for layer " + std::to_string(l));
+            return -1;
+        }
+    }
+    c->h_gdn_items.resize(n);
+    for (int i = 0; i < n; i++) {
+        const int ll = c->layer_to_lin[layers[i]];
+        const int slot = ll * g.n_seqs + seq_ids[i];
+        GdnItem &it = c->h_gdn_items[i];
+        it.w_layer = ll;
+        it.state_idx = slot;
+        it.slot = (int)(c->conv_step[slot] & 3);
+        it.pad = 0;
+        c->conv_step[slot] += 1;
+    }
+    return 0;
+}
+
+int launch_gdn(mfc_ctx *c, int n, const float *qkv, const float *z, const float *alpha,
+               const float *beta, float *out) {
+    const mfc_config &g = c->cfg;
+    GdnParams p;
+    memset(&p, 0, sizeof(p));
+    p.ssm_base = c->ssm;
+    p.conv_base = c->conv;
+    p.conv_w = c->conv_w;
+    p.a_log = c->a_log;
+    p.dt_bias = c->dt_bias;
+    p.norm_w = c->norm_w;
+    p.items = c->d_gdn_items;
+    p.qkv = qkv;
+    p.z = z;
+    p.alpha = alpha;
+    p.beta = beta;
+    p.out = out;
+    p.n_items = n;
+    p.Hv = g.linear_num_v_heads;
+    p.Hk = g.linear_num_k_heads;
+    p.conv_dim = c->conv_dim;
+    p.eps = g.rms_norm_eps;
+    CK(cudaMemcpyAsync(c->d_gdn_items, c->h_gdn_items.data(), sizeof(GdnItem) * n,
+                       cudaMemcpyHostToDevice, c->stream));
+    CK(launch_gdn_decode(p, c->gdn_rows, c->stream));
+    c->launches += 1;
+    return 0;
+}
+
+// Validation of an 'MFLX' snapshot against a geometry without touching any
+// state: header (crates/moeflux/src/riir/state_snapshot.rs:377-440) and the
+// body walk (:445-507).  Returns the bytes the snapshot occupies, or -1 with
+// the reason in `why`.
+long long snapshot_preflight(const mfc_config &g, const uint8_t *in, size_t buf_len, size_t *hbytes_out,
+                             std::string &why) {
+    const int conv_dim = 2 * g.linear_num_k_heads * GDN_DIM + g.linear_num_v_heads * GDN_DIM;
+    // header, crates/moeflux/src/riir/state_snapshot.rs:377-440
+    if (buf_len < 8) {
+        why = ("snapshot truncated: no header");
+        return -1;
+    }
+    uint32_t w[10] = {0};
+    memcpy(w, in, 8);
+    if (w[0] != SNAPSHOT_MAGIC) {
+        why = ("snapshot magic mismatch");
+        return -1;
+    }
+    if (w[1] != 1 && w[1] != 2) {
+        why = ("snapshot version " + std::to_string(w[1]) + " not understood");
+        return -1;
+    }
+    const size_t hbytes = (w[1] == 1 ? 8 : 10) * sizeof(uint32_t);
+    *hbytes_out = hbytes;
+    if (buf_len < hbytes) {
+        why = ("snapshot truncated: short header");
+        return -1;
+    }
+    memcpy(w, in, hbytes);
+    const uint32_t la_conv = (uint32_t)((CONV_TAPS - 1) * conv_dim * sizeof(float));
+    const uint32_t la_ssm = (uint32_t)((size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM * sizeof(float));
+    const uint32_t want[10] = {SNAPSHOT_MAGIC, w[1], (uint32_t)g.num_layers, (uint32_t)g.full_attn_interval,
+                               (uint32_t)g.num_kv_heads, (uint32_t)g.head_dim, la_conv, la_ssm, 0u, 0u};
+    static const char *names[10] = {"magic", "version", "num_layers", "full_attn_interval", "num_kv_heads",
+                                    "head_dim", "linear_conv_bytes", "linear_ssm_bytes", "kv_lora_rank",
+                                    "qk_rope_head_dim"};
+    for (size_t i = 2; i < hbytes / 4; i++)
+        if (w[i] != want[i]) {
+            why = (std::string("snapshot shape mismatch on field '") + names[i] + "'");
+            return -1;
+        }
+    // preflight: walk the body without touching any state (state_snapshot.rs:445-507)
+    const size_t fa_stride = (size_t)g.num_kv_heads * HEAD_DIM * sizeof(float);
+    {
+        size_t q = hbytes;
+        for (int i = 0; i < g.num_layers; i++) {
+            if (is_full_layer(g, i)) {
+                if (buf_len - q < 4) {
+                    why = ("snapshot truncated at layer " + std::to_string(i));
+                    return -1;
+                }
+                int32_t len;
+                memcpy(&len, in + q, 4);
+                q += 4;
+                if (len < 0) {
+                    why = ("snapshot layer " + std::to_string(i) + " has a negative KV length");
+                    return -1;
+                }
+                if (len > g.max_seq) {
+                    why = ("snapshot layer " + std::to_string(i) + " KV length exceeds max_seq");
+                    return -1;
+                }
+                const size_t bytes = 2 * (size_t)len * fa_stride;
+                if (buf_len - q < bytes) {
+                    why = ("snapshot truncated at layer " + std::to_string(i));
+                    return -1;
+                }
+                q += bytes;
+            } else {
+                const size_t bytes = (size_t)la_conv + la_ssm;
+                if (buf_len - q < bytes) {
+                    why = ("snapshot truncated at layer " + std::to_string(i));
+                    return -1;
+                }
+                q += bytes;
+            }
+        }
+        return (long long)q;
+    }
+}
+
+void reset_state_slot(mfc_ctx *c, int slot) {
+    const size_t ssm_elems = (size_t)c->cfg.linear_num_v_heads * GDN_DIM * GDN_DIM;
+    cudaMemsetAsync(c->ssm + (size_t)slot * ssm_elems, 0, ssm_elems * sizeof(float), c->stream);
+    cudaMemsetAsync(c->conv + (size_t)slot * CONV_TAPS * c->conv_dim, 0,
+                    sizeof(float) * CONV_TAPS * c->conv_dim, c->stream);
+    c->conv_step[slot] = 0;
+}
+
+}  // namespace
+
+// =====================================================================================
+#pragma GCC visibility push(default)
+extern "C" {
+
+void mfc_default_config(mfc_config *cfg) {
+    if (!cfg) return;
+    memset(cfg, 0, sizeof(*cfg));
+    cfg->num_layers = 60;
+    cfg->full_attn_interval = 4;
+    cfg->num_attn_heads = 32;
+    cfg->num_kv_heads = 2;
+    cfg->head_dim = 256;
+    cfg->rotary_dim = 64;
+    cfg->rope_theta = 1.0e7f;
+    cfg->linear_num_v_heads = 64;
+    cfg->linear_num_k_heads = 16;
+    cfg->linear_key_dim = 128;
+    cfg->linear_value_dim = 128;
+    cfg->conv_kernel_size = 4;
+    cfg->rms_norm_eps = 1e-6f;
+    cfg->kv_dtype = MFC_KV_F32;
+    cfg->max_seq = 8192;
+    cfg->n_seqs = 1;
+    cfg->device = 0;
+    cfg->kv_rank = 0;
+    cfg->kv_world = 1;
+    cfg->kv_block = 256;
+    cfg->max_batch = 60;
+    cfg->snapshot_version = 1;
+}
+
+const char *mfc_last_error(const mfc_ctx *ctx) { return ctx ? ctx->err.c_str() : g_open_error.c_str(); }
+
+mfc_ctx *mfc_open(const mfc_config *cfg) {
+    mfc_ctx *c = nullptr;
+    if (!cfg) {
+        fail(c, "NULL config");
+        return nullptr;
+    }
+    const mfc_config &g = *cfg;
+    // invariants of the geometry (crates/moeflux/src/riir/variants.rs:546-610) and of the kernels
+    if (g.num_layers <= 0 || g.full_attn_interval <= 0 || g.num_attn_heads <= 0 || g.num_kv_heads <= 0 ||
+        g.num_attn_heads % g.num_kv_heads != 0 || g.num_attn_heads / g.num_kv_heads > 16) {
+        fail(c, "bad head geometry: need num_attn_heads % num_kv_heads == 0 and a group of at most 16");
+        return nullptr;
+    }
+    if (g.head_dim != HEAD_DIM || g.linear_key_dim != GDN_DIM || g.linear_value_dim != GDN_DIM ||
+        g.conv_kernel_size != CONV_TAPS) {
+        fail(c, "unsupported dims: head_dim must be 256, linear key/value dim 128, conv kernel 4");
+        return nullptr;
+    }
+    if (g.rotary_dim < 0 || g.rotary_dim > HEAD_DIM || g.rotary_dim % 4 != 0) {
+        fail(c, "rotary_dim must be a multiple of 4 in [0, 256]");
+        return nullptr;
+    }
+    if (g.linear_num_v_heads <= 0 || g.linear_num_k_heads <= 0 ||
+        g.linear_num_v_heads % g.linear_num_k_heads != 0) {
+        fail(c, "linear_num_v_heads must be a positive multiple of linear_num_k_heads");
+        return nullptr;
+    }
+    if (g.kv_dtype != MFC_KV_F32 && g.kv_dtype != MFC_KV_BF16) {
+        fail(c, "kv_dtype must be MFC_KV_F32 or MFC_KV_BF16");
+        return nullptr;
+    }
+    if (g.max_seq <= 0 || g.n_seqs <= 0 || g.max_batch <= 0) {
+        fail(c, "max_seq, n_seqs and max_batch must be positive");
+        return nullptr;
+    }
+    if (g.kv_world < 1 || g.kv_rank < 0 || g.kv_rank >= g.kv_world || g.kv_block <= 0 ||
+        g.kv_block % KV_TILE != 0) {
+        fail(c, "bad KV split: need 0 <= kv_rank < kv_world and kv_block a positive multiple of 32");
+        return nullptr;
+    }
+    if (g.snapshot_version != 1 && g.snapshot_version != 2) {
+        fail(c, "snapshot_version must be 1 or 2");
+        return nullptr;
+    }
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
+        cudaGetLastError();
+        fail(c, "no CUDA device is usable; this library has no CPU path");
+        return nullptr;
+    }
+    if (g.device < 0 || g.device >= ndev || cudaSetDevice(g.device) != cudaSuccess) {
+        fail(c, "cannot select CUDA device " + std::to_string(g.device));
+        return nullptr;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, g.device) != cudaSuccess || prop.major != 10) {
+        fail(c, "device is not sm_100 (compute capability 10.x); the kernels are built for sm_100a only");
+        return nullptr;
+    }
+
+    c = new mfc_ctx();
+    c->cfg = g;
+    c->group = g.num_attn_heads / g.num_kv_heads;
+    c->kv_esize = g.kv_dtype == MFC_KV_BF16 ? 2 : 4;
+    c->conv_dim = 2 * g.linear_num_k_heads * GDN_DIM + g.linear_num_v_heads * GDN_DIM;
+    c->layer_to_full.assign(g.num_layers, -1);
+    c->layer_to_lin.assign(g.num_layers, -1);
+    for (int i = 0; i < g.num_layers; i++) {
+        if (is_full_layer(g, i)) c->layer_to_full[i] = c->n_full++;
+        else c->layer_to_lin[i] = c->n_lin++;
+    }
+    {
+        const int blocks = (g.max_seq + g.kv_block - 1) / g.kv_block;
+        const int my_blocks = (blocks + g.kv_world - 1) / g.kv_world;
+        c->cap_rows = g.kv_world > 1 ? my_blocks * g.kv_block : (g.max_seq + KV_TILE - 1) / KV_TILE * KV_TILE;
+    }
+    c->n_kv_slots = c->n_full * g.n_seqs + 1;
+    c->n_state_slots = c->n_lin * g.n_seqs + 1;
+    c->kv_len.assign(c->n_kv_slots, 0);
+    c->conv_step.assign(c->n_state_slots, 0);
+    c->lin_weights_set.assign(c->n_lin > 0 ? c->n_lin : 1, 0);
+    if (const char *e = getenv("MFC_GDN_ROWS")) c->gdn_rows = atoi(e);
+    if (const char *e = getenv("MFC_GQA_TARGET_CTAS")) c->gqa_target_ctas = atoi(e);
+    if (c->gdn_rows != 32 && c->gdn_rows != 64 && c->gdn_rows != 128) c->gdn_rows = 32;
+    if (c->gqa_target_ctas < 1) c->gqa_target_ctas = 1;
+    if (c->gqa_target_ctas > 8192) c->gqa_target_ctas = 8192;
+    c->max_parts = 8192 + g.max_batch * g.num_kv_heads;
+
+    bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess;
+    if (!ok) fail(c, "cudaStreamCreate failed");
+    const uint64_t kv_rows = (uint64_t)c->n_kv_slots * g.num_kv_heads * c->cap_rows;
+    if (ok && kv_rows >= (1ull << 32)) ok = fail(c, "KV cache has more rows than a tensor map can address");
+    const size_t kv_bytes = (size_t)kv_rows * HEAD_DIM * c->kv_esize;
+    const size_t ssm_elems = (size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM;
+    const size_t qd = (size_t)g.num_attn_heads * HEAD_DIM, kvd = (size_t)g.num_kv_heads * HEAD_DIM;
+    const size_t vd = (size_t)g.linear_num_v_heads * GDN_DIM;
+    const size_t mb = (size_t)g.max_batch;
+    ok = ok && dalloc(c, (uint8_t **)&c->k_cache, kv_bytes, true) && dalloc(c, (uint8_t **)&c->v_cache, kv_bytes, true) &&
+         dalloc(c, &c->ssm, (size_t)c->n_state_slots * ssm_elems, true) &&
+         dalloc(c, &c->conv, (size_t)c->n_state_slots * CONV_TAPS * c->conv_dim, true) &&
+         dalloc(c, &c->conv_w, (size_t)(c->n_lin + 1) * c->conv_dim * 4, true) &&
+         dalloc(c, &c->a_log, (size_t)(c->n_lin + 1) * g.linear_num_v_heads, true) &&
+         dalloc(c, &c->dt_bias, (size_t)(c->n_lin + 1) * g.linear_num_v_heads, true) &&
+         dalloc(c, &c->norm_w, (size_t)(c->n_lin + 1) * GDN_DIM, true) &&
+         dalloc(c, &c->inv_freq, (size_t)HEAD_DIM / 2, true) && dalloc(c, &c->d_gqa_items, mb, false) &&
+         dalloc(c, &c->d_gdn_items, mb, false) &&
+         dalloc(c, &c->sc_o, (size_t)c->max_parts * 16 * HEAD_DIM, false) &&
+         dalloc(c, &c->sc_m, (size_t)c->max_parts * 16, false) &&
+         dalloc(c, &c->sc_l, (size_t)c->max_parts * 16, false) &&
+         dalloc(c, &c->tickets, mb * g.num_kv_heads, true) && dalloc(c, &c->status, (size_t)1, true) &&
+         dalloc(c, &c->st_q, mb * qd, false) && dalloc(c, &c->st_gate, mb * qd, false) &&
+         dalloc(c, &c->st_k, mb * kvd, false) && dalloc(c, &c->st_v, mb * kvd, false) &&
+         dalloc(c, &c->st_out, mb * qd, false) && dalloc(c, &c->st_qkv, mb * c->conv_dim, false) &&
+         dalloc(c, &c->st_z, mb * vd, false) && dalloc(c, &c->st_alpha, mb * g.linear_num_v_heads, false) &&
+         dalloc(c, &c->st_beta, mb * g.linear_num_v_heads, false) && dalloc(c, &c->st_gout, mb * vd, false) &&
+         dalloc(c, &c->st_rows, (size_t)mfc_ctx::SNAP_ROWS * kvd, false);
+    if (ok) {
+        // the host's libm evaluates the frequencies, exactly as the reference does
+        // (crates/moeflux/src/riir/rope.rs:99-101); the device only multiplies by pos
+        std::vector<float> f(HEAD_DIM / 2, 0.0f);
+        const float rdim_f = (float)g.rotary_dim;
+        for (int i = 0; i < g.rotary_dim / 2; i++) f[i] = 1.0f / powf(g.rope_theta, (float)(2 * i) / rdim_f);
+        ok = cudaMemcpy(c->inv_freq, f.data(), sizeof(float) * f.size(), cudaMemcpyHostToDevice) == cudaSuccess;
+        if (!ok) fail(c, "cudaMemcpy(inv_freq) failed");
+    }
+    ok = ok && make_tensor_map(c, &c->kmap, c->k_cache, kv_rows) && make_tensor_map(c, &c->vmap, c->v_cache, kv_rows);
+    if (ok && (gqa_decode_configure() != cudaSuccess || gqa_decode_f32_configure() != cudaSuccess)) ok = fail(c, "cannot opt in to the kernels' shared memory size");
+    if (!ok) {
+        g_open_error = c->err;
+        free_all(c);
+        delete c;
+        cudaGetLastError();
+        return nullptr;
+    }
+    return c;
+}
+
+void mfc_free(mfc_ctx *c) {
+    if (!c) return;
+    cudaSetDevice(c->cfg.device);
+    cudaStreamSynchronize(c->stream);
+    free_all(c);
+    delete c;
+}
+
+int mfc_get_config(const mfc_ctx *c, mfc_config *out) {
+    if (!c || !out) return -1;
+    *out = c->cfg;
+    return 0;
+}
+
+void *mfc_stream(mfc_ctx *c) { return c ? (void *)c->stream : nullptr; }
+
+int mfc_synchronize(mfc_ctx *c) {
+    if (!c) return -1;
+    cudaSetDevice(c->cfg.device);
+    return check_status(c);
+}
+
+long long mfc_launch_count(const mfc_ctx *c) { return c ? c->launches : 0; }
+
+int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
+    if (!c || !key) return -1;
+    if (!strcmp(key, "gdn_rows")) {
+        if (value != 32 && value != 64 && value != 128) return -1;
+        c->gdn_rows = value;
+    } else if (!strcmp(key, "gqa_target_ctas")) {
+        if (value < 1 || value > 8192) return -1;
+        c->gqa_target_ctas = value;
+    } else if (!strcmp(key, "gqa_chunk")) {
+        if (value < 0) return -1;
+        c->gqa_forced_chunk = value;
+    } else {
+        return -1;
+    }
+    return 0;
+}
+
+int mfc_set_linear_weights(mfc_ctx *c, int32_t layer, const uint16_t *conv_w, const float *a_log,
+                           const uint16_t *dt_bias, const uint16_t *norm_w) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    // layer == -1 addresses the weight row used by the stateless hook slot only
+    if (!conv_w || !a_log || !dt_bias) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (layer < 0 || layer >= g.num_layers || is_full_layer(g, layer)) {
+        fail(c, "layer " + std::to_string(layer) + " is not a linear-attention layer");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    const int ll = c->layer_to_lin[layer];
+    CK(cudaMemcpyAsync(c->conv_w + (size_t)ll * c->conv_dim * 4, conv_w, sizeof(uint16_t) * c->conv_dim * 4,
+                       cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->a_log + (size_t)ll * g.linear_num_v_heads, a_log, sizeof(float) * g.linear_num_v_heads,
+                       cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->dt_bias + (size_t)ll * g.linear_num_v_heads, dt_bias,
+                       sizeof(uint16_t) * g.linear_num_v_heads, cudaMemcpyHostToDevice, c->stream));
+    if (norm_w)
+        CK(cudaMemcpyAsync(c->norm_w + (size_t)ll * GDN_DIM, norm_w, sizeof(uint16_t) * GDN_DIM,
+                           cudaMemcpyHostToDevice, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    c->lin_weights_set[ll] = norm_w ? 2 : 1;
+    return 0;
+}
+
+// ---------------------------------------------------------------- full attention
+
+int mfc_full_attn_step_batched_dev(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                   const int32_t *pos, const float *q, const float *gate, const float *k,
+                                   const float *v, float *out) {
+    if (!c) return -1;
+    if (!q || !gate || !k || !v || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (c->cfg.kv_world != 1) {
+        fail(c, "this context holds a share of a KV split: use mfc_full_attn_partial_batched_dev");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    int total = 0;
+    if (build_gqa_items(c, n, layers, seq_ids, pos, &total)) return -1;
+    GqaParams p;
+    fill_gqa_params(c, p, n, total);
+    p.q = q;
+    p.gate = gate;
+    p.k = k;
+    p.v = v;
+    p.out = out;
+    p.partial_mode = 0;
+    return launch_gqa(c, p);
+}
+
+int mfc_full_attn_partial_batched_dev(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                      const int32_t *pos, const float *q, const float *k, const float *v,
+                                      float *o_part, float *m_part, float *l_part) {
+    if (!c) return -1;
+    if (!q || !k || !v || !o_part || !m_part || !l_part) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    int total = 0;
+    if (build_gqa_items(c, n, layers, seq_ids, pos, &total)) return -1;
+    GqaParams p;
+    fill_gqa_params(c, p, n, total);
+    p.q = q;
+    p.gate = nullptr;
+    p.k = k;
+    p.v = v;
+    p.po = o_part;
+    p.pm = m_part;
+    p.pl = l_part;
+    p.partial_mode = 1;
+    return launch_gqa(c, p);
+}
+
+int mfc_lse_merge_gate_dev(mfc_ctx *c, int32_t n_parts, int32_t n, const float *o_parts, const float *m_parts,
+                           const float *l_parts, const float *gate, float *out) {
+    if (!c) return -1;
+    if (n_parts <= 0 || n <= 0 || !o_parts || !m_parts || !l_parts || !out) {
+        fail(c, "bad argument");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    CK(launch_lse_merge_gate(n_parts, n, c->cfg.num_attn_heads, o_parts, m_parts, l_parts, gate, out, c->stream));
+    c->launches += 1;
+    return 0;
+}
+
+int mfc_full_attn_step_batched(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                               const int32_t *pos, const float *q, const float *gate, const float *k,
+                               const float *v, float *out) {
+    if (!c) return -1;
+    if (!q || !gate || !k || !v || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (n <= 0 || n > c->cfg.max_batch) {
+        fail(c, "item count must be in [1, max_batch]");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    const size_t qd = sizeof(float) * c->cfg.num_attn_heads * HEAD_DIM * (size_t)n;
+    const size_t kd = sizeof(float) * c->cfg.num_kv_heads * HEAD_DIM * (size_t)n;
+    CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_gate, gate, qd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_k, k, kd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_v, v, kd, cudaMemcpyHostToDevice, c->stream));
+    if (mfc_full_attn_step_batched_dev(c, n, layers, seq_ids, pos, c->st_q, c->st_gate, c->st_k, c->st_v, c->st_out))
+        return -1;
+    CK(cudaMemcpyAsync(out, c->st_out, qd, cudaMemcpyDeviceToHost, c->stream));
+    return check_status(c);
+}
+
+int mfc_full_attn_step(mfc_ctx *c, int32_t layer, int32_t seq_id, int32_t pos, const float *q, const float *gate,
+                       const float *k, const float *v, float *out) {
+    return mfc_full_attn_step_batched(c, 1, &layer, &seq_id, &pos, q, gate, k, v, out);
+}
+
+// ---------------------------------------------------------------- GatedDeltaNet
+
+int mfc_linear_attn_step_batched_dev(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                     const float *qkv, const float *z, const float *alpha, const float *beta,
+                                     float *out) {
+    if (!c) return -1;
+    if (!qkv || !alpha || !beta || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    if (build_gdn_items(c, n, layers, seq_ids)) return -1;
+    if (z) {
+        for (int i = 0; i < n; i++)
+            if (c->lin_weights_set[c->h_gdn_items[i].w_layer] != 2) {
+                fail(c, "z given but no norm weight was set for layer " + std::to_string(layers[i]));
+                return -1;
+            }
+    }
+    return launch_gdn(c, n, qkv, z, alpha, beta, out);
+}
+
+int mfc_linear_attn_step_batched(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                 const float *qkv, const float *z, const float *alpha, const float *beta,
+                                 float *out) {
+    if (!c) return -1;
+    if (!qkv || !alpha || !beta || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (n <= 0 || n > c->cfg.max_batch) {
+        fail(c, "item count must be in [1, max_batch]");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    const mfc_config &g = c->cfg;
+    const size_t vd = sizeof(float) * g.linear_num_v_heads * GDN_DIM * (size_t)n;
+    const size_t hd = sizeof(float) * g.linear_num_v_heads * (size_t)n;
+    CK(cudaMemcpyAsync(c->st_qkv, qkv, sizeof(float) * c->conv_dim * (size_t)n, cudaMemcpyHostToDevice, c->stream));
+    if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, c->stream));
+    if (mfc_linear_attn_step_batched_dev(c, n, layers, seq_ids, c->st_qkv, z ? c->st_z : nullptr, c->st_alpha,
+                                         c->st_beta, c->st_gout))
+        return -1;
+    CK(cudaMemcpyAsync(out, c->st_gout, vd, cudaMemcpyDeviceToHost, c->stream));
+    return check_status(c);
+}
+
+int mfc_linear_attn_step(mfc_ctx *c, int32_t layer, int32_t seq_id, const float *qkv, const float *z,
+                         const float *alpha, const float *beta, float *out) {
+    return mfc_linear_attn_step_batched(c, 1, &layer, &seq_id, qkv, z, alpha, beta, out);
+}
+
+// ---------------------------------------------------------------- sequence state
+
+void mfc_memory_clear(mfc_ctx *c, int32_t seq_id) {
+    if (!c) return;
+    mfc_memory_seq_rm(c, seq_id, 0, -1);
+}
+
+int mfc_memory_seq_rm(mfc_ctx *c, int32_t seq_id, int32_t p0, int32_t p1) {
+    if (!c) return 0;
+    const mfc_config &g = c->cfg;
+    if (seq_id < -1 || seq_id >= g.n_seqs) return 0;
+    cudaSetDevice(g.device);
+    const int s0 = seq_id < 0 ? 0 : seq_id, s1 = seq_id < 0 ? g.n_seqs : seq_id + 1;
+    const int new_len = p0 < 0 ? 0 : p0;
+    for (int s = s0; s < s1; s++) {
+        // crates/moeflux/src/riir/state.rs:431-458
+        for (int f = 0; f < c->n_full; f++) {
+            int32_t &len = c->kv_len[f * g.n_seqs + s];
+            const int eff_end = (p1 < 0 || p1 > len) ? len : p1;
+            const int to = new_len < eff_end ? new_len : eff_end;
+            if (to <= len) len = to;
+        }
+        for (int l = 0; l < c->n_lin; l++) reset_state_slot(c, l * g.n_seqs + s);
+    }
+    return cudaStreamSynchronize(c->stream) == cudaSuccess ? 1 : 0;
+}
+
+int mfc_memory_seq_pos_max(mfc_ctx *c, int32_t seq_id) {
+    if (!c || seq_id < 0 || seq_id >= c->cfg.n_seqs) return -1;
+    int mx = -1;  // stays -1 only when the model has no full-attention layer (state.rs:460-473)
+    for (int f = 0; f < c->n_full; f++) {
+        const int len = c->kv_len[f * c->cfg.n_seqs + seq_id];
+        if (len > mx) mx = len;
+    }
+    return mx;
+}
+
+// ---------------------------------------------------------------- snapshots ('MFLX')
+
+size_t mfc_state_size(const mfc_ctx *c, int32_t seq_id) {
+    if (!c || seq_id < 0 || seq_id >= c->cfg.n_seqs) return 0;
+    const mfc_config &g = c->cfg;
+    const size_t header = (g.snapshot_version == 1 ? 8 : 10) * sizeof(uint32_t);
+    const size_t fa_stride = (size_t)g.num_kv_heads * HEAD_DIM * sizeof(float);
+    const size_t la_conv = (size_t)(CONV_TAPS - 1) * c->conv_dim * sizeof(float);
+    const size_t la_ssm = (size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM * sizeof(float);
+    size_t nbytes = header;
+    for (int i = 0; i < g.num_layers; i++) {
+        if (is_full_layer(g, i)) nbytes += 4 + 2 * (size_t)c->kv_len[c->layer_to_full[i] * g.n_seqs + seq_id] * fa_stride;
+        else nbytes += la_conv + la_ssm;
+    }
+    return nbytes;
+}
+
+long long mfc_state_save(mfc_ctx *c, int32_t seq_id, void *buf, size_t buf_len) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (!buf || seq_id < 0 || seq_id >= g.n_seqs) {
+        fail(c, "bad argument");
+        return -1;
+    }
+    if (g.kv_world != 1) {
+        fail(c, "snapshots need the whole cache in one context (kv_world == 1)");
+        return -1;
+    }
+    const size_t need = mfc_state_size(c, seq_id);
+    if (buf_len < need) {
+        fail(c, "buffer too small: need " + std::to_string(need) + " bytes");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    uint8_t *out = (uint8_t *)buf;
+    size_t off = 0;
+    const uint32_t la_conv = (uint32_t)((CONV_TAPS - 1) * c->conv_dim * sizeof(float));
+    const uint32_t la_ssm = (uint32_t)((size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM * sizeof(float));
+    const uint32_t header[10] = {SNAPSHOT_MAGIC, (uint32_t)g.snapshot_version, (uint32_t)g.num_layers,
+                                 (uint32_t)g.full_attn_interval, (uint32_t)g.num_kv_heads, (uint32_t)g.head_dim,
+                                 la_conv, la_ssm, 0u, 0u};  // words 8, 9: kv_lora_rank, qk_rope_head_dim (0 for GQA)
+    const size_t hbytes = (g.snapshot_version == 1 ? 8 : 10) * sizeof(uint32_t);
+    memcpy(out, header, hbytes);
+    off += hbytes;
+    const size_t kvd = (size_t)g.num_kv_heads * HEAD_DIM;
+    for (int i = 0; i < g.num_layers; i++) {
+        if (is_full_layer(g, i)) {
+            const int slot = c->layer_to_full[i] * g.n_seqs + seq_id;
+            const int32_t len = c->kv_len[slot];
+            memcpy(out + off, &len, 4);
+            off += 4;
+            for (int pass = 0; pass < 2; pass++) {
+                const uint8_t *cache = (const uint8_t *)(pass == 0 ? c->k_cache : c->v_cache) +
+                                       (size_t)slot * g.num_kv_heads * c->cap_rows * HEAD_DIM * c->kv_esize;
+                for (int r0 = 0; r0 < len; r0 += mfc_ctx::SNAP_ROWS) {
+                    const int nr = len - r0 < mfc_ctx::SNAP_ROWS ? len - r0 : mfc_ctx::SNAP_ROWS;
+                    CK(launch_kv_unpack(cache + (size_t)r0 * HEAD_DIM * c->kv_esize, c->st_rows, nr, g.num_kv_heads,
+                                        c->cap_rows, g.kv_dtype == MFC_KV_BF16, c->stream));
+                    c->launches += 1;
+                    CK(cudaMemcpyAsync(out + off, c->st_rows, sizeof(float) * kvd * nr, cudaMemcpyDeviceToHost,
+                                       c->stream));
+                    CK(cudaStreamSynchronize(c->stream));
+                    off += sizeof(float) * kvd * nr;
+                }
+            }
+        } else {
+            const int slot = c->layer_to_lin[i] * g.n_seqs + seq_id;
+            const float *ring = c->conv + (size_t)slot * CONV_TAPS * c->conv_dim;
+            const int t = (int)(c->conv_step[slot] & 3);
+            for (int k = 0; k < CONV_TAPS - 1; k++) {  // oldest first: slots t+1, t+2, t+3
+                CK(cudaMemcpyAsync(out + off, ring + (size_t)((t + 1 + k) & 3) * c->conv_dim,
+                                   sizeof(float) * c->conv_dim, cudaMemcpyDeviceToHost, c->stream));
+                off += sizeof(float) * c->conv_dim;
+            }
+            CK(cudaMemcpyAsync(out + off, c->ssm + (size_t)slot * (la_ssm / 4), la_ssm, cudaMemcpyDeviceToHost,
+                               c->stream));
+            off += la_ssm;
+        }
+    }
+    CK(cudaStreamSynchronize(c->stream));
+    return (long long)off;
+}
+
+int mfc_state_load(mfc_ctx *c, int32_t seq_id, const void *buf, size_t buf_len) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (!buf || seq_id < 0 || seq_id >= g.n_seqs) {
+        fail(c, "bad argument");
+        return -1;
+    }
+    if (g.kv_world != 1) {
+        fail(c, "snapshots need the whole cache in one context (kv_world == 1)");
+        return -1;
+    }
+    const uint8_t *in = (const uint8_t *)buf;
+    size_t hbytes = 0;
+    std::string why;
+    if (snapshot_preflight(g, in, buf_len, &hbytes, why) < 0) {
+        fail(c, why);
+        return -1;
+    }
+    const uint32_t la_conv = (uint32_t)((CONV_TAPS - 1) * c->conv_dim * sizeof(float));
+    const uint32_t la_ssm = (uint32_t)((size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM * sizeof(float));
+    // restore
+    cudaSetDevice(g.device);
+    size_t off = hbytes;
+    const size_t kvd = (size_t)g.num_kv_heads * HEAD_DIM;
+    for (int i = 0; i < g.num_layers; i++) {
+        if (is_full_layer(g, i)) {
+            const int slot = c->layer_to_full[i] * g.n_seqs + seq_id;
+            int32_t len;
+            memcpy(&len, in + off, 4);
+            off += 4;
+            for (int pass = 0; pass < 2; pass++) {
+                uint8_t *cache = (uint8_t *)(pass == 0 ? c->k_cache : c->v_cache) +
+                                 (size_t)slot * g.num_kv_heads * c->cap_rows * HEAD_DIM * c->kv_esize;
+                for (int r0 = 0; r0 < len; r0 += mfc_ctx::SNAP_ROWS) {
+                    const int nr = len - r0 < mfc_ctx::SNAP_ROWS ? len - r0 : mfc_ctx::SNAP_ROWS;
+                    CK(cudaMemcpyAsync(c->st_rows, in + off, sizeof(float) * kvd * nr, cudaMemcpyHostToDevice,
+                                       c->stream));
+                    CK(launch_kv_pack(c->st_rows, cache, nr, g.num_kv_heads, c->cap_rows,
+                                      g.kv_dtype == MFC_KV_BF16, r0, c->stream));
+                    c->launches += 1;
+                    CK(cudaStreamSynchronize(c->stream));
+                    off += sizeof(float) * kvd * nr;
+                }
+            }
+            c->kv_len[slot] = len;
+        } else {
+            const int slot = c->layer_to_lin[i] * g.n_seqs + seq_id;
+            float *ring = c->conv + (size_t)slot * CONV_TAPS * c->conv_dim;
+            // history rows go to slots 1..3; the next step writes slot 0
+            CK(cudaMemsetAsync(ring, 0, sizeof(float) * c->conv_dim, c->stream));
+            CK(cudaMemcpyAsync(ring + c->conv_dim, in + off, la_conv, cudaMemcpyHostToDevice, c->stream));
+            off += la_conv;
+            CK(cudaMemcpyAsync(c->ssm + (size_t)slot * (la_ssm / 4), in + off, la_ssm, cudaMemcpyHostToDevice,
+                               c->stream));
+            off += la_ssm;
+            c->conv_step[slot] = 0;
+        }
+    }
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+// ---------------------------------------------------------------- host-only helpers
+
+int mfc_kv_local_len(int32_t len, int32_t rank, int32_t world, int32_t block) {
+    if (len < 0 || world < 1 || rank < 0 || rank >= world || block <= 0) return -1;
+    return local_len_of(len, rank, world, block);
+}
+
+int mfc_kv_local_row(int32_t pos, int32_t rank, int32_t world, int32_t block) {
+    if (pos < 0 || world < 1 || rank < 0 || rank >= world || block <= 0) return -1;
+    return local_row_of(pos, rank, world, block);
+}
+
+long long mfc_snapshot_validate(const mfc_config *cfg, const void *buf, size_t buf_len) {
+    if (!cfg || !buf) return -1;
+    size_t hb = 0;
+    std::string why;
+    const long long r = snapshot_preflight(*cfg, (const uint8_t *)buf, buf_len, &hb, why);
+    if (r < 0) g_open_error = why;
+    return r;
+}
+
+// ---------------------------------------------------------------- parity hooks
+
+int mfc_apply_rotary_emb(mfc_ctx *c, int32_t pos, float *q, float *k) {
+    if (!c) return -1;
+    if (!q || !k || pos < 0) {
+        fail(c, "NULL argument or pos < 0");
+        return -1;
+    }
+    const mfc_config &g = c->cfg;
+    cudaSetDevice(g.device);
+    const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM, kd = sizeof(float) * g.num_kv_heads * HEAD_DIM;
+    CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_k, k, kd, cudaMemcpyHostToDevice, c->stream));
+    CK(launch_rope(c->st_q, c->st_k, g.num_attn_heads, g.num_kv_heads, g.rotary_dim, pos, c->inv_freq, c->stream));
+    c->launches += 1;
+    CK(cudaMemcpyAsync(q, c->st_q, qd, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(k, c->st_k, kd, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+int mfc_sdpa(mfc_ctx *c, int32_t kv_len, const float *q, const float *q_gate, const float *k_cache,
+             const float *v_cache, float *out) {
+    if (!c) return -1;
+    if (!q || !q_gate || !k_cache || !v_cache || !out || kv_len <= 0) {
+        fail(c, "NULL argument or kv_len <= 0");
+        return -1;
+    }
+    const mfc_config &g = c->cfg;
+    if (kv_len > c->cap_rows) {
+        fail(c, "kv_len exceeds the rows reserved per sequence");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    const int slot = c->n_kv_slots - 1;  // hook slot
+    const size_t kvd = (size_t)g.num_kv_heads * HEAD_DIM;
+    for (int pass = 0; pass < 2; pass++) {
+        uint8_t *cache = (uint8_t *)(pass == 0 ? c->k_cache : c->v_cache) +
+                         (size_t)slot * g.num_kv_heads * c->cap_rows * HEAD_DIM * c->kv_esize;
+        const float *src = pass == 0 ? k_cache : v_cache;
+        for (int r0 = 0; r0 < kv_len; r0 += mfc_ctx::SNAP_ROWS) {
+            const int nr = kv_len - r0 < mfc_ctx::SNAP_ROWS ? kv_len - r0 : mfc_ctx::SNAP_ROWS;
+            CK(cudaMemcpyAsync(c->st_rows, src + (size_t)r0 * kvd, sizeof(float) * kvd * nr, cudaMemcpyHostToDevice,
+                               c->stream));
+            CK(launch_kv_pack(c->st_rows, cache, nr, g.num_kv_heads, c->cap_rows, g.kv_dtype == MFC_KV_BF16, r0,
+                              c->stream));
+            c->launches += 1;
+            CK(cudaStreamSynchronize(c->stream));
+        }
+    }
+    const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM;
+    CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_gate, q_gate, qd, cudaMemcpyHostToDevice, c->stream));
+    c->h_gqa_items.resize(1);
+    GqaItem &it = c->h_gqa_items[0];
+    it.kv_slot = slot;
+    it.local_len = kv_len;
+    it.pos = 0;
+    it.append_row = -1;
+    it.in_idx = 0;
+    it.chunk_len = plan_chunk(c, (long long)kv_len * g.num_kv_heads, kv_len);
+    it.n_chunks = (kv_len + it.chunk_len - 1) / it.chunk_len;
+    it.cta_begin = 0;
+    GqaParams p;
+    fill_gqa_params(c, p, 1, it.n_chunks * g.num_kv_heads);
+    p.q = c->st_q;
+    p.gate = c->st_gate;
+    p.k = c->st_k;
+    p.v = c->st_v;
+    p.out = c->st_out;
+    p.rotary_dim = 0;  // q and the cached K are already rotated
+    if (launch_gqa(c, p)) return -1;
+    CK(cudaMemcpyAsync(out, c->st_out, qd, cudaMemcpyDeviceToHost, c->stream));
+    return check_status(c);
+}
+
+int mfc_linear_attn_step_stateless(mfc_ctx *c, int32_t layer, const float *qkv, const float *z, const float *alpha,
+                                   const float *beta, float *conv_state, float *ssm_state, float *out) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (!qkv || !alpha || !beta || !conv_state || !ssm_state || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (layer < 0 || layer >= g.num_layers || is_full_layer(g, layer) || !c->lin_weights_set[c->layer_to_lin[layer]]) {
+        fail(c, "layer is not a linear-attention layer with weights set");
+        return -1;
+    }
+    if (z && c->lin_weights_set[c->layer_to_lin[layer]] != 2) {
+        fail(c, "z given but no norm weight was set for the layer");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    const int slot = c->n_state_slots - 1;  // hook slot
+    const size_t ssm_elems = (size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM;
+    float *ring = c->conv + (size_t)slot * CONV_TAPS * c->conv_dim;
+    const size_t row = sizeof(float) * c->conv_dim;
+    CK(cudaMemcpyAsync(ring + c->conv_dim, conv_state, 3 * row, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->ssm + (size_t)slot * ssm_elems, ssm_state, sizeof(float) * ssm_elems,
+                       cudaMemcpyHostToDevice, c->stream));
+    const size_t vd = sizeof(float) * g.linear_num_v_heads * GDN_DIM;
+    const size_t hd = sizeof(float) * g.linear_num_v_heads;
+    CK(cudaMemcpyAsync(c->st_qkv, qkv, row, cudaMemcpyHostToDevice, c->stream));
+    if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, c->stream));
+    c->h_gdn_items.resize(1);
+    c->h_gdn_items[0].w_layer = c->layer_to_lin[layer];
+    c->h_gdn_items[0].state_idx = slot;
+    c->h_gdn_items[0].slot = 0;  // history sits in slots 1..3
+    c->h_gdn_items[0].pad = 0;
+    if (launch_gdn(c, 1, c->st_qkv, z ? c->st_z : nullptr, c->st_alpha, c->st_beta, c->st_gout)) return -1;
+    // advanced history = old rows 1, 2 and the new input = slots 2, 3, 0
+    CK(cudaMemcpyAsync(conv_state, ring + 2 * (size_t)c->conv_dim, 2 * row, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(conv_state + 2 * (size_t)c->conv_dim, ring, row, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(ssm_state, c->ssm + (size_t)slot * ssm_elems, sizeof(float) * ssm_elems,
+                       cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(out, c->st_gout, vd, cudaMemcpyDeviceToHost, c->stream));
+    return check_status(c);
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

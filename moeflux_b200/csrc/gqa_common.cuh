@@ -1,0 +1,190 @@
+// Pieces shared by the bf16 and fp32 split-K decode kernels: CTA -> work unit
+// lookup, RoPE of one float2, and the epilogue (finish in place, or park the
+// partial and let the last CTA of the unit merge by log-sum-exp and gate).
+#pragma once
+#include <math.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mfc {
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+// x[d], x[d+1] of one head row after partial RoPE (MLX half-split pairing,
+// crates/moeflux/src/riir/rope.rs:93-128); d even, tables indexed by pair index.
+__device__ __forceinline__ float2 load_rot2(const float *row, int d, int rotary_dim, int half,
+                                            const float *s_cos, const float *s_sin) {
+    float2 x = *reinterpret_cast<const float2 *>(row + d);
+    if (d < rotary_dim) {
+        if (d < half) {
+            const float2 pr = *reinterpret_cast<const float2 *>(row + d + half);
+            x = make_float2(x.x * s_cos[d] - pr.x * s_sin[d], x.y * s_cos[d + 1] - pr.y * s_sin[d + 1]);
+        } else {
+            const int i = d - half;
+            const float2 pr = *reinterpret_cast<const float2 *>(row + i);
+            x = make_float2(pr.x * s_sin[i] + x.x * s_cos[i], pr.y * s_sin[i + 1] + x.y * s_cos[i + 1]);
+        }
+    }
+    return x;
+}
+
+struct Located {
+    GqaItem it;
+    int item_idx;
+    int kvh;
+    int chunk;
+};
+
+__device__ __forceinline__ Located locate(const GqaParams &p, int bid) {
+    int lo = 0, hi = p.n_items - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (p.items[mid].cta_begin <= bid) lo = mid;
+        else hi = mid - 1;
+    }
+    Located L;
+    L.it = p.items[lo];
+    L.item_idx = lo;
+    const int local = bid - L.it.cta_begin;
+    L.kvh = local / L.it.n_chunks;
+    L.chunk = local % L.it.n_chunks;
+    return L;
+}
+
+// out = merge of n_src partials (slot stride given) for one (item, kv head):
+// final gated output or merged partial.  Executed by 128 threads.
+__device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L, const float *src_o,
+                           const float *src_m, const float *src_l, int n_src, float *s_w,
+                           float *s_M, float *s_L) {
+    const int tid = threadIdx.x;
+    const int group = p.group;
+    if (tid < 16) {
+        float M = -INFINITY;
+        for (int c = 0; c < n_src; c++) M = fmaxf(M, src_m[c * 16 + tid]);
+        s_M[tid] = M;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < n_src * 16; idx += 128) {
+        const float m = src_m[idx];
+        s_w[idx] = (m == -INFINITY) ? 0.0f : expf(m - s_M[idx & 15]);
+    }
+    __syncthreads();
+    if (tid < 16) {
+        float Ls = 0.0f;
+        for (int c = 0; c < n_src; c++) Ls += s_w[c * 16 + tid] * src_l[c * 16 + tid];
+        s_L[tid] = Ls;
+    }
+    __syncthreads();
+    const size_t head0 = (size_t)L.it.in_idx * p.H + (size_t)L.kvh * group;
+    for (int hr = 0; hr < group; hr++) {
+        float2 acc = make_float2(0.0f, 0.0f);
+        for (int c = 0; c < n_src; c++) {
+            const float w = s_w[c * 16 + hr];
+            const float2 o = *reinterpret_cast<const float2 *>(
+                src_o + ((size_t)c * 16 + hr) * HEAD_DIM + 2 * tid);
+            acc.x = fmaf(w, o.x, acc.x);
+            acc.y = fmaf(w, o.y, acc.y);
+        }
+        const size_t off = (head0 + hr) * HEAD_DIM + 2 * tid;
+        if (p.partial_mode) {
+            *reinterpret_cast<float2 *>(p.po + off) = acc;
+            if (tid == 0) {
+                p.pm[head0 + hr] = s_M[hr];
+                p.pl[head0 + hr] = s_L[hr];
+            }
+        } else {
+            const float inv = 1.0f / s_L[hr];
+            float2 r = make_float2(acc.x * inv, acc.y * inv);
+            if (p.gate) {
+                const float2 gt = *reinterpret_cast<const float2 *>(p.gate + off);
+                r.x *= 1.0f / (1.0f + expf(-gt.x));
+                r.y *= 1.0f / (1.0f + expf(-gt.y));
+            }
+            *reinterpret_cast<float2 *>(p.out + off) = r;
+        }
+    }
+}
+
+// Epilogue shared by both kernels.  The warp layout of the accumulators is:
+// o[nt][2x + e] = row (g + 8x), dim 64*warp + 8*nt + 2t + e;  m_r / l_r per row
+// (l_r still split over the four lanes of a row).
+__device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L, float (&o)[8][4],
+                                            float (&m_r)[2], float (&l_r)[2], float *s_w,
+                                            float *s_M, float *s_L, int *s_flag_p) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const GqaItem &it = L.it;
+    const int group = p.group;
+#pragma unroll
+    for (int x = 0; x < 2; x++) {
+        l_r[x] += __shfl_xor_sync(0xffffffffu, l_r[x], 1);
+        l_r[x] += __shfl_xor_sync(0xffffffffu, l_r[x], 2);
+    }
+
+    const size_t head0 = (size_t)it.in_idx * p.H + (size_t)L.kvh * group;
+    if (it.n_chunks == 1) {
+        // single chunk: finish in place
+#pragma unroll
+        for (int x = 0; x < 2; x++) {
+            const int row = g + 8 * x;
+            if (row >= group) continue;
+            const float m_nat = m_r[x] * p.scale;
+            if (p.partial_mode) {
+                if (warp == 0 && t == 0) {
+                    p.pm[head0 + row] = m_nat;
+                    p.pl[head0 + row] = l_r[x];
+                }
+            }
+            const float inv = p.partial_mode ? 1.0f : 1.0f / l_r[x];
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const size_t off = (head0 + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t;
+                float2 rv = make_float2(o[nt][2 * x] * inv, o[nt][2 * x + 1] * inv);
+                if (p.partial_mode) {
+                    *reinterpret_cast<float2 *>(p.po + off) = rv;
+                } else {
+                    if (p.gate) {
+                        const float2 gt = *reinterpret_cast<const float2 *>(p.gate + off);
+                        rv.x *= 1.0f / (1.0f + expf(-gt.x));
+                        rv.y *= 1.0f / (1.0f + expf(-gt.y));
+                    }
+                    *reinterpret_cast<float2 *>(p.out + off) = rv;
+                }
+            }
+        }
+        return;
+    }
+
+    // several chunks: park the partial, the last CTA of the unit merges
+    const size_t slot0 = (size_t)it.cta_begin + (size_t)L.kvh * it.n_chunks;  // first slot of the unit
+    const size_t slot = slot0 + L.chunk;
+#pragma unroll
+    for (int x = 0; x < 2; x++) {
+        const int row = g + 8 * x;
+        if (warp == 0 && t == 0) {
+            p.sc_m[slot * 16 + row] = m_r[x] * p.scale;
+            p.sc_l[slot * 16 + row] = l_r[x];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            *reinterpret_cast<float2 *>(p.sc_o + (slot * 16 + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t) =
+                make_float2(o[nt][2 * x], o[nt][2 * x + 1]);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned *tk = p.tickets + (size_t)L.item_idx * p.Hkv + L.kvh;
+        const unsigned prev = atomicAdd(tk, 1u);
+        *s_flag_p = (prev == (unsigned)(it.n_chunks - 1));
+        if (*s_flag_p) *tk = 0u;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!*s_flag_p) return;
+    __threadfence();
+    merge_unit(p, L, p.sc_o + slot0 * 16 * HEAD_DIM, p.sc_m + slot0 * 16, p.sc_l + slot0 * 16,
+               it.n_chunks, s_w, s_M, s_L);
+}
+
+}  // namespace mfc

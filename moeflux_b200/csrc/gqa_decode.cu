@@ -1,0 +1,393 @@
+// Split-K flash-decoding for GQA full attention with the sigmoid output gate,
+// bf16 KV cache, for sm_100a.
+//
+// One launch performs, for every (layer, sequence) item, what the reference
+// does with RoPE + KV append on the host and four GPU kernels
+// (crates/moeflux/src/riir/rope.rs:65-131, full_attn_forward.rs:281-323,
+// crates/moeflux/shaders/shaders.metal: attn_scores_batched :976-1019,
+// attn_softmax_batched :1026-1084, attn_values_batched :1095-1117,
+// sigmoid_gate :1125-1134), or with sdpa_cpu (sdpa.rs:63-172) outside
+// 32 <= kv_len < 8192.
+//
+// Work split.  A CTA (4 warps) owns one (item, kv head, KV chunk).  The up-to-16
+// query heads that share the kv head are the M=16 rows of mma.sync m16n8k16, so
+// a cached row is read from HBM once for all of them.  K/V tiles of 32 rows
+// arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle, four 64-column boxes
+// per tensor) into a multi-stage shared-memory ring guarded by mbarriers with
+// bounded waits.  Per tile: warp w computes the scores of rows 8w..8w+7 over
+// all 256 dims (Q fragments live in registers), the four 16x8 score blocks are
+// exchanged through shared memory, every warp runs the same online softmax
+// (warp-shuffle row max) and then accumulates P·V for its own 64 output dims.
+// Chunks write un-normalised (o, m, l) partials; the last CTA of a unit to
+// finish (atomic ticket, no spinning) merges them by log-sum-exp, applies the
+// sigmoid gate and writes the output.  With partial_mode the merged
+// un-normalised partial is written instead, for the cross-GPU KV split.
+//
+// RoPE and the append are fused: every CTA rotates q while building its
+// fragments; the CTA whose chunk holds the new row rotates k, stores k and v
+// into the cache, fences, and only then starts its TMA loads.
+#include <math.h>
+
+#include "gqa_common.cuh"
+
+namespace mfc {
+
+namespace {
+
+constexpr int BF16_STAGES = 3;
+constexpr int TILE_BYTES_BF16 = KV_TILE * HEAD_DIM * 2;  // 16 KiB per tensor per stage
+constexpr int SX_STRIDE = 40;                            // padded row stride of the score exchange
+
+__global__ void __launch_bounds__(128, 2)
+gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
+                       const __grid_constant__ CUtensorMap vmap, const GqaParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the 128-byte swizzle atoms
+    uint8_t *smem = reinterpret_cast<uint8_t *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *stages = smem;  // [STAGES][K tile | V tile]
+    float *s_sx = reinterpret_cast<float *>(smem + BF16_STAGES * 2 * TILE_BYTES_BF16);  // [2][16][40]
+    float *s_cos = s_sx + 2 * 16 * SX_STRIDE;  // [128]
+    float *s_sin = s_cos + 128;                // [128]
+    float *s_w = s_sin + 128;                  // [MAX_SPLITS*16]
+    float *s_M = s_w + MAX_SPLITS * 16;        // [16]
+    float *s_L = s_M + 16;                     // [16]
+    uint64_t *full = reinterpret_cast<uint64_t *>(s_L + 16);  // [STAGES]
+    __shared__ int s_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const Located L = locate(p, blockIdx.x);
+    const GqaItem &it = L.it;
+    const int group = p.group;
+
+    const int c0 = L.chunk * it.chunk_len;
+    const int c1 = min(c0 + it.chunk_len, it.local_len);
+    const int ntiles = (c1 > c0) ? (c1 - c0 + KV_TILE - 1) / KV_TILE : 0;
+    const int row_base = (it.kv_slot * p.Hkv + L.kvh) * p.cap_rows;
+    const bool appender = it.append_row >= c0 && it.append_row < c0 + it.chunk_len;
+
+    auto issue_tile = [&](int tile) {
+        const int st = tile % BF16_STAGES;
+        uint8_t *kdst = stages + (size_t)st * 2 * TILE_BYTES_BF16;
+        uint8_t *vdst = kdst + TILE_BYTES_BF16;
+        mbar_expect_tx(&full[st], 2 * TILE_BYTES_BF16);
+        const int y = row_base + c0 + tile * KV_TILE;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            tma_load_2d(kdst + b * 4096, &kmap, b * 64, y, &full[st]);
+            tma_load_2d(vdst + b * 4096, &vmap, b * 64, y, &full[st]);
+        }
+    };
+
+    if (tid == 0) {
+        prefetch_tmap(&kmap);
+        prefetch_tmap(&vmap);
+#pragma unroll
+        for (int s = 0; s < BF16_STAGES; s++) mbar_init(&full[s], 1);
+        mbar_fence_init();
+        if (!appender) {
+            const int n0 = min(ntiles, BF16_STAGES);
+            for (int i = 0; i < n0; i++) issue_tile(i);
+        }
+    }
+    // RoPE table for this token
+    const int half = p.rotary_dim >> 1;
+    if (tid < half) {
+        float sn, cs;
+        sincosf((float)it.pos * p.inv_freq[tid], &sn, &cs);
+        s_cos[tid] = cs;
+        s_sin[tid] = sn;
+    }
+    __syncthreads();
+
+    if (appender) {
+        // rotate k, store the new K and V rows (bf16), then let thread 0 start the loads
+        const float *ksrc = p.k + ((size_t)it.in_idx * p.Hkv + L.kvh) * HEAD_DIM;
+        const float *vsrc = p.v + ((size_t)it.in_idx * p.Hkv + L.kvh) * HEAD_DIM;
+        const int d = 2 * tid;
+        const float2 kx = load_rot2(ksrc, d, p.rotary_dim, half, s_cos, s_sin);
+        const float2 vx = *reinterpret_cast<const float2 *>(vsrc + d);
+        const size_t roff = ((size_t)row_base + it.append_row) * HEAD_DIM + d;
+        *reinterpret_cast<uint32_t *>(reinterpret_cast<__nv_bfloat16 *>(p.k_base) + roff) =
+            pack_bf16x2(kx.x, kx.y);
+        *reinterpret_cast<uint32_t *>(reinterpret_cast<__nv_bfloat16 *>(p.v_base) + roff) =
+            pack_bf16x2(vx.x, vx.y);
+        __threadfence();
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) {
+            const int n0 = min(ntiles, BF16_STAGES);
+            for (int i = 0; i < n0; i++) issue_tile(i);
+        }
+    }
+
+    // ---- Q fragments (A operand, 16 heads x 256 dims, bf16), RoPE applied ----
+    uint32_t qa[16][4];
+    {
+        const float *qbase = p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * HEAD_DIM;
+#pragma unroll
+        for (int ks = 0; ks < 16; ks++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int row = g + ((e & 1) ? 8 : 0);
+                const int d = ks * 16 + 2 * t + ((e & 2) ? 8 : 0);
+                float2 x = make_float2(0.0f, 0.0f);
+                if (row < group) {
+                    const float *qr = qbase + (size_t)row * HEAD_DIM;
+                    x = load_rot2(qr, d, p.rotary_dim, half, s_cos, s_sin);
+                }
+                qa[ks][e] = pack_bf16x2(x.x, x.y);
+            }
+        }
+    }
+
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m_r[2] = {-INFINITY, -INFINITY};
+    float l_r[2] = {0.0f, 0.0f};
+    const float sl2 = p.scale * LOG2E;
+    bool failed = false;
+
+    for (int i = 0; i < ntiles; i++) {
+        const int st = i % BF16_STAGES;
+        const unsigned par = (unsigned)(i / BF16_STAGES) & 1u;
+        const bool ok = mbar_wait_bounded(&full[st], par);
+        const uint32_t kst = smem_u32(stages + (size_t)st * 2 * TILE_BYTES_BF16);
+        const uint32_t vst = kst + TILE_BYTES_BF16;
+
+        // scores of rows 8w..8w+7 against all 16 heads
+        float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (ok) {
+            const int r = lane & 7, mi = lane >> 3;
+            const int row = 8 * warp + r;
+#pragma unroll
+            for (int jx = 0; jx < 8; jx++) {
+                const int box = jx >> 1, chunk = ((jx & 1) << 2) + mi;
+                const uint32_t addr = kst + box * 4096 + row * 128 + ((chunk ^ (row & 7)) << 4);
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, addr);
+                mma_bf16_16816(sacc, qa[2 * jx], b0, b1);
+                mma_bf16_16816(sacc, qa[2 * jx + 1], b2, b3);
+            }
+        }
+        float *sx = s_sx + (i & 1) * 16 * SX_STRIDE;
+        *reinterpret_cast<float2 *>(sx + g * SX_STRIDE + 8 * warp + 2 * t) =
+            make_float2(sacc[0], sacc[1]);
+        *reinterpret_cast<float2 *>(sx + (g + 8) * SX_STRIDE + 8 * warp + 2 * t) =
+            make_float2(sacc[2], sacc[3]);
+        if (!__syncthreads_and(ok ? 1 : 0)) {
+            failed = true;
+            break;
+        }
+        // every warp is past its reads of tile i-1: refill that stage
+        if (tid == 0 && i >= 1 && (i - 1 + BF16_STAGES) < ntiles) issue_tile(i - 1 + BF16_STAGES);
+
+        float sv[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            const float2 a = *reinterpret_cast<const float2 *>(sx + g * SX_STRIDE + 8 * nt + 2 * t);
+            const float2 b =
+                *reinterpret_cast<const float2 *>(sx + (g + 8) * SX_STRIDE + 8 * nt + 2 * t);
+            sv[nt][0] = a.x;
+            sv[nt][1] = a.y;
+            sv[nt][2] = b.x;
+            sv[nt][3] = b.y;
+        }
+        const int tile_row0 = c0 + i * KV_TILE;
+        if (tile_row0 + KV_TILE > c1) {
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const int col = tile_row0 + 8 * nt + 2 * t;
+                if (col >= c1) sv[nt][0] = sv[nt][2] = -INFINITY;
+                if (col + 1 >= c1) sv[nt][1] = sv[nt][3] = -INFINITY;
+            }
+        }
+        // online softmax, rows g (x=0) and g+8 (x=1)
+        float corr[2];
+#pragma unroll
+        for (int x = 0; x < 2; x++) {
+            float mx = fmaxf(fmaxf(sv[0][2 * x], sv[0][2 * x + 1]), fmaxf(sv[1][2 * x], sv[1][2 * x + 1]));
+            mx = fmaxf(mx, fmaxf(fmaxf(sv[2][2 * x], sv[2][2 * x + 1]), fmaxf(sv[3][2 * x], sv[3][2 * x + 1])));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_r[x], mx);
+            corr[x] = exp2f((m_r[x] - m_new) * sl2);
+            m_r[x] = m_new;
+            const float mb = m_new * sl2;
+            float rs = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                sv[nt][2 * x] = exp2f(fmaf(sv[nt][2 * x], sl2, -mb));
+                sv[nt][2 * x + 1] = exp2f(fmaf(sv[nt][2 * x + 1], sl2, -mb));
+                rs += sv[nt][2 * x] + sv[nt][2 * x + 1];
+            }
+            l_r[x] = l_r[x] * corr[x] + rs;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            o[nt][0] *= corr[0];
+            o[nt][1] *= corr[0];
+            o[nt][2] *= corr[1];
+            o[nt][3] *= corr[1];
+        }
+        // O[:, 64w..64w+63] += P (16x32) * V (32 x 64)
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16x2(sv[2 * kk][0], sv[2 * kk][1]);
+            pa[1] = pack_bf16x2(sv[2 * kk][2], sv[2 * kk][3]);
+            pa[2] = pack_bf16x2(sv[2 * kk + 1][0], sv[2 * kk + 1][1]);
+            pa[3] = pack_bf16x2(sv[2 * kk + 1][2], sv[2 * kk + 1][3]);
+            const int r = lane & 7, mi = lane >> 3;
+            const int prow = 16 * kk + 8 * (mi & 1) + r;
+#pragma unroll
+            for (int cp = 0; cp < 4; cp++) {
+                const int chunk = 2 * cp + (mi >> 1);
+                const uint32_t addr = vst + warp * 4096 + prow * 128 + ((chunk ^ (prow & 7)) << 4);
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3, addr);
+                mma_bf16_16816(o[2 * cp], pa, b0, b1);
+                mma_bf16_16816(o[2 * cp + 1], pa, b2, b3);
+            }
+        }
+    }
+    if (failed) {
+        if (tid == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);
+        return;
+    }
+
+    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag);
+}
+
+constexpr size_t BF16_SMEM = 1024 + (size_t)BF16_STAGES * 2 * TILE_BYTES_BF16 +
+                             sizeof(float) * (2 * 16 * SX_STRIDE + 256 + MAX_SPLITS * 16 + 32) +
+                             sizeof(uint64_t) * BF16_STAGES;
+
+// ---- stand-alone merge of gathered partials (cross-GPU KV split) ----------
+__global__ void __launch_bounds__(128)
+lse_merge_gate_kernel(int n_parts, int n, int H, const float *o_parts, const float *m_parts,
+                      const float *l_parts, const float *gate, float *out) {
+    // one CTA per (item, head); 128 threads x 2 dims
+    const int ih = blockIdx.x;  // item * H + head
+    const int tid = threadIdx.x;
+    const size_t stride_ml = (size_t)n * H;
+    float M = -INFINITY;
+    for (int r = 0; r < n_parts; r++) M = fmaxf(M, m_parts[r * stride_ml + ih]);
+    float Ls = 0.0f;
+    float2 acc = make_float2(0.0f, 0.0f);
+    for (int r = 0; r < n_parts; r++) {
+        const float m = m_parts[r * stride_ml + ih];
+        const float w = (m == -INFINITY) ? 0.0f : expf(m - M);
+        Ls += w * l_parts[r * stride_ml + ih];
+        const float2 o = *reinterpret_cast<const float2 *>(
+            o_parts + (r * stride_ml + ih) * HEAD_DIM + 2 * tid);
+        acc.x = fmaf(w, o.x, acc.x);
+        acc.y = fmaf(w, o.y, acc.y);
+    }
+    const float inv = 1.0f / Ls;
+    float2 rv = make_float2(acc.x * inv, acc.y * inv);
+    const size_t off = (size_t)ih * HEAD_DIM + 2 * tid;
+    if (gate) {
+        const float2 gt = *reinterpret_cast<const float2 *>(gate + off);
+        rv.x *= 1.0f / (1.0f + expf(-gt.x));
+        rv.y *= 1.0f / (1.0f + expf(-gt.y));
+    }
+    *reinterpret_cast<float2 *>(out + off) = rv;
+}
+
+// ---- RoPE hook ------------------------------------------------------------------
+__global__ void rope_kernel(float *q, float *k, int H, int Hkv, int rotary_dim, int pos,
+                            const float *inv_freq) {
+    const int half = rotary_dim >> 1;
+    const int total = (H + Hkv) * half;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += gridDim.x * blockDim.x) {
+        const int hh = idx / half, i = idx % half;
+        float *x = (hh < H) ? q + (size_t)hh * HEAD_DIM : k + (size_t)(hh - H) * HEAD_DIM;
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        const float x0 = x[i], x1 = x[i + half];
+        x[i] = x0 * cs - x1 * sn;
+        x[i + half] = x0 * sn + x1 * cs;
+    }
+}
+
+// ---- cache <-> wire layout ----------------------------------------------------
+// wire rows: [row][Hkv][256] fp32; cache: [Hkv][cap_rows][256] of the storage type
+__global__ void kv_pack_kernel(const float *src, void *dst, int n_rows, int Hkv, int cap_rows,
+                               int kv_bf16, int dst_row0) {
+    const size_t total = (size_t)n_rows * Hkv * HEAD_DIM;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int d = (int)(idx % HEAD_DIM);
+        const int hh = (int)((idx / HEAD_DIM) % Hkv);
+        const size_t row = idx / ((size_t)HEAD_DIM * Hkv);
+        const size_t o = ((size_t)hh * cap_rows + dst_row0 + row) * HEAD_DIM + d;
+        if (kv_bf16) reinterpret_cast<__nv_bfloat16 *>(dst)[o] = __float2bfloat16_rn(src[idx]);
+        else reinterpret_cast<float *>(dst)[o] = src[idx];
+    }
+}
+__global__ void kv_unpack_kernel(const void *src, float *dst, int n_rows, int Hkv, int cap_rows,
+                                 int kv_bf16) {
+    const size_t total = (size_t)n_rows * Hkv * HEAD_DIM;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int d = (int)(idx % HEAD_DIM);
+        const int hh = (int)((idx / HEAD_DIM) % Hkv);
+        const size_t row = idx / ((size_t)HEAD_DIM * Hkv);
+        const size_t o = ((size_t)hh * cap_rows + row) * HEAD_DIM + d;
+        dst[idx] = kv_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(src)[o])
+                           : reinterpret_cast<const float *>(src)[o];
+    }
+}
+
+}  // namespace
+
+cudaError_t gqa_decode_configure() {
+    return cudaFuncSetAttribute(gqa_decode_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)BF16_SMEM);
+}
+
+cudaError_t launch_gqa_decode_bf16(const CUtensorMap &kmap, const CUtensorMap &vmap,
+                                   const GqaParams &p, cudaStream_t stream) {
+    if (p.total_ctas <= 0) return cudaSuccess;
+    gqa_decode_bf16_kernel<<<p.total_ctas, 128, BF16_SMEM, stream>>>(kmap, vmap, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
+                                  const float *m_parts, const float *l_parts, const float *gate,
+                                  float *out, cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    lse_merge_gate_kernel<<<n * H, 128, 0, stream>>>(n_parts, n, H, o_parts, m_parts, l_parts, gate, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope(float *q, float *k, int H, int Hkv, int rotary_dim, int pos,
+                        const float *inv_freq, cudaStream_t stream) {
+    const int total = (H + Hkv) * (rotary_dim / 2);
+    if (total <= 0) return cudaSuccess;
+    rope_kernel<<<(total + 127) / 128, 128, 0, stream>>>(q, k, H, Hkv, rotary_dim, pos, inv_freq);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_kv_pack(const float *src_rows, void *dst_cache, int n_rows, int Hkv,
+                           int cap_rows, int kv_bf16, int dst_row0, cudaStream_t stream) {
+    if (n_rows <= 0) return cudaSuccess;
+    const size_t total = (size_t)n_rows * Hkv * HEAD_DIM;
+    const int blocks = (int)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
+    kv_pack_kernel<<<blocks, 256, 0, stream>>>(src_rows, dst_cache, n_rows, Hkv, cap_rows, kv_bf16, dst_row0);
+    return cudaGetLastError();
+}
+cudaError_t launch_kv_unpack(const void *src_cache, float *dst_rows, int n_rows, int Hkv,
+                             int cap_rows, int kv_bf16, cudaStream_t stream) {
+    if (n_rows <= 0) return cudaSuccess;
+    const size_t total = (size_t)n_rows * Hkv * HEAD_DIM;
+    const int blocks = (int)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
+    kv_unpack_kernel<<<blocks, 256, 0, stream>>>(src_cache, dst_rows, n_rows, Hkv, cap_rows, kv_bf16);
+    return cudaGetLastError();
+}
+
+}  // namespace mfc

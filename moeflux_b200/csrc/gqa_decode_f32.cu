@@ -1,0 +1,302 @@
+// Split-K flash-decoding for GQA full attention, fp32 KV cache (the reference's
+// storage type), for sm_100a.  Same work split, TMA pipeline, RoPE/append fusion
+// and epilogue as the bf16 kernel (gqa_decode.cu); the tile maths differs.
+//
+// fp32 operands run on the tensor cores as 3xTF32: every operand x is split
+// into hi = tf32(x) and lo = tf32(x - hi) and a product a*b is accumulated as
+// a_hi*b_hi + a_lo*b_hi + a_hi*b_lo in fp32, which keeps the error near 2^-21
+// relative (the reference is fp32 throughout: crates/moeflux/src/riir/sdpa.rs:
+// 114-169).  A 16x256 fp32 Q in hi/lo form does not fit in registers next to
+// the accumulators, so here each warp owns 64 of the 256 dims for BOTH
+// contractions: it computes a partial score block over its dims, the four
+// partial blocks are summed through shared memory, and P·V is accumulated for
+// the same 64 dims.  Tiles are 16 rows; K fragments come from ldmatrix (an 8x8
+// b16 matrix is an 8x4 fp32 block), V fragments from conflict-free scalar loads
+// with the k index of the MMA permuted to match the score fragment layout.
+#include <math.h>
+
+#include "gqa_common.cuh"
+
+namespace mfc {
+
+namespace {
+
+constexpr int F32_TILE = KV_TILE_F32;
+constexpr int F32_STAGES = 3;
+constexpr int TILE_BYTES_F32 = F32_TILE * HEAD_DIM * 4;  // 16 KiB per tensor per stage
+constexpr int BOX_BYTES = F32_TILE * 128;                // one [16 rows x 32 floats] box
+constexpr int SP_STRIDE = 24;                            // padded row stride of a partial score block
+
+__device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo) {
+    hi = f32_to_tf32(x);
+    lo = f32_to_tf32(x - __uint_as_float(hi));
+}
+
+__global__ void __launch_bounds__(128, 2)
+gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
+                      const __grid_constant__ CUtensorMap vmap, const GqaParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *stages = smem;  // [STAGES][K tile | V tile]
+    float *s_sp = reinterpret_cast<float *>(smem + F32_STAGES * 2 * TILE_BYTES_F32);  // [2][4][16][24]
+    float *s_cos = s_sp + 2 * 4 * 16 * SP_STRIDE;  // [128]
+    float *s_sin = s_cos + 128;                    // [128]
+    uint64_t *full = reinterpret_cast<uint64_t *>(s_sin + 128);
+    // merge scratch aliases the stage ring: it is touched only after the last tile
+    float *s_w = reinterpret_cast<float *>(stages);  // [MAX_SPLITS*16]
+    float *s_M = s_w + MAX_SPLITS * 16;              // [16]
+    float *s_L = s_M + 16;                           // [16]
+    __shared__ int s_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const Located L = locate(p, blockIdx.x);
+    const GqaItem &it = L.it;
+    const int group = p.group;
+
+    const int c0 = L.chunk * it.chunk_len;
+    const int c1 = min(c0 + it.chunk_len, it.local_len);
+    const int ntiles = (c1 > c0) ? (c1 - c0 + F32_TILE - 1) / F32_TILE : 0;
+    const int row_base = (it.kv_slot * p.Hkv + L.kvh) * p.cap_rows;
+    const bool appender = it.append_row >= c0 && it.append_row < c0 + it.chunk_len;
+
+    auto issue_tile = [&](int tile) {
+        const int st = tile % F32_STAGES;
+        uint8_t *kdst = stages + (size_t)st * 2 * TILE_BYTES_F32;
+        uint8_t *vdst = kdst + TILE_BYTES_F32;
+        mbar_expect_tx(&full[st], 2 * TILE_BYTES_F32);
+        const int y = row_base + c0 + tile * F32_TILE;
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            tma_load_2d(kdst + b * BOX_BYTES, &kmap, b * 32, y, &full[st]);
+            tma_load_2d(vdst + b * BOX_BYTES, &vmap, b * 32, y, &full[st]);
+        }
+    };
+
+    if (tid == 0) {
+        prefetch_tmap(&kmap);
+        prefetch_tmap(&vmap);
+#pragma unroll
+        for (int s = 0; s < F32_STAGES; s++) mbar_init(&full[s], 1);
+        mbar_fence_init();
+        if (!appender) {
+            const int n0 = min(ntiles, F32_STAGES);
+            for (int i = 0; i < n0; i++) issue_tile(i);
+        }
+    }
+    const int half = p.rotary_dim >> 1;
+    if (tid < half) {
+        float sn, cs;
+        sincosf((float)it.pos * p.inv_freq[tid], &sn, &cs);
+        s_cos[tid] = cs;
+        s_sin[tid] = sn;
+    }
+    __syncthreads();
+
+    if (appender) {
+        const float *ksrc = p.k + ((size_t)it.in_idx * p.Hkv + L.kvh) * HEAD_DIM;
+        const float *vsrc = p.v + ((size_t)it.in_idx * p.Hkv + L.kvh) * HEAD_DIM;
+        const int d = 2 * tid;
+        const float2 kx = load_rot2(ksrc, d, p.rotary_dim, half, s_cos, s_sin);
+        const float2 vx = *reinterpret_cast<const float2 *>(vsrc + d);
+        const size_t roff = ((size_t)row_base + it.append_row) * HEAD_DIM + d;
+        *reinterpret_cast<float2 *>(reinterpret_cast<float *>(p.k_base) + roff) = kx;
+        *reinterpret_cast<float2 *>(reinterpret_cast<float *>(p.v_base) + roff) = vx;
+        __threadfence();
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) {
+            const int n0 = min(ntiles, F32_STAGES);
+            for (int i = 0; i < n0; i++) issue_tile(i);
+        }
+    }
+
+    // ---- Q fragments for this warp's 64 dims: 8 k-steps of 8, hi and lo ----
+    // A (16x8, tf32): a0 (g, t)  a1 (g+8, t)  a2 (g, t+4)  a3 (g+8, t+4)
+    uint32_t qh[8][4], ql[8][4];
+    {
+        const float *qbase = p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * HEAD_DIM;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int row = g + ((e & 1) ? 8 : 0);
+                const int d = 64 * warp + 8 * ks + t + ((e & 2) ? 4 : 0);
+                float x = 0.0f;
+                if (row < group) {
+                    const float *qr = qbase + (size_t)row * HEAD_DIM;
+                    const float2 pr = load_rot2(qr, d & ~1, p.rotary_dim, half, s_cos, s_sin);
+                    x = (d & 1) ? pr.y : pr.x;
+                }
+                split_tf32(x, qh[ks][e], ql[ks][e]);
+            }
+        }
+    }
+
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m_r[2] = {-INFINITY, -INFINITY};
+    float l_r[2] = {0.0f, 0.0f};
+    const float sl2 = p.scale * LOG2E;
+    bool failed = false;
+
+    for (int i = 0; i < ntiles; i++) {
+        const int st = i % F32_STAGES;
+        const unsigned par = (unsigned)(i / F32_STAGES) & 1u;
+        const bool ok = mbar_wait_bounded(&full[st], par);
+        const uint8_t *kgen = stages + (size_t)st * 2 * TILE_BYTES_F32;
+        const uint32_t kst = smem_u32(kgen);
+        const uint8_t *vgen = kgen + TILE_BYTES_F32;
+
+        // partial scores over dims 64w..64w+63 for the 16 rows of the tile
+        float sp[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) sp[nt][0] = sp[nt][1] = sp[nt][2] = sp[nt][3] = 0.0f;
+        if (ok) {
+            const int r = lane & 7, mi = lane >> 3;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                const int row = 8 * nt + r;
+#pragma unroll
+                for (int jx = 0; jx < 4; jx++) {  // two k-steps per ldmatrix.x4
+                    const int box = 2 * warp + (jx >> 1);
+                    const int chunk = ((jx & 1) << 2) + mi;
+                    const uint32_t addr = kst + box * BOX_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4);
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4(r0, r1, r2, r3, addr);
+                    uint32_t h0, l0, h1, l1;
+                    split_tf32(__uint_as_float(r0), h0, l0);
+                    split_tf32(__uint_as_float(r1), h1, l1);
+                    mma_tf32_1688(sp[nt], qh[2 * jx], h0, h1);
+                    mma_tf32_1688(sp[nt], ql[2 * jx], h0, h1);
+                    mma_tf32_1688(sp[nt], qh[2 * jx], l0, l1);
+                    split_tf32(__uint_as_float(r2), h0, l0);
+                    split_tf32(__uint_as_float(r3), h1, l1);
+                    mma_tf32_1688(sp[nt], qh[2 * jx + 1], h0, h1);
+                    mma_tf32_1688(sp[nt], ql[2 * jx + 1], h0, h1);
+                    mma_tf32_1688(sp[nt], qh[2 * jx + 1], l0, l1);
+                }
+            }
+        }
+        float *spw = s_sp + ((i & 1) * 4 + warp) * 16 * SP_STRIDE;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            *reinterpret_cast<float2 *>(spw + g * SP_STRIDE + 8 * nt + 2 * t) = make_float2(sp[nt][0], sp[nt][1]);
+            *reinterpret_cast<float2 *>(spw + (g + 8) * SP_STRIDE + 8 * nt + 2 * t) =
+                make_float2(sp[nt][2], sp[nt][3]);
+        }
+        if (!__syncthreads_and(ok ? 1 : 0)) {
+            failed = true;
+            break;
+        }
+        if (tid == 0 && i >= 1 && (i - 1 + F32_STAGES) < ntiles) issue_tile(i - 1 + F32_STAGES);
+
+        // full scores = sum of the four partial blocks
+        float sv[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) sv[nt][0] = sv[nt][1] = sv[nt][2] = sv[nt][3] = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float *src = s_sp + ((i & 1) * 4 + w) * 16 * SP_STRIDE;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                const float2 a = *reinterpret_cast<const float2 *>(src + g * SP_STRIDE + 8 * nt + 2 * t);
+                const float2 b = *reinterpret_cast<const float2 *>(src + (g + 8) * SP_STRIDE + 8 * nt + 2 * t);
+                sv[nt][0] += a.x;
+                sv[nt][1] += a.y;
+                sv[nt][2] += b.x;
+                sv[nt][3] += b.y;
+            }
+        }
+        const int tile_row0 = c0 + i * F32_TILE;
+        if (tile_row0 + F32_TILE > c1) {
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                const int col = tile_row0 + 8 * nt + 2 * t;
+                if (col >= c1) sv[nt][0] = sv[nt][2] = -INFINITY;
+                if (col + 1 >= c1) sv[nt][1] = sv[nt][3] = -INFINITY;
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int x = 0; x < 2; x++) {
+            float mx = fmaxf(fmaxf(sv[0][2 * x], sv[0][2 * x + 1]), fmaxf(sv[1][2 * x], sv[1][2 * x + 1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_r[x], mx);
+            corr[x] = exp2f((m_r[x] - m_new) * sl2);
+            m_r[x] = m_new;
+            const float mb = m_new * sl2;
+            float rs = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                sv[nt][2 * x] = exp2f(fmaf(sv[nt][2 * x], sl2, -mb));
+                sv[nt][2 * x + 1] = exp2f(fmaf(sv[nt][2 * x + 1], sl2, -mb));
+                rs += sv[nt][2 * x] + sv[nt][2 * x + 1];
+            }
+            l_r[x] = l_r[x] * corr[x] + rs;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            o[nt][0] *= corr[0];
+            o[nt][1] *= corr[0];
+            o[nt][2] *= corr[1];
+            o[nt][3] *= corr[1];
+        }
+        // O[:, 64w..64w+63] += P (16x16) * V (16 x 64).  The score fragment holds
+        // columns (2t, 2t+1) where the A operand wants (t, t+4): the MMA's k index
+        // is permuted (k=t -> row 2t, k=t+4 -> row 2t+1) on both operands.
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            uint32_t ph[4], pl[4];
+            split_tf32(sv[kk][0], ph[0], pl[0]);  // (g,   k=t)   <- col 2t
+            split_tf32(sv[kk][2], ph[1], pl[1]);  // (g+8, k=t)
+            split_tf32(sv[kk][1], ph[2], pl[2]);  // (g,   k=t+4) <- col 2t+1
+            split_tf32(sv[kk][3], ph[3], pl[3]);  // (g+8, k=t+4)
+            const int prow = 8 * kk + 2 * t;
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const int box = 2 * warp + (nt >> 2);
+                const int col = 8 * (nt & 3) + g;
+                const uint8_t *bx = vgen + box * BOX_BYTES;
+                const float v0 = *reinterpret_cast<const float *>(
+                    bx + prow * 128 + ((((col >> 2) ^ (prow & 7))) << 4) + (col & 3) * 4);
+                const float v1 = *reinterpret_cast<const float *>(
+                    bx + (prow + 1) * 128 + ((((col >> 2) ^ ((prow + 1) & 7))) << 4) + (col & 3) * 4);
+                uint32_t h0, l0, h1, l1;
+                split_tf32(v0, h0, l0);
+                split_tf32(v1, h1, l1);
+                mma_tf32_1688(o[nt], ph, h0, h1);
+                mma_tf32_1688(o[nt], pl, h0, h1);
+                mma_tf32_1688(o[nt], ph, l0, l1);
+            }
+        }
+    }
+    if (failed) {
+        if (tid == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);
+        return;
+    }
+    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag);
+}
+
+constexpr size_t F32_SMEM = 1024 + (size_t)F32_STAGES * 2 * TILE_BYTES_F32 +
+                            sizeof(float) * (2 * 4 * 16 * SP_STRIDE + 256) +
+                            sizeof(uint64_t) * F32_STAGES;
+
+}  // namespace
+
+cudaError_t gqa_decode_f32_configure() {
+    return cudaFuncSetAttribute(gqa_decode_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)F32_SMEM);
+}
+
+cudaError_t launch_gqa_decode_f32(const CUtensorMap &kmap, const CUtensorMap &vmap,
+                                  const GqaParams &p, cudaStream_t stream) {
+    if (p.total_ctas <= 0) return cudaSuccess;
+    gqa_decode_f32_kernel<<<p.total_ctas, 128, F32_SMEM, stream>>>(kmap, vmap, p);
+    return cudaGetLastError();
+}
+
+}  // namespace mfc

@@ -1,0 +1,106 @@
+// Host-visible launch interface of the sm_100a kernels.  The context layer
+// (ctx.cu) builds the item lists; the kernels know nothing about sequences or
+// layers beyond the indices stored in an item.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mfc {
+
+constexpr int HEAD_DIM = 256;      // full-attention head dim
+constexpr int GDN_DIM = 128;       // GatedDeltaNet key dim == value dim
+constexpr int KV_TILE = 32;        // cache rows per pipeline stage (bf16 cache)
+constexpr int KV_TILE_F32 = 16;    // same for the fp32 cache
+constexpr int MAX_SPLITS = 64;     // most KV chunks one (item, kv head) is split into
+constexpr int CONV_TAPS = 4;
+
+// ---------------------------------------------------------------- GatedDeltaNet
+struct GdnItem {
+    int32_t w_layer;    // index into the per-layer weight arrays
+    int32_t state_idx;  // index of the (layer, sequence) state slot
+    int32_t slot;       // ring slot the new conv input is written to (step % 4)
+    int32_t pad;
+};
+
+struct GdnParams {
+    float *ssm_base;          // [state][Hv][128 value][128 key]
+    float *conv_base;         // [state][4 slots][conv_dim]
+    const uint16_t *conv_w;   // [w_layer][conv_dim][4] bf16
+    const float *a_log;       // [w_layer][Hv]
+    const uint16_t *dt_bias;  // [w_layer][Hv] bf16
+    const uint16_t *norm_w;   // [w_layer][128] bf16
+    const GdnItem *items;     // device
+    const float *qkv;         // [n][conv_dim]
+    const float *z;           // [n][Hv*128] or nullptr
+    const float *alpha;       // [n][Hv]
+    const float *beta;        // [n][Hv]
+    float *out;               // [n][Hv*128]
+    int n_items, Hv, Hk, conv_dim;
+    float eps;
+};
+
+// rows_per_cta in {32, 64, 128}: value rows of one head handled by one CTA;
+// 128 / rows_per_cta CTAs form a thread-block cluster per (item, head).
+cudaError_t launch_gdn_decode(const GdnParams &p, int rows_per_cta, cudaStream_t stream);
+
+// ---------------------------------------------------------------- full attention
+struct GqaItem {
+    int32_t kv_slot;     // (full layer index * n_seqs + seq): selects the cache rows
+    int32_t local_len;   // rows held locally, the row appended by this step included
+    int32_t pos;         // absolute position of the token (RoPE angle)
+    int32_t append_row;  // local row that receives k,v, or -1 when another context owns it
+    int32_t chunk_len;   // rows per chunk, multiple of KV_TILE
+    int32_t n_chunks;    // >= 1
+    int32_t cta_begin;   // first CTA of this item; it owns Hkv * n_chunks CTAs
+    int32_t in_idx;      // index of the item's q/gate/k/v/out rows
+};
+
+struct GqaParams {
+    void *k_base;            // cache base pointers (for the append)
+    void *v_base;
+    const GqaItem *items;    // device
+    int n_items;
+    int total_ctas;
+    const float *q;          // [n][H][256]
+    const float *gate;       // [n][H][256] or nullptr
+    const float *k;          // [n][Hkv][256]
+    const float *v;          // [n][Hkv][256]
+    float *out;              // final mode: [n][H][256]
+    float *po, *pm, *pl;     // partial mode outputs [n][H][256], [n][H], [n][H]
+    float *sc_o, *sc_m, *sc_l;  // split-K scratch, one slot per CTA
+    unsigned *tickets;       // [n][Hkv], zero between launches
+    const float *inv_freq;   // [rotary_dim/2]
+    unsigned *status;
+    int H, Hkv, group;       // group = H / Hkv <= 16
+    int rotary_dim;
+    int cap_rows;            // cache rows reserved per (kv_slot, kv head)
+    int partial_mode;        // 0: gated final output, 1: un-normalised partials
+    float scale;             // 1/sqrt(head_dim)
+};
+
+cudaError_t launch_gqa_decode_bf16(const CUtensorMap &kmap, const CUtensorMap &vmap,
+                                   const GqaParams &p, cudaStream_t stream);
+cudaError_t launch_gqa_decode_f32(const CUtensorMap &kmap, const CUtensorMap &vmap,
+                                  const GqaParams &p, cudaStream_t stream);
+// one-time opt-in to large dynamic shared memory
+cudaError_t gqa_decode_configure();
+cudaError_t gqa_decode_f32_configure();
+
+// Merge of gathered partials: [n_parts][n][H][256] etc.
+cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
+                                  const float *m_parts, const float *l_parts, const float *gate,
+                                  float *out, cudaStream_t stream);
+
+// RoPE on packed q [H][256], k [Hkv][256] in place (parity hook).
+cudaError_t launch_rope(float *q, float *k, int H, int Hkv, int rotary_dim, int pos,
+                        const float *inv_freq, cudaStream_t stream);
+
+// Layout conversions between the wire/reference layout [pos][kv_head][256] fp32
+// and the cache layout [kv_head][row][256] of the context's storage type.
+cudaError_t launch_kv_pack(const float *src_rows, void *dst_cache, int n_rows, int Hkv,
+                           int cap_rows, int kv_bf16, int dst_row0, cudaStream_t stream);
+cudaError_t launch_kv_unpack(const void *src_cache, float *dst_rows, int n_rows, int Hkv,
+                             int cap_rows, int kv_bf16, cudaStream_t stream);
+
+}  // namespace mfc

@@ -1,0 +1,279 @@
+"""``Ctx``: host-side mirror of the attention slice of ``RsCtx``
+(crates/moeflux/src/riir/mod.rs: eval_token :1218, memory_clear :1950,
+memory_seq_rm :1989, memory_seq_pos_max :2105, state_size :2113, state_save
+:2125, state_load :2156), calling the C ABI.  Arrays are numpy float32 on the
+host, or raw device pointers (ints, e.g. ``tensor.data_ptr()``) for ``*_dev``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+
+from ._lib import Config, MfcError, lib, KV_F32, KV_BF16
+
+_F = C.POINTER(C.c_float)
+_I = C.POINTER(C.c_int32)
+_U16 = C.POINTER(C.c_uint16)
+
+
+def _f32(a, n: Optional[int] = None, name: str = "array"):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    if n is not None and a.size != n:
+        raise ValueError(f"{name}: expected {n} float32 values, got {a.size}")
+    return a
+
+
+def _fp(a):
+    return a.ctypes.data_as(_F)
+
+
+def _i32(a):
+    a = np.ascontiguousarray(a, dtype=np.int32)
+    return a, a.ctypes.data_as(_I)
+
+
+def _u16(a, n: int, name: str):
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    if a.size != n:
+        raise ValueError(f"{name}: expected {n} bf16 values, got {a.size}")
+    return a
+
+
+class Ctx:
+    """One attention backend context on one GPU."""
+
+    def __init__(self, **overrides):
+        L = lib()
+        cfg = Config()
+        L.mfc_default_config(C.byref(cfg))
+        explicit_batch = "max_batch" in overrides
+        for k, v in overrides.items():
+            if not hasattr(cfg, k):
+                raise TypeError(f"unknown config field {k!r}")
+            setattr(cfg, k, v)
+        if not explicit_batch:
+            cfg.max_batch = cfg.num_layers * cfg.n_seqs
+        self._lib = L
+        self._h = L.mfc_open(C.byref(cfg))
+        if not self._h:
+            raise MfcError("mfc_open failed: " + L.mfc_last_error(None).decode())
+        self.cfg = Config()
+        L.mfc_get_config(self._h, C.byref(self.cfg))
+        g = self.cfg
+        self.q_dim = g.num_attn_heads * g.head_dim
+        self.kv_dim = g.num_kv_heads * g.head_dim
+        self.v_heads = g.linear_num_v_heads
+        self.total_value = g.linear_num_v_heads * g.linear_value_dim
+        self.conv_dim = 2 * g.linear_num_k_heads * g.linear_key_dim + self.total_value
+        self.ssm_elems = g.linear_num_v_heads * g.linear_value_dim * g.linear_key_dim
+
+    # -- lifetime -------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.mfc_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def _check(self, rc, what):
+        if rc != 0:
+            raise MfcError(f"{what}: {self._lib.mfc_last_error(self._h).decode()}")
+
+    def is_full_layer(self, layer: int) -> bool:
+        return (layer + 1) % self.cfg.full_attn_interval == 0
+
+    @property
+    def stream(self) -> int:
+        return int(self._lib.mfc_stream(self._h) or 0)
+
+    def synchronize(self):
+        self._check(self._lib.mfc_synchronize(self._h), "mfc_synchronize")
+
+    def set_tuning(self, key: str, value: int):
+        self._check(self._lib.mfc_set_tuning(self._h, key.encode(), int(value)), f"mfc_set_tuning({key})")
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.mfc_launch_count(self._h))
+
+    # -- weights --------------------------------------------------------
+    def set_linear_weights(self, layer: int, conv_w_bf16, a_log, dt_bias_bf16, norm_w_bf16=None):
+        g = self.cfg
+        cw = _u16(conv_w_bf16, self.conv_dim * g.conv_kernel_size, "conv_w_bf16")
+        al = _f32(a_log, g.linear_num_v_heads, "a_log")
+        dt = _u16(dt_bias_bf16, g.linear_num_v_heads, "dt_bias_bf16")
+        nw = None if norm_w_bf16 is None else _u16(norm_w_bf16, g.linear_value_dim, "norm_w_bf16")
+        rc = self._lib.mfc_set_linear_weights(
+            self._h, layer, cw.ctypes.data_as(_U16), _fp(al), dt.ctypes.data_as(_U16),
+            None if nw is None else nw.ctypes.data_as(_U16))
+        self._check(rc, "mfc_set_linear_weights")
+
+    # -- hot path, host arrays -------------------------------------------
+    def full_attn_step(self, layer: int, seq_id: int, pos: int, q, gate, k, v) -> np.ndarray:
+        q = _f32(q, self.q_dim, "q")
+        gate = _f32(gate, self.q_dim, "gate")
+        k = _f32(k, self.kv_dim, "k")
+        v = _f32(v, self.kv_dim, "v")
+        out = np.empty(self.q_dim, np.float32)
+        rc = self._lib.mfc_full_attn_step(self._h, layer, seq_id, pos, _fp(q), _fp(gate), _fp(k), _fp(v), _fp(out))
+        self._check(rc, "mfc_full_attn_step")
+        return out
+
+    def linear_attn_step(self, layer: int, seq_id: int, qkv, z, alpha, beta) -> np.ndarray:
+        qkv = _f32(qkv, self.conv_dim, "qkv")
+        z = None if z is None else _f32(z, self.total_value, "z")
+        alpha = _f32(alpha, self.v_heads, "alpha")
+        beta = _f32(beta, self.v_heads, "beta")
+        out = np.empty(self.total_value, np.float32)
+        rc = self._lib.mfc_linear_attn_step(self._h, layer, seq_id, _fp(qkv), None if z is None else _fp(z),
+                                            _fp(alpha), _fp(beta), _fp(out))
+        self._check(rc, "mfc_linear_attn_step")
+        return out
+
+    def full_attn_step_batched(self, layers, seq_ids, pos, q, gate, k, v, out=None) -> np.ndarray:
+        la, lp = _i32(layers)
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos)
+        n = la.size
+        q = _f32(q, n * self.q_dim, "q")
+        gate = _f32(gate, n * self.q_dim, "gate")
+        k = _f32(k, n * self.kv_dim, "k")
+        v = _f32(v, n * self.kv_dim, "v")
+        if out is None:
+            out = np.empty((n, self.q_dim), np.float32)
+        rc = self._lib.mfc_full_attn_step_batched(self._h, n, lp, sp, pp, _fp(q), _fp(gate), _fp(k), _fp(v), _fp(out))
+        self._check(rc, "mfc_full_attn_step_batched")
+        return out
+
+    def linear_attn_step_batched(self, layers, seq_ids, qkv, z, alpha, beta, out=None) -> np.ndarray:
+        la, lp = _i32(layers)
+        sa, sp = _i32(seq_ids)
+        n = la.size
+        qkv = _f32(qkv, n * self.conv_dim, "qkv")
+        z = None if z is None else _f32(z, n * self.total_value, "z")
+        alpha = _f32(alpha, n * self.v_heads, "alpha")
+        beta = _f32(beta, n * self.v_heads, "beta")
+        if out is None:
+            out = np.empty((n, self.total_value), np.float32)
+        rc = self._lib.mfc_linear_attn_step_batched(self._h, n, lp, sp, _fp(qkv), None if z is None else _fp(z),
+                                                    _fp(alpha), _fp(beta), _fp(out))
+        self._check(rc, "mfc_linear_attn_step_batched")
+        return out
+
+    # raw-pointer forms of the two batched host calls (pinned buffers, no numpy work per call)
+    def full_attn_step_batched_ptr(self, n, layers_p, seqs_p, pos_p, q_p, gate_p, k_p, v_p, out_p):
+        rc = self._lib.mfc_full_attn_step_batched(self._h, n, C.cast(layers_p, _I), C.cast(seqs_p, _I),
+                                                  C.cast(pos_p, _I), C.cast(q_p, _F), C.cast(gate_p, _F),
+                                                  C.cast(k_p, _F), C.cast(v_p, _F), C.cast(out_p, _F))
+        self._check(rc, "mfc_full_attn_step_batched")
+
+    def linear_attn_step_batched_ptr(self, n, layers_p, seqs_p, qkv_p, z_p, alpha_p, beta_p, out_p):
+        rc = self._lib.mfc_linear_attn_step_batched(self._h, n, C.cast(layers_p, _I), C.cast(seqs_p, _I),
+                                                    C.cast(qkv_p, _F), C.cast(z_p, _F) if z_p else None,
+                                                    C.cast(alpha_p, _F), C.cast(beta_p, _F), C.cast(out_p, _F))
+        self._check(rc, "mfc_linear_attn_step_batched")
+
+    # -- hot path, device pointers (asynchronous on self.stream) ------------
+    def full_attn_step_batched_dev(self, layers, seq_ids, pos, q_ptr, gate_ptr, k_ptr, v_ptr, out_ptr):
+        la, lp = _i32(layers)
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos)
+        rc = self._lib.mfc_full_attn_step_batched_dev(self._h, la.size, lp, sp, pp, q_ptr, gate_ptr, k_ptr, v_ptr,
+                                                      out_ptr)
+        self._check(rc, "mfc_full_attn_step_batched_dev")
+
+    def linear_attn_step_batched_dev(self, layers, seq_ids, qkv_ptr, z_ptr, alpha_ptr, beta_ptr, out_ptr):
+        la, lp = _i32(layers)
+        sa, sp = _i32(seq_ids)
+        rc = self._lib.mfc_linear_attn_step_batched_dev(self._h, la.size, lp, sp, qkv_ptr, z_ptr or None, alpha_ptr,
+                                                        beta_ptr, out_ptr)
+        self._check(rc, "mfc_linear_attn_step_batched_dev")
+
+    def full_attn_partial_batched_dev(self, layers, seq_ids, pos, q_ptr, k_ptr, v_ptr, o_ptr, m_ptr, l_ptr):
+        la, lp = _i32(layers)
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos)
+        rc = self._lib.mfc_full_attn_partial_batched_dev(self._h, la.size, lp, sp, pp, q_ptr, k_ptr, v_ptr, o_ptr,
+                                                         m_ptr, l_ptr)
+        self._check(rc, "mfc_full_attn_partial_batched_dev")
+
+    def lse_merge_gate_dev(self, n_parts, n, o_ptr, m_ptr, l_ptr, gate_ptr, out_ptr):
+        rc = self._lib.mfc_lse_merge_gate_dev(self._h, n_parts, n, o_ptr, m_ptr, l_ptr, gate_ptr or None, out_ptr)
+        self._check(rc, "mfc_lse_merge_gate_dev")
+
+    # -- sequence state -----------------------------------------------------
+    def memory_clear(self, seq_id: int = -1):
+        self._lib.mfc_memory_clear(self._h, seq_id)
+
+    def memory_seq_rm(self, seq_id: int, p0: int, p1: int) -> bool:
+        return self._lib.mfc_memory_seq_rm(self._h, seq_id, p0, p1) != 0
+
+    def memory_seq_pos_max(self, seq_id: int = 0) -> int:
+        return int(self._lib.mfc_memory_seq_pos_max(self._h, seq_id))
+
+    def state_size(self, seq_id: int = 0) -> int:
+        return int(self._lib.mfc_state_size(self._h, seq_id))
+
+    def state_save(self, seq_id: int = 0) -> bytes:
+        n = self.state_size(seq_id)
+        buf = np.empty(n, np.uint8)
+        wrote = self._lib.mfc_state_save(self._h, seq_id, buf.ctypes.data, n)
+        if wrote < 0:
+            raise MfcError("mfc_state_save: " + self._lib.mfc_last_error(self._h).decode())
+        return buf[:wrote].tobytes()
+
+    def state_save_into(self, seq_id: int, buf: np.ndarray) -> int:
+        return int(self._lib.mfc_state_save(self._h, seq_id, buf.ctypes.data, buf.nbytes))
+
+    def state_load(self, seq_id: int, data) -> None:
+        arr = np.frombuffer(data, dtype=np.uint8)
+        rc = self._lib.mfc_state_load(self._h, seq_id, arr.ctypes.data if arr.size else None, arr.size)
+        self._check(rc, "mfc_state_load")
+
+    # -- parity hooks ---------------------------------------------------------
+    def apply_rotary_emb(self, pos: int, q, k):
+        q = np.array(q, np.float32, copy=True).reshape(-1)
+        k = np.array(k, np.float32, copy=True).reshape(-1)
+        if q.size != self.q_dim or k.size != self.kv_dim:
+            raise ValueError("apply_rotary_emb: wrong q/k length")
+        self._check(self._lib.mfc_apply_rotary_emb(self._h, pos, _fp(q), _fp(k)), "mfc_apply_rotary_emb")
+        return q, k
+
+    def sdpa(self, kv_len: int, q, gate, k_cache, v_cache) -> np.ndarray:
+        q = _f32(q, self.q_dim, "q")
+        gate = _f32(gate, self.q_dim, "gate")
+        kc = _f32(k_cache)
+        vc = _f32(v_cache)
+        if kv_len > 0 and (kc.size < kv_len * self.kv_dim or vc.size < kv_len * self.kv_dim):
+            raise ValueError("sdpa: cache shorter than kv_len rows")
+        out = np.empty(self.q_dim, np.float32)
+        self._check(self._lib.mfc_sdpa(self._h, kv_len, _fp(q), _fp(gate), _fp(kc), _fp(vc), _fp(out)), "mfc_sdpa")
+        return out
+
+    def linear_attn_step_stateless(self, layer: int, qkv, z, alpha, beta, conv_state, ssm_state):
+        """Returns (out, new_conv_state, new_ssm_state); inputs are not modified."""
+        qkv = _f32(qkv, self.conv_dim, "qkv")
+        z = None if z is None else _f32(z, self.total_value, "z")
+        alpha = _f32(alpha, self.v_heads, "alpha")
+        beta = _f32(beta, self.v_heads, "beta")
+        cs = np.array(conv_state, np.float32, copy=True).reshape(-1)
+        ss = np.array(ssm_state, np.float32, copy=True).reshape(-1)
+        if cs.size != 3 * self.conv_dim or ss.size != self.ssm_elems:
+            raise ValueError("linear_attn_step_stateless: wrong state size")
+        out = np.empty(self.total_value, np.float32)
+        rc = self._lib.mfc_linear_attn_step_stateless(self._h, layer, _fp(qkv), None if z is None else _fp(z),
+                                                      _fp(alpha), _fp(beta), _fp(cs), _fp(ss), _fp(out))
+        self._check(rc, "mfc_linear_attn_step_stateless")
+        return out, cs, ss
