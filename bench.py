@@ -1,0 +1,462 @@
+#!/usr/bin/env python
+"""Benchmark of the attention decode path on B200.
+
+Workload ("stack"): the attention sub-blocks of one token step of the 60-layer
+hybrid decode stack -- 45 GatedDeltaNet layer-steps and 15 full-attention GQA
+layer-steps for each of 8 sequences at context 131072, bf16 KV cache, seeded
+N(0,1) activations per (layer, sequence).  One step = 480 layer-steps =
+35.4 GB of algorithmic HBM traffic.  On N GPUs the KV positions of every
+sequence are split block-cyclically over the ranks (one NCCL all-gather of the
+log-sum-exp partials per step, merged and gated by one kernel) and the
+GatedDeltaNet sequences are dealt round-robin; total work is fixed ("strong").
+
+    python bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...     # the CPU restatement, timed on the host cores
+
+Prints ONE JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_LAYERS, INTERVAL = 60, 4
+H, HKV, D = 32, 2, 256
+HV, HK, DK = 64, 16, 128
+CONV_DIM = 2 * HK * DK + HV * DK  # 12288
+Q_DIM, KV_DIM, V_DIM = H * D, HKV * D, HV * DK
+SSM_ELEMS = HV * DK * DK
+FULL_LAYERS = [i for i in range(N_LAYERS) if (i + 1) % INTERVAL == 0]
+LIN_LAYERS = [i for i in range(N_LAYERS) if (i + 1) % INTERVAL != 0]
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")
+    ap.add_argument("--batch", type=int, default=8, help="sequences")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- byte model
+def gdn_bytes_per_item():
+    # state r+w, conv history r (3 rows) + w (1 row), qkv, conv weights, gates, z in, out
+    return 2 * SSM_ELEMS * 4 + 4 * CONV_DIM * 4 + CONV_DIM * 4 + CONV_DIM * 4 * 2 + 4 * HV * 4 + 2 * V_DIM * 4
+
+
+def gqa_bytes_per_item(rows, kv_esize=2):
+    # K and V rows of both kv heads, q/gate/out, k/v in, appended row
+    return 2 * rows * KV_DIM * kv_esize + 3 * Q_DIM * 4 + 2 * KV_DIM * 4 + 2 * KV_DIM * kv_esize
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [l for (t, l) in self.samples if t0 - 0.2 <= t <= t1 + 0.2] or [l for (_, l) in self.samples]
+        for line in rows:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_sample(ctx_len, batch, seed=4):
+    """Times the oracle on a bounded sample of the stack workload and scales to
+    one token step: returns (layer_steps_per_s, cores, description)."""
+    import oracle as O
+    from oracle import A17B as G
+
+    O.build()
+    r = np.random.Generator(np.random.Philox(seed))
+    nrm = lambda *s: r.standard_normal(s, dtype=np.float32)
+    # full attention: one (layer, sequence) item at the full context
+    K = O.round_bf16(nrm(ctx_len, KV_DIM))
+    V = O.round_bf16(nrm(ctx_len, KV_DIM))
+    q, gate, k, v = nrm(Q_DIM), nrm(Q_DIM), nrm(KV_DIM), nrm(KV_DIM)
+    n_gqa = 2
+    t0 = time.perf_counter()
+    for _ in range(n_gqa):
+        O.full_attn_step(ctx_len - 1, ctx_len - 1, q, gate, k, v, K, V, G, kv_bf16=True)
+    t_gqa = (time.perf_counter() - t0) / n_gqa
+    # GatedDeltaNet: one (layer, sequence) item, repeated
+    conv_w = O.f32_to_bf16_bits(nrm(CONV_DIM, 4) * 0.5)
+    a_log = r.uniform(0, 2.7, HV).astype(np.float32)
+    dt_bias = O.f32_to_bf16_bits(nrm(HV))
+    norm_w = O.f32_to_bf16_bits(1 + 0.1 * nrm(DK))
+    conv = nrm(3, CONV_DIM)
+    ssm = nrm(SSM_ELEMS) * np.float32(0.02)
+    n_gdn = 24
+    t0 = time.perf_counter()
+    for _ in range(n_gdn):
+        O.linear_attn_step(nrm(CONV_DIM), nrm(V_DIM), nrm(HV), nrm(HV), conv_w, a_log, dt_bias, norm_w, conv, ssm, G)
+    t_gdn = (time.perf_counter() - t0) / n_gdn
+    n_full_items = len(FULL_LAYERS) * batch
+    n_lin_items = len(LIN_LAYERS) * batch
+    t_step = n_full_items * t_gqa + n_lin_items * t_gdn
+    desc = (f"{n_gqa} GQA layer-steps at ctx {ctx_len} ({t_gqa * 1e3:.1f} ms each) and {n_gdn} GatedDeltaNet "
+            f"layer-steps ({t_gdn * 1e3:.2f} ms each), scaled to {n_full_items}+{n_lin_items} per token step")
+    return (n_full_items + n_lin_items) / t_step, O.num_threads(), desc
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    vals = []
+    cores, desc = 1, ""
+    t_begin = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        v, cores, desc = cpu_sample(args.ctx, args.batch, seed=4 + i)
+        if i >= args.warmup:
+            vals.append(v)
+        if time.perf_counter() - t_begin > 240 and len(vals) >= 1:  # keep the arm within minutes
+            break
+    value = len(vals) / sum(1.0 / v for v in vals)
+    line = {
+        "impl": "reference", "metric": "attention decode layer-steps/sec", "value": value, "unit": "layer-steps/s",
+        "n_gpus": args.gpus, "steps": len(vals), "warmup": args.warmup,
+        "ms_per_step": 1e3 * (len(FULL_LAYERS) + len(LIN_LAYERS)) * args.batch / value,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (bf16 KV values)",
+        "data": "synthetic", "config": workload_config(args, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "layer-steps/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "layer-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, n):
+    return {"workload": f"60-layer hybrid attention-only decode stack (45 GatedDeltaNet + 15 GQA), batch {args.batch}, "
+                        f"ctx {args.ctx}, bf16 KV, fp32 state",
+            "layer_steps_per_step": N_LAYERS * args.batch, "context": args.ctx, "batch": args.batch,
+            "kv_dtype": "bf16", "parallelism": f"kv-sequence split x{n} + GatedDeltaNet sequences round-robin"
+            if n > 1 else "single GPU",
+            "l2": "inputs (GBs of KV and state per step) exceed the 126 MB L2; no flush needed"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import moeflux_b200 as M
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    B, CTX = args.batch, args.ctx
+    W, K = args.warmup, args.steps
+    do_e2e = not args.no_e2e
+    We, Ke = (min(W, 3), K) if do_e2e else (0, 0)
+    total_steps = W + K + We + Ke
+    L0 = CTX - total_steps  # the last timed step brings every cache to exactly CTX rows
+    assert L0 > 0
+
+    ctx = M.Ctx(max_seq=CTX, n_seqs=B, kv_dtype=M.KV_BF16, device=local_rank, kv_rank=rank, kv_world=world,
+                kv_block=256, max_batch=N_LAYERS * B)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+    gen = torch.Generator(device=dev)
+
+    # ---- state: seeded fills on the device, imported through the bulk-import calls ----
+    with torch.cuda.stream(stream):
+        gen.manual_seed(1234)  # same rows on every rank: the ranks hold shares of the same sequences
+        CH = 8192
+        for layer in FULL_LAYERS:
+            for s in range(B):
+                for p0 in range(0, L0, CH):
+                    n = min(CH, L0 - p0)
+                    kr = torch.randn(n, KV_DIM, device=dev, generator=gen)
+                    vr = torch.randn(n, KV_DIM, device=dev, generator=gen)
+                    ctx.kv_append_rows_dev(layer, s, p0, n, kr.data_ptr(), vr.data_ptr())
+                    stream.synchronize()
+        my_seqs = [s for s in range(B) if s % world == rank]
+        rs = np.random.Generator(np.random.Philox(77))
+        for layer in LIN_LAYERS:
+            conv_w = (rs.standard_normal((CONV_DIM, 4), dtype=np.float32) * 0.5)
+            conv_w_bits = (torch.tensor(conv_w).bfloat16().view(torch.int16).numpy().astype(np.uint16))
+            a_log = rs.uniform(0, 2.7, HV).astype(np.float32)
+            dt_bits = torch.tensor(rs.standard_normal(HV, dtype=np.float32)).bfloat16().view(torch.int16).numpy().astype(np.uint16)
+            nw_bits = torch.tensor(1 + 0.1 * rs.standard_normal(DK, dtype=np.float32)).bfloat16().view(torch.int16).numpy().astype(np.uint16)
+            ctx.set_linear_weights(layer, conv_w_bits, a_log, dt_bits, nw_bits)
+            for s in my_seqs:
+                cs = torch.randn(3, CONV_DIM, device=dev, generator=gen)
+                ss = torch.randn(SSM_ELEMS, device=dev, generator=gen) * 0.02
+                ctx.linear_state_set_dev(layer, s, cs.data_ptr(), ss.data_ptr())
+                stream.synchronize()
+
+    # ---- items ----
+    gqa_items = [(l, s) for l in FULL_LAYERS for s in range(B)]
+    gdn_items = [(l, s) for l in LIN_LAYERS for s in my_seqs]
+    ng, nl = len(gqa_items), len(gdn_items)
+    g_layers = np.array([l for l, _ in gqa_items], np.int32)
+    g_seqs = np.array([s for _, s in gqa_items], np.int32)
+    l_layers = np.array([l for l, _ in gdn_items], np.int32)
+    l_seqs = np.array([s for _, s in gdn_items], np.int32)
+
+    with torch.cuda.stream(stream):
+        gen.manual_seed(99)
+        q = torch.randn(ng, Q_DIM, device=dev, generator=gen)
+        gate = torch.randn(ng, Q_DIM, device=dev, generator=gen)
+        kk = torch.randn(ng, KV_DIM, device=dev, generator=gen)
+        vv = torch.randn(ng, KV_DIM, device=dev, generator=gen)
+        out_g = torch.empty(ng, Q_DIM, device=dev)
+        gen.manual_seed(100 + rank)
+        qkv = torch.randn(max(nl, 1), CONV_DIM, device=dev, generator=gen)
+        z = torch.randn(max(nl, 1), V_DIM, device=dev, generator=gen)
+        alpha = torch.randn(max(nl, 1), HV, device=dev, generator=gen)
+        beta = torch.randn(max(nl, 1), HV, device=dev, generator=gen)
+        out_l = torch.empty(max(nl, 1), V_DIM, device=dev)
+        if world > 1:
+            part_floats = ng * H * D + 2 * ng * H
+            part = torch.empty(part_floats, device=dev)
+            gathered = torch.empty(world * part_floats, device=dev)
+    stream.synchronize()
+
+    pos_now = [L0]
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    gqa_events = []
+
+    def device_step(timed):
+        pos = np.full(ng, pos_now[0], np.int32)
+        if nl:
+            ctx.linear_attn_step_batched_dev(l_layers, l_seqs, qkv.data_ptr(), z.data_ptr(), alpha.data_ptr(),
+                                             beta.data_ptr(), out_l.data_ptr())
+        if timed:
+            e0, e1 = ev(), ev()
+            e0.record(stream)
+        if world == 1:
+            ctx.full_attn_step_batched_dev(g_layers, g_seqs, pos, q.data_ptr(), gate.data_ptr(), kk.data_ptr(),
+                                           vv.data_ptr(), out_g.data_ptr())
+            if timed:
+                e1.record(stream)
+        else:
+            o_ptr = part.data_ptr()
+            m_ptr = o_ptr + 4 * ng * H * D
+            l_ptr = m_ptr + 4 * ng * H
+            ctx.full_attn_partial_batched_dev(g_layers, g_seqs, pos, q.data_ptr(), kk.data_ptr(), vv.data_ptr(), o_ptr,
+                                              m_ptr, l_ptr)
+            if timed:
+                e1.record(stream)
+            dist.all_gather_into_tensor(gathered, part)
+            go = gathered.data_ptr()
+            ctx.lse_merge_gate_dev(world, ng, go, go + 4 * ng * H * D, go + 4 * ng * H * D + 4 * ng * H,
+                                   gate.data_ptr(), out_g.data_ptr(), part_stride=part_floats)
+        if timed:
+            gqa_events.append((e0, e1))
+        pos_now[0] += 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    with torch.cuda.stream(stream):
+        for _ in range(W):
+            device_step(False)
+        barrier()
+        if sampler:
+            sampler.start()
+            time.sleep(0.3)
+        launches0 = ctx.launch_count
+        t_wall0 = time.time()
+        start, stop = ev(), ev()
+        start.record(stream)
+        for _ in range(K):
+            device_step(True)
+        stop.record(stream)
+        barrier()
+        t_wall1 = time.time()
+        launches = ctx.launch_count - launches0
+    ctx.synchronize()  # raises if a kernel reported a fault
+    ms = start.elapsed_time(stop)
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+    gqa_ms = sum(a.elapsed_time(b) for a, b in gqa_events) / len(gqa_events)
+    if world > 1:
+        t = torch.tensor([ms, gqa_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, gqa_ms = float(t[0]), float(t[1])
+
+    # ---- end to end: host (pinned) inputs in, host outputs back, every step ----
+    e2e = None
+    if do_e2e:
+        pin = lambda *shape: torch.empty(*shape, dtype=torch.float32).pin_memory()
+        hq, hgate, hk, hv, hout = pin(ng, Q_DIM), pin(ng, Q_DIM), pin(ng, KV_DIM), pin(ng, KV_DIM), pin(ng, Q_DIM)
+        hqkv, hz, ha, hb, hlo = pin(max(nl, 1), CONV_DIM), pin(max(nl, 1), V_DIM), pin(max(nl, 1), HV), pin(
+            max(nl, 1), HV), pin(max(nl, 1), V_DIM)
+        for h, d_ in ((hq, q), (hgate, gate), (hk, kk), (hv, vv), (hqkv, qkv), (hz, z), (ha, alpha), (hb, beta)):
+            h.copy_(d_.cpu())
+        h2d = 4 * (2 * ng * Q_DIM + 2 * ng * KV_DIM + nl * (CONV_DIM + V_DIM + 2 * HV))
+        d2h = 4 * (ng * Q_DIM + nl * V_DIM)
+
+        def e2e_step():
+            pos = np.full(ng, pos_now[0], np.int32)
+            if world == 1:
+                if nl:
+                    ctx.linear_attn_step_batched_ptr(nl, l_layers.ctypes.data, l_seqs.ctypes.data, hqkv.data_ptr(),
+                                                     hz.data_ptr(), ha.data_ptr(), hb.data_ptr(), hlo.data_ptr())
+                ctx.full_attn_step_batched_ptr(ng, g_layers.ctypes.data, g_seqs.ctypes.data, pos.ctypes.data,
+                                               hq.data_ptr(), hgate.data_ptr(), hk.data_ptr(), hv.data_ptr(),
+                                               hout.data_ptr())
+                pos_now[0] += 1
+            else:
+                with torch.cuda.stream(stream):
+                    q.copy_(hq, non_blocking=True)
+                    gate.copy_(hgate, non_blocking=True)
+                    kk.copy_(hk, non_blocking=True)
+                    vv.copy_(hv, non_blocking=True)
+                    if nl:
+                        qkv.copy_(hqkv, non_blocking=True)
+                        z.copy_(hz, non_blocking=True)
+                        alpha.copy_(ha, non_blocking=True)
+                        beta.copy_(hb, non_blocking=True)
+                    device_step(False)
+                    hout.copy_(out_g, non_blocking=True)
+                    if nl:
+                        hlo.copy_(out_l, non_blocking=True)
+                    stream.synchronize()
+
+        for _ in range(We):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(Ke):
+            e2e_step()
+        barrier()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t[0])
+        e2e = {"value": N_LAYERS * B * Ke / dt, "unit": "layer-steps/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * dt / Ke, "steps": Ke}
+        ctx.synchronize()
+
+    # ---- roofline of the dominant kernel (the GQA split-K decode launch of this rank) ----
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs (of measured)"
+    else:
+        peak, peak_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
+    mean_pos = L0 + W + (K - 1) / 2.0
+    rows_local = (mean_pos + 1) / world
+    gqa_alg_bytes = ng * gqa_bytes_per_item(rows_local)
+    achieved = gqa_alg_bytes / (gqa_ms * 1e-3) / 1e9
+    step_bytes = ng * gqa_bytes_per_item(mean_pos + 1) + (len(LIN_LAYERS) * B) * gdn_bytes_per_item()
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "gqa_decode_bf16_traffic.json")
+    if os.path.exists(tpath):
+        tj = json.load(open(tpath))
+        traffic = tj["dram_bytes_per_kv_row_per_head_pair"] * rows_local * ng if "dram_bytes_per_kv_row_per_head_pair" in tj else None
+    roofline = {"bound": "hbm", "kernel": "gqa_decode_bf16_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
+                "algorithmic_bytes_per_launch": gqa_alg_bytes, "ms_per_launch": gqa_ms,
+                "frac_of_8TBps": achieved / 8000.0,
+                "whole_step": {"algorithmic_bytes": step_bytes, "GBps": step_bytes / (ms / K * 1e-3) / 1e9,
+                               "frac_of_measured": step_bytes / (ms / K * 1e-3) / 1e9 / peak,
+                               "frac_of_8TBps": step_bytes / (ms / K * 1e-3) / 1e9 / 8000.0}}
+
+    line = None
+    if rank == 0:
+        value = N_LAYERS * B * K / (ms * 1e-3)
+        line = {"metric": "attention decode layer-steps/sec", "value": value, "unit": "layer-steps/s", "n_gpus": world,
+                "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16 KV, fp32 accumulate and state", "data": "synthetic",
+                "config": workload_config(args, world), "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches),
+                "clocks": clocks}
+    ctx.close()
+    return line
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path "
+                         "(use --impl reference for the CPU restatement)")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
+    line = run_ours(args, rank, world, local_rank)
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, desc = cpu_sample(args.ctx, args.batch)
+            line["cpu_baseline"] = {"value": v, "unit": "layer-steps/s", "cores": cores, "kind": "port", "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

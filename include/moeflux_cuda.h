@@ -157,10 +157,25 @@ int mfc_full_attn_partial_batched_dev(mfc_ctx *ctx, int32_t n, const int32_t *la
                                       const float *k, const float *v, float *o_part,
                                       float *m_part, float *l_part);
 /* out[i,h,:] = (sum_r e^{m_r-M} o_r / sum_r e^{m_r-M} l_r) * sigmoid(gate[i,h,:]),
- * partials laid out [n_parts][n][heads][...]; gate may be NULL (no gate). */
+ * part r of o/m/l starts part_stride floats after part r-1 (so one gathered
+ * buffer [n_parts][o | m | l] works); part_stride 0 = densely packed
+ * [n_parts][n][heads][...].  gate may be NULL (no gate). */
 int mfc_lse_merge_gate_dev(mfc_ctx *ctx, int32_t n_parts, int32_t n, const float *o_parts,
-                           const float *m_parts, const float *l_parts, const float *gate,
-                           float *out);
+                           const float *m_parts, const float *l_parts, size_t part_stride,
+                           const float *gate, float *out);
+
+/* Bulk import of state that already exists on the device (what a prefill, or a
+ * prefix cache, hands over; the reference fills the same state token by token,
+ * crates/moeflux/src/riir/mod.rs:1206-1212).  Asynchronous on mfc_stream(ctx).
+ * kv_append_rows: rows [pos0, pos0+n_rows) of a full-attention layer, post-RoPE
+ * K and V as [n_rows][num_kv_heads*head_dim] fp32; pos0 must equal the current
+ * length; a context of a KV split keeps only the rows it owns.
+ * linear_state_set: conv history [3][conv_dim] (oldest first) and ssm state
+ * [v_heads][value][key] of a GatedDeltaNet layer. */
+int mfc_kv_append_rows_dev(mfc_ctx *ctx, int32_t layer, int32_t seq_id, int32_t pos0,
+                           int32_t n_rows, const float *k_rows, const float *v_rows);
+int mfc_linear_state_set_dev(mfc_ctx *ctx, int32_t layer, int32_t seq_id,
+                             const float *conv_state, const float *ssm_state);
 
 /* ------------------------------------------------------------------------
  * Sequence state: mf_memory_clear / mf_memory_seq_rm / mf_memory_seq_pos_max

@@ -740,14 +740,15 @@ int mfc_full_attn_partial_batched_dev(mfc_ctx *c, int32_t n, const int32_t *laye
 }
 
 int mfc_lse_merge_gate_dev(mfc_ctx *c, int32_t n_parts, int32_t n, const float *o_parts, const float *m_parts,
-                           const float *l_parts, const float *gate, float *out) {
+                           const float *l_parts, size_t part_stride, const float *gate, float *out) {
     if (!c) return -1;
     if (n_parts <= 0 || n <= 0 || !o_parts || !m_parts || !l_parts || !out) {
         fail(c, "bad argument");
         return -1;
     }
     cudaSetDevice(c->cfg.device);
-    CK(launch_lse_merge_gate(n_parts, n, c->cfg.num_attn_heads, o_parts, m_parts, l_parts, gate, out, c->stream));
+    CK(launch_lse_merge_gate(n_parts, n, c->cfg.num_attn_heads, o_parts, m_parts, l_parts, part_stride, gate, out,
+                             c->stream));
     c->launches += 1;
     return 0;
 }
@@ -834,6 +835,65 @@ int mfc_linear_attn_step_batched(mfc_ctx *c, int32_t n, const int32_t *layers, c
 int mfc_linear_attn_step(mfc_ctx *c, int32_t layer, int32_t seq_id, const float *qkv, const float *z,
                          const float *alpha, const float *beta, float *out) {
     return mfc_linear_attn_step_batched(c, 1, &layer, &seq_id, qkv, z, alpha, beta, out);
+}
+
+// ---------------------------------------------------------------- bulk state import (device)
+
+int mfc_kv_append_rows_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, int32_t pos0, int32_t n_rows,
+                           const float *k_rows, const float *v_rows) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (!k_rows || !v_rows || n_rows <= 0) {
+        fail(c, "bad argument");
+        return -1;
+    }
+    if (layer < 0 || layer >= g.num_layers || !is_full_layer(g, layer) || seq_id < 0 || seq_id >= g.n_seqs) {
+        fail(c, "not a full-attention layer / seq_id out of range");
+        return -1;
+    }
+    const int slot = c->layer_to_full[layer] * g.n_seqs + seq_id;
+    if (pos0 != c->kv_len[slot]) {
+        fail(c, "pos0 " + std::to_string(pos0) + " != current length " + std::to_string(c->kv_len[slot]));
+        return -1;
+    }
+    if ((long long)pos0 + n_rows > g.max_seq) {
+        fail(c, "kv cache overflow");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    const size_t slot_off = (size_t)slot * g.num_kv_heads * c->cap_rows * HEAD_DIM * c->kv_esize;
+    CK(launch_kv_pack(k_rows, (uint8_t *)c->k_cache + slot_off, n_rows, g.num_kv_heads, c->cap_rows,
+                      g.kv_dtype == MFC_KV_BF16, pos0, g.kv_rank, g.kv_world, g.kv_block, c->stream));
+    CK(launch_kv_pack(v_rows, (uint8_t *)c->v_cache + slot_off, n_rows, g.num_kv_heads, c->cap_rows,
+                      g.kv_dtype == MFC_KV_BF16, pos0, g.kv_rank, g.kv_world, g.kv_block, c->stream));
+    c->launches += 2;
+    c->kv_len[slot] += n_rows;
+    return 0;
+}
+
+int mfc_linear_state_set_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, const float *conv_state,
+                             const float *ssm_state) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (!conv_state || !ssm_state) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (layer < 0 || layer >= g.num_layers || is_full_layer(g, layer) || seq_id < 0 || seq_id >= g.n_seqs) {
+        fail(c, "not a linear-attention layer / seq_id out of range");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    const int slot = c->layer_to_lin[layer] * g.n_seqs + seq_id;
+    const size_t ssm_elems = (size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM;
+    float *ring = c->conv + (size_t)slot * CONV_TAPS * c->conv_dim;
+    CK(cudaMemsetAsync(ring, 0, sizeof(float) * c->conv_dim, c->stream));
+    CK(cudaMemcpyAsync(ring + c->conv_dim, conv_state, sizeof(float) * 3 * c->conv_dim, cudaMemcpyDeviceToDevice,
+                       c->stream));
+    CK(cudaMemcpyAsync(c->ssm + (size_t)slot * ssm_elems, ssm_state, sizeof(float) * ssm_elems,
+                       cudaMemcpyDeviceToDevice, c->stream));
+    c->conv_step[slot] = 0;
+    return 0;
 }
 
 // ---------------------------------------------------------------- sequence state
@@ -994,7 +1054,7 @@ int mfc_state_load(mfc_ctx *c, int32_t seq_id, const void *buf, size_t buf_len) 
                     CK(cudaMemcpyAsync(c->st_rows, in + off, sizeof(float) * kvd * nr, cudaMemcpyHostToDevice,
                                        c->stream));
                     CK(launch_kv_pack(c->st_rows, cache, nr, g.num_kv_heads, c->cap_rows,
-                                      g.kv_dtype == MFC_KV_BF16, r0, c->stream));
+                                      g.kv_dtype == MFC_KV_BF16, r0, 0, 1, 1, c->stream));
                     c->launches += 1;
                     CK(cudaStreamSynchronize(c->stream));
                     off += sizeof(float) * kvd * nr;
@@ -1084,7 +1144,7 @@ int mfc_sdpa(mfc_ctx *c, int32_t kv_len, const float *q, const float *q_gate, co
             CK(cudaMemcpyAsync(c->st_rows, src + (size_t)r0 * kvd, sizeof(float) * kvd * nr, cudaMemcpyHostToDevice,
                                c->stream));
             CK(launch_kv_pack(c->st_rows, cache, nr, g.num_kv_heads, c->cap_rows, g.kv_dtype == MFC_KV_BF16, r0,
-                              c->stream));
+                              0, 1, 1, c->stream));
             c->launches += 1;
             CK(cudaStreamSynchronize(c->stream));
         }

@@ -268,11 +268,11 @@ constexpr size_t BF16_SMEM = 1024 + (size_t)BF16_STAGES * 2 * TILE_BYTES_BF16 +
 // ---- stand-alone merge of gathered partials (cross-GPU KV split) ----------
 __global__ void __launch_bounds__(128)
 lse_merge_gate_kernel(int n_parts, int n, int H, const float *o_parts, const float *m_parts,
-                      const float *l_parts, const float *gate, float *out) {
+                      const float *l_parts, size_t stride_o, size_t stride_ml, const float *gate,
+                      float *out) {
     // one CTA per (item, head); 128 threads x 2 dims
     const int ih = blockIdx.x;  // item * H + head
     const int tid = threadIdx.x;
-    const size_t stride_ml = (size_t)n * H;
     float M = -INFINITY;
     for (int r = 0; r < n_parts; r++) M = fmaxf(M, m_parts[r * stride_ml + ih]);
     float Ls = 0.0f;
@@ -282,7 +282,7 @@ lse_merge_gate_kernel(int n_parts, int n, int H, const float *o_parts, const flo
         const float w = (m == -INFINITY) ? 0.0f : expf(m - M);
         Ls += w * l_parts[r * stride_ml + ih];
         const float2 o = *reinterpret_cast<const float2 *>(
-            o_parts + (r * stride_ml + ih) * HEAD_DIM + 2 * tid);
+            o_parts + r * stride_o + (size_t)ih * HEAD_DIM + 2 * tid);
         acc.x = fmaf(w, o.x, acc.x);
         acc.y = fmaf(w, o.y, acc.y);
     }
@@ -317,14 +317,22 @@ __global__ void rope_kernel(float *q, float *k, int H, int Hkv, int rotary_dim, 
 // ---- cache <-> wire layout ----------------------------------------------------
 // wire rows: [row][Hkv][256] fp32; cache: [Hkv][cap_rows][256] of the storage type
 __global__ void kv_pack_kernel(const float *src, void *dst, int n_rows, int Hkv, int cap_rows,
-                               int kv_bf16, int dst_row0) {
+                               int kv_bf16, int pos0, int rank, int world, int block) {
+    // wire row i holds whole-sequence position pos0 + i; a context of a KV split
+    // keeps only the positions of its own blocks
     const size_t total = (size_t)n_rows * Hkv * HEAD_DIM;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const int d = (int)(idx % HEAD_DIM);
         const int hh = (int)((idx / HEAD_DIM) % Hkv);
-        const size_t row = idx / ((size_t)HEAD_DIM * Hkv);
-        const size_t o = ((size_t)hh * cap_rows + dst_row0 + row) * HEAD_DIM + d;
+        const int pos = pos0 + (int)(idx / ((size_t)HEAD_DIM * Hkv));
+        int row = pos;
+        if (world > 1) {
+            const int blk = pos / block;
+            if (blk % world != rank) continue;
+            row = (blk / world) * block + pos % block;
+        }
+        const size_t o = ((size_t)hh * cap_rows + row) * HEAD_DIM + d;
         if (kv_bf16) reinterpret_cast<__nv_bfloat16 *>(dst)[o] = __float2bfloat16_rn(src[idx]);
         else reinterpret_cast<float *>(dst)[o] = src[idx];
     }
@@ -358,10 +366,12 @@ cudaError_t launch_gqa_decode_bf16(const CUtensorMap &kmap, const CUtensorMap &v
 }
 
 cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
-                                  const float *m_parts, const float *l_parts, const float *gate,
-                                  float *out, cudaStream_t stream) {
+                                  const float *m_parts, const float *l_parts, size_t part_stride,
+                                  const float *gate, float *out, cudaStream_t stream) {
     if (n <= 0) return cudaSuccess;
-    lse_merge_gate_kernel<<<n * H, 128, 0, stream>>>(n_parts, n, H, o_parts, m_parts, l_parts, gate, out);
+    const size_t so = part_stride ? part_stride : (size_t)n * H * HEAD_DIM;
+    const size_t sml = part_stride ? part_stride : (size_t)n * H;
+    lse_merge_gate_kernel<<<n * H, 128, 0, stream>>>(n_parts, n, H, o_parts, m_parts, l_parts, so, sml, gate, out);
     return cudaGetLastError();
 }
 
@@ -374,11 +384,13 @@ cudaError_t launch_rope(float *q, float *k, int H, int Hkv, int rotary_dim, int 
 }
 
 cudaError_t launch_kv_pack(const float *src_rows, void *dst_cache, int n_rows, int Hkv,
-                           int cap_rows, int kv_bf16, int dst_row0, cudaStream_t stream) {
+                           int cap_rows, int kv_bf16, int pos0, int rank, int world, int block,
+                           cudaStream_t stream) {
     if (n_rows <= 0) return cudaSuccess;
     const size_t total = (size_t)n_rows * Hkv * HEAD_DIM;
     const int blocks = (int)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
-    kv_pack_kernel<<<blocks, 256, 0, stream>>>(src_rows, dst_cache, n_rows, Hkv, cap_rows, kv_bf16, dst_row0);
+    kv_pack_kernel<<<blocks, 256, 0, stream>>>(src_rows, dst_cache, n_rows, Hkv, cap_rows, kv_bf16, pos0, rank,
+                                               world, block);
     return cudaGetLastError();
 }
 cudaError_t launch_kv_unpack(const void *src_cache, float *dst_rows, int n_rows, int Hkv,

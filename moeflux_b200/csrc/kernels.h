@@ -87,10 +87,11 @@ cudaError_t launch_gqa_decode_f32(const CUtensorMap &kmap, const CUtensorMap &vm
 cudaError_t gqa_decode_configure();
 cudaError_t gqa_decode_f32_configure();
 
-// Merge of gathered partials: [n_parts][n][H][256] etc.
+// Merge of gathered partials.  Part r of o/m/l starts part_stride floats after
+// part r-1; part_stride 0 means densely packed [n_parts][n][H][256] / [n_parts][n][H].
 cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
-                                  const float *m_parts, const float *l_parts, const float *gate,
-                                  float *out, cudaStream_t stream);
+                                  const float *m_parts, const float *l_parts, size_t part_stride,
+                                  const float *gate, float *out, cudaStream_t stream);
 
 // RoPE on packed q [H][256], k [Hkv][256] in place (parity hook).
 cudaError_t launch_rope(float *q, float *k, int H, int Hkv, int rotary_dim, int pos,
@@ -98,8 +99,11 @@ cudaError_t launch_rope(float *q, float *k, int H, int Hkv, int rotary_dim, int 
 
 // Layout conversions between the wire/reference layout [pos][kv_head][256] fp32
 // and the cache layout [kv_head][row][256] of the context's storage type.
+// Wire row i is whole-sequence position pos0 + i; with world > 1 only the rows
+// of this rank's blocks are stored (block-cyclic split).
 cudaError_t launch_kv_pack(const float *src_rows, void *dst_cache, int n_rows, int Hkv,
-                           int cap_rows, int kv_bf16, int dst_row0, cudaStream_t stream);
+                           int cap_rows, int kv_bf16, int pos0, int rank, int world, int block,
+                           cudaStream_t stream);
 cudaError_t launch_kv_unpack(const void *src_cache, float *dst_rows, int n_rows, int Hkv,
                              int cap_rows, int kv_bf16, cudaStream_t stream);
 

@@ -209,9 +209,19 @@ class Ctx:
                                                          m_ptr, l_ptr)
         self._check(rc, "mfc_full_attn_partial_batched_dev")
 
-    def lse_merge_gate_dev(self, n_parts, n, o_ptr, m_ptr, l_ptr, gate_ptr, out_ptr):
-        rc = self._lib.mfc_lse_merge_gate_dev(self._h, n_parts, n, o_ptr, m_ptr, l_ptr, gate_ptr or None, out_ptr)
+    def lse_merge_gate_dev(self, n_parts, n, o_ptr, m_ptr, l_ptr, gate_ptr, out_ptr, part_stride=0):
+        rc = self._lib.mfc_lse_merge_gate_dev(self._h, n_parts, n, o_ptr, m_ptr, l_ptr, part_stride,
+                                              gate_ptr or None, out_ptr)
         self._check(rc, "mfc_lse_merge_gate_dev")
+
+    # -- bulk state import from device memory ------------------------------------
+    def kv_append_rows_dev(self, layer, seq_id, pos0, n_rows, k_rows_ptr, v_rows_ptr):
+        rc = self._lib.mfc_kv_append_rows_dev(self._h, layer, seq_id, pos0, n_rows, k_rows_ptr, v_rows_ptr)
+        self._check(rc, "mfc_kv_append_rows_dev")
+
+    def linear_state_set_dev(self, layer, seq_id, conv_ptr, ssm_ptr):
+        rc = self._lib.mfc_linear_state_set_dev(self._h, layer, seq_id, conv_ptr, ssm_ptr)
+        self._check(rc, "mfc_linear_state_set_dev")
 
     # -- sequence state -----------------------------------------------------
     def memory_clear(self, seq_id: int = -1):

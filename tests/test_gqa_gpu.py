@@ -1,0 +1,233 @@
+"""GPU parity of the full-attention path (RoPE, append, split-K SDPA, sigmoid
+gate) against the CPU oracle, through the C ABI.  Probe points follow the
+reference's tests: kv_len {1, 8, 32, 33, 64, 128, 512}, pos {0, 1, 17, 1024,
+65535} (crates/moeflux/tests/diff_oracle.rs:1379-1442, 1541-1615, 2712-2955,
+3505-3654)."""
+import numpy as np
+import pytest
+
+import moeflux_b200 as M
+import oracle as O
+from oracle import A17B as G
+from tests import inputs as I
+from tests.gpu_common import TOL_BF16, TOL_F32, make_pair
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def f32_pair():
+    ctx, orc = make_pair(max_seq=1024, n_seqs=2, linear_layers=[])
+    yield ctx, orc
+    ctx.close()
+
+
+@pytest.fixture(scope="module")
+def bf16_pair():
+    ctx, orc = make_pair(max_seq=4096, n_seqs=2, kv_bf16=True, linear_layers=[])
+    yield ctx, orc
+    ctx.close()
+
+
+@pytest.mark.parametrize("pos", [0, 1, 17, 1024, 65535])
+def test_rope_hook(f32_pair, pos):
+    ctx, _ = f32_pair
+    q = I.ramp_sin(G.q_dim, 0.013, 0.7, 0.1)
+    k = I.ramp_cos(G.kv_dim, 0.019, 0.5, -0.2)
+    gq, gk = ctx.apply_rotary_emb(pos, q, k)
+    rq, rk = O.apply_rotary_emb(pos, q, k)
+    if pos == 0:
+        assert np.array_equal(gq, q) and np.array_equal(gk, k)
+    # the reference's own bound is 128 ULP; near 1.0 that is 1.5e-5
+    assert np.max(np.abs(gq - rq)) <= 2e-6 and np.max(np.abs(gk - rk)) <= 2e-6
+
+
+def test_rope_hook_rejects_negative_pos(f32_pair):
+    ctx, _ = f32_pair
+    with pytest.raises(M.MfcError):
+        ctx.apply_rotary_emb(-1, np.zeros(G.q_dim, np.float32), np.zeros(G.kv_dim, np.float32))
+
+
+@pytest.mark.parametrize("kv_len", [1, 8, 32, 33, 64, 128, 512])
+def test_sdpa_hook_fp32_reference_inputs(f32_pair, kv_len):
+    ctx, _ = f32_pair
+    q = I.ramp_sin(G.q_dim, 0.011, 0.6, 0.05)
+    gate = I.ramp_cos(G.q_dim, 0.007, 1.2, -0.1)
+    K = I.ramp_sin(kv_len * G.kv_dim, 0.013, 0.5, 0.02)
+    V = I.ramp_cos(kv_len * G.kv_dim, 0.017, 0.4, -0.05)
+    got = ctx.sdpa(kv_len, q, gate, K, V)
+    ref = O.sdpa(kv_len, q, gate, K, V)
+    assert np.isfinite(got).all()
+    assert I.cosine(got, ref) >= 0.9999
+    assert I.rel_err(got, ref) <= TOL_F32
+
+
+def test_sdpa_hook_known_answers(f32_pair):
+    ctx, _ = f32_pair
+    r = I.rng(21)
+    q, gate, k, v = I.gqa_step_inputs(r)
+    got = ctx.sdpa(1, q, gate, k, v).reshape(G.num_attn_heads, -1)
+    sig = 1 / (1 + np.exp(-gate.astype(np.float64))).reshape(G.num_attn_heads, -1)
+    ref = np.repeat(v.reshape(G.num_kv_heads, -1), 16, axis=0) * sig
+    assert I.rel_err(got, ref) <= 1e-5
+    n = 100
+    K = np.tile(k, (n, 1))
+    V = I.normal(r, (n, G.kv_dim))
+    got = ctx.sdpa(n, q, gate, K, V).reshape(G.num_attn_heads, -1)
+    ref = np.repeat(V.astype(np.float64).mean(0).reshape(G.num_kv_heads, -1), 16, axis=0) * sig
+    assert I.rel_err(got, ref) <= 1e-4
+    with pytest.raises(M.MfcError):
+        ctx.sdpa(0, q, gate, k, v)
+
+
+@pytest.mark.parametrize("kv_len", [1, 33, 512, 1000])
+def test_sdpa_hook_fp32_seeded_normal(f32_pair, kv_len):
+    ctx, _ = f32_pair
+    r = I.rng(30 + kv_len)
+    q, gate, _, _ = I.gqa_step_inputs(r)
+    K, V = I.normal(r, (kv_len, G.kv_dim)), I.normal(r, (kv_len, G.kv_dim))
+    assert I.rel_err(ctx.sdpa(kv_len, q, gate, K, V), O.sdpa(kv_len, q, gate, K, V)) <= TOL_F32
+
+
+@pytest.mark.parametrize("kv_len", [1, 31, 33, 512, 3000])
+def test_sdpa_hook_bf16_cache(bf16_pair, kv_len):
+    ctx, _ = bf16_pair
+    r = I.rng(40 + kv_len)
+    q, gate, _, _ = I.gqa_step_inputs(r)
+    K, V = I.normal(r, (kv_len, G.kv_dim)), I.normal(r, (kv_len, G.kv_dim))
+    ref = O.sdpa(kv_len, q, gate, O.round_bf16(K), O.round_bf16(V))
+    got = ctx.sdpa(kv_len, q, gate, K, V)
+    assert np.isfinite(got).all()
+    assert I.rel_err(got, ref) <= TOL_BF16
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_split_k_merge_equals_unsplit(f32_pair, bf16_pair, bf16):
+    ctx, _ = bf16_pair if bf16 else f32_pair
+    r = I.rng(50)
+    n = 1000
+    q, gate, _, _ = I.gqa_step_inputs(r)
+    K, V = I.normal(r, (n, G.kv_dim)), I.normal(r, (n, G.kv_dim))
+    ctx.set_tuning("gqa_chunk", 1024)
+    one = ctx.sdpa(n, q, gate, K, V)
+    outs = []
+    for chunk in (32, 96, 512):
+        ctx.set_tuning("gqa_chunk", chunk)
+        outs.append(ctx.sdpa(n, q, gate, K, V))
+    ctx.set_tuning("gqa_chunk", 0)
+    for o in outs:
+        # the split only reorders fp32 sums; with bf16 P the rounding points move too
+        assert I.rel_err(o, one) <= (2e-3 if bf16 else 2e-6)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_decode_steps_from_empty_cache(f32_pair, bf16_pair, bf16):
+    ctx, orc = bf16_pair if bf16 else f32_pair
+    ctx.memory_clear(-1)
+    orc.memory_clear(-1)
+    r = I.rng(60)
+    tol = TOL_BF16 if bf16 else TOL_F32
+    for pos in range(70):  # crosses the 32/64-row tile boundaries
+        for layer, seq in ((3, 0), (59, 1)):
+            q, gate, k, v = I.gqa_step_inputs(r)
+            got = ctx.full_attn_step(layer, seq, pos, q, gate, k, v)
+            ref = orc.full_attn_step(layer, seq, pos, q, gate, k, v)
+            assert I.rel_err(got, ref) <= tol, (pos, layer)
+    assert ctx.memory_seq_pos_max(0) == orc.memory_seq_pos_max(0) == 70
+    assert ctx.memory_seq_pos_max(1) == 70
+
+
+def test_step_argument_errors(f32_pair):
+    ctx, _ = f32_pair
+    ctx.memory_clear(-1)
+    z = np.zeros(G.q_dim, np.float32)
+    kz = np.zeros(G.kv_dim, np.float32)
+    with pytest.raises(M.MfcError, match="not a full-attention layer"):
+        ctx.full_attn_step(0, 0, 0, z, z, kz, kz)
+    with pytest.raises(M.MfcError, match="current length"):
+        ctx.full_attn_step(3, 0, 5, z, z, kz, kz)  # pos must equal the length (full_attn_forward.rs:73-78)
+    with pytest.raises(M.MfcError):
+        ctx.full_attn_step(3, 7, 0, z, z, kz, kz)  # seq_id out of range
+    with pytest.raises(M.MfcError):
+        ctx.linear_attn_step(3, 0, np.zeros(ctx.conv_dim, np.float32), None, np.zeros(64, np.float32),
+                             np.zeros(64, np.float32))  # full layer given to the linear step
+    assert ctx.memory_seq_pos_max(0) == 0  # failed calls changed nothing
+
+
+def test_cache_overflow_is_an_error():
+    ctx, _ = make_pair(max_seq=33, linear_layers=[])
+    r = I.rng(61)
+    for pos in range(33):
+        ctx.full_attn_step(3, 0, pos, *I.gqa_step_inputs(r))
+    with pytest.raises(M.MfcError, match="overflow"):
+        ctx.full_attn_step(3, 0, 33, *I.gqa_step_inputs(r))
+    ctx.close()
+
+
+def test_ragged_batched_decode_bf16():
+    """Batched step over sequences of unequal length (the shape of the ragged
+    64-sequence configuration, scaled down), contexts installed through
+    state_load, several chunks per sequence."""
+    n_seqs = 6
+    ctx, orc = make_pair(max_seq=2048, n_seqs=n_seqs, kv_bf16=True, linear_layers=[])
+    r = I.rng(70)
+    lens = [1, 31, 257, 1024, 1500, 2047]
+    layers = [3, 7]
+    for s, ln in enumerate(lens):
+        for layer in layers:
+            orc.load_kv(layer, s, I.normal(r, (ln, G.kv_dim)), I.normal(r, (ln, G.kv_dim)))
+        ctx.state_load(s, orc.state_save(s))
+    ctx.set_tuning("gqa_target_ctas", 64)  # forces several chunks for the long sequences
+    items = [(l, s) for s in range(n_seqs) for l in layers]
+    for step in range(2):
+        ins = [I.gqa_step_inputs(r) for _ in items]
+        pos = [orc.len[(l, s)] for l, s in items]
+        got = ctx.full_attn_step_batched([l for l, _ in items], [s for _, s in items], pos,
+                                         np.stack([i[0] for i in ins]), np.stack([i[1] for i in ins]),
+                                         np.stack([i[2] for i in ins]), np.stack([i[3] for i in ins]))
+        for j, (l, s) in enumerate(items):
+            ref = orc.full_attn_step(l, s, pos[j], *ins[j])
+            assert I.rel_err(got[j], ref) <= TOL_BF16, (step, l, s)
+    ctx.close()
+
+
+def test_kv_split_partials_merge_to_the_whole():
+    """Two contexts hold the block-cyclic halves of every sequence; their
+    partials merged by log-sum-exp equal the single-context result."""
+    import torch
+
+    dev = torch.device("cuda:0")
+    kw = dict(max_seq=512, n_seqs=2, linear_layers=[])
+    whole, orc = make_pair(**kw)
+    parts = [make_pair(kv_rank=rk, kv_world=2, kv_block=32, **kw)[0] for rk in range(2)]
+    r = I.rng(80)
+    items = [(3, 0), (3, 1), (11, 1)]
+    layers, seqs = [i[0] for i in items], [i[1] for i in items]
+    n = len(items)
+    H, D = G.num_attn_heads, G.head_dim
+    for pos in range(100):
+        ins = [I.gqa_step_inputs(r) for _ in items]
+        q = torch.tensor(np.stack([i[0] for i in ins]), device=dev)
+        gate = torch.tensor(np.stack([i[1] for i in ins]), device=dev)
+        k = torch.tensor(np.stack([i[2] for i in ins]), device=dev)
+        v = torch.tensor(np.stack([i[3] for i in ins]), device=dev)
+        o = torch.empty(2, n, H, D, device=dev)
+        m = torch.empty(2, n, H, device=dev)
+        l = torch.empty(2, n, H, device=dev)
+        torch.cuda.synchronize()
+        for rk, c in enumerate(parts):
+            c.full_attn_partial_batched_dev(layers, seqs, [pos] * n, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                            o[rk].data_ptr(), m[rk].data_ptr(), l[rk].data_ptr())
+            c.synchronize()
+        out = torch.empty(n, H * D, device=dev)
+        parts[0].lse_merge_gate_dev(2, n, o.data_ptr(), m.data_ptr(), l.data_ptr(), gate.data_ptr(), out.data_ptr())
+        parts[0].synchronize()
+        out = out.cpu().numpy()
+        for j, (layer, seq) in enumerate(items):
+            ref = orc.full_attn_step(layer, seq, pos, *ins[j])
+            assert I.rel_err(out[j], ref) <= TOL_F32, (pos, j)
+        if pos < 40:  # early steps: rank 1 owns no row yet -> empty partial (m = -inf, l = 0)
+            if pos < 32:
+                assert torch.isinf(m[1]).all() and (l[1] == 0).all()
+    for c in parts + [whole]:
+        c.close()
