@@ -44,7 +44,7 @@ LIN_LAYERS = [i for i in range(N_LAYERS) if (i + 1) % INTERVAL != 0]
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")

@@ -116,8 +116,8 @@ def test_split_k_merge_equals_unsplit(f32_pair, bf16_pair, bf16):
         outs.append(ctx.sdpa(n, q, gate, K, V))
     ctx.set_tuning("gqa_chunk", 0)
     for o in outs:
-        # the split only reorders fp32 sums; with bf16 P the rounding points move too
-        assert I.rel_err(o, one) <= (2e-3 if bf16 else 2e-6)
+        # the split reorders fp32 sums and moves the rounding points of P (bf16, or the tf32 hi/lo split)
+        assert I.rel_err(o, one) <= (2e-3 if bf16 else 2e-5)
 
 
 @pytest.mark.parametrize("bf16", [False, True])
@@ -171,7 +171,7 @@ def test_ragged_batched_decode_bf16():
     n_seqs = 6
     ctx, orc = make_pair(max_seq=2048, n_seqs=n_seqs, kv_bf16=True, linear_layers=[])
     r = I.rng(70)
-    lens = [1, 31, 257, 1024, 1500, 2047]
+    lens = [1, 31, 257, 1024, 1500, 2046]
     layers = [3, 7]
     for s, ln in enumerate(lens):
         for layer in layers:
