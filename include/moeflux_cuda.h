@@ -235,6 +235,39 @@ int mfc_linear_attn_step_stateless(mfc_ctx *ctx, int32_t layer, const float *qkv
                                    const float *alpha, const float *beta, float *conv_state,
                                    float *ssm_state, float *out);
 
+/* Gated SDPA over a caller-held KV cache that allocates nothing.  It has no
+ * counterpart in the reference.  It is for callers that cannot call cudaMalloc
+ * where they need attention: a plugin inside a host application that budgets
+ * every byte of device memory, a latency-critical path that must not enter the
+ * driver's allocator, or a process whose own pool already owns all free memory.
+ * Such a caller cannot open an mfc_ctx (mfc_open allocates caches and scratch).
+ *
+ * The caller passes every input and the output as device pointers on the
+ * CURRENT device; the call is asynchronous on `stream` (a cudaStream_t):
+ *   q, gate, out : [num_attn_heads][256] fp32; q is post-RoPE; gate may be NULL;
+ *   k_cache, v_cache : [num_kv_heads][cap_rows][256] of kv_dtype (bf16 or fp32),
+ *                      16-byte aligned, post-RoPE K; rows [0, kv_len) are used.
+ * The split-K partials, chunk counters and work descriptor of the kernel live in
+ * one fixed array inside the library's device image (about 4 MiB, held by every
+ * GPU that loads the library until the process exits).  Limits that follow from
+ * its size: num_kv_heads <= MFC_STATIC_MAX_KV_HEADS and
+ * kv_len <= MFC_STATIC_MAX_ROWS; larger requests are refused with -1 and a
+ * message (mfc_last_error(NULL)).  It calls no cudaMalloc / cudaFree and no
+ * allocating library routine.
+ *
+ * All calls on a device share that array, and the array keeps the previous
+ * call's contents (the entry point clears the counters it needs at zero on
+ * `stream` before the kernel).  Two calls whose kernels may overlap on the GPU
+ * (different streams, different threads) therefore race: serialise them.
+ * The first call on each device resolves the array's device address and raises
+ * the kernel's shared-memory limit; make that first call before any stream
+ * capture begins.  Returns 0 on success, -1 on error. */
+#define MFC_STATIC_MAX_KV_HEADS 8
+#define MFC_STATIC_MAX_ROWS 262144
+int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv_dtype,
+                        int32_t kv_len, int32_t cap_rows, const float *q, const float *gate,
+                        const void *k_cache, const void *v_cache, float *out, void *stream);
+
 /* Tuning knobs (tests and sweeps): "gdn_rows" in {32,64,128} state rows per
  * CTA; "gqa_target_ctas" CTAs a launch aims for when it picks the KV chunk
  * length; "gqa_chunk" forces the chunk length (0 = automatic). */

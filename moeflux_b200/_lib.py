@@ -82,6 +82,7 @@ SIGNATURES = {
     "mfc_kv_local_len": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "mfc_kv_local_row": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "mfc_snapshot_validate": (C.c_longlong, [C.POINTER(Config), _P, C.c_size_t]),
+    "mfc_sdpa_static_dev": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P]),
     "mfc_set_tuning": (C.c_int, [_P, C.c_char_p, C.c_int]),
     "mfc_launch_count": (C.c_longlong, [_P]),
 }

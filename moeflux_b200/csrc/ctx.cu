@@ -41,6 +41,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 }  // namespace
 
+// Message slot of failures that have no context to attach to (mfc_open and the
+// context-free entry points); read back through mfc_last_error(NULL).
+namespace mfc {
+std::string &no_ctx_error() { return g_open_error; }
+}  // namespace mfc
+
 struct mfc_ctx {
     mfc_config cfg;
     int n_full = 0, n_lin = 0;

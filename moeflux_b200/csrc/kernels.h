@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string>
+
 namespace mfc {
 
 constexpr int HEAD_DIM = 256;      // full-attention head dim
@@ -106,5 +108,8 @@ cudaError_t launch_kv_pack(const float *src_rows, void *dst_cache, int n_rows, i
                            cudaStream_t stream);
 cudaError_t launch_kv_unpack(const void *src_cache, float *dst_rows, int n_rows, int Hkv,
                              int cap_rows, int kv_bf16, cudaStream_t stream);
+
+// Per-thread message of the last failure that had no context (ctx.cu).
+std::string &no_ctx_error();
 
 }  // namespace mfc

@@ -287,3 +287,17 @@ class Ctx:
                                                       _fp(alpha), _fp(beta), _fp(cs), _fp(ss), _fp(out))
         self._check(rc, "mfc_linear_attn_step_stateless")
         return out, cs, ss
+
+
+def sdpa_static_dev(num_attn_heads: int, num_kv_heads: int, kv_dtype: int, kv_len: int, cap_rows: int,
+                    q_ptr: int, gate_ptr: int, k_cache_ptr: int, v_cache_ptr: int, out_ptr: int, stream: int = 0):
+    """``mfc_sdpa_static_dev``: gated SDPA over a caller-held device cache
+    ``[num_kv_heads][cap_rows][256]`` with every working byte taken from a fixed
+    array inside the library, for callers that cannot allocate device memory
+    (no context is needed, and none is created).  Asynchronous on ``stream``;
+    calls that may overlap on the GPU race on the shared array."""
+    L = lib()
+    rc = L.mfc_sdpa_static_dev(num_attn_heads, num_kv_heads, kv_dtype, kv_len, cap_rows, q_ptr, gate_ptr or None,
+                               k_cache_ptr, v_cache_ptr, out_ptr, stream or None)
+    if rc != 0:
+        raise MfcError("mfc_sdpa_static_dev: " + L.mfc_last_error(None).decode())
