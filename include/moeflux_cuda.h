@@ -85,6 +85,11 @@ const char *mfc_last_error(const mfc_ctx *ctx);
 int mfc_get_config(const mfc_ctx *ctx, mfc_config *out);
 /* cudaStream_t of the context, as void*; `_dev` calls are ordered on it. */
 void *mfc_stream(mfc_ctx *ctx);
+/* Makes the context issue all further work on the caller's stream (a
+ * cudaStream_t on the context's device; NULL = the legacy default stream).  The
+ * caller keeps ownership and must keep the stream alive while the context uses
+ * it.  Waits for the work already queued on the previous stream. */
+int mfc_set_stream(mfc_ctx *ctx, void *stream);
 /* Blocks until the context's stream is idle; -1 if a kernel reported a fault
  * (bounded wait expired) since the last call. */
 int mfc_synchronize(mfc_ctx *ctx);
@@ -268,8 +273,8 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
                         int32_t kv_len, int32_t cap_rows, const float *q, const float *gate,
                         const void *k_cache, const void *v_cache, float *out, void *stream);
 
-/* Tuning knobs (tests and sweeps): "gdn_rows" in {32,64,128} state rows per
- * CTA; "gqa_target_ctas" CTAs a launch aims for when it picks the KV chunk
+/* Tuning knobs (tests and sweeps): "gdn_rows" in {0,32,64,128} state rows per
+ * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a launch aims for when it picks the KV chunk
  * length; "gqa_chunk" forces the chunk length (0 = automatic). */
 int mfc_set_tuning(mfc_ctx *ctx, const char *key, int value);
 

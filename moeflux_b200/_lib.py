@@ -58,6 +58,7 @@ SIGNATURES = {
     "mfc_last_error": (C.c_char_p, [_P]),
     "mfc_get_config": (C.c_int, [_P, C.POINTER(Config)]),
     "mfc_stream": (_P, [_P]),
+    "mfc_set_stream": (C.c_int, [_P, _P]),
     "mfc_synchronize": (C.c_int, [_P]),
     "mfc_set_linear_weights": (C.c_int, [_P, C.c_int32, _U16, _F, _U16, _U16]),
     "mfc_full_attn_step": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _F, _F, _F, _F, _F]),

@@ -57,6 +57,7 @@ struct mfc_ctx {
     int n_kv_slots = 0, n_state_slots = 0;
     size_t kv_esize = 4;
     cudaStream_t stream = nullptr;
+    bool owns_stream = true;
 
     void *k_cache = nullptr, *v_cache = nullptr;
     CUtensorMap kmap, vmap;
@@ -83,7 +84,7 @@ struct mfc_ctx {
     float *st_rows = nullptr;  // snapshot / hook staging, SNAP_ROWS wire rows
     static constexpr int SNAP_ROWS = 4096;
 
-    int gdn_rows = 32;
+    int gdn_rows = 0;  // 0: chosen per launch from the item count
     int gqa_target_ctas = 148 * 2 * 4;
     int gqa_forced_chunk = 0;
     long long launches = 0;
@@ -164,7 +165,7 @@ void free_all(mfc_ctx *c) {
                     c->st_alpha, c->st_beta, c->st_gout, c->st_rows};
     for (void *p : ptrs)
         if (p) cudaFree(p);
-    if (c->stream) cudaStreamDestroy(c->stream);
+    if (c->stream && c->owns_stream) cudaStreamDestroy(c->stream);
 }
 
 int check_status(mfc_ctx *c) {
@@ -357,7 +358,14 @@ int launch_gdn(mfc_ctx *c, int n, const float *qkv, const float *z, const float 
     p.eps = g.rms_norm_eps;
     CK(cudaMemcpyAsync(c->d_gdn_items, c->h_gdn_items.data(), sizeof(GdnItem) * n,
                        cudaMemcpyHostToDevice, c->stream));
-    CK(launch_gdn_decode(p, c->gdn_rows, c->stream));
+    // Whole heads per CTA (128 rows) amortise the conv/norm prologue best; smaller
+    // blocks only when the launch would otherwise leave SMs without work.
+    int rows = c->gdn_rows;
+    if (rows == 0) {
+        const long long heads = (long long)n * g.linear_num_v_heads;
+        rows = heads >= 2 * 592 ? 128 : (heads >= 592 ? 64 : 32);
+    }
+    CK(launch_gdn_decode(p, rows, c->stream));
     c->launches += 1;
     return 0;
 }
@@ -569,7 +577,7 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     c->lin_weights_set.assign(c->n_lin > 0 ? c->n_lin : 1, 0);
     if (const char *e = getenv("MFC_GDN_ROWS")) c->gdn_rows = atoi(e);
     if (const char *e = getenv("MFC_GQA_TARGET_CTAS")) c->gqa_target_ctas = atoi(e);
-    if (c->gdn_rows != 32 && c->gdn_rows != 64 && c->gdn_rows != 128) c->gdn_rows = 32;
+    if (c->gdn_rows != 32 && c->gdn_rows != 64 && c->gdn_rows != 128) c->gdn_rows = 0;
     if (c->gqa_target_ctas < 1) c->gqa_target_ctas = 1;
     if (c->gqa_target_ctas > 8192) c->gqa_target_ctas = 8192;
     c->max_parts = 8192 + g.max_batch * g.num_kv_heads;
@@ -639,6 +647,19 @@ int mfc_get_config(const mfc_ctx *c, mfc_config *out) {
 
 void *mfc_stream(mfc_ctx *c) { return c ? (void *)c->stream : nullptr; }
 
+int mfc_set_stream(mfc_ctx *c, void *stream) {
+    if (!c) return -1;
+    cudaSetDevice(c->cfg.device);
+    if (cudaStreamSynchronize(c->stream) != cudaSuccess) {
+        fail(c, "the context's previous stream is in a failed state");
+        return -1;
+    }
+    if (c->owns_stream && c->stream) cudaStreamDestroy(c->stream);
+    c->stream = (cudaStream_t)stream;
+    c->owns_stream = false;
+    return 0;
+}
+
 int mfc_synchronize(mfc_ctx *c) {
     if (!c) return -1;
     cudaSetDevice(c->cfg.device);
@@ -650,7 +671,7 @@ long long mfc_launch_count(const mfc_ctx *c) { return c ? c->launches : 0; }
 int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
     if (!c || !key) return -1;
     if (!strcmp(key, "gdn_rows")) {
-        if (value != 32 && value != 64 && value != 128) return -1;
+        if (value != 0 && value != 32 && value != 64 && value != 128) return -1;
         c->gdn_rows = value;
     } else if (!strcmp(key, "gqa_target_ctas")) {
         if (value < 1 || value > 8192) return -1;

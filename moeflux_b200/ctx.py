@@ -98,6 +98,10 @@ class Ctx:
     def stream(self) -> int:
         return int(self._lib.mfc_stream(self._h) or 0)
 
+    def set_stream(self, stream: int):
+        """Issue all further work on the caller's stream (e.g. ``torch.cuda.Stream().cuda_stream``)."""
+        self._check(self._lib.mfc_set_stream(self._h, stream or None), "mfc_set_stream")
+
     def synchronize(self):
         self._check(self._lib.mfc_synchronize(self._h), "mfc_synchronize")
 

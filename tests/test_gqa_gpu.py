@@ -154,6 +154,22 @@ def test_step_argument_errors(f32_pair):
     assert ctx.memory_seq_pos_max(0) == 0  # failed calls changed nothing
 
 
+def test_caller_owned_stream(f32_pair):
+    """mfc_set_stream: the context works on a stream the caller owns (here torch's)."""
+    import torch
+
+    ctx, orc = make_pair(max_seq=128, linear_layers=[])
+    s = torch.cuda.Stream()
+    ctx.set_stream(s.cuda_stream)
+    assert ctx.stream == s.cuda_stream
+    r = I.rng(62)
+    for pos in range(3):
+        ins = I.gqa_step_inputs(r)
+        assert I.rel_err(ctx.full_attn_step(3, 0, pos, *ins), orc.full_attn_step(3, 0, pos, *ins)) <= TOL_F32
+    ctx.close()
+    s.synchronize()  # still alive after the context is gone
+
+
 def test_cache_overflow_is_an_error():
     ctx, _ = make_pair(max_seq=33, linear_layers=[])
     r = I.rng(61)
