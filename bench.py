@@ -359,12 +359,10 @@ def run_ours(args, rank, world, local_rank):
         def e2e_step():
             pos = np.full(ng, pos_now[0], np.int32)
             if world == 1:
-                if nl:
-                    ctx.linear_attn_step_batched_ptr(nl, l_layers.ctypes.data, l_seqs.ctypes.data, hqkv.data_ptr(),
-                                                     hz.data_ptr(), ha.data_ptr(), hb.data_ptr(), hlo.data_ptr())
-                ctx.full_attn_step_batched_ptr(ng, g_layers.ctypes.data, g_seqs.ctypes.data, pos.ctypes.data,
-                                               hq.data_ptr(), hgate.data_ptr(), hk.data_ptr(), hv.data_ptr(),
-                                               hout.data_ptr())
+                ctx.eval_token_attn_ptr(ng, g_layers.ctypes.data, g_seqs.ctypes.data, pos.ctypes.data, hq.data_ptr(),
+                                        hgate.data_ptr(), hk.data_ptr(), hv.data_ptr(), hout.data_ptr(), nl,
+                                        l_layers.ctypes.data, l_seqs.ctypes.data, hqkv.data_ptr(), hz.data_ptr(),
+                                        ha.data_ptr(), hb.data_ptr(), hlo.data_ptr())
                 pos_now[0] += 1
             else:
                 with torch.cuda.stream(stream):

@@ -140,6 +140,21 @@ int mfc_linear_attn_step_batched(mfc_ctx *ctx, int32_t n, const int32_t *layers,
                                  const int32_t *seq_ids, const float *qkv, const float *z,
                                  const float *alpha, const float *beta, float *out);
 
+/* One token step of the attention sub-blocks of a whole layer stack, host
+ * pointers: n_full full-attention items and n_lin GatedDeltaNet items (either
+ * may be 0), arguments as in the two batched calls above.  It is what
+ * RsCtx::eval_token (crates/moeflux/src/riir/mod.rs:1218) does across its layer
+ * loop for this path, for layers whose inputs do not depend on one another's
+ * outputs; the two groups run on two queues so that the host<->device copies of
+ * one overlap the kernel of the other.  All arguments are validated before
+ * anything is queued: on -1 no state has changed. */
+int mfc_eval_token_attn(mfc_ctx *ctx, int32_t n_full, const int32_t *full_layers,
+                        const int32_t *full_seqs, const int32_t *pos, const float *q,
+                        const float *gate, const float *k, const float *v, float *full_out,
+                        int32_t n_lin, const int32_t *lin_layers, const int32_t *lin_seqs,
+                        const float *qkv, const float *z, const float *alpha, const float *beta,
+                        float *lin_out);
+
 /* Device-pointer forms: same meaning, q/gate/k/v/out (qkv/z/alpha/beta/out) are
  * device pointers, layers/seq_ids/pos stay host arrays.  Asynchronous on
  * mfc_stream(ctx); the per-sequence lengths advance at call time. */

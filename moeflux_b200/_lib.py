@@ -65,6 +65,8 @@ SIGNATURES = {
     "mfc_linear_attn_step": (C.c_int, [_P, C.c_int32, C.c_int32, _F, _F, _F, _F, _F]),
     "mfc_full_attn_step_batched": (C.c_int, [_P, C.c_int32, _I, _I, _I, _F, _F, _F, _F, _F]),
     "mfc_linear_attn_step_batched": (C.c_int, [_P, C.c_int32, _I, _I, _F, _F, _F, _F, _F]),
+    "mfc_eval_token_attn": (C.c_int, [_P, C.c_int32, _I, _I, _I, _F, _F, _F, _F, _F, C.c_int32, _I, _I, _F, _F, _F, _F,
+                                      _F]),
     "mfc_full_attn_step_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P, _P, _P]),
     "mfc_linear_attn_step_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _P, _P, _P, _P, _P]),
     "mfc_full_attn_partial_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P, _P, _P, _P]),

@@ -58,6 +58,8 @@ struct mfc_ctx {
     size_t kv_esize = 4;
     cudaStream_t stream = nullptr;
     bool owns_stream = true;
+    cudaStream_t side_stream = nullptr;  // second queue of mfc_eval_token_attn
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 
     void *k_cache = nullptr, *v_cache = nullptr;
     CUtensorMap kmap, vmap;
@@ -166,6 +168,9 @@ void free_all(mfc_ctx *c) {
     for (void *p : ptrs)
         if (p) cudaFree(p);
     if (c->stream && c->owns_stream) cudaStreamDestroy(c->stream);
+    if (c->side_stream) cudaStreamDestroy(c->side_stream);
+    if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+    if (c->ev_join) cudaEventDestroy(c->ev_join);
 }
 
 int check_status(mfc_ctx *c) {
@@ -582,7 +587,10 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     if (c->gqa_target_ctas > 8192) c->gqa_target_ctas = 8192;
     c->max_parts = 8192 + g.max_batch * g.num_kv_heads;
 
-    bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess;
+    bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) == cudaSuccess;
     if (!ok) fail(c, "cudaStreamCreate failed");
     const uint64_t kv_rows = (uint64_t)c->n_kv_slots * g.num_kv_heads * c->cap_rows;
     if (ok && kv_rows >= (1ull << 32)) ok = fail(c, "KV cache has more rows than a tensor map can address");
@@ -862,6 +870,84 @@ int mfc_linear_attn_step_batched(mfc_ctx *c, int32_t n, const int32_t *layers, c
 int mfc_linear_attn_step(mfc_ctx *c, int32_t layer, int32_t seq_id, const float *qkv, const float *z,
                          const float *alpha, const float *beta, float *out) {
     return mfc_linear_attn_step_batched(c, 1, &layer, &seq_id, qkv, z, alpha, beta, out);
+}
+
+// ---------------------------------------------------------------- whole-stack step
+
+int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, const int32_t *full_seqs,
+                        const int32_t *pos, const float *q, const float *gate, const float *k, const float *v,
+                        float *full_out, int32_t n_lin, const int32_t *lin_layers, const int32_t *lin_seqs,
+                        const float *qkv, const float *z, const float *alpha, const float *beta, float *lin_out) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (n_full < 0 || n_lin < 0 || n_full + n_lin == 0 || n_full > g.max_batch || n_lin > g.max_batch) {
+        fail(c, "item counts must be in [0, max_batch] and not both zero");
+        return -1;
+    }
+    if ((n_full && (!q || !gate || !k || !v || !full_out)) || (n_lin && (!qkv || !alpha || !beta || !lin_out))) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (g.kv_world != 1) {
+        fail(c, "this context holds a share of a KV split: use the partial entry points");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    // validate both groups before anything is queued; a failure leaves every state as it was
+    if (n_lin) {
+        if (build_gdn_items(c, n_lin, lin_layers, lin_seqs)) return -1;
+        if (z)
+            for (int i = 0; i < n_lin; i++)
+                if (c->lin_weights_set[c->h_gdn_items[i].w_layer] != 2) {
+                    for (int j = 0; j < n_lin; j++) c->conv_step[c->h_gdn_items[j].state_idx] -= 1;
+                    fail(c, "z given but no norm weight was set for layer " + std::to_string(lin_layers[i]));
+                    return -1;
+                }
+    }
+    int total = 0;
+    if (n_full && build_gqa_items(c, n_full, full_layers, full_seqs, pos, &total)) {
+        for (int j = 0; j < n_lin; j++) c->conv_step[c->h_gdn_items[j].state_idx] -= 1;
+        return -1;
+    }
+    cudaStream_t main_stream = c->stream;
+    if (n_lin) {
+        // GatedDeltaNet group on the side queue: its copies and kernel overlap the attention group
+        CK(cudaEventRecord(c->ev_fork, main_stream));
+        CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
+        cudaStream_t s2 = c->side_stream;
+        const size_t vd = sizeof(float) * g.linear_num_v_heads * GDN_DIM * (size_t)n_lin;
+        const size_t hd = sizeof(float) * g.linear_num_v_heads * (size_t)n_lin;
+        CK(cudaMemcpyAsync(c->st_qkv, qkv, sizeof(float) * c->conv_dim * (size_t)n_lin, cudaMemcpyHostToDevice, s2));
+        if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, s2));
+        CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, s2));
+        CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, s2));
+        c->stream = s2;
+        const int rc = launch_gdn(c, n_lin, c->st_qkv, z ? c->st_z : nullptr, c->st_alpha, c->st_beta, c->st_gout);
+        c->stream = main_stream;
+        if (rc) return -1;
+        CK(cudaMemcpyAsync(lin_out, c->st_gout, vd, cudaMemcpyDeviceToHost, s2));
+        CK(cudaEventRecord(c->ev_join, s2));
+    }
+    if (n_full) {
+        const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)n_full;
+        const size_t kd = sizeof(float) * g.num_kv_heads * HEAD_DIM * (size_t)n_full;
+        CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, main_stream));
+        CK(cudaMemcpyAsync(c->st_gate, gate, qd, cudaMemcpyHostToDevice, main_stream));
+        CK(cudaMemcpyAsync(c->st_k, k, kd, cudaMemcpyHostToDevice, main_stream));
+        CK(cudaMemcpyAsync(c->st_v, v, kd, cudaMemcpyHostToDevice, main_stream));
+        GqaParams p;
+        fill_gqa_params(c, p, n_full, total);
+        p.q = c->st_q;
+        p.gate = c->st_gate;
+        p.k = c->st_k;
+        p.v = c->st_v;
+        p.out = c->st_out;
+        p.partial_mode = 0;
+        if (launch_gqa(c, p)) return -1;
+        CK(cudaMemcpyAsync(full_out, c->st_out, qd, cudaMemcpyDeviceToHost, main_stream));
+    }
+    if (n_lin) CK(cudaStreamWaitEvent(main_stream, c->ev_join, 0));
+    return check_status(c);
 }
 
 // ---------------------------------------------------------------- bulk state import (device)

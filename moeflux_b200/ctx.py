@@ -189,6 +189,43 @@ class Ctx:
                                                     C.cast(alpha_p, _F), C.cast(beta_p, _F), C.cast(out_p, _F))
         self._check(rc, "mfc_linear_attn_step_batched")
 
+    def eval_token_attn(self, full_items, pos, q, gate, k, v, lin_items, qkv, z, alpha, beta):
+        """One token step of a layer stack's attention sub-blocks: ``full_items`` and
+        ``lin_items`` are lists of (layer, seq_id).  Returns (full_out [n_full, q_dim],
+        lin_out [n_lin, total_value])."""
+        nf, nl = len(full_items), len(lin_items)
+        fl, flp = _i32([l for l, _ in full_items] or [0])
+        fs, fsp = _i32([s for _, s in full_items] or [0])
+        pa, pp = _i32(list(pos) or [0])
+        ll, llp = _i32([l for l, _ in lin_items] or [0])
+        ls, lsp = _i32([s for _, s in lin_items] or [0])
+        fo = np.empty((nf, self.q_dim), np.float32)
+        lo = np.empty((nl, self.total_value), np.float32)
+        if nf:
+            q, gate = _f32(q, nf * self.q_dim, "q"), _f32(gate, nf * self.q_dim, "gate")
+            k, v = _f32(k, nf * self.kv_dim, "k"), _f32(v, nf * self.kv_dim, "v")
+        if nl:
+            qkv = _f32(qkv, nl * self.conv_dim, "qkv")
+            z = None if z is None else _f32(z, nl * self.total_value, "z")
+            alpha, beta = _f32(alpha, nl * self.v_heads, "alpha"), _f32(beta, nl * self.v_heads, "beta")
+        P = lambda a: _fp(a) if a is not None else None
+        rc = self._lib.mfc_eval_token_attn(
+            self._h, nf, flp, fsp, pp, P(q) if nf else None, P(gate) if nf else None, P(k) if nf else None,
+            P(v) if nf else None, _fp(fo) if nf else None, nl, llp, lsp, P(qkv) if nl else None,
+            P(z) if nl else None, P(alpha) if nl else None, P(beta) if nl else None, _fp(lo) if nl else None)
+        self._check(rc, "mfc_eval_token_attn")
+        return fo, lo
+
+    def eval_token_attn_ptr(self, nf, fl_p, fs_p, pos_p, q_p, gate_p, k_p, v_p, fo_p, nl, ll_p, ls_p, qkv_p, z_p,
+                            alpha_p, beta_p, lo_p):
+        """Raw-pointer form (pinned host buffers, no numpy work per call)."""
+        F = lambda p: C.cast(p, _F) if p else None
+        Ip = lambda p: C.cast(p, _I) if p else None
+        rc = self._lib.mfc_eval_token_attn(self._h, nf, Ip(fl_p), Ip(fs_p), Ip(pos_p), F(q_p), F(gate_p), F(k_p),
+                                           F(v_p), F(fo_p), nl, Ip(ll_p), Ip(ls_p), F(qkv_p), F(z_p), F(alpha_p),
+                                           F(beta_p), F(lo_p))
+        self._check(rc, "mfc_eval_token_attn")
+
     # -- hot path, device pointers (asynchronous on self.stream) ------------
     def full_attn_step_batched_dev(self, layers, seq_ids, pos, q_ptr, gate_ptr, k_ptr, v_ptr, out_ptr):
         la, lp = _i32(layers)
