@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")
     ap.add_argument("--batch", type=int, default=8, help="sequences")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "f32"], help="KV cache storage type")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -188,9 +189,9 @@ def run_reference(args, rank):
 
 def workload_config(args, n):
     return {"workload": f"60-layer hybrid attention-only decode stack (45 GatedDeltaNet + 15 GQA), batch {args.batch}, "
-                        f"ctx {args.ctx}, bf16 KV, fp32 state",
+                        f"ctx {args.ctx}, {args.kv} KV, fp32 state",
             "layer_steps_per_step": N_LAYERS * args.batch, "context": args.ctx, "batch": args.batch,
-            "kv_dtype": "bf16", "parallelism": f"kv-sequence split x{n} + GatedDeltaNet sequences round-robin"
+            "kv_dtype": args.kv, "parallelism": f"kv-sequence split x{n} + GatedDeltaNet sequences round-robin"
             if n > 1 else "single GPU",
             "l2": "inputs (GBs of KV and state per step) exceed the 126 MB L2; no flush needed"}
 
@@ -212,7 +213,8 @@ def run_ours(args, rank, world, local_rank):
     L0 = CTX - total_steps  # the last timed step brings every cache to exactly CTX rows
     assert L0 > 0
 
-    ctx = M.Ctx(max_seq=CTX, n_seqs=B, kv_dtype=M.KV_BF16, device=local_rank, kv_rank=rank, kv_world=world,
+    kv_esize = 2 if args.kv == "bf16" else 4
+    ctx = M.Ctx(max_seq=CTX, n_seqs=B, kv_dtype=M.KV_BF16 if args.kv == "bf16" else M.KV_F32, device=local_rank, kv_rank=rank, kv_world=world,
                 kv_block=256, max_batch=N_LAYERS * B)
     stream = torch.cuda.Stream(device=dev)  # owned by torch, so tensors allocated on it outlive the context safely
     ctx.set_stream(stream.cuda_stream)
@@ -405,15 +407,14 @@ def run_ours(args, rank, world, local_rank):
         peak, peak_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
     mean_pos = L0 + W + (K - 1) / 2.0
     rows_local = (mean_pos + 1) / world
-    gqa_alg_bytes = ng * gqa_bytes_per_item(rows_local)
+    gqa_alg_bytes = ng * gqa_bytes_per_item(rows_local, kv_esize)
     achieved = gqa_alg_bytes / (gqa_ms * 1e-3) / 1e9
-    step_bytes = ng * gqa_bytes_per_item(mean_pos + 1) + (len(LIN_LAYERS) * B) * gdn_bytes_per_item()
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "gqa_decode_bf16_traffic.json")
-    if os.path.exists(tpath):
-        tj = json.load(open(tpath))
-        traffic = tj["dram_bytes_per_kv_row_per_head_pair"] * rows_local * ng if "dram_bytes_per_kv_row_per_head_pair" in tj else None
-    roofline = {"bound": "hbm", "kernel": "gqa_decode_bf16_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+    step_bytes = ng * gqa_bytes_per_item(mean_pos + 1, kv_esize) + (len(LIN_LAYERS) * B) * gdn_bytes_per_item()
+    # DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum) over algorithmic bytes, captured on the
+    # ctx-8192 case of this workload; the traffic is the streamed KV rows, so it scales with the rows of a launch.
+    dram_over_algorithmic = {"bf16": 1.013, "f32": 1.007}[args.kv]
+    traffic = gqa_alg_bytes * dram_over_algorithmic
+    roofline = {"bound": "hbm", "kernel": f"gqa_decode_{args.kv}_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": gqa_alg_bytes, "ms_per_launch": gqa_ms,
                 "frac_of_8TBps": achieved / 8000.0,
@@ -430,7 +431,7 @@ def run_ours(args, rank, world, local_rank):
         value = N_LAYERS * B * K / (ms * 1e-3)
         line = {"metric": "attention decode layer-steps/sec", "value": value, "unit": "layer-steps/s", "n_gpus": world,
                 "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "bf16 KV, fp32 accumulate and state", "data": "synthetic",
+                "vs_baseline": None, "dtype": f"{args.kv} KV, fp32 accumulate and state", "data": "synthetic",
                 "config": workload_config(args, world), "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches),
                 "clocks": clocks}
     ctx.close()
