@@ -36,12 +36,26 @@ struct Located {
     int chunk;
 };
 
-__device__ __forceinline__ Located locate(const GqaParams &p, int bid) {
+// CTA -> (item, kv head, chunk).  The items' first-CTA indices are staged in
+// shared memory once per CTA so that the search costs one round of global loads
+// instead of a chain of dependent ones.  Contains a __syncthreads.
+constexpr int LOCATE_SMEM_ITEMS = 512;
+__device__ __forceinline__ Located locate(const GqaParams &p, int bid, int *s_begin) {
     int lo = 0, hi = p.n_items - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (p.items[mid].cta_begin <= bid) lo = mid;
-        else hi = mid - 1;
+    if (p.n_items <= LOCATE_SMEM_ITEMS) {
+        for (int i = threadIdx.x; i < p.n_items; i += blockDim.x) s_begin[i] = p.items[i].cta_begin;
+        __syncthreads();
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_begin[mid] <= bid) lo = mid;
+            else hi = mid - 1;
+        }
+    } else {
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (p.items[mid].cta_begin <= bid) lo = mid;
+            else hi = mid - 1;
+        }
     }
     Located L;
     L.it = p.items[lo];

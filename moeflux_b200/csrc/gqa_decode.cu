@@ -54,10 +54,11 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
     float *s_L = s_M + 16;                     // [16]
     uint64_t *full = reinterpret_cast<uint64_t *>(s_L + 16);  // [STAGES]
     __shared__ int s_flag;
+    __shared__ int s_begin[LOCATE_SMEM_ITEMS];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const Located L = locate(p, blockIdx.x);
+    const Located L = locate(p, blockIdx.x, s_begin);
     const GqaItem &it = L.it;
     const int group = p.group;
 
@@ -213,14 +214,14 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(m_r[x], mx);
-            corr[x] = exp2f((m_r[x] - m_new) * sl2);
+            corr[x] = ex2_approx((m_r[x] - m_new) * sl2);
             m_r[x] = m_new;
             const float mb = m_new * sl2;
             float rs = 0.0f;
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) {
-                sv[nt][2 * x] = exp2f(fmaf(sv[nt][2 * x], sl2, -mb));
-                sv[nt][2 * x + 1] = exp2f(fmaf(sv[nt][2 * x + 1], sl2, -mb));
+                sv[nt][2 * x] = ex2_approx(fmaf(sv[nt][2 * x], sl2, -mb));
+                sv[nt][2 * x + 1] = ex2_approx(fmaf(sv[nt][2 * x + 1], sl2, -mb));
                 rs += sv[nt][2 * x] + sv[nt][2 * x + 1];
             }
             l_r[x] = l_r[x] * corr[x] + rs;

@@ -3,7 +3,7 @@
 // and epilogue as the bf16 kernel (gqa_decode.cu); the tile maths differs.
 //
 // fp32 operands run on the tensor cores as 3xTF32: every operand x is split
-// into hi = tf32(x) and lo = tf32(x - hi) and a product a*b is accumulated as
+// into hi = x truncated to tf32 and lo = x - hi, and a product a*b is accumulated as
 // a_hi*b_hi + a_lo*b_hi + a_hi*b_lo in fp32, which keeps the error near 2^-21
 // relative (the reference is fp32 throughout: crates/moeflux/src/riir/sdpa.rs:
 // 114-169).  A 16x256 fp32 Q in hi/lo form does not fit in registers next to
@@ -27,9 +27,11 @@ constexpr int TILE_BYTES_F32 = F32_TILE * HEAD_DIM * 4;  // 16 KiB per tensor pe
 constexpr int BOX_BYTES = F32_TILE * 128;                // one [16 rows x 32 floats] box
 constexpr int SP_STRIDE = 24;                            // padded row stride of a partial score block
 
+// x = hi + lo with hi = x truncated to tf32 precision (exact subtraction), lo the
+// remainder; the tensor core reads only the tf32 bits of lo.  Two instructions.
 __device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo) {
-    hi = f32_to_tf32(x);
-    lo = f32_to_tf32(x - __uint_as_float(hi));
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
 __global__ void __launch_bounds__(128, 2)
@@ -48,10 +50,11 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     float *s_M = s_w + MAX_SPLITS * 16;              // [16]
     float *s_L = s_M + 16;                           // [16]
     __shared__ int s_flag;
+    __shared__ int s_begin[LOCATE_SMEM_ITEMS];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const Located L = locate(p, blockIdx.x);
+    const Located L = locate(p, blockIdx.x, s_begin);
     const GqaItem &it = L.it;
     const int group = p.group;
 
@@ -226,14 +229,14 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(m_r[x], mx);
-            corr[x] = exp2f((m_r[x] - m_new) * sl2);
+            corr[x] = ex2_approx((m_r[x] - m_new) * sl2);
             m_r[x] = m_new;
             const float mb = m_new * sl2;
             float rs = 0.0f;
 #pragma unroll
             for (int nt = 0; nt < 2; nt++) {
-                sv[nt][2 * x] = exp2f(fmaf(sv[nt][2 * x], sl2, -mb));
-                sv[nt][2 * x + 1] = exp2f(fmaf(sv[nt][2 * x + 1], sl2, -mb));
+                sv[nt][2 * x] = ex2_approx(fmaf(sv[nt][2 * x], sl2, -mb));
+                sv[nt][2 * x + 1] = ex2_approx(fmaf(sv[nt][2 * x + 1], sl2, -mb));
                 rs += sv[nt][2 * x] + sv[nt][2 * x + 1];
             }
             l_r[x] = l_r[x] * corr[x] + rs;
