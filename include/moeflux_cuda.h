@@ -184,6 +184,20 @@ int mfc_lse_merge_gate_dev(mfc_ctx *ctx, int32_t n_parts, int32_t n, const float
                            const float *m_parts, const float *l_parts, size_t part_stride,
                            const float *gate, float *out);
 
+/* Prefill of n_tokens tokens of one full-attention layer in one call, device
+ * pointers, bf16 activations: token t (absolute position start_pos + t) gets
+ * exactly what mfc_full_attn_step computes for it -- RoPE, append, causal SDPA
+ * over rows [0, start_pos + t], sigmoid gate.  The reference prefills by
+ * running its decode step per token (RsCtx::eval_prompt,
+ * crates/moeflux/src/riir/mod.rs:1196-1214); this is the batched form on the
+ * tcgen05 tensor cores.  q, gate, out: [n_tokens][num_attn_heads][256] bf16
+ * (gate may be NULL); k, v: [n_tokens][num_kv_heads][256] bf16.  start_pos must
+ * equal the layer's current length.  Needs a bf16 KV cache and kv_world == 1.
+ * Asynchronous on mfc_stream(ctx). */
+int mfc_full_attn_prefill_dev(mfc_ctx *ctx, int32_t layer, int32_t seq_id, int32_t start_pos,
+                              int32_t n_tokens, const void *q_bf16, const void *gate_bf16,
+                              const void *k_bf16, const void *v_bf16, void *out_bf16);
+
 /* Bulk import of state that already exists on the device (what a prefill, or a
  * prefix cache, hands over; the reference fills the same state token by token,
  * crates/moeflux/src/riir/mod.rs:1206-1212).  Asynchronous on mfc_stream(ctx).

@@ -71,6 +71,7 @@ SIGNATURES = {
     "mfc_linear_attn_step_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _P, _P, _P, _P, _P]),
     "mfc_full_attn_partial_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "mfc_lse_merge_gate_dev": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P, C.c_size_t, _P, _P]),
+    "mfc_full_attn_prefill_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "mfc_kv_append_rows_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "mfc_linear_state_set_dev": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P]),
     "mfc_memory_clear": (None, [_P, C.c_int32]),

@@ -63,6 +63,8 @@ struct mfc_ctx {
 
     void *k_cache = nullptr, *v_cache = nullptr;
     CUtensorMap kmap, vmap;
+    CUtensorMap kmap_pf, vmap_pf;  // same caches, 64-row boxes for the prefill kernel (bf16 cache only)
+    float *pf_cos_sin = nullptr;   // [max_seq][32] (cos, sin) of the tokens of a prefill call
     float *ssm = nullptr, *conv = nullptr;
     uint16_t *conv_w = nullptr, *dt_bias = nullptr, *norm_w = nullptr;
     float *a_log = nullptr;
@@ -141,7 +143,7 @@ bool dalloc(mfc_ctx *c, T **p, size_t n, bool zero) {
     return true;
 }
 
-bool make_tensor_map(mfc_ctx *c, CUtensorMap *map, void *base, uint64_t rows) {
+bool make_tensor_map(mfc_ctx *c, CUtensorMap *map, void *base, uint64_t rows, int box_rows = 0) {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -150,7 +152,7 @@ bool make_tensor_map(mfc_ctx *c, CUtensorMap *map, void *base, uint64_t rows) {
     const bool bf16 = c->cfg.kv_dtype == MFC_KV_BF16;
     cuuint64_t dims[2] = {(cuuint64_t)HEAD_DIM, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)(HEAD_DIM * c->kv_esize)};
-    cuuint32_t box[2] = {(cuuint32_t)(bf16 ? 64 : 32), (cuuint32_t)(bf16 ? KV_TILE : KV_TILE_F32)};  // 128-byte inner extent
+    cuuint32_t box[2] = {(cuuint32_t)(bf16 ? 64 : 32), (cuuint32_t)(box_rows ? box_rows : (bf16 ? KV_TILE : KV_TILE_F32))};  // 128-byte inner extent
     cuuint32_t estr[2] = {1, 1};
     CUresult r = ((EncodeTiledFn)fn)(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                                      2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -164,7 +166,7 @@ void free_all(mfc_ctx *c) {
     void *ptrs[] = {c->k_cache, c->v_cache, c->ssm, c->conv, c->conv_w, c->dt_bias, c->norm_w, c->a_log,
                     c->inv_freq, c->d_gqa_items, c->d_gdn_items, c->sc_o, c->sc_m, c->sc_l, c->tickets,
                     c->status, c->st_q, c->st_gate, c->st_k, c->st_v, c->st_out, c->st_qkv, c->st_z,
-                    c->st_alpha, c->st_beta, c->st_gout, c->st_rows};
+                    c->st_alpha, c->st_beta, c->st_gout, c->st_rows, c->pf_cos_sin};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     if (c->stream && c->owns_stream) cudaStreamDestroy(c->stream);
@@ -617,7 +619,8 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
          dalloc(c, &c->st_out, mb * qd, false) && dalloc(c, &c->st_qkv, mb * c->conv_dim, false) &&
          dalloc(c, &c->st_z, mb * vd, false) && dalloc(c, &c->st_alpha, mb * g.linear_num_v_heads, false) &&
          dalloc(c, &c->st_beta, mb * g.linear_num_v_heads, false) && dalloc(c, &c->st_gout, mb * vd, false) &&
-         dalloc(c, &c->st_rows, (size_t)mfc_ctx::SNAP_ROWS * kvd, false);
+         dalloc(c, &c->st_rows, (size_t)mfc_ctx::SNAP_ROWS * kvd, false) &&
+         dalloc(c, &c->pf_cos_sin, (size_t)g.max_seq * 64, false);
     if (ok) {
         // the host's libm evaluates the frequencies, exactly as the reference does
         // (crates/moeflux/src/riir/rope.rs:99-101); the device only multiplies by pos
@@ -628,6 +631,9 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
         if (!ok) fail(c, "cudaMemcpy(inv_freq) failed");
     }
     ok = ok && make_tensor_map(c, &c->kmap, c->k_cache, kv_rows) && make_tensor_map(c, &c->vmap, c->v_cache, kv_rows);
+    if (ok && g.kv_dtype == MFC_KV_BF16)
+        ok = make_tensor_map(c, &c->kmap_pf, c->k_cache, kv_rows, 64) && make_tensor_map(c, &c->vmap_pf, c->v_cache, kv_rows, 64);
+    if (ok && gqa_prefill_configure() != cudaSuccess) ok = fail(c, "cannot opt in to the prefill kernel's shared memory size");
     if (ok && (gqa_decode_configure() != cudaSuccess || gqa_decode_f32_configure() != cudaSuccess)) ok = fail(c, "cannot opt in to the kernels' shared memory size");
     if (!ok) {
         g_open_error = c->err;
@@ -948,6 +954,84 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
     }
     if (n_lin) CK(cudaStreamWaitEvent(main_stream, c->ev_join, 0));
     return check_status(c);
+}
+
+// ---------------------------------------------------------------- prefill
+
+int mfc_full_attn_prefill_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, int32_t start_pos, int32_t n_tokens,
+                              const void *q_bf16, const void *gate_bf16, const void *k_bf16, const void *v_bf16,
+                              void *out_bf16) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (!q_bf16 || !k_bf16 || !v_bf16 || !out_bf16 || n_tokens <= 0) {
+        fail(c, "NULL argument or n_tokens <= 0");
+        return -1;
+    }
+    if (layer < 0 || layer >= g.num_layers || !is_full_layer(g, layer) || seq_id < 0 || seq_id >= g.n_seqs) {
+        fail(c, "not a full-attention layer / seq_id out of range");
+        return -1;
+    }
+    if (g.kv_dtype != MFC_KV_BF16 || g.kv_world != 1 || g.rotary_dim > 64) {
+        fail(c, "prefill needs a bf16 KV cache held by one context and rotary_dim <= 64");
+        return -1;
+    }
+    const int slot = c->layer_to_full[layer] * g.n_seqs + seq_id;
+    if (start_pos != c->kv_len[slot]) {
+        fail(c, "start_pos " + std::to_string(start_pos) + " != current length " + std::to_string(c->kv_len[slot]));
+        return -1;
+    }
+    if ((long long)start_pos + n_tokens > g.max_seq) {
+        fail(c, "kv cache overflow");
+        return -1;
+    }
+    if (((uintptr_t)q_bf16 & 15) || ((uintptr_t)out_bf16 & 15) || ((uintptr_t)gate_bf16 & 15)) {
+        fail(c, "q, gate and out must be 16-byte aligned");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    // 3-D map over q [T][H][256]: box = 64 dims x 1 head x 128 tokens
+    CUtensorMap qmap;
+    {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) {
+            fail(c, "cuTensorMapEncodeTiled is not available from the driver");
+            return -1;
+        }
+        cuuint64_t dims[3] = {(cuuint64_t)HEAD_DIM, (cuuint64_t)g.num_attn_heads, (cuuint64_t)n_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)HEAD_DIM * 2, (cuuint64_t)HEAD_DIM * 2 * g.num_attn_heads};
+        cuuint32_t box[3] = {64, 1, 128};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = ((EncodeTiledFn)fn)(&qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(q_bf16), dims,
+                                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            fail(c, "cuTensorMapEncodeTiled(q) failed, code " + std::to_string((int)r));
+            return -1;
+        }
+    }
+    const size_t slot_row0 = (size_t)slot * g.num_kv_heads * c->cap_rows;
+    CK(launch_prefill_kv_append(k_bf16, v_bf16, c->k_cache, c->v_cache, 1, c->pf_cos_sin, c->inv_freq, n_tokens,
+                                g.num_kv_heads, g.rotary_dim, start_pos, slot_row0, c->cap_rows, 0, 1, 1, c->stream));
+    PrefillAttnParams p;
+    memset(&p, 0, sizeof(p));
+    p.gate = reinterpret_cast<const __nv_bfloat16 *>(gate_bf16);
+    p.out = reinterpret_cast<__nv_bfloat16 *>(out_bf16);
+    p.cos_sin = c->pf_cos_sin;
+    p.T = n_tokens;
+    p.H = g.num_attn_heads;
+    p.Hkv = g.num_kv_heads;
+    p.group = c->group;
+    p.start_pos = start_pos;
+    p.rotary_dim = g.rotary_dim;
+    p.kv_slot = slot;
+    p.cap_rows = c->cap_rows;
+    p.scale = 1.0f / sqrtf((float)g.head_dim);
+    p.status = c->status;
+    CK(launch_gqa_prefill(qmap, c->kmap_pf, c->vmap_pf, p, c->stream));
+    c->launches += 2;
+    c->kv_len[slot] += n_tokens;
+    return 0;
 }
 
 // ---------------------------------------------------------------- bulk state import (device)

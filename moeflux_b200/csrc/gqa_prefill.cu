@@ -1,0 +1,499 @@
+// Causal GQA prefill (flash-attention forward) on the 5th-generation tensor
+// cores: tcgen05.mma with operands staged in shared memory by TMA and the
+// accumulators in tensor memory (TMEM).
+//
+// The reference has no batched prefill: eval_prompt runs the decode step once
+// per token (crates/moeflux/src/riir/mod.rs:1206-1212).  This kernel computes
+// the same result for T tokens at once: for token t (absolute position
+// start_pos + t) the full-attention step of crates/moeflux/src/riir/
+// full_attn_forward.rs:278-389 -- RoPE(q, k), append, softmax(q K^T / 16) V over
+// rows [0, start_pos + t], sigmoid gate -- with bf16 activations.
+//
+// Two launches:
+//   1. prefill_kv_append_kernel: per token, the RoPE table entry (accurate
+//      sincosf of pos * inv_freq, shared by all heads), rotated K and V rows
+//      stored into the cache.
+//   2. gqa_prefill_kernel: CTA = 128 query tokens of one query head (M = 128).
+//      Per 64-row KV tile: S = Q K^T (16 tcgen05.mma of K=16, N=64, fp32 in
+//      TMEM), softmax with one thread per query row (tcgen05.ld, no shuffles),
+//      P written to shared memory as bf16, O += P V (4 tcgen05.mma, N=256,
+//      V as an MN-major operand straight from the cache layout).  S is double
+//      buffered in TMEM so Q K^T of tile j+1 runs under the softmax of tile j;
+//      O is rescaled in TMEM only when a row maximum grows by more than 2^8
+//      (stale-max trick), which is rare after the first tiles.
+// Every mbarrier wait is bounded; a wait that expires sets a status bit, the CTA
+// frees its TMEM and leaves.
+#include <math.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mfc {
+
+namespace {
+
+constexpr int PF_M = 128;        // query rows per CTA
+constexpr int PF_N = 64;         // KV rows per tile
+constexpr int PF_STAGES = 2;
+constexpr float LOG2E_PF = 1.4426950408889634f;
+
+constexpr uint32_t Q_BYTES = PF_M * HEAD_DIM * 2;      // 64 KiB: 4 boxes of [128 x 64]
+constexpr uint32_t Q_BOX = PF_M * 128;                 // 16 KiB
+constexpr uint32_t KV_TILE_BYTES = PF_N * HEAD_DIM * 2;  // 32 KiB: 4 boxes of [64 x 64]
+constexpr uint32_t KV_BOX = PF_N * 128;                // 8 KiB
+constexpr uint32_t P_BYTES = PF_M * PF_N * 2;          // 16 KiB
+constexpr uint32_t OFF_Q = 0;
+constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
+constexpr uint32_t OFF_V = OFF_K + PF_STAGES * KV_TILE_BYTES;
+constexpr uint32_t OFF_P = OFF_V + PF_STAGES * KV_TILE_BYTES;
+constexpr uint32_t OFF_BAR = OFF_P + 2 * P_BYTES;
+constexpr uint32_t PF_SMEM = OFF_BAR + 128 + 1024;     // + barriers + alignment slack
+
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TM_S = 0;      // two S buffers of 64 columns
+constexpr uint32_t TM_O = 128;    // O accumulator, 256 columns
+
+// ---- tcgen05 wrappers --------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, fp32 accumulate
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+// 32 lanes x 32 consecutive columns: thread i of warp w reads TMEM lane 32*(w%4)+i
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+          "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+          "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+          "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+          "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+          "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor
+// version 1.  lbo/sbo in bytes.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fff);
+    d |= (uint64_t)((lbo >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, M = 128.
+__host__ __device__ constexpr uint32_t idesc_bf16(int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(PF_M >> 4) << 24);
+}
+
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, int c0, int c1, int c2,
+                                            uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(smem_dst)),
+        "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(128, 1)
+gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                   const __grid_constant__ CUtensorMap vmap, const PrefillAttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + OFF_BAR);
+    uint64_t *full_q = bars + 0;
+    uint64_t *full_k = bars + 1;   // [2]
+    uint64_t *full_v = bars + 3;   // [2]
+    uint64_t *s_ready = bars + 5;  // [2]
+    uint64_t *pv_done = bars + 7;  // [2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int n_qt = (p.T + PF_M - 1) / PF_M;
+    const int qt = n_qt - 1 - (int)blockIdx.x;  // longest tiles first
+    const int h = blockIdx.y;
+    const int kvh = h / p.group;
+    const int t0 = qt * PF_M;
+    const int row_tok = t0 + tid;                     // this thread's query token
+    const int qpos = p.start_pos + row_tok;           // its absolute position
+    const int kv_need = p.start_pos + min(p.T, t0 + PF_M);  // rows this tile may attend to
+    const int ntiles = (kv_need + PF_N - 1) / PF_N;
+    const int kv_row0 = (p.kv_slot * p.Hkv + kvh) * p.cap_rows;
+
+    if (tid == 0) {
+        prefetch_tmap(&qmap);
+        prefetch_tmap(&kmap);
+        prefetch_tmap(&vmap);
+        for (int i = 0; i < 9; i++) mbar_init(&bars[i], 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+
+    auto load_k = [&](int tile) {
+        const int st = tile & 1;
+        mbar_expect_tx(&full_k[st], KV_TILE_BYTES);
+#pragma unroll
+        for (int b = 0; b < 4; b++)
+            tma_load_2d(smem + OFF_K + st * KV_TILE_BYTES + b * KV_BOX, &kmap, b * 64, kv_row0 + tile * PF_N,
+                        &full_k[st]);
+    };
+    auto load_v = [&](int tile) {
+        const int st = tile & 1;
+        mbar_expect_tx(&full_v[st], KV_TILE_BYTES);
+#pragma unroll
+        for (int b = 0; b < 4; b++)
+            tma_load_2d(smem + OFF_V + st * KV_TILE_BYTES + b * KV_BOX, &vmap, b * 64, kv_row0 + tile * PF_N,
+                        &full_v[st]);
+    };
+    constexpr uint32_t IDESC_QK = idesc_bf16(PF_N, 0);
+    constexpr uint32_t IDESC_PV = idesc_bf16(HEAD_DIM, 1);
+    const uint32_t q_s = smem_u32(smem + OFF_Q);
+    auto issue_qk = [&](int tile) {  // S[tile&1] = Q K^T
+        const uint32_t k_s = smem_u32(smem + OFF_K + (tile & 1) * KV_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 16; ks++) {
+            const uint64_t a = smem_desc_sw128(q_s + (ks >> 2) * Q_BOX + (ks & 3) * 32, 16, 1024);
+            const uint64_t b = smem_desc_sw128(k_s + (ks >> 2) * KV_BOX + (ks & 3) * 32, 16, 1024);
+            tc_mma_bf16(tmem + TM_S + (tile & 1) * PF_N, a, b, IDESC_QK, ks > 0);
+        }
+        tc_commit(&s_ready[tile & 1]);
+    };
+    auto issue_pv = [&](int tile) {  // O += P V
+        const uint32_t p_s = smem_u32(smem + OFF_P + (tile & 1) * P_BYTES);
+        const uint32_t v_s = smem_u32(smem + OFF_V + (tile & 1) * KV_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < PF_N / 16; ks++) {
+            const uint64_t a = smem_desc_sw128(p_s + ks * 32, 16, 1024);
+            // V: MN-major; 64-dim atoms KV_BOX apart (LBO), 8-row groups 1024 B apart (SBO)
+            const uint64_t b = smem_desc_sw128(v_s + ks * 2048, KV_BOX, 1024);
+            tc_mma_bf16(tmem + TM_O, a, b, IDESC_PV, (tile > 0) || (ks > 0));
+        }
+        tc_commit(&pv_done[tile & 1]);
+    };
+
+    if (tid == 0) {
+        mbar_expect_tx(full_q, Q_BYTES);
+#pragma unroll
+        for (int b = 0; b < 4; b++) tma_load_3d(smem + OFF_Q + b * Q_BOX, &qmap, b * 64, h, t0, full_q);
+        load_k(0);
+        load_v(0);
+        if (ntiles > 1) {
+            load_k(1);
+            load_v(1);
+        }
+    }
+
+    // ---- RoPE on this thread's Q row, in shared memory (dims 0..63 live in box 0) ----
+    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(full_q, 0));
+    if (ok && p.rotary_dim > 0 && row_tok < p.T) {
+        const int half = p.rotary_dim >> 1;  // <= 32 here (rotary_dim <= 64)
+        uint8_t *rowp = smem + OFF_Q + tid * 128;
+        const float2 *cs = reinterpret_cast<const float2 *>(p.cos_sin) + (size_t)row_tok * 32;
+        for (int i0 = 0; i0 < half; i0 += 8) {
+            const int c_lo = i0 >> 3, c_hi = (i0 + half) >> 3;
+            uint4 *plo = reinterpret_cast<uint4 *>(rowp + ((c_lo ^ (tid & 7)) << 4));
+            uint4 *phi = reinterpret_cast<uint4 *>(rowp + ((c_hi ^ (tid & 7)) << 4));
+            uint4 lo = *plo, hi = *phi;
+            __nv_bfloat16 *a = reinterpret_cast<__nv_bfloat16 *>(&lo);
+            __nv_bfloat16 *b = reinterpret_cast<__nv_bfloat16 *>(&hi);
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const float2 c = cs[i0 + e];  // (cos, sin)
+                const float x0 = __bfloat162float(a[e]), x1 = __bfloat162float(b[e]);
+                a[e] = __float2bfloat16_rn(x0 * c.x - x1 * c.y);
+                b[e] = __float2bfloat16_rn(x0 * c.y + x1 * c.x);
+            }
+            *plo = lo;
+            *phi = hi;
+        }
+    }
+    fence_proxy_async_smem();
+    if (__syncthreads_or(ok ? 0 : 1)) ok = false;
+
+    float m_run = -INFINITY, l_run = 0.0f;
+    const float sl2 = p.scale * LOG2E_PF;
+
+    if (ok && tid == 0) {
+        if (mbar_wait_bounded(&full_k[0], 0)) {
+            tc_fence_after();
+            issue_qk(0);
+        } else {
+            ok = false;
+        }
+    }
+
+    // thread 0's own failures (its extra waits) reach the others through the block-wide OR below
+    for (int j = 0; j < ntiles; j++) {
+        const int b = j & 1;
+        const unsigned par = (unsigned)(j >> 1) & 1u;
+        // tile j's scores are in TMEM once s_ready[b] completes; K stage b is then free
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_ready[b], par));
+        if (!ok) break;
+        tc_fence_after();
+        if (tid == 0) {
+            if (j + 2 < ntiles) load_k(j + 2);
+            if (j + 1 < ntiles) {  // start Q K^T of the next tile under this tile's softmax
+                if (mbar_wait_bounded(&full_k[(j + 1) & 1], (unsigned)((j + 1) >> 1) & 1u)) issue_qk(j + 1);
+                else ok = false;
+            }
+        }
+        float s[PF_N];
+        {
+            float t32[32];
+            tmem_ld32(lane_base + TM_S + b * PF_N, t32);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i++) s[i] = t32[i];
+            tmem_ld32(lane_base + TM_S + b * PF_N + 32, t32);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i++) s[32 + i] = t32[i];
+        }
+        const int kv0 = j * PF_N;
+        if (kv0 + PF_N - 1 > p.start_pos + t0) {  // tile touches the diagonal
+#pragma unroll
+            for (int c = 0; c < PF_N; c++)
+                if (kv0 + c > qpos) s[c] = -INFINITY;
+        }
+        float mx = s[0];
+#pragma unroll
+        for (int c = 1; c < PF_N; c++) mx = fmaxf(mx, s[c]);
+        const float m_new = fmaxf(m_run, mx);
+        // rescale O only when some row of the warp moved its maximum by more than 2^8
+        const bool need = (m_new - m_run) * sl2 > 8.0f;  // also true on the first tile (m_run = -inf)
+        const bool warp_rescale = __any_sync(0xffffffffu, need);
+        float corr = 1.0f;
+        if (warp_rescale) {
+            corr = ex2_approx((m_run - m_new) * sl2);
+            m_run = m_new;
+        }
+        const float mb = m_run * sl2;
+        float rs = 0.0f;
+        uint32_t pk[PF_N / 2];
+#pragma unroll
+        for (int c = 0; c < PF_N; c += 2) {
+            const float p0 = ex2_approx(fmaf(s[c], sl2, -mb));
+            const float p1 = ex2_approx(fmaf(s[c + 1], sl2, -mb));
+            rs += p0 + p1;
+            pk[c >> 1] = pack_bf16x2(p0, p1);
+        }
+        l_run = l_run * corr + rs;
+
+        // O and the P buffer are free once P V of tile j-1 has completed
+        if (j > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[(j - 1) & 1], (unsigned)((j - 1) >> 1) & 1u));
+            tc_fence_after();
+        }
+        if (warp_rescale && j > 0 && ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+                float o[32];
+                tmem_ld32(lane_base + TM_O + c0, o);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i++) o[i] *= corr;
+                tmem_st32(lane_base + TM_O + c0, o);
+            }
+            tc_wait_st();
+        }
+        {
+            uint8_t *prow = smem + OFF_P + b * P_BYTES + tid * 128;
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                *reinterpret_cast<uint4 *>(prow + ((c ^ (tid & 7)) << 4)) =
+                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(ok ? 0 : 1)) {
+            ok = false;
+            break;
+        }
+        if (tid == 0) {
+            tc_fence_after();
+            if (mbar_wait_bounded(&full_v[b], par)) {
+                issue_pv(j);
+                // V stage (j+1)&1 is free once P V of tile j-1 is done, which this thread saw above
+                if (j >= 1 && j + 1 < ntiles) load_v(j + 1);
+            } else {
+                ok = false;
+            }
+        }
+    }
+    // V of tile 1 was loaded in the prologue; tiles >= 2 are loaded in the loop one tile ahead
+
+    if (__syncthreads_or(ok ? 0 : 1)) ok = false;
+    if (ok && ntiles > 0) {
+        ok = mbar_wait_bounded(&pv_done[(ntiles - 1) & 1], (unsigned)((ntiles - 1) >> 1) & 1u);
+        tc_fence_after();
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+        // every lane takes part in the warp-wide TMEM loads; only the global accesses are predicated
+        const bool valid = row_tok < p.T;
+        const float inv = 1.0f / l_run;
+        const size_t off = ((size_t)(valid ? row_tok : 0) * p.H + h) * HEAD_DIM;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+            float o[32];
+            tmem_ld32(lane_base + TM_O + c0, o);
+            tc_wait_ld();
+            if (valid) {
+#pragma unroll
+                for (int v8 = 0; v8 < 4; v8++) {
+                    uint4 g4 = make_uint4(0, 0, 0, 0);
+                    if (p.gate) g4 = *reinterpret_cast<const uint4 *>(p.gate + off + c0 + v8 * 8);
+                    const __nv_bfloat16 *gb = reinterpret_cast<const __nv_bfloat16 *>(&g4);
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float x0 = o[v8 * 8 + 2 * e] * inv, x1 = o[v8 * 8 + 2 * e + 1] * inv;
+                        if (p.gate) {
+                            x0 *= 1.0f / (1.0f + expf(-__bfloat162float(gb[2 * e])));
+                            x1 *= 1.0f / (1.0f + expf(-__bfloat162float(gb[2 * e + 1])));
+                        }
+                        w[e] = pack_bf16x2(x0, x1);
+                    }
+                    *reinterpret_cast<uint4 *>(p.out + off + c0 + v8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    if (!ok && tid == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ---- RoPE table + KV append for T tokens ------------------------------------------
+template <typename CacheT>
+__global__ void __launch_bounds__(128)
+prefill_kv_append_kernel(const __nv_bfloat16 *k, const __nv_bfloat16 *v, CacheT *k_cache, CacheT *v_cache,
+                         float *cos_sin, const float *inv_freq, int T, int Hkv, int rotary_dim, int start_pos,
+                         size_t slot_row0, int cap_rows, int rank, int world, int block) {
+    __shared__ float s_cos[128], s_sin[128];
+    const int t = blockIdx.x;
+    const int pos = start_pos + t;
+    const int half = rotary_dim >> 1;
+    if (threadIdx.x < half) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[threadIdx.x], &sn, &cs);
+        s_cos[threadIdx.x] = cs;
+        s_sin[threadIdx.x] = sn;
+        if (threadIdx.x < 32) reinterpret_cast<float2 *>(cos_sin)[(size_t)t * 32 + threadIdx.x] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    int row = pos;
+    if (world > 1) {
+        const int blk = pos / block;
+        if (blk % world != rank) return;  // another context stores this position
+        row = (blk / world) * block + pos % block;
+    }
+    for (int idx = threadIdx.x; idx < Hkv * HEAD_DIM; idx += blockDim.x) {
+        const int hh = idx / HEAD_DIM, d = idx % HEAD_DIM;
+        const __nv_bfloat16 *kr = k + ((size_t)t * Hkv + hh) * HEAD_DIM;
+        float x = __bfloat162float(kr[d]);
+        if (d < rotary_dim) {
+            if (d < half) x = x * s_cos[d] - __bfloat162float(kr[d + half]) * s_sin[d];
+            else x = __bfloat162float(kr[d - half]) * s_sin[d - half] + x * s_cos[d - half];
+        }
+        const size_t o = (slot_row0 + (size_t)hh * cap_rows + row) * HEAD_DIM + d;
+        k_cache[o] = (CacheT)x;
+        v_cache[o] = (CacheT)__bfloat162float(v[((size_t)t * Hkv + hh) * HEAD_DIM + d]);
+    }
+}
+
+}  // namespace
+
+cudaError_t gqa_prefill_configure() {
+    return cudaFuncSetAttribute(gqa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
+}
+
+cudaError_t launch_prefill_kv_append(const void *k_bf16, const void *v_bf16, void *k_cache, void *v_cache,
+                                     int kv_bf16, float *cos_sin, const float *inv_freq, int T, int Hkv,
+                                     int rotary_dim, int start_pos, size_t slot_row0, int cap_rows, int rank,
+                                     int world, int block, cudaStream_t stream) {
+    if (T <= 0) return cudaSuccess;
+    const __nv_bfloat16 *k = reinterpret_cast<const __nv_bfloat16 *>(k_bf16);
+    const __nv_bfloat16 *v = reinterpret_cast<const __nv_bfloat16 *>(v_bf16);
+    if (kv_bf16)
+        prefill_kv_append_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(
+            k, v, reinterpret_cast<__nv_bfloat16 *>(k_cache), reinterpret_cast<__nv_bfloat16 *>(v_cache), cos_sin,
+            inv_freq, T, Hkv, rotary_dim, start_pos, slot_row0, cap_rows, rank, world, block);
+    else
+        prefill_kv_append_kernel<float><<<T, 128, 0, stream>>>(k, v, reinterpret_cast<float *>(k_cache),
+                                                               reinterpret_cast<float *>(v_cache), cos_sin, inv_freq,
+                                                               T, Hkv, rotary_dim, start_pos, slot_row0, cap_rows,
+                                                               rank, world, block);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gqa_prefill(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap,
+                               const PrefillAttnParams &p, cudaStream_t stream) {
+    if (p.T <= 0) return cudaSuccess;
+    dim3 grid((unsigned)((p.T + PF_M - 1) / PF_M), (unsigned)p.H, 1);
+    gqa_prefill_kernel<<<grid, 128, PF_SMEM, stream>>>(qmap, kmap, vmap, p);
+    return cudaGetLastError();
+}
+
+}  // namespace mfc

@@ -3,6 +3,7 @@
 // layers beyond the indices stored in an item.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -108,6 +109,28 @@ cudaError_t launch_kv_pack(const float *src_rows, void *dst_cache, int n_rows, i
                            cudaStream_t stream);
 cudaError_t launch_kv_unpack(const void *src_cache, float *dst_rows, int n_rows, int Hkv,
                              int cap_rows, int kv_bf16, cudaStream_t stream);
+
+// ---------------------------------------------------------------- prefill
+struct PrefillAttnParams {
+    const __nv_bfloat16 *gate;  // [T][H][256] bf16, or nullptr
+    __nv_bfloat16 *out;         // [T][H][256] bf16
+    const float *cos_sin;       // [T][32] (cos, sin) pairs written by the append kernel
+    int T, H, Hkv, group;
+    int start_pos;              // absolute position of token 0
+    int rotary_dim;             // <= 64
+    int kv_slot, cap_rows;
+    float scale;
+    unsigned *status;
+};
+cudaError_t gqa_prefill_configure();
+// RoPE table, rotated K and V of T tokens stored into the cache (bf16 inputs).
+cudaError_t launch_prefill_kv_append(const void *k_bf16, const void *v_bf16, void *k_cache, void *v_cache,
+                                     int kv_bf16, float *cos_sin, const float *inv_freq, int T, int Hkv,
+                                     int rotary_dim, int start_pos, size_t slot_row0, int cap_rows, int rank,
+                                     int world, int block, cudaStream_t stream);
+// qmap: 3-D map over q [T][H][256] bf16 with box {64, 1, 128}; kmap/vmap: cache maps with box {64, 64}.
+cudaError_t launch_gqa_prefill(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap,
+                               const PrefillAttnParams &p, cudaStream_t stream);
 
 // Per-thread message of the last failure that had no context (ctx.cu).
 std::string &no_ctx_error();

@@ -255,6 +255,12 @@ class Ctx:
                                               gate_ptr or None, out_ptr)
         self._check(rc, "mfc_lse_merge_gate_dev")
 
+    # -- prefill (device pointers, bf16 activations) ---------------------------
+    def full_attn_prefill_dev(self, layer, seq_id, start_pos, n_tokens, q_ptr, gate_ptr, k_ptr, v_ptr, out_ptr):
+        rc = self._lib.mfc_full_attn_prefill_dev(self._h, layer, seq_id, start_pos, n_tokens, q_ptr,
+                                                 gate_ptr or None, k_ptr, v_ptr, out_ptr)
+        self._check(rc, "mfc_full_attn_prefill_dev")
+
     # -- bulk state import from device memory ------------------------------------
     def kv_append_rows_dev(self, layer, seq_id, pos0, n_rows, k_rows_ptr, v_rows_ptr):
         rc = self._lib.mfc_kv_append_rows_dev(self._h, layer, seq_id, pos0, n_rows, k_rows_ptr, v_rows_ptr)
