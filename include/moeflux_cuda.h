@@ -65,6 +65,8 @@ typedef struct mfc_config {
     int32_t kv_block;            /* positions per block of the cyclic split (multiple of 32) */
     int32_t max_batch;           /* most (layer, sequence) items one batched call may carry */
     int32_t snapshot_version;    /* 1 (C engine's header, 8 words) or 2 (Rust port's, 10 words) */
+    int32_t max_prefill;         /* most tokens one mfc_linear_attn_prefill_dev call may carry
+                                    (sizes its scratch); 0 = min(max_seq, 8192) */
 } mfc_config;
 
 /* Fills *cfg with the A17B geometry, bf16 KV off (fp32), max_seq 8192,
@@ -197,6 +199,17 @@ int mfc_lse_merge_gate_dev(mfc_ctx *ctx, int32_t n_parts, int32_t n, const float
 int mfc_full_attn_prefill_dev(mfc_ctx *ctx, int32_t layer, int32_t seq_id, int32_t start_pos,
                               int32_t n_tokens, const void *q_bf16, const void *gate_bf16,
                               const void *k_bf16, const void *v_bf16, void *out_bf16);
+
+/* Prefill of n_tokens tokens of one GatedDeltaNet layer in one call, device
+ * pointers, bf16 activations: equal to n_tokens calls of mfc_linear_attn_step
+ * (which is how the reference prefills, mod.rs:1206-1212), computed as a causal
+ * conv over the tokens followed by the delta rule in chunks of 64 tokens on the
+ * tensor cores.  qkv: [n_tokens][conv_dim] bf16; z: [n_tokens][v_heads*128] bf16
+ * or NULL; alpha, beta: [n_tokens][v_heads] bf16; out: [n_tokens][v_heads*128]
+ * bf16.  n_tokens <= max_prefill.  Asynchronous on mfc_stream(ctx). */
+int mfc_linear_attn_prefill_dev(mfc_ctx *ctx, int32_t layer, int32_t seq_id, int32_t n_tokens,
+                                const void *qkv_bf16, const void *z_bf16, const void *alpha_bf16,
+                                const void *beta_bf16, void *out_bf16);
 
 /* Bulk import of state that already exists on the device (what a prefill, or a
  * prefix cache, hands over; the reference fills the same state token by token,

@@ -42,6 +42,7 @@ class Config(C.Structure):
         ("kv_block", C.c_int32),
         ("max_batch", C.c_int32),
         ("snapshot_version", C.c_int32),
+        ("max_prefill", C.c_int32),
     ]
 
 
@@ -72,6 +73,7 @@ SIGNATURES = {
     "mfc_full_attn_partial_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "mfc_lse_merge_gate_dev": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P, C.c_size_t, _P, _P]),
     "mfc_full_attn_prefill_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
+    "mfc_linear_attn_prefill_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "mfc_kv_append_rows_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "mfc_linear_state_set_dev": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P]),
     "mfc_memory_clear": (None, [_P, C.c_int32]),

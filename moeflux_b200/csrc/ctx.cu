@@ -65,6 +65,9 @@ struct mfc_ctx {
     CUtensorMap kmap, vmap;
     CUtensorMap kmap_pf, vmap_pf;  // same caches, 64-row boxes for the prefill kernel (bf16 cache only)
     float *pf_cos_sin = nullptr;   // [max_seq][32] (cos, sin) of the tokens of a prefill call
+    // GatedDeltaNet prefill scratch, max_prefill tokens
+    void *pf_q = nullptr, *pf_k = nullptr;
+    float *pf_v = nullptr, *pf_lg = nullptr, *pf_beta = nullptr;
     float *ssm = nullptr, *conv = nullptr;
     uint16_t *conv_w = nullptr, *dt_bias = nullptr, *norm_w = nullptr;
     float *a_log = nullptr;
@@ -166,7 +169,8 @@ void free_all(mfc_ctx *c) {
     void *ptrs[] = {c->k_cache, c->v_cache, c->ssm, c->conv, c->conv_w, c->dt_bias, c->norm_w, c->a_log,
                     c->inv_freq, c->d_gqa_items, c->d_gdn_items, c->sc_o, c->sc_m, c->sc_l, c->tickets,
                     c->status, c->st_q, c->st_gate, c->st_k, c->st_v, c->st_out, c->st_qkv, c->st_z,
-                    c->st_alpha, c->st_beta, c->st_gout, c->st_rows, c->pf_cos_sin};
+                    c->st_alpha, c->st_beta, c->st_gout, c->st_rows, c->pf_cos_sin, c->pf_q, c->pf_k, c->pf_v,
+                    c->pf_lg, c->pf_beta};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     if (c->stream && c->owns_stream) cudaStreamDestroy(c->stream);
@@ -497,6 +501,7 @@ void mfc_default_config(mfc_config *cfg) {
     cfg->kv_block = 256;
     cfg->max_batch = 60;
     cfg->snapshot_version = 1;
+    cfg->max_prefill = 0;
 }
 
 const char *mfc_last_error(const mfc_ctx *ctx) { return ctx ? ctx->err.c_str() : g_open_error.c_str(); }
@@ -563,6 +568,8 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
 
     c = new mfc_ctx();
     c->cfg = g;
+    if (c->cfg.max_prefill <= 0) c->cfg.max_prefill = g.max_seq < 8192 ? g.max_seq : 8192;
+    if (c->cfg.max_prefill > g.max_seq) c->cfg.max_prefill = g.max_seq;
     c->group = g.num_attn_heads / g.num_kv_heads;
     c->kv_esize = g.kv_dtype == MFC_KV_BF16 ? 2 : 4;
     c->conv_dim = 2 * g.linear_num_k_heads * GDN_DIM + g.linear_num_v_heads * GDN_DIM;
@@ -620,7 +627,12 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
          dalloc(c, &c->st_z, mb * vd, false) && dalloc(c, &c->st_alpha, mb * g.linear_num_v_heads, false) &&
          dalloc(c, &c->st_beta, mb * g.linear_num_v_heads, false) && dalloc(c, &c->st_gout, mb * vd, false) &&
          dalloc(c, &c->st_rows, (size_t)mfc_ctx::SNAP_ROWS * kvd, false) &&
-         dalloc(c, &c->pf_cos_sin, (size_t)g.max_seq * 64, false);
+         dalloc(c, &c->pf_cos_sin, (size_t)g.max_seq * 64, false) &&
+         dalloc(c, (uint16_t **)&c->pf_q, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
+         dalloc(c, (uint16_t **)&c->pf_k, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
+         dalloc(c, &c->pf_v, (size_t)c->cfg.max_prefill * vd, false) &&
+         dalloc(c, &c->pf_lg, (size_t)c->cfg.max_prefill * g.linear_num_v_heads, false) &&
+         dalloc(c, &c->pf_beta, (size_t)c->cfg.max_prefill * g.linear_num_v_heads, false);
     if (ok) {
         // the host's libm evaluates the frequencies, exactly as the reference does
         // (crates/moeflux/src/riir/rope.rs:99-101); the device only multiplies by pos
@@ -633,6 +645,7 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     ok = ok && make_tensor_map(c, &c->kmap, c->k_cache, kv_rows) && make_tensor_map(c, &c->vmap, c->v_cache, kv_rows);
     if (ok && g.kv_dtype == MFC_KV_BF16)
         ok = make_tensor_map(c, &c->kmap_pf, c->k_cache, kv_rows, 64) && make_tensor_map(c, &c->vmap_pf, c->v_cache, kv_rows, 64);
+    if (ok && gdn_prefill_configure() != cudaSuccess) ok = fail(c, "cannot opt in to the prefill kernel's shared memory size");
     if (ok && gqa_prefill_configure() != cudaSuccess) ok = fail(c, "cannot opt in to the prefill kernel's shared memory size");
     if (ok && (gqa_decode_configure() != cudaSuccess || gqa_decode_f32_configure() != cudaSuccess)) ok = fail(c, "cannot opt in to the kernels' shared memory size");
     if (!ok) {
@@ -1031,6 +1044,63 @@ int mfc_full_attn_prefill_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, int32_t
     CK(launch_gqa_prefill(qmap, c->kmap_pf, c->vmap_pf, p, c->stream));
     c->launches += 2;
     c->kv_len[slot] += n_tokens;
+    return 0;
+}
+
+int mfc_linear_attn_prefill_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, int32_t n_tokens, const void *qkv_bf16,
+                                const void *z_bf16, const void *alpha_bf16, const void *beta_bf16, void *out_bf16) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (!qkv_bf16 || !alpha_bf16 || !beta_bf16 || !out_bf16 || n_tokens <= 0) {
+        fail(c, "NULL argument or n_tokens <= 0");
+        return -1;
+    }
+    if (layer < 0 || layer >= g.num_layers || is_full_layer(g, layer) || seq_id < 0 || seq_id >= g.n_seqs) {
+        fail(c, "not a linear-attention layer / seq_id out of range");
+        return -1;
+    }
+    const int ll = c->layer_to_lin[layer];
+    if (!c->lin_weights_set[ll] || (z_bf16 && c->lin_weights_set[ll] != 2)) {
+        fail(c, "mfc_set_linear_weights was not called for layer " + std::to_string(layer) + " (or no norm weight for z)");
+        return -1;
+    }
+    if (n_tokens > g.max_prefill) {
+        fail(c, "n_tokens " + std::to_string(n_tokens) + " exceeds max_prefill " + std::to_string(g.max_prefill));
+        return -1;
+    }
+    if ((g.linear_num_v_heads * GDN_DIM) % g.linear_num_k_heads != 0 || ((uintptr_t)qkv_bf16 & 15)) {
+        fail(c, "unsupported head geometry or misaligned qkv");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    const int slot = ll * g.n_seqs + seq_id;
+    GdnPrefillParams p;
+    memset(&p, 0, sizeof(p));
+    p.qkv = qkv_bf16;
+    p.z = z_bf16;
+    p.alpha = alpha_bf16;
+    p.beta = beta_bf16;
+    p.out = out_bf16;
+    p.ssm = c->ssm + (size_t)slot * g.linear_num_v_heads * GDN_DIM * GDN_DIM;
+    p.ring = c->conv + (size_t)slot * CONV_TAPS * c->conv_dim;
+    p.slot0 = (int)(c->conv_step[slot] & 3);
+    p.conv_w = c->conv_w + (size_t)ll * c->conv_dim * 4;
+    p.a_log = c->a_log + (size_t)ll * g.linear_num_v_heads;
+    p.dt_bias = c->dt_bias + (size_t)ll * g.linear_num_v_heads;
+    p.norm_w = c->norm_w + (size_t)ll * GDN_DIM;
+    p.q_hat = c->pf_q;
+    p.k_hat = c->pf_k;
+    p.v_io = c->pf_v;
+    p.lg = c->pf_lg;
+    p.beta_gate = c->pf_beta;
+    p.T = n_tokens;
+    p.Hk = g.linear_num_k_heads;
+    p.Hv = g.linear_num_v_heads;
+    p.conv_dim = c->conv_dim;
+    p.eps = g.rms_norm_eps;
+    CK(launch_gdn_prefill(p, c->stream));
+    c->launches += 4;
+    c->conv_step[slot] += n_tokens;
     return 0;
 }
 

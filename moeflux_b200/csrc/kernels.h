@@ -132,6 +132,26 @@ cudaError_t launch_prefill_kv_append(const void *k_bf16, const void *v_bf16, voi
 cudaError_t launch_gqa_prefill(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap,
                                const PrefillAttnParams &p, cudaStream_t stream);
 
+struct GdnPrefillParams {
+    const void *qkv;          // [T][conv_dim] bf16
+    const void *z;            // [T][Hv*128] bf16 or nullptr
+    const void *alpha, *beta; // [T][Hv] bf16
+    void *out;                // [T][Hv*128] bf16
+    float *ssm;               // this (layer, sequence)'s state [Hv][128][128]
+    float *ring;              // its conv ring [4][conv_dim]
+    int slot0;                // ring slot of token 0 (conv step & 3)
+    const uint16_t *conv_w;   // the layer's weights
+    const float *a_log;
+    const uint16_t *dt_bias, *norm_w;
+    void *q_hat, *k_hat;      // scratch [T][Hk*128] bf16
+    float *v_io;              // scratch [T][Hv*128] fp32 (v in, raw read-out out)
+    float *lg, *beta_gate;    // scratch [T][Hv]
+    int T, Hk, Hv, conv_dim;
+    float eps;
+};
+cudaError_t gdn_prefill_configure();
+cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, cudaStream_t stream);
+
 // Per-thread message of the last failure that had no context (ctx.cu).
 std::string &no_ctx_error();
 

@@ -261,6 +261,11 @@ class Ctx:
                                                  gate_ptr or None, k_ptr, v_ptr, out_ptr)
         self._check(rc, "mfc_full_attn_prefill_dev")
 
+    def linear_attn_prefill_dev(self, layer, seq_id, n_tokens, qkv_ptr, z_ptr, alpha_ptr, beta_ptr, out_ptr):
+        rc = self._lib.mfc_linear_attn_prefill_dev(self._h, layer, seq_id, n_tokens, qkv_ptr, z_ptr or None,
+                                                   alpha_ptr, beta_ptr, out_ptr)
+        self._check(rc, "mfc_linear_attn_prefill_dev")
+
     # -- bulk state import from device memory ------------------------------------
     def kv_append_rows_dev(self, layer, seq_id, pos0, n_rows, k_rows_ptr, v_rows_ptr):
         rc = self._lib.mfc_kv_append_rows_dev(self._h, layer, seq_id, pos0, n_rows, k_rows_ptr, v_rows_ptr)

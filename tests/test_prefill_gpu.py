@@ -74,3 +74,60 @@ def test_prefill_then_prefill_then_decode():
     with pytest.raises(M.MfcError, match="current length"):
         ctx.full_attn_prefill_dev(7, 1, 5, 4, 1, 0, 1, 1, 1)
     ctx.close()
+
+
+def _prefill_linear(ctx, orc, layer, seq, T, r, dev, use_z=True):
+    import torch
+
+    qkv = O.round_bf16(I.normal(r, (T, G.conv_dim)))
+    z = O.round_bf16(I.normal(r, (T, G.total_value)))
+    alpha = O.round_bf16(I.normal(r, (T, 64)))
+    beta = O.round_bf16(I.normal(r, (T, 64)))
+    dq, dz, da, db = (_bf16_dev(a, dev) for a in (qkv, z, alpha, beta))
+    out = torch.zeros(T, G.total_value, dtype=torch.bfloat16, device=dev)
+    torch.cuda.synchronize()
+    ctx.linear_attn_prefill_dev(layer, seq, T, dq.data_ptr(), dz.data_ptr() if use_z else 0, da.data_ptr(),
+                                db.data_ptr(), out.data_ptr())
+    ctx.synchronize()
+    got = out.float().cpu().numpy()
+    worst = 0.0
+    for t in range(T):
+        ref = orc.linear_attn_step(layer, seq, qkv[t], z[t] if use_z else None, alpha[t], beta[t])
+        worst = max(worst, I.rel_err(got[t], ref))
+    return worst
+
+
+@pytest.mark.parametrize("T", [1, 2, 64, 100, 200])
+def test_linear_attn_prefill_from_empty(T):
+    import torch
+
+    dev = torch.device("cuda:0")
+    ctx, orc = make_pair(max_seq=256, linear_layers=[0, 1])
+    worst = _prefill_linear(ctx, orc, 1, 0, T, I.rng(520 + T), dev)
+    assert worst <= TOL_BF16, worst
+    # the state left behind is the state of the sequential steps
+    from oracle import snapshot as snap
+    a, b = snap.state_load(G, ctx.state_save(0)), snap.state_load(G, orc.state_save(0))
+    assert np.array_equal(a[1][1], b[1][1])                      # conv history: moved, exact
+    assert I.rel_err(a[1][2], b[1][2]) <= TOL_BF16               # ssm state
+    ctx.close()
+
+
+def test_linear_prefill_chained_with_decode():
+    """decode steps, prefill, prefill without z, decode again: one continuous sequence."""
+    import torch
+
+    dev = torch.device("cuda:0")
+    ctx, orc = make_pair(max_seq=512, n_seqs=2, linear_layers=[0, 2])
+    r = I.rng(530)
+    for _ in range(5):
+        ins = I.gdn_step_inputs(r)
+        assert I.rel_err(ctx.linear_attn_step(2, 1, *ins), orc.linear_attn_step(2, 1, *ins)) <= 1e-4
+    assert _prefill_linear(ctx, orc, 2, 1, 150, r, dev) <= TOL_BF16
+    assert _prefill_linear(ctx, orc, 2, 1, 70, r, dev, use_z=False) <= TOL_BF16
+    for _ in range(6):
+        ins = I.gdn_step_inputs(r)
+        assert I.rel_err(ctx.linear_attn_step(2, 1, *ins), orc.linear_attn_step(2, 1, *ins)) <= TOL_BF16
+    with pytest.raises(M.MfcError, match="max_prefill"):
+        ctx.linear_attn_prefill_dev(2, 1, 100000, 16, 16, 16, 16, 16)
+    ctx.close()
