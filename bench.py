@@ -49,6 +49,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")
     ap.add_argument("--batch", type=int, default=8, help="sequences")
+    ap.add_argument("--workload", default="stack", choices=["stack", "prefill"],
+                    help="stack: the decode stack (headline); prefill: 8192-token chunked prefill of one hybrid block")
+    ap.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "f32"], help="KV cache storage type")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -438,6 +441,88 @@ def run_ours(args, rank, world, local_rank):
     return line
 
 
+# --------------------------------------------------------------------------- prefill workload
+def run_prefill(args):
+    """Chunked prefill of one hybrid block (3 GatedDeltaNet layers + 1 causal GQA layer), bf16
+    activations, seeded N(0,1) inputs; single GPU.  A step = the four prefill calls on an empty state."""
+    import torch
+
+    import moeflux_b200 as M
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    T, K, W = args.tokens, args.steps, args.warmup
+    ctx = M.Ctx(num_layers=4, max_seq=T, n_seqs=1, kv_dtype=M.KV_BF16, max_prefill=T)
+    stream = torch.cuda.Stream(device=dev)
+    ctx.set_stream(stream.cuda_stream)
+    rs = np.random.Generator(np.random.Philox(78))
+    bits = lambda a: torch.tensor(np.asarray(a, np.float32)).bfloat16().view(torch.int16).numpy().astype(np.uint16)
+    for layer in range(3):
+        ctx.set_linear_weights(layer, bits(rs.standard_normal((CONV_DIM, 4), dtype=np.float32) * 0.5),
+                               rs.uniform(0, 2.7, HV).astype(np.float32), bits(rs.standard_normal(HV, dtype=np.float32)),
+                               bits(1 + 0.1 * rs.standard_normal(DK, dtype=np.float32)))
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    bf = lambda *shape: torch.randn(*shape, device=dev, generator=gen).bfloat16()
+    with torch.cuda.stream(stream):
+        lin_in = [(bf(T, CONV_DIM), bf(T, V_DIM), bf(T, HV), bf(T, HV)) for _ in range(3)]
+        lin_out = [torch.empty(T, V_DIM, device=dev, dtype=torch.bfloat16) for _ in range(3)]
+        q, gate, k, v = bf(T, Q_DIM), bf(T, Q_DIM), bf(T, KV_DIM), bf(T, KV_DIM)
+        out = torch.empty(T, Q_DIM, device=dev, dtype=torch.bfloat16)
+    stream.synchronize()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    t_lin, t_att, t_all = [], [], []
+    sampler = ClockSampler(0)
+    with torch.cuda.stream(stream):
+        for it in range(W + K):
+            ctx.memory_clear(0)
+            if it == W:
+                sampler.start()
+                time.sleep(0.3)
+                launches0 = ctx.launch_count
+                t0 = time.time()
+            e0, e1, e2 = ev(), ev(), ev()
+            e0.record(stream)
+            for layer in range(3):
+                x, z, a, b = lin_in[layer]
+                ctx.linear_attn_prefill_dev(layer, 0, T, x.data_ptr(), z.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                            lin_out[layer].data_ptr())
+            e1.record(stream)
+            ctx.full_attn_prefill_dev(3, 0, 0, T, q.data_ptr(), gate.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                      out.data_ptr())
+            e2.record(stream)
+            stream.synchronize()
+            if it >= W:
+                t_lin.append(e0.elapsed_time(e1))
+                t_att.append(e1.elapsed_time(e2))
+                t_all.append(e0.elapsed_time(e2))
+    ctx.synchronize()
+    clocks = sampler.stop(t0, time.time())
+    launches = ctx.launch_count - launches0
+    ms, ms_att, ms_lin = sum(t_all) / K, sum(t_att) / K, sum(t_lin) / K
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks_path))["bf16_tflops_sustained"]) if os.path.exists(peaks_path) else 1400.0
+    att_flops = 4.0 * H * D * T * (T + 1) / 2            # QK^T and PV over the causal half
+    chunk = 64
+    gdn_flops_chunk = 2.0 * (2 * chunk * chunk * DK + 2 * chunk * DK * DK + chunk * chunk * DK + DK * chunk * DK)
+    gdn_flops = 3 * HV * ((T + chunk - 1) // chunk) * gdn_flops_chunk
+    line = {"metric": "chunked prefill tokens/sec (hybrid block: 3 GatedDeltaNet + 1 causal GQA layer)",
+            "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 activations and KV, fp32 accumulate and state", "data": "synthetic",
+            "config": {"workload": f"chunked prefill of {T} tokens, 3 GatedDeltaNet layers (chunk 64) + 1 causal GQA layer",
+                       "tokens": T},
+            "roofline": {"bound": "tensor", "kernel": "gqa_prefill_kernel (tcgen05)", "achieved": att_flops / (ms_att * 1e-3) / 1e12,
+                         "peak": peak, "unit": "TFLOP/s", "frac": att_flops / (ms_att * 1e-3) / 1e12 / peak,
+                         "traffic": None, "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)",
+                         "ms_per_launch": ms_att, "flops_per_launch": att_flops,
+                         "other_kernels": {"gdn_prefill (3 layers)": {"ms": ms_lin, "flops": gdn_flops,
+                                                                      "achieved": gdn_flops / (ms_lin * 1e-3) / 1e12}}},
+            "e2e": None, "gpu_launches": int(launches), "clocks": clocks}
+    ctx.close()
+    return line
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -457,6 +542,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
+    if args.workload == "prefill":
+        if rank == 0:
+            print(json.dumps(run_prefill(args)), flush=True)
+        return
     line = run_ours(args, rank, world, local_rank)
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

@@ -103,6 +103,11 @@ int mfc_synchronize(mfc_ctx *ctx);
 int mfc_set_linear_weights(mfc_ctx *ctx, int32_t layer, const uint16_t *conv_w_bf16,
                            const float *a_log, const uint16_t *dt_bias_bf16,
                            const uint16_t *norm_w_bf16);
+/* q_norm / k_norm weights (bf16 [head_dim] each) of a full-attention layer, as
+ * read at crates/moeflux/src/riir/full_attn_forward.rs:257-276. */
+int mfc_set_full_attn_norm_weights(mfc_ctx *ctx, int32_t layer, const uint16_t *q_norm_bf16,
+                                   const uint16_t *k_norm_bf16);
+
 /* ------------------------------------------------------------------------
  * The hot path, one (layer, sequence) item per call.
  * ---------------------------------------------------------------------- */
@@ -141,6 +146,24 @@ int mfc_full_attn_step_batched(mfc_ctx *ctx, int32_t n, const int32_t *layers,
 int mfc_linear_attn_step_batched(mfc_ctx *ctx, int32_t n, const int32_t *layers,
                                  const int32_t *seq_ids, const float *qkv, const float *z,
                                  const float *alpha, const float *beta, float *out);
+
+/* Full-attention step taken from the projection outputs as the reference has
+ * them right after its q/k/v matvecs (full_attn_forward.rs:233-236): q_proj is
+ * [n][num_attn_heads][q (head_dim) | gate (head_dim)] interleaved per head.  The
+ * kernel de-interleaves (full_attn_forward.rs:238-254), applies the per-head
+ * RMSNorm of q and k with the weights of mfc_set_full_attn_norm_weights
+ * (:256-276), then RoPE, append, SDPA and the sigmoid gate as
+ * mfc_full_attn_step does.  k, v: [n][num_kv_heads*head_dim]; out:
+ * [n][num_attn_heads*head_dim].  Host pointers; the _dev form takes device
+ * pointers and is asynchronous. */
+int mfc_full_attn_step_qproj_batched(mfc_ctx *ctx, int32_t n, const int32_t *layers,
+                                     const int32_t *seq_ids, const int32_t *pos,
+                                     const float *q_proj, const float *k, const float *v,
+                                     float *out);
+int mfc_full_attn_step_qproj_batched_dev(mfc_ctx *ctx, int32_t n, const int32_t *layers,
+                                         const int32_t *seq_ids, const int32_t *pos,
+                                         const float *q_proj, const float *k, const float *v,
+                                         float *out);
 
 /* One token step of the attention sub-blocks of a whole layer stack, host
  * pointers: n_full full-attention items and n_lin GatedDeltaNet items (either
@@ -248,6 +271,20 @@ int mfc_memory_seq_pos_max(mfc_ctx *ctx, int32_t seq_id);
 size_t mfc_state_size(const mfc_ctx *ctx, int32_t seq_id);
 long long mfc_state_save(mfc_ctx *ctx, int32_t seq_id, void *buf, size_t buf_len);
 int mfc_state_load(mfc_ctx *ctx, int32_t seq_id, const void *buf, size_t buf_len);
+
+/* Position-keyed snapshots of one sequence kept inside the context:
+ * RsCtx::checkpoint_pos / restore_to / set_max_checkpoints / checkpoint_count
+ * (crates/moeflux/src/riir/mod.rs:2015-2100).  checkpoint_pos stores the current
+ * state under `pos` (overwriting an entry at the same pos) and, above the cap
+ * (default 4), evicts the least recently stored entry that is neither pos 0 nor
+ * the one just stored.  restore_to reloads the state stored under exactly `pos`
+ * (-1 with "no checkpoint stored at position ..." otherwise) and drops every
+ * entry with a larger position.  mfc_memory_clear drops them all;
+ * mfc_memory_seq_rm leaves them.  0 on success, -1 on error. */
+int mfc_checkpoint_pos(mfc_ctx *ctx, int32_t seq_id, int32_t pos);
+int mfc_restore_to(mfc_ctx *ctx, int32_t seq_id, int32_t pos);
+void mfc_set_max_checkpoints(mfc_ctx *ctx, int32_t n);
+int mfc_checkpoint_count(const mfc_ctx *ctx, int32_t seq_id);
 
 /* Host-only helpers (no GPU needed).
  * Block-cyclic KV split: rows of a sequence of whole length `len` that rank

@@ -62,6 +62,9 @@ SIGNATURES = {
     "mfc_set_stream": (C.c_int, [_P, _P]),
     "mfc_synchronize": (C.c_int, [_P]),
     "mfc_set_linear_weights": (C.c_int, [_P, C.c_int32, _U16, _F, _U16, _U16]),
+    "mfc_set_full_attn_norm_weights": (C.c_int, [_P, C.c_int32, _U16, _U16]),
+    "mfc_full_attn_step_qproj_batched": (C.c_int, [_P, C.c_int32, _I, _I, _I, _F, _F, _F, _F]),
+    "mfc_full_attn_step_qproj_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P, _P]),
     "mfc_full_attn_step": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _F, _F, _F, _F, _F]),
     "mfc_linear_attn_step": (C.c_int, [_P, C.c_int32, C.c_int32, _F, _F, _F, _F, _F]),
     "mfc_full_attn_step_batched": (C.c_int, [_P, C.c_int32, _I, _I, _I, _F, _F, _F, _F, _F]),
@@ -85,6 +88,10 @@ SIGNATURES = {
     "mfc_apply_rotary_emb": (C.c_int, [_P, C.c_int32, _F, _F]),
     "mfc_sdpa": (C.c_int, [_P, C.c_int32, _F, _F, _F, _F, _F]),
     "mfc_linear_attn_step_stateless": (C.c_int, [_P, C.c_int32, _F, _F, _F, _F, _F, _F, _F]),
+    "mfc_checkpoint_pos": (C.c_int, [_P, C.c_int32, C.c_int32]),
+    "mfc_restore_to": (C.c_int, [_P, C.c_int32, C.c_int32]),
+    "mfc_set_max_checkpoints": (None, [_P, C.c_int32]),
+    "mfc_checkpoint_count": (C.c_int, [_P, C.c_int32]),
     "mfc_kv_local_len": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "mfc_kv_local_row": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "mfc_snapshot_validate": (C.c_longlong, [C.POINTER(Config), _P, C.c_size_t]),

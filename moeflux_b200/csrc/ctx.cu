@@ -20,6 +20,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <deque>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -72,6 +74,9 @@ struct mfc_ctx {
     uint16_t *conv_w = nullptr, *dt_bias = nullptr, *norm_w = nullptr;
     float *a_log = nullptr;
     float *inv_freq = nullptr;
+    uint16_t *qnorm_w = nullptr, *knorm_w = nullptr;  // [n_full][256] bf16, optional per-head norm weights
+    std::vector<uint8_t> full_norm_set;
+    float *st_qproj = nullptr;                        // staging of interleaved q|gate rows
 
     std::vector<int32_t> kv_len;     // [n_full * n_seqs + 1] whole-sequence lengths
     std::vector<int64_t> conv_step;  // [n_state_slots]
@@ -90,6 +95,11 @@ struct mfc_ctx {
     float *st_qkv = nullptr, *st_z = nullptr, *st_alpha = nullptr, *st_beta = nullptr, *st_gout = nullptr;
     float *st_rows = nullptr;  // snapshot / hook staging, SNAP_ROWS wire rows
     static constexpr int SNAP_ROWS = 4096;
+
+    // Per-sequence store of snapshots keyed by position (crates/moeflux/src/riir/mod.rs:2015-2087)
+    std::vector<std::map<int32_t, std::vector<uint8_t>>> checkpoints;
+    std::vector<std::deque<int32_t>> checkpoint_order;  // least recently stored first
+    size_t max_checkpoints = 4;                         // DEFAULT_MAX_CHECKPOINTS, mod.rs:108
 
     int gdn_rows = 0;  // 0: chosen per launch from the item count
     int gqa_target_ctas = 148 * 2 * 4;
@@ -170,7 +180,7 @@ void free_all(mfc_ctx *c) {
                     c->inv_freq, c->d_gqa_items, c->d_gdn_items, c->sc_o, c->sc_m, c->sc_l, c->tickets,
                     c->status, c->st_q, c->st_gate, c->st_k, c->st_v, c->st_out, c->st_qkv, c->st_z,
                     c->st_alpha, c->st_beta, c->st_gout, c->st_rows, c->pf_cos_sin, c->pf_q, c->pf_k, c->pf_v,
-                    c->pf_lg, c->pf_beta};
+                    c->pf_lg, c->pf_beta, c->qnorm_w, c->knorm_w, c->st_qproj};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     if (c->stream && c->owns_stream) cudaStreamDestroy(c->stream);
@@ -295,6 +305,10 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
     p.rotary_dim = g.rotary_dim;
     p.cap_rows = c->cap_rows;
     p.scale = 1.0f / sqrtf((float)g.head_dim);
+    p.q_row_stride = HEAD_DIM;
+    p.gate_row_stride = HEAD_DIM;
+    p.n_seqs = g.n_seqs;
+    p.norm_eps = g.rms_norm_eps;
 }
 
 int launch_gqa(mfc_ctx *c, const GqaParams &p) {
@@ -589,6 +603,9 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     c->kv_len.assign(c->n_kv_slots, 0);
     c->conv_step.assign(c->n_state_slots, 0);
     c->lin_weights_set.assign(c->n_lin > 0 ? c->n_lin : 1, 0);
+    c->full_norm_set.assign(c->n_full > 0 ? c->n_full : 1, 0);
+    c->checkpoints.resize(g.n_seqs);
+    c->checkpoint_order.resize(g.n_seqs);
     if (const char *e = getenv("MFC_GDN_ROWS")) c->gdn_rows = atoi(e);
     if (const char *e = getenv("MFC_GQA_TARGET_CTAS")) c->gqa_target_ctas = atoi(e);
     if (c->gdn_rows != 32 && c->gdn_rows != 64 && c->gdn_rows != 128) c->gdn_rows = 0;
@@ -628,6 +645,8 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
          dalloc(c, &c->st_beta, mb * g.linear_num_v_heads, false) && dalloc(c, &c->st_gout, mb * vd, false) &&
          dalloc(c, &c->st_rows, (size_t)mfc_ctx::SNAP_ROWS * kvd, false) &&
          dalloc(c, &c->pf_cos_sin, (size_t)g.max_seq * 64, false) &&
+         dalloc(c, &c->qnorm_w, (size_t)(c->n_full + 1) * HEAD_DIM, true) &&
+         dalloc(c, &c->knorm_w, (size_t)(c->n_full + 1) * HEAD_DIM, true) && dalloc(c, &c->st_qproj, mb * qd * 2, false) &&
          dalloc(c, (uint16_t **)&c->pf_q, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
          dalloc(c, (uint16_t **)&c->pf_k, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
          dalloc(c, &c->pf_v, (size_t)c->cfg.max_prefill * vd, false) &&
@@ -835,6 +854,92 @@ int mfc_full_attn_step_batched(mfc_ctx *c, int32_t n, const int32_t *layers, con
 int mfc_full_attn_step(mfc_ctx *c, int32_t layer, int32_t seq_id, int32_t pos, const float *q, const float *gate,
                        const float *k, const float *v, float *out) {
     return mfc_full_attn_step_batched(c, 1, &layer, &seq_id, &pos, q, gate, k, v, out);
+}
+
+// ---------------------------------------------------------------- q projection layout + per-head norms
+
+int mfc_set_full_attn_norm_weights(mfc_ctx *c, int32_t layer, const uint16_t *q_norm_bf16, const uint16_t *k_norm_bf16) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (!q_norm_bf16 || !k_norm_bf16) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (layer < 0 || layer >= g.num_layers || !is_full_layer(g, layer)) {
+        fail(c, "layer " + std::to_string(layer) + " is not a full-attention layer");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    const int fl = c->layer_to_full[layer];
+    CK(cudaMemcpyAsync(c->qnorm_w + (size_t)fl * HEAD_DIM, q_norm_bf16, sizeof(uint16_t) * HEAD_DIM,
+                       cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->knorm_w + (size_t)fl * HEAD_DIM, k_norm_bf16, sizeof(uint16_t) * HEAD_DIM,
+                       cudaMemcpyHostToDevice, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    c->full_norm_set[fl] = 1;
+    return 0;
+}
+
+int mfc_full_attn_step_qproj_batched_dev(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                         const int32_t *pos, const float *q_proj, const float *k, const float *v,
+                                         float *out) {
+    if (!c) return -1;
+    if (!q_proj || !k || !v || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (c->cfg.kv_world != 1) {
+        fail(c, "this context holds a share of a KV split");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    if (layers && n > 0 && n <= c->cfg.max_batch)
+        for (int i = 0; i < n; i++) {
+            const int l = layers[i];
+            if (l < 0 || l >= c->cfg.num_layers || !is_full_layer(c->cfg, l) || !c->full_norm_set[c->layer_to_full[l]]) {
+                fail(c, "mfc_set_full_attn_norm_weights was not called for layer " + std::to_string(l));
+                return -1;
+            }
+        }
+    int total = 0;
+    if (build_gqa_items(c, n, layers, seq_ids, pos, &total)) return -1;
+    GqaParams p;
+    fill_gqa_params(c, p, n, total);
+    p.q = q_proj;                    // head row h: [q (256) | gate (256)]
+    p.gate = q_proj + HEAD_DIM;
+    p.q_row_stride = 2 * HEAD_DIM;
+    p.gate_row_stride = 2 * HEAD_DIM;
+    p.qnorm_w = c->qnorm_w;
+    p.knorm_w = c->knorm_w;
+    p.k = k;
+    p.v = v;
+    p.out = out;
+    p.partial_mode = 0;
+    return launch_gqa(c, p);
+}
+
+int mfc_full_attn_step_qproj_batched(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                     const int32_t *pos, const float *q_proj, const float *k, const float *v,
+                                     float *out) {
+    if (!c) return -1;
+    if (!q_proj || !k || !v || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (n <= 0 || n > c->cfg.max_batch) {
+        fail(c, "item count must be in [1, max_batch]");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    const size_t qd = sizeof(float) * c->cfg.num_attn_heads * HEAD_DIM * (size_t)n;
+    const size_t kd = sizeof(float) * c->cfg.num_kv_heads * HEAD_DIM * (size_t)n;
+    CK(cudaMemcpyAsync(c->st_qproj, q_proj, 2 * qd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_k, k, kd, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->st_v, v, kd, cudaMemcpyHostToDevice, c->stream));
+    if (mfc_full_attn_step_qproj_batched_dev(c, n, layers, seq_ids, pos, c->st_qproj, c->st_k, c->st_v, c->st_out))
+        return -1;
+    CK(cudaMemcpyAsync(out, c->st_out, qd, cudaMemcpyDeviceToHost, c->stream));
+    return check_status(c);
 }
 
 // ---------------------------------------------------------------- GatedDeltaNet
@@ -1168,6 +1273,12 @@ int mfc_linear_state_set_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, const fl
 void mfc_memory_clear(mfc_ctx *c, int32_t seq_id) {
     if (!c) return;
     mfc_memory_seq_rm(c, seq_id, 0, -1);
+    // a full clear invalidates every stored position (mod.rs:1964-1968)
+    if (seq_id >= -1 && seq_id < c->cfg.n_seqs)
+        for (int s = (seq_id < 0 ? 0 : seq_id); s < (seq_id < 0 ? c->cfg.n_seqs : seq_id + 1); s++) {
+            c->checkpoints[s].clear();
+            c->checkpoint_order[s].clear();
+        }
 }
 
 int mfc_memory_seq_rm(mfc_ctx *c, int32_t seq_id, int32_t p0, int32_t p1) {
@@ -1343,6 +1454,71 @@ int mfc_state_load(mfc_ctx *c, int32_t seq_id, const void *buf, size_t buf_len) 
     }
     CK(cudaStreamSynchronize(c->stream));
     return 0;
+}
+
+// ---------------------------------------------------------------- checkpoints (mod.rs:2015-2087)
+
+int mfc_checkpoint_pos(mfc_ctx *c, int32_t seq_id, int32_t pos) {
+    if (!c) return -1;
+    if (seq_id < 0 || seq_id >= c->cfg.n_seqs) {
+        fail(c, "seq_id out of range");
+        return -1;
+    }
+    std::vector<uint8_t> buf(mfc_state_size(c, seq_id));
+    if (mfc_state_save(c, seq_id, buf.data(), buf.size()) < 0) return -1;
+    auto &store = c->checkpoints[seq_id];
+    auto &order = c->checkpoint_order[seq_id];
+    if (store.count(pos)) {  // overwrite: refresh its place in the order
+        for (auto it = order.begin(); it != order.end(); ++it)
+            if (*it == pos) {
+                order.erase(it);
+                break;
+            }
+    }
+    store[pos] = std::move(buf);
+    order.push_back(pos);
+    // evict the oldest entries, never position 0 nor the one just stored
+    while (store.size() > c->max_checkpoints) {
+        bool evicted = false;
+        for (auto it = order.begin(); it != order.end(); ++it) {
+            if (*it == 0 || *it == pos) continue;
+            store.erase(*it);
+            order.erase(it);
+            evicted = true;
+            break;
+        }
+        if (!evicted) break;
+    }
+    return 0;
+}
+
+int mfc_restore_to(mfc_ctx *c, int32_t seq_id, int32_t pos) {
+    if (!c) return -1;
+    if (seq_id < 0 || seq_id >= c->cfg.n_seqs) {
+        fail(c, "seq_id out of range");
+        return -1;
+    }
+    auto &store = c->checkpoints[seq_id];
+    auto it = store.find(pos);
+    if (it == store.end()) {
+        fail(c, "no checkpoint stored at position " + std::to_string(pos));
+        return -1;
+    }
+    if (mfc_state_load(c, seq_id, it->second.data(), it->second.size())) return -1;
+    // positions after pos are about to be rewritten: their snapshots are void
+    for (auto e = store.begin(); e != store.end();) e = (e->first > pos) ? store.erase(e) : std::next(e);
+    auto &order = c->checkpoint_order[seq_id];
+    for (auto e = order.begin(); e != order.end();) e = (*e > pos) ? order.erase(e) : std::next(e);
+    return 0;
+}
+
+void mfc_set_max_checkpoints(mfc_ctx *c, int32_t n) {
+    if (c && n >= 0) c->max_checkpoints = (size_t)n;
+}
+
+int mfc_checkpoint_count(const mfc_ctx *c, int32_t seq_id) {
+    if (!c || seq_id < 0 || seq_id >= c->cfg.n_seqs) return -1;
+    return (int)c->checkpoints[seq_id].size();
 }
 
 // ---------------------------------------------------------------- host-only helpers

@@ -11,22 +11,51 @@ namespace mfc {
 
 constexpr float LOG2E = 1.4426950408889634f;
 
-// x[d], x[d+1] of one head row after partial RoPE (MLX half-split pairing,
-// crates/moeflux/src/riir/rope.rs:93-128); d even, tables indexed by pair index.
-__device__ __forceinline__ float2 load_rot2(const float *row, int d, int rotary_dim, int half,
-                                            const float *s_cos, const float *s_sin) {
+// x[d], x[d+1] of one head row after the optional per-head RMSNorm (x * inv_rms *
+// w[d], crates/moeflux/src/riir/rms_norm.rs:140-152) and partial RoPE (MLX
+// half-split pairing, crates/moeflux/src/riir/rope.rs:93-128); d even, tables
+// indexed by pair index.  nw == nullptr: no norm.
+__device__ __forceinline__ float2 load_norm2(const float *row, int d, float inv_rms, const uint16_t *nw) {
     float2 x = *reinterpret_cast<const float2 *>(row + d);
+    if (nw) {
+        const uint32_t wb = *reinterpret_cast<const uint32_t *>(nw + d);
+        x.x = x.x * inv_rms * bf16_bits_to_f32((uint16_t)(wb & 0xffffu));
+        x.y = x.y * inv_rms * bf16_bits_to_f32((uint16_t)(wb >> 16));
+    }
+    return x;
+}
+__device__ __forceinline__ float2 load_rot2(const float *row, int d, int rotary_dim, int half,
+                                            const float *s_cos, const float *s_sin, float inv_rms = 1.0f,
+                                            const uint16_t *nw = nullptr) {
+    float2 x = load_norm2(row, d, inv_rms, nw);
     if (d < rotary_dim) {
         if (d < half) {
-            const float2 pr = *reinterpret_cast<const float2 *>(row + d + half);
+            const float2 pr = load_norm2(row, d + half, inv_rms, nw);
             x = make_float2(x.x * s_cos[d] - pr.x * s_sin[d], x.y * s_cos[d + 1] - pr.y * s_sin[d + 1]);
         } else {
             const int i = d - half;
-            const float2 pr = *reinterpret_cast<const float2 *>(row + i);
+            const float2 pr = load_norm2(row, i, inv_rms, nw);
             x = make_float2(pr.x * s_sin[i] + x.x * s_cos[i], pr.y * s_sin[i + 1] + x.y * s_cos[i + 1]);
         }
     }
     return x;
+}
+
+// 1/rms of the 16 (or fewer) query head rows of a unit, by 4 warps: s_inv[row].
+// qbase points at row 0; rows are q_row_stride floats apart.  Contains a __syncthreads.
+__device__ __forceinline__ void head_inv_rms(const float *qbase, int rows, int row_stride, float eps, float *s_inv) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < 16; r += 4) {
+        float ss = 0.0f;
+        if (r < rows) {
+            const float4 a = *reinterpret_cast<const float4 *>(qbase + (size_t)r * row_stride + lane * 8);
+            const float4 b = *reinterpret_cast<const float4 *>(qbase + (size_t)r * row_stride + lane * 8 + 4);
+            ss = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_inv[r] = 1.0f / sqrtf(ss / (float)HEAD_DIM + eps);
+    }
+    __syncthreads();
 }
 
 struct Located {
@@ -101,6 +130,7 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
             acc.y = fmaf(w, o.y, acc.y);
         }
         const size_t off = (head0 + hr) * HEAD_DIM + 2 * tid;
+        const size_t goff = (head0 + hr) * (size_t)p.gate_row_stride + 2 * tid;
         if (p.partial_mode) {
             *reinterpret_cast<float2 *>(p.po + off) = acc;
             if (tid == 0) {
@@ -111,7 +141,7 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
             const float inv = 1.0f / s_L[hr];
             float2 r = make_float2(acc.x * inv, acc.y * inv);
             if (p.gate) {
-                const float2 gt = *reinterpret_cast<const float2 *>(p.gate + off);
+                const float2 gt = *reinterpret_cast<const float2 *>(p.gate + goff);
                 r.x *= 1.0f / (1.0f + expf(-gt.x));
                 r.y *= 1.0f / (1.0f + expf(-gt.y));
             }
@@ -159,7 +189,8 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
                     *reinterpret_cast<float2 *>(p.po + off) = rv;
                 } else {
                     if (p.gate) {
-                        const float2 gt = *reinterpret_cast<const float2 *>(p.gate + off);
+                        const float2 gt = *reinterpret_cast<const float2 *>(
+                            p.gate + (head0 + row) * (size_t)p.gate_row_stride + 64 * warp + 8 * nt + 2 * t);
                         rv.x *= 1.0f / (1.0f + expf(-gt.x));
                         rv.y *= 1.0f / (1.0f + expf(-gt.y));
                     }

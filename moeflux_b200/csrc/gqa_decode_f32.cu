@@ -51,6 +51,8 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     float *s_L = s_M + 16;                           // [16]
     __shared__ int s_flag;
     __shared__ int s_begin[LOCATE_SMEM_ITEMS];
+    __shared__ float s_inv[16];
+    __shared__ float s_kred[4];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -101,7 +103,16 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         const float *ksrc = p.k + ((size_t)it.in_idx * p.Hkv + L.kvh) * HEAD_DIM;
         const float *vsrc = p.v + ((size_t)it.in_idx * p.Hkv + L.kvh) * HEAD_DIM;
         const int d = 2 * tid;
-        const float2 kx = load_rot2(ksrc, d, p.rotary_dim, half, s_cos, s_sin);
+        float k_inv = 1.0f;
+        const uint16_t *knw = p.knorm_w ? p.knorm_w + (size_t)(it.kv_slot / p.n_seqs) * HEAD_DIM : nullptr;
+        if (knw) {  // per-head RMSNorm of k before the rotation
+            const float2 kr = *reinterpret_cast<const float2 *>(ksrc + d);
+            const float ss = warp_sum(kr.x * kr.x + kr.y * kr.y);
+            if (lane == 0) s_kred[warp] = ss;
+            __syncthreads();
+            k_inv = 1.0f / sqrtf(((s_kred[0] + s_kred[1]) + (s_kred[2] + s_kred[3])) / (float)HEAD_DIM + p.norm_eps);
+        }
+        const float2 kx = load_rot2(ksrc, d, p.rotary_dim, half, s_cos, s_sin, k_inv, knw);
         const float2 vx = *reinterpret_cast<const float2 *>(vsrc + d);
         const size_t roff = ((size_t)row_base + it.append_row) * HEAD_DIM + d;
         *reinterpret_cast<float2 *>(reinterpret_cast<float *>(p.k_base) + roff) = kx;
@@ -119,7 +130,9 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     // A (16x8, tf32): a0 (g, t)  a1 (g+8, t)  a2 (g, t+4)  a3 (g+8, t+4)
     uint32_t qh[8][4], ql[8][4];
     {
-        const float *qbase = p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * HEAD_DIM;
+        const float *qbase = p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * (size_t)p.q_row_stride;
+        const uint16_t *qnw = p.qnorm_w ? p.qnorm_w + (size_t)(it.kv_slot / p.n_seqs) * HEAD_DIM : nullptr;
+        if (qnw) head_inv_rms(qbase, group, p.q_row_stride, p.norm_eps, s_inv);
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
 #pragma unroll
@@ -128,8 +141,9 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
                 const int d = 64 * warp + 8 * ks + t + ((e & 2) ? 4 : 0);
                 float x = 0.0f;
                 if (row < group) {
-                    const float *qr = qbase + (size_t)row * HEAD_DIM;
-                    const float2 pr = load_rot2(qr, d & ~1, p.rotary_dim, half, s_cos, s_sin);
+                    const float *qr = qbase + (size_t)row * p.q_row_stride;
+                    const float qinv = qnw ? s_inv[row] : 1.0f;
+                    const float2 pr = load_rot2(qr, d & ~1, p.rotary_dim, half, s_cos, s_sin, qinv, qnw);
                     x = (d & 1) ? pr.y : pr.x;
                 }
                 split_tf32(x, qh[ks][e], ql[ks][e]);

@@ -80,6 +80,13 @@ struct GqaParams {
     int cap_rows;            // cache rows reserved per (kv_slot, kv head)
     int partial_mode;        // 0: gated final output, 1: un-normalised partials
     float scale;             // 1/sqrt(head_dim)
+    // Fused prologue of the projection outputs (all optional):
+    int q_row_stride;        // floats between consecutive head rows of q (256 packed; 512 when q and gate
+    int gate_row_stride;     //   are interleaved per head as the q projection emits them), same for gate
+    const uint16_t *qnorm_w; // [full layer][256] bf16 per-head RMSNorm weights of q, or nullptr
+    const uint16_t *knorm_w; // same for k
+    int n_seqs;              // kv_slot / n_seqs = full-layer index of an item
+    float norm_eps;
 };
 
 cudaError_t launch_gqa_decode_bf16(const CUtensorMap &kmap, const CUtensorMap &vmap,

@@ -124,6 +124,28 @@ class Ctx:
             None if nw is None else nw.ctypes.data_as(_U16))
         self._check(rc, "mfc_set_linear_weights")
 
+    def set_full_attn_norm_weights(self, layer: int, q_norm_bf16, k_norm_bf16):
+        g = self.cfg
+        qn = _u16(q_norm_bf16, g.head_dim, "q_norm_bf16")
+        kn = _u16(k_norm_bf16, g.head_dim, "k_norm_bf16")
+        rc = self._lib.mfc_set_full_attn_norm_weights(self._h, layer, qn.ctypes.data_as(_U16), kn.ctypes.data_as(_U16))
+        self._check(rc, "mfc_set_full_attn_norm_weights")
+
+    def full_attn_step_qproj_batched(self, layers, seq_ids, pos, q_proj, k, v) -> np.ndarray:
+        """q_proj: [n][heads][q | gate] as the q projection emits it; de-interleave and the
+        per-head q/k RMSNorm run inside the attention kernel."""
+        la, lp = _i32(layers)
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos)
+        n = la.size
+        qp = _f32(q_proj, 2 * n * self.q_dim, "q_proj")
+        k = _f32(k, n * self.kv_dim, "k")
+        v = _f32(v, n * self.kv_dim, "v")
+        out = np.empty((n, self.q_dim), np.float32)
+        rc = self._lib.mfc_full_attn_step_qproj_batched(self._h, n, lp, sp, pp, _fp(qp), _fp(k), _fp(v), _fp(out))
+        self._check(rc, "mfc_full_attn_step_qproj_batched")
+        return out
+
     # -- hot path, host arrays -------------------------------------------
     def full_attn_step(self, layer: int, seq_id: int, pos: int, q, gate, k, v) -> np.ndarray:
         q = _f32(q, self.q_dim, "q")
@@ -303,6 +325,19 @@ class Ctx:
         arr = np.frombuffer(data, dtype=np.uint8)
         rc = self._lib.mfc_state_load(self._h, seq_id, arr.ctypes.data if arr.size else None, arr.size)
         self._check(rc, "mfc_state_load")
+
+    # -- checkpoints (RsCtx::checkpoint_pos / restore_to) -------------------------
+    def checkpoint_pos(self, pos: int, seq_id: int = 0):
+        self._check(self._lib.mfc_checkpoint_pos(self._h, seq_id, pos), "mfc_checkpoint_pos")
+
+    def restore_to(self, pos: int, seq_id: int = 0):
+        self._check(self._lib.mfc_restore_to(self._h, seq_id, pos), "mfc_restore_to")
+
+    def set_max_checkpoints(self, n: int):
+        self._lib.mfc_set_max_checkpoints(self._h, n)
+
+    def checkpoint_count(self, seq_id: int = 0) -> int:
+        return int(self._lib.mfc_checkpoint_count(self._h, seq_id))
 
     # -- parity hooks ---------------------------------------------------------
     def apply_rotary_emb(self, pos: int, q, k):

@@ -1,0 +1,93 @@
+"""The multi-GPU plan of the path on CPU ranks (gloo, world_size 2): the
+block-cyclic KV-sequence split partitions every position once, each rank's
+partial over its own rows all-gathered as one [o | m | l] buffer merges to the
+unsplit result, appends go to the owner of the position, and the GatedDeltaNet
+sequences are dealt round-robin without overlap.  The arithmetic is the
+oracle's; the split arithmetic is the library's host-side code."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import moeflux_b200 as M
+import oracle as O
+from oracle import A17B as G
+from tests import inputs as I
+
+WORLD = 2
+BLOCK = 32
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, port, ctx_len, n_steps, result_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    L = M.lib()
+    r = I.rng(600)  # same stream on every rank: the ranks hold shares of the same sequence
+    K, V = I.normal(r, (ctx_len + n_steps, G.kv_dim)), I.normal(r, (ctx_len + n_steps, G.kv_dim))
+    H, D = G.num_attn_heads, G.head_dim
+    # this rank's compact local cache, filled by ownership
+    rows = [p for p in range(ctx_len) if L.mfc_kv_local_row(p, rank, WORLD, BLOCK) >= 0]
+    assert [L.mfc_kv_local_row(p, rank, WORLD, BLOCK) for p in rows] == list(range(len(rows)))
+    assert len(rows) == L.mfc_kv_local_len(ctx_len, rank, WORLD, BLOCK)
+    Kl, Vl = list(K[rows]), list(V[rows])
+    worst = 0.0
+    for step in range(n_steps):
+        pos = ctx_len + step
+        q, gate = I.normal(r, G.q_dim), I.normal(r, G.q_dim)
+        if L.mfc_kv_local_row(pos, rank, WORLD, BLOCK) >= 0:  # the owner appends
+            assert L.mfc_kv_local_row(pos, rank, WORLD, BLOCK) == len(Kl)
+            Kl.append(K[pos])
+            Vl.append(V[pos])
+        n_loc = len(Kl)
+        assert n_loc == L.mfc_kv_local_len(pos + 1, rank, WORLD, BLOCK)
+        if n_loc:
+            o, m, l = O.sdpa_partial(0, n_loc, q, np.stack(Kl), np.stack(Vl))
+        else:
+            o, m, l = np.zeros((H, D), np.float32), np.full(H, -np.inf, np.float32), np.zeros(H, np.float32)
+        part = torch.tensor(np.concatenate([o.reshape(-1), m, l]))
+        gathered = torch.empty(WORLD * part.numel())
+        dist.all_gather_into_tensor(gathered, part)
+        g = gathered.numpy().reshape(WORLD, -1)
+        got = O.lse_merge_gate(g[:, :H * D].reshape(WORLD, H, D), g[:, H * D:H * D + H], g[:, H * D + H:], gate)
+        ref = O.sdpa(pos + 1, q, gate, K[:pos + 1], V[:pos + 1])
+        worst = max(worst, I.rel_err(got, ref))
+    # every position has exactly one owner across the ranks
+    owned = torch.zeros(ctx_len + n_steps)
+    for p in range(ctx_len + n_steps):
+        if L.mfc_kv_local_row(p, rank, WORLD, BLOCK) >= 0:
+            owned[p] = 1
+    dist.all_reduce(owned)
+    assert bool((owned == 1).all())
+    # GatedDeltaNet sequences: round-robin, disjoint, complete
+    mine = torch.zeros(8)
+    for s in range(8):
+        if s % WORLD == rank:
+            mine[s] = 1
+    dist.all_reduce(mine)
+    assert bool((mine == 1).all())
+    w = torch.tensor([worst], dtype=torch.float64)
+    dist.all_reduce(w, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        with open(result_path, "w") as f:
+            f.write(repr(float(w[0])))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("ctx_len", [0, 100])
+def test_kv_split_two_ranks_gloo(tmp_path, ctx_len):
+    O.build()
+    path = str(tmp_path / "worst.txt")
+    mp.spawn(_worker, args=(_free_port(), ctx_len, 70, path), nprocs=WORLD, join=True)
+    worst = float(open(path).read())
+    assert worst <= 1e-5, worst

@@ -247,3 +247,33 @@ def test_kv_split_partials_merge_to_the_whole():
                 assert torch.isinf(m[1]).all() and (l[1] == 0).all()
     for c in parts + [whole]:
         c.close()
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_step_from_projection_outputs(bf16):
+    """q|gate de-interleave and per-head q/k RMSNorm fused into the kernel
+    (crates/moeflux/src/riir/full_attn_forward.rs:238-276), then the usual step."""
+    ctx, orc = make_pair(max_seq=128, n_seqs=2, kv_bf16=bf16, linear_layers=[])
+    r = I.rng(90)
+    qw = O.f32_to_bf16_bits(1.0 + I.normal(r, G.head_dim, 0.1))
+    kw = O.f32_to_bf16_bits(1.0 + I.normal(r, G.head_dim, 0.1))
+    with pytest.raises(M.MfcError, match="mfc_set_full_attn_norm_weights"):
+        ctx.full_attn_step_qproj_batched([3], [0], [0], np.zeros(2 * G.q_dim, np.float32), np.zeros(G.kv_dim, np.float32),
+                                         np.zeros(G.kv_dim, np.float32))
+    for layer in (3, 7):
+        ctx.set_full_attn_norm_weights(layer, qw, kw)
+    items = [(3, 0), (3, 1), (7, 1)]
+    tol = TOL_BF16 if bf16 else TOL_F32
+    for pos in range(40):
+        qp = [I.normal(r, 2 * G.q_dim) * 3.0 for _ in items]   # un-normalised projection outputs
+        k = [I.normal(r, G.kv_dim) * 2.0 for _ in items]
+        v = [I.normal(r, G.kv_dim) for _ in items]
+        got = ctx.full_attn_step_qproj_batched([l for l, _ in items], [s for _, s in items], [pos] * 3, np.stack(qp),
+                                               np.stack(k), np.stack(v))
+        for j, (l, s) in enumerate(items):
+            q, gate = O.split_q_gate(qp[j])
+            qn = O.rms_norm_per_head(qw, G.num_attn_heads, G.head_dim, q)
+            kn = O.rms_norm_per_head(kw, G.num_kv_heads, G.head_dim, k[j])
+            ref = orc.full_attn_step(l, s, pos, qn, gate, kn, v[j])
+            assert I.rel_err(got[j], ref) <= tol, (pos, j)
+    ctx.close()

@@ -132,3 +132,46 @@ def test_memory_seq_rm_and_pos_max_semantics():
     # decoding resumes at the truncated length
     _run_steps(ctx, orc, r, 2, start=ctx.memory_seq_pos_max(0))
     ctx.close()
+
+
+def test_checkpoint_restore_lru():
+    """checkpoint_pos / restore_to, the shapes of crates/moeflux/tests/checkpoint_restore.rs:
+    round trip, unknown position, memory_clear drops snapshots, LRU keeps the last n,
+    position 0 is protected."""
+    ctx, orc = make_pair(G8, max_seq=64)
+    r = I.rng(205)
+    ctx.checkpoint_pos(0)
+    _run_steps(ctx, orc, r, 3)
+    ctx.checkpoint_pos(3)
+    at3 = ctx.state_save(0)
+    orc3 = orc.state_save(0)
+    _run_steps(ctx, orc, r, 4, start=3)           # mutate by decoding
+    assert ctx.state_save(0) != at3
+    ctx.restore_to(3)
+    assert ctx.state_save(0) == at3 and ctx.memory_seq_pos_max(0) == 3
+    orc.state_load(0, orc3)
+    _run_steps(ctx, orc, r, 2, start=3)           # decoding resumes identically after the rewind
+    with pytest.raises(M.MfcError, match="no checkpoint stored at position 17"):
+        ctx.restore_to(17)
+    # LRU: cap 4, position 0 protected, the oldest other entry goes first
+    assert ctx.checkpoint_count() == 2
+    for p in (5, 6, 7, 8):
+        ctx.checkpoint_pos(p)
+    assert ctx.checkpoint_count() == 4
+    ctx.restore_to(0)                              # 0 survived; entries > 0 are dropped by the restore
+    assert ctx.checkpoint_count() == 1 and ctx.memory_seq_pos_max(0) == 0
+    with pytest.raises(M.MfcError):
+        ctx.restore_to(8)
+    ctx.checkpoint_pos(2)
+    ctx.checkpoint_pos(2)                          # overwrite keeps one entry
+    assert ctx.checkpoint_count() == 2
+    ctx.set_max_checkpoints(2)
+    ctx.checkpoint_pos(9)
+    assert ctx.checkpoint_count() == 2             # 2 evicted, 0 and 9 kept
+    with pytest.raises(M.MfcError):
+        ctx.restore_to(2)
+    ctx.memory_seq_rm(0, 1, -1)
+    assert ctx.checkpoint_count() == 2             # truncation keeps snapshots
+    ctx.memory_clear(0)
+    assert ctx.checkpoint_count() == 0             # a full clear drops them
+    ctx.close()
