@@ -194,7 +194,9 @@ def workload_config(args, n):
     return {"workload": f"60-layer hybrid attention-only decode stack (45 GatedDeltaNet + 15 GQA), batch {args.batch}, "
                         f"ctx {args.ctx}, {args.kv} KV, fp32 state",
             "layer_steps_per_step": N_LAYERS * args.batch, "context": args.ctx, "batch": args.batch,
-            "kv_dtype": args.kv, "parallelism": f"kv-sequence split x{n} + GatedDeltaNet sequences round-robin"
+            "kv_dtype": args.kv, "parallelism": f"kv-sequence split x{n} with one NCCL all-to-all of the log-sum-exp "
+                                                f"partials per step (each sequence is finished on its own rank) + "
+                                                f"GatedDeltaNet sequences round-robin"
             if n > 1 else "single GPU",
             "l2": "inputs (GBs of KV and state per step) exceed the 126 MB L2; no flush needed"}
 
@@ -221,6 +223,10 @@ def run_ours(args, rank, world, local_rank):
                 kv_block=256, max_batch=N_LAYERS * B)
     stream = torch.cuda.Stream(device=dev)  # owned by torch, so tensors allocated on it outlive the context safely
     ctx.set_stream(stream.cuda_stream)
+    if world > 1:
+        # the GatedDeltaNet launch runs beside the attention launch: with the KV split the attention
+        # launch is short enough to leave bandwidth unused at its edges
+        ctx.set_tuning("gdn_side_queue", 1)
     gen = torch.Generator(device=dev)
 
     # ---- state: seeded fills on the device, imported through the bulk-import calls ----
@@ -251,7 +257,12 @@ def run_ours(args, rank, world, local_rank):
                 stream.synchronize()
 
     # ---- items ----
-    gqa_items = [(l, s) for l in FULL_LAYERS for s in range(B)]
+    # full-attention items sorted by the rank that finishes them (the owner of the sequence), so the partial
+    # blocks of one destination are contiguous in the send buffer of the all-to-all
+    seq_order = sorted(range(B), key=lambda s: (s % world, s))
+    gqa_items = [(l, s) for s in seq_order for l in FULL_LAYERS]
+    if world > 1:
+        assert len(gqa_items) % world == 0, "batch must divide over the ranks"
     gdn_items = [(l, s) for l in LIN_LAYERS for s in my_seqs]
     ng, nl = len(gqa_items), len(gdn_items)
     g_layers = np.array([l for l, _ in gqa_items], np.int32)
@@ -273,9 +284,11 @@ def run_ours(args, rank, world, local_rank):
         beta = torch.randn(max(nl, 1), HV, device=dev, generator=gen)
         out_l = torch.empty(max(nl, 1), V_DIM, device=dev)
         if world > 1:
-            part_floats = ng * H * D + 2 * ng * H
-            part = torch.empty(part_floats, device=dev)
-            gathered = torch.empty(world * part_floats, device=dev)
+            item_floats = H * D + 2 * H           # [o | m | l] of one item
+            npr = ng // world                     # items this rank finishes
+            send = torch.empty(ng * item_floats, device=dev)
+            recv = torch.empty(world * npr * item_floats, device=dev)
+            out_own = torch.empty(npr, Q_DIM, device=dev)
     stream.synchronize()
 
     pos_now = [L0]
@@ -286,34 +299,41 @@ def run_ours(args, rank, world, local_rank):
     def device_step(timed):
         pos = np.full(ng, pos_now[0], np.int32)
         if timed:
-            d0 = ev()
-            d0.record(stream)
-        if nl:
-            ctx.linear_attn_step_batched_dev(l_layers, l_seqs, qkv.data_ptr(), z.data_ptr(), alpha.data_ptr(),
-                                             beta.data_ptr(), out_l.data_ptr())
-        if timed:
-            e0, e1 = ev(), ev()
-            e0.record(stream)
-            gdn_events.append((d0, e0))
+            d0, d1, e0, e1 = ev(), ev(), ev(), ev()
+
+        def gdn():
+            if timed:
+                d0.record(stream)
+            if nl:
+                ctx.linear_attn_step_batched_dev(l_layers, l_seqs, qkv.data_ptr(), z.data_ptr(), alpha.data_ptr(),
+                                                 beta.data_ptr(), out_l.data_ptr())
+            if timed:
+                d1.record(stream)
+
         if world == 1:
+            gdn()
+            if timed:
+                e0.record(stream)
             ctx.full_attn_step_batched_dev(g_layers, g_seqs, pos, q.data_ptr(), gate.data_ptr(), kk.data_ptr(),
                                            vv.data_ptr(), out_g.data_ptr())
             if timed:
                 e1.record(stream)
         else:
-            o_ptr = part.data_ptr()
-            m_ptr = o_ptr + 4 * ng * H * D
-            l_ptr = m_ptr + 4 * ng * H
-            ctx.full_attn_partial_batched_dev(g_layers, g_seqs, pos, q.data_ptr(), kk.data_ptr(), vv.data_ptr(), o_ptr,
-                                              m_ptr, l_ptr)
+            gdn()  # on the side queue
+            if timed:
+                e0.record(stream)
+            ctx.full_attn_partial_packed_dev(g_layers, g_seqs, pos, q.data_ptr(), kk.data_ptr(), vv.data_ptr(),
+                                             send.data_ptr())
             if timed:
                 e1.record(stream)
-            dist.all_gather_into_tensor(gathered, part)
-            go = gathered.data_ptr()
-            ctx.lse_merge_gate_dev(world, ng, go, go + 4 * ng * H * D, go + 4 * ng * H * D + 4 * ng * H,
-                                   gate.data_ptr(), out_g.data_ptr(), part_stride=part_floats)
+            # every item's partials travel to the rank that owns its sequence
+            dist.all_to_all_single(recv, send)
+            ctx.join()
+            ctx.lse_merge_gate_packed_dev(world, npr, recv.data_ptr(), gate[rank * npr:(rank + 1) * npr].data_ptr(),
+                                          out_own.data_ptr())
         if timed:
             gqa_events.append((e0, e1))
+            gdn_events.append((d0, d1))
         pos_now[0] += 1
 
     def barrier():
@@ -359,7 +379,9 @@ def run_ours(args, rank, world, local_rank):
         for h, d_ in ((hq, q), (hgate, gate), (hk, kk), (hv, vv), (hqkv, qkv), (hz, z), (ha, alpha), (hb, beta)):
             h.copy_(d_.cpu())
         h2d = 4 * (2 * ng * Q_DIM + 2 * ng * KV_DIM + nl * (CONV_DIM + V_DIM + 2 * HV))
-        d2h = 4 * (ng * Q_DIM + nl * V_DIM)
+        n_out = ng if world == 1 else ng // world
+        hout_own = hout[:n_out]
+        d2h = 4 * (n_out * Q_DIM + nl * V_DIM)
 
         def e2e_step():
             pos = np.full(ng, pos_now[0], np.int32)
@@ -381,7 +403,7 @@ def run_ours(args, rank, world, local_rank):
                         alpha.copy_(ha, non_blocking=True)
                         beta.copy_(hb, non_blocking=True)
                     device_step(False)
-                    hout.copy_(out_g, non_blocking=True)
+                    hout_own.copy_(out_own, non_blocking=True)
                     if nl:
                         hlo.copy_(out_l, non_blocking=True)
                     stream.synchronize()
@@ -417,6 +439,7 @@ def run_ours(args, rank, world, local_rank):
     # ctx-8192 case of this workload; the traffic is the streamed KV rows, so it scales with the rows of a launch.
     dram_over_algorithmic = {"bf16": 1.013, "f32": 1.007}[args.kv]
     traffic = gqa_alg_bytes * dram_over_algorithmic
+    launches_per_step = 2 if world == 1 else 3
     roofline = {"bound": "hbm", "kernel": f"gqa_decode_{args.kv}_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": gqa_alg_bytes, "ms_per_launch": gqa_ms,

@@ -234,6 +234,18 @@ int mfc_linear_attn_prefill_dev(mfc_ctx *ctx, int32_t layer, int32_t seq_id, int
                                 const void *qkv_bf16, const void *z_bf16, const void *alpha_bf16,
                                 const void *beta_bf16, void *out_bf16);
 
+/* Packed forms for an exchange that sends every item to one destination
+ * (all-to-all by sequence): the partial of item i is one block
+ * [o (heads*256) | m (heads) | l (heads)] at packed + i*(heads*258), so items
+ * sorted by destination form contiguous, equal-sized send segments.  The merge
+ * takes [n_parts][n] such blocks (what the all-to-all delivers for the n items
+ * this context finishes) and writes the gated outputs of those n items. */
+int mfc_full_attn_partial_packed_dev(mfc_ctx *ctx, int32_t n, const int32_t *layers,
+                                     const int32_t *seq_ids, const int32_t *pos, const float *q,
+                                     const float *k, const float *v, float *packed);
+int mfc_lse_merge_gate_packed_dev(mfc_ctx *ctx, int32_t n_parts, int32_t n,
+                                  const float *packed_parts, const float *gate, float *out);
+
 /* Bulk import of state that already exists on the device (what a prefill, or a
  * prefix cache, hands over; the reference fills the same state token by token,
  * crates/moeflux/src/riir/mod.rs:1206-1212).  Asynchronous on mfc_stream(ctx).
@@ -354,8 +366,16 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
 
 /* Tuning knobs (tests and sweeps): "gdn_rows" in {0,32,64,128} state rows per
  * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a launch aims for when it picks the KV chunk
- * length; "gqa_chunk" forces the chunk length (0 = automatic). */
+ * length (0 = wave-aware automatic plan); "gqa_chunk" forces the chunk length (0 = automatic); "gdn_side_queue" (see
+ * mfc_join). */
 int mfc_set_tuning(mfc_ctx *ctx, const char *key, int value);
+/* With the tuning "gdn_side_queue" = 1, mfc_linear_attn_step_batched_dev issues
+ * its kernel on a second queue of the context: it starts after everything
+ * already queued on mfc_stream(ctx) and runs beside whatever is queued there
+ * next (a bandwidth-bound attention launch leaves room for it).  mfc_join makes
+ * mfc_stream(ctx) wait for that kernel; mfc_synchronize and every host-pointer
+ * entry point join implicitly. */
+int mfc_join(mfc_ctx *ctx);
 
 /* Number of kernels this library has launched on the context so far. */
 long long mfc_launch_count(const mfc_ctx *ctx);

@@ -74,6 +74,8 @@ SIGNATURES = {
     "mfc_full_attn_step_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P, _P, _P]),
     "mfc_linear_attn_step_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _P, _P, _P, _P, _P]),
     "mfc_full_attn_partial_batched_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "mfc_full_attn_partial_packed_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P, _P]),
+    "mfc_lse_merge_gate_packed_dev": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P]),
     "mfc_lse_merge_gate_dev": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P, C.c_size_t, _P, _P]),
     "mfc_full_attn_prefill_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "mfc_linear_attn_prefill_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
@@ -96,6 +98,7 @@ SIGNATURES = {
     "mfc_kv_local_row": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "mfc_snapshot_validate": (C.c_longlong, [C.POINTER(Config), _P, C.c_size_t]),
     "mfc_sdpa_static_dev": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P]),
+    "mfc_join": (C.c_int, [_P]),
     "mfc_set_tuning": (C.c_int, [_P, C.c_char_p, C.c_int]),
     "mfc_launch_count": (C.c_longlong, [_P]),
 }

@@ -101,8 +101,11 @@ struct mfc_ctx {
     std::vector<std::deque<int32_t>> checkpoint_order;  // least recently stored first
     size_t max_checkpoints = 4;                         // DEFAULT_MAX_CHECKPOINTS, mod.rs:108
 
+    bool gdn_side = false;  // issue GatedDeltaNet _dev launches on the side queue (joined by mfc_join)
+    bool side_pending = false;
     int gdn_rows = 0;  // 0: chosen per launch from the item count
-    int gqa_target_ctas = 148 * 2 * 4;
+    int gqa_target_ctas = 0;  // 0: wave-aware plan; > 0: aim for this many CTAs per launch
+    int gqa_slots = 296;      // CTAs resident at once (2 per SM)
     int gqa_forced_chunk = 0;
     long long launches = 0;
     std::string err;
@@ -191,6 +194,10 @@ void free_all(mfc_ctx *c) {
 
 int check_status(mfc_ctx *c) {
     unsigned st = 0;
+    if (c->side_pending) {
+        CK(cudaStreamWaitEvent(c->stream, c->ev_join, 0));
+        c->side_pending = false;
+    }
     CK(cudaMemcpyAsync(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     if (st) {
@@ -203,20 +210,49 @@ int check_status(mfc_ctx *c) {
 
 // ---- item list construction ---------------------------------------------------------
 
-// Chunk length for one launch: enough CTAs to fill the GPU several times over,
-// at most MAX_SPLITS chunks per (item, kv head).
-int plan_chunk(const mfc_ctx *c, long long total_rows, int max_len) {
+// Chunk length for one launch.  CTAs are equal-sized and the GPU holds
+// `gqa_slots` of them at a time (2 per SM), so the launch runs in
+// ceil(total / slots) rounds: a plan of 4.05 waves costs 5 rounds.  Among plans
+// of 2 to 10 waves the one with the fewest CTAs whose last round is nearly
+// full wins (every CTA pays a fixed prologue and a partial write); at most
+// MAX_SPLITS chunks per (item, kv head), at least 256 rows per chunk.
+int plan_chunk(const mfc_ctx *c, long long total_rows, int max_len, const GqaItem *items = nullptr, int n_items = 0) {
+    const int min_ch = ((max_len + MAX_SPLITS - 1) / MAX_SPLITS + KV_TILE - 1) / KV_TILE * KV_TILE;
     if (c->gqa_forced_chunk > 0) {
         int ch = (c->gqa_forced_chunk + KV_TILE - 1) / KV_TILE * KV_TILE;
-        const int min_ch = ((max_len + MAX_SPLITS - 1) / MAX_SPLITS + KV_TILE - 1) / KV_TILE * KV_TILE;
         return ch > min_ch ? ch : min_ch;
     }
-    long long ch = (total_rows + c->gqa_target_ctas - 1) / c->gqa_target_ctas;
-    if (ch < 256) ch = 256;
-    const long long min_ch = (max_len + MAX_SPLITS - 1) / MAX_SPLITS;
-    if (ch < min_ch) ch = min_ch;
-    ch = (ch + KV_TILE - 1) / KV_TILE * KV_TILE;
-    return (int)ch;
+    auto clamp = [&](long long ch) {
+        if (ch < 256) ch = 256;
+        if (ch < min_ch) ch = min_ch;
+        return (int)((ch + KV_TILE - 1) / KV_TILE * KV_TILE);
+    };
+    if (c->gqa_target_ctas > 0) return clamp((total_rows + c->gqa_target_ctas - 1) / c->gqa_target_ctas);
+    const int slots = c->gqa_slots;
+    const int Hkv = c->cfg.num_kv_heads;
+    int best_ch = clamp((total_rows + 4 * slots - 1) / (4 * slots));
+    double best_eff = -1.0;
+    // candidates from 2 to 10 waves in quarter-wave steps; the first (fewest CTAs) whose
+    // last round is at least 95 % full wins, otherwise the fullest
+    for (int q = 8; q <= 40; q++) {
+        const long long target = (long long)q * slots / 4;
+        const int ch = clamp((total_rows + target - 1) / target);
+        long long total = 0;
+        if (items)
+            for (int i = 0; i < n_items; i++) total += (long long)Hkv * (items[i].local_len > 0 ? (items[i].local_len + ch - 1) / ch : 1);
+        else
+            total = (total_rows + ch - 1) / ch;
+        const double eff = (double)total / (double)(((total + slots - 1) / slots) * slots);
+        if (eff > best_eff) {
+            best_eff = eff;
+            best_ch = ch;
+        }
+        if (eff >= 0.95) {
+            best_ch = ch;
+            break;
+        }
+    }
+    return best_ch;
 }
 
 // Validates the items, advances the lengths and fills c->h_gqa_items.
@@ -267,7 +303,7 @@ int build_gqa_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq
         total_rows += (long long)it.local_len * g.num_kv_heads;
         if (it.local_len > max_len) max_len = it.local_len;
     }
-    const int chunk = plan_chunk(c, total_rows, max_len);
+    const int chunk = plan_chunk(c, total_rows, max_len, c->h_gqa_items.data(), n);
     int cta = 0;
     for (int i = 0; i < n; i++) {
         GqaItem &it = c->h_gqa_items[i];
@@ -307,6 +343,8 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
     p.scale = 1.0f / sqrtf((float)g.head_dim);
     p.q_row_stride = HEAD_DIM;
     p.gate_row_stride = HEAD_DIM;
+    p.po_item_stride = (size_t)g.num_attn_heads * HEAD_DIM;
+    p.pml_item_stride = (size_t)g.num_attn_heads;
     p.n_seqs = g.n_seqs;
     p.norm_eps = g.rms_norm_eps;
 }
@@ -609,8 +647,9 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     if (const char *e = getenv("MFC_GDN_ROWS")) c->gdn_rows = atoi(e);
     if (const char *e = getenv("MFC_GQA_TARGET_CTAS")) c->gqa_target_ctas = atoi(e);
     if (c->gdn_rows != 32 && c->gdn_rows != 64 && c->gdn_rows != 128) c->gdn_rows = 0;
-    if (c->gqa_target_ctas < 1) c->gqa_target_ctas = 1;
+    if (c->gqa_target_ctas < 0) c->gqa_target_ctas = 0;
     if (c->gqa_target_ctas > 8192) c->gqa_target_ctas = 8192;
+    c->gqa_slots = 2 * prop.multiProcessorCount;
     c->max_parts = 8192 + g.max_batch * g.num_kv_heads;
 
     bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
@@ -720,8 +759,11 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
         if (value != 0 && value != 32 && value != 64 && value != 128) return -1;
         c->gdn_rows = value;
     } else if (!strcmp(key, "gqa_target_ctas")) {
-        if (value < 1 || value > 8192) return -1;
+        if (value < 0 || value > 8192) return -1;
         c->gqa_target_ctas = value;
+    } else if (!strcmp(key, "gdn_side_queue")) {
+        if (mfc_join(c)) return -1;
+        c->gdn_side = value != 0;
     } else if (!strcmp(key, "gqa_chunk")) {
         if (value < 0) return -1;
         c->gqa_forced_chunk = value;
@@ -822,6 +864,49 @@ int mfc_lse_merge_gate_dev(mfc_ctx *c, int32_t n_parts, int32_t n, const float *
     cudaSetDevice(c->cfg.device);
     CK(launch_lse_merge_gate(n_parts, n, c->cfg.num_attn_heads, o_parts, m_parts, l_parts, part_stride, gate, out,
                              c->stream));
+    c->launches += 1;
+    return 0;
+}
+
+int mfc_full_attn_partial_packed_dev(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                     const int32_t *pos, const float *q, const float *k, const float *v,
+                                     float *packed) {
+    if (!c) return -1;
+    if (!q || !k || !v || !packed) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    int total = 0;
+    if (build_gqa_items(c, n, layers, seq_ids, pos, &total)) return -1;
+    const size_t hd = (size_t)c->cfg.num_attn_heads * HEAD_DIM, hh = (size_t)c->cfg.num_attn_heads;
+    GqaParams p;
+    fill_gqa_params(c, p, n, total);
+    p.q = q;
+    p.gate = nullptr;
+    p.k = k;
+    p.v = v;
+    p.po = packed;  // item i: [o (H*256) | m (H) | l (H)]
+    p.pm = packed + hd;
+    p.pl = packed + hd + hh;
+    p.po_item_stride = hd + 2 * hh;
+    p.pml_item_stride = hd + 2 * hh;
+    p.partial_mode = 1;
+    return launch_gqa(c, p);
+}
+
+int mfc_lse_merge_gate_packed_dev(mfc_ctx *c, int32_t n_parts, int32_t n, const float *packed_parts,
+                                  const float *gate, float *out) {
+    if (!c) return -1;
+    if (n_parts <= 0 || n <= 0 || !packed_parts || !out) {
+        fail(c, "bad argument");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    const size_t hd = (size_t)c->cfg.num_attn_heads * HEAD_DIM, hh = (size_t)c->cfg.num_attn_heads;
+    const size_t item = hd + 2 * hh;
+    CK(launch_lse_merge_gate(n_parts, n, c->cfg.num_attn_heads, packed_parts, packed_parts + hd, packed_parts + hd + hh,
+                             (size_t)n * item, gate, out, c->stream, item, item));
     c->launches += 1;
     return 0;
 }
@@ -961,7 +1046,28 @@ int mfc_linear_attn_step_batched_dev(mfc_ctx *c, int32_t n, const int32_t *layer
                 return -1;
             }
     }
-    return launch_gdn(c, n, qkv, z, alpha, beta, out);
+    if (!c->gdn_side) return launch_gdn(c, n, qkv, z, alpha, beta, out);
+    // side queue: ordered after everything already on the main queue, runs beside what follows on it
+    cudaStream_t main_stream = c->stream;
+    CK(cudaEventRecord(c->ev_fork, main_stream));
+    CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
+    c->stream = c->side_stream;
+    const int rc = launch_gdn(c, n, qkv, z, alpha, beta, out);
+    c->stream = main_stream;
+    if (rc) return -1;
+    CK(cudaEventRecord(c->ev_join, c->side_stream));
+    c->side_pending = true;
+    return 0;
+}
+
+int mfc_join(mfc_ctx *c) {
+    if (!c) return -1;
+    if (c->side_pending) {
+        cudaSetDevice(c->cfg.device);
+        CK(cudaStreamWaitEvent(c->stream, c->ev_join, 0));
+        c->side_pending = false;
+    }
+    return 0;
 }
 
 int mfc_linear_attn_step_batched(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,

@@ -132,10 +132,11 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
         const size_t off = (head0 + hr) * HEAD_DIM + 2 * tid;
         const size_t goff = (head0 + hr) * (size_t)p.gate_row_stride + 2 * tid;
         if (p.partial_mode) {
-            *reinterpret_cast<float2 *>(p.po + off) = acc;
+            const int hl = L.kvh * group + hr;  // head within the item
+            *reinterpret_cast<float2 *>(p.po + (size_t)L.it.in_idx * p.po_item_stride + (size_t)hl * HEAD_DIM + 2 * tid) = acc;
             if (tid == 0) {
-                p.pm[head0 + hr] = s_M[hr];
-                p.pl[head0 + hr] = s_L[hr];
+                p.pm[(size_t)L.it.in_idx * p.pml_item_stride + hl] = s_M[hr];
+                p.pl[(size_t)L.it.in_idx * p.pml_item_stride + hl] = s_L[hr];
             }
         } else {
             const float inv = 1.0f / s_L[hr];
@@ -176,8 +177,8 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
             const float m_nat = m_r[x] * p.scale;
             if (p.partial_mode) {
                 if (warp == 0 && t == 0) {
-                    p.pm[head0 + row] = m_nat;
-                    p.pl[head0 + row] = l_r[x];
+                    p.pm[(size_t)it.in_idx * p.pml_item_stride + L.kvh * group + row] = m_nat;
+                    p.pl[(size_t)it.in_idx * p.pml_item_stride + L.kvh * group + row] = l_r[x];
                 }
             }
             const float inv = p.partial_mode ? 1.0f : 1.0f / l_r[x];
@@ -186,7 +187,8 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
                 const size_t off = (head0 + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t;
                 float2 rv = make_float2(o[nt][2 * x] * inv, o[nt][2 * x + 1] * inv);
                 if (p.partial_mode) {
-                    *reinterpret_cast<float2 *>(p.po + off) = rv;
+                    *reinterpret_cast<float2 *>(p.po + (size_t)it.in_idx * p.po_item_stride +
+                                                (size_t)(L.kvh * group + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t) = rv;
                 } else {
                     if (p.gate) {
                         const float2 gt = *reinterpret_cast<const float2 *>(

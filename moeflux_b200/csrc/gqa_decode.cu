@@ -283,27 +283,28 @@ constexpr size_t BF16_SMEM = 1024 + (size_t)BF16_STAGES * 2 * TILE_BYTES_BF16 +
 // ---- stand-alone merge of gathered partials (cross-GPU KV split) ----------
 __global__ void __launch_bounds__(128)
 lse_merge_gate_kernel(int n_parts, int n, int H, const float *o_parts, const float *m_parts,
-                      const float *l_parts, size_t stride_o, size_t stride_ml, const float *gate,
-                      float *out) {
-    // one CTA per (item, head); 128 threads x 2 dims
-    const int ih = blockIdx.x;  // item * H + head
+                      const float *l_parts, size_t stride_o, size_t stride_ml, size_t item_o, size_t item_ml,
+                      const float *gate, float *out) {
+    // one CTA per (item, head); 128 threads x 2 dims.  Part r, item i, head h:
+    // o at o_parts + r*stride_o + i*item_o + h*256, m/l at + r*stride_ml + i*item_ml + h.
+    const int item = blockIdx.x / H, head = blockIdx.x % H;
     const int tid = threadIdx.x;
+    const size_t oo = (size_t)item * item_o + (size_t)head * HEAD_DIM, mo = (size_t)item * item_ml + head;
     float M = -INFINITY;
-    for (int r = 0; r < n_parts; r++) M = fmaxf(M, m_parts[r * stride_ml + ih]);
+    for (int r = 0; r < n_parts; r++) M = fmaxf(M, m_parts[r * stride_ml + mo]);
     float Ls = 0.0f;
     float2 acc = make_float2(0.0f, 0.0f);
     for (int r = 0; r < n_parts; r++) {
-        const float m = m_parts[r * stride_ml + ih];
+        const float m = m_parts[r * stride_ml + mo];
         const float w = (m == -INFINITY) ? 0.0f : expf(m - M);
-        Ls += w * l_parts[r * stride_ml + ih];
-        const float2 o = *reinterpret_cast<const float2 *>(
-            o_parts + r * stride_o + (size_t)ih * HEAD_DIM + 2 * tid);
+        Ls += w * l_parts[r * stride_ml + mo];
+        const float2 o = *reinterpret_cast<const float2 *>(o_parts + r * stride_o + oo + 2 * tid);
         acc.x = fmaf(w, o.x, acc.x);
         acc.y = fmaf(w, o.y, acc.y);
     }
     const float inv = 1.0f / Ls;
     float2 rv = make_float2(acc.x * inv, acc.y * inv);
-    const size_t off = (size_t)ih * HEAD_DIM + 2 * tid;
+    const size_t off = (size_t)blockIdx.x * HEAD_DIM + 2 * tid;
     if (gate) {
         const float2 gt = *reinterpret_cast<const float2 *>(gate + off);
         rv.x *= 1.0f / (1.0f + expf(-gt.x));
@@ -382,11 +383,15 @@ cudaError_t launch_gqa_decode_bf16(const CUtensorMap &kmap, const CUtensorMap &v
 
 cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
                                   const float *m_parts, const float *l_parts, size_t part_stride,
-                                  const float *gate, float *out, cudaStream_t stream) {
+                                  const float *gate, float *out, cudaStream_t stream, size_t o_item_stride,
+                                  size_t ml_item_stride) {
     if (n <= 0) return cudaSuccess;
-    const size_t so = part_stride ? part_stride : (size_t)n * H * HEAD_DIM;
-    const size_t sml = part_stride ? part_stride : (size_t)n * H;
-    lse_merge_gate_kernel<<<n * H, 128, 0, stream>>>(n_parts, n, H, o_parts, m_parts, l_parts, so, sml, gate, out);
+    const size_t io = o_item_stride ? o_item_stride : (size_t)H * HEAD_DIM;
+    const size_t iml = ml_item_stride ? ml_item_stride : (size_t)H;
+    const size_t so = part_stride ? part_stride : (size_t)n * io;
+    const size_t sml = part_stride ? part_stride : (size_t)n * iml;
+    lse_merge_gate_kernel<<<n * H, 128, 0, stream>>>(n_parts, n, H, o_parts, m_parts, l_parts, so, sml, io, iml, gate,
+                                                     out);
     return cudaGetLastError();
 }
 

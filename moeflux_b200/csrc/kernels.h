@@ -70,7 +70,9 @@ struct GqaParams {
     const float *k;          // [n][Hkv][256]
     const float *v;          // [n][Hkv][256]
     float *out;              // final mode: [n][H][256]
-    float *po, *pm, *pl;     // partial mode outputs [n][H][256], [n][H], [n][H]
+    float *po, *pm, *pl;     // partial mode outputs: item i at po + i*po_item_stride ([H][256]) and
+    size_t po_item_stride;   //   pm/pl + i*pml_item_stride ([H]); dense = H*256 and H, packed per item
+    size_t pml_item_stride;  //   [o | m | l] = H*256 + 2H for both
     float *sc_o, *sc_m, *sc_l;  // split-K scratch, one slot per CTA
     unsigned *tickets;       // [n][Hkv], zero between launches
     const float *inv_freq;   // [rotary_dim/2]
@@ -101,7 +103,8 @@ cudaError_t gqa_decode_f32_configure();
 // part r-1; part_stride 0 means densely packed [n_parts][n][H][256] / [n_parts][n][H].
 cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
                                   const float *m_parts, const float *l_parts, size_t part_stride,
-                                  const float *gate, float *out, cudaStream_t stream);
+                                  const float *gate, float *out, cudaStream_t stream,
+                                  size_t o_item_stride = 0, size_t ml_item_stride = 0);
 
 // RoPE on packed q [H][256], k [Hkv][256] in place (parity hook).
 cudaError_t launch_rope(float *q, float *k, int H, int Hkv, int rotary_dim, int pos,

@@ -185,6 +185,8 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
     p.scale = 1.0f / sqrtf((float)HEAD_DIM);
     p.q_row_stride = HEAD_DIM;
     p.gate_row_stride = HEAD_DIM;
+    p.po_item_stride = (size_t)num_attn_heads * HEAD_DIM;
+    p.pml_item_stride = (size_t)num_attn_heads;
     p.n_seqs = 1;
     e = bf16 ? launch_gqa_decode_bf16(kmap, vmap, p, stream) : launch_gqa_decode_f32(kmap, vmap, p, stream);
     if (e != cudaSuccess) return fail(std::string("kernel launch: ") + cudaGetErrorString(e));

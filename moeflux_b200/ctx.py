@@ -108,6 +108,10 @@ class Ctx:
     def set_tuning(self, key: str, value: int):
         self._check(self._lib.mfc_set_tuning(self._h, key.encode(), int(value)), f"mfc_set_tuning({key})")
 
+    def join(self):
+        """Make ``self.stream`` wait for a GatedDeltaNet launch issued on the side queue."""
+        self._check(self._lib.mfc_join(self._h), "mfc_join")
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.mfc_launch_count(self._h))
@@ -271,6 +275,17 @@ class Ctx:
         rc = self._lib.mfc_full_attn_partial_batched_dev(self._h, la.size, lp, sp, pp, q_ptr, k_ptr, v_ptr, o_ptr,
                                                          m_ptr, l_ptr)
         self._check(rc, "mfc_full_attn_partial_batched_dev")
+
+    def full_attn_partial_packed_dev(self, layers, seq_ids, pos, q_ptr, k_ptr, v_ptr, packed_ptr):
+        la, lp = _i32(layers)
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos)
+        rc = self._lib.mfc_full_attn_partial_packed_dev(self._h, la.size, lp, sp, pp, q_ptr, k_ptr, v_ptr, packed_ptr)
+        self._check(rc, "mfc_full_attn_partial_packed_dev")
+
+    def lse_merge_gate_packed_dev(self, n_parts, n, packed_ptr, gate_ptr, out_ptr):
+        rc = self._lib.mfc_lse_merge_gate_packed_dev(self._h, n_parts, n, packed_ptr, gate_ptr or None, out_ptr)
+        self._check(rc, "mfc_lse_merge_gate_packed_dev")
 
     def lse_merge_gate_dev(self, n_parts, n, o_ptr, m_ptr, l_ptr, gate_ptr, out_ptr, part_stride=0):
         rc = self._lib.mfc_lse_merge_gate_dev(self._h, n_parts, n, o_ptr, m_ptr, l_ptr, part_stride,

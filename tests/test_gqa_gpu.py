@@ -216,6 +216,7 @@ def test_kv_split_partials_merge_to_the_whole():
     kw = dict(max_seq=512, n_seqs=2, linear_layers=[])
     whole, orc = make_pair(**kw)
     parts = [make_pair(kv_rank=rk, kv_world=2, kv_block=32, **kw)[0] for rk in range(2)]
+    packed_parts = [make_pair(kv_rank=rk, kv_world=2, kv_block=32, **kw)[0] for rk in range(2)]
     r = I.rng(80)
     items = [(3, 0), (3, 1), (11, 1)]
     layers, seqs = [i[0] for i in items], [i[1] for i in items]
@@ -239,13 +240,27 @@ def test_kv_split_partials_merge_to_the_whole():
         parts[0].lse_merge_gate_dev(2, n, o.data_ptr(), m.data_ptr(), l.data_ptr(), gate.data_ptr(), out.data_ptr())
         parts[0].synchronize()
         out = out.cpu().numpy()
-        for j, (layer, seq) in enumerate(items):
-            ref = orc.full_attn_step(layer, seq, pos, *ins[j])
-            assert I.rel_err(out[j], ref) <= TOL_F32, (pos, j)
+        refs = [orc.full_attn_step(layer, seq, pos, *ins[j]) for j, (layer, seq) in enumerate(items)]
+        for j in range(n):
+            assert I.rel_err(out[j], refs[j]) <= TOL_F32, (pos, j)
+        # packed form on a second pair of contexts: one [o | m | l] block per item, the
+        # layout an all-to-all by destination delivers
+        item = H * D + 2 * H
+        packed = torch.empty(2, n, item, device=dev)
+        for rk, c in enumerate(packed_parts):
+            c.full_attn_partial_packed_dev(layers, seqs, [pos] * n, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                           packed[rk].data_ptr())
+            c.synchronize()
+        out2 = torch.empty(n, H * D, device=dev)
+        packed_parts[0].lse_merge_gate_packed_dev(2, n, packed.data_ptr(), gate.data_ptr(), out2.data_ptr())
+        packed_parts[0].synchronize()
+        out2 = out2.cpu().numpy()
+        for j in range(n):
+            assert I.rel_err(out2[j], refs[j]) <= TOL_F32, ("packed", pos, j)
         if pos < 40:  # early steps: rank 1 owns no row yet -> empty partial (m = -inf, l = 0)
             if pos < 32:
                 assert torch.isinf(m[1]).all() and (l[1] == 0).all()
-    for c in parts + [whole]:
+    for c in parts + packed_parts + [whole]:
         c.close()
 
 
