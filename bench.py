@@ -133,6 +133,7 @@ def cpu_sample(ctx_len, batch, seed=4):
     from oracle import A17B as G
 
     O.build()
+    O.use_all_cores()
     r = np.random.Generator(np.random.Philox(seed))
     nrm = lambda *s: r.standard_normal(s, dtype=np.float32)
     # full attention: one (layer, sequence) item at the full context
@@ -378,7 +379,8 @@ def run_ours(args, rank, world, local_rank):
             max(nl, 1), HV), pin(max(nl, 1), V_DIM)
         for h, d_ in ((hq, q), (hgate, gate), (hk, kk), (hv, vv), (hqkv, qkv), (hz, z), (ha, alpha), (hb, beta)):
             h.copy_(d_.cpu())
-        h2d = 4 * (2 * ng * Q_DIM + 2 * ng * KV_DIM + nl * (CONV_DIM + V_DIM + 2 * HV))
+        n_gate = ng if world == 1 else ng // world  # gate rows are needed only where an item is finished
+        h2d = 4 * ((ng + n_gate) * Q_DIM + 2 * ng * KV_DIM + nl * (CONV_DIM + V_DIM + 2 * HV))
         n_out = ng if world == 1 else ng // world
         hout_own = hout[:n_out]
         d2h = 4 * (n_out * Q_DIM + nl * V_DIM)
@@ -394,7 +396,7 @@ def run_ours(args, rank, world, local_rank):
             else:
                 with torch.cuda.stream(stream):
                     q.copy_(hq, non_blocking=True)
-                    gate.copy_(hgate, non_blocking=True)
+                    gate[rank * npr:(rank + 1) * npr].copy_(hgate[rank * npr:(rank + 1) * npr], non_blocking=True)
                     kk.copy_(hk, non_blocking=True)
                     vv.copy_(hv, non_blocking=True)
                     if nl:

@@ -113,6 +113,17 @@ def num_threads() -> int:
     return int(lib().mfo_num_threads())
 
 
+def use_all_cores() -> int:
+    """Let the OpenMP loops use every core this process may run on (launchers
+    such as torchrun export OMP_NUM_THREADS=1).  Returns the thread count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().mfo_set_num_threads(int(n))
+    return num_threads()
+
+
 def f32_to_bf16_bits(x) -> np.ndarray:
     """Round-to-nearest-even f32 -> bf16 bit patterns (vectorised twin of
     ``mfo_f32_to_bf16``; inputs must be finite)."""

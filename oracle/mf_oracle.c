@@ -54,6 +54,16 @@ MFO_API void mfo_round_bf16(const float *x, float *out, size_t n) {
     for (size_t i = 0; i < n; i++) out[i] = bf16_to_f32(mfo_f32_to_bf16(x[i]));
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed CPU baseline asks
+ * for all the host's cores explicitly. */
+MFO_API void mfo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 MFO_API int mfo_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
