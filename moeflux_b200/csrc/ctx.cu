@@ -89,6 +89,7 @@ struct mfc_ctx {
     float *sc_o = nullptr, *sc_m = nullptr, *sc_l = nullptr;
     unsigned *tickets = nullptr, *status = nullptr;
     int max_parts = 0;
+    int plan_tiles_per_cta = 1, plan_total_tiles = 0;  // split of the launch being built
 
     // device staging for the host-pointer entry points (max_batch items)
     float *st_q = nullptr, *st_gate = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
@@ -210,52 +211,28 @@ int check_status(mfc_ctx *c) {
 
 // ---- item list construction ---------------------------------------------------------
 
-// Chunk length for one launch.  Measured on B200 (240 equal units, bf16): a CTA
-// costs about 12 us of start-up and epilogue besides its streaming, so launches
-// want few, fat CTAs (>= ~4 MB of KV each) but about six waves of them when the
-// work allows (tail balance), and plans whose last round is nearly empty (4.05
-// waves) lose 3-7 %.  Policy: base CTA count = total bytes / 4 MB clamped to
-// [2, 6] waves of `gqa_slots` (2 CTAs per SM); within +-25 % of it take the
-// plan whose last round is at least 90 % full and that is closest to the base
-// count, else the fullest.  At most MAX_SPLITS chunks per (item, kv head), at
-// least 256 rows per chunk.
-int plan_chunk(const mfc_ctx *c, long long total_rows, int max_len, const GqaItem *items = nullptr, int n_items = 0) {
-    const int min_ch = ((max_len + MAX_SPLITS - 1) / MAX_SPLITS + KV_TILE - 1) / KV_TILE * KV_TILE;
+// Work split of one launch ("stream-K" over KV tiles).  The tiles of all (item, kv
+// head) units form one sequence; it is cut into equal runs of `tiles_per_cta` tiles,
+// one CTA each, across unit boundaries, so that one wave of CTAs (2 per SM) carries
+// the whole launch with equal work per CTA.  A unit cut by a run boundary is merged
+// from the partials of the CTAs that share it.  Constraints: at least 256 rows per
+// CTA (a CTA's start-up and epilogue cost about as much as streaming that), at most
+// MAX_SPLITS partials per unit.
+int plan_tiles_per_cta(const mfc_ctx *c, long long total_tiles, int max_unit_tiles) {
+    const int tile = c->cfg.kv_dtype == MFC_KV_BF16 ? KV_TILE : KV_TILE_F32;
+    long long w;
     if (c->gqa_forced_chunk > 0) {
-        int ch = (c->gqa_forced_chunk + KV_TILE - 1) / KV_TILE * KV_TILE;
-        return ch > min_ch ? ch : min_ch;
+        w = (c->gqa_forced_chunk + tile - 1) / tile;
+    } else {
+        const long long ctas = c->gqa_target_ctas > 0 ? c->gqa_target_ctas : c->gqa_slots;
+        w = (total_tiles + ctas - 1) / ctas;
+        const long long w_min = 256 / tile;
+        if (w < w_min) w = w_min;
     }
-    auto clamp = [&](long long ch) {
-        if (ch < 256) ch = 256;
-        if (ch < min_ch) ch = min_ch;
-        return (int)((ch + KV_TILE - 1) / KV_TILE * KV_TILE);
-    };
-    if (c->gqa_target_ctas > 0) return clamp((total_rows + c->gqa_target_ctas - 1) / c->gqa_target_ctas);
-    const long long slots = c->gqa_slots;
-    const int Hkv = c->cfg.num_kv_heads;
-    const long long bytes = total_rows * 2 * HEAD_DIM * (long long)c->kv_esize;
-    long long base = bytes / (4ll << 20);
-    if (base < 2 * slots) base = 2 * slots;
-    if (base > 6 * slots) base = 6 * slots;
-    int best_ch = clamp((total_rows + base - 1) / base);
-    double best_score = -1e30;
-    for (int pct = 80; pct <= 125; pct += 3) {
-        const long long target = base * pct / 100;
-        const int ch = clamp((total_rows + target - 1) / target);
-        long long total = 0;
-        if (items)
-            for (int i = 0; i < n_items; i++) total += (long long)Hkv * (items[i].local_len > 0 ? (items[i].local_len + ch - 1) / ch : 1);
-        else
-            total = (total_rows + ch - 1) / ch;
-        const double eff = (double)total / (double)(((total + slots - 1) / slots) * slots);
-        const double dist = (double)(total > base ? total - base : base - total) / (double)base;
-        const double score = (eff >= 0.9 ? 1.0 : eff) - 0.1 * dist;
-        if (score > best_score) {
-            best_score = score;
-            best_ch = ch;
-        }
-    }
-    return best_ch;
+    const long long w_split = (max_unit_tiles + (MAX_SPLITS - 2) - 1) / (MAX_SPLITS - 2);
+    if (w < w_split) w = w_split;
+    if (w < 1) w = 1;
+    return (int)w;
 }
 
 // Validates the items, advances the lengths and fills c->h_gqa_items.
@@ -293,8 +270,6 @@ int build_gqa_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq
         }
     }
     c->h_gqa_items.resize(n);
-    long long total_rows = 0;
-    int max_len = 0;
     for (int i = 0; i < n; i++) {
         GqaItem &it = c->h_gqa_items[i];
         const int slot = c->layer_to_full[layers[i]] * g.n_seqs + seq_ids[i];
@@ -303,19 +278,26 @@ int build_gqa_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq
         it.local_len = local_len_of(pos[i] + 1, g.kv_rank, g.kv_world, g.kv_block);
         it.append_row = local_row_of(pos[i], g.kv_rank, g.kv_world, g.kv_block);
         it.in_idx = i;
-        total_rows += (long long)it.local_len * g.num_kv_heads;
-        if (it.local_len > max_len) max_len = it.local_len;
     }
-    const int chunk = plan_chunk(c, total_rows, max_len, c->h_gqa_items.data(), n);
-    int cta = 0;
+    const int tile = g.kv_dtype == MFC_KV_BF16 ? KV_TILE : KV_TILE_F32;
+    long long total_tiles = 0;
+    int max_unit_tiles = 1;
     for (int i = 0; i < n; i++) {
         GqaItem &it = c->h_gqa_items[i];
-        it.chunk_len = chunk;
-        it.n_chunks = it.local_len > 0 ? (it.local_len + chunk - 1) / chunk : 1;
-        it.cta_begin = cta;
-        cta += it.n_chunks * g.num_kv_heads;
+        const int nt = it.local_len > 0 ? (it.local_len + tile - 1) / tile : 1;
+        it.tile_begin = (int32_t)total_tiles;
+        it.pad0 = it.pad1 = 0;
+        total_tiles += (long long)nt * g.num_kv_heads;
+        if (nt > max_unit_tiles) max_unit_tiles = nt;
     }
-    if (cta > c->max_parts) {
+    if (total_tiles >= (1ll << 31)) {
+        fail(c, "too many KV tiles in one launch");
+        return -1;
+    }
+    c->plan_tiles_per_cta = plan_tiles_per_cta(c, total_tiles, max_unit_tiles);
+    c->plan_total_tiles = (int)total_tiles;
+    const int cta = (int)((total_tiles + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta);
+    if (cta + n * g.num_kv_heads > c->max_parts) {
         fail(c, "internal: split plan exceeds the scratch reserved at open");
         return -1;
     }
@@ -332,6 +314,8 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
     p.items = c->d_gqa_items;
     p.n_items = n;
     p.total_ctas = total_ctas;
+    p.tiles_per_cta = c->plan_tiles_per_cta;
+    p.total_tiles = c->plan_total_tiles;
     p.sc_o = c->sc_o;
     p.sc_m = c->sc_m;
     p.sc_l = c->sc_l;
@@ -653,7 +637,7 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     if (c->gqa_target_ctas < 0) c->gqa_target_ctas = 0;
     if (c->gqa_target_ctas > 8192) c->gqa_target_ctas = 8192;
     c->gqa_slots = 2 * prop.multiProcessorCount;
-    c->max_parts = 8192 + g.max_batch * g.num_kv_heads;
+    c->max_parts = 8192 + g.max_batch * g.num_kv_heads;  // one slot per (unit, CTA) pair: units + CTAs at most
 
     bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking) == cudaSuccess &&
@@ -1711,11 +1695,16 @@ int mfc_sdpa(mfc_ctx *c, int32_t kv_len, const float *q, const float *q_gate, co
     it.pos = 0;
     it.append_row = -1;
     it.in_idx = 0;
-    it.chunk_len = plan_chunk(c, (long long)kv_len * g.num_kv_heads, kv_len);
-    it.n_chunks = (kv_len + it.chunk_len - 1) / it.chunk_len;
-    it.cta_begin = 0;
+    it.tile_begin = 0;
+    it.pad0 = it.pad1 = 0;
+    {
+        const int tile = g.kv_dtype == MFC_KV_BF16 ? KV_TILE : KV_TILE_F32;
+        const int nt = (kv_len + tile - 1) / tile;
+        c->plan_total_tiles = nt * g.num_kv_heads;
+        c->plan_tiles_per_cta = plan_tiles_per_cta(c, c->plan_total_tiles, nt);
+    }
     GqaParams p;
-    fill_gqa_params(c, p, 1, it.n_chunks * g.num_kv_heads);
+    fill_gqa_params(c, p, 1, (c->plan_total_tiles + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta);
     p.q = c->st_q;
     p.gate = c->st_gate;
     p.k = c->st_k;

@@ -58,40 +58,53 @@ __device__ __forceinline__ void head_inv_rms(const float *qbase, int rows, int r
     __syncthreads();
 }
 
+// A segment of work: the part of one (item, kv head) unit that falls into this
+// CTA's range of the launch-wide tile sequence.
 struct Located {
     GqaItem it;
     int item_idx;
     int kvh;
-    int chunk;
+    int t0;        // first tile of the segment, within the unit
+    int seg;       // tiles in the segment
+    int n_parts;   // CTAs that share the unit (1: this CTA finishes it alone)
+    int part_idx;  // this CTA's rank among them
+    int slot0;     // scratch slot of the unit's first partial
 };
 
-// CTA -> (item, kv head, chunk).  The items' first-CTA indices are staged in
-// shared memory once per CTA so that the search costs one round of global loads
-// instead of a chain of dependent ones.  Contains a __syncthreads.
 constexpr int LOCATE_SMEM_ITEMS = 512;
-__device__ __forceinline__ Located locate(const GqaParams &p, int bid, int *s_begin) {
+// Stages the items' first-tile indices in shared memory (one round of global
+// loads instead of a dependent chain per lookup).  Contains a __syncthreads.
+__device__ __forceinline__ void stage_tile_begins(const GqaParams &p, int *s_begin) {
+    if (p.n_items <= LOCATE_SMEM_ITEMS)
+        for (int i = threadIdx.x; i < p.n_items; i += blockDim.x) s_begin[i] = p.items[i].tile_begin;
+    __syncthreads();
+}
+// Segment that starts at tile `gt` of the launch-wide sequence and ends at the
+// unit's end or at `gt_end`, whichever comes first.
+template <int TILE_ROWS>
+__device__ __forceinline__ Located locate_tile(const GqaParams &p, int gt, int gt_end, const int *s_begin) {
     int lo = 0, hi = p.n_items - 1;
-    if (p.n_items <= LOCATE_SMEM_ITEMS) {
-        for (int i = threadIdx.x; i < p.n_items; i += blockDim.x) s_begin[i] = p.items[i].cta_begin;
-        __syncthreads();
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (s_begin[mid] <= bid) lo = mid;
-            else hi = mid - 1;
-        }
-    } else {
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (p.items[mid].cta_begin <= bid) lo = mid;
-            else hi = mid - 1;
-        }
+    const bool in_smem = p.n_items <= LOCATE_SMEM_ITEMS;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        const int tb = in_smem ? s_begin[mid] : p.items[mid].tile_begin;
+        if (tb <= gt) lo = mid;
+        else hi = mid - 1;
     }
     Located L;
     L.it = p.items[lo];
     L.item_idx = lo;
-    const int local = bid - L.it.cta_begin;
-    L.kvh = local / L.it.n_chunks;
-    L.chunk = local % L.it.n_chunks;
+    const int nt = L.it.local_len > 0 ? (L.it.local_len + TILE_ROWS - 1) / TILE_ROWS : 1;
+    const int local = gt - L.it.tile_begin;
+    L.kvh = local / nt;
+    L.t0 = local - L.kvh * nt;
+    L.seg = min(nt - L.t0, gt_end - gt);
+    const int tb_u = L.it.tile_begin + L.kvh * nt;
+    const int first_cta = tb_u / p.tiles_per_cta, last_cta = (tb_u + nt - 1) / p.tiles_per_cta;
+    L.n_parts = last_cta - first_cta + 1;
+    L.part_idx = (int)blockIdx.x - first_cta;
+    // (unit index + CTA index) grows strictly along the tile sequence: a unique slot per pair
+    L.slot0 = lo * p.Hkv + L.kvh + first_cta;
     return L;
 }
 
@@ -168,8 +181,8 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
     }
 
     const size_t head0 = (size_t)it.in_idx * p.H + (size_t)L.kvh * group;
-    if (it.n_chunks == 1) {
-        // single chunk: finish in place
+    if (L.n_parts == 1) {
+        // the unit was not split: finish in place
 #pragma unroll
         for (int x = 0; x < 2; x++) {
             const int row = g + 8 * x;
@@ -203,9 +216,9 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
         return;
     }
 
-    // several chunks: park the partial, the last CTA of the unit merges
-    const size_t slot0 = (size_t)it.cta_begin + (size_t)L.kvh * it.n_chunks;  // first slot of the unit
-    const size_t slot = slot0 + L.chunk;
+    // the unit is shared: park the partial, the last CTA of the unit to finish merges
+    const size_t slot0 = (size_t)L.slot0;  // first slot of the unit
+    const size_t slot = slot0 + L.part_idx;
 #pragma unroll
     for (int x = 0; x < 2; x++) {
         const int row = g + 8 * x;
@@ -224,14 +237,14 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
     if (tid == 0) {
         unsigned *tk = p.tickets + (size_t)L.item_idx * p.Hkv + L.kvh;
         const unsigned prev = atomicAdd(tk, 1u);
-        *s_flag_p = (prev == (unsigned)(it.n_chunks - 1));
+        *s_flag_p = (prev == (unsigned)(L.n_parts - 1));
         if (*s_flag_p) *tk = 0u;  // ready for the next launch
     }
     __syncthreads();
     if (!*s_flag_p) return;
     __threadfence();
     merge_unit(p, L, p.sc_o + slot0 * 16 * HEAD_DIM, p.sc_m + slot0 * 16, p.sc_l + slot0 * 16,
-               it.n_chunks, s_w, s_M, s_L);
+               L.n_parts, s_w, s_M, s_L);
 }
 
 }  // namespace mfc

@@ -56,18 +56,32 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const Located L = locate(p, blockIdx.x, s_begin);
+    if (tid == 0) {
+        prefetch_tmap(&kmap);
+        prefetch_tmap(&vmap);
+#pragma unroll
+        for (int s = 0; s < F32_STAGES; s++) mbar_init(&full[s], 1);
+        mbar_fence_init();
+    }
+    stage_tile_begins(p, s_begin);  // also publishes the barrier initialisation
+
+    // This CTA's share of the launch-wide tile sequence, one unit segment at a time.
+    int gt = (int)blockIdx.x * p.tiles_per_cta;
+    const int gt_end = min(gt + p.tiles_per_cta, p.total_tiles);
+    unsigned pc = 0;  // tiles pushed through the stage ring so far: stage and phase follow from it
+    while (gt < gt_end) {
+    const Located L = locate_tile<F32_TILE>(p, gt, gt_end, s_begin);
     const GqaItem &it = L.it;
     const int group = p.group;
 
-    const int c0 = L.chunk * it.chunk_len;
-    const int c1 = min(c0 + it.chunk_len, it.local_len);
+    const int c0 = L.t0 * F32_TILE;
+    const int c1 = min(c0 + L.seg * F32_TILE, it.local_len);
     const int ntiles = (c1 > c0) ? (c1 - c0 + F32_TILE - 1) / F32_TILE : 0;
     const int row_base = (it.kv_slot * p.Hkv + L.kvh) * p.cap_rows;
-    const bool appender = it.append_row >= c0 && it.append_row < c0 + it.chunk_len;
+    const bool appender = it.append_row >= c0 && it.append_row < c0 + L.seg * F32_TILE;
 
     auto issue_tile = [&](int tile) {
-        const int st = tile % F32_STAGES;
+        const int st = (int)((pc + (unsigned)tile) % F32_STAGES);
         uint8_t *kdst = stages + (size_t)st * 2 * TILE_BYTES_F32;
         uint8_t *vdst = kdst + TILE_BYTES_F32;
         mbar_expect_tx(&full[st], 2 * TILE_BYTES_F32);
@@ -79,16 +93,9 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         }
     };
 
-    if (tid == 0) {
-        prefetch_tmap(&kmap);
-        prefetch_tmap(&vmap);
-#pragma unroll
-        for (int s = 0; s < F32_STAGES; s++) mbar_init(&full[s], 1);
-        mbar_fence_init();
-        if (!appender) {
-            const int n0 = min(ntiles, F32_STAGES);
-            for (int i = 0; i < n0; i++) issue_tile(i);
-        }
+    if (tid == 0 && !appender) {
+        const int n0 = min(ntiles, F32_STAGES);
+        for (int i = 0; i < n0; i++) issue_tile(i);
     }
     const int half = p.rotary_dim >> 1;
     if (tid < half) {
@@ -160,8 +167,8 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     bool failed = false;
 
     for (int i = 0; i < ntiles; i++) {
-        const int st = i % F32_STAGES;
-        const unsigned par = (unsigned)(i / F32_STAGES) & 1u;
+        const int st = (int)((pc + (unsigned)i) % F32_STAGES);
+        const unsigned par = ((pc + (unsigned)i) / F32_STAGES) & 1u;
         const bool ok = mbar_wait_bounded(&full[st], par);
         const uint8_t *kgen = stages + (size_t)st * 2 * TILE_BYTES_F32;
         const uint32_t kst = smem_u32(kgen);
@@ -296,6 +303,11 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         return;
     }
     finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag);
+    pc += (unsigned)ntiles;
+    gt += L.seg;
+    fence_proxy_async();  // the next segment's TMA loads overwrite memory this segment touched
+    __syncthreads();  // shared scratch (RoPE table, score exchange, merge weights) is reused by the next segment
+    }
 }
 
 constexpr size_t F32_SMEM = 1024 + (size_t)F32_STAGES * 2 * TILE_BYTES_F32 +

@@ -53,9 +53,9 @@ struct GqaItem {
     int32_t local_len;   // rows held locally, the row appended by this step included
     int32_t pos;         // absolute position of the token (RoPE angle)
     int32_t append_row;  // local row that receives k,v, or -1 when another context owns it
-    int32_t chunk_len;   // rows per chunk, multiple of KV_TILE
-    int32_t n_chunks;    // >= 1
-    int32_t cta_begin;   // first CTA of this item; it owns Hkv * n_chunks CTAs
+    int32_t tile_begin;  // index, in the launch-wide tile sequence, of the first tile of kv head 0;
+                         //   every kv head of the item has max(1, ceil(local_len / tile rows)) tiles
+    int32_t pad0, pad1;
     int32_t in_idx;      // index of the item's q/gate/k/v/out rows
 };
 
@@ -65,6 +65,10 @@ struct GqaParams {
     const GqaItem *items;    // device
     int n_items;
     int total_ctas;
+    // The tiles of all (item, kv head) units form one sequence; CTA c works on tiles
+    // [c * tiles_per_cta, (c+1) * tiles_per_cta) of it, across unit boundaries.
+    int tiles_per_cta;
+    int total_tiles;
     const float *q;          // [n][H][256]
     const float *gate;       // [n][H][256] or nullptr
     const float *k;          // [n][Hkv][256]

@@ -134,21 +134,25 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
     const uint64_t rows = (uint64_t)num_kv_heads * cap_rows;
     if (encode_map(&kmap, k_cache, rows, bf16) || encode_map(&vmap, v_cache, rows, bf16)) return -1;
 
-    // chunking: at most STATIC_SLOTS partials in total, at most MAX_SPLITS per head
-    const int per_head = STATIC_SLOTS / num_kv_heads < MAX_SPLITS ? STATIC_SLOTS / num_kv_heads : MAX_SPLITS;
-    int chunk = (kv_len + per_head - 1) / per_head;
-    if (chunk < 256) chunk = 256;
-    chunk = (chunk + KV_TILE - 1) / KV_TILE * KV_TILE;
+    // split: runs of equal tile counts over the heads' tiles, at most STATIC_SLOTS - num_kv_heads CTAs
+    // (a slot per (head, CTA) pair) and at most MAX_SPLITS partials per head
+    const int tile = bf16 ? KV_TILE : KV_TILE_F32;
+    const int nt = (kv_len + tile - 1) / tile;
+    const int total_tiles = nt * num_kv_heads;
+    int w = (total_tiles + (STATIC_SLOTS - num_kv_heads) - 1) / (STATIC_SLOTS - num_kv_heads);
+    if (w < 256 / tile) w = 256 / tile;
+    const int w_split = (nt + (MAX_SPLITS - 2) - 1) / (MAX_SPLITS - 2);
+    if (w < w_split) w = w_split;
+    const int n_ctas = (total_tiles + w - 1) / w;
     GqaItem it;
     it.kv_slot = 0;
     it.local_len = kv_len;
     it.pos = 0;
     it.append_row = -1;
-    it.chunk_len = chunk;
-    it.n_chunks = (kv_len + chunk - 1) / chunk;
-    it.cta_begin = 0;
+    it.tile_begin = 0;
+    it.pad0 = it.pad1 = 0;
     it.in_idx = 0;
-    if (it.n_chunks * num_kv_heads > STATIC_SLOTS) return fail("internal: split plan exceeds the fixed scratch");
+    if (n_ctas + num_kv_heads > STATIC_SLOTS) return fail("internal: split plan exceeds the fixed scratch");
 
     // The array keeps whatever the previous call left: the chunk counters and the
     // status word must start at zero.  (The partial slots are fully written before
@@ -164,7 +168,9 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
     p.v_base = const_cast<void *>(v_cache);
     p.items = reinterpret_cast<const GqaItem *>(scratch + OFF_ITEM);
     p.n_items = 1;
-    p.total_ctas = it.n_chunks * num_kv_heads;
+    p.total_ctas = n_ctas;
+    p.tiles_per_cta = w;
+    p.total_tiles = total_tiles;
     p.q = q;
     p.gate = gate;
     p.k = nullptr;
