@@ -13,7 +13,9 @@
 //   1. prefill_kv_append_kernel: per token, the RoPE table entry (accurate
 //      sincosf of pos * inv_freq, shared by all heads), rotated K and V rows
 //      stored into the cache.
-//   2. gqa_prefill_kernel: CTA = 128 query tokens of one query head (M = 128).
+//   2. gqa_prefill_kernel: CTA = 128 query tokens of one query head (M = 128);
+//      four softmax warps (thread = query row) and one warp that issues every TMA
+//      load and every tcgen05.mma.
 //      Per 64-row KV tile: S = Q K^T (16 tcgen05.mma of K=16, N=64, fp32 in
 //      TMEM), softmax with one thread per query row (tcgen05.ld, no shuffles),
 //      P written to shared memory as bf16, O += P V (4 tcgen05.mma, N=256,
@@ -84,20 +86,12 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, ui
         : "memory");
 }
 // 32 lanes x 32 consecutive columns: thread i of warp w reads TMEM lane 32*(w%4)+i
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-#pragma unroll
-    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+// The destination registers are bound straight to v[]: nothing may read them before tc_wait_ld().
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]), "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
     asm volatile(
@@ -147,18 +141,28 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(128, 1)
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 160 threads: warps 0-3 own the 128 query rows (softmax, rescale, epilogue);
+// warp 4 issues every TMA load and every tcgen05.mma, so that building
+// descriptors and issuing the 20 MMAs of a tile never sits on the softmax path.
+__global__ void __launch_bounds__(160, 1)
 gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const PrefillAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + OFF_BAR);
-    uint64_t *full_q = bars + 0;
-    uint64_t *full_k = bars + 1;   // [2]
-    uint64_t *full_v = bars + 3;   // [2]
-    uint64_t *s_ready = bars + 5;  // [2]
-    uint64_t *pv_done = bars + 7;  // [2]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
+    uint64_t *full_q = bars + 0;    // TMA: Q tile landed
+    uint64_t *full_k = bars + 1;    // [2] TMA: K stage landed
+    uint64_t *full_v = bars + 3;    // [2] TMA: V stage landed
+    uint64_t *s_ready = bars + 5;   // [2] tcgen05.commit: scores of a tile are in TMEM
+    uint64_t *pv_done = bars + 7;   // [2] tcgen05.commit: P V of a tile has been accumulated
+    uint64_t *p_ready = bars + 9;   // [2] 128 arrivals: P of a tile is in shared memory, S has been read
+    uint64_t *q_ready = bars + 11;  // 128 arrivals: Q has been rotated in shared memory
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
+    volatile int *s_fail = reinterpret_cast<volatile int *>(bars + 13);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int n_qt = (p.T + PF_M - 1) / PF_M;
@@ -166,8 +170,6 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     const int h = blockIdx.y;
     const int kvh = h / p.group;
     const int t0 = qt * PF_M;
-    const int row_tok = t0 + tid;                     // this thread's query token
-    const int qpos = p.start_pos + row_tok;           // its absolute position
     const int kv_need = p.start_pos + min(p.T, t0 + PF_M);  // rows this tile may attend to
     const int ntiles = (kv_need + PF_N - 1) / PF_N;
     const int kv_row0 = (p.kv_slot * p.Hkv + kvh) * p.cap_rows;
@@ -177,6 +179,10 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         prefetch_tmap(&kmap);
         prefetch_tmap(&vmap);
         for (int i = 0; i < 9; i++) mbar_init(&bars[i], 1);
+        mbar_init(&p_ready[0], 128);
+        mbar_init(&p_ready[1], 128);
+        mbar_init(q_ready, 128);
+        *s_fail = 0;
         mbar_fence_init();
     }
     if (warp == 0) {
@@ -187,241 +193,239 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    bool ok = true;
 
-    auto load_k = [&](int tile) {
-        const int st = tile & 1;
-        mbar_expect_tx(&full_k[st], KV_TILE_BYTES);
+    if (warp == 4) {
+        // ================= issuer warp: one lane drives TMA and the tensor core =================
+        if ((tid & 31) == 0) {
+            auto load_k = [&](int tile) {
+                const int st = tile & 1;
+                mbar_expect_tx(&full_k[st], KV_TILE_BYTES);
 #pragma unroll
-        for (int b = 0; b < 4; b++)
-            tma_load_2d(smem + OFF_K + st * KV_TILE_BYTES + b * KV_BOX, &kmap, b * 64, kv_row0 + tile * PF_N,
-                        &full_k[st]);
-    };
-    auto load_v = [&](int tile) {
-        const int st = tile & 1;
-        mbar_expect_tx(&full_v[st], KV_TILE_BYTES);
+                for (int b = 0; b < 4; b++)
+                    tma_load_2d(smem + OFF_K + st * KV_TILE_BYTES + b * KV_BOX, &kmap, b * 64, kv_row0 + tile * PF_N,
+                                &full_k[st]);
+            };
+            auto load_v = [&](int tile) {
+                const int st = tile & 1;
+                mbar_expect_tx(&full_v[st], KV_TILE_BYTES);
 #pragma unroll
-        for (int b = 0; b < 4; b++)
-            tma_load_2d(smem + OFF_V + st * KV_TILE_BYTES + b * KV_BOX, &vmap, b * 64, kv_row0 + tile * PF_N,
-                        &full_v[st]);
-    };
-    constexpr uint32_t IDESC_QK = idesc_bf16(PF_N, 0);
-    constexpr uint32_t IDESC_PV = idesc_bf16(HEAD_DIM, 1);
-    const uint32_t q_s = smem_u32(smem + OFF_Q);
-    auto issue_qk = [&](int tile) {  // S[tile&1] = Q K^T
-        const uint32_t k_s = smem_u32(smem + OFF_K + (tile & 1) * KV_TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-            const uint64_t a = smem_desc_sw128(q_s + (ks >> 2) * Q_BOX + (ks & 3) * 32, 16, 1024);
-            const uint64_t b = smem_desc_sw128(k_s + (ks >> 2) * KV_BOX + (ks & 3) * 32, 16, 1024);
-            tc_mma_bf16(tmem + TM_S + (tile & 1) * PF_N, a, b, IDESC_QK, ks > 0);
-        }
-        tc_commit(&s_ready[tile & 1]);
-    };
-    auto issue_pv = [&](int tile) {  // O += P V
-        const uint32_t p_s = smem_u32(smem + OFF_P + (tile & 1) * P_BYTES);
-        const uint32_t v_s = smem_u32(smem + OFF_V + (tile & 1) * KV_TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < PF_N / 16; ks++) {
-            const uint64_t a = smem_desc_sw128(p_s + ks * 32, 16, 1024);
+                for (int b = 0; b < 4; b++)
+                    tma_load_2d(smem + OFF_V + st * KV_TILE_BYTES + b * KV_BOX, &vmap, b * 64, kv_row0 + tile * PF_N,
+                                &full_v[st]);
+            };
+            constexpr uint32_t IDESC_QK = idesc_bf16(PF_N, 0);
+            constexpr uint32_t IDESC_PV = idesc_bf16(HEAD_DIM, 1);
+            // descriptors differ only in their start-address field: build the bases once
+            const uint64_t q_desc = smem_desc_sw128(smem_u32(smem + OFF_Q), 16, 1024);
+            const uint64_t k_desc0 = smem_desc_sw128(smem_u32(smem + OFF_K), 16, 1024);
+            const uint64_t p_desc0 = smem_desc_sw128(smem_u32(smem + OFF_P), 16, 1024);
             // V: MN-major; 64-dim atoms KV_BOX apart (LBO), 8-row groups 1024 B apart (SBO)
-            const uint64_t b = smem_desc_sw128(v_s + ks * 2048, KV_BOX, 1024);
-            tc_mma_bf16(tmem + TM_O, a, b, IDESC_PV, (tile > 0) || (ks > 0));
-        }
-        tc_commit(&pv_done[tile & 1]);
-    };
-
-    if (tid == 0) {
-        mbar_expect_tx(full_q, Q_BYTES);
+            const uint64_t v_desc0 = smem_desc_sw128(smem_u32(smem + OFF_V), KV_BOX, 1024);
+            auto issue_qk = [&](int tile) {  // S[tile&1] = Q K^T
+                const uint64_t kd = k_desc0 + (uint64_t)(((tile & 1) * KV_TILE_BYTES) >> 4);
 #pragma unroll
-        for (int b = 0; b < 4; b++) tma_load_3d(smem + OFF_Q + b * Q_BOX, &qmap, b * 64, h, t0, full_q);
-        load_k(0);
-        load_v(0);
-        if (ntiles > 1) {
-            load_k(1);
-            load_v(1);
-        }
-    }
-
-    // ---- RoPE on this thread's Q row, in shared memory (dims 0..63 live in box 0) ----
-    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(full_q, 0));
-    if (ok && p.rotary_dim > 0 && row_tok < p.T) {
-        const int half = p.rotary_dim >> 1;  // <= 32 here (rotary_dim <= 64)
-        uint8_t *rowp = smem + OFF_Q + tid * 128;
-        const float2 *cs = reinterpret_cast<const float2 *>(p.cos_sin) + (size_t)row_tok * 32;
-        for (int i0 = 0; i0 < half; i0 += 8) {
-            const int c_lo = i0 >> 3, c_hi = (i0 + half) >> 3;
-            uint4 *plo = reinterpret_cast<uint4 *>(rowp + ((c_lo ^ (tid & 7)) << 4));
-            uint4 *phi = reinterpret_cast<uint4 *>(rowp + ((c_hi ^ (tid & 7)) << 4));
-            uint4 lo = *plo, hi = *phi;
-            __nv_bfloat16 *a = reinterpret_cast<__nv_bfloat16 *>(&lo);
-            __nv_bfloat16 *b = reinterpret_cast<__nv_bfloat16 *>(&hi);
+                for (int ks = 0; ks < 16; ks++)
+                    tc_mma_bf16(tmem + TM_S + (tile & 1) * PF_N, q_desc + (uint64_t)(((ks >> 2) * Q_BOX + (ks & 3) * 32) >> 4),
+                                kd + (uint64_t)(((ks >> 2) * KV_BOX + (ks & 3) * 32) >> 4), IDESC_QK, ks > 0);
+                tc_commit(&s_ready[tile & 1]);
+            };
+            auto issue_pv = [&](int tile) {  // O += P V
+                const uint64_t pd = p_desc0 + (uint64_t)(((tile & 1) * P_BYTES) >> 4);
+                const uint64_t vd = v_desc0 + (uint64_t)(((tile & 1) * KV_TILE_BYTES) >> 4);
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const float2 c = cs[i0 + e];  // (cos, sin)
-                const float x0 = __bfloat162float(a[e]), x1 = __bfloat162float(b[e]);
-                a[e] = __float2bfloat16_rn(x0 * c.x - x1 * c.y);
-                b[e] = __float2bfloat16_rn(x0 * c.y + x1 * c.x);
+                for (int ks = 0; ks < PF_N / 16; ks++)
+                    tc_mma_bf16(tmem + TM_O, pd + (uint64_t)((ks * 32) >> 4), vd + (uint64_t)((ks * 2048) >> 4), IDESC_PV,
+                                (tile > 0) || (ks > 0));
+                tc_commit(&pv_done[tile & 1]);
+            };
+
+            mbar_expect_tx(full_q, Q_BYTES);
+#pragma unroll
+            for (int b = 0; b < 4; b++) tma_load_3d(smem + OFF_Q + b * Q_BOX, &qmap, b * 64, h, t0, full_q);
+            load_k(0);
+            load_v(0);
+            if (ntiles > 1) {
+                load_k(1);
+                load_v(1);
             }
-            *plo = lo;
-            *phi = hi;
+            ok = mbar_wait_bounded(q_ready, 0) && mbar_wait_bounded(&full_k[0], 0);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; j < ntiles && ok; j++) {
+                const int b = j & 1;
+                const unsigned par = (unsigned)(j >> 1) & 1u;
+                if (j + 1 < ntiles) {
+                    // S[(j+1)&1] was read by the softmax of tile j-1, which this thread saw finish (p_ready) last turn
+                    ok = mbar_wait_bounded(&full_k[(j + 1) & 1], (unsigned)((j + 1) >> 1) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                // P of tile j is in shared memory (so Q K^T of tile j is long complete: its K stage is free)
+                ok = mbar_wait_bounded(&p_ready[b], par);
+                if (!ok) break;
+                if (j + 2 < ntiles) load_k(j + 2);
+                ok = mbar_wait_bounded(&full_v[b], par);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(j);
+                if (j >= 1 && j + 1 < ntiles) {
+                    // V stage (j+1)&1 held tile j-1: free once its P V has completed
+                    ok = mbar_wait_bounded(&pv_done[(j - 1) & 1], (unsigned)((j - 1) >> 1) & 1u);
+                    if (!ok) break;
+                    load_v(j + 1);
+                }
+            }
+            if (!ok) *s_fail = 1;
         }
-    }
-    fence_proxy_async_smem();
-    if (__syncthreads_or(ok ? 0 : 1)) ok = false;
+    } else {
+        // ================= softmax warps: thread = query row =================
+        const int row_tok = t0 + tid;            // this thread's query token
+        const int qpos = p.start_pos + row_tok;  // its absolute position
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
 
-    float m_run = -INFINITY, l_run = 0.0f;
-    const float sl2 = p.scale * LOG2E_PF;
-
-    if (ok && tid == 0) {
-        if (mbar_wait_bounded(&full_k[0], 0)) {
-            tc_fence_after();
-            issue_qk(0);
-        } else {
-            ok = false;
-        }
-    }
-
-    // thread 0's own failures (its extra waits) reach the others through the block-wide OR below
-    for (int j = 0; j < ntiles; j++) {
-        const int b = j & 1;
-        const unsigned par = (unsigned)(j >> 1) & 1u;
-        // tile j's scores are in TMEM once s_ready[b] completes; K stage b is then free
-        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_ready[b], par));
-        if (!ok) break;
-        tc_fence_after();
-        if (tid == 0) {
-            if (j + 2 < ntiles) load_k(j + 2);
-            if (j + 1 < ntiles) {  // start Q K^T of the next tile under this tile's softmax
-                if (mbar_wait_bounded(&full_k[(j + 1) & 1], (unsigned)((j + 1) >> 1) & 1u)) issue_qk(j + 1);
-                else ok = false;
+        // ---- RoPE on this thread's Q row, in shared memory (dims 0..63 live in box 0) ----
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(full_q, 0));
+        if (ok && p.rotary_dim > 0 && row_tok < p.T) {
+            const int half = p.rotary_dim >> 1;  // <= 32 here (rotary_dim <= 64)
+            uint8_t *rowp = smem + OFF_Q + tid * 128;
+            const float2 *cs = reinterpret_cast<const float2 *>(p.cos_sin) + (size_t)row_tok * 32;
+            for (int i0 = 0; i0 < half; i0 += 8) {
+                const int c_lo = i0 >> 3, c_hi = (i0 + half) >> 3;
+                uint4 *plo = reinterpret_cast<uint4 *>(rowp + ((c_lo ^ (tid & 7)) << 4));
+                uint4 *phi = reinterpret_cast<uint4 *>(rowp + ((c_hi ^ (tid & 7)) << 4));
+                uint4 lo = *plo, hi = *phi;
+                __nv_bfloat16 *a = reinterpret_cast<__nv_bfloat16 *>(&lo);
+                __nv_bfloat16 *b = reinterpret_cast<__nv_bfloat16 *>(&hi);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float2 c = cs[i0 + e];  // (cos, sin)
+                    const float x0 = __bfloat162float(a[e]), x1 = __bfloat162float(b[e]);
+                    a[e] = __float2bfloat16_rn(x0 * c.x - x1 * c.y);
+                    b[e] = __float2bfloat16_rn(x0 * c.y + x1 * c.x);
+                }
+                *plo = lo;
+                *phi = hi;
             }
         }
-        float s[PF_N];
-        {
-            float t32[32];
-            tmem_ld32(lane_base + TM_S + b * PF_N, t32);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; i++) s[i] = t32[i];
-            tmem_ld32(lane_base + TM_S + b * PF_N + 32, t32);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; i++) s[32 + i] = t32[i];
-        }
-        const int kv0 = j * PF_N;
-        if (kv0 + PF_N - 1 > p.start_pos + t0) {  // tile touches the diagonal
-#pragma unroll
-            for (int c = 0; c < PF_N; c++)
-                if (kv0 + c > qpos) s[c] = -INFINITY;
-        }
-        float mx = s[0];
-#pragma unroll
-        for (int c = 1; c < PF_N; c++) mx = fmaxf(mx, s[c]);
-        const float m_new = fmaxf(m_run, mx);
-        // rescale O only when some row of the warp moved its maximum by more than 2^8
-        const bool need = (m_new - m_run) * sl2 > 8.0f;  // also true on the first tile (m_run = -inf)
-        const bool warp_rescale = __any_sync(0xffffffffu, need);
-        float corr = 1.0f;
-        if (warp_rescale) {
-            corr = ex2_approx((m_run - m_new) * sl2);
-            m_run = m_new;
-        }
-        const float mb = m_run * sl2;
-        float rs = 0.0f;
-        uint32_t pk[PF_N / 2];
-#pragma unroll
-        for (int c = 0; c < PF_N; c += 2) {
-            const float p0 = ex2_approx(fmaf(s[c], sl2, -mb));
-            const float p1 = ex2_approx(fmaf(s[c + 1], sl2, -mb));
-            rs += p0 + p1;
-            pk[c >> 1] = pack_bf16x2(p0, p1);
-        }
-        l_run = l_run * corr + rs;
+        fence_proxy_async_smem();
+        mbar_arrive(q_ready);
 
-        // O and the P buffer are free once P V of tile j-1 has completed
-        if (j > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[(j - 1) & 1], (unsigned)((j - 1) >> 1) & 1u));
+        float m_run = -INFINITY, l_run = 0.0f;
+        const float sl2 = p.scale * LOG2E_PF;
+        for (int j = 0; j < ntiles && ok; j++) {
+            const int b = j & 1;
+            const unsigned par = (unsigned)(j >> 1) & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_ready[b], par) && *s_fail == 0);
+            if (!ok) break;
+            tc_fence_after();
+            float s[PF_N];
+            tmem_ld32(lane_base + TM_S + b * PF_N, s);
+            tmem_ld32(lane_base + TM_S + b * PF_N + 32, s + 32);
+            tc_wait_ld();
+            const int kv0 = j * PF_N;
+            if (kv0 + PF_N - 1 > p.start_pos + t0) {  // tile touches the diagonal
+#pragma unroll
+                for (int c = 0; c < PF_N; c++)
+                    if (kv0 + c > qpos) s[c] = -INFINITY;
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int c = 1; c < PF_N; c++) mx = fmaxf(mx, s[c]);
+            const float m_new = fmaxf(m_run, mx);
+            // rescale O only when some row of the warp moved its maximum by more than 2^8
+            const bool need = (m_new - m_run) * sl2 > 8.0f;  // also true on the first tile (m_run = -inf)
+            const bool warp_rescale = __any_sync(0xffffffffu, need);
+            float corr = 1.0f;
+            if (warp_rescale) {
+                corr = ex2_approx((m_run - m_new) * sl2);
+                m_run = m_new;
+            }
+            const float mb = m_run * sl2;
+            float rs = 0.0f;
+            uint32_t pk[PF_N / 2];
+#pragma unroll
+            for (int c = 0; c < PF_N; c += 2) {
+                const float p0 = ex2_approx(fmaf(s[c], sl2, -mb));
+                const float p1 = ex2_approx(fmaf(s[c + 1], sl2, -mb));
+                rs += p0 + p1;
+                pk[c >> 1] = pack_bf16x2(p0, p1);
+            }
+            l_run = l_run * corr + rs;
+
+            // P buffer b last fed P V of tile j-2, which the commit behind s_ready[b] already covers.
+            // O may be touched only once P V of tile j-1 has completed.
+            if (warp_rescale && j > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[(j - 1) & 1], (unsigned)((j - 1) >> 1) & 1u));
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(lane_base + TM_O + c0, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] *= corr;
+                    tmem_st32(lane_base + TM_O + c0, o);
+                }
+                tc_wait_st();
+            }
+            {
+                uint8_t *prow = smem + OFF_P + b * P_BYTES + tid * 128;
+#pragma unroll
+                for (int c = 0; c < 8; c++)
+                    *reinterpret_cast<uint4 *>(prow + ((c ^ (tid & 7)) << 4)) =
+                        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(&p_ready[b]);
+        }
+        if (ok && ntiles > 0) {
+            ok = __all_sync(0xffffffffu,
+                            mbar_wait_bounded(&pv_done[(ntiles - 1) & 1], (unsigned)((ntiles - 1) >> 1) & 1u));
             tc_fence_after();
         }
-        if (warp_rescale && j > 0 && ok) {
+        if (ok) {
+            // every lane takes part in the warp-wide TMEM loads; only the global accesses are predicated
+            const bool valid = row_tok < p.T;
+            const float inv = 1.0f / l_run;
+            const size_t off = ((size_t)(valid ? row_tok : 0) * p.H + h) * HEAD_DIM;
 #pragma unroll 1
             for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
                 float o[32];
                 tmem_ld32(lane_base + TM_O + c0, o);
                 tc_wait_ld();
+                if (valid) {
 #pragma unroll
-                for (int i = 0; i < 32; i++) o[i] *= corr;
-                tmem_st32(lane_base + TM_O + c0, o);
-            }
-            tc_wait_st();
-        }
-        {
-            uint8_t *prow = smem + OFF_P + b * P_BYTES + tid * 128;
+                    for (int v8 = 0; v8 < 4; v8++) {
+                        uint4 g4 = make_uint4(0, 0, 0, 0);
+                        if (p.gate) g4 = *reinterpret_cast<const uint4 *>(p.gate + off + c0 + v8 * 8);
+                        const __nv_bfloat16 *gb = reinterpret_cast<const __nv_bfloat16 *>(&g4);
+                        uint32_t w[4];
 #pragma unroll
-            for (int c = 0; c < 8; c++)
-                *reinterpret_cast<uint4 *>(prow + ((c ^ (tid & 7)) << 4)) =
-                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-        }
-        fence_proxy_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(ok ? 0 : 1)) {
-            ok = false;
-            break;
-        }
-        if (tid == 0) {
-            tc_fence_after();
-            if (mbar_wait_bounded(&full_v[b], par)) {
-                issue_pv(j);
-                // V stage (j+1)&1 is free once P V of tile j-1 is done, which this thread saw above
-                if (j >= 1 && j + 1 < ntiles) load_v(j + 1);
-            } else {
-                ok = false;
-            }
-        }
-    }
-    // V of tile 1 was loaded in the prologue; tiles >= 2 are loaded in the loop one tile ahead
-
-    if (__syncthreads_or(ok ? 0 : 1)) ok = false;
-    if (ok && ntiles > 0) {
-        ok = mbar_wait_bounded(&pv_done[(ntiles - 1) & 1], (unsigned)((ntiles - 1) >> 1) & 1u);
-        tc_fence_after();
-    }
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-        // every lane takes part in the warp-wide TMEM loads; only the global accesses are predicated
-        const bool valid = row_tok < p.T;
-        const float inv = 1.0f / l_run;
-        const size_t off = ((size_t)(valid ? row_tok : 0) * p.H + h) * HEAD_DIM;
-#pragma unroll 1
-        for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
-            float o[32];
-            tmem_ld32(lane_base + TM_O + c0, o);
-            tc_wait_ld();
-            if (valid) {
-#pragma unroll
-                for (int v8 = 0; v8 < 4; v8++) {
-                    uint4 g4 = make_uint4(0, 0, 0, 0);
-                    if (p.gate) g4 = *reinterpret_cast<const uint4 *>(p.gate + off + c0 + v8 * 8);
-                    const __nv_bfloat16 *gb = reinterpret_cast<const __nv_bfloat16 *>(&g4);
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        float x0 = o[v8 * 8 + 2 * e] * inv, x1 = o[v8 * 8 + 2 * e + 1] * inv;
-                        if (p.gate) {
-                            x0 *= 1.0f / (1.0f + expf(-__bfloat162float(gb[2 * e])));
-                            x1 *= 1.0f / (1.0f + expf(-__bfloat162float(gb[2 * e + 1])));
+                        for (int e = 0; e < 4; e++) {
+                            float x0 = o[v8 * 8 + 2 * e] * inv, x1 = o[v8 * 8 + 2 * e + 1] * inv;
+                            if (p.gate) {
+                                x0 *= 1.0f / (1.0f + expf(-__bfloat162float(gb[2 * e])));
+                                x1 *= 1.0f / (1.0f + expf(-__bfloat162float(gb[2 * e + 1])));
+                            }
+                            w[e] = pack_bf16x2(x0, x1);
                         }
-                        w[e] = pack_bf16x2(x0, x1);
+                        *reinterpret_cast<uint4 *>(p.out + off + c0 + v8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    *reinterpret_cast<uint4 *>(p.out + off + c0 + v8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
+        } else if ((tid & 31) == 0) {
+            *s_fail = 1;
         }
     }
-    if (!ok && tid == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);
     tc_fence_before();
     __syncthreads();
+    if (tid == 0 && *s_fail) atomicOr(p.status, STATUS_TMA_TIMEOUT);
     if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
@@ -492,7 +496,7 @@ cudaError_t launch_gqa_prefill(const CUtensorMap &qmap, const CUtensorMap &kmap,
                                const PrefillAttnParams &p, cudaStream_t stream) {
     if (p.T <= 0) return cudaSuccess;
     dim3 grid((unsigned)((p.T + PF_M - 1) / PF_M), (unsigned)p.H, 1);
-    gqa_prefill_kernel<<<grid, 128, PF_SMEM, stream>>>(qmap, kmap, vmap, p);
+    gqa_prefill_kernel<<<grid, 160, PF_SMEM, stream>>>(qmap, kmap, vmap, p);
     return cudaGetLastError();
 }
 
