@@ -68,7 +68,7 @@ struct mfc_ctx {
     CUtensorMap kmap_pf, vmap_pf;  // same caches, 64-row boxes for the prefill kernel (bf16 cache only)
     float *pf_cos_sin = nullptr;   // [max_seq][32] (cos, sin) of the tokens of a prefill call
     // GatedDeltaNet prefill scratch, max_prefill tokens
-    void *pf_q = nullptr, *pf_k = nullptr;
+    void *pf_q = nullptr, *pf_k = nullptr, *pf_wt = nullptr, *pf_wm = nullptr;
     float *pf_v = nullptr, *pf_lg = nullptr, *pf_beta = nullptr;
     float *ssm = nullptr, *conv = nullptr;
     uint16_t *conv_w = nullptr, *dt_bias = nullptr, *norm_w = nullptr;
@@ -184,7 +184,7 @@ void free_all(mfc_ctx *c) {
                     c->inv_freq, c->d_gqa_items, c->d_gdn_items, c->sc_o, c->sc_m, c->sc_l, c->tickets,
                     c->status, c->st_q, c->st_gate, c->st_k, c->st_v, c->st_out, c->st_qkv, c->st_z,
                     c->st_alpha, c->st_beta, c->st_gout, c->st_rows, c->pf_cos_sin, c->pf_q, c->pf_k, c->pf_v,
-                    c->pf_lg, c->pf_beta, c->qnorm_w, c->knorm_w, c->st_qproj};
+                    c->pf_lg, c->pf_beta, c->pf_wt, c->pf_wm, c->qnorm_w, c->knorm_w, c->st_qproj};
     for (void *p : ptrs)
         if (p) cudaFree(p);
     if (c->stream && c->owns_stream) cudaStreamDestroy(c->stream);
@@ -675,6 +675,8 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
          dalloc(c, &c->knorm_w, (size_t)(c->n_full + 1) * HEAD_DIM, true) && dalloc(c, &c->st_qproj, mb * qd * 2, false) &&
          dalloc(c, (uint16_t **)&c->pf_q, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
          dalloc(c, (uint16_t **)&c->pf_k, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
+         dalloc(c, (uint16_t **)&c->pf_wt, (size_t)c->cfg.max_prefill * vd, false) &&
+         dalloc(c, (uint16_t **)&c->pf_wm, (size_t)c->cfg.max_prefill * g.linear_num_v_heads * 64, false) &&
          dalloc(c, &c->pf_v, (size_t)c->cfg.max_prefill * vd, false) &&
          dalloc(c, &c->pf_lg, (size_t)c->cfg.max_prefill * g.linear_num_v_heads, false) &&
          dalloc(c, &c->pf_beta, (size_t)c->cfg.max_prefill * g.linear_num_v_heads, false);
@@ -1291,6 +1293,8 @@ int mfc_linear_attn_prefill_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, int32
     p.v_io = c->pf_v;
     p.lg = c->pf_lg;
     p.beta_gate = c->pf_beta;
+    p.w_tilde = c->pf_wt;
+    p.w_mask = c->pf_wm;
     p.T = n_tokens;
     p.Hk = g.linear_num_k_heads;
     p.Hv = g.linear_num_v_heads;

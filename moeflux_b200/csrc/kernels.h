@@ -160,6 +160,8 @@ struct GdnPrefillParams {
     void *q_hat, *k_hat;      // scratch [T][Hk*128] bf16
     float *v_io;              // scratch [T][Hv*128] fp32 (v in, raw read-out out)
     float *lg, *beta_gate;    // scratch [T][Hv]
+    void *w_tilde;            // scratch [T][Hv*128] bf16
+    void *w_mask;             // scratch [T][Hv*64] bf16
     int T, Hk, Hv, conv_dim;
     float eps;
 };
