@@ -1301,7 +1301,7 @@ int mfc_linear_attn_prefill_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, int32
     p.conv_dim = c->conv_dim;
     p.eps = g.rms_norm_eps;
     CK(launch_gdn_prefill(p, c->stream));
-    c->launches += 4;
+    c->launches += 5;
     c->conv_step[slot] += n_tokens;
     return 0;
 }

@@ -2,17 +2,21 @@
 // storage type), for sm_100a.  Same work split, TMA pipeline, RoPE/append fusion
 // and epilogue as the bf16 kernel (gqa_decode.cu); the tile maths differs.
 //
-// fp32 operands run on the tensor cores as 3xTF32: every operand x is split
-// into hi = x truncated to tf32 and lo = x - hi, and a product a*b is accumulated as
-// a_hi*b_hi + a_lo*b_hi + a_hi*b_lo in fp32, which keeps the error near 2^-21
-// relative (the reference is fp32 throughout: crates/moeflux/src/riir/sdpa.rs:
-// 114-169).  A 16x256 fp32 Q in hi/lo form does not fit in registers next to
-// the accumulators, so here each warp owns 64 of the 256 dims for BOTH
-// contractions: it computes a partial score block over its dims, the four
-// partial blocks are summed through shared memory, and P·V is accumulated for
+// fp32 operands run on the tensor cores as a two-piece bf16 expansion: every
+// operand x is split into hi = bf16(x) and mid = bf16(x - hi) (16 mantissa bits,
+// fp32's exponent range), and a product a*b is accumulated in fp32 as
+// a_hi*b_hi + a_mid*b_hi + a_hi*b_mid.  What is dropped (a_mid*b_mid and the two
+// remainders) is below 2^-16 of |a||b| per term, which leaves the attention output
+// within about 1e-5 relative of the fp32 reference (crates/moeflux/src/riir/sdpa.rs:
+// 114-169) at half the tensor-pipe instructions of a 3xTF32 scheme: mma.sync
+// m16n8k16 covers 16 k per instruction where the tf32 shape covers 8, and this
+// kernel is bound by that pipe, not by memory.  Each warp owns 64 of the 256 dims
+// for BOTH contractions: it computes a partial score block over its dims, the four
+// partial blocks are summed through shared memory, and P V is accumulated for
 // the same 64 dims.  Tiles are 16 rows; K fragments come from ldmatrix (an 8x8
-// b16 matrix is an 8x4 fp32 block), V fragments from conflict-free scalar loads
-// with the k index of the MMA permuted to match the score fragment layout.
+// b16 matrix is an 8x4 fp32 block) with the k index of the MMA permuted so that the
+// two floats a lane receives form one bf16x2 operand register; V fragments come
+// from conflict-free scalar loads.
 #include <math.h>
 
 #include "gqa_common.cuh"
@@ -27,11 +31,10 @@ constexpr int TILE_BYTES_F32 = F32_TILE * HEAD_DIM * 4;  // 16 KiB per tensor pe
 constexpr int BOX_BYTES = F32_TILE * 128;                // one [16 rows x 32 floats] box
 constexpr int SP_STRIDE = 24;                            // padded row stride of a partial score block
 
-// x = hi + lo with hi = x truncated to tf32 precision (exact subtraction), lo the
-// remainder; the tensor core reads only the tf32 bits of lo.  Two instructions.
-__device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo) {
-    hi = __float_as_uint(x) & 0xffffe000u;
-    lo = __float_as_uint(x - __uint_as_float(hi));
+// (x0, x1) -> bf16x2 registers hi and mid with x = hi + mid + O(2^-18 |x|); x0 in the low half.
+__device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t &hi, uint32_t &mid) {
+    hi = pack_bf16x2(x0, x1);
+    mid = pack_bf16x2(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xffff0000u));
 }
 
 __global__ void __launch_bounds__(128, 2)
@@ -133,27 +136,30 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         }
     }
 
-    // ---- Q fragments for this warp's 64 dims: 8 k-steps of 8, hi and lo ----
-    // A (16x8, tf32): a0 (g, t)  a1 (g+8, t)  a2 (g, t+4)  a3 (g+8, t+4)
-    uint32_t qh[8][4], ql[8][4];
+    // ---- Q fragments for this warp's 64 dims: 4 k-steps of 16, hi and mid ----
+    // A (16x16, bf16): a0 (g, k=2t,2t+1)  a1 (g+8, same k)  a2 (g, k=2t+8,2t+9)  a3 (g+8, same k).
+    // k -> dim map inside a 16-dim step: 2t -> t, 2t+1 -> t+4, 2t+8 -> t+8, 2t+9 -> t+12 (see the K fragments).
+    uint32_t qh[4][4], qm[4][4];
     {
         const float *qbase = p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * (size_t)p.q_row_stride;
         const uint16_t *qnw = p.qnorm_w ? p.qnorm_w + (size_t)(it.kv_slot / p.n_seqs) * HEAD_DIM : nullptr;
         if (qnw) head_inv_rms(qbase, group, p.q_row_stride, p.norm_eps, s_inv);
 #pragma unroll
-        for (int ks = 0; ks < 8; ks++) {
+        for (int ks = 0; ks < 4; ks++) {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const int row = g + ((e & 1) ? 8 : 0);
-                const int d = 64 * warp + 8 * ks + t + ((e & 2) ? 4 : 0);
-                float x = 0.0f;
+                const int d = 64 * warp + 16 * ks + t + ((e & 2) ? 8 : 0);
+                float xa = 0.0f, xb = 0.0f;
                 if (row < group) {
                     const float *qr = qbase + (size_t)row * p.q_row_stride;
                     const float qinv = qnw ? s_inv[row] : 1.0f;
-                    const float2 pr = load_rot2(qr, d & ~1, p.rotary_dim, half, s_cos, s_sin, qinv, qnw);
-                    x = (d & 1) ? pr.y : pr.x;
+                    const float2 pa = load_rot2(qr, d & ~1, p.rotary_dim, half, s_cos, s_sin, qinv, qnw);
+                    const float2 pb = load_rot2(qr, (d + 4) & ~1, p.rotary_dim, half, s_cos, s_sin, qinv, qnw);
+                    xa = (d & 1) ? pa.y : pa.x;
+                    xb = (d & 1) ? pb.y : pb.x;
                 }
-                split_tf32(x, qh[ks][e], ql[ks][e]);
+                split_bf16x2(xa, xb, qh[ks][e], qm[ks][e]);
             }
         }
     }
@@ -184,23 +190,18 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
             for (int nt = 0; nt < 2; nt++) {
                 const int row = 8 * nt + r;
 #pragma unroll
-                for (int jx = 0; jx < 4; jx++) {  // two k-steps per ldmatrix.x4
+                for (int jx = 0; jx < 4; jx++) {  // one 16-dim k-step per ldmatrix.x4
                     const int box = 2 * warp + (jx >> 1);
                     const int chunk = ((jx & 1) << 2) + mi;
                     const uint32_t addr = kst + box * BOX_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4);
-                    uint32_t r0, r1, r2, r3;
+                    uint32_t r0, r1, r2, r3;  // K[row g][16 jx + t, + 4, + 8, + 12] of this warp's dims
                     ldmatrix_x4(r0, r1, r2, r3, addr);
-                    uint32_t h0, l0, h1, l1;
-                    split_tf32(__uint_as_float(r0), h0, l0);
-                    split_tf32(__uint_as_float(r1), h1, l1);
-                    mma_tf32_1688(sp[nt], qh[2 * jx], h0, h1);
-                    mma_tf32_1688(sp[nt], ql[2 * jx], h0, h1);
-                    mma_tf32_1688(sp[nt], qh[2 * jx], l0, l1);
-                    split_tf32(__uint_as_float(r2), h0, l0);
-                    split_tf32(__uint_as_float(r3), h1, l1);
-                    mma_tf32_1688(sp[nt], qh[2 * jx + 1], h0, h1);
-                    mma_tf32_1688(sp[nt], ql[2 * jx + 1], h0, h1);
-                    mma_tf32_1688(sp[nt], qh[2 * jx + 1], l0, l1);
+                    uint32_t h0, m0, h1, m1;
+                    split_bf16x2(__uint_as_float(r0), __uint_as_float(r1), h0, m0);
+                    split_bf16x2(__uint_as_float(r2), __uint_as_float(r3), h1, m1);
+                    mma_bf16_16816(sp[nt], qh[jx], h0, h1);
+                    mma_bf16_16816(sp[nt], qm[jx], h0, h1);
+                    mma_bf16_16816(sp[nt], qh[jx], m0, m1);
                 }
             }
         }
@@ -269,32 +270,27 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
             o[nt][2] *= corr[1];
             o[nt][3] *= corr[1];
         }
-        // O[:, 64w..64w+63] += P (16x16) * V (16 x 64).  The score fragment holds
-        // columns (2t, 2t+1) where the A operand wants (t, t+4): the MMA's k index
-        // is permuted (k=t -> row 2t, k=t+4 -> row 2t+1) on both operands.
-#pragma unroll
-        for (int kk = 0; kk < 2; kk++) {
-            uint32_t ph[4], pl[4];
-            split_tf32(sv[kk][0], ph[0], pl[0]);  // (g,   k=t)   <- col 2t
-            split_tf32(sv[kk][2], ph[1], pl[1]);  // (g+8, k=t)
-            split_tf32(sv[kk][1], ph[2], pl[2]);  // (g,   k=t+4) <- col 2t+1
-            split_tf32(sv[kk][3], ph[3], pl[3]);  // (g+8, k=t+4)
-            const int prow = 8 * kk + 2 * t;
+        // O[:, 64w..64w+63] += P (16x16) * V (16 x 64): one k-step of 16 tile rows; the score
+        // fragment (columns 2t, 2t+1 of each 8-column block) is already in A-operand order.
+        {
+            uint32_t ph[4], pm[4];
+            split_bf16x2(sv[0][0], sv[0][1], ph[0], pm[0]);  // (g,   rows 2t, 2t+1)
+            split_bf16x2(sv[0][2], sv[0][3], ph[1], pm[1]);  // (g+8, rows 2t, 2t+1)
+            split_bf16x2(sv[1][0], sv[1][1], ph[2], pm[2]);  // (g,   rows 2t+8, 2t+9)
+            split_bf16x2(sv[1][2], sv[1][3], ph[3], pm[3]);  // (g+8, rows 2t+8, 2t+9)
+            auto v_at = [&](const uint8_t *bx, int r, int col) {
+                return *reinterpret_cast<const float *>(bx + r * 128 + ((((col >> 2) ^ (r & 7))) << 4) + (col & 3) * 4);
+            };
 #pragma unroll
             for (int nt = 0; nt < 8; nt++) {
-                const int box = 2 * warp + (nt >> 2);
+                const uint8_t *bx = vgen + (2 * warp + (nt >> 2)) * BOX_BYTES;
                 const int col = 8 * (nt & 3) + g;
-                const uint8_t *bx = vgen + box * BOX_BYTES;
-                const float v0 = *reinterpret_cast<const float *>(
-                    bx + prow * 128 + ((((col >> 2) ^ (prow & 7))) << 4) + (col & 3) * 4);
-                const float v1 = *reinterpret_cast<const float *>(
-                    bx + (prow + 1) * 128 + ((((col >> 2) ^ ((prow + 1) & 7))) << 4) + (col & 3) * 4);
-                uint32_t h0, l0, h1, l1;
-                split_tf32(v0, h0, l0);
-                split_tf32(v1, h1, l1);
-                mma_tf32_1688(o[nt], ph, h0, h1);
-                mma_tf32_1688(o[nt], pl, h0, h1);
-                mma_tf32_1688(o[nt], ph, l0, l1);
+                uint32_t h0, m0, h1, m1;
+                split_bf16x2(v_at(bx, 2 * t, col), v_at(bx, 2 * t + 1, col), h0, m0);
+                split_bf16x2(v_at(bx, 2 * t + 8, col), v_at(bx, 2 * t + 9, col), h1, m1);
+                mma_bf16_16816(o[nt], ph, h0, h1);
+                mma_bf16_16816(o[nt], pm, h0, h1);
+                mma_bf16_16816(o[nt], ph, m0, m1);
             }
         }
     }
