@@ -160,6 +160,25 @@ bool dalloc(mfc_ctx *c, T **p, size_t n, bool zero) {
     return true;
 }
 
+// 2-D map over a row-major [rows][cols] array, 128-byte swizzle; box_cols * esize must be 128.
+bool make_map_2d(mfc_ctx *c, CUtensorMap *map, void *base, CUtensorMapDataType dtype, int esize, uint64_t cols,
+                 uint64_t rows, int box_cols, int box_rows) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || !fn || qres != cudaDriverEntryPointSuccess)
+        return fail(c, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(cols * esize)};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = ((EncodeTiledFn)fn)(map, dtype, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(c, "cuTensorMapEncodeTiled failed, code " + std::to_string((int)r));
+    return true;
+}
+
 bool make_tensor_map(mfc_ctx *c, CUtensorMap *map, void *base, uint64_t rows, int box_rows = 0) {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -1300,7 +1319,17 @@ int mfc_linear_attn_prefill_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, int32
     p.Hv = g.linear_num_v_heads;
     p.conv_dim = c->conv_dim;
     p.eps = g.rms_norm_eps;
-    CK(launch_gdn_prefill(p, c->stream));
+    p.status = c->status;
+    GdnPrefillMaps m;
+    const uint64_t kd = (uint64_t)g.linear_num_k_heads * GDN_DIM, vd = (uint64_t)g.linear_num_v_heads * GDN_DIM;
+    if (!make_map_2d(c, &m.wt, c->pf_wt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, vd, n_tokens, 64, 64) ||
+        !make_map_2d(c, &m.q, c->pf_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kd, n_tokens, 64, 64) ||
+        !make_map_2d(c, &m.k, c->pf_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kd, n_tokens, 64, 64) ||
+        !make_map_2d(c, &m.wm, c->pf_wm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)g.linear_num_v_heads * 64, n_tokens,
+                     64, 64) ||
+        !make_map_2d(c, &m.ut, c->pf_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, vd, n_tokens, 32, 64))
+        return -1;
+    CK(launch_gdn_prefill(p, m, c->stream));
     c->launches += 5;
     c->conv_step[slot] += n_tokens;
     return 0;

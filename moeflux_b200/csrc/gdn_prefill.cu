@@ -33,6 +33,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tcgen05.cuh"
 
 namespace mfc {
 
@@ -361,172 +362,287 @@ gdn_prefill_intra_kernel(const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat,
 }
 
 // ------------------------------------------------------------------ 2b. the serial part: state across chunks
-// grid 2*Hv, 256 threads.  One CTA owns 64 of the 128 value rows of one v-head, keeps
-// that half-state in registers in fp32 across all chunks (a bf16 operand copy in shared
-// memory) and per chunk runs
-//   U = Ut - Wt S0^T;   O = diag(gamma) Q S0^T + Wm U;   S = gamma_C S0 + (diag(gamma_C/gamma) U)^T K
-// on the tensor cores (mma.sync m16n8k16, bf16 operands, fp32 accumulate).  Operands of
-// chunk c+1 are requested while chunk c is worked on.
-struct StateSmem {
-    __nv_bfloat16 K[2][CH][LDK];
-    __nv_bfloat16 Q[2][CH][LDK];
-    __nv_bfloat16 Wt[2][CH][LDK];
-    __nv_bfloat16 Wm[2][CH][LDT];
-    __nv_bfloat16 Sb[DVC][LDK];   // bf16 operand copy of the state rows
-    __nv_bfloat16 U[CH][LDT];     // [token][value row]
-    __nv_bfloat16 Us[CH][LDT];    // rows scaled by gamma_C/gamma_t
-};
+// grid 2*Hv, 160 threads.  One CTA owns 64 of the 128 value rows of one v-head and keeps
+// that half-state, transposed (key index = TMEM lane, value row = column), in tensor
+// memory in fp32 across all chunks.  Per chunk, three groups of tcgen05.mma (M = 128,
+// N = 64, bf16 operands, fp32 accumulate):
+//   D1 = [Wt ; Q] S0^T          rows 0-63: Wt S0^T, rows 64-127: Q S0^T        (K = 128 key dims)
+//   D2 = [ . ; Wm] U            rows 64-127: Wm U                              (K = 64 tokens)
+//   ST = gamma_C ST + K^T Us    Us = diag(gamma_C/gamma_t) U                   (K = 64 tokens)
+// with U = Ut - D1[0:64] and O = diag(gamma) D1[64:128] + D2[64:128] computed by the four
+// epilogue warps (thread = TMEM lane).  Operands arrive by TMA (128-byte swizzle) into a
+// two-stage ring; S0 (bf16), U and Us are written to shared memory by the epilogue warps
+// as MN-major operands, one 128-byte row per thread.  Warp 4 issues every TMA load and
+// every MMA.  Every mbarrier wait is bounded; a wait that expires sets a status bit and
+// the CTA frees its TMEM and leaves.
+constexpr uint32_t ST_A1 = 0;                    // [2 boxes][128 rows][128 B]: rows 0-63 Wt, rows 64-127 q^
+constexpr uint32_t ST_K = ST_A1 + 32768;         // [2 boxes][64 rows][128 B]
+constexpr uint32_t ST_WM = ST_K + 16384;         // [64 rows][128 B]
+constexpr uint32_t ST_UT = ST_WM + 8192;         // [2 boxes][64 rows][128 B] fp32
+constexpr uint32_t STAGE_BYTES = ST_UT + 16384;  // 72 KiB
+constexpr uint32_t LOAD_A_BYTES = 32768 + 16384;  // Wt, q^ and Ut
+constexpr uint32_t LOAD_B_BYTES = 16384 + 8192;   // k^ and Wm
+constexpr uint32_t TC_OFF_SB = 2 * STAGE_BYTES;   // [128 key rows][128 B]
+constexpr uint32_t TC_OFF_U = TC_OFF_SB + 16384;  // [64 token rows][128 B]
+constexpr uint32_t TC_OFF_US = TC_OFF_U + 8192;
+constexpr uint32_t TC_OFF_BAR = TC_OFF_US + 8192;
+constexpr uint32_t TC_SMEM = TC_OFF_BAR + 128 + 1024;
+constexpr uint32_t TC_TMEM_COLS = 256;
+constexpr uint32_t TM_ST = 0, TM_D1 = 64, TM_D2 = 128;
 
-__global__ void __launch_bounds__(256, 1)
-gdn_prefill_state_kernel(float *ssm, const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat, float *v_io,
-                         const float *lgc, const __nv_bfloat16 *w_tilde, const __nv_bfloat16 *w_mask, int T, int Hk,
-                         int Hv) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    StateSmem &sm = *reinterpret_cast<StateSmem *>(smem_raw);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t4 = lane & 3;
+// address of 16-byte chunk c of row r in a [rows][128 B] region laid out with the 128-byte swizzle
+__device__ __forceinline__ uint8_t *sw128_chunk(uint8_t *base, int r, int c) { return base + r * 128 + ((c ^ (r & 7)) << 4); }
+
+__global__ void __launch_bounds__(160, 1)
+gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __grid_constant__ CUtensorMap q_map,
+                         const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap wm_map,
+                         const __grid_constant__ CUtensorMap ut_map, float *ssm, float *v_io, const float *lgc, int T,
+                         int Hk, int Hv, unsigned *status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_OFF_BAR);
+    uint64_t *full = bars + 0;      // [2] TMA: a stage has landed (two arrivals: the A part and the B part)
+    uint64_t *d1_ready = bars + 2;  // tcgen05.commit
+    uint64_t *d2_ready = bars + 3;  // tcgen05.commit
+    uint64_t *g3_done = bars + 4;   // tcgen05.commit: the state update of a chunk has been accumulated
+    uint64_t *u_ready = bars + 5;   // 64 arrivals: U and Us are in shared memory, D1[0:64] and Ut have been read
+    uint64_t *s_ready = bars + 6;   // 128 arrivals: S0 (bf16) is in shared memory, ST is scaled, D1/D2 have been read
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
+    volatile int *s_fail = reinterpret_cast<volatile int *>(bars + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
     const int h = blockIdx.x >> 1, half = blockIdx.x & 1;
     const int j = h / (Hv / Hk);
     const size_t vrow = (size_t)Hv * GDN_DIM;
-    float *Sg = ssm + ((size_t)h * GDN_DIM + half * DVC) * GDN_DIM;
     const int vcol0 = h * GDN_DIM + half * DVC;  // first value channel of this CTA in [T][Hv*128] arrays
+    float *Sg = ssm + ((size_t)h * GDN_DIM + half * DVC) * GDN_DIM;
     const int n_chunks = (T + CH - 1) / CH;
 
-    // roles: products over tokens: (16-token tile mt, 32-value-row half nh); state update: (16 value rows sm_, 64 key columns sn)
-    const int mt = warp & 3, nh = warp >> 2;
-    const int r0 = 16 * mt + g, r1 = r0 + 8;
-    const int srow0 = 16 * (warp & 3) + g, scol0 = 64 * (warp >> 2);
-
-    auto prefetch = [&](int cc_) {
-        const int base = cc_ * CH, buf = cc_ & 1;
-        for (int i = tid; i < CH * (GDN_DIM / 8); i += 256) {
-            const int r = i >> 4, col = (i & 15) * 8;
-            const bool in = base + r < T;
-            const unsigned nbytes = in ? 16u : 0u;
-            const size_t tk = (size_t)(in ? base + r : 0);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&sm.K[buf][r][col])),
-                         "l"(k_hat + (tk * Hk + j) * GDN_DIM + col), "r"(nbytes)
-                         : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&sm.Q[buf][r][col])),
-                         "l"(q_hat + (tk * Hk + j) * GDN_DIM + col), "r"(nbytes)
-                         : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&sm.Wt[buf][r][col])),
-                         "l"(w_tilde + (tk * Hv + h) * GDN_DIM + col), "r"(nbytes)
-                         : "memory");
-        }
-        for (int i = tid; i < CH * (CH / 8); i += 256) {
-            const int r = i >> 3, col = (i & 7) * 8;
-            const bool in = base + r < T;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(&sm.Wm[buf][r][col])),
-                         "l"(w_mask + ((size_t)(in ? base + r : 0) * Hv + h) * CH + col), "r"(in ? 16u : 0u)
-                         : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    // per-thread values of a chunk that come straight from global memory: its Ut elements and decay logs
-    struct ChunkRegs {
-        float2 ut[4][2];
-        float lg0, lg1, lgC;
-    };
-    auto fetch_regs = [&](int cc_, ChunkRegs &cr) {
-        const int base = cc_ * CH;
-        const bool in0 = base + r0 < T, in1 = base + r1 < T;
-#pragma unroll
-        for (int n = 0; n < 4; n++) {
-            const int col = vcol0 + 32 * nh + 8 * n + 2 * t4;
-            cr.ut[n][0] = in0 ? *reinterpret_cast<const float2 *>(&v_io[(size_t)(base + r0) * vrow + col]) : make_float2(0.0f, 0.0f);
-            cr.ut[n][1] = in1 ? *reinterpret_cast<const float2 *>(&v_io[(size_t)(base + r1) * vrow + col]) : make_float2(0.0f, 0.0f);
-        }
-        cr.lg0 = lgc[(size_t)min(base + r0, T - 1) * Hv + h];
-        cr.lg1 = lgc[(size_t)min(base + r1, T - 1) * Hv + h];
-        cr.lgC = lgc[(size_t)min(base + CH - 1, T - 1) * Hv + h];
-    };
-
-    prefetch(0);
-    ChunkRegs nxt;
-    fetch_regs(0, nxt);
-    float S[8][4];  // state rows srow0, srow0+8; columns scol0 + 8n + 2*t4 + {0,1}
-#pragma unroll
-    for (int n = 0; n < 8; n++) {
-        const int col = scol0 + 8 * n + 2 * t4;
-        const float2 a = *reinterpret_cast<const float2 *>(&Sg[(size_t)srow0 * GDN_DIM + col]);
-        const float2 b = *reinterpret_cast<const float2 *>(&Sg[(size_t)(srow0 + 8) * GDN_DIM + col]);
-        S[n][0] = a.x;
-        S[n][1] = a.y;
-        S[n][2] = b.x;
-        S[n][3] = b.y;
-        *reinterpret_cast<uint32_t *>(&sm.Sb[srow0][col]) = pack_bf16x2(a.x, a.y);
-        *reinterpret_cast<uint32_t *>(&sm.Sb[srow0 + 8][col]) = pack_bf16x2(b.x, b.y);
+    if (tid == 0) {
+        prefetch_tmap(&wt_map);
+        prefetch_tmap(&q_map);
+        prefetch_tmap(&k_map);
+        prefetch_tmap(&wm_map);
+        prefetch_tmap(&ut_map);
+        mbar_init(&full[0], 2);
+        mbar_init(&full[1], 2);
+        mbar_init(d1_ready, 1);
+        mbar_init(d2_ready, 1);
+        mbar_init(g3_done, 1);
+        mbar_init(u_ready, 64);
+        mbar_init(s_ready, 128);
+        *s_fail = 0;
+        mbar_fence_init();
     }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, TC_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+    auto lg_at = [&](int tok) { return lgc[(size_t)min(tok, T - 1) * Hv + h]; };
 
-    for (int c = 0; c < n_chunks; c++) {
-        const int buf = c & 1, tok0 = c * CH;
-        asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's copies of chunk c have landed
-        __syncthreads();  // everyone's have; Sb holds the current state; the other buffers are free
-        const ChunkRegs cur = nxt;
-        if (c + 1 < n_chunks) {
-            prefetch(c + 1);
-            fetch_regs(c + 1, nxt);
-        }
-        // ---- U = Ut - Wt S0^T and Q S0^T (same B operand) ----
-        float aw[4][4], o[4][4];
+    if (warp == 4) {
+        // ================= issuer: one lane drives TMA and the tensor core =================
+        if ((tid & 31) == 0) {
+            auto load_a = [&](int cc) {  // Wt, q^ and Ut of chunk cc
+                uint8_t *st = smem + (cc & 1) * STAGE_BYTES;
+                uint64_t *bar = &full[cc & 1];
+                mbar_expect_tx(bar, LOAD_A_BYTES);
 #pragma unroll
-        for (int n = 0; n < 4; n++)
+                for (int b = 0; b < 2; b++) {
+                    tma_load_2d(st + ST_A1 + b * 16384, &wt_map, h * GDN_DIM + b * 64, cc * CH, bar);
+                    tma_load_2d(st + ST_A1 + b * 16384 + 8192, &q_map, j * GDN_DIM + b * 64, cc * CH, bar);
+                    tma_load_2d(st + ST_UT + b * 8192, &ut_map, vcol0 + b * 32, cc * CH, bar);
+                }
+            };
+            auto load_b = [&](int cc) {  // k^ and Wm of chunk cc
+                uint8_t *st = smem + (cc & 1) * STAGE_BYTES;
+                uint64_t *bar = &full[cc & 1];
+                mbar_expect_tx(bar, LOAD_B_BYTES);
 #pragma unroll
-            for (int e = 0; e < 4; e++) aw[n][e] = o[n][e] = 0.0f;
-        warp_gemm2_nmajor<4, 8>(aw, o, &sm.Wt[buf][16 * mt][0], &sm.Q[buf][16 * mt][0], LDK, &sm.Sb[32 * nh][0], LDK, lane);
-        {
-            const float f0 = ex2_approx(cur.lgC - cur.lg0), f1 = ex2_approx(cur.lgC - cur.lg1);
-            const float e0 = ex2_approx(cur.lg0), e1 = ex2_approx(cur.lg1);
-#pragma unroll
-            for (int n = 0; n < 4; n++) {
-                const int col = 32 * nh + 8 * n + 2 * t4;
-                const float u00 = cur.ut[n][0].x - aw[n][0], u01 = cur.ut[n][0].y - aw[n][1];
-                const float u10 = cur.ut[n][1].x - aw[n][2], u11 = cur.ut[n][1].y - aw[n][3];
-                *reinterpret_cast<uint32_t *>(&sm.U[r0][col]) = pack_bf16x2(u00, u01);
-                *reinterpret_cast<uint32_t *>(&sm.U[r1][col]) = pack_bf16x2(u10, u11);
-                *reinterpret_cast<uint32_t *>(&sm.Us[r0][col]) = pack_bf16x2(u00 * f0, u01 * f0);
-                *reinterpret_cast<uint32_t *>(&sm.Us[r1][col]) = pack_bf16x2(u10 * f1, u11 * f1);
-                o[n][0] *= e0;
-                o[n][1] *= e0;
-                o[n][2] *= e1;
-                o[n][3] *= e1;
+                for (int b = 0; b < 2; b++) tma_load_2d(st + ST_K + b * 8192, &k_map, j * GDN_DIM + b * 64, cc * CH, bar);
+                tma_load_2d(st + ST_WM, &wm_map, h * CH, cc * CH, bar);
+            };
+            constexpr uint32_t IDESC_KN = idesc_bf16(DVC, 1, 0);  // A K-major, B MN-major
+            constexpr uint32_t IDESC_MN = idesc_bf16(DVC, 1, 1);  // A and B MN-major
+            const uint32_t sbase = smem_u32(smem);
+            const uint64_t sb_desc = smem_desc_sw128(sbase + TC_OFF_SB, 16384, 1024);
+            const uint64_t u_desc = smem_desc_sw128(sbase + TC_OFF_U, 8192, 1024);
+            const uint64_t us_desc = smem_desc_sw128(sbase + TC_OFF_US, 8192, 1024);
+
+            load_a(0);
+            load_b(0);
+            if (n_chunks > 1) {
+                load_a(1);
+                load_b(1);
             }
-        }
-        __syncthreads();  // U and Us are complete; nobody reads Sb any more
-        // ---- O += Wm U -> written over v_io (fp32) ----
-        warp_gemm_kmajor<4, 4>(o, &sm.Wm[buf][16 * mt][0], LDT, &sm.U[0][32 * nh], LDT, lane);
-        {
-            const bool in0 = tok0 + r0 < T, in1 = tok0 + r1 < T;
+            for (int c = 0; c < n_chunks && ok; c++) {
+                const uint32_t st = sbase + (c & 1) * STAGE_BYTES;
+                const unsigned par = (unsigned)c & 1u;
+                ok = mbar_wait_bounded(&full[c & 1], (unsigned)(c >> 1) & 1u) && mbar_wait_bounded(s_ready, par);
+                if (!ok) break;
+                // the other stage held chunk c-1, whose last reader (the state update) completed before s_ready
+                if (c >= 1 && c + 1 < n_chunks) load_b(c + 1);
+                tc_fence_after();
+                {
+                    const uint64_t a1 = smem_desc_sw128(st + ST_A1, 16, 1024);
 #pragma unroll
-            for (int n = 0; n < 4; n++) {
-                const int col = vcol0 + 32 * nh + 8 * n + 2 * t4;
-                if (in0) *reinterpret_cast<float2 *>(&v_io[(size_t)(tok0 + r0) * vrow + col]) = make_float2(o[n][0], o[n][1]);
-                if (in1) *reinterpret_cast<float2 *>(&v_io[(size_t)(tok0 + r1) * vrow + col]) = make_float2(o[n][2], o[n][3]);
+                    for (int ks = 0; ks < 8; ks++)
+                        tc_mma_bf16(tmem + TM_D1, a1 + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4),
+                                    sb_desc + (uint64_t)((ks * 2048) >> 4), IDESC_KN, ks > 0);
+                    tc_commit(d1_ready);
+                }
+                ok = mbar_wait_bounded(u_ready, par);
+                if (!ok) break;
+                // Wt, q^ (read by the MMAs above, complete since D1 was read) and Ut of this stage are free
+                if (c + 2 < n_chunks) load_a(c + 2);
+                tc_fence_after();
+                {
+                    // rows 0-63 of this A operand are the 8 KiB in front of Wm (finite k^ data); only rows 64-127 of D2 are used
+                    const uint64_t wm = smem_desc_sw128(st + ST_WM - 8192, 16, 1024);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        tc_mma_bf16(tmem + TM_D2, wm + (uint64_t)((ks * 32) >> 4), u_desc + (uint64_t)((ks * 2048) >> 4),
+                                    IDESC_KN, ks > 0);
+                    tc_commit(d2_ready);
+                    const uint64_t kd = smem_desc_sw128(st + ST_K, 8192, 1024);  // m = key dim: two 64-wide atoms 8 KiB apart
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        tc_mma_bf16(tmem + TM_ST, kd + (uint64_t)((ks * 2048) >> 4), us_desc + (uint64_t)((ks * 2048) >> 4),
+                                    IDESC_MN, 1);
+                    tc_commit(g3_done);
+                }
             }
+            if (!ok) *s_fail = 1;
         }
-        // ---- S = gamma_C S + Us^T K ----
+    } else {
+        // ================= epilogue warps: thread = TMEM lane =================
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const int r = tid & 63;  // token row of this thread in D1 / D2 (warps 0-1: U rows, warps 2-3: O rows)
+        // ---- initial state: column tid of S (key dim) over the 64 value rows ----
         {
-            const float gC = ex2_approx(cur.lgC);
+            float sv[DVC];
 #pragma unroll
-            for (int n = 0; n < 8; n++)
+            for (int d = 0; d < DVC; d++) sv[d] = Sg[(size_t)d * GDN_DIM + tid];
+            const float g0 = ex2_approx(lg_at(CH - 1));
 #pragma unroll
-                for (int e = 0; e < 4; e++) S[n][e] *= gC;
-            warp_gemm_at_kmajor<8, 4>(S, &sm.Us[0][16 * (warp & 3)], LDT, &sm.K[buf][0][scol0], LDK, lane);
+            for (int cch = 0; cch < 8; cch++) {
+                uint32_t w[4];
 #pragma unroll
-            for (int n = 0; n < 8; n++) {
-                const int col = scol0 + 8 * n + 2 * t4;
-                *reinterpret_cast<uint32_t *>(&sm.Sb[srow0][col]) = pack_bf16x2(S[n][0], S[n][1]);
-                *reinterpret_cast<uint32_t *>(&sm.Sb[srow0 + 8][col]) = pack_bf16x2(S[n][2], S[n][3]);
+                for (int e = 0; e < 4; e++) w[e] = pack_bf16x2(sv[8 * cch + 2 * e], sv[8 * cch + 2 * e + 1]);
+                *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_SB, tid, cch)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
+#pragma unroll
+            for (int d = 0; d < DVC; d++) sv[d] *= g0;
+            tmem_st32(lane_base + TM_ST, *reinterpret_cast<float(*)[32]>(&sv[0]));
+            tmem_st32(lane_base + TM_ST + 32, *reinterpret_cast<float(*)[32]>(&sv[32]));
+            tc_wait_st();
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(s_ready);
         }
+        float lg_r = lg_at(r), lg_c = lg_at(CH - 1);
+        for (int c = 0; c < n_chunks && ok; c++) {
+            uint8_t *st = smem + (c & 1) * STAGE_BYTES;
+            const unsigned par = (unsigned)c & 1u;
+            const int tok = c * CH + r;
+            // decay logs of the next chunk, requested now
+            const float lg_r_next = lg_at((c + 1) * CH + r), lg_c_next = lg_at((c + 1) * CH + CH - 1);
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(d1_ready, par) && *s_fail == 0);
+            if (!ok) break;
+            tc_fence_after();
+            float d1[DVC];
+            tmem_ld32(lane_base + TM_D1, d1);
+            tmem_ld32(lane_base + TM_D1 + 32, d1 + 32);
+            tc_wait_ld();
+            if (warp < 2) {
+                // ---- U = Ut - Wt S0^T ; Us = (gamma_C/gamma_t) U ----
+                const float f = ex2_approx(lg_c - lg_r);
+#pragma unroll
+                for (int cch = 0; cch < 8; cch++) {
+                    uint32_t wu[4], ws[4];
+#pragma unroll
+                    for (int e2 = 0; e2 < 2; e2++) {
+                        const int d0 = 8 * cch + 4 * e2;  // value row of the first of four floats
+                        const float4 ut = *reinterpret_cast<const float4 *>(
+                            sw128_chunk(st + ST_UT + (d0 >> 5) * 8192, r, (d0 & 31) >> 2));
+                        const float u0 = ut.x - d1[d0], u1 = ut.y - d1[d0 + 1], u2 = ut.z - d1[d0 + 2], u3 = ut.w - d1[d0 + 3];
+                        wu[2 * e2] = pack_bf16x2(u0, u1);
+                        wu[2 * e2 + 1] = pack_bf16x2(u2, u3);
+                        ws[2 * e2] = pack_bf16x2(u0 * f, u1 * f);
+                        ws[2 * e2 + 1] = pack_bf16x2(u2 * f, u3 * f);
+                    }
+                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_U, r, cch)) = make_uint4(wu[0], wu[1], wu[2], wu[3]);
+                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_US, r, cch)) = make_uint4(ws[0], ws[1], ws[2], ws[3]);
+                }
+                fence_proxy_async_smem();
+                tc_fence_before();
+                mbar_arrive(u_ready);
+            } else {
+                // ---- O = gamma_t Q S0^T + Wm U -> written over v_io (fp32) ----
+                const float e = ex2_approx(lg_r);
+#pragma unroll
+                for (int d = 0; d < DVC; d++) d1[d] *= e;
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(d2_ready, par));
+                if (!ok) break;
+                tc_fence_after();
+                float *dst = v_io + (size_t)tok * vrow + vcol0;
+#pragma unroll
+                for (int hb = 0; hb < 2; hb++) {
+                    float d2[32];
+                    tmem_ld32(lane_base + TM_D2 + 32 * hb, d2);
+                    tc_wait_ld();
+                    if (tok < T) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; q4++)
+                            *reinterpret_cast<float4 *>(dst + 32 * hb + 4 * q4) =
+                                make_float4(d1[32 * hb + 4 * q4] + d2[4 * q4], d1[32 * hb + 4 * q4 + 1] + d2[4 * q4 + 1],
+                                            d1[32 * hb + 4 * q4 + 2] + d2[4 * q4 + 2], d1[32 * hb + 4 * q4 + 3] + d2[4 * q4 + 3]);
+                    }
+                }
+            }
+            // ---- state pass: S of this chunk -> bf16 operand copy, and the decay of the next chunk ----
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(g3_done, par));
+            if (!ok) break;
+            tc_fence_after();
+            float sv[DVC];
+            tmem_ld32(lane_base + TM_ST, sv);
+            tmem_ld32(lane_base + TM_ST + 32, sv + 32);
+            tc_wait_ld();
+            if (c + 1 < n_chunks) {
+#pragma unroll
+                for (int cch = 0; cch < 8; cch++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) w[e] = pack_bf16x2(sv[8 * cch + 2 * e], sv[8 * cch + 2 * e + 1]);
+                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_SB, tid, cch)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                const float gn = ex2_approx(lg_c_next);
+#pragma unroll
+                for (int d = 0; d < DVC; d++) sv[d] *= gn;
+                tmem_st32(lane_base + TM_ST, *reinterpret_cast<float(*)[32]>(&sv[0]));
+                tmem_st32(lane_base + TM_ST + 32, *reinterpret_cast<float(*)[32]>(&sv[32]));
+                tc_wait_st();
+                fence_proxy_async_smem();
+                tc_fence_before();
+                mbar_arrive(s_ready);
+            } else {
+#pragma unroll
+                for (int d = 0; d < DVC; d++) Sg[(size_t)d * GDN_DIM + tid] = sv[d];
+            }
+            lg_r = lg_r_next;
+            lg_c = lg_c_next;
+        }
+        if (!ok && (tid & 31) == 0) *s_fail = 1;
     }
-#pragma unroll
-    for (int n = 0; n < 8; n++) {
-        const int col = scol0 + 8 * n + 2 * t4;
-        *reinterpret_cast<float2 *>(&Sg[(size_t)srow0 * GDN_DIM + col]) = make_float2(S[n][0], S[n][1]);
-        *reinterpret_cast<float2 *>(&Sg[(size_t)(srow0 + 8) * GDN_DIM + col]) = make_float2(S[n][2], S[n][3]);
-    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *s_fail) atomicOr(status, STATUS_TMA_TIMEOUT);
+    if (warp == 0) tmem_dealloc(tmem, TC_TMEM_COLS);
 }
 
 // ------------------------------------------------------------------ 3. read-out epilogue
@@ -565,11 +681,10 @@ cudaError_t gdn_prefill_configure() {
     cudaError_t e = cudaFuncSetAttribute(gdn_prefill_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)sizeof(IntraSmem));
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(gdn_prefill_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)sizeof(StateSmem));
+    return cudaFuncSetAttribute(gdn_prefill_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
 }
 
-cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, cudaStream_t stream) {
+cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, const GdnPrefillMaps &m, cudaStream_t stream) {
     if (p.T <= 0) return cudaSuccess;
     const __nv_bfloat16 *x = reinterpret_cast<const __nv_bfloat16 *>(p.qkv);
     dim3 g1((unsigned)p.T, (unsigned)((p.conv_dim + 2047) / 2048), 1);
@@ -587,10 +702,8 @@ cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, cudaStream_t stream) {
         p.beta_gate, reinterpret_cast<__nv_bfloat16 *>(p.w_tilde), reinterpret_cast<__nv_bfloat16 *>(p.w_mask), p.T, p.Hk,
         p.Hv);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    gdn_prefill_state_kernel<<<2 * p.Hv, 256, sizeof(StateSmem), stream>>>(
-        p.ssm, reinterpret_cast<const __nv_bfloat16 *>(p.q_hat), reinterpret_cast<const __nv_bfloat16 *>(p.k_hat), p.v_io,
-        p.lg, reinterpret_cast<const __nv_bfloat16 *>(p.w_tilde), reinterpret_cast<const __nv_bfloat16 *>(p.w_mask), p.T,
-        p.Hk, p.Hv);
+    gdn_prefill_state_kernel<<<2 * p.Hv, 160, TC_SMEM, stream>>>(m.wt, m.q, m.k, m.wm, m.ut, p.ssm, p.v_io, p.lg, p.T, p.Hk,
+                                                               p.Hv, p.status);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     gdn_prefill_out_kernel<<<(unsigned)p.T, 256, 0, stream>>>(p.v_io, reinterpret_cast<const __nv_bfloat16 *>(p.z), p.norm_w,
                                                    reinterpret_cast<__nv_bfloat16 *>(p.out), p.Hv, p.eps);

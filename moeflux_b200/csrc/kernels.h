@@ -162,11 +162,17 @@ struct GdnPrefillParams {
     float *lg, *beta_gate;    // scratch [T][Hv]
     void *w_tilde;            // scratch [T][Hv*128] bf16
     void *w_mask;             // scratch [T][Hv*64] bf16
+    unsigned *status;         // device status word (bounded waits that expired)
     int T, Hk, Hv, conv_dim;
     float eps;
 };
 cudaError_t gdn_prefill_configure();
-cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, cudaStream_t stream);
+// Tensor maps over the first T rows of the scratch arrays (128-byte swizzle, 64-row boxes):
+// w_tilde, q^, k^ and w_mask with 64 bf16 columns per box, v_io with 32 fp32 columns per box.
+struct GdnPrefillMaps {
+    CUtensorMap wt, q, k, wm, ut;
+};
+cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, const GdnPrefillMaps &m, cudaStream_t stream);
 
 // Per-thread message of the last failure that had no context (ctx.cu).
 std::string &no_ctx_error();
