@@ -42,7 +42,6 @@ namespace {
 constexpr int CH = 64;          // tokens per chunk
 constexpr int DVC = 64;         // value rows per CTA
 constexpr int LDK = GDN_DIM + 8;  // padded leading dim (bf16) of [.][128] operand tiles
-constexpr int LDT = CH + 8;       // padded leading dim (bf16) of [.][64] operand tiles
 
 // ------------------------------------------------------------------ 1. conv / norm / gates
 // grid (T, conv_dim / 2048), 256 threads: a thread owns 8 consecutive channels of one
@@ -132,65 +131,14 @@ __global__ void gdn_prefill_ring_kernel(const __nv_bfloat16 *x, float *ring, int
     for (int t = max(0, T - 3); t < T; t++) ring[(size_t)((slot0 + t) & 3) * conv_dim + c] = __bfloat162float(x[(size_t)t * conv_dim + c]);
 }
 
-// ------------------------------------------------------------------ warp-level GEMM pieces
-// acc[NT][4] (16 rows x NT*8 cols, fp32) += A(16 x K) * B, A row-major bf16 (lda), K = KS*16.
-// B given "n-major": element (n, k) at B[n*ldb + k].
-template <int NT, int KS>
-__device__ __forceinline__ void warp_gemm_nmajor(float (&acc)[NT][4], const __nv_bfloat16 *A, int lda,
-                                                 const __nv_bfloat16 *B, int ldb, int lane) {
-#pragma unroll
-    for (int ks = 0; ks < KS; ks++) {
-        uint32_t a[4];
-        ldmatrix_x4(a[0], a[1], a[2], a[3], smem_u32(A + (lane & 15) * lda + ks * 16 + (lane >> 4) * 8));
-#pragma unroll
-        for (int nt = 0; nt < NT; nt += 2) {
-            uint32_t b0, b1, b2, b3;
-            ldmatrix_x4(b0, b1, b2, b3,
-                        smem_u32(B + (nt * 8 + (lane & 7) + ((lane >> 4) << 3)) * ldb + ks * 16 + ((lane >> 3) & 1) * 8));
-            mma_bf16_16816(acc[nt], a, b0, b1);
-            mma_bf16_16816(acc[nt + 1], a, b2, b3);
-        }
-    }
+// ------------------------------------------------------------------ warp-level MMA pieces
+// (x0, x1) -> bf16x2 registers hi and mid with x = hi + mid + O(2^-18 |x|); x0 in the low half.
+__device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t &hi, uint32_t &mid) {
+    hi = pack_bf16x2(x0, x1);
+    mid = pack_bf16x2(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xffff0000u));
 }
-// Same with B given "k-major": element (k, n) at B[k*ldb + n].
-template <int NT, int KS>
-__device__ __forceinline__ void warp_gemm_kmajor(float (&acc)[NT][4], const __nv_bfloat16 *A, int lda,
-                                                 const __nv_bfloat16 *B, int ldb, int lane) {
-#pragma unroll
-    for (int ks = 0; ks < KS; ks++) {
-        uint32_t a[4];
-        ldmatrix_x4(a[0], a[1], a[2], a[3], smem_u32(A + (lane & 15) * lda + ks * 16 + (lane >> 4) * 8));
-#pragma unroll
-        for (int nt = 0; nt < NT; nt += 2) {
-            uint32_t b0, b1, b2, b3;
-            ldmatrix_x4_trans(b0, b1, b2, b3,
-                              smem_u32(B + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldb + nt * 8 + (lane >> 4) * 8));
-            mma_bf16_16816(acc[nt], a, b0, b1);
-            mma_bf16_16816(acc[nt + 1], a, b2, b3);
-        }
-    }
-}
-
-// Same as warp_gemm_kmajor with A given transposed: element (m, k) at At[k*lda + m].
-template <int NT, int KS>
-__device__ __forceinline__ void warp_gemm_at_kmajor(float (&acc)[NT][4], const __nv_bfloat16 *At, int lda,
-                                                    const __nv_bfloat16 *B, int ldb, int lane) {
-#pragma unroll
-    for (int ks = 0; ks < KS; ks++) {
-        uint32_t a[4];
-        ldmatrix_x4_trans(a[0], a[1], a[2], a[3],
-                          smem_u32(At + (ks * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * lda + ((lane >> 3) & 1) * 8));
-#pragma unroll
-        for (int nt = 0; nt < NT; nt += 2) {
-            uint32_t b0, b1, b2, b3;
-            ldmatrix_x4_trans(b0, b1, b2, b3,
-                              smem_u32(B + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldb + nt * 8 + (lane >> 4) * 8));
-            mma_bf16_16816(acc[nt], a, b0, b1);
-            mma_bf16_16816(acc[nt + 1], a, b2, b3);
-        }
-    }
-}
-// Two products that share the n-major B operand: acc1 += A1 B, acc2 += A2 B.
+// Two products that share the n-major B operand (element (n, k) at B[n*ldb + k]): acc1 += A1 B, acc2 += A2 B,
+// A row-major bf16 (lda), K = KS*16.
 template <int NT, int KS>
 __device__ __forceinline__ void warp_gemm2_nmajor(float (&acc1)[NT][4], float (&acc2)[NT][4], const __nv_bfloat16 *A1,
                                                   const __nv_bfloat16 *A2, int lda, const __nv_bfloat16 *B, int ldb,
@@ -212,23 +160,47 @@ __device__ __forceinline__ void warp_gemm2_nmajor(float (&acc1)[NT][4], float (&
         }
     }
 }
+// acc (16 x 16, two n-tiles) += X (16 x 16, A fragments in hi/mid form) * B^T, where the 16 x 16 block B is
+// given in hi/mid form, row-major with leading dimension ldb (element (n, k) at B[n*ldb + k]); the three
+// cross products hi*hi, mid*hi, hi*mid are kept.
+__device__ __forceinline__ void mma_block_split(float (&acc)[2][4], const uint32_t (&xh)[4], const uint32_t (&xm)[4],
+                                                const __nv_bfloat16 *Bh, const __nv_bfloat16 *Bm, int ldb, int lane) {
+    const int off = ((lane & 7) + ((lane >> 4) << 3)) * ldb + ((lane >> 3) & 1) * 8;
+    uint32_t h0, h1, h2, h3, m0, m1, m2, m3;
+    ldmatrix_x4(h0, h1, h2, h3, smem_u32(Bh + off));
+    ldmatrix_x4(m0, m1, m2, m3, smem_u32(Bm + off));
+    mma_bf16_16816(acc[0], xh, h0, h1);
+    mma_bf16_16816(acc[0], xm, h0, h1);
+    mma_bf16_16816(acc[0], xh, m0, m1);
+    mma_bf16_16816(acc[1], xh, h2, h3);
+    mma_bf16_16816(acc[1], xm, h2, h3);
+    mma_bf16_16816(acc[1], xh, m2, m3);
+}
 
 // ------------------------------------------------------------------ 2a. per-chunk work that does not need the state
 // grid (chunks, Hv), 256 threads.  Everything of a chunk that is independent of the
 // running state is done here, for all chunks in parallel:
 //   lg      <- inclusive prefix sum of log2 g inside the chunk (in place)
-//   A_ti    = beta_t (gamma_t/gamma_i) (k_t.k_i), i < t                     shared memory, fp32
+//   A_ti    = beta_t (gamma_t/gamma_i) (k_t.k_i), i < t;  L = I + A
 //   Wm_ti   = (gamma_t/gamma_i) (q_t.k_i), i <= t                           -> w_mask (bf16)
-//   (I + A) Wt = diag(beta gamma) K      forward substitution, fp32         -> w_tilde (bf16)
-//   (I + A) Ut = diag(beta) V            forward substitution, fp32         -> v_io in place (fp32)
-// so that the serial kernel is left with U = Ut - Wt S0^T.  A thread owns one of the
-// 128 + 128 right-hand-side columns and keeps its 64 unknowns in registers.
-constexpr int LDA4 = CH + 4;  // fp32 [64][64] tile, rows 16-byte aligned
+//   L Wt = diag(beta gamma) K                                               -> w_tilde (bf16)
+//   L Ut = diag(beta) V                                                     -> v_io in place (fp32)
+// so that the serial kernel is left with U = Ut - Wt S0^T.  The two triangular solves are
+// one blocked forward substitution over 16-row blocks with 256 right-hand-side columns:
+//   X_k = D_k (B_k - sum_{m<k} A_km X_m),   D_k = L_kk^-1 (16 x 16, by scalar substitution in fp32),
+// run transposed (rows = right-hand-side columns) so that the accumulator fragments of X_m^T
+// are directly the A operand of the next product; a warp owns 32 of the columns and never
+// synchronises with the others inside the solve.  fp32 operands enter mma.sync m16n8k16 as
+// two-piece bf16 expansions (hi + mid, three products each), which keeps ~2^-17 relative.
+constexpr int LDM = CH + 8;        // bf16 [64][64] tiles
+constexpr int LDV = GDN_DIM + 4;   // fp32 [64][128] tile: rows 16-byte aligned, conflict-free column walks
 struct IntraSmem {
-    __nv_bfloat16 K[CH][LDK];
+    __nv_bfloat16 K[CH][LDK];      // k^ of the chunk; overwritten in place by Wt
     __nv_bfloat16 Q[CH][LDK];
-    float A[CH][LDA4];
-    float V[CH][GDN_DIM];
+    float V[CH][LDV];              // v of this head; overwritten in place by Ut
+    float Ad[4][16][17];           // diagonal 16 x 16 blocks of A, fp32
+    __nv_bfloat16 Mh[CH][LDM];     // hi parts: block (k, m < k) = -A_km, block (k, k) = D_k
+    __nv_bfloat16 Mm[CH][LDM];     // mid parts of the same
     float lg[CH];
     float bt[CH];
 };
@@ -289,75 +261,156 @@ gdn_prefill_intra_kernel(const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat,
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
 
-    // ---- A and Wm: warp = (16-token row tile, 32-column half) ----
+    // ---- A and Wm: warp = (16-token row tile mt, 32-column half nh); blocks above the diagonal are skipped ----
     {
         const int mt = warp & 3, nh = warp >> 2;
         const int r0 = 16 * mt + g, r1 = r0 + 8;
-        const float lg0 = sm.lg[r0], lg1 = sm.lg[r1], b0 = sm.bt[r0], b1 = sm.bt[r1];
-        float acc[4][4], acq[4][4];
-#pragma unroll
-        for (int n = 0; n < 4; n++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) acc[n][e] = acq[n][e] = 0.0f;
-        warp_gemm2_nmajor<4, 8>(acc, acq, &sm.K[16 * mt][0], &sm.Q[16 * mt][0], LDK, &sm.K[32 * nh][0], LDK, lane);
         const bool in0 = tok0 + r0 < T, in1 = tok0 + r1 < T;
+        if (32 * nh <= 16 * mt + 15) {
+            const float lg0 = sm.lg[r0], lg1 = sm.lg[r1], b0 = sm.bt[r0], b1 = sm.bt[r1];
+            float acc[4][4], acq[4][4];
 #pragma unroll
-        for (int n = 0; n < 4; n++) {
-            const int col = 32 * nh + 8 * n + 2 * t4;
-            const float d00 = ex2_approx(lg0 - sm.lg[col]), d01 = ex2_approx(lg0 - sm.lg[col + 1]);
-            const float d10 = ex2_approx(lg1 - sm.lg[col]), d11 = ex2_approx(lg1 - sm.lg[col + 1]);
-            sm.A[r0][col] = (col < r0) ? b0 * d00 * acc[n][0] : 0.0f;
-            sm.A[r0][col + 1] = (col + 1 < r0) ? b0 * d01 * acc[n][1] : 0.0f;
-            sm.A[r1][col] = (col < r1) ? b1 * d10 * acc[n][2] : 0.0f;
-            sm.A[r1][col + 1] = (col + 1 < r1) ? b1 * d11 * acc[n][3] : 0.0f;
-            if (in0)
-                *reinterpret_cast<uint32_t *>(&w_mask[((size_t)(tok0 + r0) * Hv + h) * CH + col]) =
-                    pack_bf16x2((col <= r0) ? d00 * acq[n][0] : 0.0f, (col + 1 <= r0) ? d01 * acq[n][1] : 0.0f);
-            if (in1)
-                *reinterpret_cast<uint32_t *>(&w_mask[((size_t)(tok0 + r1) * Hv + h) * CH + col]) =
-                    pack_bf16x2((col <= r1) ? d10 * acq[n][2] : 0.0f, (col + 1 <= r1) ? d11 * acq[n][3] : 0.0f);
+            for (int n = 0; n < 4; n++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[n][e] = acq[n][e] = 0.0f;
+            warp_gemm2_nmajor<4, 8>(acc, acq, &sm.K[16 * mt][0], &sm.Q[16 * mt][0], LDK, &sm.K[32 * nh][0], LDK, lane);
+#pragma unroll
+            for (int n = 0; n < 4; n++) {
+                const int col = 32 * nh + 8 * n + 2 * t4;  // even: col and col+1 lie in the same 16-block
+                const float d00 = ex2_approx(lg0 - sm.lg[col]), d01 = ex2_approx(lg0 - sm.lg[col + 1]);
+                const float d10 = ex2_approx(lg1 - sm.lg[col]), d11 = ex2_approx(lg1 - sm.lg[col + 1]);
+                const float a00 = (col < r0) ? b0 * d00 * acc[n][0] : 0.0f, a01 = (col + 1 < r0) ? b0 * d01 * acc[n][1] : 0.0f;
+                const float a10 = (col < r1) ? b1 * d10 * acc[n][2] : 0.0f, a11 = (col + 1 < r1) ? b1 * d11 * acc[n][3] : 0.0f;
+                if ((col >> 4) == mt) {  // diagonal block (r0 and r1 are in block mt): kept in fp32
+                    sm.Ad[mt][r0 & 15][col & 15] = a00;
+                    sm.Ad[mt][r0 & 15][(col & 15) + 1] = a01;
+                    sm.Ad[mt][r1 & 15][col & 15] = a10;
+                    sm.Ad[mt][r1 & 15][(col & 15) + 1] = a11;
+                } else if ((col >> 4) < mt) {
+                    uint32_t hi, mid;
+                    split_bf16x2(-a00, -a01, hi, mid);
+                    *reinterpret_cast<uint32_t *>(&sm.Mh[r0][col]) = hi;
+                    *reinterpret_cast<uint32_t *>(&sm.Mm[r0][col]) = mid;
+                    split_bf16x2(-a10, -a11, hi, mid);
+                    *reinterpret_cast<uint32_t *>(&sm.Mh[r1][col]) = hi;
+                    *reinterpret_cast<uint32_t *>(&sm.Mm[r1][col]) = mid;
+                }
+                if (in0)
+                    *reinterpret_cast<uint32_t *>(&w_mask[((size_t)(tok0 + r0) * Hv + h) * CH + col]) =
+                        pack_bf16x2((col <= r0) ? d00 * acq[n][0] : 0.0f, (col + 1 <= r0) ? d01 * acq[n][1] : 0.0f);
+                if (in1)
+                    *reinterpret_cast<uint32_t *>(&w_mask[((size_t)(tok0 + r1) * Hv + h) * CH + col]) =
+                        pack_bf16x2((col <= r1) ? d10 * acq[n][2] : 0.0f, (col + 1 <= r1) ? d11 * acq[n][3] : 0.0f);
+            }
+        } else {  // nothing to the right of the diagonal: Wm is zero there
+#pragma unroll
+            for (int n = 0; n < 4; n++) {
+                const int col = 32 * nh + 8 * n + 2 * t4;
+                if (in0) *reinterpret_cast<uint32_t *>(&w_mask[((size_t)(tok0 + r0) * Hv + h) * CH + col]) = 0u;
+                if (in1) *reinterpret_cast<uint32_t *>(&w_mask[((size_t)(tok0 + r1) * Hv + h) * CH + col]) = 0u;
+            }
         }
     }
     __syncthreads();
 
-    // ---- forward substitution, one right-hand-side column per thread ----
-    {
-        const int col = tid & 127;
-        const bool is_v = tid >= 128;  // warp-uniform
-        float u[CH];
-        if (is_v) {
+    // ---- D_k = (I + A_kk)^-1: thread = (block k, column c), 16-step substitution in fp32 ----
+    if (tid < 64) {
+        const int k = tid >> 4, c = tid & 15;
+        float x[16];
 #pragma unroll
-            for (int t = 0; t < CH; t++) u[t] = sm.bt[t] * sm.V[t][col];
-        } else {
+        for (int i = 0; i < 16; i++) {
+            float s = (i == c) ? 1.0f : 0.0f;
 #pragma unroll
-            for (int t = 0; t < CH; t++) u[t] = sm.bt[t] * ex2_approx(sm.lg[t]) * __bfloat162float(sm.K[t][col]);
+            for (int jj = 0; jj < i; jj++) s = fmaf(-sm.Ad[k][i][jj], x[jj], s);
+            x[i] = s;
         }
 #pragma unroll
-        for (int t = 1; t < CH; t++) {
-            // A[t][i] is zero for i >= t, so whole groups of four can be taken; four partial sums keep the chain short
-            float s0 = u[t], s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        for (int i = 0; i < 16; i++) {
+            const __nv_bfloat16 hi = __float2bfloat16_rn(x[i]);
+            sm.Mh[16 * k + i][16 * k + c] = hi;
+            sm.Mm[16 * k + i][16 * k + c] = __float2bfloat16_rn(x[i] - __bfloat162float(hi));
+        }
+    }
+    __syncthreads();
+
+    // ---- blocked forward substitution, transposed: a warp owns right-hand-side columns
+    //      [16 warp, 16 warp + 16) of diag(beta gamma) K and the same columns of diag(beta) V ----
+#pragma unroll 1
+    for (int which = 0; which < 2; which++) {
+        const int n0 = 16 * warp;  // this warp's 16 columns; fragment rows g and g+8 are columns n0+g, n0+g+8
+        uint32_t xh[3][4], xm[3][4];
 #pragma unroll
-            for (int i = 0; i < t; i += 4) {
-                const float4 a = *reinterpret_cast<const float4 *>(&sm.A[t][i]);
-                s0 = fmaf(-a.x, u[i], s0);
-                s1 = fmaf(-a.y, u[i + 1], s1);
-                s2 = fmaf(-a.z, u[i + 2], s2);
-                s3 = fmaf(-a.w, u[i + 3], s3);
+        for (int k = 0; k < 4; k++) {
+            float acc[2][4];
+#pragma unroll
+            for (int jn = 0; jn < 2; jn++) {
+                const int t = 16 * k + 8 * jn + 2 * t4;
+                if (which == 0) {
+                    const float f0 = sm.bt[t] * ex2_approx(sm.lg[t]), f1 = sm.bt[t + 1] * ex2_approx(sm.lg[t + 1]);
+                    acc[jn][0] = f0 * __bfloat162float(sm.K[t][n0 + g]);
+                    acc[jn][1] = f1 * __bfloat162float(sm.K[t + 1][n0 + g]);
+                    acc[jn][2] = f0 * __bfloat162float(sm.K[t][n0 + g + 8]);
+                    acc[jn][3] = f1 * __bfloat162float(sm.K[t + 1][n0 + g + 8]);
+                } else {
+                    const float f0 = sm.bt[t], f1 = sm.bt[t + 1];
+                    acc[jn][0] = f0 * sm.V[t][n0 + g];
+                    acc[jn][1] = f1 * sm.V[t + 1][n0 + g];
+                    acc[jn][2] = f0 * sm.V[t][n0 + g + 8];
+                    acc[jn][3] = f1 * sm.V[t + 1][n0 + g + 8];
+                }
             }
-            u[t] = (s0 + s1) + (s2 + s3);
-        }
-        const int n_in = min(CH, T - tok0);
-        if (is_v) {
-            float *dst = v_io + (size_t)tok0 * vrow + (size_t)h * GDN_DIM + col;
 #pragma unroll
-            for (int t = 0; t < CH; t++)
-                if (t < n_in) dst[(size_t)t * vrow] = u[t];
-        } else {
-            __nv_bfloat16 *dst = w_tilde + ((size_t)tok0 * Hv + h) * GDN_DIM + col;
+            for (int m = 0; m < k; m++)
+                mma_block_split(acc, xh[m], xm[m], &sm.Mh[16 * k][16 * m], &sm.Mm[16 * k][16 * m], LDM, lane);
+            // Y^T (accumulator fragments) -> A fragments, then X_k^T = Y^T D_k^T
+            uint32_t yh[4], ym[4];
+            split_bf16x2(acc[0][0], acc[0][1], yh[0], ym[0]);
+            split_bf16x2(acc[0][2], acc[0][3], yh[1], ym[1]);
+            split_bf16x2(acc[1][0], acc[1][1], yh[2], ym[2]);
+            split_bf16x2(acc[1][2], acc[1][3], yh[3], ym[3]);
+            float out[2][4];
 #pragma unroll
-            for (int t = 0; t < CH; t++)
-                if (t < n_in) dst[(size_t)t * vrow] = __float2bfloat16_rn(u[t]);
+            for (int jn = 0; jn < 2; jn++) out[jn][0] = out[jn][1] = out[jn][2] = out[jn][3] = 0.0f;
+            mma_block_split(out, yh, ym, &sm.Mh[16 * k][16 * k], &sm.Mm[16 * k][16 * k], LDM, lane);
+            if (k < 3) {
+                split_bf16x2(out[0][0], out[0][1], xh[k][0], xm[k][0]);
+                split_bf16x2(out[0][2], out[0][3], xh[k][1], xm[k][1]);
+                split_bf16x2(out[1][0], out[1][1], xh[k][2], xm[k][2]);
+                split_bf16x2(out[1][2], out[1][3], xh[k][3], xm[k][3]);
+            }
+            // in place: element (t, column) is read and written by this thread only
+#pragma unroll
+            for (int jn = 0; jn < 2; jn++) {
+                const int t = 16 * k + 8 * jn + 2 * t4;
+                if (which == 0) {
+                    sm.K[t][n0 + g] = __float2bfloat16_rn(out[jn][0]);
+                    sm.K[t + 1][n0 + g] = __float2bfloat16_rn(out[jn][1]);
+                    sm.K[t][n0 + g + 8] = __float2bfloat16_rn(out[jn][2]);
+                    sm.K[t + 1][n0 + g + 8] = __float2bfloat16_rn(out[jn][3]);
+                } else {
+                    sm.V[t][n0 + g] = out[jn][0];
+                    sm.V[t + 1][n0 + g] = out[jn][1];
+                    sm.V[t][n0 + g + 8] = out[jn][2];
+                    sm.V[t + 1][n0 + g + 8] = out[jn][3];
+                }
+            }
         }
+    }
+    __syncthreads();
+
+    // ---- copy out: Wt (bf16) and Ut (fp32), 16-byte stores, valid rows only ----
+    const int n_in = min(CH, T - tok0);
+    for (int i = tid; i < CH * (GDN_DIM / 8); i += 256) {
+        const int r = i >> 4, col = (i & 15) * 8;
+        if (r < n_in)
+            *reinterpret_cast<uint4 *>(w_tilde + ((size_t)(tok0 + r) * Hv + h) * GDN_DIM + col) =
+                *reinterpret_cast<const uint4 *>(&sm.K[r][col]);
+    }
+    for (int i = tid; i < CH * (GDN_DIM / 4); i += 256) {
+        const int r = i >> 5, col = (i & 31) * 4;
+        if (r < n_in)
+            *reinterpret_cast<float4 *>(v_io + (size_t)(tok0 + r) * vrow + (size_t)h * GDN_DIM + col) =
+                *reinterpret_cast<const float4 *>(&sm.V[r][col]);
     }
 }
 
