@@ -196,16 +196,20 @@ constexpr int LDM = CH + 8;        // bf16 [64][64] tiles
 constexpr int LDV = GDN_DIM + 4;   // fp32 [64][128] tile: rows 16-byte aligned, conflict-free column walks
 struct IntraSmem {
     __nv_bfloat16 K[CH][LDK];      // k^ of the chunk; overwritten in place by Wt
-    __nv_bfloat16 Q[CH][LDK];
+    union {
+        __nv_bfloat16 Q[CH][LDK];  // q^ of the chunk, dead once the products with k^ are in registers
+        struct {
+            __nv_bfloat16 Mh[CH][LDM];  // hi parts: block (k, m < k) = -A_km, block (k, k) = D_k
+            __nv_bfloat16 Mm[CH][LDM];  // mid parts of the same
+        };
+    };
     float V[CH][LDV];              // v of this head; overwritten in place by Ut
     float Ad[4][16][17];           // diagonal 16 x 16 blocks of A, fp32
-    __nv_bfloat16 Mh[CH][LDM];     // hi parts: block (k, m < k) = -A_km, block (k, k) = D_k
-    __nv_bfloat16 Mm[CH][LDM];     // mid parts of the same
     float lg[CH];
     float bt[CH];
 };
 
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, 3)
 gdn_prefill_intra_kernel(const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat, float *v_io, float *lg_io,
                          const float *beta_in, __nv_bfloat16 *w_tilde, __nv_bfloat16 *w_mask, int T, int Hk, int Hv) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -266,14 +270,17 @@ gdn_prefill_intra_kernel(const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat,
         const int mt = warp & 3, nh = warp >> 2;
         const int r0 = 16 * mt + g, r1 = r0 + 8;
         const bool in0 = tok0 + r0 < T, in1 = tok0 + r1 < T;
-        if (32 * nh <= 16 * mt + 15) {
-            const float lg0 = sm.lg[r0], lg1 = sm.lg[r1], b0 = sm.bt[r0], b1 = sm.bt[r1];
-            float acc[4][4], acq[4][4];
+        const bool active = 32 * nh <= 16 * mt + 15;
+        float acc[4][4], acq[4][4];
 #pragma unroll
-            for (int n = 0; n < 4; n++)
+        for (int n = 0; n < 4; n++)
 #pragma unroll
-                for (int e = 0; e < 4; e++) acc[n][e] = acq[n][e] = 0.0f;
+            for (int e = 0; e < 4; e++) acc[n][e] = acq[n][e] = 0.0f;
+        if (active)
             warp_gemm2_nmajor<4, 8>(acc, acq, &sm.K[16 * mt][0], &sm.Q[16 * mt][0], LDK, &sm.K[32 * nh][0], LDK, lane);
+        __syncthreads();  // q^ has been consumed: its memory now takes the M tiles
+        if (active) {
+            const float lg0 = sm.lg[r0], lg1 = sm.lg[r1], b0 = sm.bt[r0], b1 = sm.bt[r1];
 #pragma unroll
             for (int n = 0; n < 4; n++) {
                 const int col = 32 * nh + 8 * n + 2 * t4;  // even: col and col+1 lie in the same 16-block
