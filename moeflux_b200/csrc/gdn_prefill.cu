@@ -422,19 +422,21 @@ gdn_prefill_intra_kernel(const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat,
 }
 
 // ------------------------------------------------------------------ 2b. the serial part: state across chunks
-// grid 2*Hv, 160 threads.  One CTA owns 64 of the 128 value rows of one v-head and keeps
+// grid 2*Hv, 288 threads.  One CTA owns 64 of the 128 value rows of one v-head and keeps
 // that half-state, transposed (key index = TMEM lane, value row = column), in tensor
 // memory in fp32 across all chunks.  Per chunk, three groups of tcgen05.mma (M = 128,
 // N = 64, bf16 operands, fp32 accumulate):
 //   D1 = [Wt ; Q] S0^T          rows 0-63: Wt S0^T, rows 64-127: Q S0^T        (K = 128 key dims)
-//   D2 = [ . ; Wm] U            rows 64-127: Wm U                              (K = 64 tokens)
 //   ST = gamma_C ST + K^T Us    Us = diag(gamma_C/gamma_t) U                   (K = 64 tokens)
-// with U = Ut - D1[0:64] and O = diag(gamma) D1[64:128] + D2[64:128] computed by the four
-// epilogue warps (thread = TMEM lane).  Operands arrive by TMA (128-byte swizzle) into a
-// two-stage ring; S0 (bf16), U and Us are written to shared memory by the epilogue warps
-// as MN-major operands, one 128-byte row per thread.  Warp 4 issues every TMA load and
-// every MMA.  Every mbarrier wait is bounded; a wait that expires sets a status bit and
-// the CTA frees its TMEM and leaves.
+//   D2 = [ . ; Wm] U            rows 64-127: Wm U                              (K = 64 tokens)
+// with U = Ut - D1[0:64] and O = diag(gamma) D1[64:128] + D2[64:128] computed by eight
+// epilogue warps (thread = TMEM lane x half of the 64 columns).  Operands arrive by TMA
+// (128-byte swizzle) into a two-stage ring; S0 (bf16), U and Us are written to shared
+// memory by the epilogue warps as MN-major operands.  Warp 8 issues every TMA load and
+// every MMA.  The recurrence S0 -> D1 -> U -> ST -> S0 is the critical path; the read-out
+// (D2, O) of chunk c is finished under the first product of chunk c+1.  Every mbarrier
+// wait is bounded; a wait that expires sets a status bit and the CTA frees its TMEM and
+// leaves.
 constexpr uint32_t ST_A1 = 0;                    // [2 boxes][128 rows][128 B]: rows 0-63 Wt, rows 64-127 q^
 constexpr uint32_t ST_K = ST_A1 + 32768;         // [2 boxes][64 rows][128 B]
 constexpr uint32_t ST_WM = ST_K + 16384;         // [64 rows][128 B]
@@ -449,11 +451,12 @@ constexpr uint32_t TC_OFF_BAR = TC_OFF_US + 8192;
 constexpr uint32_t TC_SMEM = TC_OFF_BAR + 128 + 1024;
 constexpr uint32_t TC_TMEM_COLS = 256;
 constexpr uint32_t TM_ST = 0, TM_D1 = 64, TM_D2 = 128;
+constexpr int TC_THREADS = 288;
 
 // address of 16-byte chunk c of row r in a [rows][128 B] region laid out with the 128-byte swizzle
 __device__ __forceinline__ uint8_t *sw128_chunk(uint8_t *base, int r, int c) { return base + r * 128 + ((c ^ (r & 7)) << 4); }
 
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __grid_constant__ CUtensorMap q_map,
                          const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap wm_map,
                          const __grid_constant__ CUtensorMap ut_map, float *ssm, float *v_io, const float *lgc, int T,
@@ -465,12 +468,14 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
     uint64_t *d1_ready = bars + 2;  // tcgen05.commit
     uint64_t *d2_ready = bars + 3;  // tcgen05.commit
     uint64_t *g3_done = bars + 4;   // tcgen05.commit: the state update of a chunk has been accumulated
-    uint64_t *u_ready = bars + 5;   // 64 arrivals: U and Us are in shared memory, D1[0:64] and Ut have been read
-    uint64_t *s_ready = bars + 6;   // 128 arrivals: S0 (bf16) is in shared memory, ST is scaled, D1/D2 have been read
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
-    volatile int *s_fail = reinterpret_cast<volatile int *>(bars + 8);
+    uint64_t *u_ready = bars + 5;   // 128 arrivals: U and Us are in shared memory, D1[0:64] and Ut have been read
+    uint64_t *s_ready = bars + 6;   // 256 arrivals: S0 (bf16) is in shared memory, D1 has been read
+    uint64_t *st_ready = bars + 7;  // 256 arrivals: ST has been scaled by the decay of the coming chunk
+    uint64_t *o_done = bars + 8;    // 128 arrivals: D2 of the previous chunk has been read
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
+    volatile int *s_fail = reinterpret_cast<volatile int *>(bars + 10);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane_id = tid & 31;
     const int h = blockIdx.x >> 1, half = blockIdx.x & 1;
     const int j = h / (Hv / Hk);
     const size_t vrow = (size_t)Hv * GDN_DIM;
@@ -489,8 +494,10 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
         mbar_init(d1_ready, 1);
         mbar_init(d2_ready, 1);
         mbar_init(g3_done, 1);
-        mbar_init(u_ready, 64);
-        mbar_init(s_ready, 128);
+        mbar_init(u_ready, 128);
+        mbar_init(s_ready, 256);
+        mbar_init(st_ready, 256);
+        mbar_init(o_done, 128);
         *s_fail = 0;
         mbar_fence_init();
     }
@@ -505,9 +512,9 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
     bool ok = true;
     auto lg_at = [&](int tok) { return lgc[(size_t)min(tok, T - 1) * Hv + h]; };
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ================= issuer: one lane drives TMA and the tensor core =================
-        if ((tid & 31) == 0) {
+        if (lane_id == 0) {
             auto load_a = [&](int cc) {  // Wt, q^ and Ut of chunk cc
                 uint8_t *st = smem + (cc & 1) * STAGE_BYTES;
                 uint64_t *bar = &full[cc & 1];
@@ -545,8 +552,6 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                 const unsigned par = (unsigned)c & 1u;
                 ok = mbar_wait_bounded(&full[c & 1], (unsigned)(c >> 1) & 1u) && mbar_wait_bounded(s_ready, par);
                 if (!ok) break;
-                // the other stage held chunk c-1, whose last reader (the state update) completed before s_ready
-                if (c >= 1 && c + 1 < n_chunks) load_b(c + 1);
                 tc_fence_after();
                 {
                     const uint64_t a1 = smem_desc_sw128(st + ST_A1, 16, 1024);
@@ -556,10 +561,30 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                                     sb_desc + (uint64_t)((ks * 2048) >> 4), IDESC_KN, ks > 0);
                     tc_commit(d1_ready);
                 }
+                // the other stage held chunk c-1: k^ was last read by its state update (complete before s_ready),
+                // Wm by its read-out product
+                if (c >= 1 && c + 1 < n_chunks) {
+                    ok = mbar_wait_bounded(d2_ready, (unsigned)(c - 1) & 1u);
+                    if (!ok) break;
+                    load_b(c + 1);
+                }
                 ok = mbar_wait_bounded(u_ready, par);
                 if (!ok) break;
                 // Wt, q^ (read by the MMAs above, complete since D1 was read) and Ut of this stage are free
                 if (c + 2 < n_chunks) load_a(c + 2);
+                ok = mbar_wait_bounded(st_ready, par);
+                if (!ok) break;
+                tc_fence_after();
+                {
+                    const uint64_t kd = smem_desc_sw128(st + ST_K, 8192, 1024);  // m = key dim: two 64-wide atoms 8 KiB apart
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        tc_mma_bf16(tmem + TM_ST, kd + (uint64_t)((ks * 2048) >> 4), us_desc + (uint64_t)((ks * 2048) >> 4),
+                                    IDESC_MN, 1);
+                    tc_commit(g3_done);
+                }
+                ok = mbar_wait_bounded(o_done, par);  // D2 of chunk c-1 has been read
+                if (!ok) break;
                 tc_fence_after();
                 {
                     // rows 0-63 of this A operand are the 8 KiB in front of Wm (finite k^ data); only rows 64-127 of D2 are used
@@ -569,135 +594,143 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                         tc_mma_bf16(tmem + TM_D2, wm + (uint64_t)((ks * 32) >> 4), u_desc + (uint64_t)((ks * 2048) >> 4),
                                     IDESC_KN, ks > 0);
                     tc_commit(d2_ready);
-                    const uint64_t kd = smem_desc_sw128(st + ST_K, 8192, 1024);  // m = key dim: two 64-wide atoms 8 KiB apart
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++)
-                        tc_mma_bf16(tmem + TM_ST, kd + (uint64_t)((ks * 2048) >> 4), us_desc + (uint64_t)((ks * 2048) >> 4),
-                                    IDESC_MN, 1);
-                    tc_commit(g3_done);
                 }
             }
             if (!ok) *s_fail = 1;
         }
     } else {
-        // ================= epilogue warps: thread = TMEM lane =================
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        const int r = tid & 63;  // token row of this thread in D1 / D2 (warps 0-1: U rows, warps 2-3: O rows)
-        // ---- initial state: column tid of S (key dim) over the 64 value rows ----
+        // ================= epilogue warps: thread = (TMEM lane, half of the 64 columns) =================
+        const int quad = warp & 3, ch = warp >> 2;       // lane quadrant, column half
+        const int lane = 32 * quad + lane_id;            // TMEM lane = key dim of ST / row of D1, D2
+        const int r = lane & 63;                         // token row in D1 / D2 (quadrants 0-1: U rows, 2-3: O rows)
+        const uint32_t lane_base = tmem + ((uint32_t)(32 * quad) << 16) + 32 * ch;
+        const bool u_role = quad < 2;
+        // ---- initial state: element (key dim = lane) of value rows 32 ch .. 32 ch + 31 ----
         {
-            float sv[DVC];
+            float sv[32];
 #pragma unroll
-            for (int d = 0; d < DVC; d++) sv[d] = Sg[(size_t)d * GDN_DIM + tid];
-            const float g0 = ex2_approx(lg_at(CH - 1));
+            for (int d = 0; d < 32; d++) sv[d] = Sg[(size_t)(32 * ch + d) * GDN_DIM + lane];
 #pragma unroll
-            for (int cch = 0; cch < 8; cch++) {
+            for (int cc = 0; cc < 4; cc++) {
                 uint32_t w[4];
 #pragma unroll
-                for (int e = 0; e < 4; e++) w[e] = pack_bf16x2(sv[8 * cch + 2 * e], sv[8 * cch + 2 * e + 1]);
-                *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_SB, tid, cch)) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int e = 0; e < 4; e++) w[e] = pack_bf16x2(sv[8 * cc + 2 * e], sv[8 * cc + 2 * e + 1]);
+                *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_SB, lane, 4 * ch + cc)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-#pragma unroll
-            for (int d = 0; d < DVC; d++) sv[d] *= g0;
-            tmem_st32(lane_base + TM_ST, *reinterpret_cast<float(*)[32]>(&sv[0]));
-            tmem_st32(lane_base + TM_ST + 32, *reinterpret_cast<float(*)[32]>(&sv[32]));
-            tc_wait_st();
             fence_proxy_async_smem();
-            tc_fence_before();
             mbar_arrive(s_ready);
+            const float g0 = ex2_approx(lg_at(CH - 1));
+#pragma unroll
+            for (int d = 0; d < 32; d++) sv[d] *= g0;
+            tmem_st32(lane_base + TM_ST, *reinterpret_cast<float(*)[32]>(&sv[0]));
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(st_ready);
         }
         float lg_r = lg_at(r), lg_c = lg_at(CH - 1);
+        float o1[32];  // O rows: gamma_t (Q S0^T) of the chunk whose read-out is still open
+        // finishes the read-out of chunk cc: O = o1 + D2 -> written over v_io (fp32)
+        auto finish_o = [&](int cc) -> bool {
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(d2_ready, (unsigned)cc & 1u))) return false;
+            tc_fence_after();
+            float d2[32];
+            tmem_ld32(lane_base + TM_D2, d2);
+            tc_wait_ld();
+            const int tok = cc * CH + r;
+            if (tok < T) {
+                float *dst = v_io + (size_t)tok * vrow + vcol0 + 32 * ch;
+#pragma unroll
+                for (int q4 = 0; q4 < 8; q4++)
+                    *reinterpret_cast<float4 *>(dst + 4 * q4) =
+                        make_float4(o1[4 * q4] + d2[4 * q4], o1[4 * q4 + 1] + d2[4 * q4 + 1], o1[4 * q4 + 2] + d2[4 * q4 + 2],
+                                    o1[4 * q4 + 3] + d2[4 * q4 + 3]);
+            }
+            return true;
+        };
         for (int c = 0; c < n_chunks && ok; c++) {
             uint8_t *st = smem + (c & 1) * STAGE_BYTES;
             const unsigned par = (unsigned)c & 1u;
-            const int tok = c * CH + r;
             // decay logs of the next chunk, requested now
             const float lg_r_next = lg_at((c + 1) * CH + r), lg_c_next = lg_at((c + 1) * CH + CH - 1);
+            if (!u_role) {
+                if (c > 0) {
+                    ok = finish_o(c - 1);
+                    if (!ok) break;
+                }
+                tc_fence_before();
+                mbar_arrive(o_done);
+            } else if (c > 0) {
+                // U of chunk c-1 is still the operand of its read-out product until that has completed
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(d2_ready, (unsigned)(c - 1) & 1u));
+                if (!ok) break;
+            }
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(d1_ready, par) && *s_fail == 0);
             if (!ok) break;
             tc_fence_after();
-            float d1[DVC];
+            float d1[32];
             tmem_ld32(lane_base + TM_D1, d1);
-            tmem_ld32(lane_base + TM_D1 + 32, d1 + 32);
             tc_wait_ld();
-            if (warp < 2) {
-                // ---- U = Ut - Wt S0^T ; Us = (gamma_C/gamma_t) U ----
+            if (u_role) {
+                // ---- U = Ut - Wt S0^T ; Us = (gamma_C/gamma_t) U : value rows 32 ch .. 32 ch + 31 of token r ----
                 const float f = ex2_approx(lg_c - lg_r);
 #pragma unroll
-                for (int cch = 0; cch < 8; cch++) {
+                for (int cc = 0; cc < 4; cc++) {
                     uint32_t wu[4], ws[4];
 #pragma unroll
                     for (int e2 = 0; e2 < 2; e2++) {
-                        const int d0 = 8 * cch + 4 * e2;  // value row of the first of four floats
-                        const float4 ut = *reinterpret_cast<const float4 *>(
-                            sw128_chunk(st + ST_UT + (d0 >> 5) * 8192, r, (d0 & 31) >> 2));
+                        const int d0 = 8 * cc + 4 * e2;
+                        const float4 ut = *reinterpret_cast<const float4 *>(sw128_chunk(st + ST_UT + ch * 8192, r, d0 >> 2));
                         const float u0 = ut.x - d1[d0], u1 = ut.y - d1[d0 + 1], u2 = ut.z - d1[d0 + 2], u3 = ut.w - d1[d0 + 3];
                         wu[2 * e2] = pack_bf16x2(u0, u1);
                         wu[2 * e2 + 1] = pack_bf16x2(u2, u3);
                         ws[2 * e2] = pack_bf16x2(u0 * f, u1 * f);
                         ws[2 * e2 + 1] = pack_bf16x2(u2 * f, u3 * f);
                     }
-                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_U, r, cch)) = make_uint4(wu[0], wu[1], wu[2], wu[3]);
-                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_US, r, cch)) = make_uint4(ws[0], ws[1], ws[2], ws[3]);
+                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_U, r, 4 * ch + cc)) = make_uint4(wu[0], wu[1], wu[2], wu[3]);
+                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_US, r, 4 * ch + cc)) = make_uint4(ws[0], ws[1], ws[2], ws[3]);
                 }
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(u_ready);
             } else {
-                // ---- O = gamma_t Q S0^T + Wm U -> written over v_io (fp32) ----
                 const float e = ex2_approx(lg_r);
 #pragma unroll
-                for (int d = 0; d < DVC; d++) d1[d] *= e;
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(d2_ready, par));
-                if (!ok) break;
-                tc_fence_after();
-                float *dst = v_io + (size_t)tok * vrow + vcol0;
-#pragma unroll
-                for (int hb = 0; hb < 2; hb++) {
-                    float d2[32];
-                    tmem_ld32(lane_base + TM_D2 + 32 * hb, d2);
-                    tc_wait_ld();
-                    if (tok < T) {
-#pragma unroll
-                        for (int q4 = 0; q4 < 8; q4++)
-                            *reinterpret_cast<float4 *>(dst + 32 * hb + 4 * q4) =
-                                make_float4(d1[32 * hb + 4 * q4] + d2[4 * q4], d1[32 * hb + 4 * q4 + 1] + d2[4 * q4 + 1],
-                                            d1[32 * hb + 4 * q4 + 2] + d2[4 * q4 + 2], d1[32 * hb + 4 * q4 + 3] + d2[4 * q4 + 3]);
-                    }
-                }
+                for (int d = 0; d < 32; d++) o1[d] = d1[d] * e;
             }
-            // ---- state pass: S of this chunk -> bf16 operand copy, and the decay of the next chunk ----
+            // ---- state pass: S of this chunk -> bf16 operand copy; then the decay of the next chunk ----
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(g3_done, par));
             if (!ok) break;
             tc_fence_after();
-            float sv[DVC];
+            float sv[32];
             tmem_ld32(lane_base + TM_ST, sv);
-            tmem_ld32(lane_base + TM_ST + 32, sv + 32);
             tc_wait_ld();
             if (c + 1 < n_chunks) {
 #pragma unroll
-                for (int cch = 0; cch < 8; cch++) {
+                for (int cc = 0; cc < 4; cc++) {
                     uint32_t w[4];
 #pragma unroll
-                    for (int e = 0; e < 4; e++) w[e] = pack_bf16x2(sv[8 * cch + 2 * e], sv[8 * cch + 2 * e + 1]);
-                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_SB, tid, cch)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int e = 0; e < 4; e++) w[e] = pack_bf16x2(sv[8 * cc + 2 * e], sv[8 * cc + 2 * e + 1]);
+                    *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_SB, lane, 4 * ch + cc)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                const float gn = ex2_approx(lg_c_next);
-#pragma unroll
-                for (int d = 0; d < DVC; d++) sv[d] *= gn;
-                tmem_st32(lane_base + TM_ST, *reinterpret_cast<float(*)[32]>(&sv[0]));
-                tmem_st32(lane_base + TM_ST + 32, *reinterpret_cast<float(*)[32]>(&sv[32]));
-                tc_wait_st();
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(s_ready);
+                const float gn = ex2_approx(lg_c_next);
+#pragma unroll
+                for (int d = 0; d < 32; d++) sv[d] *= gn;
+                tmem_st32(lane_base + TM_ST, *reinterpret_cast<float(*)[32]>(&sv[0]));
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(st_ready);
             } else {
 #pragma unroll
-                for (int d = 0; d < DVC; d++) Sg[(size_t)d * GDN_DIM + tid] = sv[d];
+                for (int d = 0; d < 32; d++) Sg[(size_t)(32 * ch + d) * GDN_DIM + lane] = sv[d];
             }
             lg_r = lg_r_next;
             lg_c = lg_c_next;
         }
-        if (!ok && (tid & 31) == 0) *s_fail = 1;
+        if (ok && !u_role && n_chunks > 0) ok = finish_o(n_chunks - 1);
+        if (!ok && lane_id == 0) *s_fail = 1;
     }
     tc_fence_before();
     __syncthreads();
@@ -762,7 +795,7 @@ cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, const GdnPrefillMaps &
         p.beta_gate, reinterpret_cast<__nv_bfloat16 *>(p.w_tilde), reinterpret_cast<__nv_bfloat16 *>(p.w_mask), p.T, p.Hk,
         p.Hv);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    gdn_prefill_state_kernel<<<2 * p.Hv, 160, TC_SMEM, stream>>>(m.wt, m.q, m.k, m.wm, m.ut, p.ssm, p.v_io, p.lg, p.T, p.Hk,
+    gdn_prefill_state_kernel<<<2 * p.Hv, TC_THREADS, TC_SMEM, stream>>>(m.wt, m.q, m.k, m.wm, m.ut, p.ssm, p.v_io, p.lg, p.T, p.Hk,
                                                                p.Hv, p.status);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     gdn_prefill_out_kernel<<<(unsigned)p.T, 256, 0, stream>>>(p.v_io, reinterpret_cast<const __nv_bfloat16 *>(p.z), p.norm_w,
