@@ -431,20 +431,21 @@ gdn_prefill_intra_kernel(const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat,
 //   D2 = [ . ; Wm] U            rows 64-127: Wm U                              (K = 64 tokens)
 // with U = Ut - D1[0:64] and O = diag(gamma) D1[64:128] + D2[64:128] computed by eight
 // epilogue warps (thread = TMEM lane x half of the 64 columns).  Operands arrive by TMA
-// (128-byte swizzle) into a two-stage ring; S0 (bf16), U and Us are written to shared
+// (128-byte swizzle) into a ring (two stages for what a chunk needs first, three for the rest); S0 (bf16), U and Us are written to shared
 // memory by the epilogue warps as MN-major operands.  Warp 8 issues every TMA load and
 // every MMA.  The recurrence S0 -> D1 -> U -> ST -> S0 is the critical path; the read-out
 // (D2, O) of chunk c is finished under the first product of chunk c+1.  Every mbarrier
 // wait is bounded; a wait that expires sets a status bit and the CTA frees its TMEM and
 // leaves.
-constexpr uint32_t ST_A1 = 0;                    // [2 boxes][128 rows][128 B]: rows 0-63 Wt, rows 64-127 q^
-constexpr uint32_t ST_K = ST_A1 + 32768;         // [2 boxes][64 rows][128 B]
-constexpr uint32_t ST_WM = ST_K + 16384;         // [64 rows][128 B]
-constexpr uint32_t ST_UT = ST_WM + 8192;         // [2 boxes][64 rows][128 B] fp32
-constexpr uint32_t STAGE_BYTES = ST_UT + 16384;  // 72 KiB
-constexpr uint32_t LOAD_A_BYTES = 32768 + 16384;  // Wt, q^ and Ut
-constexpr uint32_t LOAD_B_BYTES = 16384 + 8192;   // k^ and Wm
-constexpr uint32_t TC_OFF_SB = 2 * STAGE_BYTES;   // [128 key rows][128 B]
+// operand ring: two A stages (Wt, q^, Ut: needed first in a chunk) and three B stages (k^, Wm: needed last)
+constexpr uint32_t SA_A1 = 0;                    // [2 boxes][128 rows][128 B]: rows 0-63 Wt, rows 64-127 q^
+constexpr uint32_t SA_UT = SA_A1 + 32768;        // [2 boxes][64 rows][128 B] fp32
+constexpr uint32_t STAGE_A_BYTES = SA_UT + 16384;  // 48 KiB
+constexpr uint32_t SB_K = 0;                     // [2 boxes][64 rows][128 B]
+constexpr uint32_t SB_WM = SB_K + 16384;         // [64 rows][128 B]
+constexpr uint32_t STAGE_B_BYTES = SB_WM + 8192;   // 24 KiB
+constexpr uint32_t TC_OFF_B = 2 * STAGE_A_BYTES;
+constexpr uint32_t TC_OFF_SB = TC_OFF_B + 3 * STAGE_B_BYTES;  // [128 key rows][128 B]
 constexpr uint32_t TC_OFF_U = TC_OFF_SB + 16384;  // [64 token rows][128 B]
 constexpr uint32_t TC_OFF_US = TC_OFF_U + 8192;
 constexpr uint32_t TC_OFF_BAR = TC_OFF_US + 8192;
@@ -453,6 +454,11 @@ constexpr uint32_t TC_TMEM_COLS = 256;
 constexpr uint32_t TM_ST = 0, TM_D1 = 64, TM_D2 = 128;
 constexpr int TC_THREADS = 288;
 
+// one arrival for the whole warp, after every lane's earlier writes and fences
+__device__ __forceinline__ void warp_arrive(uint64_t *bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 // address of 16-byte chunk c of row r in a [rows][128 B] region laid out with the 128-byte swizzle
 __device__ __forceinline__ uint8_t *sw128_chunk(uint8_t *base, int r, int c) { return base + r * 128 + ((c ^ (r & 7)) << 4); }
 
@@ -464,16 +470,19 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_OFF_BAR);
-    uint64_t *full = bars + 0;      // [2] TMA: a stage has landed (two arrivals: the A part and the B part)
-    uint64_t *d1_ready = bars + 2;  // tcgen05.commit
-    uint64_t *d2_ready = bars + 3;  // tcgen05.commit
-    uint64_t *g3_done = bars + 4;   // tcgen05.commit: the state update of a chunk has been accumulated
-    uint64_t *u_ready = bars + 5;   // 128 arrivals: U and Us are in shared memory, D1[0:64] and Ut have been read
-    uint64_t *s_ready = bars + 6;   // 256 arrivals: S0 (bf16) is in shared memory, D1 has been read
-    uint64_t *st_ready = bars + 7;  // 256 arrivals: ST has been scaled by the decay of the coming chunk
-    uint64_t *o_done = bars + 8;    // 128 arrivals: D2 of the previous chunk has been read
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
-    volatile int *s_fail = reinterpret_cast<volatile int *>(bars + 10);
+    uint64_t *full_a = bars + 0;    // [2] TMA: an A stage has landed
+    uint64_t *full_b = bars + 2;    // [3] TMA: a B stage has landed
+    uint64_t *d1_ready = bars + 5;  // tcgen05.commit
+    uint64_t *d2_ready = bars + 6;  // tcgen05.commit
+    uint64_t *g3_done = bars + 7;   // tcgen05.commit: the state update of a chunk has been accumulated
+    // the next four are arrived on once per warp (lane 0, after __syncwarp): hundreds of per-thread arrivals on
+    // one barrier serialise in the shared-memory unit and were the larger part of a chunk's latency
+    uint64_t *u_ready = bars + 8;   // 4 warps: U and Us are in shared memory, D1[0:64] and Ut have been read
+    uint64_t *s_ready = bars + 9;   // 8 warps: S0 (bf16) is in shared memory, D1 has been read
+    uint64_t *st_ready = bars + 10; // 8 warps: ST has been scaled by the decay of the coming chunk
+    uint64_t *o_done = bars + 11;   // 4 warps: D2 of the previous chunk has been read
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
+    volatile int *s_fail = reinterpret_cast<volatile int *>(bars + 13);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane_id = tid & 31;
     const int h = blockIdx.x >> 1, half = blockIdx.x & 1;
@@ -489,15 +498,14 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
         prefetch_tmap(&k_map);
         prefetch_tmap(&wm_map);
         prefetch_tmap(&ut_map);
-        mbar_init(&full[0], 2);
-        mbar_init(&full[1], 2);
+        for (int i = 0; i < 5; i++) mbar_init(&bars[i], 1);
         mbar_init(d1_ready, 1);
         mbar_init(d2_ready, 1);
         mbar_init(g3_done, 1);
-        mbar_init(u_ready, 128);
-        mbar_init(s_ready, 256);
-        mbar_init(st_ready, 256);
-        mbar_init(o_done, 128);
+        mbar_init(u_ready, 4);
+        mbar_init(s_ready, 8);
+        mbar_init(st_ready, 8);
+        mbar_init(o_done, 4);
         *s_fail = 0;
         mbar_fence_init();
     }
@@ -516,23 +524,23 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
         // ================= issuer: one lane drives TMA and the tensor core =================
         if (lane_id == 0) {
             auto load_a = [&](int cc) {  // Wt, q^ and Ut of chunk cc
-                uint8_t *st = smem + (cc & 1) * STAGE_BYTES;
-                uint64_t *bar = &full[cc & 1];
-                mbar_expect_tx(bar, LOAD_A_BYTES);
+                uint8_t *st = smem + (cc & 1) * STAGE_A_BYTES;
+                uint64_t *bar = &full_a[cc & 1];
+                mbar_expect_tx(bar, STAGE_A_BYTES);
 #pragma unroll
                 for (int b = 0; b < 2; b++) {
-                    tma_load_2d(st + ST_A1 + b * 16384, &wt_map, h * GDN_DIM + b * 64, cc * CH, bar);
-                    tma_load_2d(st + ST_A1 + b * 16384 + 8192, &q_map, j * GDN_DIM + b * 64, cc * CH, bar);
-                    tma_load_2d(st + ST_UT + b * 8192, &ut_map, vcol0 + b * 32, cc * CH, bar);
+                    tma_load_2d(st + SA_A1 + b * 16384, &wt_map, h * GDN_DIM + b * 64, cc * CH, bar);
+                    tma_load_2d(st + SA_A1 + b * 16384 + 8192, &q_map, j * GDN_DIM + b * 64, cc * CH, bar);
+                    tma_load_2d(st + SA_UT + b * 8192, &ut_map, vcol0 + b * 32, cc * CH, bar);
                 }
             };
             auto load_b = [&](int cc) {  // k^ and Wm of chunk cc
-                uint8_t *st = smem + (cc & 1) * STAGE_BYTES;
-                uint64_t *bar = &full[cc & 1];
-                mbar_expect_tx(bar, LOAD_B_BYTES);
+                uint8_t *st = smem + TC_OFF_B + (cc % 3) * STAGE_B_BYTES;
+                uint64_t *bar = &full_b[cc % 3];
+                mbar_expect_tx(bar, STAGE_B_BYTES);
 #pragma unroll
-                for (int b = 0; b < 2; b++) tma_load_2d(st + ST_K + b * 8192, &k_map, j * GDN_DIM + b * 64, cc * CH, bar);
-                tma_load_2d(st + ST_WM, &wm_map, h * CH, cc * CH, bar);
+                for (int b = 0; b < 2; b++) tma_load_2d(st + SB_K + b * 8192, &k_map, j * GDN_DIM + b * 64, cc * CH, bar);
+                tma_load_2d(st + SB_WM, &wm_map, h * CH, cc * CH, bar);
             };
             constexpr uint32_t IDESC_KN = idesc_bf16(DVC, 1, 0);  // A K-major, B MN-major
             constexpr uint32_t IDESC_MN = idesc_bf16(DVC, 1, 1);  // A and B MN-major
@@ -547,36 +555,34 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                 load_a(1);
                 load_b(1);
             }
+            if (n_chunks > 2) load_b(2);
             for (int c = 0; c < n_chunks && ok; c++) {
-                const uint32_t st = sbase + (c & 1) * STAGE_BYTES;
+                const uint32_t sta = sbase + (c & 1) * STAGE_A_BYTES;
+                const uint32_t stb = sbase + TC_OFF_B + (c % 3) * STAGE_B_BYTES;
                 const unsigned par = (unsigned)c & 1u;
-                ok = mbar_wait_bounded(&full[c & 1], (unsigned)(c >> 1) & 1u) && mbar_wait_bounded(s_ready, par);
+                ok = mbar_wait_bounded(&full_a[c & 1], (unsigned)(c >> 1) & 1u) && mbar_wait_bounded(s_ready, par);
                 if (!ok) break;
                 tc_fence_after();
                 {
-                    const uint64_t a1 = smem_desc_sw128(st + ST_A1, 16, 1024);
+                    const uint64_t a1 = smem_desc_sw128(sta + SA_A1, 16, 1024);
 #pragma unroll
                     for (int ks = 0; ks < 8; ks++)
                         tc_mma_bf16(tmem + TM_D1, a1 + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4),
                                     sb_desc + (uint64_t)((ks * 2048) >> 4), IDESC_KN, ks > 0);
                     tc_commit(d1_ready);
                 }
-                // the other stage held chunk c-1: k^ was last read by its state update (complete before s_ready),
-                // Wm by its read-out product
-                if (c >= 1 && c + 1 < n_chunks) {
+                // the B stage of chunk c-1 is free once its read-out product (issued after its state update) has completed
+                if (c >= 1 && c + 2 < n_chunks) {
                     ok = mbar_wait_bounded(d2_ready, (unsigned)(c - 1) & 1u);
                     if (!ok) break;
-                    load_b(c + 1);
+                    load_b(c + 2);
                 }
-                ok = mbar_wait_bounded(u_ready, par);
-                if (!ok) break;
-                // Wt, q^ (read by the MMAs above, complete since D1 was read) and Ut of this stage are free
-                if (c + 2 < n_chunks) load_a(c + 2);
-                ok = mbar_wait_bounded(st_ready, par);
+                ok = mbar_wait_bounded(u_ready, par) && mbar_wait_bounded(st_ready, par) &&
+                     mbar_wait_bounded(&full_b[c % 3], (unsigned)(c / 3) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 {
-                    const uint64_t kd = smem_desc_sw128(st + ST_K, 8192, 1024);  // m = key dim: two 64-wide atoms 8 KiB apart
+                    const uint64_t kd = smem_desc_sw128(stb + SB_K, 8192, 1024);  // m = key dim: two 64-wide atoms 8 KiB apart
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
                         tc_mma_bf16(tmem + TM_ST, kd + (uint64_t)((ks * 2048) >> 4), us_desc + (uint64_t)((ks * 2048) >> 4),
@@ -588,13 +594,15 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                 tc_fence_after();
                 {
                     // rows 0-63 of this A operand are the 8 KiB in front of Wm (finite k^ data); only rows 64-127 of D2 are used
-                    const uint64_t wm = smem_desc_sw128(st + ST_WM - 8192, 16, 1024);
+                    const uint64_t wm = smem_desc_sw128(stb + SB_WM - 8192, 16, 1024);
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
                         tc_mma_bf16(tmem + TM_D2, wm + (uint64_t)((ks * 32) >> 4), u_desc + (uint64_t)((ks * 2048) >> 4),
                                     IDESC_KN, ks > 0);
                     tc_commit(d2_ready);
                 }
+                // Wt, q^ (read by the first product, complete since D1 was read) and Ut of this A stage are free since u_ready
+                if (c + 2 < n_chunks) load_a(c + 2);
             }
             if (!ok) *s_fail = 1;
         }
@@ -618,14 +626,14 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                 *reinterpret_cast<uint4 *>(sw128_chunk(smem + TC_OFF_SB, lane, 4 * ch + cc)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             fence_proxy_async_smem();
-            mbar_arrive(s_ready);
+            warp_arrive(s_ready);
             const float g0 = ex2_approx(lg_at(CH - 1));
 #pragma unroll
             for (int d = 0; d < 32; d++) sv[d] *= g0;
             tmem_st32(lane_base + TM_ST, *reinterpret_cast<float(*)[32]>(&sv[0]));
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(st_ready);
+            warp_arrive(st_ready);
         }
         float lg_r = lg_at(r), lg_c = lg_at(CH - 1);
         float o1[32];  // O rows: gamma_t (Q S0^T) of the chunk whose read-out is still open
@@ -648,7 +656,7 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
             return true;
         };
         for (int c = 0; c < n_chunks && ok; c++) {
-            uint8_t *st = smem + (c & 1) * STAGE_BYTES;
+            uint8_t *st = smem + (c & 1) * STAGE_A_BYTES;
             const unsigned par = (unsigned)c & 1u;
             // decay logs of the next chunk, requested now
             const float lg_r_next = lg_at((c + 1) * CH + r), lg_c_next = lg_at((c + 1) * CH + CH - 1);
@@ -658,7 +666,7 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                     if (!ok) break;
                 }
                 tc_fence_before();
-                mbar_arrive(o_done);
+                warp_arrive(o_done);
             } else if (c > 0) {
                 // U of chunk c-1 is still the operand of its read-out product until that has completed
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(d2_ready, (unsigned)(c - 1) & 1u));
@@ -679,7 +687,7 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
 #pragma unroll
                     for (int e2 = 0; e2 < 2; e2++) {
                         const int d0 = 8 * cc + 4 * e2;
-                        const float4 ut = *reinterpret_cast<const float4 *>(sw128_chunk(st + ST_UT + ch * 8192, r, d0 >> 2));
+                        const float4 ut = *reinterpret_cast<const float4 *>(sw128_chunk(st + SA_UT + ch * 8192, r, d0 >> 2));
                         const float u0 = ut.x - d1[d0], u1 = ut.y - d1[d0 + 1], u2 = ut.z - d1[d0 + 2], u3 = ut.w - d1[d0 + 3];
                         wu[2 * e2] = pack_bf16x2(u0, u1);
                         wu[2 * e2 + 1] = pack_bf16x2(u2, u3);
@@ -691,7 +699,7 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                 }
                 fence_proxy_async_smem();
                 tc_fence_before();
-                mbar_arrive(u_ready);
+                warp_arrive(u_ready);
             } else {
                 const float e = ex2_approx(lg_r);
 #pragma unroll
@@ -714,14 +722,14 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                 }
                 fence_proxy_async_smem();
                 tc_fence_before();
-                mbar_arrive(s_ready);
+                warp_arrive(s_ready);
                 const float gn = ex2_approx(lg_c_next);
 #pragma unroll
                 for (int d = 0; d < 32; d++) sv[d] *= gn;
                 tmem_st32(lane_base + TM_ST, *reinterpret_cast<float(*)[32]>(&sv[0]));
                 tc_wait_st();
                 tc_fence_before();
-                mbar_arrive(st_ready);
+                warp_arrive(st_ready);
             } else {
 #pragma unroll
                 for (int d = 0; d < 32; d++) Sg[(size_t)(32 * ch + d) * GDN_DIM + lane] = sv[d];
