@@ -422,7 +422,7 @@ gdn_prefill_intra_kernel(const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat,
 }
 
 // ------------------------------------------------------------------ 2b. the serial part: state across chunks
-// grid 2*Hv, 288 threads.  One CTA owns 64 of the 128 value rows of one v-head and keeps
+// grid 2*Hv, 320 threads.  One CTA owns 64 of the 128 value rows of one v-head and keeps
 // that half-state, transposed (key index = TMEM lane, value row = column), in tensor
 // memory in fp32 across all chunks.  Per chunk, three groups of tcgen05.mma (M = 128,
 // N = 64, bf16 operands, fp32 accumulate):
@@ -432,8 +432,8 @@ gdn_prefill_intra_kernel(const __nv_bfloat16 *q_hat, const __nv_bfloat16 *k_hat,
 // with U = Ut - D1[0:64] and O = diag(gamma) D1[64:128] + D2[64:128] computed by eight
 // epilogue warps (thread = TMEM lane x half of the 64 columns).  Operands arrive by TMA
 // (128-byte swizzle) into a ring (two stages for what a chunk needs first, three for the rest); S0 (bf16), U and Us are written to shared
-// memory by the epilogue warps as MN-major operands.  Warp 8 issues every TMA load and
-// every MMA.  The recurrence S0 -> D1 -> U -> ST -> S0 is the critical path; the read-out
+// memory by the epilogue warps as MN-major operands.  Warp 8 issues every MMA, warp 9
+// every TMA load.  The recurrence S0 -> D1 -> U -> ST -> S0 is the critical path; the read-out
 // (D2, O) of chunk c is finished under the first product of chunk c+1.  Every mbarrier
 // wait is bounded; a wait that expires sets a status bit and the CTA frees its TMEM and
 // leaves.
@@ -452,7 +452,7 @@ constexpr uint32_t TC_OFF_BAR = TC_OFF_US + 8192;
 constexpr uint32_t TC_SMEM = TC_OFF_BAR + 128 + 1024;
 constexpr uint32_t TC_TMEM_COLS = 256;
 constexpr uint32_t TM_ST = 0, TM_D1 = 64, TM_D2 = 128;
-constexpr int TC_THREADS = 288;
+constexpr int TC_THREADS = 320;
 
 // one arrival for the whole warp, after every lane's earlier writes and fences
 __device__ __forceinline__ void warp_arrive(uint64_t *bar) {
@@ -520,8 +520,8 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
     bool ok = true;
     auto lg_at = [&](int tok) { return lgc[(size_t)min(tok, T - 1) * Hv + h]; };
 
-    if (warp == 8) {
-        // ================= issuer: one lane drives TMA and the tensor core =================
+    if (warp == 9) {
+        // ================= producer: one lane issues every TMA load =================
         if (lane_id == 0) {
             auto load_a = [&](int cc) {  // Wt, q^ and Ut of chunk cc
                 uint8_t *st = smem + (cc & 1) * STAGE_A_BYTES;
@@ -542,13 +542,6 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                 for (int b = 0; b < 2; b++) tma_load_2d(st + SB_K + b * 8192, &k_map, j * GDN_DIM + b * 64, cc * CH, bar);
                 tma_load_2d(st + SB_WM, &wm_map, h * CH, cc * CH, bar);
             };
-            constexpr uint32_t IDESC_KN = idesc_bf16(DVC, 1, 0);  // A K-major, B MN-major
-            constexpr uint32_t IDESC_MN = idesc_bf16(DVC, 1, 1);  // A and B MN-major
-            const uint32_t sbase = smem_u32(smem);
-            const uint64_t sb_desc = smem_desc_sw128(sbase + TC_OFF_SB, 16384, 1024);
-            const uint64_t u_desc = smem_desc_sw128(sbase + TC_OFF_U, 8192, 1024);
-            const uint64_t us_desc = smem_desc_sw128(sbase + TC_OFF_US, 8192, 1024);
-
             load_a(0);
             load_b(0);
             if (n_chunks > 1) {
@@ -556,6 +549,29 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                 load_b(1);
             }
             if (n_chunks > 2) load_b(2);
+            for (int c = 0; c + 2 < n_chunks && ok; c++) {
+                if (c >= 1) {
+                    // the B stage of chunk c-1 is free once its read-out product (issued after its state update) has completed
+                    ok = mbar_wait_bounded(d2_ready, (unsigned)(c - 1) & 1u);
+                    if (!ok) break;
+                    load_b(c + 2);
+                }
+                // Wt, q^ (read by the first product, complete once D1 was read) and Ut of chunk c's A stage are free at u_ready
+                ok = mbar_wait_bounded(u_ready, (unsigned)c & 1u);
+                if (!ok) break;
+                load_a(c + 2);
+            }
+            if (!ok) *s_fail = 1;
+        }
+    } else if (warp == 8) {
+        // ================= issuer: one lane drives the tensor core =================
+        if (lane_id == 0) {
+            constexpr uint32_t IDESC_KN = idesc_bf16(DVC, 1, 0);  // A K-major, B MN-major
+            constexpr uint32_t IDESC_MN = idesc_bf16(DVC, 1, 1);  // A and B MN-major
+            const uint32_t sbase = smem_u32(smem);
+            const uint64_t sb_desc = smem_desc_sw128(sbase + TC_OFF_SB, 16384, 1024);
+            const uint64_t u_desc = smem_desc_sw128(sbase + TC_OFF_U, 8192, 1024);
+            const uint64_t us_desc = smem_desc_sw128(sbase + TC_OFF_US, 8192, 1024);
             for (int c = 0; c < n_chunks && ok; c++) {
                 const uint32_t sta = sbase + (c & 1) * STAGE_A_BYTES;
                 const uint32_t stb = sbase + TC_OFF_B + (c % 3) * STAGE_B_BYTES;
@@ -570,12 +586,6 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                         tc_mma_bf16(tmem + TM_D1, a1 + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4),
                                     sb_desc + (uint64_t)((ks * 2048) >> 4), IDESC_KN, ks > 0);
                     tc_commit(d1_ready);
-                }
-                // the B stage of chunk c-1 is free once its read-out product (issued after its state update) has completed
-                if (c >= 1 && c + 2 < n_chunks) {
-                    ok = mbar_wait_bounded(d2_ready, (unsigned)(c - 1) & 1u);
-                    if (!ok) break;
-                    load_b(c + 2);
                 }
                 ok = mbar_wait_bounded(u_ready, par) && mbar_wait_bounded(st_ready, par) &&
                      mbar_wait_bounded(&full_b[c % 3], (unsigned)(c / 3) & 1u);
@@ -601,8 +611,6 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
                                     IDESC_KN, ks > 0);
                     tc_commit(d2_ready);
                 }
-                // Wt, q^ (read by the first product, complete since D1 was read) and Ut of this A stage are free since u_ready
-                if (c + 2 < n_chunks) load_a(c + 2);
             }
             if (!ok) *s_fail = 1;
         }
