@@ -44,23 +44,31 @@ constexpr int DVC = 64;         // value rows per CTA
 constexpr int LDK = GDN_DIM + 8;  // padded leading dim (bf16) of [.][128] operand tiles
 
 // ------------------------------------------------------------------ 1. conv / norm / gates
-// grid (T, conv_dim / 2048), 256 threads: a thread owns 8 consecutive channels of one
-// token (16-byte loads of the four input rows and of the weights).  A q or k head is
-// 128 channels = 16 neighbouring lanes, reduced by shuffles.  Block y == 0 also
-// computes the per-head gates of the token.
+// grid (ceil(T / CONV_TT), conv_dim / 2048), 256 threads: a thread owns 8 consecutive channels of
+// CONV_TT consecutive tokens (16-byte loads of the input rows of the sliding window and of the
+// weights).  A q or k head is 128 channels = 16 neighbouring lanes, reduced by shuffles.
+// Block y == 0 also computes the per-head gates.  The kernel is bound by instruction issue
+// (SiLU) about as much as by memory, so SiLU uses ex2.approx and an approximate division
+// (the results feed bf16 operands), and one token per thread wins over input reuse: four
+// tokens per thread halved the threads in flight and took 319 us against 225 us.
+constexpr int CONV_TT = 1;
 __global__ void __launch_bounds__(256)
 gdn_prefill_conv_kernel(const __nv_bfloat16 *x, const __nv_bfloat16 *alpha, const __nv_bfloat16 *beta,
                         float *ring, int slot0, const uint16_t *conv_w, const float *a_log,
                         const uint16_t *dt_bias, __nv_bfloat16 *q_hat, __nv_bfloat16 *k_hat, float *v_out,
                         float *lg_out, float *beta_out, int T, int Hk, int Hv, int conv_dim) {
-    const int t = blockIdx.x, tid = threadIdx.x;
+    const int t0 = blockIdx.x * CONV_TT, tid = threadIdx.x;
     const int c0 = (blockIdx.y * 256 + tid) * 8;
     const int total_key = Hk * GDN_DIM;
-    if (c0 < conv_dim) {
-        float xr[4][8];  // rows t-3 .. t
+    const bool in_c = c0 < conv_dim;
+    float xr[CONV_TT + 3][8];  // rows t0-3 .. t0+3
+    float wf[8][4];            // taps of the 8 channels
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int tt = t - 3 + k;
+    for (int k = 0; k < CONV_TT + 3; k++) {
+        const int tt = t0 - 3 + k;
+#pragma unroll
+        for (int e = 0; e < 8; e++) xr[k][e] = 0.0f;
+        if (in_c && tt < T) {
             if (tt >= 0) {
                 const uint4 raw = *reinterpret_cast<const uint4 *>(x + (size_t)tt * conv_dim + c0);
                 const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -75,30 +83,43 @@ gdn_prefill_conv_kernel(const __nv_bfloat16 *x, const __nv_bfloat16 *alpha, cons
                 for (int e = 0; e < 8; e++) xr[k][e] = hr[e];
             }
         }
-        float y[8];
+    }
 #pragma unroll
-        for (int e2 = 0; e2 < 4; e2++) {  // weights of two channels per 16-byte load
-            const uint4 wr = *reinterpret_cast<const uint4 *>(conv_w + (size_t)(c0 + 2 * e2) * 4);
-            const uint32_t w[4] = {wr.x, wr.y, wr.z, wr.w};
+    for (int e2 = 0; e2 < 4; e2++) {  // weights of two channels per 16-byte load
+        uint4 wr = make_uint4(0, 0, 0, 0);
+        if (in_c) wr = *reinterpret_cast<const uint4 *>(conv_w + (size_t)(c0 + 2 * e2) * 4);
+        const uint32_t w[4] = {wr.x, wr.y, wr.z, wr.w};
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                const int e = 2 * e2 + u;
-                float acc = fmaf(xr[0][e], bf16_bits_to_f32((uint16_t)(w[2 * u] & 0xffffu)), 0.0f);
-                acc = fmaf(xr[1][e], bf16_bits_to_f32((uint16_t)(w[2 * u] >> 16)), acc);
-                acc = fmaf(xr[2][e], bf16_bits_to_f32((uint16_t)(w[2 * u + 1] & 0xffffu)), acc);
-                acc = fmaf(xr[3][e], bf16_bits_to_f32((uint16_t)(w[2 * u + 1] >> 16)), acc);
-                y[e] = acc / (1.0f + expf(-acc));
-            }
+        for (int u = 0; u < 2; u++) {
+            wf[2 * e2 + u][0] = bf16_bits_to_f32((uint16_t)(w[2 * u] & 0xffffu));
+            wf[2 * e2 + u][1] = bf16_bits_to_f32((uint16_t)(w[2 * u] >> 16));
+            wf[2 * e2 + u][2] = bf16_bits_to_f32((uint16_t)(w[2 * u + 1] & 0xffffu));
+            wf[2 * e2 + u][3] = bf16_bits_to_f32((uint16_t)(w[2 * u + 1] >> 16));
         }
-        if (c0 < 2 * total_key) {  // q or k: normalise over the head (16 lanes x 8 channels)
-            float ss = 0.0f;
+    }
+    const bool is_qk = c0 < 2 * total_key, is_q = c0 < total_key;
 #pragma unroll
-            for (int e = 0; e < 8; e++) ss += y[e] * y[e];
+    for (int tt = 0; tt < CONV_TT; tt++) {
+        const int t = t0 + tt;
+        if (t >= T) break;  // uniform over the block
+        float y[8];
+        float ss = 0.0f;
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        for (int e = 0; e < 8; e++) {
+            float acc = fmaf(xr[tt][e], wf[e][0], 0.0f);
+            acc = fmaf(xr[tt + 1][e], wf[e][1], acc);
+            acc = fmaf(xr[tt + 2][e], wf[e][2], acc);
+            acc = fmaf(xr[tt + 3][e], wf[e][3], acc);
+            y[e] = __fdividef(acc, 1.0f + __expf(-acc));
+            ss += y[e] * y[e];
+        }
+        // q or k: normalise over the head (16 lanes x 8 channels); every lane takes part in the shuffles
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (!in_c) continue;
+        if (is_qk) {
             const float inv_scale = 1.0f / sqrtf((float)GDN_DIM);
             const float inv = 1.0f / sqrtf(ss / (float)GDN_DIM + 1e-6f);
-            const bool is_q = c0 < total_key;
             const int cc = is_q ? c0 : c0 - total_key;
             uint32_t pk[4];
 #pragma unroll
@@ -116,11 +137,14 @@ gdn_prefill_conv_kernel(const __nv_bfloat16 *x, const __nv_bfloat16 *alpha, cons
         }
     }
     if (blockIdx.y == 0 && tid < Hv) {
-        const float a_val = __bfloat162float(alpha[(size_t)t * Hv + tid]);
         const float dt_b = bf16_bits_to_f32(dt_bias[tid]);
-        const float softplus = logf(1.0f + expf(a_val + dt_b));
-        lg_out[(size_t)t * Hv + tid] = -expf(a_log[tid]) * softplus * 1.4426950408889634f;  // log2 of the decay g
-        beta_out[(size_t)t * Hv + tid] = 1.0f / (1.0f + expf(-__bfloat162float(beta[(size_t)t * Hv + tid])));
+        const float neg_a = -expf(a_log[tid]);
+        for (int t = t0; t < min(t0 + CONV_TT, T); t++) {
+            const float a_val = __bfloat162float(alpha[(size_t)t * Hv + tid]);
+            const float softplus = logf(1.0f + expf(a_val + dt_b));
+            lg_out[(size_t)t * Hv + tid] = neg_a * softplus * 1.4426950408889634f;  // log2 of the decay g
+            beta_out[(size_t)t * Hv + tid] = 1.0f / (1.0f + expf(-__bfloat162float(beta[(size_t)t * Hv + tid])));
+        }
     }
 }
 
@@ -755,32 +779,51 @@ gdn_prefill_state_kernel(const __grid_constant__ CUtensorMap wt_map, const __gri
 }
 
 // ------------------------------------------------------------------ 3. read-out epilogue
-// grid (T), 256 threads: a warp takes one head at a time (4 values per lane):
-// out = o * rsqrt(mean o^2 + eps) * w * silu(z), or out = o.
+// grid (T), 256 threads: a warp takes heads warp, warp+8, ... (4 values per lane), four heads
+// in flight at a time: out = o * rsqrt(mean o^2 + eps) * w * silu(z), or out = o.
 __global__ void __launch_bounds__(256)
 gdn_prefill_out_kernel(const float *o_raw, const __nv_bfloat16 *z, const uint16_t *norm_w, __nv_bfloat16 *out,
                        int Hv, float eps) {
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int h = warp; h < Hv; h += 8) {
-        const size_t idx = ((size_t)t * Hv + h) * GDN_DIM + lane * 4;
-        const float4 o = *reinterpret_cast<const float4 *>(o_raw + idx);
-        float r[4] = {o.x, o.y, o.z, o.w};
-        if (z != nullptr) {
-            const float tot = warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w);
-            const float inv_rms = 1.0f / sqrtf(tot / (float)GDN_DIM + eps);
-            const uint2 zz = *reinterpret_cast<const uint2 *>(z + idx);
-            const uint2 ww = *reinterpret_cast<const uint2 *>(norm_w + lane * 4);
-            const float zf[4] = {bf16_bits_to_f32((uint16_t)(zz.x & 0xffffu)), bf16_bits_to_f32((uint16_t)(zz.x >> 16)),
-                                 bf16_bits_to_f32((uint16_t)(zz.y & 0xffffu)), bf16_bits_to_f32((uint16_t)(zz.y >> 16))};
-            const float wf[4] = {bf16_bits_to_f32((uint16_t)(ww.x & 0xffffu)), bf16_bits_to_f32((uint16_t)(ww.x >> 16)),
-                                 bf16_bits_to_f32((uint16_t)(ww.y & 0xffffu)), bf16_bits_to_f32((uint16_t)(ww.y >> 16))};
+    float wf[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+    if (z != nullptr) {
+        const uint2 ww = *reinterpret_cast<const uint2 *>(norm_w + lane * 4);
+        wf[0] = bf16_bits_to_f32((uint16_t)(ww.x & 0xffffu));
+        wf[1] = bf16_bits_to_f32((uint16_t)(ww.x >> 16));
+        wf[2] = bf16_bits_to_f32((uint16_t)(ww.y & 0xffffu));
+        wf[3] = bf16_bits_to_f32((uint16_t)(ww.y >> 16));
+    }
+    for (int hb = warp; hb < Hv; hb += 32) {
+        float4 o[4];
+        uint2 zz[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float silu_z = zf[e] / (1.0f + expf(-zf[e]));
-                r[e] = r[e] * inv_rms * wf[e] * silu_z;
+        for (int u = 0; u < 4; u++) {
+            const int h = hb + 8 * u;
+            if (h < Hv) {
+                const size_t idx = ((size_t)t * Hv + h) * GDN_DIM + lane * 4;
+                o[u] = *reinterpret_cast<const float4 *>(o_raw + idx);
+                if (z != nullptr) zz[u] = *reinterpret_cast<const uint2 *>(z + idx);
             }
         }
-        *reinterpret_cast<uint2 *>(out + idx) = make_uint2(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]));
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int h = hb + 8 * u;
+            if (h >= Hv) break;  // uniform over the warp
+            const size_t idx = ((size_t)t * Hv + h) * GDN_DIM + lane * 4;
+            float r[4] = {o[u].x, o[u].y, o[u].z, o[u].w};
+            if (z != nullptr) {
+                const float tot = warp_sum(o[u].x * o[u].x + o[u].y * o[u].y + o[u].z * o[u].z + o[u].w * o[u].w);
+                const float inv_rms = 1.0f / sqrtf(tot / (float)GDN_DIM + eps);
+                const float zf[4] = {bf16_bits_to_f32((uint16_t)(zz[u].x & 0xffffu)), bf16_bits_to_f32((uint16_t)(zz[u].x >> 16)),
+                                     bf16_bits_to_f32((uint16_t)(zz[u].y & 0xffffu)), bf16_bits_to_f32((uint16_t)(zz[u].y >> 16))};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float silu_z = zf[e] / (1.0f + expf(-zf[e]));
+                    r[e] = r[e] * inv_rms * wf[e] * silu_z;
+                }
+            }
+            *reinterpret_cast<uint2 *>(out + idx) = make_uint2(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]));
+        }
     }
 }
 
@@ -796,7 +839,7 @@ cudaError_t gdn_prefill_configure() {
 cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, const GdnPrefillMaps &m, cudaStream_t stream) {
     if (p.T <= 0) return cudaSuccess;
     const __nv_bfloat16 *x = reinterpret_cast<const __nv_bfloat16 *>(p.qkv);
-    dim3 g1((unsigned)p.T, (unsigned)((p.conv_dim + 2047) / 2048), 1);
+    dim3 g1((unsigned)((p.T + CONV_TT - 1) / CONV_TT), (unsigned)((p.conv_dim + 2047) / 2048), 1);
     gdn_prefill_conv_kernel<<<g1, 256, 0, stream>>>(
         x, reinterpret_cast<const __nv_bfloat16 *>(p.alpha), reinterpret_cast<const __nv_bfloat16 *>(p.beta), p.ring,
         p.slot0, p.conv_w, p.a_log, p.dt_bias, reinterpret_cast<__nv_bfloat16 *>(p.q_hat),
