@@ -14,8 +14,8 @@
 //      sincosf of pos * inv_freq, shared by all heads), rotated K and V rows
 //      stored into the cache.
 //   2. gqa_prefill_kernel: CTA = 128 query tokens of one query head (M = 128);
-//      four softmax warps (thread = query row) and one warp that issues every TMA
-//      load and every tcgen05.mma.
+//      four softmax warps (thread = query row), one warp that issues every
+//      tcgen05.mma and one that issues every TMA load.
 //      Per 64-row KV tile: S = Q K^T (16 tcgen05.mma of K=16, N=64, fp32 in
 //      TMEM), softmax with one thread per query row (tcgen05.ld, no shuffles),
 //      P written to shared memory as bf16, O += P V (4 tcgen05.mma, N=256,
@@ -56,10 +56,11 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_S = 0;      // two S buffers of 64 columns
 constexpr uint32_t TM_O = 128;    // O accumulator, 256 columns
 
-// 160 threads: warps 0-3 own the 128 query rows (softmax, rescale, epilogue);
-// warp 4 issues every TMA load and every tcgen05.mma, so that building
-// descriptors and issuing the 20 MMAs of a tile never sits on the softmax path.
-__global__ void __launch_bounds__(160, 1)
+// 192 threads: warps 0-3 own the 128 query rows (softmax, rescale, epilogue); warp 4
+// issues every tcgen05.mma and warp 5 every TMA load.  The MMA issue of a tile blocks its
+// thread for about as long as the tensor core needs (~1350 cycles), so neither the
+// softmax nor the issue of the loads (~550 cycles a tile) may share that thread.
+__global__ void __launch_bounds__(192, 1)
 gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const PrefillAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -106,8 +107,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
 
-    if (warp == 4) {
-        // ================= issuer warp: one lane drives TMA and the tensor core =================
+    if (warp == 5) {
+        // ================= producer warp: one lane issues every TMA load =================
         if ((tid & 31) == 0) {
             auto load_k = [&](int tile) {
                 const int st = tile & 1;
@@ -125,6 +126,31 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
                     tma_load_2d(smem + OFF_V + st * KV_TILE_BYTES + b * KV_BOX, &vmap, b * 64, kv_row0 + tile * PF_N,
                                 &full_v[st]);
             };
+            mbar_expect_tx(full_q, Q_BYTES);
+#pragma unroll
+            for (int b = 0; b < 4; b++) tma_load_3d(smem + OFF_Q + b * Q_BOX, &qmap, b * 64, h, t0, full_q);
+            load_k(0);
+            load_v(0);
+            if (ntiles > 1) {
+                load_k(1);
+                load_v(1);
+            }
+            for (int j = 0; j + 2 < ntiles && ok; j++) {
+                const int b = j & 1;
+                const unsigned par = (unsigned)(j >> 1) & 1u;
+                // the K stage of tile j is free once Q K^T of tile j has completed, its V stage once P V of tile j has
+                ok = mbar_wait_bounded(&s_ready[b], par);
+                if (!ok) break;
+                load_k(j + 2);
+                ok = mbar_wait_bounded(&pv_done[b], par);
+                if (!ok) break;
+                load_v(j + 2);
+            }
+            if (!ok) *s_fail = 1;
+        }
+    } else if (warp == 4) {
+        // ================= issuer warp: one lane drives the tensor core =================
+        if ((tid & 31) == 0) {
             constexpr uint32_t IDESC_QK = idesc_bf16(PF_N, 0);
             constexpr uint32_t IDESC_PV = idesc_bf16(HEAD_DIM, 1);
             // descriptors differ only in their start-address field: build the bases once
@@ -150,16 +176,6 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
                                 (tile > 0) || (ks > 0));
                 tc_commit(&pv_done[tile & 1]);
             };
-
-            mbar_expect_tx(full_q, Q_BYTES);
-#pragma unroll
-            for (int b = 0; b < 4; b++) tma_load_3d(smem + OFF_Q + b * Q_BOX, &qmap, b * 64, h, t0, full_q);
-            load_k(0);
-            load_v(0);
-            if (ntiles > 1) {
-                load_k(1);
-                load_v(1);
-            }
             ok = mbar_wait_bounded(q_ready, 0) && mbar_wait_bounded(&full_k[0], 0);
             if (ok) {
                 tc_fence_after();
@@ -175,20 +191,11 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
                     tc_fence_after();
                     issue_qk(j + 1);
                 }
-                // P of tile j is in shared memory (so Q K^T of tile j is long complete: its K stage is free)
-                ok = mbar_wait_bounded(&p_ready[b], par);
-                if (!ok) break;
-                if (j + 2 < ntiles) load_k(j + 2);
-                ok = mbar_wait_bounded(&full_v[b], par);
+                // P of tile j is in shared memory, V of tile j has landed
+                ok = mbar_wait_bounded(&p_ready[b], par) && mbar_wait_bounded(&full_v[b], par);
                 if (!ok) break;
                 tc_fence_after();
                 issue_pv(j);
-                if (j >= 1 && j + 1 < ntiles) {
-                    // V stage (j+1)&1 held tile j-1: free once its P V has completed
-                    ok = mbar_wait_bounded(&pv_done[(j - 1) & 1], (unsigned)((j - 1) >> 1) & 1u);
-                    if (!ok) break;
-                    load_v(j + 1);
-                }
             }
             if (!ok) *s_fail = 1;
         }
@@ -407,7 +414,7 @@ cudaError_t launch_gqa_prefill(const CUtensorMap &qmap, const CUtensorMap &kmap,
                                const PrefillAttnParams &p, cudaStream_t stream) {
     if (p.T <= 0) return cudaSuccess;
     dim3 grid((unsigned)((p.T + PF_M - 1) / PF_M), (unsigned)p.H, 1);
-    gqa_prefill_kernel<<<grid, 160, PF_SMEM, stream>>>(qmap, kmap, vmap, p);
+    gqa_prefill_kernel<<<grid, 192, PF_SMEM, stream>>>(qmap, kmap, vmap, p);
     return cudaGetLastError();
 }
 
