@@ -14,8 +14,8 @@
 //      sincosf of pos * inv_freq, shared by all heads), rotated K and V rows
 //      stored into the cache.
 //   2. gqa_prefill_kernel: CTA = 128 query tokens of one query head (M = 128);
-//      four softmax warps (thread = query row), one warp that issues every
-//      tcgen05.mma and one that issues every TMA load.
+//      eight softmax warps (thread = query row x half of the columns), one warp
+//      that issues every tcgen05.mma and one that issues every TMA load.
 //      Per 64-row KV tile: S = Q K^T (16 tcgen05.mma of K=16, N=64, fp32 in
 //      TMEM), softmax with one thread per query row (tcgen05.ld, no shuffles),
 //      P written to shared memory as bf16, O += P V (4 tcgen05.mma, N=256,
@@ -50,17 +50,20 @@ constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
 constexpr uint32_t OFF_V = OFF_K + PF_STAGES * KV_TILE_BYTES;
 constexpr uint32_t OFF_P = OFF_V + PF_STAGES * KV_TILE_BYTES;
 constexpr uint32_t OFF_BAR = OFF_P + 2 * P_BYTES;
-constexpr uint32_t PF_SMEM = OFF_BAR + 128 + 1024;     // + barriers + alignment slack
+constexpr uint32_t OFF_XM = OFF_BAR + 256;               // row-maximum exchange, bf16 [2 tiles][2 halves][128 rows]
+constexpr uint32_t PF_SMEM = OFF_XM + 1024 + 1024;      // + alignment slack
+constexpr int PF_THREADS = 320;
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_S = 0;      // two S buffers of 64 columns
 constexpr uint32_t TM_O = 128;    // O accumulator, 256 columns
 
-// 192 threads: warps 0-3 own the 128 query rows (softmax, rescale, epilogue); warp 4
-// issues every tcgen05.mma and warp 5 every TMA load.  The MMA issue of a tile blocks its
+// 320 threads: warps 0-7 own the 128 query rows, two warps (column halves) per TMEM lane
+// quadrant (softmax, rescale, epilogue); warp 8 issues every tcgen05.mma and warp 9 every
+// TMA load.  The MMA issue of a tile blocks its
 // thread for about as long as the tensor core needs (~1350 cycles), so neither the
 // softmax nor the issue of the loads (~550 cycles a tile) may share that thread.
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(PF_THREADS, 1)
 gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const PrefillAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -71,10 +74,11 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     uint64_t *full_v = bars + 3;    // [2] TMA: V stage landed
     uint64_t *s_ready = bars + 5;   // [2] tcgen05.commit: scores of a tile are in TMEM
     uint64_t *pv_done = bars + 7;   // [2] tcgen05.commit: P V of a tile has been accumulated
-    uint64_t *p_ready = bars + 9;   // [2] 128 arrivals: P of a tile is in shared memory, S has been read
-    uint64_t *q_ready = bars + 11;  // 128 arrivals: Q has been rotated in shared memory
+    uint64_t *p_ready = bars + 9;   // [2] 8 warps: P of a tile is in shared memory, S has been read
+    uint64_t *q_ready = bars + 11;  // 8 warps: Q has been rotated in shared memory
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
     volatile int *s_fail = reinterpret_cast<volatile int *>(bars + 13);
+    uint64_t *x_ready = bars + 14;  // [4] 2 warps: both column halves of a lane quadrant have published their row maxima
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int n_qt = (p.T + PF_M - 1) / PF_M;
@@ -91,9 +95,10 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         prefetch_tmap(&kmap);
         prefetch_tmap(&vmap);
         for (int i = 0; i < 9; i++) mbar_init(&bars[i], 1);
-        mbar_init(&p_ready[0], 128);
-        mbar_init(&p_ready[1], 128);
-        mbar_init(q_ready, 128);
+        mbar_init(&p_ready[0], 8);  // one arrival per softmax warp
+        mbar_init(&p_ready[1], 8);
+        mbar_init(q_ready, 8);
+        for (int i = 0; i < 4; i++) mbar_init(&x_ready[i], 2);
         *s_fail = 0;
         mbar_fence_init();
     }
@@ -107,7 +112,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
 
-    if (warp == 5) {
+    if (warp == 9) {
         // ================= producer warp: one lane issues every TMA load =================
         if ((tid & 31) == 0) {
             auto load_k = [&](int tile) {
@@ -148,7 +153,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             }
             if (!ok) *s_fail = 1;
         }
-    } else if (warp == 4) {
+    } else if (warp == 8) {
         // ================= issuer warp: one lane drives the tensor core =================
         if ((tid & 31) == 0) {
             constexpr uint32_t IDESC_QK = idesc_bf16(PF_N, 0);
@@ -200,21 +205,38 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             if (!ok) *s_fail = 1;
         }
     } else {
-        // ================= softmax warps: thread = query row =================
-        const int row_tok = t0 + tid;            // this thread's query token
+        // ================= softmax warps: thread = (query row, half of the columns) =================
+        // warps w and w+4 share TMEM lane quadrant w: warp w takes columns 0-31 of a 64-column score tile (and
+        // dims 0-127 of O), warp w+4 the rest; the two exchange their row maxima through shared memory.
+        const int quad = warp & 3, hf = warp >> 2;
+        const int row = 32 * quad + (tid & 31);  // query row of the tile = TMEM lane
+        const int row_tok = t0 + row;            // this thread's query token
         const int qpos = p.start_pos + row_tok;  // its absolute position
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_base = tmem + ((uint32_t)(32 * quad) << 16);
+        __nv_bfloat16 *xm = reinterpret_cast<__nv_bfloat16 *>(smem + OFF_XM);
+        auto warp_arrive = [&](uint64_t *bar) {
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(bar);
+        };
+        // exchange point of the two warps of a quadrant (bounded, like every other wait here)
+        unsigned x_phase = 0;
+        auto pair_sync = [&]() -> bool {
+            warp_arrive(&x_ready[quad]);
+            const bool done = __all_sync(0xffffffffu, mbar_wait_bounded(&x_ready[quad], x_phase & 1u));
+            x_phase++;
+            return done;
+        };
 
-        // ---- RoPE on this thread's Q row, in shared memory (dims 0..63 live in box 0) ----
+        // ---- RoPE on this thread's share of its Q row, in shared memory (dims 0..63 live in box 0) ----
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(full_q, 0));
         if (ok && p.rotary_dim > 0 && row_tok < p.T) {
             const int half = p.rotary_dim >> 1;  // <= 32 here (rotary_dim <= 64)
-            uint8_t *rowp = smem + OFF_Q + tid * 128;
+            uint8_t *rowp = smem + OFF_Q + row * 128;
             const float2 *cs = reinterpret_cast<const float2 *>(p.cos_sin) + (size_t)row_tok * 32;
-            for (int i0 = 0; i0 < half; i0 += 8) {
+            for (int i0 = 8 * hf; i0 < half; i0 += 16) {
                 const int c_lo = i0 >> 3, c_hi = (i0 + half) >> 3;
-                uint4 *plo = reinterpret_cast<uint4 *>(rowp + ((c_lo ^ (tid & 7)) << 4));
-                uint4 *phi = reinterpret_cast<uint4 *>(rowp + ((c_hi ^ (tid & 7)) << 4));
+                uint4 *plo = reinterpret_cast<uint4 *>(rowp + ((c_lo ^ (row & 7)) << 4));
+                uint4 *phi = reinterpret_cast<uint4 *>(rowp + ((c_hi ^ (row & 7)) << 4));
                 uint4 lo = *plo, hi = *phi;
                 __nv_bfloat16 *a = reinterpret_cast<__nv_bfloat16 *>(&lo);
                 __nv_bfloat16 *b = reinterpret_cast<__nv_bfloat16 *>(&hi);
@@ -230,9 +252,9 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             }
         }
         fence_proxy_async_smem();
-        mbar_arrive(q_ready);
+        warp_arrive(q_ready);
 
-        float m_run = -INFINITY, l_run = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f;  // l_run: this thread's 32 columns of every tile only
         const float sl2 = p.scale * LOG2E_PF;
         for (int j = 0; j < ntiles && ok; j++) {
             const int b = j & 1;
@@ -240,21 +262,27 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_ready[b], par) && *s_fail == 0);
             if (!ok) break;
             tc_fence_after();
-            float s[PF_N];
-            tmem_ld32(lane_base + TM_S + b * PF_N, s);
-            tmem_ld32(lane_base + TM_S + b * PF_N + 32, s + 32);
+            float s[32];
+            tmem_ld32(lane_base + TM_S + b * PF_N + 32 * hf, s);
             tc_wait_ld();
-            const int kv0 = j * PF_N;
-            if (kv0 + PF_N - 1 > p.start_pos + t0) {  // tile touches the diagonal
+            const int kv0 = j * PF_N + 32 * hf;
+            if (j * PF_N + PF_N - 1 > p.start_pos + t0) {  // tile touches the diagonal
 #pragma unroll
-                for (int c = 0; c < PF_N; c++)
+                for (int c = 0; c < 32; c++)
                     if (kv0 + c > qpos) s[c] = -INFINITY;
             }
             float mx = s[0];
 #pragma unroll
-            for (int c = 1; c < PF_N; c++) mx = fmaxf(mx, s[c]);
-            const float m_new = fmaxf(m_run, mx);
-            // rescale O only when some row of the warp moved its maximum by more than 2^8
+            for (int c = 1; c < 32; c++) mx = fmaxf(mx, s[c]);
+            // The two halves of a row must agree on the maximum they use: both round their own up to bf16 (the
+            // running maximum only has to bound the scores from above, roughly) and take the larger.
+            __nv_bfloat16 mx_b = __float2bfloat16_ru(mx);
+            xm[(b * 2 + hf) * PF_M + row] = mx_b;
+            ok = pair_sync();
+            if (!ok) break;
+            const float m_tile = fmaxf(__bfloat162float(mx_b), __bfloat162float(xm[(b * 2 + (hf ^ 1)) * PF_M + row]));
+            const float m_new = fmaxf(m_run, m_tile);
+            // rescale O only when some row of the quadrant moved its maximum by more than 2^8
             const bool need = (m_new - m_run) * sl2 > 8.0f;  // also true on the first tile (m_run = -inf)
             const bool warp_rescale = __any_sync(0xffffffffu, need);
             float corr = 1.0f;
@@ -264,9 +292,9 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             }
             const float mb = m_run * sl2;
             float rs = 0.0f;
-            uint32_t pk[PF_N / 2];
+            uint32_t pk[16];
 #pragma unroll
-            for (int c = 0; c < PF_N; c += 2) {
+            for (int c = 0; c < 32; c += 2) {
                 const float p0 = ex2_approx(fmaf(s[c], sl2, -mb));
                 const float p1 = ex2_approx(fmaf(s[c + 1], sl2, -mb));
                 rs += p0 + p1;
@@ -281,31 +309,39 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll 1
-                for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+                for (int c0 = 128 * hf; c0 < 128 * hf + 128; c0 += 32) {
                     float o[32];
                     tmem_ld32(lane_base + TM_O + c0, o);
                     tc_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] *= corr;
-                    tmem_st32(lane_base + TM_O + c0, o);
+                    tmem_st32(lane_base + TM_O + c0, *reinterpret_cast<float(*)[32]>(&o[0]));
                 }
                 tc_wait_st();
             }
             {
-                uint8_t *prow = smem + OFF_P + b * P_BYTES + tid * 128;
+                uint8_t *prow = smem + OFF_P + b * P_BYTES + row * 128;
 #pragma unroll
-                for (int c = 0; c < 8; c++)
-                    *reinterpret_cast<uint4 *>(prow + ((c ^ (tid & 7)) << 4)) =
+                for (int c = 0; c < 4; c++)
+                    *reinterpret_cast<uint4 *>(prow + (((4 * hf + c) ^ (row & 7)) << 4)) =
                         make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             }
             fence_proxy_async_smem();
             tc_fence_before();
-            mbar_arrive(&p_ready[b]);
+            warp_arrive(&p_ready[b]);
         }
         if (ok && ntiles > 0) {
             ok = __all_sync(0xffffffffu,
                             mbar_wait_bounded(&pv_done[(ntiles - 1) & 1], (unsigned)((ntiles - 1) >> 1) & 1u));
             tc_fence_after();
+        }
+        // row sum = the two halves' partial sums (both carry the same running maximum); every MMA has completed,
+        // so the P buffers are free to carry the exchange
+        float *xl = reinterpret_cast<float *>(smem + OFF_P);
+        if (ok) {
+            xl[hf * PF_M + row] = l_run;
+            ok = pair_sync();
+            l_run += xl[(hf ^ 1) * PF_M + row];
         }
         if (ok) {
             // every lane takes part in the warp-wide TMEM loads; only the global accesses are predicated
@@ -313,7 +349,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             const float inv = 1.0f / l_run;
             const size_t off = ((size_t)(valid ? row_tok : 0) * p.H + h) * HEAD_DIM;
 #pragma unroll 1
-            for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+            for (int c0 = 128 * hf; c0 < 128 * hf + 128; c0 += 32) {
                 float o[32];
                 tmem_ld32(lane_base + TM_O + c0, o);
                 tc_wait_ld();
@@ -414,7 +450,7 @@ cudaError_t launch_gqa_prefill(const CUtensorMap &qmap, const CUtensorMap &kmap,
                                const PrefillAttnParams &p, cudaStream_t stream) {
     if (p.T <= 0) return cudaSuccess;
     dim3 grid((unsigned)((p.T + PF_M - 1) / PF_M), (unsigned)p.H, 1);
-    gqa_prefill_kernel<<<grid, 192, PF_SMEM, stream>>>(qmap, kmap, vmap, p);
+    gqa_prefill_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(qmap, kmap, vmap, p);
     return cudaGetLastError();
 }
 
