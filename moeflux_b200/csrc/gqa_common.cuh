@@ -133,33 +133,51 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
     }
     __syncthreads();
     const size_t head0 = (size_t)L.it.in_idx * p.H + (size_t)L.kvh * group;
-    for (int hr = 0; hr < group; hr++) {
-        float2 acc = make_float2(0.0f, 0.0f);
-        for (int c = 0; c < n_src; c++) {
-            const float w = s_w[c * 16 + hr];
-            const float2 o = *reinterpret_cast<const float2 *>(
-                src_o + ((size_t)c * 16 + hr) * HEAD_DIM + 2 * tid);
-            acc.x = fmaf(w, o.x, acc.x);
-            acc.y = fmaf(w, o.y, acc.y);
+    // Eight heads at a time with every load of a round in flight together: the merging CTA is the last of its unit to
+    // finish, usually at the very end of the launch, so this latency is on the launch's critical path.
+    for (int hr0 = 0; hr0 < group; hr0 += 8) {
+        float2 acc[8], gt[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            acc[u] = make_float2(0.0f, 0.0f);
+            gt[u] = make_float2(0.0f, 0.0f);
+            if (!p.partial_mode && p.gate && hr0 + u < group)
+                gt[u] = *reinterpret_cast<const float2 *>(p.gate + (head0 + hr0 + u) * (size_t)p.gate_row_stride + 2 * tid);
         }
-        const size_t off = (head0 + hr) * HEAD_DIM + 2 * tid;
-        const size_t goff = (head0 + hr) * (size_t)p.gate_row_stride + 2 * tid;
-        if (p.partial_mode) {
-            const int hl = L.kvh * group + hr;  // head within the item
-            *reinterpret_cast<float2 *>(p.po + (size_t)L.it.in_idx * p.po_item_stride + (size_t)hl * HEAD_DIM + 2 * tid) = acc;
-            if (tid == 0) {
-                p.pm[(size_t)L.it.in_idx * p.pml_item_stride + hl] = s_M[hr];
-                p.pl[(size_t)L.it.in_idx * p.pml_item_stride + hl] = s_L[hr];
+        for (int c = 0; c < n_src; c++) {
+            float2 o[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                o[u] = (hr0 + u < group) ? *reinterpret_cast<const float2 *>(src_o + ((size_t)c * 16 + hr0 + u) * HEAD_DIM + 2 * tid)
+                                         : make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float w = s_w[c * 16 + ((hr0 + u) & 15)];
+                acc[u].x = fmaf(w, o[u].x, acc[u].x);
+                acc[u].y = fmaf(w, o[u].y, acc[u].y);
             }
-        } else {
-            const float inv = 1.0f / s_L[hr];
-            float2 r = make_float2(acc.x * inv, acc.y * inv);
-            if (p.gate) {
-                const float2 gt = *reinterpret_cast<const float2 *>(p.gate + goff);
-                r.x *= 1.0f / (1.0f + expf(-gt.x));
-                r.y *= 1.0f / (1.0f + expf(-gt.y));
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int hr = hr0 + u;
+            if (hr >= group) break;
+            const size_t off = (head0 + hr) * HEAD_DIM + 2 * tid;
+            if (p.partial_mode) {
+                const int hl = L.kvh * group + hr;  // head within the item
+                *reinterpret_cast<float2 *>(p.po + (size_t)L.it.in_idx * p.po_item_stride + (size_t)hl * HEAD_DIM + 2 * tid) = acc[u];
+                if (tid == 0) {
+                    p.pm[(size_t)L.it.in_idx * p.pml_item_stride + hl] = s_M[hr];
+                    p.pl[(size_t)L.it.in_idx * p.pml_item_stride + hl] = s_L[hr];
+                }
+            } else {
+                const float inv = 1.0f / s_L[hr];
+                float2 r = make_float2(acc[u].x * inv, acc[u].y * inv);
+                if (p.gate) {
+                    r.x *= 1.0f / (1.0f + expf(-gt[u].x));
+                    r.y *= 1.0f / (1.0f + expf(-gt[u].y));
+                }
+                *reinterpret_cast<float2 *>(p.out + off) = r;
             }
-            *reinterpret_cast<float2 *>(p.out + off) = r;
         }
     }
 }
