@@ -41,6 +41,21 @@ __device__ __forceinline__ float2 load_rot2(const float *row, int d, int rotary_
     return x;
 }
 
+// Copies the query head rows of a unit (q_row_stride floats apart in device memory) into shared memory with
+// 16-byte loads that are all in flight together; the fragment builders then read shared memory.  (Building the
+// fragments straight from device memory serialised ~64 dependent-latency loads per thread: 30 us per segment.)
+constexpr int Q_STAGE_STRIDE = HEAD_DIM + 4;  // floats: rows stay 16-byte aligned and spread over the banks
+__device__ __forceinline__ void stage_q_rows(const float *qbase, int rows, int q_row_stride, float *s_q) {
+#pragma unroll
+    for (int k = 0; k < 16 * (HEAD_DIM / 4) / 128; k++) {
+        const int i = k * 128 + (int)threadIdx.x;
+        const int r = i >> 6, c = (i & 63) * 4;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (r < rows) v = *reinterpret_cast<const float4 *>(qbase + (size_t)r * q_row_stride + c);
+        *reinterpret_cast<float4 *>(s_q + r * Q_STAGE_STRIDE + c) = v;
+    }
+}
+
 // 1/rms of the 16 (or fewer) query head rows of a unit, by 4 warps: s_inv[row].
 // qbase points at row 0; rows are q_row_stride floats apart.  Contains a __syncthreads.
 __device__ __forceinline__ void head_inv_rms(const float *qbase, int rows, int row_stride, float eps, float *s_inv) {

@@ -97,10 +97,13 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
         }
     };
 
+    // the first tiles of the segment; the last stage of the ring first carries the Q rows (below)
     if (tid == 0 && !appender) {
-        const int n0 = min(ntiles, BF16_STAGES);
+        const int n0 = min(ntiles, BF16_STAGES - 1);
         for (int i = 0; i < n0; i++) issue_tile(i);
     }
+    float *s_q = reinterpret_cast<float *>(stages + (size_t)((pc + BF16_STAGES - 1) % BF16_STAGES) * 2 * TILE_BYTES_BF16);
+    stage_q_rows(p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * (size_t)p.q_row_stride, group, p.q_row_stride, s_q);
     // RoPE table for this token
     const int half = p.rotary_dim >> 1;
     if (tid < half) {
@@ -136,33 +139,37 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
         fence_proxy_async();
         __syncthreads();
         if (tid == 0) {
-            const int n0 = min(ntiles, BF16_STAGES);
+            const int n0 = min(ntiles, BF16_STAGES - 1);
             for (int i = 0; i < n0; i++) issue_tile(i);
         }
     }
 
     // ---- Q fragments (A operand, 16 heads x 256 dims, bf16), RoPE applied ----
+    // Two compact steps (a long unrolled build runs once per segment from a cold instruction cache and cost
+    // ~12 us): normalise / rotate into a bf16 tile beside the staged rows, then one ldmatrix per k-step.
     uint32_t qa[16][4];
     {
-        const float *qbase = p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * (size_t)p.q_row_stride;
+        constexpr int QB_STRIDE = HEAD_DIM + 8;  // bf16: rows 16-byte aligned, conflict-free for ldmatrix
+        __nv_bfloat16 *s_qb = reinterpret_cast<__nv_bfloat16 *>(s_q + 16 * Q_STAGE_STRIDE);
         const uint16_t *qnw = p.qnorm_w ? p.qnorm_w + (size_t)(it.kv_slot / p.n_seqs) * HEAD_DIM : nullptr;
-        if (qnw) head_inv_rms(qbase, group, p.q_row_stride, p.norm_eps, s_inv);
-#pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int row = g + ((e & 1) ? 8 : 0);
-                const int d = ks * 16 + 2 * t + ((e & 2) ? 8 : 0);
-                float2 x = make_float2(0.0f, 0.0f);
-                if (row < group) {
-                    const float *qr = qbase + (size_t)row * p.q_row_stride;
-                    const float qinv = qnw ? s_inv[row] : 1.0f;
-                    x = load_rot2(qr, d, p.rotary_dim, half, s_cos, s_sin, qinv, qnw);
-                }
-                qa[ks][e] = pack_bf16x2(x.x, x.y);
-            }
+        if (qnw) head_inv_rms(s_q, group, Q_STAGE_STRIDE, p.norm_eps, s_inv);
+#pragma unroll 1
+        for (int idx = tid; idx < 16 * (HEAD_DIM / 2); idx += 128) {
+            const int row = idx >> 7, d = (idx & 127) * 2;
+            float2 x = make_float2(0.0f, 0.0f);
+            if (row < group)
+                x = load_rot2(s_q + row * Q_STAGE_STRIDE, d, p.rotary_dim, half, s_cos, s_sin, qnw ? s_inv[row] : 1.0f, qnw);
+            *reinterpret_cast<uint32_t *>(s_qb + row * QB_STRIDE + d) = pack_bf16x2(x.x, x.y);
         }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < 16; ks++)
+            ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
+                        smem_u32(s_qb + (lane & 15) * QB_STRIDE + 16 * ks + (lane >> 4) * 8));
     }
+    fence_proxy_async();  // the Q staging area goes back to the ring
+    __syncthreads();
+    if (tid == 0 && ntiles >= BF16_STAGES) issue_tile(BF16_STAGES - 1);
 
     float o[8][4];
 #pragma unroll

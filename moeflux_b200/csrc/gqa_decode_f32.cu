@@ -96,10 +96,13 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         }
     };
 
+    // the first tiles of the segment; the last stage of the ring first carries the Q rows (below)
     if (tid == 0 && !appender) {
-        const int n0 = min(ntiles, F32_STAGES);
+        const int n0 = min(ntiles, F32_STAGES - 1);
         for (int i = 0; i < n0; i++) issue_tile(i);
     }
+    float *s_q = reinterpret_cast<float *>(stages + (size_t)((pc + F32_STAGES - 1) % F32_STAGES) * 2 * TILE_BYTES_F32);
+    stage_q_rows(p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * (size_t)p.q_row_stride, group, p.q_row_stride, s_q);
     const int half = p.rotary_dim >> 1;
     if (tid < half) {
         float sn, cs;
@@ -131,7 +134,7 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         fence_proxy_async();
         __syncthreads();
         if (tid == 0) {
-            const int n0 = min(ntiles, F32_STAGES);
+            const int n0 = min(ntiles, F32_STAGES - 1);
             for (int i = 0; i < n0; i++) issue_tile(i);
         }
     }
@@ -139,30 +142,44 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     // ---- Q fragments for this warp's 64 dims: 4 k-steps of 16, hi and mid ----
     // A (16x16, bf16): a0 (g, k=2t,2t+1)  a1 (g+8, same k)  a2 (g, k=2t+8,2t+9)  a3 (g+8, same k).
     // k -> dim map inside a 16-dim step: 2t -> t, 2t+1 -> t+4, 2t+8 -> t+8, 2t+9 -> t+12 (see the K fragments).
+    // The rows are first normalised / rotated in shared memory by compact loops (an unrolled build straight from
+    // the inputs runs once per segment from a cold instruction cache); the fragments are then plain loads.
     uint32_t qh[4][4], qm[4][4];
     {
-        const float *qbase = p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * (size_t)p.q_row_stride;
         const uint16_t *qnw = p.qnorm_w ? p.qnorm_w + (size_t)(it.kv_slot / p.n_seqs) * HEAD_DIM : nullptr;
-        if (qnw) head_inv_rms(qbase, group, p.q_row_stride, p.norm_eps, s_inv);
+        if (qnw) head_inv_rms(s_q, group, Q_STAGE_STRIDE, p.norm_eps, s_inv);
+        // in place: the thread that owns dims (d, d+1) below `half` also owns their partners (d + half, d + half + 1)
+#pragma unroll 1
+        for (int idx = tid; idx < 16 * (HEAD_DIM / 2); idx += 128) {
+            const int row = idx >> 7, d = (idx & 127) * 2;
+            if (row >= group) continue;  // rows past the group were staged as zeros
+            float *qr = s_q + row * Q_STAGE_STRIDE;
+            const float qinv = qnw ? s_inv[row] : 1.0f;
+            if (d < half) {
+                const float2 lo = load_norm2(qr, d, qinv, qnw), hi = load_norm2(qr, d + half, qinv, qnw);
+                *reinterpret_cast<float2 *>(qr + d) =
+                    make_float2(lo.x * s_cos[d] - hi.x * s_sin[d], lo.y * s_cos[d + 1] - hi.y * s_sin[d + 1]);
+                *reinterpret_cast<float2 *>(qr + d + half) =
+                    make_float2(lo.x * s_sin[d] + hi.x * s_cos[d], lo.y * s_sin[d + 1] + hi.y * s_cos[d + 1]);
+            } else if (d >= p.rotary_dim && qnw) {
+                *reinterpret_cast<float2 *>(qr + d) = load_norm2(qr, d, qinv, qnw);
+            }
+        }
+        __syncthreads();
 #pragma unroll
         for (int ks = 0; ks < 4; ks++) {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const int row = g + ((e & 1) ? 8 : 0);
                 const int d = 64 * warp + 16 * ks + t + ((e & 2) ? 8 : 0);
-                float xa = 0.0f, xb = 0.0f;
-                if (row < group) {
-                    const float *qr = qbase + (size_t)row * p.q_row_stride;
-                    const float qinv = qnw ? s_inv[row] : 1.0f;
-                    const float2 pa = load_rot2(qr, d & ~1, p.rotary_dim, half, s_cos, s_sin, qinv, qnw);
-                    const float2 pb = load_rot2(qr, (d + 4) & ~1, p.rotary_dim, half, s_cos, s_sin, qinv, qnw);
-                    xa = (d & 1) ? pa.y : pa.x;
-                    xb = (d & 1) ? pb.y : pb.x;
-                }
-                split_bf16x2(xa, xb, qh[ks][e], qm[ks][e]);
+                split_bf16x2(s_q[row * Q_STAGE_STRIDE + d], s_q[row * Q_STAGE_STRIDE + d + 4], qh[ks][e], qm[ks][e]);
             }
         }
     }
+
+    fence_proxy_async();  // the Q staging area goes back to the ring
+    __syncthreads();
+    if (tid == 0 && ntiles >= F32_STAGES) issue_tile(F32_STAGES - 1);
 
     float o[8][4];
 #pragma unroll
