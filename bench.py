@@ -49,8 +49,10 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")
     ap.add_argument("--batch", type=int, default=8, help="sequences")
-    ap.add_argument("--workload", default="stack", choices=["stack", "prefill"],
-                    help="stack: the decode stack (headline); prefill: 8192-token chunked prefill of one hybrid block")
+    ap.add_argument("--workload", default="stack", choices=["stack", "prefill", "matvec"],
+                    help="stack: the decode stack (headline); prefill: 8192-token chunked prefill of one hybrid block; "
+                         "matvec: the 4-bit projections around the attention sub-blocks of one hybrid block")
+    ap.add_argument("--vecs", type=int, default=1, help="input vectors per projection (--workload matvec)")
     ap.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "f32"], help="KV cache storage type")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -551,6 +553,121 @@ def run_prefill(args):
     return line
 
 
+# --------------------------------------------------------------------------- projection (matvec) workload
+def run_matvec(args):
+    """The 4-bit group-64 projections on either side of the attention sub-blocks of one hybrid block (3
+    GatedDeltaNet layers + 1 full-attention layer, hidden 4096) for one decode token (or --vecs tokens): per
+    full layer q_proj 4096->16384, k_proj and v_proj 4096->512, o_proj 8192->4096; per GatedDeltaNet layer
+    in_proj_qkv 4096->12288, in_proj_z 4096->8192, in_proj_a / in_proj_b 4096->64, out_proj 8192->4096.
+    A step = all 24 products in 8 launches (products that share their input go together); the weights of the block (258 MB) exceed L2, so every step streams them from HBM."""
+    import torch
+
+    import moeflux_b200 as M
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    K, W, NV = args.steps, args.warmup, args.vecs
+    full = [(4096, 16384), (4096, 512), (4096, 512), (8192, 4096)]
+    lin = [(4096, 12288), (4096, 8192), (4096, 64), (4096, 64), (8192, 4096)]
+    shapes = lin * 3 + full
+    ctx = M.Ctx(num_layers=4, max_seq=64, n_seqs=1, kv_dtype=M.KV_BF16)
+    stream = torch.cuda.Stream(device=dev)
+    ctx.set_stream(stream.cuda_stream)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2024)
+    ops = []
+    with torch.cuda.stream(stream):
+        for in_dim, out_dim in shapes:
+            w = torch.randint(-2**31, 2**31 - 1, (out_dim, in_dim // 8), device=dev, dtype=torch.int32, generator=gen)
+            sc = (torch.randn(out_dim, in_dim // 64, device=dev, generator=gen).abs() * 0.02 + 1e-3).bfloat16()
+            bi = (-8.0 * sc.float() + 0.01 * torch.randn(out_dim, in_dim // 64, device=dev, generator=gen)).bfloat16()
+            x = torch.randn(NV, in_dim, device=dev, generator=gen)
+            out = torch.empty(NV, out_dim, device=dev)
+            ops.append((w, sc, bi, in_dim, out_dim, x, out))
+    stream.synchronize()
+    weight_bytes = sum(o * i // 2 + 2 * 2 * o * (i // 64) for i, o in shapes)
+    io_bytes = sum(4 * NV * (i + o) for i, o in shapes)
+
+    # projections of a layer that share their input go into one launch (q/k/v_proj; in_proj_qkv/z/a/b), as the
+    # reference encodes them into one command buffer; o_proj / out_proj have their own input
+    groups = []
+    for base, n_in, n_all in [(0, 4, 5), (5, 4, 5), (10, 4, 5), (15, 3, 4)]:
+        groups.append(list(range(base, base + n_in)))
+        groups.append(list(range(base + n_in, base + n_all)))
+
+    def step():
+        for idx in groups:
+            sel = [ops[k] for k in idx]
+            ctx.dequant_matvec_4bit_multi_dev([o[0].data_ptr() for o in sel], [o[1].data_ptr() for o in sel],
+                                              [o[2].data_ptr() for o in sel], sel[0][3], [o[4] for o in sel],
+                                              sel[0][5].data_ptr(), NV, [o[6].data_ptr() for o in sel])
+
+    sampler = ClockSampler(0)
+    with torch.cuda.stream(stream):
+        for _ in range(W):
+            step()
+        stream.synchronize()
+    # the 24 launches of a step are a few microseconds each: replayed as one CUDA graph, as a decode loop would
+    graph = torch.cuda.CUDAGraph()
+    launches0 = ctx.launch_count
+    with torch.cuda.graph(graph, stream=stream):
+        step()
+    launches_per_step = ctx.launch_count - launches0
+    with torch.cuda.stream(stream):
+        graph.replay()
+        stream.synchronize()
+        sampler.start()
+        time.sleep(0.3)
+        t0 = time.time()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(K):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    ctx.synchronize()
+    clocks = sampler.stop(t0, time.time())
+    launches = launches_per_step * K
+    ms = e0.elapsed_time(e1) / K
+    # end to end: host vectors in, host results out, weights resident (they are model state)
+    hx = [torch.empty(NV, i).normal_().pin_memory() for i, _ in shapes]
+    ho = [torch.empty(NV, o).pin_memory() for _, o in shapes]
+
+    def e2e_step():
+        with torch.cuda.stream(stream):
+            for idx in groups:  # one input per group, every product's result back to the host
+                ops[idx[0]][5].copy_(hx[idx[0]], non_blocking=True)
+            step()
+            for k, op in enumerate(ops):
+                ho[k].copy_(op[6], non_blocking=True)
+            stream.synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    t1 = time.perf_counter()
+    for _ in range(K):
+        e2e_step()
+    dt = (time.perf_counter() - t1) / K
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+    achieved = (weight_bytes + io_bytes) / (ms * 1e-3) / 1e9
+    line = {"metric": "4-bit projection products/sec (attention sub-block projections of one hybrid block)",
+            "value": len(shapes) * NV / (ms * 1e-3), "unit": "matvec/s", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u4 weights, bf16 scales and biases, f32 vectors and accumulate", "data": "synthetic",
+            "config": {"workload": f"24 group-64 4-bit projections of a hybrid block (3 GatedDeltaNet + 1 full layer, hidden "
+                                   f"4096), {NV} vector(s) each; 258 MB of weights per step, larger than L2", "vecs": NV},
+            "roofline": {"bound": "hbm", "kernel": f"dequant_matvec_4bit_kernel<{NV}>", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)",
+                         "algorithmic_bytes_per_step": weight_bytes + io_bytes, "frac_of_8TBps": achieved / 8000.0},
+            "e2e": {"value": len(shapes) * NV / dt, "unit": "matvec/s", "h2d_bytes_per_step": sum(4 * NV * shapes[g[0]][0] for g in groups),
+                    "d2h_bytes_per_step": sum(4 * NV * o for _, o in shapes)},
+            "gpu_launches": int(launches), "clocks": clocks}
+    ctx.close()
+    return line
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -573,6 +690,10 @@ def main():
     if args.workload == "prefill":
         if rank == 0:
             print(json.dumps(run_prefill(args)), flush=True)
+        return
+    if args.workload == "matvec":
+        if rank == 0:
+            print(json.dumps(run_matvec(args)), flush=True)
         return
     line = run_ours(args, rank, world, local_rank)
     if rank == 0:

@@ -364,6 +364,42 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
                         int32_t kv_len, int32_t cap_rows, const float *q, const float *gate,
                         const void *k_cache, const void *v_cache, float *out, void *stream);
 
+/* ---- The step either side of the path: 4-bit affine-quantised projections ----
+ * Replaces dequant_matvec_4bit_cpu (crates/moeflux/src/riir/cpu_matvec.rs:83-171) and the
+ * GPU dispatch encode_matvec (riir/gpu_matvec.rs:84-129; kernels dequant_matvec_4bit_v3 /
+ * _fast, shaders/shaders.metal:251-340, and the batched form :667) for the q/k/v/o_proj,
+ * in_proj_qkv/z/a/b and out_proj products around the attention sub-block.
+ *   w_packed [out_dim][in_dim/8] u32: eight nibbles per word, least significant nibble =
+ *            lowest input feature;  scales, biases [out_dim][in_dim/64] bf16 bit patterns;
+ *   out[v][r] = sum_c (nibble(r,c) * scale[r][c/64] + bias[r][c/64]) * x[v][c]
+ * for n_vec (1..8) input vectors x [n_vec][in_dim] -> out [n_vec][out_dim], fp32, the
+ * weights read once per pass.  in_dim must be a positive multiple of 64 (the reference's
+ * InDimNotMultiple error).  One pass takes as many vectors as fit in shared memory
+ * (n_vec * in_dim * 4.125 bytes: all 8 at in_dim 4096, 6 at 8192, 3 at 16384); more
+ * vectors take further passes; in_dim itself is limited to 55,000 or so.
+ * _dev: device pointers (w_packed and x 16-byte aligned), asynchronous on mfc_stream(ctx).
+ * The host-pointer form stages the operands in device memory for the call (a hook for
+ * tests and bring-up, like mfc_sdpa).  Return 0 on success, -1 on error. */
+#define MFC_MATVEC_GROUP_SIZE 64
+#define MFC_MATVEC_MAX_VECS 8
+int mfc_dequant_matvec_4bit_dev(mfc_ctx *ctx, const uint32_t *w_packed, const uint16_t *scales,
+                                const uint16_t *biases, int32_t in_dim, int32_t out_dim, const float *x,
+                                int32_t n_vec, float *out);
+int mfc_dequant_matvec_4bit(mfc_ctx *ctx, const uint32_t *w_packed, const uint16_t *scales,
+                            const uint16_t *biases, int32_t in_dim, int32_t out_dim, const float *x,
+                            int32_t n_vec, float *out);
+/* Several matrices applied to the same input in one launch (the reference encodes such a
+ * batch of MatvecSpec into one command buffer: gpu_encode_batch_matvec, infer.m:1534-1542,
+ * riir/gpu_matvec.rs:84; e.g. q/k/v_proj of a full-attention layer, or in_proj_qkv/z/a/b of
+ * a GatedDeltaNet layer).  n_mat in 1..8 matrices of the same in_dim; the four tables are
+ * host arrays of n_mat device pointers, out_dims a host array; outs[m] is [n_vec][out_dims[m]].
+ * A launch has a fixed cost of several microseconds, more than streaming a 20 MB matrix takes. */
+#define MFC_MATVEC_MAX_MATS 8
+int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *ctx, int32_t n_mat, const uint32_t *const *w_packed,
+                                      const uint16_t *const *scales, const uint16_t *const *biases,
+                                      int32_t in_dim, const int32_t *out_dims, const float *x, int32_t n_vec,
+                                      float *const *outs);
+
 /* Tuning knobs (tests and sweeps): "gdn_rows" in {0,32,64,128} state rows per
  * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a launch aims for when it picks the KV chunk
  * length (0 = wave-aware automatic plan); "gqa_chunk" forces the chunk length (0 = automatic); "gdn_side_queue" (see

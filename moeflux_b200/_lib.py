@@ -99,6 +99,9 @@ SIGNATURES = {
     "mfc_snapshot_validate": (C.c_longlong, [C.POINTER(Config), _P, C.c_size_t]),
     "mfc_sdpa_static_dev": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P]),
     "mfc_join": (C.c_int, [_P]),
+    "mfc_dequant_matvec_4bit_dev": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
+    "mfc_dequant_matvec_4bit": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
+    "mfc_dequant_matvec_4bit_multi_dev": (C.c_int, [_P, C.c_int32, _P, _P, _P, C.c_int32, _P, _P, C.c_int32, _P]),
     "mfc_set_tuning": (C.c_int, [_P, C.c_char_p, C.c_int]),
     "mfc_launch_count": (C.c_longlong, [_P]),
 }

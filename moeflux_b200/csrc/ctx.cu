@@ -107,6 +107,8 @@ struct mfc_ctx {
     int gdn_rows = 0;  // 0: chosen per launch from the item count
     int gqa_target_ctas = 0;  // 0: wave-aware plan; > 0: aim for this many CTAs per launch
     int gqa_slots = 296;      // CTAs resident at once (2 per SM)
+    int n_sms = 148;
+    size_t smem_optin = 227 * 1024;
     int gqa_forced_chunk = 0;
     long long launches = 0;
     std::string err;
@@ -656,6 +658,8 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     if (c->gqa_target_ctas < 0) c->gqa_target_ctas = 0;
     if (c->gqa_target_ctas > 8192) c->gqa_target_ctas = 8192;
     c->gqa_slots = 2 * prop.multiProcessorCount;
+    c->n_sms = prop.multiProcessorCount;
+    c->smem_optin = prop.sharedMemPerBlockOptin;
     c->max_parts = 8192 + g.max_batch * g.num_kv_heads;  // one slot per (unit, CTA) pair: units + CTAs at most
 
     bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
@@ -760,6 +764,118 @@ int mfc_synchronize(mfc_ctx *c) {
 }
 
 long long mfc_launch_count(const mfc_ctx *c) { return c ? c->launches : 0; }
+
+// ---------------------------------------------------------------- projections: 4-bit dequant matvec
+
+namespace {
+int check_matvec_args(mfc_ctx *c, const void *w, const void *s, const void *b, int32_t in_dim, int32_t out_dim,
+                      const float *x, int32_t n_vec, const float *out) {
+    if (!w || !s || !b || !x || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (in_dim <= 0 || in_dim % MFC_MATVEC_GROUP_SIZE != 0) {  // CpuMatvecError::InDimNotMultiple
+        fail(c, "in_dim " + std::to_string(in_dim) + " is not a positive multiple of the group size 64");
+        return -1;
+    }
+    if (out_dim <= 0 || n_vec < 1 || n_vec > MFC_MATVEC_MAX_VECS) {
+        fail(c, "out_dim must be positive and n_vec in [1, 8]");
+        return -1;
+    }
+    if (dequant_matvec_4bit_smem(in_dim, 1) > c->smem_optin) {
+        fail(c, "in_dim too large for the shared-memory staging of x (" +
+                    std::to_string(dequant_matvec_4bit_smem(in_dim, 1)) + " bytes needed)");
+        return -1;
+    }
+    if (((uintptr_t)w & 15) || ((uintptr_t)x & 15)) {
+        fail(c, "w_packed and x must be 16-byte aligned");
+        return -1;
+    }
+    return 0;
+}
+}  // namespace
+
+int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *c, int32_t n_mat, const uint32_t *const *w_packed,
+                                      const uint16_t *const *scales, const uint16_t *const *biases, int32_t in_dim,
+                                      const int32_t *out_dims, const float *x, int32_t n_vec, float *const *outs) {
+    if (!c) return -1;
+    if (n_mat < 1 || n_mat > MATVEC_MAX_MATS || !w_packed || !scales || !biases || !out_dims || !outs) {
+        fail(c, "n_mat must be in [1, 8] and the pointer tables non-NULL");
+        return -1;
+    }
+    MatvecBatch mb;
+    memset(&mb, 0, sizeof(mb));
+    mb.n_mat = n_mat;
+    for (int m = 0; m < n_mat; m++) {
+        if (check_matvec_args(c, w_packed[m], scales[m], biases[m], in_dim, out_dims[m], x, n_vec, outs[m])) return -1;
+        mb.w[m] = w_packed[m];
+        mb.scales[m] = scales[m];
+        mb.biases[m] = biases[m];
+        mb.out[m] = outs[m];
+        mb.out_dim[m] = out_dims[m];
+    }
+    cudaSetDevice(c->cfg.device);
+    // as many vectors per pass over the weights as the staging of x allows
+    int per_pass = n_vec;
+    while (per_pass > 1 && dequant_matvec_4bit_smem(in_dim, per_pass) > c->smem_optin) per_pass--;
+    for (int v0 = 0; v0 < n_vec; v0 += per_pass) {
+        const int nv = n_vec - v0 < per_pass ? n_vec - v0 : per_pass;
+        MatvecBatch pass = mb;
+        for (int m = 0; m < n_mat; m++) pass.out[m] = outs[m] + (size_t)v0 * out_dims[m];
+        CK(launch_dequant_matvec_4bit(pass, x + (size_t)v0 * in_dim, in_dim, nv, c->n_sms, c->stream));
+        c->launches += 1;
+    }
+    return 0;
+}
+
+int mfc_dequant_matvec_4bit_dev(mfc_ctx *c, const uint32_t *w_packed, const uint16_t *scales, const uint16_t *biases,
+                                int32_t in_dim, int32_t out_dim, const float *x, int32_t n_vec, float *out) {
+    return mfc_dequant_matvec_4bit_multi_dev(c, 1, &w_packed, &scales, &biases, in_dim, &out_dim, x, n_vec, &out);
+}
+
+int mfc_dequant_matvec_4bit(mfc_ctx *c, const uint32_t *w_packed, const uint16_t *scales, const uint16_t *biases,
+                            int32_t in_dim, int32_t out_dim, const float *x, int32_t n_vec, float *out) {
+    if (!c) return -1;
+    if (!w_packed || !scales || !biases || !x || !out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (in_dim <= 0 || in_dim % MFC_MATVEC_GROUP_SIZE != 0 || out_dim <= 0 || n_vec < 1 || n_vec > MFC_MATVEC_MAX_VECS) {
+        fail(c, "in_dim must be a positive multiple of 64, out_dim positive, n_vec in [1, 8]");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    // a hook for tests and bring-up, not a hot path: the operands are staged in device memory for this call only
+    const size_t wb = sizeof(uint32_t) * (size_t)out_dim * (in_dim / 8), sb = sizeof(uint16_t) * (size_t)out_dim * (in_dim / 64);
+    const size_t xb = sizeof(float) * (size_t)n_vec * in_dim, ob = sizeof(float) * (size_t)n_vec * out_dim;
+    uint8_t *d = nullptr;
+    const size_t o_w = 0, o_s = (wb + 255) & ~(size_t)255, o_b = (o_s + sb + 255) & ~(size_t)255,
+                 o_x = (o_b + sb + 255) & ~(size_t)255, o_o = (o_x + xb + 255) & ~(size_t)255;
+    CK(cudaMalloc(&d, o_o + ob));
+    int rc = -1;
+    do {
+        if (cudaMemcpyAsync(d + o_w, w_packed, wb, cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+            cudaMemcpyAsync(d + o_s, scales, sb, cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+            cudaMemcpyAsync(d + o_b, biases, sb, cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+            cudaMemcpyAsync(d + o_x, x, xb, cudaMemcpyHostToDevice, c->stream) != cudaSuccess) {
+            fail(c, "host to device copy failed");
+            break;
+        }
+        if (mfc_dequant_matvec_4bit_dev(c, (const uint32_t *)(d + o_w), (const uint16_t *)(d + o_s),
+                                        (const uint16_t *)(d + o_b), in_dim, out_dim, (const float *)(d + o_x), n_vec,
+                                        (float *)(d + o_o)))
+            break;
+        if (cudaMemcpyAsync(out, d + o_o, ob, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess ||
+            cudaStreamSynchronize(c->stream) != cudaSuccess) {
+            fail(c, "device to host copy failed");
+            break;
+        }
+        rc = 0;
+    } while (0);
+    cudaStreamSynchronize(c->stream);
+    cudaFree(d);
+    return rc;
+}
 
 int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
     if (!c || !key) return -1;

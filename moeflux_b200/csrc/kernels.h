@@ -174,6 +174,22 @@ struct GdnPrefillMaps {
 };
 cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, const GdnPrefillMaps &m, cudaStream_t stream);
 
+// 4-bit group-64 dequant matvec (matvec.cu): for every matrix m of the batch and vector v,
+// out[m][v][r] = sum_c (nibble * scale + bias)(m; r, c) * x[v][c]; the matrices share in_dim and x; n_vec in 1..8.
+constexpr int MATVEC_MAX_MATS = 8;
+struct MatvecBatch {
+    int n_mat;
+    const uint32_t *w[MATVEC_MAX_MATS];
+    const uint16_t *scales[MATVEC_MAX_MATS], *biases[MATVEC_MAX_MATS];
+    float *out[MATVEC_MAX_MATS];
+    int out_dim[MATVEC_MAX_MATS];
+    int group_begin[MATVEC_MAX_MATS];  // filled by the launcher: first row group of each matrix
+    int total_groups;
+};
+size_t dequant_matvec_4bit_smem(int in_dim, int n_vec);
+cudaError_t launch_dequant_matvec_4bit(MatvecBatch mb, const float *x, int in_dim, int n_vec, int n_sms,
+                                       cudaStream_t stream);
+
 // Per-thread message of the last failure that had no context (ctx.cu).
 std::string &no_ctx_error();
 

@@ -374,6 +374,43 @@ class Ctx:
         self._check(self._lib.mfc_sdpa(self._h, kv_len, _fp(q), _fp(gate), _fp(kc), _fp(vc), _fp(out)), "mfc_sdpa")
         return out
 
+    # -- projections: 4-bit group-64 dequant matvec (cpu_matvec.rs:83, gpu_matvec.rs:84) ------
+    def dequant_matvec_4bit(self, packed, scales, biases, in_dim: int, out_dim: int, x) -> np.ndarray:
+        """out[v][r] = sum_c (nibble * scale + bias)(r, c) * x[v][c]; x is [in_dim] or [n_vec][in_dim]."""
+        pk = np.ascontiguousarray(packed, dtype=np.uint32).reshape(-1)
+        sc = np.ascontiguousarray(scales, dtype=np.uint16).reshape(-1)
+        bi = np.ascontiguousarray(biases, dtype=np.uint16).reshape(-1)
+        xv = np.ascontiguousarray(x, dtype=np.float32)
+        single = xv.ndim == 1
+        xv = xv.reshape(1, -1) if single else xv
+        n_vec = xv.shape[0]
+        if in_dim > 0 and in_dim % 64 == 0 and out_dim > 0:
+            for name, got, exp in (("packed", pk.size, out_dim * in_dim // 8), ("scales", sc.size, out_dim * in_dim // 64),
+                                   ("biases", bi.size, out_dim * in_dim // 64), ("x", xv.shape[1], in_dim)):
+                if got != exp:
+                    raise ValueError(f"slice length mismatch on '{name}': got {got} elements, expected {exp}")
+        out = np.empty((n_vec, max(out_dim, 0)), np.float32)
+        rc = self._lib.mfc_dequant_matvec_4bit(self._h, pk.ctypes.data, sc.ctypes.data, bi.ctypes.data, in_dim, out_dim,
+                                               _fp(xv), n_vec, _fp(out))
+        self._check(rc, "mfc_dequant_matvec_4bit")
+        return out[0] if single else out
+
+    def dequant_matvec_4bit_dev(self, packed_ptr, scales_ptr, biases_ptr, in_dim, out_dim, x_ptr, n_vec, out_ptr):
+        rc = self._lib.mfc_dequant_matvec_4bit_dev(self._h, packed_ptr, scales_ptr, biases_ptr, in_dim, out_dim, x_ptr,
+                                                   n_vec, out_ptr)
+        self._check(rc, "mfc_dequant_matvec_4bit_dev")
+
+    def dequant_matvec_4bit_multi_dev(self, packed_ptrs, scales_ptrs, biases_ptrs, in_dim, out_dims, x_ptr, n_vec, out_ptrs):
+        """Up to 8 matrices of the same in_dim applied to the same x in one launch (device pointers)."""
+        n = len(out_dims)
+        if not (len(packed_ptrs) == len(scales_ptrs) == len(biases_ptrs) == len(out_ptrs) == n):
+            raise ValueError("dequant_matvec_4bit_multi_dev: tables of different length")
+        tab = lambda ptrs: (C.c_void_p * n)(*[int(p) for p in ptrs])
+        dims = (C.c_int32 * n)(*[int(d) for d in out_dims])
+        rc = self._lib.mfc_dequant_matvec_4bit_multi_dev(self._h, n, tab(packed_ptrs), tab(scales_ptrs), tab(biases_ptrs),
+                                                         in_dim, dims, x_ptr, n_vec, tab(out_ptrs))
+        self._check(rc, "mfc_dequant_matvec_4bit_multi_dev")
+
     def linear_attn_step_stateless(self, layer: int, qkv, z, alpha, beta, conv_state, ssm_state):
         """Returns (out, new_conv_state, new_ssm_state); inputs are not modified."""
         qkv = _f32(qkv, self.conv_dim, "qkv")

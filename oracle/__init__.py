@@ -166,6 +166,26 @@ def rms_norm_per_head(w_bits, num_heads: int, head_dim: int, x, eps: float = 1e-
     return x
 
 
+def dequant_matvec_4bit(packed, scales, biases, in_dim: int, out_dim: int, x) -> np.ndarray:
+    """cpu_matvec.rs:83-171.  Raises ValueError where the reference returns an error
+    (in_dim not a multiple of 64, slice lengths that do not match the shape)."""
+    pk = np.ascontiguousarray(packed, dtype=np.uint32).reshape(-1)
+    sc, scp = _u16(np.asarray(scales).reshape(-1))
+    bi, bip = _u16(np.asarray(biases).reshape(-1))
+    xv, xp = _f(np.asarray(x).reshape(-1))
+    if in_dim <= 0 or in_dim % 64 != 0:
+        raise ValueError(f"in_dim {in_dim} is not a multiple of GROUP_SIZE=64")
+    for name, got, exp in (("packed", pk.size, out_dim * in_dim // 8), ("scales", sc.size, out_dim * in_dim // 64),
+                           ("biases", bi.size, out_dim * in_dim // 64), ("x", xv.size, in_dim)):
+        if got != exp:
+            raise ValueError(f"slice length mismatch on '{name}': got {got} elements, expected {exp}")
+    out = np.zeros(out_dim, np.float32)
+    if lib().mfo_dequant_matvec_4bit(pk.ctypes.data_as(C.POINTER(C.c_uint32)), scp, bip, int(in_dim), int(out_dim), xp,
+                                     out.ctypes.data_as(C.POINTER(C.c_float))):
+        raise ValueError("dequant_matvec_4bit: bad arguments")
+    return out
+
+
 def split_q_gate(q_proj, g: Geometry = A17B):
     qp_, p = _f(q_proj)
     q = np.zeros(g.q_dim, np.float32)

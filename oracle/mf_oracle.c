@@ -11,7 +11,9 @@
  * tests for this path (its tests are tolerance-based differentials between its
  * C and Rust engines on Apple hardware), and neither engine builds on Linux.
  * The restatement is pinned only by closed-form known answers derived from the
- * reference's formulas (see tests/test_oracle_kat.py).
+ * reference's formulas (see tests/test_oracle_kat.py).  One exception is PINNED:
+ * mfo_dequant_matvec_4bit reproduces the known answers of the reference's own unit
+ * tests for that function (crates/moeflux/src/riir/cpu_matvec.rs:370-451).
  *
  * Every function cites the reference source it follows, by path inside the
  * reference project.  Rust `mul_add` call sites are kept as fmaf(); all other
@@ -126,6 +128,43 @@ MFO_API int mfo_rms_norm_per_head(const uint16_t *w_bf16, int num_heads, int hea
         for (int i = 0; i < head_dim; i++) sum_sq += xh[i] * xh[i];
         float inv_rms = 1.0f / sqrtf(sum_sq / (float)head_dim + eps);
         for (int i = 0; i < head_dim; i++) xh[i] = xh[i] * inv_rms * bf16_to_f32(w_bf16[i]);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------
+ * 4-bit group-64 affine dequant matvec.  crates/moeflux/src/riir/cpu_matvec.rs:83-171
+ * (GPU twin: crates/moeflux/shaders/shaders.metal:48-91): per row, groups in order,
+ * words in order, nibbles least significant first; w = nibble.mul_add(scale, bias),
+ * acc = w.mul_add(x, acc).  Rows are independent (rayon there, OpenMP here).
+ * Returns -1 for the reference's InDimNotMultiple / bad-argument errors.
+ * ---------------------------------------------------------------------- */
+#define MFO_GROUP_SIZE 64
+MFO_API int mfo_dequant_matvec_4bit(const uint32_t *packed, const uint16_t *scales, const uint16_t *biases,
+                                    int in_dim, int out_dim, const float *x, float *out) {
+    if (!packed || !scales || !biases || !x || !out || in_dim <= 0 || out_dim <= 0) return -1;
+    if (in_dim % MFO_GROUP_SIZE != 0) return -1;
+    const int in_packed = in_dim / 8, in_groups = in_dim / MFO_GROUP_SIZE, packed_per_group = MFO_GROUP_SIZE / 8;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < out_dim; r++) {
+        const uint32_t *packed_row = packed + (size_t)r * in_packed;
+        const uint16_t *scale_row = scales + (size_t)r * in_groups;
+        const uint16_t *bias_row = biases + (size_t)r * in_groups;
+        float acc = 0.0f;
+        for (int g = 0; g < in_groups; g++) {
+            const float scale = bf16_to_f32(scale_row[g]);
+            const float bias = bf16_to_f32(bias_row[g]);
+            for (int p = 0; p < packed_per_group; p++) {
+                const uint32_t word = packed_row[g * packed_per_group + p];
+                const float *x_chunk = x + (size_t)g * MFO_GROUP_SIZE + p * 8;
+                for (int n = 0; n < 8; n++) {
+                    const float nibble = (float)((word >> (n * 4)) & 0xFu);
+                    const float w = fmaf(nibble, scale, bias);
+                    acc = fmaf(w, x_chunk[n], acc);
+                }
+            }
+        }
+        out[r] = acc;
     }
     return 0;
 }

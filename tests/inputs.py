@@ -35,6 +35,15 @@ def normal(r, shape, std=1.0):
     return (r.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
 
 
+def quant_weights(r, in_dim: int, out_dim: int):
+    """A 4-bit group-64 affine-quantised matrix as the reference's converter lays it out: packed words of eight
+    random nibbles, per-group scale ~ |N(0, 0.02)| + 1e-3 and bias = -8 * scale + N(0, 0.01), both bf16."""
+    packed = r.integers(0, 1 << 32, size=out_dim * in_dim // 8, dtype=np.uint64).astype(np.uint32)
+    sc = np.abs(normal(r, out_dim * in_dim // 64, 0.02)) + np.float32(1e-3)
+    bi = -8.0 * sc + normal(r, out_dim * in_dim // 64, 0.01)
+    return packed, f32_to_bf16_bits(sc), f32_to_bf16_bits(bi)
+
+
 def gdn_weights(r, g: Geometry = A17B):
     """conv_w ~ N(0, 0.5) bf16, A_log ~ U(0, 2.7), dt_bias ~ N(0,1) bf16, norm_w ~ 1 + N(0, 0.1) bf16."""
     conv_w = f32_to_bf16_bits(normal(r, (g.conv_dim, g.conv_kernel_size), 0.5))

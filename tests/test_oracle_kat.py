@@ -255,3 +255,42 @@ def test_split_q_gate_and_per_head_norm():
     xd = q.reshape(G.num_attn_heads, -1).astype(np.float64)
     ref = xd / np.sqrt((xd * xd).mean(1, keepdims=True) + 1e-6) * O.bf16_bits_to_f32(w)
     assert np.max(np.abs(y - ref)) < 1e-5
+
+
+# ---- 4-bit dequant matvec: the reference's own known answers (crates/moeflux/src/riir/cpu_matvec.rs:370-451) ----
+def test_dequant_matvec_all_ones():
+    # every nibble 1, scale 1.0 (bf16 0x3F80), bias 0: an all-ones row against x = ones gives 64
+    out = O.dequant_matvec_4bit(np.full(8, 0x11111111, np.uint32), [0x3F80], [0x0000], 64, 1, np.ones(64, np.float32))
+    assert out.tolist() == [64.0]
+
+
+def test_dequant_matvec_zero_input_yields_zero_output():
+    out = O.dequant_matvec_4bit(np.full(16, 0xFFFFFFFF, np.uint32), [0x3F80] * 2, [0x3F80] * 2, 64, 2,
+                                np.zeros(64, np.float32))
+    assert out.tolist() == [0.0, 0.0]
+
+
+def test_dequant_matvec_bias_only_path():
+    # nibble 0, scale 5.0 (0x40A0), bias 2.0 (0x4000): every weight is 2, the sum is 128
+    out = O.dequant_matvec_4bit(np.zeros(8, np.uint32), [0x40A0], [0x4000], 64, 1, np.ones(64, np.float32))
+    assert out.tolist() == [128.0]
+
+
+def test_dequant_matvec_errors_like_the_reference():
+    with pytest.raises(ValueError, match="packed"):  # SliceLen { field: "packed", got: 7, expected: 8 }
+        O.dequant_matvec_4bit(np.zeros(7, np.uint32), [0x3F80], [0x0000], 64, 1, np.ones(64, np.float32))
+    with pytest.raises(ValueError, match="multiple"):  # InDimNotMultiple
+        O.dequant_matvec_4bit(np.zeros(12, np.uint32), [0x3F80], [0x0000], 96, 1, np.ones(96, np.float32))
+
+
+def test_dequant_matvec_against_float64_restatement():
+    r = I.rng(31)
+    in_dim, out_dim = 256, 37
+    packed, scales, biases = I.quant_weights(r, in_dim, out_dim)
+    x = I.normal(r, in_dim)
+    out = O.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    nib = ((packed.reshape(out_dim, in_dim // 8, 1) >> (4 * np.arange(8, dtype=np.uint32))) & 0xF).reshape(out_dim, in_dim)
+    s = np.repeat(O.bf16_bits_to_f32(scales).reshape(out_dim, -1), 64, axis=1).astype(np.float64)
+    b = np.repeat(O.bf16_bits_to_f32(biases).reshape(out_dim, -1), 64, axis=1).astype(np.float64)
+    ref = ((nib * s + b) * x.astype(np.float64)).sum(1)
+    assert np.max(np.abs(out - ref)) <= 1e-5 * max(1.0, np.max(np.abs(ref)))
