@@ -15,10 +15,10 @@
 //     shared memory once per CTA;
 //   * a lane owns 16-byte chunks (32 nibbles, half a group) lane, lane+32, ... of FOUR rows
 //     at a time, so a chunk of x read from shared memory serves four rows;
-//   * a nibble n becomes the float 1 + n/16 with one shift and one LOP3 (its four bits are
-//     placed at the top of the mantissa of 1.0f), so per nibble there is shift, LOP3, FMA;
-//     with D = sum (1 + n/16) x and X = sum x over the chunk,
-//     sum (n s + b) x = 16 s (D - X) + b X   (D - X cancels at most ~2 bits).
+//   * a nibble n becomes the float 1 + n/128 by byte surgery (three ALU operations per word of eight nibbles,
+//     then one PRMT per nibble), so per nibble there is about one ALU operation and one FMA;
+//     with D = sum (1 + n/128) x and X = sum x over the chunk,
+//     sum (n s + b) x = 128 s (D - X) + b X   (D - X cancels ~5 bits of the 24).
 #include <stdint.h>
 
 #include "common.cuh"
@@ -32,18 +32,27 @@ constexpr int MV_ROWS = 4;      // rows a lane works on at a time
 constexpr int MV_WARPS = 8;     // warps per CTA
 constexpr int MV_THREADS = MV_WARPS * 32;
 
-// nibble j (0..7) of w as the float 1 + n/16
-template <int J>
-__device__ __forceinline__ float nib_float(uint32_t w) {
-    constexpr int SH = 19 - 4 * J;  // nibble to bits 19..22
-    const uint32_t v = SH >= 0 ? (w << (SH >= 0 ? SH : 0)) : (w >> (SH < 0 ? -SH : 0));
-    return __uint_as_float((v & 0x00780000u) | 0x3f800000u);
+// The eight nibbles of a packed word as the floats 1 + n/128: with the nibble in the low half of byte 2 and the
+// constant 0x80 in its high half, the bit pattern is 0x3F80'0000 | n << 16.  Two masks put 0x80 | n into every byte
+// (three ALU operations per word), then one PRMT per nibble assembles the float: byte 3 = 0x3F, byte 2 = 0x80 | n.
+__device__ __forceinline__ void nib_floats(uint32_t w, float (&f)[8]) {
+    const uint32_t lo = (w & 0x0f0f0f0fu) | 0x80808080u;         // nibbles 0, 2, 4, 6
+    const uint32_t hi = ((w >> 4) & 0x0f0f0f0fu) | 0x80808080u;  // nibbles 1, 3, 5, 7
+    constexpr uint32_t K = 0x0000003fu;                          // byte 4 of the PRMT pair = 0x3F, bytes 5-7 = 0
+    f[0] = __uint_as_float(__byte_perm(lo, K, 0x4055));
+    f[1] = __uint_as_float(__byte_perm(hi, K, 0x4055));
+    f[2] = __uint_as_float(__byte_perm(lo, K, 0x4155));
+    f[3] = __uint_as_float(__byte_perm(hi, K, 0x4155));
+    f[4] = __uint_as_float(__byte_perm(lo, K, 0x4255));
+    f[5] = __uint_as_float(__byte_perm(hi, K, 0x4255));
+    f[6] = __uint_as_float(__byte_perm(lo, K, 0x4355));
+    f[7] = __uint_as_float(__byte_perm(hi, K, 0x4355));
 }
 
-template <int NV> struct MvDepth { static constexpr int value = NV == 1 ? 4 : NV <= 2 ? 2 : 1; };  // 16-byte chunks per row a lane has in flight
+template <int NV> struct MvDepth { static constexpr int value = NV <= 2 ? 2 : 1; };  // 16-byte chunks per row a lane has in flight
 
 template <int NV>
-__global__ void __launch_bounds__(MV_THREADS)
+__global__ void __launch_bounds__(MV_THREADS, NV <= 2 ? 2 : 1)
 dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *__restrict__ x, int in_dim) {
     extern __shared__ __align__(16) float smem_f[];
     float *xs = smem_f;                    // [NV][in_dim]
@@ -109,7 +118,7 @@ dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *
     }
     __syncthreads();
 
-    // D = sum over the chunk of (1 + n/16) x, for MV_ROWS rows and NV vectors
+    // D = sum over the chunk of (1 + n/128) x, for MV_ROWS rows and NV vectors
     auto chunk_dot = [&](const Chunk &ch, int c, float (&acc)[MV_ROWS][NV]) {
         float d[MV_ROWS][NV];
 #pragma unroll
@@ -129,8 +138,8 @@ dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *
 #pragma unroll
             for (int r = 0; r < MV_ROWS; r++) {
                 const uint32_t word = q == 0 ? ch.w[r].x : q == 1 ? ch.w[r].y : q == 2 ? ch.w[r].z : ch.w[r].w;
-                const float f[8] = {nib_float<0>(word), nib_float<1>(word), nib_float<2>(word), nib_float<3>(word),
-                                    nib_float<4>(word), nib_float<5>(word), nib_float<6>(word), nib_float<7>(word)};
+                float f[8];
+                nib_floats(word, f);
 #pragma unroll
                 for (int v = 0; v < NV; v++)
 #pragma unroll
@@ -142,7 +151,7 @@ dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *
             const float xsum = xh[v * n_chunks + c];
 #pragma unroll
             for (int r = 0; r < MV_ROWS; r++)
-                acc[r][v] += fmaf(16.0f * bf16_bits_to_f32(ch.sc[r]), d[r][v] - xsum, bf16_bits_to_f32(ch.bi[r]) * xsum);
+                acc[r][v] += fmaf(128.0f * bf16_bits_to_f32(ch.sc[r]), d[r][v] - xsum, bf16_bits_to_f32(ch.bi[r]) * xsum);
         }
     };
 
