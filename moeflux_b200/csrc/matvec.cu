@@ -189,6 +189,213 @@ dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *
     }
 }
 
+// ------------------------------------------------------------------ several vectors: tensor cores
+// With n_vec >= 2 the CUDA-core kernel above spends one FMA per nibble and vector and is bound by instruction
+// issue, so batching vectors buys nothing.  Here the vectors are the N = 8 columns of mma.sync m16n8k16 (unused
+// columns are zero), 16 rows of W are the M rows and 16 nibbles the K step:
+//   * a nibble n enters as the bf16 16 + n = 0x4180 | n << 3, which is exact: one shift and one LOP3 give the
+//     bf16x2 {16 + n_j, 16 + n_(j+4)} of a word (a larger offset, e.g. 128 + n, would cost accuracy below);
+//   * x enters as a two-piece bf16 expansion (hi + mid, two MMAs per step), staged once per CTA in shared
+//     memory in fragment order; the K index of the MMA is permuted to fit the nibble pairs above;
+//   * per group of 64 features the 16 x 8 accumulator D = sum (16 + n) x is folded into the result as
+//     s (D - 16 X) + b X with X = sum x over the group (cancels under 2 bits);
+//   * a lane reads 8 bytes per row and group (a quad reads one 32-byte sector), eight groups in flight.
+// The MMA sums over K, so every lane ends with finished outputs: rows g, g+8 x vectors 2t, 2t+1.
+constexpr int MM_WARPS = 8;
+constexpr int MM_THREADS = MM_WARPS * 32;
+constexpr int MM_DEPTH = 8;  // groups of 64 features a lane has in flight
+
+__device__ __forceinline__ void split_bf16x2_mv(float x0, float x1, uint32_t &hi, uint32_t &mid) {
+    hi = pack_bf16x2(x0, x1);
+    mid = pack_bf16x2(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xffff0000u));
+}
+
+// ks = 1, 2, 4 or 8 warps share a tile of 16 rows, each taking a contiguous range of groups (so that short
+// launches still fill every warp slot of the GPU); their partial results are added in a fixed order.
+template <int NV>
+__global__ void __launch_bounds__(MM_THREADS, NV <= 3 ? 2 : 1)
+dequant_matvec_4bit_mma_kernel(const __grid_constant__ MatvecBatch mb, const float *__restrict__ x, int in_dim, int ks) {
+    extern __shared__ __align__(16) uint8_t smem_b[];
+    // B fragments: [group][step 0/1][t][g < NV] x 32 bytes {hi: m1b0, m1b1, m2b0, m2b1 | mid: the same}
+    uint4 *xb = reinterpret_cast<uint4 *>(smem_b);
+    const int n_groups = in_dim >> 6;
+    float *xg = reinterpret_cast<float *>(smem_b + (size_t)n_groups * 8 * NV * 32);  // [NV][n_groups] group sums
+    float4 *red = reinterpret_cast<float4 *>(xg + NV * n_groups);                     // [MM_WARPS][32] partial results
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int row_stride_w = in_dim >> 3;
+
+    // ---- stage x: entry e = (group, step, t) of vector v covers x[v][64 group + 16 t + 8 step + 0..7] ----
+    const int n_entries = n_groups * 8;
+    for (int i0 = 0; i0 < NV * n_entries; i0 += 2 * MM_THREADS) {
+        float4 a[2], b[2];
+        int vv[2], ee[2];
+        bool in[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {  // two entries (four 16-byte loads) in flight per thread
+            const int i = i0 + u * MM_THREADS + tid;
+            in[u] = i < NV * n_entries;
+            vv[u] = in[u] ? i / n_entries : 0;
+            ee[u] = in[u] ? i - vv[u] * n_entries : 0;
+            const int gi = ee[u] >> 3, st = (ee[u] >> 2) & 1, tt = ee[u] & 3;
+            const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)vv[u] * in_dim + 64 * gi + 16 * tt + 8 * st);
+            a[u] = in[u] ? __ldg(src) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            b[u] = in[u] ? __ldg(src + 1) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            if (in[u]) {
+                uint32_t h[4], m[4];
+                split_bf16x2_mv(a[u].x, b[u].x, h[0], m[0]);  // MMA 1, b0: k slots (2t, 2t+1)   <- features 0, 4
+                split_bf16x2_mv(a[u].y, b[u].y, h[1], m[1]);  // MMA 1, b1: k slots (2t+8, 2t+9) <- features 1, 5
+                split_bf16x2_mv(a[u].z, b[u].z, h[2], m[2]);  // MMA 2, b0                        <- features 2, 6
+                split_bf16x2_mv(a[u].w, b[u].w, h[3], m[3]);  // MMA 2, b1                        <- features 3, 7
+                uint4 *dst = xb + ((size_t)ee[u] * NV + vv[u]) * 2;
+                dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                dst[1] = make_uint4(m[0], m[1], m[2], m[3]);
+            }
+            // the eight entries of a group sit in eight consecutive threads
+            float sm = ((a[u].x + a[u].y) + (a[u].z + a[u].w)) + ((b[u].x + b[u].y) + (b[u].z + b[u].w));
+            sm += __shfl_xor_sync(0xffffffffu, sm, 1);
+            sm += __shfl_xor_sync(0xffffffffu, sm, 2);
+            sm += __shfl_xor_sync(0xffffffffu, sm, 4);
+            if ((tid & 7) == 0 && in[u]) xg[vv[u] * n_groups + (ee[u] >> 3)] = sm;
+        }
+    }
+    __syncthreads();
+
+    const int tiles_total = mb.total_groups;  // here: tiles of 16 rows (see the launcher)
+    const int tiles_per_cta = MM_WARPS / ks;
+    const int tile_in_cta = warp / ks, split = warp - tile_in_cta * ks;
+    const int gps = (n_groups + ks - 1) / ks;
+    const int g_begin = split * gps, g_end = min(g_begin + gps, n_groups);
+    for (int tile0 = blockIdx.x * tiles_per_cta; tile0 < tiles_total; tile0 += gridDim.x * tiles_per_cta) {
+        const int tile = tile0 + tile_in_cta;
+        const bool active = tile < tiles_total;
+        // tile -> matrix (tiles never straddle two matrices: the launcher counts them per matrix)
+        int m = 0;
+#pragma unroll
+        for (int k = 1; k < MATVEC_MAX_MATS; k++)
+            if (k < mb.n_mat && tile >= mb.group_begin[k]) m = k;
+        const int row0 = active ? (tile - mb.group_begin[m]) * 16 : 0;
+        const int out_dim = mb.out_dim[m];
+        float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // (row g, vec 2t), (row g, vec 2t+1), (row g+8, ...), (row g+8, ...)
+        if (active) {
+            const int r_lo = min(row0 + g, out_dim - 1), r_hi = min(row0 + g + 8, out_dim - 1);  // clamped, not stored
+            const uint2 *w_lo = reinterpret_cast<const uint2 *>(mb.w[m] + (size_t)r_lo * row_stride_w) + t;
+            const uint2 *w_hi = reinterpret_cast<const uint2 *>(mb.w[m] + (size_t)r_hi * row_stride_w) + t;
+            const uint16_t *s_lo = mb.scales[m] + (size_t)r_lo * n_groups, *s_hi = mb.scales[m] + (size_t)r_hi * n_groups;
+            const uint16_t *b_lo = mb.biases[m] + (size_t)r_lo * n_groups, *b_hi = mb.biases[m] + (size_t)r_hi * n_groups;
+            for (int g0 = g_begin; g0 < g_end; g0 += MM_DEPTH) {
+                uint2 wl[MM_DEPTH], wh[MM_DEPTH];
+                uint16_t sl[MM_DEPTH], sh[MM_DEPTH], bl[MM_DEPTH], bh[MM_DEPTH];
+#pragma unroll
+                for (int k = 0; k < MM_DEPTH; k++) {
+                    const int gi = min(g0 + k, g_end - 1);
+                    wl[k] = __ldg(w_lo + 4 * gi);  // 8 words per row and group; this lane takes words 2t, 2t+1
+                    wh[k] = __ldg(w_hi + 4 * gi);
+                    sl[k] = __ldg(s_lo + gi);
+                    sh[k] = __ldg(s_hi + gi);
+                    bl[k] = __ldg(b_lo + gi);
+                    bh[k] = __ldg(b_hi + gi);
+                }
+#pragma unroll
+                for (int k = 0; k < MM_DEPTH; k++) {
+                    const int gi = g0 + k;
+                    if (gi >= g_end) break;
+                    float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int st = 0; st < 2; st++) {
+                        const uint32_t a_lo = st == 0 ? wl[k].x : wl[k].y, a_hi = st == 0 ? wh[k].x : wh[k].y;
+                        uint4 bh4 = make_uint4(0, 0, 0, 0), bm4 = make_uint4(0, 0, 0, 0);
+                        if (g < NV) {
+                            const uint4 *src = xb + ((size_t)((gi * 2 + st) * 4 + t) * NV + g) * 2;
+                            bh4 = src[0];
+                            bm4 = src[1];
+                        }
+                        // bf16 16 + n = 0x4180 | n << 3 (exact): nibble pairs (j, j + 4) of a word in one register
+                        constexpr uint32_t MASK = 0x00780078u, BASE = 0x41804180u;
+                        uint32_t a1[4] = {((a_lo << 3) & MASK) | BASE, ((a_hi << 3) & MASK) | BASE,
+                                          ((a_lo >> 1) & MASK) | BASE, ((a_hi >> 1) & MASK) | BASE};
+                        uint32_t a2[4] = {((a_lo >> 5) & MASK) | BASE, ((a_hi >> 5) & MASK) | BASE,
+                                          ((a_lo >> 9) & MASK) | BASE, ((a_hi >> 9) & MASK) | BASE};
+                        mma_bf16_16816(d, a1, bh4.x, bh4.y);
+                        mma_bf16_16816(d, a1, bm4.x, bm4.y);
+                        mma_bf16_16816(d, a2, bh4.z, bh4.w);
+                        mma_bf16_16816(d, a2, bm4.z, bm4.w);
+                    }
+                    const float x0 = (2 * t < NV) ? xg[(2 * t) * n_groups + gi] : 0.0f;
+                    const float x1 = (2 * t + 1 < NV) ? xg[(2 * t + 1) * n_groups + gi] : 0.0f;
+                    const float s0 = bf16_bits_to_f32(sl[k]), s1 = bf16_bits_to_f32(sh[k]);
+                    const float c0 = bf16_bits_to_f32(bl[k]), c1 = bf16_bits_to_f32(bh[k]);
+                    tot[0] += fmaf(s0, fmaf(-16.0f, x0, d[0]), c0 * x0);
+                    tot[1] += fmaf(s0, fmaf(-16.0f, x1, d[1]), c0 * x1);
+                    tot[2] += fmaf(s1, fmaf(-16.0f, x0, d[2]), c1 * x0);
+                    tot[3] += fmaf(s1, fmaf(-16.0f, x1, d[3]), c1 * x1);
+                }
+            }
+        }
+        if (ks > 1) {  // uniform over the CTA
+            red[warp * 32 + lane] = make_float4(tot[0], tot[1], tot[2], tot[3]);
+            __syncthreads();
+            if (split == 0)
+                for (int k = 1; k < ks; k++) {
+                    const float4 p = red[(warp + k) * 32 + lane];
+                    tot[0] += p.x;
+                    tot[1] += p.y;
+                    tot[2] += p.z;
+                    tot[3] += p.w;
+                }
+            __syncthreads();
+        }
+        if (active && split == 0) {
+            float *o = mb.out[m];
+            if (row0 + g < out_dim) {
+                if (2 * t < NV) o[(size_t)(2 * t) * out_dim + row0 + g] = tot[0];
+                if (2 * t + 1 < NV) o[(size_t)(2 * t + 1) * out_dim + row0 + g] = tot[1];
+            }
+            if (row0 + g + 8 < out_dim) {
+                if (2 * t < NV) o[(size_t)(2 * t) * out_dim + row0 + g + 8] = tot[2];
+                if (2 * t + 1 < NV) o[(size_t)(2 * t + 1) * out_dim + row0 + g + 8] = tot[3];
+            }
+        }
+    }
+}
+
+size_t mma_smem(int in_dim, int nv) {
+    return (size_t)(in_dim >> 6) * 8 * nv * 32 + sizeof(float) * (size_t)nv * (in_dim >> 6) + sizeof(float4) * MM_WARPS * 32;
+}
+
+template <int NV>
+cudaError_t launch_mma(MatvecBatch mb, const float *x, int in_dim, int n_sms, cudaStream_t stream) {
+    const size_t smem = mma_smem(in_dim, NV);
+    static thread_local bool configured[64] = {false};  // per device: the opt-in is a host call of several microseconds
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(dequant_matvec_4bit_mma_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)(227 * 1024));
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    int tiles = 0;  // here group_begin counts tiles of 16 rows per matrix
+    for (int m = 0; m < mb.n_mat; m++) {
+        mb.group_begin[m] = tiles;
+        tiles += (mb.out_dim[m] + 15) / 16;
+    }
+    mb.total_groups = tiles;
+    // warps per tile: enough to give every warp slot of the GPU work, while a warp keeps at least 8 groups
+    const int ctas_per_sm = (NV <= 3 && smem <= 100 * 1024) ? 2 : 1;
+    const int slots = n_sms * ctas_per_sm * MM_WARPS;
+    int ks = 1;
+    while (ks < MM_WARPS && tiles * ks < slots && (in_dim >> 6) / (2 * ks) >= 8) ks *= 2;
+    const int tiles_per_cta = MM_WARPS / ks;
+    int grid = (tiles + tiles_per_cta - 1) / tiles_per_cta;
+    if (grid > n_sms * ctas_per_sm) grid = n_sms * ctas_per_sm;
+    dequant_matvec_4bit_mma_kernel<NV><<<grid, MM_THREADS, smem, stream>>>(mb, x, in_dim, ks);
+    return cudaGetLastError();
+}
+
 template <int NV>
 cudaError_t launch_nv(const MatvecBatch &mb, const float *x, int in_dim, int n_sms, cudaStream_t stream) {
     const size_t smem = sizeof(float) * (size_t)NV * (in_dim + in_dim / 32);
@@ -222,7 +429,10 @@ cudaError_t launch_nv(const MatvecBatch &mb, const float *x, int in_dim, int n_s
 
 }  // namespace
 
-size_t dequant_matvec_4bit_smem(int in_dim, int n_vec) { return sizeof(float) * (size_t)n_vec * (in_dim + in_dim / 32); }
+size_t dequant_matvec_4bit_smem(int in_dim, int n_vec) {
+    if (n_vec == 1) return sizeof(float) * (size_t)(in_dim + in_dim / 32);
+    return mma_smem(in_dim, n_vec);
+}
 
 cudaError_t launch_dequant_matvec_4bit(MatvecBatch mb, const float *x, int in_dim, int n_vec, int n_sms,
                                        cudaStream_t stream) {
@@ -235,13 +445,13 @@ cudaError_t launch_dequant_matvec_4bit(MatvecBatch mb, const float *x, int in_di
     mb.total_groups = g;
     switch (n_vec) {
         case 1: return launch_nv<1>(mb, x, in_dim, n_sms, stream);
-        case 2: return launch_nv<2>(mb, x, in_dim, n_sms, stream);
-        case 3: return launch_nv<3>(mb, x, in_dim, n_sms, stream);
-        case 4: return launch_nv<4>(mb, x, in_dim, n_sms, stream);
-        case 5: return launch_nv<5>(mb, x, in_dim, n_sms, stream);
-        case 6: return launch_nv<6>(mb, x, in_dim, n_sms, stream);
-        case 7: return launch_nv<7>(mb, x, in_dim, n_sms, stream);
-        case 8: return launch_nv<8>(mb, x, in_dim, n_sms, stream);
+        case 2: return launch_mma<2>(mb, x, in_dim, n_sms, stream);
+        case 3: return launch_mma<3>(mb, x, in_dim, n_sms, stream);
+        case 4: return launch_mma<4>(mb, x, in_dim, n_sms, stream);
+        case 5: return launch_mma<5>(mb, x, in_dim, n_sms, stream);
+        case 6: return launch_mma<6>(mb, x, in_dim, n_sms, stream);
+        case 7: return launch_mma<7>(mb, x, in_dim, n_sms, stream);
+        case 8: return launch_mma<8>(mb, x, in_dim, n_sms, stream);
         default: return cudaErrorInvalidValue;
     }
 }
