@@ -55,8 +55,11 @@ template <int NV>
 __global__ void __launch_bounds__(MV_THREADS, NV <= 2 ? 2 : 1)
 dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *__restrict__ x, int in_dim) {
     extern __shared__ __align__(16) float smem_f[];
-    float *xs = smem_f;                    // [NV][in_dim]
-    float *xh = smem_f + NV * in_dim;      // [NV][in_dim / 32]: sums of x over half groups
+    // [NV][in_dim / 32][36]: a chunk of 32 features padded to 36 floats, so that lanes reading consecutive chunks
+    // (128 bytes apart unpadded: one bank) spread over the banks
+    float *xs = smem_f;
+    const int in_dim_p = (in_dim >> 5) * 36;
+    float *xh = smem_f + NV * in_dim_p;    // [NV][in_dim / 32]: sums of x over half groups
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_chunks = in_dim >> 5;      // 16-byte chunks per row
     const int n_groups = in_dim >> 6;
@@ -108,7 +111,10 @@ dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             const int i = i0 + u * MV_THREADS + tid;
-            if (i < n_f4) reinterpret_cast<float4 *>(xs)[i] = v[u];
+            if (i < n_f4) {
+                const int vec = i / (in_dim >> 2), f = (i - vec * (in_dim >> 2)) * 4;  // feature index of the first float
+                *reinterpret_cast<float4 *>(xs + (size_t)vec * in_dim_p + (f >> 5) * 36 + (f & 31)) = v[u];
+            }
             float sm = (v[u].x + v[u].y) + (v[u].z + v[u].w);
             sm += __shfl_xor_sync(0xffffffffu, sm, 1);
             sm += __shfl_xor_sync(0xffffffffu, sm, 2);
@@ -130,8 +136,8 @@ dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *
             float xv[NV][8];
 #pragma unroll
             for (int v = 0; v < NV; v++) {
-                const float4 a = *reinterpret_cast<const float4 *>(xs + (size_t)v * in_dim + 32 * c + 8 * q);
-                const float4 b = *reinterpret_cast<const float4 *>(xs + (size_t)v * in_dim + 32 * c + 8 * q + 4);
+                const float4 a = *reinterpret_cast<const float4 *>(xs + (size_t)v * in_dim_p + 36 * c + 8 * q);
+                const float4 b = *reinterpret_cast<const float4 *>(xs + (size_t)v * in_dim_p + 36 * c + 8 * q + 4);
                 xv[v][0] = a.x; xv[v][1] = a.y; xv[v][2] = a.z; xv[v][3] = a.w;
                 xv[v][4] = b.x; xv[v][5] = b.y; xv[v][6] = b.z; xv[v][7] = b.w;
             }
@@ -216,7 +222,8 @@ template <int NV>
 __global__ void __launch_bounds__(MM_THREADS, NV <= 3 ? 2 : 1)
 dequant_matvec_4bit_mma_kernel(const __grid_constant__ MatvecBatch mb, const float *__restrict__ x, int in_dim, int ks) {
     extern __shared__ __align__(16) uint8_t smem_b[];
-    // B fragments: [group][step 0/1][t][g < NV] x 32 bytes {hi: m1b0, m1b1, m2b0, m2b1 | mid: the same}
+    // B fragments: [group][step 0/1][hi | mid][g < NV][t] x 16 bytes {m1b0, m1b1, m2b0, m2b1}: the lanes of a
+    // quarter warp read consecutive 16-byte words
     uint4 *xb = reinterpret_cast<uint4 *>(smem_b);
     const int n_groups = in_dim >> 6;
     float *xg = reinterpret_cast<float *>(smem_b + (size_t)n_groups * 8 * NV * 32);  // [NV][n_groups] group sums
@@ -250,9 +257,9 @@ dequant_matvec_4bit_mma_kernel(const __grid_constant__ MatvecBatch mb, const flo
                 split_bf16x2_mv(a[u].y, b[u].y, h[1], m[1]);  // MMA 1, b1: k slots (2t+8, 2t+9) <- features 1, 5
                 split_bf16x2_mv(a[u].z, b[u].z, h[2], m[2]);  // MMA 2, b0                        <- features 2, 6
                 split_bf16x2_mv(a[u].w, b[u].w, h[3], m[3]);  // MMA 2, b1                        <- features 3, 7
-                uint4 *dst = xb + ((size_t)ee[u] * NV + vv[u]) * 2;
-                dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
-                dst[1] = make_uint4(m[0], m[1], m[2], m[3]);
+                const int gs = ee[u] >> 2, tt = ee[u] & 3;  // (group, step), t
+                xb[((size_t)(gs * 2 + 0) * NV + vv[u]) * 4 + tt] = make_uint4(h[0], h[1], h[2], h[3]);
+                xb[((size_t)(gs * 2 + 1) * NV + vv[u]) * 4 + tt] = make_uint4(m[0], m[1], m[2], m[3]);
             }
             // the eight entries of a group sit in eight consecutive threads
             float sm = ((a[u].x + a[u].y) + (a[u].z + a[u].w)) + ((b[u].x + b[u].y) + (b[u].z + b[u].w));
@@ -309,9 +316,9 @@ dequant_matvec_4bit_mma_kernel(const __grid_constant__ MatvecBatch mb, const flo
                         const uint32_t a_lo = st == 0 ? wl[k].x : wl[k].y, a_hi = st == 0 ? wh[k].x : wh[k].y;
                         uint4 bh4 = make_uint4(0, 0, 0, 0), bm4 = make_uint4(0, 0, 0, 0);
                         if (g < NV) {
-                            const uint4 *src = xb + ((size_t)((gi * 2 + st) * 4 + t) * NV + g) * 2;
-                            bh4 = src[0];
-                            bm4 = src[1];
+                            const int gs = gi * 2 + st;
+                            bh4 = xb[((size_t)(gs * 2 + 0) * NV + g) * 4 + t];
+                            bm4 = xb[((size_t)(gs * 2 + 1) * NV + g) * 4 + t];
                         }
                         // bf16 16 + n = 0x4180 | n << 3 (exact): nibble pairs (j, j + 4) of a word in one register
                         constexpr uint32_t MASK = 0x00780078u, BASE = 0x41804180u;
@@ -398,7 +405,7 @@ cudaError_t launch_mma(MatvecBatch mb, const float *x, int in_dim, int n_sms, cu
 
 template <int NV>
 cudaError_t launch_nv(const MatvecBatch &mb, const float *x, int in_dim, int n_sms, cudaStream_t stream) {
-    const size_t smem = sizeof(float) * (size_t)NV * (in_dim + in_dim / 32);
+    const size_t smem = sizeof(float) * (size_t)NV * ((in_dim >> 5) * 36 + in_dim / 32);
     // the shared-memory opt-in and the occupancy query are host calls of several microseconds: once per size
     static thread_local size_t cfg_smem[16] = {0};
     static thread_local int cfg_dev[16], cfg_per_sm[16];
@@ -430,7 +437,7 @@ cudaError_t launch_nv(const MatvecBatch &mb, const float *x, int in_dim, int n_s
 }  // namespace
 
 size_t dequant_matvec_4bit_smem(int in_dim, int n_vec) {
-    if (n_vec == 1) return sizeof(float) * (size_t)(in_dim + in_dim / 32);
+    if (n_vec == 1) return sizeof(float) * (size_t)((in_dim >> 5) * 36 + in_dim / 32);
     return mma_smem(in_dim, n_vec);
 }
 
