@@ -1264,24 +1264,9 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
         return -1;
     }
     cudaStream_t main_stream = c->stream;
-    if (n_lin) {
-        // GatedDeltaNet group on the side queue: its copies and kernel overlap the attention group
-        CK(cudaEventRecord(c->ev_fork, main_stream));
-        CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
-        cudaStream_t s2 = c->side_stream;
-        const size_t vd = sizeof(float) * g.linear_num_v_heads * GDN_DIM * (size_t)n_lin;
-        const size_t hd = sizeof(float) * g.linear_num_v_heads * (size_t)n_lin;
-        CK(cudaMemcpyAsync(c->st_qkv, qkv, sizeof(float) * c->conv_dim * (size_t)n_lin, cudaMemcpyHostToDevice, s2));
-        if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, s2));
-        CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, s2));
-        CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, s2));
-        c->stream = s2;
-        const int rc = launch_gdn(c, n_lin, c->st_qkv, z ? c->st_z : nullptr, c->st_alpha, c->st_beta, c->st_gout);
-        c->stream = main_stream;
-        if (rc) return -1;
-        CK(cudaMemcpyAsync(lin_out, c->st_gout, vd, cudaMemcpyDeviceToHost, s2));
-        CK(cudaEventRecord(c->ev_join, s2));
-    }
+    // The attention group goes first: its inputs are small and its kernel is the long one, so the copy engine
+    // should not make it wait behind the GatedDeltaNet inputs (3.5x larger), which then travel under that kernel.
+    if (n_lin) CK(cudaEventRecord(c->ev_fork, main_stream));
     if (n_full) {
         const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)n_full;
         const size_t kd = sizeof(float) * g.num_kv_heads * HEAD_DIM * (size_t)n_full;
@@ -1299,6 +1284,23 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
         p.partial_mode = 0;
         if (launch_gqa(c, p)) return -1;
         CK(cudaMemcpyAsync(full_out, c->st_out, qd, cudaMemcpyDeviceToHost, main_stream));
+    }
+    if (n_lin) {
+        // GatedDeltaNet group on the side queue: its copies and kernel overlap the attention kernel
+        CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
+        cudaStream_t s2 = c->side_stream;
+        const size_t vd = sizeof(float) * g.linear_num_v_heads * GDN_DIM * (size_t)n_lin;
+        const size_t hd = sizeof(float) * g.linear_num_v_heads * (size_t)n_lin;
+        CK(cudaMemcpyAsync(c->st_qkv, qkv, sizeof(float) * c->conv_dim * (size_t)n_lin, cudaMemcpyHostToDevice, s2));
+        if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, s2));
+        CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, s2));
+        CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, s2));
+        c->stream = s2;
+        const int rc = launch_gdn(c, n_lin, c->st_qkv, z ? c->st_z : nullptr, c->st_alpha, c->st_beta, c->st_gout);
+        c->stream = main_stream;
+        if (rc) return -1;
+        CK(cudaMemcpyAsync(lin_out, c->st_gout, vd, cudaMemcpyDeviceToHost, s2));
+        CK(cudaEventRecord(c->ev_join, s2));
     }
     if (n_lin) CK(cudaStreamWaitEvent(main_stream, c->ev_join, 0));
     return check_status(c);
