@@ -127,53 +127,68 @@ __device__ __forceinline__ Located locate_tile(const GqaParams &p, int gt, int g
 // final gated output or merged partial.  Executed by 128 threads.
 __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L, const float *src_o,
                            const float *src_m, const float *src_l, int n_src, float *s_w,
-                           float *s_M, float *s_L) {
+                           float *s_M, float *s_L, float *s_tmp) {
     const int tid = threadIdx.x;
     const int group = p.group;
+    // m and l of every partial come in with all loads in flight (s_tmp: n_src * 16 floats of scratch); the
+    // reductions then run out of shared memory in the order they always had
+    for (int idx = tid; idx < n_src * 16; idx += 128) {
+        s_w[idx] = src_m[idx];
+        s_tmp[idx] = src_l[idx];
+    }
+    __syncthreads();
     if (tid < 16) {
         float M = -INFINITY;
-        for (int c = 0; c < n_src; c++) M = fmaxf(M, src_m[c * 16 + tid]);
+        for (int c = 0; c < n_src; c++) M = fmaxf(M, s_w[c * 16 + tid]);
         s_M[tid] = M;
     }
     __syncthreads();
     for (int idx = tid; idx < n_src * 16; idx += 128) {
-        const float m = src_m[idx];
+        const float m = s_w[idx];
         s_w[idx] = (m == -INFINITY) ? 0.0f : expf(m - s_M[idx & 15]);
     }
     __syncthreads();
     if (tid < 16) {
         float Ls = 0.0f;
-        for (int c = 0; c < n_src; c++) Ls += s_w[c * 16 + tid] * src_l[c * 16 + tid];
+        for (int c = 0; c < n_src; c++) Ls += s_w[c * 16 + tid] * s_tmp[c * 16 + tid];
         s_L[tid] = Ls;
     }
     __syncthreads();
     const size_t head0 = (size_t)L.it.in_idx * p.H + (size_t)L.kvh * group;
-    // Eight heads at a time with every load of a round in flight together: the merging CTA is the last of its unit to
-    // finish, usually at the very end of the launch, so this latency is on the launch's critical path.
-    for (int hr0 = 0; hr0 < group; hr0 += 8) {
-        float2 acc[8], gt[8];
+    // Four heads x four partials per round, every load of a round in flight together: the merging CTA is the last of
+    // its unit to finish, usually at the very end of the launch, so this latency is on the launch's critical path
+    // (and with one long sequence per launch a unit has up to MAX_SPLITS partials).
+    for (int hr0 = 0; hr0 < group; hr0 += 4) {
+        float2 acc[4], gt[4];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < 4; u++) {
             acc[u] = make_float2(0.0f, 0.0f);
             gt[u] = make_float2(0.0f, 0.0f);
             if (!p.partial_mode && p.gate && hr0 + u < group)
                 gt[u] = *reinterpret_cast<const float2 *>(p.gate + (head0 + hr0 + u) * (size_t)p.gate_row_stride + 2 * tid);
         }
-        for (int c = 0; c < n_src; c++) {
-            float2 o[8];
+        for (int c0 = 0; c0 < n_src; c0 += 4) {
+            float2 o[4][4];
 #pragma unroll
-            for (int u = 0; u < 8; u++)
-                o[u] = (hr0 + u < group) ? *reinterpret_cast<const float2 *>(src_o + ((size_t)c * 16 + hr0 + u) * HEAD_DIM + 2 * tid)
-                                         : make_float2(0.0f, 0.0f);
+            for (int k = 0; k < 4; k++)
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const float w = s_w[c * 16 + ((hr0 + u) & 15)];
-                acc[u].x = fmaf(w, o[u].x, acc[u].x);
-                acc[u].y = fmaf(w, o[u].y, acc[u].y);
+                for (int u = 0; u < 4; u++)
+                    o[k][u] = (c0 + k < n_src && hr0 + u < group)
+                                  ? *reinterpret_cast<const float2 *>(src_o + ((size_t)(c0 + k) * 16 + hr0 + u) * HEAD_DIM + 2 * tid)
+                                  : make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {  // partials are added in index order, as before
+                if (c0 + k >= n_src) break;
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const float w = s_w[(c0 + k) * 16 + ((hr0 + u) & 15)];
+                    acc[u].x = fmaf(w, o[k][u].x, acc[u].x);
+                    acc[u].y = fmaf(w, o[k][u].y, acc[u].y);
+                }
             }
         }
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < 4; u++) {
             const int hr = hr0 + u;
             if (hr >= group) break;
             const size_t off = (head0 + hr) * HEAD_DIM + 2 * tid;
@@ -202,7 +217,7 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
 // (l_r still split over the four lanes of a row).
 __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L, float (&o)[8][4],
                                             float (&m_r)[2], float (&l_r)[2], float *s_w,
-                                            float *s_M, float *s_L, int *s_flag_p) {
+                                            float *s_M, float *s_L, int *s_flag_p, float *s_tmp) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const GqaItem &it = L.it;
@@ -277,7 +292,7 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
     if (!*s_flag_p) return;
     __threadfence();
     merge_unit(p, L, p.sc_o + slot0 * 16 * HEAD_DIM, p.sc_m + slot0 * 16, p.sc_l + slot0 * 16,
-               L.n_parts, s_w, s_M, s_L);
+               L.n_parts, s_w, s_M, s_L, s_tmp);
 }
 
 }  // namespace mfc

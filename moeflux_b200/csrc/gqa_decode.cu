@@ -287,7 +287,7 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
         return;
     }
 
-    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag);
+    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag, reinterpret_cast<float *>(stages));  // the stage ring is idle here: scratch for the merge
     pc += (unsigned)ntiles;
     gt += L.seg;
     fence_proxy_async();  // the next segment's TMA loads overwrite memory this segment touched

@@ -315,7 +315,7 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         if (tid == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);
         return;
     }
-    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag);
+    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag, s_L + 16);  // the stage ring is idle here: scratch for the merge
     pc += (unsigned)ntiles;
     gt += L.seg;
     fence_proxy_async();  // the next segment's TMA loads overwrite memory this segment touched
