@@ -61,7 +61,7 @@ struct mfc_ctx {
     cudaStream_t stream = nullptr;
     bool owns_stream = true;
     cudaStream_t side_stream = nullptr;  // second queue of mfc_eval_token_attn
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_gate = nullptr;
 
     void *k_cache = nullptr, *v_cache = nullptr;
     CUtensorMap kmap, vmap;
@@ -212,6 +212,7 @@ void free_all(mfc_ctx *c) {
     if (c->side_stream) cudaStreamDestroy(c->side_stream);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->ev_join) cudaEventDestroy(c->ev_join);
+    if (c->ev_gate) cudaEventDestroy(c->ev_gate);
 }
 
 int check_status(mfc_ctx *c) {
@@ -665,7 +666,8 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
-              cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) == cudaSuccess;
+              cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&c->ev_gate, cudaEventDisableTiming) == cudaSuccess;
     if (!ok) fail(c, "cudaStreamCreate failed");
     const uint64_t kv_rows = (uint64_t)c->n_kv_slots * g.num_kv_heads * c->cap_rows;
     if (ok && kv_rows >= (1ull << 32)) ok = fail(c, "KV cache has more rows than a tensor map can address");
@@ -1266,23 +1268,30 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
     cudaStream_t main_stream = c->stream;
     // The attention group goes first: its inputs are small and its kernel is the long one, so the copy engine
     // should not make it wait behind the GatedDeltaNet inputs (3.5x larger), which then travel under that kernel.
-    if (n_lin) CK(cudaEventRecord(c->ev_fork, main_stream));
+    CK(cudaEventRecord(c->ev_fork, main_stream));
     if (n_full) {
         const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)n_full;
         const size_t kd = sizeof(float) * g.num_kv_heads * HEAD_DIM * (size_t)n_full;
+        // q, k, v first; the gate logits (as many bytes as q) are only needed after the attention kernel, so they
+        // travel on the side queue under it and are applied by a separate elementwise pass
         CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, main_stream));
-        CK(cudaMemcpyAsync(c->st_gate, gate, qd, cudaMemcpyHostToDevice, main_stream));
         CK(cudaMemcpyAsync(c->st_k, k, kd, cudaMemcpyHostToDevice, main_stream));
         CK(cudaMemcpyAsync(c->st_v, v, kd, cudaMemcpyHostToDevice, main_stream));
+        CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
+        CK(cudaMemcpyAsync(c->st_gate, gate, qd, cudaMemcpyHostToDevice, c->side_stream));
+        CK(cudaEventRecord(c->ev_gate, c->side_stream));
         GqaParams p;
         fill_gqa_params(c, p, n_full, total);
         p.q = c->st_q;
-        p.gate = c->st_gate;
+        p.gate = nullptr;
         p.k = c->st_k;
         p.v = c->st_v;
         p.out = c->st_out;
         p.partial_mode = 0;
         if (launch_gqa(c, p)) return -1;
+        CK(cudaStreamWaitEvent(main_stream, c->ev_gate, 0));
+        CK(launch_sigmoid_gate(c->st_out, c->st_gate, qd / sizeof(float), main_stream));
+        c->launches += 1;
         CK(cudaMemcpyAsync(full_out, c->st_out, qd, cudaMemcpyDeviceToHost, main_stream));
     }
     if (n_lin) {

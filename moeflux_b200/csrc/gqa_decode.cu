@@ -414,6 +414,26 @@ cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_part
     return cudaGetLastError();
 }
 
+// out *= sigmoid(gate), four floats per thread: the gate applied after the fact with the fused epilogue's arithmetic
+static __global__ void sigmoid_gate_kernel(float *out, const float *gate, size_t n4) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 o = reinterpret_cast<float4 *>(out)[i];
+    const float4 g = reinterpret_cast<const float4 *>(gate)[i];
+    o.x *= 1.0f / (1.0f + expf(-g.x));
+    o.y *= 1.0f / (1.0f + expf(-g.y));
+    o.z *= 1.0f / (1.0f + expf(-g.z));
+    o.w *= 1.0f / (1.0f + expf(-g.w));
+    reinterpret_cast<float4 *>(out)[i] = o;
+}
+
+cudaError_t launch_sigmoid_gate(float *out, const float *gate, size_t n, cudaStream_t stream) {
+    const size_t n4 = n / 4;
+    if (n4 == 0) return cudaSuccess;
+    sigmoid_gate_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(out, gate, n4);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_rope(float *q, float *k, int H, int Hkv, int rotary_dim, int pos,
                         const float *inv_freq, cudaStream_t stream) {
     const int total = (H + Hkv) * (rotary_dim / 2);

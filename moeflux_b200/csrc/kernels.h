@@ -111,6 +111,9 @@ cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_part
                                   size_t o_item_stride = 0, size_t ml_item_stride = 0);
 
 // RoPE on packed q [H][256], k [Hkv][256] in place (parity hook).
+// out[i] *= sigmoid(gate[i]) for n floats (n a multiple of 4): the gate applied after the fact, with the arithmetic
+// of the fused epilogue, when the gate logits arrive later than q, k and v.
+cudaError_t launch_sigmoid_gate(float *out, const float *gate, size_t n, cudaStream_t stream);
 cudaError_t launch_rope(float *q, float *k, int H, int Hkv, int rotary_dim, int pos,
                         const float *inv_freq, cudaStream_t stream);
 
