@@ -4,7 +4,8 @@ TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by ``__graft_entry__.smoke()``
 and by ``bench.py``'s CPU-baseline leg, as the checker.  The library in
 ``moeflux_b200`` never imports this package.
 
-Parity unpinned: see the header of ``mf_oracle.c``.
+Parity pinned against the reference's own C functions (``oracle/ref.py``,
+``tests/test_oracle_ref.py``): see the header of ``mf_oracle.c``.
 """
 from __future__ import annotations
 

@@ -7,13 +7,17 @@
  * operation order.  It is the checker that the CUDA path is compared with and
  * the timed CPU baseline.  Nothing the library ships may call into it.
  *
- * PARITY UNPINNED: the reference stores no golden vectors or known-answer
- * tests for this path (its tests are tolerance-based differentials between its
- * C and Rust engines on Apple hardware), and neither engine builds on Linux.
- * The restatement is pinned only by closed-form known answers derived from the
- * reference's formulas (see tests/test_oracle_kat.py).  One exception is PINNED:
- * mfo_dequant_matvec_4bit reproduces the known answers of the reference's own unit
- * tests for that function (crates/moeflux/src/riir/cpu_matvec.rs:370-451).
+ * PARITY PINNED against the reference's own C code: oracle/ref.py compiles the
+ * plain-C CPU twins of this path out of the reference's
+ * crates/moeflux-sys/metal_infer/infer.m (cpu_sdpa, apply_rotary_emb,
+ * cpu_conv1d_step, cpu_rms_norm_bare/_gated/_per_head,
+ * cpu_gated_delta_recurrence, cpu_dequant_matvec) into oracle/_ref/, and
+ * tests/test_oracle_ref.py holds every function below to them on the inputs and
+ * at the bounds of the reference's differential tests (128 ULP; cosine 0.9999
+ * and 1e-3 for SDPA).  The reference stores no golden vectors for this path;
+ * closed-form known answers derived from its formulas (tests/test_oracle_kat.py)
+ * and the known answers of its unit tests of the 4-bit matvec
+ * (crates/moeflux/src/riir/cpu_matvec.rs:370-451) are checked as well.
  *
  * Every function cites the reference source it follows, by path inside the
  * reference project.  Rust `mul_add` call sites are kept as fmaf(); all other
