@@ -6,9 +6,13 @@ hybrid decode stack -- 45 GatedDeltaNet layer-steps and 15 full-attention GQA
 layer-steps for each of 8 sequences at context 131072, bf16 KV cache, seeded
 N(0,1) activations per (layer, sequence).  One step = 480 layer-steps =
 35.4 GB of algorithmic HBM traffic.  On N GPUs the KV positions of every
-sequence are split block-cyclically over the ranks (one NCCL all-gather of the
-log-sum-exp partials per step, merged and gated by one kernel) and the
-GatedDeltaNet sequences are dealt round-robin; total work is fixed ("strong").
+sequence are split block-cyclically over the ranks; the decode kernel stores
+each item's log-sum-exp partial straight into the memory of the rank that
+finishes the item (peer stores over NVLink, step flags), which merges and gates
+it; the GatedDeltaNet sequences are dealt round-robin; total work is fixed
+("strong").  After the timed region one more step is computed and checked
+against the CPU oracle ("parity" in the JSON line; non-zero exit above the
+tolerance).
 
     python bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...     # the CPU restatement, timed on the host cores
@@ -49,9 +53,13 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")
     ap.add_argument("--batch", type=int, default=8, help="sequences")
-    ap.add_argument("--workload", default="stack", choices=["stack", "prefill", "matvec"],
-                    help="stack: the decode stack (headline); prefill: 8192-token chunked prefill of one hybrid block; "
+    ap.add_argument("--workload", default="stack", choices=["stack", "ragged", "prefill", "matvec"],
+                    help="stack: the decode stack (headline); ragged: 64 sequences of ragged context, one full-attention "
+                         "layer-step each, sharded by sequence; prefill: 8192-token chunked prefill of one hybrid block; "
                          "matvec: the 4-bit projections around the attention sub-blocks of one hybrid block")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="KV-split exchange at N > 1: partials stored by the decode kernel into the finishing rank's "
+                         "memory (fused), or one NCCL all-to-all per step (nccl)")
     ap.add_argument("--vecs", type=int, default=1, help="input vectors per projection (--workload matvec)")
     ap.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "f32"], help="KV cache storage type")
@@ -128,65 +136,137 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_sample(ctx_len, batch, seed=4):
-    """Times the oracle on a bounded sample of the stack workload and scales to
-    one token step: returns (layer_steps_per_s, cores, description)."""
+def _host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_sample(ctx_len, batch, seed=4, kind="port", n_full_layers=None, n_lin_layers=None):
+    """Times the CPU statement of the path on a bounded sample of the stack workload and scales to one token step:
+    returns (layer_steps_per_s, cores, description, kind).
+
+    kind "port": the oracle (oracle/mf_oracle.c), OpenMP over heads.  kind "reference": the reference's own C
+    functions (oracle/_ref, lifted from infer.m by oracle/ref.py), which are single-threaded, so independent
+    layer-steps run side by side, one per host thread, as a batch of sequences would."""
     import oracle as O
     from oracle import A17B as G
 
+    n_full_layers = len(FULL_LAYERS) if n_full_layers is None else n_full_layers
+    n_lin_layers = len(LIN_LAYERS) if n_lin_layers is None else n_lin_layers
     O.build()
-    O.use_all_cores()
     r = np.random.Generator(np.random.Philox(seed))
     nrm = lambda *s: r.standard_normal(s, dtype=np.float32)
-    # full attention: one (layer, sequence) item at the full context
-    K = O.round_bf16(nrm(ctx_len, KV_DIM))
-    V = O.round_bf16(nrm(ctx_len, KV_DIM))
-    q, gate, k, v = nrm(Q_DIM), nrm(Q_DIM), nrm(KV_DIM), nrm(KV_DIM)
-    n_gqa = 2
-    t0 = time.perf_counter()
-    for _ in range(n_gqa):
-        O.full_attn_step(ctx_len - 1, ctx_len - 1, q, gate, k, v, K, V, G, kv_bf16=True)
-    t_gqa = (time.perf_counter() - t0) / n_gqa
-    # GatedDeltaNet: one (layer, sequence) item, repeated
     conv_w = O.f32_to_bf16_bits(nrm(CONV_DIM, 4) * 0.5)
     a_log = r.uniform(0, 2.7, HV).astype(np.float32)
     dt_bias = O.f32_to_bf16_bits(nrm(HV))
     norm_w = O.f32_to_bf16_bits(1 + 0.1 * nrm(DK))
-    conv = nrm(3, CONV_DIM)
-    ssm = nrm(SSM_ELEMS) * np.float32(0.02)
-    n_gdn = 24
-    t0 = time.perf_counter()
-    for _ in range(n_gdn):
-        O.linear_attn_step(nrm(CONV_DIM), nrm(V_DIM), nrm(HV), nrm(HV), conv_w, a_log, dt_bias, norm_w, conv, ssm, G)
-    t_gdn = (time.perf_counter() - t0) / n_gdn
-    n_full_items = len(FULL_LAYERS) * batch
-    n_lin_items = len(LIN_LAYERS) * batch
+    K = O.round_bf16(nrm(ctx_len, KV_DIM))
+    V = O.round_bf16(nrm(ctx_len, KV_DIM))
+    n_full_items = n_full_layers * batch
+    n_lin_items = n_lin_layers * batch
+    if kind == "reference":
+        import oracle.ref as R
+        from concurrent.futures import ThreadPoolExecutor
+
+        threads = _host_threads()
+        # full attention: `threads` layer-steps at the full context side by side.  They read one copy of the cache
+        # rows (a copy per thread would not fit) and append the same row, so the concurrent writes store equal values.
+        n_gqa = min(threads, max(n_full_items, 1))
+        q, gate, k, v = nrm(Q_DIM), nrm(Q_DIM), nrm(KV_DIM), nrm(KV_DIM)
+
+        def gqa(i):
+            R.full_attn_step(ctx_len - 1, ctx_len - 1, q, gate, k, v, K, V, H, HKV, D, G.rotary_dim)
+
+        t_gqa = 0.0
+        if n_full_items:
+            with ThreadPoolExecutor(threads) as ex:
+                t0 = time.perf_counter()
+                list(ex.map(gqa, range(n_gqa)))
+                t_gqa = (time.perf_counter() - t0) / n_gqa  # wall time per layer-step with all threads busy
+        per = max(1, min(4, n_lin_items // max(threads, 1)))
+        n_gdn = threads * per
+        states = [(nrm(3, CONV_DIM), nrm(SSM_ELEMS) * np.float32(0.02)) for _ in range(threads)]
+        gin = [(nrm(CONV_DIM), nrm(V_DIM), nrm(HV), nrm(HV)) for _ in range(threads)]
+
+        def gdn(i):
+            conv, ssm = states[i]
+            for _ in range(per):
+                R.linear_attn_step(*gin[i], conv_w, a_log, dt_bias, norm_w, conv, ssm, G)
+
+        t_gdn = 0.0
+        if n_lin_items:
+            with ThreadPoolExecutor(threads) as ex:
+                t0 = time.perf_counter()
+                list(ex.map(gdn, range(threads)))
+                t_gdn = (time.perf_counter() - t0) / n_gdn
+        cores = threads
+        how = (f"the reference's own C functions (infer.m cpu_sdpa, apply_rotary_emb, cpu_conv1d_step, "
+               f"cpu_gated_delta_recurrence, cpu_rms_norm_gated; single-threaded each, {threads} independent layer-steps "
+               f"side by side)")
+    else:
+        O.use_all_cores()
+        q, gate, k, v = nrm(Q_DIM), nrm(Q_DIM), nrm(KV_DIM), nrm(KV_DIM)
+        n_gqa = 2 if n_full_items else 0
+        t0 = time.perf_counter()
+        for _ in range(n_gqa):
+            O.full_attn_step(ctx_len - 1, ctx_len - 1, q, gate, k, v, K, V, G, kv_bf16=True)
+        t_gqa = (time.perf_counter() - t0) / max(n_gqa, 1)
+        conv = nrm(3, CONV_DIM)
+        ssm = nrm(SSM_ELEMS) * np.float32(0.02)
+        n_gdn = 24 if n_lin_items else 0
+        t0 = time.perf_counter()
+        for _ in range(n_gdn):
+            O.linear_attn_step(nrm(CONV_DIM), nrm(V_DIM), nrm(HV), nrm(HV), conv_w, a_log, dt_bias, norm_w, conv, ssm, G)
+        t_gdn = (time.perf_counter() - t0) / max(n_gdn, 1)
+        cores = O.num_threads()
+        how = "the C restatement of the reference math (oracle/mf_oracle.c, OpenMP over heads)"
     t_step = n_full_items * t_gqa + n_lin_items * t_gdn
-    desc = (f"{n_gqa} GQA layer-steps at ctx {ctx_len} ({t_gqa * 1e3:.1f} ms each) and {n_gdn} GatedDeltaNet "
-            f"layer-steps ({t_gdn * 1e3:.2f} ms each), scaled to {n_full_items}+{n_lin_items} per token step")
-    return (n_full_items + n_lin_items) / t_step, O.num_threads(), desc
+    desc = (f"{how}: {n_gqa} GQA layer-steps at ctx {ctx_len} ({t_gqa * 1e3:.1f} ms each at full load) and {n_gdn} "
+            f"GatedDeltaNet layer-steps ({t_gdn * 1e3:.2f} ms each), scaled to {n_full_items}+{n_lin_items} per token step")
+    return (n_full_items + n_lin_items) / t_step, cores, desc, kind
+
+
+def reference_kind():
+    """"reference" when the reference's own C functions are built (oracle/_ref) or can be built here, else "port"."""
+    try:
+        import oracle.ref as R
+
+        if R.available():
+            R.lib()
+            return "reference"
+    except Exception:
+        pass
+    return "port"
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
+    kind = reference_kind()
     vals = []
     cores, desc = 1, ""
     t_begin = time.perf_counter()
+    ragged = args.workload == "ragged"
     for i in range(args.warmup + args.steps):
-        v, cores, desc = cpu_sample(args.ctx, args.batch, seed=4 + i)
+        if ragged:
+            v, cores, desc, kind = cpu_sample_ragged(args, kind, seed=4 + i)
+        else:
+            v, cores, desc, kind = cpu_sample(args.ctx, args.batch, seed=4 + i, kind=kind)
         if i >= args.warmup:
             vals.append(v)
-        if time.perf_counter() - t_begin > 240 and len(vals) >= 1:  # keep the arm within minutes
+        if time.perf_counter() - t_begin > 200 and len(vals) >= 1:  # keep the arm within minutes
             break
     value = len(vals) / sum(1.0 / v for v in vals)
+    n_units = RAGGED_SEQS if ragged else N_LAYERS * args.batch
     line = {
         "impl": "reference", "metric": "attention decode layer-steps/sec", "value": value, "unit": "layer-steps/s",
         "n_gpus": args.gpus, "steps": len(vals), "warmup": args.warmup,
-        "ms_per_step": 1e3 * (len(FULL_LAYERS) + len(LIN_LAYERS)) * args.batch / value,
+        "ms_per_step": 1e3 * n_units / value,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (bf16 KV values)",
-        "data": "synthetic", "config": workload_config(args, args.gpus),
-        "cpu_baseline": {"value": value, "unit": "layer-steps/s", "cores": cores, "kind": "port", "sample": desc},
+        "data": "synthetic", "config": ragged_config(args, args.gpus) if ragged else workload_config(args, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "layer-steps/s", "cores": cores, "kind": kind, "sample": desc},
         "e2e": {"value": value, "unit": "layer-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -197,11 +277,19 @@ def workload_config(args, n):
     return {"workload": f"60-layer hybrid attention-only decode stack (45 GatedDeltaNet + 15 GQA), batch {args.batch}, "
                         f"ctx {args.ctx}, {args.kv} KV, fp32 state",
             "layer_steps_per_step": N_LAYERS * args.batch, "context": args.ctx, "batch": args.batch,
-            "kv_dtype": args.kv, "parallelism": f"kv-sequence split x{n} with one NCCL all-to-all of the log-sum-exp "
-                                                f"partials per step (each sequence is finished on its own rank) + "
-                                                f"GatedDeltaNet sequences round-robin"
+            "kv_dtype": args.kv, "parallelism": (f"kv-sequence split x{n}: the decode kernel stores each item's log-sum-exp "
+                                                f"partial straight into the receive buffer of the rank that finishes the "
+                                                f"item (peer stores over NVLink + step flags; --exchange nccl: one NCCL "
+                                                f"all-to-all per step instead), merged and gated there + GatedDeltaNet "
+                                                f"sequences round-robin")
             if n > 1 else "single GPU",
             "l2": "inputs (GBs of KV and state per step) exceed the 126 MB L2; no flush needed"}
+
+
+def repeats_for(k_steps, est_ms_per_step):
+    """Timed blocks of k_steps steps: at least 7, and enough for about a second of timed work."""
+    block_s = max(k_steps * est_ms_per_step * 1e-3, 1e-6)
+    return int(min(64, max(7, -(-1.0 // block_s))))
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -216,44 +304,56 @@ def run_ours(args, rank, world, local_rank):
     B, CTX = args.batch, args.ctx
     W, K = args.warmup, args.steps
     do_e2e = not args.no_e2e
-    We, Ke = (min(W, 3), K) if do_e2e else (0, 0)
-    total_steps = W + K + We + Ke
-    L0 = CTX - total_steps  # the last timed step brings every cache to exactly CTX rows
-    assert L0 > 0
+    fused = world > 1 and args.exchange == "fused"
+    R = repeats_for(K, 4.9 * (CTX / 131072.0) * (B / 8.0) / world)
+    We, Re = (min(W, 3), min(R, 7)) if do_e2e else (0, 0)
+    total_steps = W + R * K + We + Re * K + 1  # + the step whose outputs are checked against the oracle
+    L0 = CTX - total_steps  # the checked step brings every cache to exactly CTX rows
+    assert L0 > 0, "context too short for this many steps"
 
     kv_esize = 2 if args.kv == "bf16" else 4
     ctx = M.Ctx(max_seq=CTX, n_seqs=B, kv_dtype=M.KV_BF16 if args.kv == "bf16" else M.KV_F32, device=local_rank, kv_rank=rank, kv_world=world,
                 kv_block=256, max_batch=N_LAYERS * B)
     stream = torch.cuda.Stream(device=dev)  # owned by torch, so tensors allocated on it outlive the context safely
     ctx.set_stream(stream.cuda_stream)
+    side = torch.cuda.ExternalStream(ctx.side_stream, device=dev)
     if world > 1:
         # the GatedDeltaNet launch runs beside the attention launch: with the KV split the attention
         # launch is short enough to leave bandwidth unused at its edges
         ctx.set_tuning("gdn_side_queue", 1)
     gen = torch.Generator(device=dev)
+    kv_seed = lambda layer, s: 1234 + 1000 * layer + s
+    st_seed = lambda layer, s: 500000 + 1000 * layer + s
 
     # ---- state: seeded fills on the device, imported through the bulk-import calls ----
+    CH = 8192
+
+    def kv_rows(layer, s, p0, n):
+        """Rows [p0, p0+n) of the seeded cache of (layer, s): the same values on every rank and for the checker."""
+        gen.manual_seed(kv_seed(layer, s) * 4096 + p0 // CH)
+        return (torch.randn(n, KV_DIM, device=dev, generator=gen), torch.randn(n, KV_DIM, device=dev, generator=gen))
+
     with torch.cuda.stream(stream):
-        gen.manual_seed(1234)  # same rows on every rank: the ranks hold shares of the same sequences
-        CH = 8192
         for layer in FULL_LAYERS:
             for s in range(B):
                 for p0 in range(0, L0, CH):
                     n = min(CH, L0 - p0)
-                    kr = torch.randn(n, KV_DIM, device=dev, generator=gen)
-                    vr = torch.randn(n, KV_DIM, device=dev, generator=gen)
+                    kr, vr = kv_rows(layer, s, p0, n)
                     ctx.kv_append_rows_dev(layer, s, p0, n, kr.data_ptr(), vr.data_ptr())
                     stream.synchronize()
         my_seqs = [s for s in range(B) if s % world == rank]
         rs = np.random.Generator(np.random.Philox(77))
+        lin_weights = {}
         for layer in LIN_LAYERS:
             conv_w = (rs.standard_normal((CONV_DIM, 4), dtype=np.float32) * 0.5)
             conv_w_bits = (torch.tensor(conv_w).bfloat16().view(torch.int16).numpy().astype(np.uint16))
             a_log = rs.uniform(0, 2.7, HV).astype(np.float32)
             dt_bits = torch.tensor(rs.standard_normal(HV, dtype=np.float32)).bfloat16().view(torch.int16).numpy().astype(np.uint16)
             nw_bits = torch.tensor(1 + 0.1 * rs.standard_normal(DK, dtype=np.float32)).bfloat16().view(torch.int16).numpy().astype(np.uint16)
+            lin_weights[layer] = (conv_w_bits, a_log, dt_bits, nw_bits)
             ctx.set_linear_weights(layer, conv_w_bits, a_log, dt_bits, nw_bits)
             for s in my_seqs:
+                gen.manual_seed(st_seed(layer, s))
                 cs = torch.randn(3, CONV_DIM, device=dev, generator=gen)
                 ss = torch.randn(SSM_ELEMS, device=dev, generator=gen) * 0.02
                 ctx.linear_state_set_dev(layer, s, cs.data_ptr(), ss.data_ptr())
@@ -261,13 +361,15 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- items ----
     # full-attention items sorted by the rank that finishes them (the owner of the sequence), so the partial
-    # blocks of one destination are contiguous in the send buffer of the all-to-all
+    # blocks of one destination are contiguous
     seq_order = sorted(range(B), key=lambda s: (s % world, s))
     gqa_items = [(l, s) for s in seq_order for l in FULL_LAYERS]
     if world > 1:
-        assert len(gqa_items) % world == 0, "batch must divide over the ranks"
+        assert B % world == 0, "batch must divide over the ranks"
     gdn_items = [(l, s) for l in LIN_LAYERS for s in my_seqs]
     ng, nl = len(gqa_items), len(gdn_items)
+    npr = ng // world                     # items this rank finishes
+    own = slice(rank * npr, (rank + 1) * npr)
     g_layers = np.array([l for l, _ in gqa_items], np.int32)
     g_seqs = np.array([s for _, s in gqa_items], np.int32)
     l_layers = np.array([l for l, _ in gdn_items], np.int32)
@@ -288,11 +390,16 @@ def run_ours(args, rank, world, local_rank):
         out_l = torch.empty(max(nl, 1), V_DIM, device=dev)
         if world > 1:
             item_floats = H * D + 2 * H           # [o | m | l] of one item
-            npr = ng // world                     # items this rank finishes
             send = torch.empty(ng * item_floats, device=dev)
             recv = torch.empty(world * npr * item_floats, device=dev)
             out_own = torch.empty(npr, Q_DIM, device=dev)
     stream.synchronize()
+    if fused:
+        handle = ctx.exchange_create(npr)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        ctx.exchange_connect(handles)
+        dist.barrier()
 
     pos_now = [L0]
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -305,13 +412,15 @@ def run_ours(args, rank, world, local_rank):
             d0, d1, e0, e1 = ev(), ev(), ev(), ev()
 
         def gdn():
+            # with the side queue on, the kernel starts when the main queue reaches this point and runs on the
+            # second queue: its duration is the time from an event here to an event behind it on that queue
             if timed:
                 d0.record(stream)
             if nl:
                 ctx.linear_attn_step_batched_dev(l_layers, l_seqs, qkv.data_ptr(), z.data_ptr(), alpha.data_ptr(),
                                                  beta.data_ptr(), out_l.data_ptr())
             if timed:
-                d1.record(stream)
+                d1.record(side if world > 1 else stream)
 
         if world == 1:
             gdn()
@@ -321,6 +430,15 @@ def run_ours(args, rank, world, local_rank):
                                            vv.data_ptr(), out_g.data_ptr())
             if timed:
                 e1.record(stream)
+        elif fused:
+            gdn()  # on the side queue
+            if timed:
+                e0.record(stream)
+            ctx.full_attn_partial_exchange_dev(g_layers, g_seqs, pos, q.data_ptr(), kk.data_ptr(), vv.data_ptr())
+            if timed:
+                e1.record(stream)
+            ctx.lse_merge_gate_exchange_dev(gate[own].data_ptr(), out_own.data_ptr())
+            ctx.join()
         else:
             gdn()  # on the side queue
             if timed:
@@ -332,8 +450,7 @@ def run_ours(args, rank, world, local_rank):
             # every item's partials travel to the rank that owns its sequence
             dist.all_to_all_single(recv, send)
             ctx.join()
-            ctx.lse_merge_gate_packed_dev(world, npr, recv.data_ptr(), gate[rank * npr:(rank + 1) * npr].data_ptr(),
-                                          out_own.data_ptr())
+            ctx.lse_merge_gate_packed_dev(world, npr, recv.data_ptr(), gate[own].data_ptr(), out_own.data_ptr())
         if timed:
             gqa_events.append((e0, e1))
             gdn_events.append((d0, d1))
@@ -345,62 +462,66 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize(dev)
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    blocks = []
     with torch.cuda.stream(stream):
         for _ in range(W):
             device_step(False)
         if sampler:
             sampler.start()
             time.sleep(0.3)  # before the barrier: every rank enters the timed region together
-        barrier()
         launches0 = ctx.launch_count
         t_wall0 = time.time()
-        start, stop = ev(), ev()
-        start.record(stream)
-        for _ in range(K):
-            device_step(True)
-        stop.record(stream)
-        barrier()
+        pos_first_timed = pos_now[0]
+        for _ in range(R):
+            barrier()
+            start, stop = ev(), ev()
+            start.record(stream)
+            for _ in range(K):
+                device_step(True)
+            stop.record(stream)
+            barrier()
+            blocks.append(start.elapsed_time(stop))
         t_wall1 = time.time()
-        launches = ctx.launch_count - launches0
+        launches = (ctx.launch_count - launches0) // R  # of one block of K steps
     ctx.synchronize()  # raises if a kernel reported a fault
-    ms = start.elapsed_time(stop)
-    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+    mean_pos = pos_first_timed + (R * K - 1) / 2.0
     gqa_ms = sum(a.elapsed_time(b) for a, b in gqa_events) / len(gqa_events)
-    # at N>1 the GatedDeltaNet launch runs on the context's side queue, beside the attention launch:
-    # events on the main queue do not bracket it
-    gdn_ms = sum(a.elapsed_time(b) for a, b in gdn_events) / len(gdn_events) if world == 1 else 0.0
+    gdn_ms = sum(a.elapsed_time(b) for a, b in gdn_events) / len(gdn_events) if nl else 0.0
+    blocks_t = torch.tensor(blocks + [gqa_ms, gdn_ms], device=dev, dtype=torch.float64)
     if world > 1:
-        t = torch.tensor([ms, gqa_ms, gdn_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, gqa_ms, gdn_ms = float(t[0]), float(t[1]), float(t[2])
+        dist.all_reduce(blocks_t, op=dist.ReduceOp.MAX)  # every block: the slowest rank
+    blocks = [float(x) for x in blocks_t[:R]]
+    gqa_ms, gdn_ms = float(blocks_t[R]), float(blocks_t[R + 1])
+    ms = statistics.median(blocks)
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
 
-    # ---- end to end: host (pinned) inputs in, host outputs back, every step ----
+    # ---- end to end: host (pinned) inputs in, host outputs back, every step, through the host-pointer call ----
     e2e = None
     if do_e2e:
         pin = lambda *shape: torch.empty(*shape, dtype=torch.float32).pin_memory()
-        hq, hgate, hk, hv, hout = pin(ng, Q_DIM), pin(ng, Q_DIM), pin(ng, KV_DIM), pin(ng, KV_DIM), pin(ng, Q_DIM)
+        n_gate = ng if world == 1 else npr  # gate rows and outputs are needed only where an item is finished
+        hq, hgate, hk, hv, hout = pin(ng, Q_DIM), pin(n_gate, Q_DIM), pin(ng, KV_DIM), pin(ng, KV_DIM), pin(n_gate, Q_DIM)
         hqkv, hz, ha, hb, hlo = pin(max(nl, 1), CONV_DIM), pin(max(nl, 1), V_DIM), pin(max(nl, 1), HV), pin(
             max(nl, 1), HV), pin(max(nl, 1), V_DIM)
-        for h, d_ in ((hq, q), (hgate, gate), (hk, kk), (hv, vv), (hqkv, qkv), (hz, z), (ha, alpha), (hb, beta)):
+        for h, d_ in ((hq, q), (hgate, gate if world == 1 else gate[own]), (hk, kk), (hv, vv), (hqkv, qkv), (hz, z),
+                      (ha, alpha), (hb, beta)):
             h.copy_(d_.cpu())
-        n_gate = ng if world == 1 else ng // world  # gate rows are needed only where an item is finished
         h2d = 4 * ((ng + n_gate) * Q_DIM + 2 * ng * KV_DIM + nl * (CONV_DIM + V_DIM + 2 * HV))
-        n_out = ng if world == 1 else ng // world
-        hout_own = hout[:n_out]
-        d2h = 4 * (n_out * Q_DIM + nl * V_DIM)
+        d2h = 4 * (n_gate * Q_DIM + nl * V_DIM)
+        use_abi = world == 1 or fused
 
         def e2e_step():
             pos = np.full(ng, pos_now[0], np.int32)
-            if world == 1:
+            if use_abi:
                 ctx.eval_token_attn_ptr(ng, g_layers.ctypes.data, g_seqs.ctypes.data, pos.ctypes.data, hq.data_ptr(),
                                         hgate.data_ptr(), hk.data_ptr(), hv.data_ptr(), hout.data_ptr(), nl,
-                                        l_layers.ctypes.data, l_seqs.ctypes.data, hqkv.data_ptr(), hz.data_ptr(),
-                                        ha.data_ptr(), hb.data_ptr(), hlo.data_ptr())
+                                        l_layers.ctypes.data if nl else 0, l_seqs.ctypes.data if nl else 0,
+                                        hqkv.data_ptr(), hz.data_ptr(), ha.data_ptr(), hb.data_ptr(), hlo.data_ptr())
                 pos_now[0] += 1
             else:
                 with torch.cuda.stream(stream):
                     q.copy_(hq, non_blocking=True)
-                    gate[rank * npr:(rank + 1) * npr].copy_(hgate[rank * npr:(rank + 1) * npr], non_blocking=True)
+                    gate[own].copy_(hgate, non_blocking=True)
                     kk.copy_(hk, non_blocking=True)
                     vv.copy_(hv, non_blocking=True)
                     if nl:
@@ -409,26 +530,95 @@ def run_ours(args, rank, world, local_rank):
                         alpha.copy_(ha, non_blocking=True)
                         beta.copy_(hb, non_blocking=True)
                     device_step(False)
-                    hout_own.copy_(out_own, non_blocking=True)
+                    hout.copy_(out_own, non_blocking=True)
                     if nl:
                         hlo.copy_(out_l, non_blocking=True)
                     stream.synchronize()
 
+        if use_abi and world > 1:
+            ctx.set_tuning("gdn_side_queue", 0)  # the call runs its two groups on its two queues itself
         for _ in range(We):
             e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(Ke):
-            e2e_step()
-        barrier()
-        dt = time.perf_counter() - t0
+        e_blocks = []
+        for _ in range(Re):
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(K):
+                e2e_step()
+            barrier()
+            e_blocks.append(time.perf_counter() - t0)
         if world > 1:
-            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+            t = torch.tensor(e_blocks, device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t[0])
-        e2e = {"value": N_LAYERS * B * Ke / dt, "unit": "layer-steps/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * dt / Ke, "steps": Ke}
+            e_blocks = [float(x) for x in t]
+        dt = statistics.median(e_blocks)
+        e2e = {"value": N_LAYERS * B * K / dt, "unit": "layer-steps/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * dt / K, "steps": K, "repeats": Re,
+               "min": N_LAYERS * B * K / max(e_blocks), "max": N_LAYERS * B * K / min(e_blocks),
+               "api": "mfc_eval_token_attn (host pointers; copies, kernels and exchange inside the call)" if use_abi
+               else "torch copies around the _dev calls and one NCCL all-to-all"}
         ctx.synchronize()
+        if use_abi and world > 1:
+            ctx.set_tuning("gdn_side_queue", 1)
+
+    # ---- parity: one more step, its outputs against the CPU oracle on the same seeded rows ----
+    parity = None
+    with torch.cuda.stream(stream):
+        final_pos = pos_now[0]
+        device_step(False)
+        stream.synchronize()
+    ctx.synchronize()
+    if rank == 0:
+        import oracle as O
+        from oracle import A17B as G
+
+        O.build()
+        O.use_all_cores()
+        tol = 2e-2 if args.kv == "bf16" else 1e-4
+        out_dev = out_g if world == 1 else out_own
+        check = sorted({0, npr - 1}) if world > 1 else sorted({0, ng - 1})  # items this rank finished (index in out_dev)
+        worst = 0.0
+        rnd = O.round_bf16 if args.kv == "bf16" else (lambda a: a)
+        for j in check:
+            gi = j if world == 1 else rank * npr + j
+            layer, s = gqa_items[gi]
+            n_rows = final_pos + 1
+            Kh = np.empty((n_rows, KV_DIM), np.float32)
+            Vh = np.empty((n_rows, KV_DIM), np.float32)
+            for p0 in range(0, L0, CH):
+                n = min(CH, L0 - p0)
+                kr, vr = kv_rows(layer, s, p0, n)
+                Kh[p0:p0 + n] = kr.cpu().numpy()
+                Vh[p0:p0 + n] = vr.cpu().numpy()
+            k_in, v_in = kk[gi].cpu().numpy(), vv[gi].cpu().numpy()
+            zq = np.zeros(Q_DIM, np.float32)
+            for p in range(L0, final_pos):  # the rows the earlier steps appended: RoPE(k) at each position, v as is
+                Kh[p] = O.apply_rotary_emb(p, zq, k_in)[1]
+                Vh[p] = v_in
+            Kh[:final_pos] = rnd(Kh[:final_pos])
+            Vh[:final_pos] = rnd(Vh[:final_pos])
+            ref = O.full_attn_step(final_pos, final_pos, q[gi].cpu().numpy(), gate[gi].cpu().numpy(), k_in, v_in, Kh, Vh, G,
+                                   kv_bf16=args.kv == "bf16")
+            got = out_dev[j].cpu().numpy()
+            worst = max(worst, float(np.max(np.abs(got - ref)) / max(np.max(np.abs(ref)), 1e-30)))
+        parity = {"max_rel_err": worst, "items": len(check), "tol": tol, "context": final_pos + 1,
+                  "what": "outputs of full-attention items of the step after the timed region vs the CPU oracle on the "
+                          "same seeded cache rows" + (f" (every item's partials come from all {world} ranks)" if world > 1 else "")}
+        # one GatedDeltaNet item: every step since the seeded state, replayed on the CPU with the same inputs
+        if nl:
+            layer, s = gdn_items[0]
+            gen.manual_seed(st_seed(layer, s))
+            conv = torch.randn(3, CONV_DIM, device=dev, generator=gen).cpu().numpy().copy()
+            ssm = (torch.randn(SSM_ELEMS, device=dev, generator=gen) * 0.02).cpu().numpy().copy()
+            ins = [t[0].cpu().numpy() for t in (qkv, z, alpha, beta)]
+            ref = None
+            for _ in range(final_pos - L0 + 1):
+                ref = O.linear_attn_step(*ins, *lin_weights[layer], conv, ssm, G)
+            got = out_l[0].cpu().numpy()
+            parity["gdn_max_rel_err"] = float(np.max(np.abs(got - ref)) / max(np.max(np.abs(ref)), 1e-30))
+            parity["gdn_tol"] = 1e-4
+            parity["gdn_steps_replayed"] = final_pos - L0 + 1
+        parity["ok"] = bool(worst <= tol and parity.get("gdn_max_rel_err", 0.0) <= 1e-4)
 
     # ---- roofline of the dominant kernel (the GQA split-K decode launch of this rank) ----
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -436,7 +626,6 @@ def run_ours(args, rank, world, local_rank):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs (of measured)"
     else:
         peak, peak_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
-    mean_pos = L0 + W + (K - 1) / 2.0
     rows_local = (mean_pos + 1) / world
     gqa_alg_bytes = ng * gqa_bytes_per_item(rows_local, kv_esize)
     achieved = gqa_alg_bytes / (gqa_ms * 1e-3) / 1e9
@@ -445,15 +634,16 @@ def run_ours(args, rank, world, local_rank):
     # ctx-8192 case of this workload; the traffic is the streamed KV rows, so it scales with the rows of a launch.
     dram_over_algorithmic = {"bf16": 1.009, "f32": 1.007}[args.kv]
     traffic = gqa_alg_bytes * dram_over_algorithmic
-    launches_per_step = 2 if world == 1 else 3
+    gdn_alg = nl * gdn_bytes_per_item()
     roofline = {"bound": "hbm", "kernel": f"gqa_decode_{args.kv}_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": gqa_alg_bytes, "ms_per_launch": gqa_ms,
                 "frac_of_8TBps": achieved / 8000.0,
                 "other_kernels": {"gdn_decode_kernel": {
-                    "ms_per_launch": gdn_ms, "algorithmic_bytes_per_launch": nl * gdn_bytes_per_item(),
-                    "achieved": (nl * gdn_bytes_per_item() / (gdn_ms * 1e-3) / 1e9) if nl and gdn_ms > 0 else None,
-                    "frac": (nl * gdn_bytes_per_item() / (gdn_ms * 1e-3) / 1e9 / peak) if nl and gdn_ms > 0 else None}},
+                    "ms_per_launch": gdn_ms, "algorithmic_bytes_per_launch": gdn_alg,
+                    "achieved": (gdn_alg / (gdn_ms * 1e-3) / 1e9) if nl and gdn_ms > 0 else None,
+                    "frac": (gdn_alg / (gdn_ms * 1e-3) / 1e9 / peak) if nl and gdn_ms > 0 else None,
+                    "note": "runs on the second queue beside the attention launch" if world > 1 else "runs alone"}},
                 "whole_step": {"algorithmic_bytes_all_gpus": step_bytes,
                                "GBps_per_gpu": step_bytes / world / (ms / K * 1e-3) / 1e9,
                                "frac_of_measured": step_bytes / world / (ms / K * 1e-3) / 1e9 / peak,
@@ -465,8 +655,301 @@ def run_ours(args, rank, world, local_rank):
         line = {"metric": "attention decode layer-steps/sec", "value": value, "unit": "layer-steps/s", "n_gpus": world,
                 "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": f"{args.kv} KV, fp32 accumulate and state", "data": "synthetic",
-                "config": workload_config(args, world), "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches),
-                "clocks": clocks}
+                "config": workload_config(args, world), "repeats": R,
+                "min": N_LAYERS * B * K / (max(blocks) * 1e-3), "max": N_LAYERS * B * K / (min(blocks) * 1e-3),
+                "value_is": f"median of {R} timed blocks of {K} steps (CUDA events, slowest rank per block)",
+                "roofline": roofline, "e2e": e2e, "parity": parity, "gpu_launches": int(launches), "clocks": clocks}
+    ctx.close()
+    return line
+
+
+# --------------------------------------------------------------------------- ragged batch, sharded by sequence
+RAGGED_SEQS = 64
+RAGGED_LO, RAGGED_HI = 1024, 32768
+RAGGED_LAYER = 3  # the full-attention layer of a 4-layer block
+
+
+def ragged_lengths(seed=2):
+    """The 64 seeded context lengths, U[1024, 32768]."""
+    r = np.random.Generator(np.random.Philox(seed))
+    return [int(x) for x in r.integers(RAGGED_LO, RAGGED_HI + 1, RAGGED_SEQS)]
+
+
+def ragged_shards(lens, world):
+    """Sequences dealt to `world` ranks greedily, longest first, each to the rank with the fewest rows so far."""
+    load = [0] * world
+    shards = [[] for _ in range(world)]
+    for s in sorted(range(len(lens)), key=lambda i: (-lens[i], i)):
+        rk = min(range(world), key=lambda k: (load[k], k))
+        shards[rk].append(s)
+        load[rk] += lens[s]
+    return shards, load
+
+
+def ragged_config(args, n):
+    lens = ragged_lengths()
+    return {"workload": f"{RAGGED_SEQS} independent sequences, ragged contexts U[{RAGGED_LO},{RAGGED_HI}] (seeded: "
+                        f"{sum(lens)} cached rows in all), one full-attention GQA layer-step each per step, bf16 KV, "
+                        f"fp32 accumulate",
+            "layer_steps_per_step": RAGGED_SEQS, "rows_total": sum(lens), "kv_dtype": "bf16",
+            "parallelism": (f"sequences dealt over {n} ranks greedily, longest first; no exchange in the data path, the "
+                            f"outputs are gathered (one NCCL all-gather of 32 KiB per sequence)") if n > 1 else "single GPU",
+            "l2": "the KV rows of a step (2.2 GB in all) exceed the 126 MB L2; no flush needed"}
+
+
+def cpu_sample_ragged(args, kind, seed=4):
+    """CPU statement of the ragged batch on a bounded sample: four of the 64 sequences (shortest, two middle,
+    longest), scaled by cached rows to the whole batch."""
+    import oracle as O
+    from oracle import A17B as G
+
+    O.build()
+    lens = ragged_lengths()
+    order = sorted(range(RAGGED_SEQS), key=lambda i: lens[i])
+    sample = [order[0], order[21], order[42], order[-1]]
+    r = np.random.Generator(np.random.Philox(seed))
+    nrm = lambda *s: r.standard_normal(s, dtype=np.float32)
+    t_total, rows = 0.0, 0
+    if kind == "reference":
+        import oracle.ref as R
+        from concurrent.futures import ThreadPoolExecutor
+
+        threads = _host_threads()
+        caches = {s: (O.round_bf16(nrm(lens[s] + 1, KV_DIM)), O.round_bf16(nrm(lens[s] + 1, KV_DIM))) for s in sample}
+        jobs = [sample[i % len(sample)] for i in range(max(threads, len(sample)))]
+        ins = {s: (nrm(Q_DIM), nrm(Q_DIM), nrm(KV_DIM), nrm(KV_DIM)) for s in sample}  # jobs of a sequence append equal rows
+
+        def run(i):
+            s = jobs[i]
+            Kc, Vc = caches[s]
+            R.full_attn_step(lens[s], lens[s], *ins[s], Kc, Vc, H, HKV, D, G.rotary_dim)
+
+        with ThreadPoolExecutor(threads) as ex:
+            t0 = time.perf_counter()
+            list(ex.map(run, range(len(jobs))))
+            t_total = time.perf_counter() - t0
+        rows = sum(lens[s] + 1 for s in jobs)
+        cores = threads
+        how = f"the reference's own C functions (single-threaded each), {len(jobs)} layer-steps side by side on {threads} threads"
+    else:
+        O.use_all_cores()
+        for s in sample:
+            Kc, Vc = O.round_bf16(nrm(lens[s] + 1, KV_DIM)), O.round_bf16(nrm(lens[s] + 1, KV_DIM))
+            ins = (nrm(Q_DIM), nrm(Q_DIM), nrm(KV_DIM), nrm(KV_DIM))
+            t0 = time.perf_counter()
+            O.full_attn_step(lens[s], lens[s], *ins, Kc, Vc, G, kv_bf16=True)
+            t_total += time.perf_counter() - t0
+            rows += lens[s] + 1
+        cores = O.num_threads()
+        how = "the C restatement (oracle/mf_oracle.c, OpenMP over heads), one layer-step at a time"
+    t_step = t_total * (sum(lens) + RAGGED_SEQS) / rows
+    desc = (f"{how}: sequences of {[lens[s] for s in sample]} rows, {rows} rows in {t_total * 1e3:.0f} ms, scaled by rows "
+            f"to the {RAGGED_SEQS} sequences ({sum(lens)} rows)")
+    return RAGGED_SEQS / t_step, cores, desc, kind
+
+
+def run_ragged(args, rank, world, local_rank):
+    """64 ragged sequences, one full-attention layer-step each per step, sharded by sequence."""
+    import torch
+    import torch.distributed as dist
+
+    import moeflux_b200 as M
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    W, K = args.warmup, args.steps
+    lens = ragged_lengths()
+    shards, load = ragged_shards(lens, world)
+    mine = shards[rank]
+    n = len(mine)
+    n_max = max(len(x) for x in shards)
+    R = repeats_for(K, 0.33 * max(load) / sum(lens))
+    do_e2e = not args.no_e2e
+    We, Re = (min(W, 3), min(R, 7)) if do_e2e else (0, 0)
+    total_steps = W + R * K + We + Re * K + 1
+    ctx = M.Ctx(num_layers=4, max_seq=RAGGED_HI + total_steps, n_seqs=max(n, 1), kv_dtype=M.KV_BF16, device=local_rank,
+                max_batch=max(n, 1))
+    stream = torch.cuda.Stream(device=dev)
+    ctx.set_stream(stream.cuda_stream)
+    gen = torch.Generator(device=dev)
+    CH = 8192
+
+    def kv_rows(s, p0, cnt):
+        gen.manual_seed(7000000 + s * 64 + p0 // CH)
+        return (torch.randn(cnt, KV_DIM, device=dev, generator=gen), torch.randn(cnt, KV_DIM, device=dev, generator=gen))
+
+    with torch.cuda.stream(stream):
+        for j, s in enumerate(mine):
+            for p0 in range(0, lens[s], CH):
+                cnt = min(CH, lens[s] - p0)
+                kr, vr = kv_rows(s, p0, cnt)
+                ctx.kv_append_rows_dev(RAGGED_LAYER, j, p0, cnt, kr.data_ptr(), vr.data_ptr())
+                stream.synchronize()
+        gen.manual_seed(4242)
+        q_all = torch.randn(RAGGED_SEQS, Q_DIM, device=dev, generator=gen)
+        gate_all = torch.randn(RAGGED_SEQS, Q_DIM, device=dev, generator=gen)
+        k_all = torch.randn(RAGGED_SEQS, KV_DIM, device=dev, generator=gen)
+        v_all = torch.randn(RAGGED_SEQS, KV_DIM, device=dev, generator=gen)
+        idx = torch.tensor(mine, device=dev, dtype=torch.long)
+        q, gate, kk, vv = (t[idx].contiguous() for t in (q_all, gate_all, k_all, v_all))
+        out_pad = torch.zeros(n_max, Q_DIM, device=dev)      # this rank's outputs, padded to the largest shard
+        gathered = torch.empty(world * n_max, Q_DIM, device=dev) if world > 1 else None
+    stream.synchronize()
+    layers = np.full(n, RAGGED_LAYER, np.int32)
+    seqs = np.arange(n, dtype=np.int32)
+    step_no = [0]
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    k_events = []
+
+    def device_step(timed):
+        pos = np.array([lens[s] + step_no[0] for s in mine], np.int32)
+        if timed:
+            e0, e1 = ev(), ev()
+            e0.record(stream)
+        ctx.full_attn_step_batched_dev(layers, seqs, pos, q.data_ptr(), gate.data_ptr(), kk.data_ptr(), vv.data_ptr(),
+                                       out_pad.data_ptr())
+        if timed:
+            e1.record(stream)
+            k_events.append((e0, e1))
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out_pad)
+        step_no[0] += 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    blocks = []
+    with torch.cuda.stream(stream):
+        for _ in range(W):
+            device_step(False)
+        if sampler:
+            sampler.start()
+            time.sleep(0.3)
+        launches0 = ctx.launch_count
+        t_wall0 = time.time()
+        first_timed = step_no[0]
+        for _ in range(R):
+            barrier()
+            start, stop = ev(), ev()
+            start.record(stream)
+            for _ in range(K):
+                device_step(True)
+            stop.record(stream)
+            barrier()
+            blocks.append(start.elapsed_time(stop))
+        t_wall1 = time.time()
+        launches = (ctx.launch_count - launches0) // R
+    ctx.synchronize()
+    k_ms = sum(a.elapsed_time(b) for a, b in k_events) / len(k_events)
+    t = torch.tensor(blocks + [k_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    blocks, k_ms = [float(x) for x in t[:R]], float(t[R])
+    ms = statistics.median(blocks)
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+
+    e2e = None
+    if do_e2e:
+        pin = lambda *shape: torch.empty(*shape, dtype=torch.float32).pin_memory()
+        hq, hgate, hk, hv, hout = pin(n, Q_DIM), pin(n, Q_DIM), pin(n, KV_DIM), pin(n, KV_DIM), pin(n, Q_DIM)
+        for h, d_ in ((hq, q), (hgate, gate), (hk, kk), (hv, vv)):
+            h.copy_(d_.cpu())
+
+        def e2e_step():
+            pos = np.array([lens[s] + step_no[0] for s in mine], np.int32)
+            ctx.full_attn_step_batched_ptr(n, layers.ctypes.data, seqs.ctypes.data, pos.ctypes.data, hq.data_ptr(),
+                                           hgate.data_ptr(), hk.data_ptr(), hv.data_ptr(), hout.data_ptr())
+            step_no[0] += 1
+
+        for _ in range(We):
+            e2e_step()
+        e_blocks = []
+        for _ in range(Re):
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(K):
+                e2e_step()
+            barrier()
+            e_blocks.append(time.perf_counter() - t0)
+        if world > 1:
+            te = torch.tensor(e_blocks, device=dev, dtype=torch.float64)
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            e_blocks = [float(x) for x in te]
+        dt = statistics.median(e_blocks)
+        e2e = {"value": RAGGED_SEQS * K / dt, "unit": "layer-steps/s", "h2d_bytes_per_step": 4 * n * (2 * Q_DIM + 2 * KV_DIM),
+               "d2h_bytes_per_step": 4 * n * Q_DIM, "ms_per_step": 1e3 * dt / K, "steps": K, "repeats": Re,
+               "api": "mfc_full_attn_step_batched (host pointers; each rank's shard, results stay on the rank's host)",
+               "bytes_are": "this rank's"}
+
+    # parity: the step after the timed region, this rank's shortest and longest sequence against the oracle
+    parity = None
+    with torch.cuda.stream(stream):
+        final = step_no[0]
+        device_step(False)
+        stream.synchronize()
+    ctx.synchronize()
+    if rank == 0 and n:
+        import oracle as O
+        from oracle import A17B as G
+
+        O.build()
+        O.use_all_cores()
+        by_len = sorted(range(n), key=lambda j: lens[mine[j]])
+        worst = 0.0
+        zq = np.zeros(Q_DIM, np.float32)
+        for j in sorted({by_len[0], by_len[-1]}):
+            s = mine[j]
+            rows = lens[s] + final
+            Kh = np.empty((rows + 1, KV_DIM), np.float32)
+            Vh = np.empty((rows + 1, KV_DIM), np.float32)
+            for p0 in range(0, lens[s], CH):
+                cnt = min(CH, lens[s] - p0)
+                kr, vr = kv_rows(s, p0, cnt)
+                Kh[p0:p0 + cnt] = kr.cpu().numpy()
+                Vh[p0:p0 + cnt] = vr.cpu().numpy()
+            k_in, v_in = kk[j].cpu().numpy(), vv[j].cpu().numpy()
+            for p in range(lens[s], rows):
+                Kh[p] = O.apply_rotary_emb(p, zq, k_in)[1]
+                Vh[p] = v_in
+            Kh[:rows] = O.round_bf16(Kh[:rows])
+            Vh[:rows] = O.round_bf16(Vh[:rows])
+            ref = O.full_attn_step(rows, rows, q[j].cpu().numpy(), gate[j].cpu().numpy(), k_in, v_in, Kh, Vh, G, kv_bf16=True)
+            got = out_pad[j].cpu().numpy()
+            worst = max(worst, float(np.max(np.abs(got - ref)) / max(np.max(np.abs(ref)), 1e-30)))
+            if world > 1:  # and the gathered copy of the same row
+                gg = gathered[rank * n_max + j].cpu().numpy()
+                worst = max(worst, float(np.max(np.abs(gg - ref)) / max(np.max(np.abs(ref)), 1e-30)))
+        parity = {"max_rel_err": worst, "items": 2, "tol": 2e-2, "ok": bool(worst <= 2e-2),
+                  "what": "rank 0's shortest and longest sequence, the step after the timed region, vs the CPU oracle"}
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs (of measured)"
+    else:
+        peak, peak_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
+    mean_step = first_timed + (R * K - 1) / 2.0
+    # the slowest rank sets the time: its rows are what the launch time is compared with
+    shard_rows = max(sum(lens[s] + mean_step + 1 for s in sh) for sh in shards)
+    n_slow = max(len(sh) for sh in shards)
+    alg = 2 * shard_rows * KV_DIM * 2 + n_slow * (3 * Q_DIM * 4 + 2 * KV_DIM * 4 + 2 * KV_DIM * 2)
+    achieved = alg / (k_ms * 1e-3) / 1e9
+    line = None
+    if rank == 0:
+        line = {"metric": "attention decode layer-steps/sec", "value": RAGGED_SEQS * K / (ms * 1e-3), "unit": "layer-steps/s",
+                "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16 KV, fp32 accumulate", "data": "synthetic",
+                "config": ragged_config(args, world), "repeats": R,
+                "min": RAGGED_SEQS * K / (max(blocks) * 1e-3), "max": RAGGED_SEQS * K / (min(blocks) * 1e-3),
+                "value_is": f"median of {R} timed blocks of {K} steps (CUDA events, slowest rank per block)",
+                "shard_rows": load,
+                "roofline": {"bound": "hbm", "kernel": "gqa_decode_bf16_kernel", "achieved": achieved, "peak": peak,
+                             "unit": "GB/s", "frac": achieved / peak, "traffic": alg * 1.009, "peak_source": peak_src,
+                             "algorithmic_bytes_per_launch": alg, "ms_per_launch": k_ms,
+                             "frac_of_8TBps": achieved / 8000.0, "launch_is": "the largest shard's"},
+                "e2e": e2e, "parity": parity, "gpu_launches": int(launches), "clocks": clocks}
     ctx.close()
     return line
 
@@ -695,15 +1178,23 @@ def main():
         if rank == 0:
             print(json.dumps(run_matvec(args)), flush=True)
         return
-    line = run_ours(args, rank, world, local_rank)
+    line = run_ragged(args, rank, world, local_rank) if args.workload == "ragged" else run_ours(args, rank, world, local_rank)
+    failed = False
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
-            v, cores, desc = cpu_sample(args.ctx, args.batch)
-            line["cpu_baseline"] = {"value": v, "unit": "layer-steps/s", "cores": cores, "kind": "port", "sample": desc}
+            kind = reference_kind()
+            if args.workload == "ragged":
+                v, cores, desc, kind = cpu_sample_ragged(args, kind)
+            else:
+                v, cores, desc, kind = cpu_sample(args.ctx, args.batch, kind=kind)
+            line["cpu_baseline"] = {"value": v, "unit": "layer-steps/s", "cores": cores, "kind": kind, "sample": desc}
         print(json.dumps(line), flush=True)
+        failed = bool(line.get("parity")) and not line["parity"]["ok"]
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("parity check failed: " + json.dumps(line["parity"]))
 
 
 if __name__ == "__main__":

@@ -75,8 +75,12 @@ void mfc_default_config(mfc_config *cfg);
 
 /* Replaces mf_init_model / RsCtx::open for this path (moeflux.h:55,
  * crates/moeflux/src/riir/mod.rs:270).  Allocates the KV caches, the
- * GatedDeltaNet states (zeroed) and all working memory up front; no other entry
- * point allocates device memory.  NULL on failure (mfc_last_error(NULL)). */
+ * GatedDeltaNet states (zeroed) and all working memory up front.  No entry
+ * point of the hot path allocates device memory afterwards; the exceptions are
+ * mfc_exchange_create (once, at set-up) and the host-pointer test hook
+ * mfc_dequant_matvec_4bit (a temporary allocation per call).  Every allocation
+ * of the context sits between two bands of 0xFF bytes that no kernel may touch
+ * (mfc_check_guards).  NULL on failure (mfc_last_error(NULL)). */
 mfc_ctx *mfc_open(const mfc_config *cfg);
 /* mf_free_model (moeflux.h:66).  No-op on NULL. */
 void mfc_free(mfc_ctx *ctx);
@@ -87,13 +91,17 @@ const char *mfc_last_error(const mfc_ctx *ctx);
 int mfc_get_config(const mfc_ctx *ctx, mfc_config *out);
 /* cudaStream_t of the context, as void*; `_dev` calls are ordered on it. */
 void *mfc_stream(mfc_ctx *ctx);
+/* The context's second queue (see mfc_join), as void*: for recording events around what runs there. */
+void *mfc_side_stream(mfc_ctx *ctx);
 /* Makes the context issue all further work on the caller's stream (a
  * cudaStream_t on the context's device; NULL = the legacy default stream).  The
  * caller keeps ownership and must keep the stream alive while the context uses
  * it.  Waits for the work already queued on the previous stream. */
 int mfc_set_stream(mfc_ctx *ctx, void *stream);
-/* Blocks until the context's stream is idle; -1 if a kernel reported a fault
- * (bounded wait expired) since the last call. */
+/* Blocks until the context's stream is idle; -1 if a kernel gave up since the
+ * last call (a bounded wait ran out, or an item failed the kernel's range
+ * checks): the message names which.  The report is cleared and the context
+ * stays usable. */
 int mfc_synchronize(mfc_ctx *ctx);
 
 /* Per-layer constant tensors of a GatedDeltaNet layer, read where the reference
@@ -172,7 +180,10 @@ int mfc_full_attn_step_qproj_batched_dev(mfc_ctx *ctx, int32_t n, const int32_t 
  * loop for this path, for layers whose inputs do not depend on one another's
  * outputs; the two groups run on two queues so that the host<->device copies of
  * one overlap the kernel of the other.  All arguments are validated before
- * anything is queued: on -1 no state has changed. */
+ * anything is queued: on -1 no state has changed.  On a context of a KV split
+ * (kv_world > 1, exchange connected) the full-attention group is the whole
+ * step's item list sorted by finishing rank, and gate / full_out cover the
+ * items_per_rank items this rank finishes (see mfc_exchange_create). */
 int mfc_eval_token_attn(mfc_ctx *ctx, int32_t n_full, const int32_t *full_layers,
                         const int32_t *full_seqs, const int32_t *pos, const float *q,
                         const float *gate, const float *k, const float *v, float *full_out,
@@ -357,12 +368,20 @@ int mfc_linear_attn_step_stateless(mfc_ctx *ctx, int32_t layer, const float *qkv
  * (different streams, different threads) therefore race: serialise them.
  * The first call on each device resolves the array's device address and raises
  * the kernel's shared-memory limit; make that first call before any stream
- * capture begins.  Returns 0 on success, -1 on error. */
+ * capture begins.  Nothing is read from host memory after the call returns (the
+ * work descriptor travels as a kernel argument).  The cache rows past kv_len
+ * are never used, whatever they hold.  Returns 0 on success, -1 on error.
+ *
+ * mfc_sdpa_static_status(stream) waits for `stream` and reports what the kernels
+ * of the calls since the previous status call found: 0, or -1 (a bounded wait on
+ * a load ran out; message in mfc_last_error(NULL)).  It allocates nothing and
+ * clears the report. */
 #define MFC_STATIC_MAX_KV_HEADS 8
 #define MFC_STATIC_MAX_ROWS 262144
 int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv_dtype,
                         int32_t kv_len, int32_t cap_rows, const float *q, const float *gate,
                         const void *k_cache, const void *v_cache, float *out, void *stream);
+int mfc_sdpa_static_status(void *stream);
 
 /* ---- The step either side of the path: 4-bit affine-quantised projections ----
  * Replaces dequant_matvec_4bit_cpu (crates/moeflux/src/riir/cpu_matvec.rs:83-171) and the
@@ -401,20 +420,65 @@ int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *ctx, int32_t n_mat, const uint32_
                                       float *const *outs);
 
 /* Tuning knobs (tests and sweeps): "gdn_rows" in {0,32,64,128} state rows per
- * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a launch aims for when it picks the KV chunk
- * length (0 = wave-aware automatic plan); "gqa_chunk" forces the chunk length (0 = automatic); "gdn_side_queue" (see
- * mfc_join). */
+ * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a decode launch aims for when it cuts the launch's
+ * KV tiles into equal runs (0 = one wave: two CTAs per SM); "gqa_chunk" forces the rows per CTA (0 = automatic);
+ * "gdn_side_queue" (see mfc_join); "gqa_wait_spins" poll limit of the kernels' bounded waits (0 = default);
+ * "gqa_inject_lost_load" 1 = the first CTA of the next decode launches arms the barrier of its first KV tile and
+ * issues no load for it, so that its bounded wait runs out with nothing in flight (exercises the failure path
+ * without faulting the GPU: the kernel returns, mfc_synchronize reports -1, the context stays usable);
+ * "gqa_phase_trace" 1 = decode launches of at most 1024 CTAs record per-CTA time stamps (mfc_read_phase_trace). */
 int mfc_set_tuning(mfc_ctx *ctx, const char *key, int value);
 /* With the tuning "gdn_side_queue" = 1, mfc_linear_attn_step_batched_dev issues
  * its kernel on a second queue of the context: it starts after everything
  * already queued on mfc_stream(ctx) and runs beside whatever is queued there
  * next (a bandwidth-bound attention launch leaves room for it).  mfc_join makes
- * mfc_stream(ctx) wait for that kernel; mfc_synchronize and every host-pointer
- * entry point join implicitly. */
+ * mfc_stream(ctx) wait for that kernel; mfc_synchronize, every host-pointer
+ * entry point and every call that reads or writes GatedDeltaNet state outside
+ * the step (snapshots, checkpoints, truncation, bulk import, prefill) join
+ * implicitly. */
 int mfc_join(mfc_ctx *ctx);
 
 /* Number of kernels this library has launched on the context so far. */
 long long mfc_launch_count(const mfc_ctx *ctx);
+
+/* Waits for the context's work and verifies the bands of 0xFF bytes that surround every device allocation of the
+ * context (KV caches, states, weights, split-K scratch, counters, staging).  0 when all are intact; -1 and the name
+ * of the allocation in mfc_last_error when a kernel wrote outside its buffer.  Stands in for a memory checker (the
+ * reference relies on Rust ownership, crates/moeflux/src/lib.rs:37); the GPU tests call it after every test. */
+int mfc_check_guards(mfc_ctx *ctx);
+/* Time stamps (nanoseconds, %globaltimer) of the CTAs of the last decode launch made with the tuning
+ * "gqa_phase_trace" on: out[cta][8] = {start, first segment's Q fragments ready, its last KV tile consumed, its
+ * epilogue done, CTA done, 0, 0, 0}.  Returns the number of CTAs written (at most max_ctas), or -1. */
+int mfc_read_phase_trace(mfc_ctx *ctx, unsigned long long *out, int32_t max_ctas);
+
+/* ---- KV-sequence split: the exchange fused into the decode kernel ----
+ * New (the reference is single-device).  With the KV positions of every sequence split over kv_world contexts, one
+ * per GPU, each context computes un-normalised partials for all items and every item is finished on one rank (the
+ * owner of its sequence).  Instead of writing the partials locally and handing them to a collective, the decode
+ * kernel stores each merged partial block [o | m | l] straight into the receive buffer of the owner through a
+ * peer-mapped pointer (plain stores over NVLink; no multicast, no TMA from or to peer memory), and its last CTA
+ * publishes a step number in every peer's flag array once the stores are visible.  The owner's merge kernel waits
+ * (bounded) for the step number of every rank, merges by log-sum-exp and applies the gate.  Receive buffers are
+ * double-buffered by step parity, which is enough: a rank cannot start step s+2 before every peer has merged step s.
+ *
+ * Set-up, once: every rank calls mfc_exchange_create (allocates its receive buffers and flags, returns a CUDA IPC
+ * handle of MFC_IPC_HANDLE_BYTES bytes), the ranks exchange the handles by any means (e.g. an all-gather), and each
+ * calls mfc_exchange_connect with the kv_world handles in rank order.  Contexts that live in ONE process (tests)
+ * call mfc_exchange_connect_local with the kv_world context pointers instead (ipc_handle_out may be NULL).
+ * items_per_rank: full-attention items each rank finishes per step; a step carries items_per_rank * kv_world items
+ * sorted by finishing rank (item i is finished by rank i / items_per_rank).
+ *
+ * Per step: mfc_full_attn_partial_exchange_dev (arguments as mfc_full_attn_partial_packed_dev, no output pointer),
+ * then mfc_lse_merge_gate_exchange_dev: gate [items_per_rank][heads*256] (may be NULL) and out of the same shape
+ * for the items this rank finishes, in item order.  Every rank must issue the same steps.  mfc_eval_token_attn on
+ * such a context does both, with gate and full_out covering this rank's items only. */
+#define MFC_IPC_HANDLE_BYTES 64
+int mfc_exchange_create(mfc_ctx *ctx, int32_t items_per_rank, void *ipc_handle_out);
+int mfc_exchange_connect(mfc_ctx *ctx, const void *ipc_handles);
+int mfc_exchange_connect_local(mfc_ctx *ctx, mfc_ctx *const *peers);
+int mfc_full_attn_partial_exchange_dev(mfc_ctx *ctx, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                       const int32_t *pos, const float *q, const float *k, const float *v);
+int mfc_lse_merge_gate_exchange_dev(mfc_ctx *ctx, const float *gate, float *out);
 
 #ifdef __cplusplus
 }

@@ -7,6 +7,6 @@ is in ``libmoeflux_cuda.so``; there is no Python or CPU fallback, and importing
 the library without the built shared object raises.
 """
 from ._lib import MfcError, Config, lib, lib_path, KV_F32, KV_BF16
-from .ctx import Ctx, sdpa_static_dev
+from .ctx import Ctx, live_contexts, sdpa_static_dev, sdpa_static_status
 
-__all__ = ["Ctx", "sdpa_static_dev", "Config", "MfcError", "lib", "lib_path", "KV_F32", "KV_BF16"]
+__all__ = ["Ctx", "live_contexts", "sdpa_static_dev", "sdpa_static_status", "Config", "MfcError", "lib", "lib_path", "KV_F32", "KV_BF16"]

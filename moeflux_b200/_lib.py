@@ -59,6 +59,7 @@ SIGNATURES = {
     "mfc_last_error": (C.c_char_p, [_P]),
     "mfc_get_config": (C.c_int, [_P, C.POINTER(Config)]),
     "mfc_stream": (_P, [_P]),
+    "mfc_side_stream": (_P, [_P]),
     "mfc_set_stream": (C.c_int, [_P, _P]),
     "mfc_synchronize": (C.c_int, [_P]),
     "mfc_set_linear_weights": (C.c_int, [_P, C.c_int32, _U16, _F, _U16, _U16]),
@@ -98,7 +99,15 @@ SIGNATURES = {
     "mfc_kv_local_row": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "mfc_snapshot_validate": (C.c_longlong, [C.POINTER(Config), _P, C.c_size_t]),
     "mfc_sdpa_static_dev": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P]),
+    "mfc_sdpa_static_status": (C.c_int, [_P]),
     "mfc_join": (C.c_int, [_P]),
+    "mfc_check_guards": (C.c_int, [_P]),
+    "mfc_read_phase_trace": (C.c_int, [_P, _P, C.c_int32]),
+    "mfc_exchange_create": (C.c_int, [_P, C.c_int32, _P]),
+    "mfc_exchange_connect": (C.c_int, [_P, _P]),
+    "mfc_exchange_connect_local": (C.c_int, [_P, _P]),
+    "mfc_full_attn_partial_exchange_dev": (C.c_int, [_P, C.c_int32, _I, _I, _I, _P, _P, _P]),
+    "mfc_lse_merge_gate_exchange_dev": (C.c_int, [_P, _P, _P]),
     "mfc_dequant_matvec_4bit_dev": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
     "mfc_dequant_matvec_4bit": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
     "mfc_dequant_matvec_4bit_multi_dev": (C.c_int, [_P, C.c_int32, _P, _P, _P, C.c_int32, _P, _P, C.c_int32, _P]),

@@ -14,6 +14,7 @@ namespace mfc {
 enum : unsigned {
     STATUS_TMA_TIMEOUT = 1u,
     STATUS_BAD_ITEM = 2u,
+    STATUS_PEER_TIMEOUT = 4u,
 };
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) {

@@ -86,9 +86,48 @@ struct mfc_ctx {
     GdnItem *d_gdn_items = nullptr;
     std::vector<GqaItem> h_gqa_items;
     std::vector<GdnItem> h_gdn_items;
+    // Item lists travel through a small ring of pinned host slots: a copy from pageable memory is staged by the
+    // driver and blocks the calling thread, a copy from pinned memory is queued like a kernel.
+    static constexpr int PIN_SLOTS = 8;
+    uint8_t *pin_items = nullptr;
+    size_t pin_slot_bytes = 0;
+    cudaEvent_t pin_ev[PIN_SLOTS] = {};
+    bool pin_used[PIN_SLOTS] = {};
+    unsigned pin_next = 0;
     float *sc_o = nullptr, *sc_m = nullptr, *sc_l = nullptr;
-    unsigned *tickets = nullptr, *status = nullptr;
+    unsigned *tickets = nullptr, *group_tickets = nullptr, *status = nullptr;
     int max_parts = 0;
+    // every device allocation of the context, with a band of 0xFF bytes on either side (mfc_check_guards)
+    struct Alloc {
+        uint8_t *base;
+        size_t bytes;  // user bytes between the bands
+        const char *name;
+        bool banded;   // false: a plain allocation (the exchange buffer, whose IPC handle names it from its base)
+    };
+    std::vector<Alloc> allocs;
+    static constexpr size_t GUARD = 4096;
+    // diagnostics
+    unsigned gqa_wait_spins = 0;
+    int gqa_inject_lost_load = 0;
+    unsigned long long *phase_trace = nullptr;  // [MAX_TRACE_CTAS][PHASE_TRACE_WORDS]
+    static constexpr int MAX_TRACE_CTAS = 1024;
+    bool phase_trace_on = false;
+    int last_launch_ctas = 0;
+    // fused exchange of the KV-sequence split (mfc_exchange_*)
+    struct Exchange {
+        uint8_t *base = nullptr;        // one allocation: [2][world][npr][item floats] receive blocks, then flags
+        float *recv = nullptr;
+        unsigned *flags = nullptr;      // [world], written by the peers
+        size_t bytes = 0, recv_bytes = 0;
+        int npr = 0;                    // items this rank finishes per step
+        std::vector<uint8_t *> peer_base;   // this process's mapping of every rank's allocation
+        std::vector<bool> peer_is_ipc;
+        float **d_peer_recv = nullptr;      // device [2][world]
+        unsigned **d_peer_flags = nullptr;  // device [world]
+        unsigned *done_counter = nullptr;
+        unsigned step = 0;              // steps issued so far (flag value of the latest one)
+        bool connected = false;
+    } xc;
     int plan_tiles_per_cta = 1, plan_total_tiles = 0;  // split of the launch being built
 
     // device staging for the host-pointer entry points (max_batch items)
@@ -150,15 +189,21 @@ int local_row_of(int p, int r, int W, int B) {
     return (blk / W) * B + p % B;
 }
 
+// Device allocation with a band of GUARD bytes of 0xFF before and after the user range.  Kernels never write
+// there; mfc_check_guards() verifies that they did not (evidence of in-bounds writes where no memory checker runs).
 template <typename T>
-bool dalloc(mfc_ctx *c, T **p, size_t n, bool zero) {
+bool dalloc(mfc_ctx *c, T **p, size_t n, bool zero, const char *name = "buffer") {
     if (n == 0) n = 1;
-    cudaError_t e = cudaMalloc((void **)p, n * sizeof(T));
-    if (e != cudaSuccess) return fail(c, std::string("cudaMalloc: ") + cudaGetErrorString(e));
-    if (zero) {
-        e = cudaMemset(*p, 0, n * sizeof(T));
-        if (e != cudaSuccess) return fail(c, std::string("cudaMemset: ") + cudaGetErrorString(e));
-    }
+    const size_t bytes = (n * sizeof(T) + 255) & ~(size_t)255;
+    uint8_t *base = nullptr;
+    cudaError_t e = cudaMalloc((void **)&base, bytes + 2 * mfc_ctx::GUARD);
+    if (e != cudaSuccess) return fail(c, std::string("cudaMalloc(") + name + "): " + cudaGetErrorString(e));
+    c->allocs.push_back({base, bytes, name, true});
+    e = cudaMemset(base, 0xFF, mfc_ctx::GUARD);
+    if (e == cudaSuccess) e = cudaMemset(base + mfc_ctx::GUARD + bytes, 0xFF, mfc_ctx::GUARD);
+    if (e == cudaSuccess && zero) e = cudaMemset(base + mfc_ctx::GUARD, 0, bytes);
+    if (e != cudaSuccess) return fail(c, std::string("cudaMemset: ") + cudaGetErrorString(e));
+    *p = reinterpret_cast<T *>(base + mfc_ctx::GUARD);
     return true;
 }
 
@@ -201,18 +246,34 @@ bool make_tensor_map(mfc_ctx *c, CUtensorMap *map, void *base, uint64_t rows, in
 }
 
 void free_all(mfc_ctx *c) {
-    void *ptrs[] = {c->k_cache, c->v_cache, c->ssm, c->conv, c->conv_w, c->dt_bias, c->norm_w, c->a_log,
-                    c->inv_freq, c->d_gqa_items, c->d_gdn_items, c->sc_o, c->sc_m, c->sc_l, c->tickets,
-                    c->status, c->st_q, c->st_gate, c->st_k, c->st_v, c->st_out, c->st_qkv, c->st_z,
-                    c->st_alpha, c->st_beta, c->st_gout, c->st_rows, c->pf_cos_sin, c->pf_q, c->pf_k, c->pf_v,
-                    c->pf_lg, c->pf_beta, c->pf_wt, c->pf_wm, c->qnorm_w, c->knorm_w, c->st_qproj};
-    for (void *p : ptrs)
-        if (p) cudaFree(p);
+    for (size_t r = 0; r < c->xc.peer_base.size(); r++)
+        if (c->xc.peer_base[r] && c->xc.peer_is_ipc[r]) cudaIpcCloseMemHandle(c->xc.peer_base[r]);
+    for (const mfc_ctx::Alloc &a : c->allocs) cudaFree(a.base);
+    c->allocs.clear();
+    if (c->pin_items) cudaFreeHost(c->pin_items);
+    for (cudaEvent_t e : c->pin_ev)
+        if (e) cudaEventDestroy(e);
     if (c->stream && c->owns_stream) cudaStreamDestroy(c->stream);
     if (c->side_stream) cudaStreamDestroy(c->side_stream);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->ev_join) cudaEventDestroy(c->ev_join);
     if (c->ev_gate) cudaEventDestroy(c->ev_gate);
+}
+
+// Queues the copy of an item list to the device through the next pinned slot.
+int upload_items(mfc_ctx *c, void *dst, const void *src, size_t bytes, cudaStream_t stream) {
+    if (bytes > c->pin_slot_bytes) {
+        fail(c, "internal: item list larger than a staging slot");
+        return -1;
+    }
+    const int slot = (int)(c->pin_next++ % mfc_ctx::PIN_SLOTS);
+    if (c->pin_used[slot]) CK(cudaEventSynchronize(c->pin_ev[slot]));  // the copy that last read this slot
+    uint8_t *h = c->pin_items + (size_t)slot * c->pin_slot_bytes;
+    memcpy(h, src, bytes);
+    CK(cudaMemcpyAsync(dst, h, bytes, cudaMemcpyHostToDevice, stream));
+    CK(cudaEventRecord(c->pin_ev[slot], stream));
+    c->pin_used[slot] = true;
+    return 0;
 }
 
 int check_status(mfc_ctx *c) {
@@ -224,8 +285,19 @@ int check_status(mfc_ctx *c) {
     CK(cudaMemcpyAsync(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     if (st) {
-        fail(c, "a kernel gave up on a bounded wait (device status " + std::to_string(st) +
-                    "); results of this context are no longer valid");
+        // the counters of the split-K merge return to zero by themselves (a CTA that gives up still takes its
+        // tickets); they are cleared all the same, with the status word, so that the context stays usable
+        cudaMemsetAsync(c->status, 0, sizeof(unsigned), c->stream);
+        cudaMemsetAsync(c->tickets, 0, sizeof(unsigned) * (size_t)c->cfg.max_batch * c->cfg.num_kv_heads, c->stream);
+        cudaMemsetAsync(c->group_tickets, 0, sizeof(unsigned) * (size_t)c->max_parts, c->stream);
+        if (c->xc.done_counter) cudaMemsetAsync(c->xc.done_counter, 0, sizeof(unsigned), c->stream);
+        cudaStreamSynchronize(c->stream);
+        std::string what;
+        if (st & 1u) what += " a load did not arrive within the wait limit;";
+        if (st & 2u) what += " an item failed its range checks;";
+        if (st & 4u) what += " a peer's partials did not arrive within the wait limit;";
+        fail(c, "a kernel gave up (device status " + std::to_string(st) + ":" + what +
+                    ") the results since the last synchronisation are not valid");
         return -1;
     }
     return 0;
@@ -239,7 +311,7 @@ int check_status(mfc_ctx *c) {
 // the whole launch with equal work per CTA.  A unit cut by a run boundary is merged
 // from the partials of the CTAs that share it.  Constraints: at least 256 rows per
 // CTA (a CTA's start-up and epilogue cost about as much as streaming that), at most
-// MAX_SPLITS partials per unit.
+// MAX_UNIT_PARTS partials per unit.
 int plan_tiles_per_cta(const mfc_ctx *c, long long total_tiles, int max_unit_tiles) {
     const int tile = c->cfg.kv_dtype == MFC_KV_BF16 ? KV_TILE : KV_TILE_F32;
     long long w;
@@ -251,7 +323,7 @@ int plan_tiles_per_cta(const mfc_ctx *c, long long total_tiles, int max_unit_til
         const long long w_min = 256 / tile;
         if (w < w_min) w = w_min;
     }
-    const long long w_split = (max_unit_tiles + (MAX_SPLITS - 2) - 1) / (MAX_SPLITS - 2);
+    const long long w_split = (max_unit_tiles + (MAX_UNIT_PARTS - 2) - 1) / (MAX_UNIT_PARTS - 2);
     if (w < w_split) w = w_split;
     if (w < 1) w = 1;
     return (int)w;
@@ -342,6 +414,12 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
     p.sc_m = c->sc_m;
     p.sc_l = c->sc_l;
     p.tickets = c->tickets;
+    p.group_tickets = c->group_tickets;
+    p.n_kv_slots = c->n_kv_slots;
+    p.wait_spins = c->gqa_wait_spins;
+    p.inject_lost_load = c->gqa_inject_lost_load;
+    p.phase_trace = (c->phase_trace_on && total_ctas <= mfc_ctx::MAX_TRACE_CTAS) ? c->phase_trace : nullptr;
+    c->last_launch_ctas = total_ctas;
     p.inv_freq = c->inv_freq;
     p.status = c->status;
     p.H = g.num_attn_heads;
@@ -359,8 +437,7 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
 }
 
 int launch_gqa(mfc_ctx *c, const GqaParams &p) {
-    CK(cudaMemcpyAsync(c->d_gqa_items, c->h_gqa_items.data(), sizeof(GqaItem) * p.n_items,
-                       cudaMemcpyHostToDevice, c->stream));
+    if (upload_items(c, c->d_gqa_items, c->h_gqa_items.data(), sizeof(GqaItem) * p.n_items, c->stream)) return -1;
     if (c->cfg.kv_dtype == MFC_KV_BF16) CK(launch_gqa_decode_bf16(c->kmap, c->vmap, p, c->stream));
     else CK(launch_gqa_decode_f32(c->kmap, c->vmap, p, c->stream));
     c->launches += 1;
@@ -428,8 +505,7 @@ int launch_gdn(mfc_ctx *c, int n, const float *qkv, const float *z, const float 
     p.Hk = g.linear_num_k_heads;
     p.conv_dim = c->conv_dim;
     p.eps = g.rms_norm_eps;
-    CK(cudaMemcpyAsync(c->d_gdn_items, c->h_gdn_items.data(), sizeof(GdnItem) * n,
-                       cudaMemcpyHostToDevice, c->stream));
+    if (upload_items(c, c->d_gdn_items, c->h_gdn_items.data(), sizeof(GdnItem) * n, c->stream)) return -1;
     // Whole heads per CTA (128 rows) amortise the conv/norm prologue best; smaller
     // blocks only when the launch would otherwise leave SMs without work.
     int rows = c->gdn_rows;
@@ -676,35 +752,40 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     const size_t qd = (size_t)g.num_attn_heads * HEAD_DIM, kvd = (size_t)g.num_kv_heads * HEAD_DIM;
     const size_t vd = (size_t)g.linear_num_v_heads * GDN_DIM;
     const size_t mb = (size_t)g.max_batch;
-    ok = ok && dalloc(c, (uint8_t **)&c->k_cache, kv_bytes, true) && dalloc(c, (uint8_t **)&c->v_cache, kv_bytes, true) &&
-         dalloc(c, &c->ssm, (size_t)c->n_state_slots * ssm_elems, true) &&
-         dalloc(c, &c->conv, (size_t)c->n_state_slots * CONV_TAPS * c->conv_dim, true) &&
-         dalloc(c, &c->conv_w, (size_t)(c->n_lin + 1) * c->conv_dim * 4, true) &&
-         dalloc(c, &c->a_log, (size_t)(c->n_lin + 1) * g.linear_num_v_heads, true) &&
-         dalloc(c, &c->dt_bias, (size_t)(c->n_lin + 1) * g.linear_num_v_heads, true) &&
-         dalloc(c, &c->norm_w, (size_t)(c->n_lin + 1) * GDN_DIM, true) &&
-         dalloc(c, &c->inv_freq, (size_t)HEAD_DIM / 2, true) && dalloc(c, &c->d_gqa_items, mb, false) &&
-         dalloc(c, &c->d_gdn_items, mb, false) &&
-         dalloc(c, &c->sc_o, (size_t)c->max_parts * 16 * HEAD_DIM, false) &&
-         dalloc(c, &c->sc_m, (size_t)c->max_parts * 16, false) &&
-         dalloc(c, &c->sc_l, (size_t)c->max_parts * 16, false) &&
-         dalloc(c, &c->tickets, mb * g.num_kv_heads, true) && dalloc(c, &c->status, (size_t)1, true) &&
-         dalloc(c, &c->st_q, mb * qd, false) && dalloc(c, &c->st_gate, mb * qd, false) &&
-         dalloc(c, &c->st_k, mb * kvd, false) && dalloc(c, &c->st_v, mb * kvd, false) &&
-         dalloc(c, &c->st_out, mb * qd, false) && dalloc(c, &c->st_qkv, mb * c->conv_dim, false) &&
-         dalloc(c, &c->st_z, mb * vd, false) && dalloc(c, &c->st_alpha, mb * g.linear_num_v_heads, false) &&
-         dalloc(c, &c->st_beta, mb * g.linear_num_v_heads, false) && dalloc(c, &c->st_gout, mb * vd, false) &&
-         dalloc(c, &c->st_rows, (size_t)mfc_ctx::SNAP_ROWS * kvd, false) &&
-         dalloc(c, &c->pf_cos_sin, (size_t)g.max_seq * 64, false) &&
-         dalloc(c, &c->qnorm_w, (size_t)(c->n_full + 1) * HEAD_DIM, true) &&
-         dalloc(c, &c->knorm_w, (size_t)(c->n_full + 1) * HEAD_DIM, true) && dalloc(c, &c->st_qproj, mb * qd * 2, false) &&
-         dalloc(c, (uint16_t **)&c->pf_q, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
-         dalloc(c, (uint16_t **)&c->pf_k, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
-         dalloc(c, (uint16_t **)&c->pf_wt, (size_t)c->cfg.max_prefill * vd, false) &&
-         dalloc(c, (uint16_t **)&c->pf_wm, (size_t)c->cfg.max_prefill * g.linear_num_v_heads * 64, false) &&
-         dalloc(c, &c->pf_v, (size_t)c->cfg.max_prefill * vd, false) &&
-         dalloc(c, &c->pf_lg, (size_t)c->cfg.max_prefill * g.linear_num_v_heads, false) &&
-         dalloc(c, &c->pf_beta, (size_t)c->cfg.max_prefill * g.linear_num_v_heads, false);
+#define DA(field, count, zero) dalloc(c, &c->field, (size_t)(count), zero, #field)
+#define DAV(field, type, count, zero) dalloc(c, (type **)&c->field, (size_t)(count), zero, #field)
+    ok = ok && DAV(k_cache, uint8_t, kv_bytes, true) && DAV(v_cache, uint8_t, kv_bytes, true) &&
+         DA(ssm, (size_t)c->n_state_slots * ssm_elems, true) &&
+         DA(conv, (size_t)c->n_state_slots * CONV_TAPS * c->conv_dim, true) &&
+         DA(conv_w, (size_t)(c->n_lin + 1) * c->conv_dim * 4, true) &&
+         DA(a_log, (size_t)(c->n_lin + 1) * g.linear_num_v_heads, true) &&
+         DA(dt_bias, (size_t)(c->n_lin + 1) * g.linear_num_v_heads, true) &&
+         DA(norm_w, (size_t)(c->n_lin + 1) * GDN_DIM, true) && DA(inv_freq, HEAD_DIM / 2, true) &&
+         DA(d_gqa_items, mb, false) && DA(d_gdn_items, mb, false) &&
+         DA(sc_o, (size_t)c->max_parts * 16 * HEAD_DIM, false) && DA(sc_m, (size_t)c->max_parts * 16, false) &&
+         DA(sc_l, (size_t)c->max_parts * 16, false) && DA(tickets, mb * g.num_kv_heads, true) &&
+         DA(group_tickets, c->max_parts, true) && DA(status, 1, true) &&
+         DA(phase_trace, (size_t)mfc_ctx::MAX_TRACE_CTAS * PHASE_TRACE_WORDS, true) && DA(st_q, mb * qd, false) &&
+         DA(st_gate, mb * qd, false) && DA(st_k, mb * kvd, false) && DA(st_v, mb * kvd, false) &&
+         DA(st_out, mb * qd, false) && DA(st_qkv, mb * c->conv_dim, false) && DA(st_z, mb * vd, false) &&
+         DA(st_alpha, mb * g.linear_num_v_heads, false) && DA(st_beta, mb * g.linear_num_v_heads, false) &&
+         DA(st_gout, mb * vd, false) && DA(st_rows, (size_t)mfc_ctx::SNAP_ROWS * kvd, false) &&
+         DA(pf_cos_sin, (size_t)g.max_seq * 64, false) && DA(qnorm_w, (size_t)(c->n_full + 1) * HEAD_DIM, true) &&
+         DA(knorm_w, (size_t)(c->n_full + 1) * HEAD_DIM, true) && DA(st_qproj, mb * qd * 2, false) &&
+         DAV(pf_q, uint16_t, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
+         DAV(pf_k, uint16_t, (size_t)c->cfg.max_prefill * g.linear_num_k_heads * GDN_DIM, false) &&
+         DAV(pf_wt, uint16_t, (size_t)c->cfg.max_prefill * vd, false) &&
+         DAV(pf_wm, uint16_t, (size_t)c->cfg.max_prefill * g.linear_num_v_heads * 64, false) &&
+         DA(pf_v, (size_t)c->cfg.max_prefill * vd, false) &&
+         DA(pf_lg, (size_t)c->cfg.max_prefill * g.linear_num_v_heads, false) &&
+         DA(pf_beta, (size_t)c->cfg.max_prefill * g.linear_num_v_heads, false);
+    if (ok) {
+        c->pin_slot_bytes = (mb * (sizeof(GqaItem) > sizeof(GdnItem) ? sizeof(GqaItem) : sizeof(GdnItem)) + 255) & ~(size_t)255;
+        ok = cudaHostAlloc((void **)&c->pin_items, c->pin_slot_bytes * mfc_ctx::PIN_SLOTS, cudaHostAllocDefault) == cudaSuccess;
+        for (int i = 0; ok && i < mfc_ctx::PIN_SLOTS; i++)
+            ok = cudaEventCreateWithFlags(&c->pin_ev[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) fail(c, "cannot allocate the pinned staging slots of the item lists");
+    }
     if (ok) {
         // the host's libm evaluates the frequencies, exactly as the reference does
         // (crates/moeflux/src/riir/rope.rs:99-101); the device only multiplies by pos
@@ -745,10 +826,12 @@ int mfc_get_config(const mfc_ctx *c, mfc_config *out) {
 }
 
 void *mfc_stream(mfc_ctx *c) { return c ? (void *)c->stream : nullptr; }
+void *mfc_side_stream(mfc_ctx *c) { return c ? (void *)c->side_stream : nullptr; }
 
 int mfc_set_stream(mfc_ctx *c, void *stream) {
     if (!c) return -1;
     cudaSetDevice(c->cfg.device);
+    if (mfc_join(c)) return -1;
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) {
         fail(c, "the context's previous stream is in a failed state");
         return -1;
@@ -766,6 +849,216 @@ int mfc_synchronize(mfc_ctx *c) {
 }
 
 long long mfc_launch_count(const mfc_ctx *c) { return c ? c->launches : 0; }
+
+// ---------------------------------------------------------------- diagnostics
+
+int mfc_check_guards(mfc_ctx *c) {
+    if (!c) return -1;
+    cudaSetDevice(c->cfg.device);
+    if (mfc_join(c)) return -1;
+    CK(cudaStreamSynchronize(c->stream));
+    std::vector<uint8_t> band(2 * mfc_ctx::GUARD);
+    for (const mfc_ctx::Alloc &a : c->allocs) {
+        if (!a.banded) continue;
+        CK(cudaMemcpy(band.data(), a.base, mfc_ctx::GUARD, cudaMemcpyDeviceToHost));
+        CK(cudaMemcpy(band.data() + mfc_ctx::GUARD, a.base + mfc_ctx::GUARD + a.bytes, mfc_ctx::GUARD,
+                      cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < band.size(); i++)
+            if (band[i] != 0xFF) {
+                const bool before = i < mfc_ctx::GUARD;
+                fail(c, std::string("guard band ") + (before ? "before" : "after") + " '" + a.name +
+                            "' was written: byte " + std::to_string(before ? i : i - mfc_ctx::GUARD) + " of the band");
+                return -1;
+            }
+    }
+    return 0;
+}
+
+int mfc_read_phase_trace(mfc_ctx *c, unsigned long long *out, int32_t max_ctas) {
+    if (!c || !out || max_ctas <= 0) return -1;
+    cudaSetDevice(c->cfg.device);
+    CK(cudaStreamSynchronize(c->stream));
+    int n = c->last_launch_ctas < max_ctas ? c->last_launch_ctas : max_ctas;
+    if (n > mfc_ctx::MAX_TRACE_CTAS) n = mfc_ctx::MAX_TRACE_CTAS;
+    CK(cudaMemcpy(out, c->phase_trace, sizeof(unsigned long long) * PHASE_TRACE_WORDS * (size_t)n,
+                  cudaMemcpyDeviceToHost));
+    return n;
+}
+
+// ---------------------------------------------------------------- fused exchange of the KV-sequence split
+
+namespace {
+size_t xc_item_floats(const mfc_ctx *c) { return (size_t)c->cfg.num_attn_heads * (HEAD_DIM + 2); }
+
+int xc_finish_connect(mfc_ctx *c) {
+    const int W = c->cfg.kv_world;
+    std::vector<float *> recv(2 * (size_t)W);
+    std::vector<unsigned *> flags(W);
+    const size_t half = (size_t)W * c->xc.npr * xc_item_floats(c);  // floats of one receive buffer
+    for (int r = 0; r < W; r++) {
+        uint8_t *b = c->xc.peer_base[r];
+        recv[r] = reinterpret_cast<float *>(b);
+        recv[W + r] = reinterpret_cast<float *>(b) + half;
+        flags[r] = reinterpret_cast<unsigned *>(b + c->xc.recv_bytes);
+    }
+    CK(cudaMemcpy(c->xc.d_peer_recv, recv.data(), sizeof(float *) * recv.size(), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(c->xc.d_peer_flags, flags.data(), sizeof(unsigned *) * flags.size(), cudaMemcpyHostToDevice));
+    c->xc.connected = true;
+    return 0;
+}
+}  // namespace
+
+int mfc_exchange_create(mfc_ctx *c, int32_t items_per_rank, void *ipc_handle_out) {
+    if (!c) return -1;
+    const mfc_config &g = c->cfg;
+    if (g.kv_world < 2 || g.kv_world > 128) {
+        fail(c, "the exchange needs a context of a KV split (2 <= kv_world <= 128)");
+        return -1;
+    }
+    if (items_per_rank <= 0 || (long long)items_per_rank * g.kv_world > g.max_batch) {
+        fail(c, "items_per_rank * kv_world must be in [kv_world, max_batch]");
+        return -1;
+    }
+    if (c->xc.base) {
+        fail(c, "the exchange was already created");
+        return -1;
+    }
+    cudaSetDevice(g.device);
+    c->xc.npr = items_per_rank;
+    c->xc.recv_bytes = (2 * (size_t)g.kv_world * items_per_rank * xc_item_floats(c) * sizeof(float) + 255) & ~(size_t)255;
+    c->xc.bytes = c->xc.recv_bytes + 256;
+    // its own cudaMalloc (no guard bands): an IPC handle names a whole allocation, from its base
+    CK(cudaMalloc((void **)&c->xc.base, c->xc.bytes));
+    c->allocs.push_back({c->xc.base, c->xc.bytes, "exchange", false});  // freed with the rest; not band-checked
+    CK(cudaMemset(c->xc.base, 0, c->xc.bytes));
+    c->xc.recv = reinterpret_cast<float *>(c->xc.base);
+    c->xc.flags = reinterpret_cast<unsigned *>(c->xc.base + c->xc.recv_bytes);
+    if (!dalloc(c, &c->xc.d_peer_recv, 2 * (size_t)g.kv_world, true, "xc.d_peer_recv") ||
+        !dalloc(c, &c->xc.d_peer_flags, (size_t)g.kv_world, true, "xc.d_peer_flags") ||
+        !dalloc(c, &c->xc.done_counter, 1, true, "xc.done_counter"))
+        return -1;
+    c->xc.peer_base.assign(g.kv_world, nullptr);
+    c->xc.peer_is_ipc.assign(g.kv_world, false);
+    c->xc.peer_base[g.kv_rank] = c->xc.base;
+    if (ipc_handle_out) {
+        cudaIpcMemHandle_t h;
+        CK(cudaIpcGetMemHandle(&h, c->xc.base));
+        static_assert(sizeof(h) == MFC_IPC_HANDLE_BYTES, "handle size");
+        memcpy(ipc_handle_out, &h, sizeof(h));
+    }
+    return 0;
+}
+
+int mfc_exchange_connect(mfc_ctx *c, const void *ipc_handles) {
+    if (!c) return -1;
+    if (!c->xc.base || !ipc_handles) {
+        fail(c, "mfc_exchange_create first; handles must not be NULL");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    for (int r = 0; r < c->cfg.kv_world; r++) {
+        if (r == c->cfg.kv_rank || c->xc.peer_base[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)ipc_handles + (size_t)r * sizeof(h), sizeof(h));
+        void *ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            fail(c, "cudaIpcOpenMemHandle(rank " + std::to_string(r) + "): " + cudaGetErrorString(e));
+            cudaGetLastError();
+            return -1;
+        }
+        c->xc.peer_base[r] = (uint8_t *)ptr;
+        c->xc.peer_is_ipc[r] = true;
+    }
+    return xc_finish_connect(c);
+}
+
+int mfc_exchange_connect_local(mfc_ctx *c, mfc_ctx *const *peers) {
+    if (!c) return -1;
+    if (!c->xc.base || !peers) {
+        fail(c, "mfc_exchange_create first; peers must not be NULL");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    for (int r = 0; r < c->cfg.kv_world; r++) {
+        if (r == c->cfg.kv_rank) continue;
+        const mfc_ctx *o = peers[r];
+        if (!o || !o->xc.base || o->cfg.kv_world != c->cfg.kv_world || o->cfg.kv_rank != r || o->xc.npr != c->xc.npr) {
+            fail(c, "peer " + std::to_string(r) + " is not the matching context of this split with its exchange created");
+            return -1;
+        }
+        if (o->cfg.device != c->cfg.device) {
+            cudaError_t e = cudaDeviceEnablePeerAccess(o->cfg.device, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+                fail(c, std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(e));
+                cudaGetLastError();
+                return -1;
+            }
+            cudaGetLastError();
+        }
+        c->xc.peer_base[r] = o->xc.base;
+    }
+    return xc_finish_connect(c);
+}
+
+int mfc_full_attn_partial_exchange_dev(mfc_ctx *c, int32_t n, const int32_t *layers, const int32_t *seq_ids,
+                                       const int32_t *pos, const float *q, const float *k, const float *v) {
+    if (!c) return -1;
+    if (!q || !k || !v) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (!c->xc.connected) {
+        fail(c, "the exchange is not connected (mfc_exchange_create, mfc_exchange_connect)");
+        return -1;
+    }
+    if (n != c->xc.npr * c->cfg.kv_world) {
+        fail(c, "n must be items_per_rank * kv_world, items sorted by the rank that finishes them");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    int total = 0;
+    if (build_gqa_items(c, n, layers, seq_ids, pos, &total)) return -1;
+    GqaParams p;
+    fill_gqa_params(c, p, n, total);
+    c->xc.step += 1;
+    p.q = q;
+    p.gate = nullptr;
+    p.k = k;
+    p.v = v;
+    p.partial_mode = 1;
+    p.po_item_stride = xc_item_floats(c);
+    p.pml_item_stride = xc_item_floats(c);
+    p.peer_recv = c->xc.d_peer_recv + (size_t)(c->xc.step & 1u) * c->cfg.kv_world;
+    p.peer_flags = c->xc.d_peer_flags;
+    p.done_counter = c->xc.done_counter;
+    p.items_per_dest = c->xc.npr;
+    p.my_rank = c->cfg.kv_rank;
+    p.world = c->cfg.kv_world;
+    p.flag_value = c->xc.step;
+    return launch_gqa(c, p);
+}
+
+int mfc_lse_merge_gate_exchange_dev(mfc_ctx *c, const float *gate, float *out) {
+    if (!c) return -1;
+    if (!out) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (!c->xc.connected || c->xc.step == 0) {
+        fail(c, "no exchanged step to merge");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    const size_t hd = (size_t)c->cfg.num_attn_heads * HEAD_DIM, hh = (size_t)c->cfg.num_attn_heads;
+    const size_t item = xc_item_floats(c);
+    const float *buf = c->xc.recv + (size_t)(c->xc.step & 1u) * c->cfg.kv_world * c->xc.npr * item;
+    CK(launch_lse_merge_gate(c->cfg.kv_world, c->xc.npr, c->cfg.num_attn_heads, buf, buf + hd, buf + hd + hh,
+                             (size_t)c->xc.npr * item, gate, out, c->stream, item, item, c->xc.flags, c->xc.step,
+                             c->gqa_wait_spins, c->status));
+    c->launches += 1;
+    return 0;
+}
 
 // ---------------------------------------------------------------- projections: 4-bit dequant matvec
 
@@ -893,6 +1186,13 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
     } else if (!strcmp(key, "gqa_chunk")) {
         if (value < 0) return -1;
         c->gqa_forced_chunk = value;
+    } else if (!strcmp(key, "gqa_wait_spins")) {
+        if (value < 0) return -1;
+        c->gqa_wait_spins = (unsigned)value;
+    } else if (!strcmp(key, "gqa_inject_lost_load")) {
+        c->gqa_inject_lost_load = value != 0;
+    } else if (!strcmp(key, "gqa_phase_trace")) {
+        c->phase_trace_on = value != 0;
     } else {
         return -1;
     }
@@ -1244,8 +1544,10 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
         fail(c, "NULL argument");
         return -1;
     }
-    if (g.kv_world != 1) {
-        fail(c, "this context holds a share of a KV split: use the partial entry points");
+    const bool split = g.kv_world != 1;
+    if (split && n_full && (!c->xc.connected || n_full != c->xc.npr * g.kv_world)) {
+        fail(c, "this context holds a share of a KV split: connect the exchange (mfc_exchange_create / _connect) and "
+                "pass items_per_rank * kv_world full-attention items sorted by the rank that finishes them");
         return -1;
     }
     cudaSetDevice(g.device);
@@ -1272,13 +1574,15 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
     if (n_full) {
         const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)n_full;
         const size_t kd = sizeof(float) * g.num_kv_heads * HEAD_DIM * (size_t)n_full;
+        // with a KV split, gate and full_out cover the items this rank finishes only
+        const size_t own_qd = split ? sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)c->xc.npr : qd;
         // q, k, v first; the gate logits (as many bytes as q) are only needed after the attention kernel, so they
-        // travel on the side queue under it and are applied by a separate elementwise pass
+        // travel on the side queue under it and are applied by a separate elementwise pass (or by the merge)
         CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, main_stream));
         CK(cudaMemcpyAsync(c->st_k, k, kd, cudaMemcpyHostToDevice, main_stream));
         CK(cudaMemcpyAsync(c->st_v, v, kd, cudaMemcpyHostToDevice, main_stream));
         CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
-        CK(cudaMemcpyAsync(c->st_gate, gate, qd, cudaMemcpyHostToDevice, c->side_stream));
+        CK(cudaMemcpyAsync(c->st_gate, gate, own_qd, cudaMemcpyHostToDevice, c->side_stream));
         CK(cudaEventRecord(c->ev_gate, c->side_stream));
         GqaParams p;
         fill_gqa_params(c, p, n_full, total);
@@ -1288,11 +1592,28 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
         p.v = c->st_v;
         p.out = c->st_out;
         p.partial_mode = 0;
+        if (split) {
+            // partials straight into the owners' receive buffers; the merge below waits for the peers' flags
+            c->xc.step += 1;
+            p.partial_mode = 1;
+            p.po_item_stride = p.pml_item_stride = (size_t)g.num_attn_heads * (HEAD_DIM + 2);
+            p.peer_recv = c->xc.d_peer_recv + (size_t)(c->xc.step & 1u) * g.kv_world;
+            p.peer_flags = c->xc.d_peer_flags;
+            p.done_counter = c->xc.done_counter;
+            p.items_per_dest = c->xc.npr;
+            p.my_rank = g.kv_rank;
+            p.world = g.kv_world;
+            p.flag_value = c->xc.step;
+        }
         if (launch_gqa(c, p)) return -1;
         CK(cudaStreamWaitEvent(main_stream, c->ev_gate, 0));
-        CK(launch_sigmoid_gate(c->st_out, c->st_gate, qd / sizeof(float), main_stream));
-        c->launches += 1;
-        CK(cudaMemcpyAsync(full_out, c->st_out, qd, cudaMemcpyDeviceToHost, main_stream));
+        if (split) {
+            if (mfc_lse_merge_gate_exchange_dev(c, c->st_gate, c->st_out)) return -1;
+        } else {
+            CK(launch_sigmoid_gate(c->st_out, c->st_gate, qd / sizeof(float), main_stream));
+            c->launches += 1;
+        }
+        CK(cudaMemcpyAsync(full_out, c->st_out, own_qd, cudaMemcpyDeviceToHost, main_stream));
     }
     if (n_lin) {
         // GatedDeltaNet group on the side queue: its copies and kernel overlap the attention kernel
@@ -1419,6 +1740,7 @@ int mfc_linear_attn_prefill_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, int32
         return -1;
     }
     cudaSetDevice(g.device);
+    if (mfc_join(c)) return -1;  // a GatedDeltaNet launch may still be running on the side queue
     const int slot = ll * g.n_seqs + seq_id;
     GdnPrefillParams p;
     memset(&p, 0, sizeof(p));
@@ -1509,6 +1831,7 @@ int mfc_linear_state_set_dev(mfc_ctx *c, int32_t layer, int32_t seq_id, const fl
         return -1;
     }
     cudaSetDevice(g.device);
+    if (mfc_join(c)) return -1;  // a GatedDeltaNet launch may still be running on the side queue
     const int slot = c->layer_to_lin[layer] * g.n_seqs + seq_id;
     const size_t ssm_elems = (size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM;
     float *ring = c->conv + (size_t)slot * CONV_TAPS * c->conv_dim;
@@ -1539,6 +1862,7 @@ int mfc_memory_seq_rm(mfc_ctx *c, int32_t seq_id, int32_t p0, int32_t p1) {
     const mfc_config &g = c->cfg;
     if (seq_id < -1 || seq_id >= g.n_seqs) return 0;
     cudaSetDevice(g.device);
+    if (mfc_join(c)) return 0;  // a GatedDeltaNet launch may still be running on the side queue
     const int s0 = seq_id < 0 ? 0 : seq_id, s1 = seq_id < 0 ? g.n_seqs : seq_id + 1;
     const int new_len = p0 < 0 ? 0 : p0;
     for (int s = s0; s < s1; s++) {
@@ -1598,6 +1922,7 @@ long long mfc_state_save(mfc_ctx *c, int32_t seq_id, void *buf, size_t buf_len) 
         return -1;
     }
     cudaSetDevice(g.device);
+    if (mfc_join(c)) return -1;  // a GatedDeltaNet launch may still be running on the side queue
     uint8_t *out = (uint8_t *)buf;
     size_t off = 0;
     const uint32_t la_conv = (uint32_t)((CONV_TAPS - 1) * c->conv_dim * sizeof(float));
@@ -1669,6 +1994,7 @@ int mfc_state_load(mfc_ctx *c, int32_t seq_id, const void *buf, size_t buf_len) 
     const uint32_t la_ssm = (uint32_t)((size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM * sizeof(float));
     // restore
     cudaSetDevice(g.device);
+    if (mfc_join(c)) return -1;  // a GatedDeltaNet launch may still be running on the side queue
     size_t off = hbytes;
     const size_t kvd = (size_t)g.num_kv_heads * HEAD_DIM;
     for (int i = 0; i < g.num_layers; i++) {
@@ -1893,6 +2219,7 @@ int mfc_linear_attn_step_stateless(mfc_ctx *c, int32_t layer, const float *qkv, 
         return -1;
     }
     cudaSetDevice(g.device);
+    if (mfc_join(c)) return -1;  // a GatedDeltaNet launch may still be running on the side queue
     const int slot = c->n_state_slots - 1;  // hook slot
     const size_t ssm_elems = (size_t)g.linear_num_v_heads * GDN_DIM * GDN_DIM;
     float *ring = c->conv + (size_t)slot * CONV_TAPS * c->conv_dim;

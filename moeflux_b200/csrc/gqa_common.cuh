@@ -84,6 +84,7 @@ struct Located {
     int n_parts;   // CTAs that share the unit (1: this CTA finishes it alone)
     int part_idx;  // this CTA's rank among them
     int slot0;     // scratch slot of the unit's first partial
+    bool bad;      // the item failed its range checks: the unit is skipped (its tickets are still taken)
 };
 
 constexpr int LOCATE_SMEM_ITEMS = 512;
@@ -120,21 +121,60 @@ __device__ __forceinline__ Located locate_tile(const GqaParams &p, int gt, int g
     L.part_idx = (int)blockIdx.x - first_cta;
     // (unit index + CTA index) grows strictly along the tile sequence: a unique slot per pair
     L.slot0 = lo * p.Hkv + L.kvh + first_cta;
+    // what the kernel indexes memory with must lie inside the caches and the input arrays
+    L.bad = L.it.kv_slot < 0 || L.it.kv_slot >= p.n_kv_slots || L.it.local_len < 0 || L.it.local_len > p.cap_rows ||
+            L.it.append_row >= L.it.local_len || L.it.in_idx < 0 || L.it.in_idx >= p.n_items ||
+            L.n_parts > MAX_UNIT_PARTS;
     return L;
 }
 
-// out = merge of n_src partials (slot stride given) for one (item, kv head):
-// final gated output or merged partial.  Executed by 128 threads.
-__device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L, const float *src_o,
-                           const float *src_m, const float *src_l, int n_src, float *s_w,
-                           float *s_M, float *s_L, float *s_tmp) {
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Optional per-CTA phase trace (thread 0 only): word w of this CTA's record.
+__device__ __forceinline__ void trace_phase(const GqaParams &p, int w) {
+    if (p.phase_trace && threadIdx.x == 0 && w < PHASE_TRACE_WORDS)
+        p.phase_trace[(size_t)blockIdx.x * PHASE_TRACE_WORDS + w] = global_timer_ns();
+}
+
+// Where a merged un-normalised partial of an item goes in partial mode: the caller's buffers, or (fused exchange of
+// the KV-sequence split) the receive buffer of the rank that finishes the item, through its peer-mapped pointer.
+struct PartialDst {
+    float *o, *m, *l;  // o: [H][256], m / l: [H]
+};
+__device__ __forceinline__ PartialDst partial_dst(const GqaParams &p, int in_idx) {
+    PartialDst d;
+    if (p.peer_recv) {
+        const int dest = in_idx / p.items_per_dest, j = in_idx - dest * p.items_per_dest;
+        float *blk = p.peer_recv[dest] + ((size_t)p.my_rank * p.items_per_dest + j) * p.po_item_stride;
+        d.o = blk;
+        d.m = blk + (size_t)p.H * HEAD_DIM;
+        d.l = d.m + p.H;
+    } else {
+        d.o = p.po + (size_t)in_idx * p.po_item_stride;
+        d.m = p.pm + (size_t)in_idx * p.pml_item_stride;
+        d.l = p.pl + (size_t)in_idx * p.pml_item_stride;
+    }
+    return d;
+}
+
+// Merge of n_src partials of one (item, kv head) unit by log-sum-exp; partial c sits in scratch slot
+// src_slot0 + c * slot_stride.  to_slot >= 0: first level of a two-level merge, the un-normalised result (o, M, L)
+// goes to that scratch slot (it may be one of the sources: every thread reads its elements of all sources before it
+// writes them).  to_slot < 0: the unit is finished here, as the gated output or, in partial mode, as the
+// un-normalised partial of the item.  Executed by 128 threads; s_w: n_src * 16 floats, s_tmp: n_src * 16 floats.
+__device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L, size_t src_slot0, int slot_stride,
+                                           int n_src, long long to_slot, float *s_w, float *s_M, float *s_L,
+                                           float *s_tmp) {
     const int tid = threadIdx.x;
     const int group = p.group;
-    // m and l of every partial come in with all loads in flight (s_tmp: n_src * 16 floats of scratch); the
-    // reductions then run out of shared memory in the order they always had
+    // m and l of every partial come in with all loads in flight; the reductions then run out of shared memory
     for (int idx = tid; idx < n_src * 16; idx += 128) {
-        s_w[idx] = src_m[idx];
-        s_tmp[idx] = src_l[idx];
+        const size_t so = (src_slot0 + (size_t)(idx >> 4) * slot_stride) * 16 + (idx & 15);
+        s_w[idx] = p.sc_m[so];
+        s_tmp[idx] = p.sc_l[so];
     }
     __syncthreads();
     if (tid < 16) {
@@ -155,29 +195,32 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
     }
     __syncthreads();
     const size_t head0 = (size_t)L.it.in_idx * p.H + (size_t)L.kvh * group;
-    // Four heads x four partials per round, every load of a round in flight together: the merging CTA is the last of
-    // its unit to finish, usually at the very end of the launch, so this latency is on the launch's critical path
-    // (and with one long sequence per launch a unit has up to MAX_SPLITS partials).
+    const bool final_out = to_slot < 0 && !p.partial_mode;
+    PartialDst pd;
+    if (to_slot < 0 && p.partial_mode) pd = partial_dst(p, L.it.in_idx);
+    // Four heads x eight partials per round, every load of a round in flight together: the merging CTA is the last of
+    // its group to finish, often at the very end of the launch, so this latency is on the launch's critical path.
     for (int hr0 = 0; hr0 < group; hr0 += 4) {
         float2 acc[4], gt[4];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             acc[u] = make_float2(0.0f, 0.0f);
             gt[u] = make_float2(0.0f, 0.0f);
-            if (!p.partial_mode && p.gate && hr0 + u < group)
+            if (final_out && p.gate && hr0 + u < group)
                 gt[u] = *reinterpret_cast<const float2 *>(p.gate + (head0 + hr0 + u) * (size_t)p.gate_row_stride + 2 * tid);
         }
-        for (int c0 = 0; c0 < n_src; c0 += 4) {
-            float2 o[4][4];
+        for (int c0 = 0; c0 < n_src; c0 += MERGE_GROUP) {
+            float2 o[MERGE_GROUP][4];
 #pragma unroll
-            for (int k = 0; k < 4; k++)
+            for (int k = 0; k < MERGE_GROUP; k++)
 #pragma unroll
                 for (int u = 0; u < 4; u++)
                     o[k][u] = (c0 + k < n_src && hr0 + u < group)
-                                  ? *reinterpret_cast<const float2 *>(src_o + ((size_t)(c0 + k) * 16 + hr0 + u) * HEAD_DIM + 2 * tid)
+                                  ? *reinterpret_cast<const float2 *>(
+                                        p.sc_o + ((src_slot0 + (size_t)(c0 + k) * slot_stride) * 16 + hr0 + u) * HEAD_DIM + 2 * tid)
                                   : make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int k = 0; k < 4; k++) {  // partials are added in index order, as before
+            for (int k = 0; k < MERGE_GROUP; k++) {  // partials are added in index order
                 if (c0 + k >= n_src) break;
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
@@ -191,15 +234,17 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
         for (int u = 0; u < 4; u++) {
             const int hr = hr0 + u;
             if (hr >= group) break;
-            const size_t off = (head0 + hr) * HEAD_DIM + 2 * tid;
-            if (p.partial_mode) {
+            if (to_slot >= 0) {
+                *reinterpret_cast<float2 *>(p.sc_o + ((size_t)to_slot * 16 + hr) * HEAD_DIM + 2 * tid) = acc[u];
+            } else if (p.partial_mode) {
                 const int hl = L.kvh * group + hr;  // head within the item
-                *reinterpret_cast<float2 *>(p.po + (size_t)L.it.in_idx * p.po_item_stride + (size_t)hl * HEAD_DIM + 2 * tid) = acc[u];
+                *reinterpret_cast<float2 *>(pd.o + (size_t)hl * HEAD_DIM + 2 * tid) = acc[u];
                 if (tid == 0) {
-                    p.pm[(size_t)L.it.in_idx * p.pml_item_stride + hl] = s_M[hr];
-                    p.pl[(size_t)L.it.in_idx * p.pml_item_stride + hl] = s_L[hr];
+                    pd.m[hl] = s_M[hr];
+                    pd.l[hl] = s_L[hr];
                 }
             } else {
+                const size_t off = (head0 + hr) * HEAD_DIM + 2 * tid;
                 const float inv = 1.0f / s_L[hr];
                 float2 r = make_float2(acc[u].x * inv, acc[u].y * inv);
                 if (p.gate) {
@@ -210,6 +255,10 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
             }
         }
     }
+    if (to_slot >= 0 && tid < 16) {  // every thread is past its reads of the sources' m and l (staged above)
+        p.sc_m[(size_t)to_slot * 16 + tid] = s_M[tid];
+        p.sc_l[(size_t)to_slot * 16 + tid] = s_L[tid];
+    }
 }
 
 // Epilogue shared by both kernels.  The warp layout of the accumulators is:
@@ -217,7 +266,7 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
 // (l_r still split over the four lanes of a row).
 __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L, float (&o)[8][4],
                                             float (&m_r)[2], float (&l_r)[2], float *s_w,
-                                            float *s_M, float *s_L, int *s_flag_p, float *s_tmp) {
+                                            float *s_M, float *s_L, int *s_flag_p, float *s_tmp, bool abandoned) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const GqaItem &it = L.it;
@@ -230,7 +279,10 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
 
     const size_t head0 = (size_t)it.in_idx * p.H + (size_t)L.kvh * group;
     if (L.n_parts == 1) {
+        if (abandoned) return;
         // the unit was not split: finish in place
+        PartialDst pd;
+        if (p.partial_mode) pd = partial_dst(p, it.in_idx);
 #pragma unroll
         for (int x = 0; x < 2; x++) {
             const int row = g + 8 * x;
@@ -238,8 +290,8 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
             const float m_nat = m_r[x] * p.scale;
             if (p.partial_mode) {
                 if (warp == 0 && t == 0) {
-                    p.pm[(size_t)it.in_idx * p.pml_item_stride + L.kvh * group + row] = m_nat;
-                    p.pl[(size_t)it.in_idx * p.pml_item_stride + L.kvh * group + row] = l_r[x];
+                    pd.m[L.kvh * group + row] = m_nat;
+                    pd.l[L.kvh * group + row] = l_r[x];
                 }
             }
             const float inv = p.partial_mode ? 1.0f : 1.0f / l_r[x];
@@ -248,8 +300,7 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
                 const size_t off = (head0 + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t;
                 float2 rv = make_float2(o[nt][2 * x] * inv, o[nt][2 * x + 1] * inv);
                 if (p.partial_mode) {
-                    *reinterpret_cast<float2 *>(p.po + (size_t)it.in_idx * p.po_item_stride +
-                                                (size_t)(L.kvh * group + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t) = rv;
+                    *reinterpret_cast<float2 *>(pd.o + (size_t)(L.kvh * group + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t) = rv;
                 } else {
                     if (p.gate) {
                         const float2 gt = *reinterpret_cast<const float2 *>(
@@ -264,35 +315,81 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
         return;
     }
 
-    // the unit is shared: park the partial, the last CTA of the unit to finish merges
+    // The unit is shared: park the partial; the last CTA to arrive merges.  Up to MERGE_GROUP partials are merged in
+    // one level.  Beyond that the partials form groups of MERGE_GROUP consecutive ones: the last arriver of a group
+    // merges it into the group's first slot (many groups merge side by side on different SMs), then arrives at the
+    // unit's ticket, and the last group to arrive merges the group results.  Nothing ever spins: a CTA that is not
+    // last simply leaves.  A CTA that gave up on its loads still takes its tickets, so that the counters return to
+    // zero for the next launch; what it would have merged is not merged (the status word says so to the host).
     const size_t slot0 = (size_t)L.slot0;  // first slot of the unit
     const size_t slot = slot0 + L.part_idx;
+    if (!abandoned) {
 #pragma unroll
-    for (int x = 0; x < 2; x++) {
-        const int row = g + 8 * x;
-        if (warp == 0 && t == 0) {
-            p.sc_m[slot * 16 + row] = m_r[x] * p.scale;
-            p.sc_l[slot * 16 + row] = l_r[x];
-        }
+        for (int x = 0; x < 2; x++) {
+            const int row = g + 8 * x;
+            if (warp == 0 && t == 0) {
+                p.sc_m[slot * 16 + row] = m_r[x] * p.scale;
+                p.sc_l[slot * 16 + row] = l_r[x];
+            }
 #pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-            *reinterpret_cast<float2 *>(p.sc_o + (slot * 16 + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t) =
-                make_float2(o[nt][2 * x], o[nt][2 * x + 1]);
+            for (int nt = 0; nt < 8; nt++) {
+                *reinterpret_cast<float2 *>(p.sc_o + (slot * 16 + row) * HEAD_DIM + 64 * warp + 8 * nt + 2 * t) =
+                    make_float2(o[nt][2 * x], o[nt][2 * x + 1]);
+            }
         }
     }
+    const bool two_level = L.n_parts > MERGE_GROUP;
+    const int gi = L.part_idx / MERGE_GROUP;
+    const int n_groups = (L.n_parts + MERGE_GROUP - 1) / MERGE_GROUP;
+    unsigned *unit_ticket = p.tickets + (size_t)L.item_idx * p.Hkv + L.kvh;
     __threadfence();
     __syncthreads();
+    if (two_level) {
+        const int gsize = min(MERGE_GROUP, L.n_parts - gi * MERGE_GROUP);
+        const size_t gslot = slot0 + (size_t)gi * MERGE_GROUP;
+        if (tid == 0) {
+            unsigned *tk = p.group_tickets + gslot;
+            const unsigned prev = atomicAdd(tk, 1u);
+            *s_flag_p = (prev == (unsigned)(gsize - 1));
+            if (*s_flag_p) *tk = 0u;  // ready for the next launch
+        }
+        __syncthreads();
+        if (!*s_flag_p) return;
+        __threadfence();
+        if (!abandoned) merge_unit(p, L, gslot, 1, gsize, (long long)gslot, s_w, s_M, s_L, s_tmp);
+        __threadfence();
+        __syncthreads();
+    }
     if (tid == 0) {
-        unsigned *tk = p.tickets + (size_t)L.item_idx * p.Hkv + L.kvh;
-        const unsigned prev = atomicAdd(tk, 1u);
-        *s_flag_p = (prev == (unsigned)(L.n_parts - 1));
-        if (*s_flag_p) *tk = 0u;  // ready for the next launch
+        const unsigned prev = atomicAdd(unit_ticket, 1u);
+        *s_flag_p = (prev == (unsigned)((two_level ? n_groups : L.n_parts) - 1));
+        if (*s_flag_p) *unit_ticket = 0u;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!*s_flag_p || abandoned) return;
+    __threadfence();
+    if (two_level) merge_unit(p, L, slot0, MERGE_GROUP, n_groups, -1, s_w, s_M, s_L, s_tmp);
+    else merge_unit(p, L, slot0, 1, L.n_parts, -1, s_w, s_M, s_L, s_tmp);
+}
+
+// End of a CTA's work in a launch with the fused exchange: once every CTA has made its stores to the peers'
+// receive buffers visible system-wide, the last one publishes this rank's flag in every peer's flag array.
+__device__ __forceinline__ void publish_exchange_flags(const GqaParams &p, int *s_flag_p) {
+    if (!p.peer_flags) return;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(p.done_counter, 1u);
+        *s_flag_p = (prev == gridDim.x - 1);
+        if (*s_flag_p) *p.done_counter = 0u;
     }
     __syncthreads();
     if (!*s_flag_p) return;
-    __threadfence();
-    merge_unit(p, L, p.sc_o + slot0 * 16 * HEAD_DIM, p.sc_m + slot0 * 16, p.sc_l + slot0 * 16,
-               L.n_parts, s_w, s_M, s_L, s_tmp);
+    __threadfence_system();
+    if ((int)threadIdx.x < p.world) {
+        unsigned *dst = p.peer_flags[threadIdx.x] + p.my_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(p.flag_value) : "memory");
+    }
 }
 
 }  // namespace mfc

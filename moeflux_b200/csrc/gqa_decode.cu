@@ -9,19 +9,24 @@
 // sigmoid_gate :1125-1134), or with sdpa_cpu (sdpa.rs:63-172) outside
 // 32 <= kv_len < 8192.
 //
-// Work split.  A CTA (4 warps) owns one (item, kv head, KV chunk).  The up-to-16
-// query heads that share the kv head are the M=16 rows of mma.sync m16n8k16, so
-// a cached row is read from HBM once for all of them.  K/V tiles of 32 rows
+// Work split ("stream-K" over KV tiles).  The 32-row tiles of all (item, kv head)
+// units of a launch form one sequence, cut into equal runs, one CTA (4 warps) per
+// run, across unit boundaries; a CTA walks its run one unit segment at a time.
+// The up-to-16 query heads that share the kv head are the M=16 rows of mma.sync
+// m16n8k16, so a cached row is read from HBM once for all of them.  K/V tiles
 // arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle, four 64-column boxes
 // per tensor) into a multi-stage shared-memory ring guarded by mbarriers with
 // bounded waits.  Per tile: warp w computes the scores of rows 8w..8w+7 over
 // all 256 dims (Q fragments live in registers), the four 16x8 score blocks are
 // exchanged through shared memory, every warp runs the same online softmax
 // (warp-shuffle row max) and then accumulates P·V for its own 64 output dims.
-// Chunks write un-normalised (o, m, l) partials; the last CTA of a unit to
-// finish (atomic ticket, no spinning) merges them by log-sum-exp, applies the
-// sigmoid gate and writes the output.  With partial_mode the merged
-// un-normalised partial is written instead, for the cross-GPU KV split.
+// A unit that lies inside one run is finished in place; a unit cut by run
+// boundaries is merged from the un-normalised (o, m, l) partials of the CTAs
+// that share it by the last of them to finish (atomic tickets, no spinning, two
+// levels when more than eight CTAs share it), which applies the sigmoid gate
+// and writes the output.  With partial_mode the merged un-normalised partial is
+// written instead, for the cross-GPU KV split -- to local memory, or straight
+// into the receive buffer of the GPU that finishes the item (peer stores).
 //
 // RoPE and the append are fused: every CTA rotates q while building its
 // fragments; the CTA whose chunk holds the new row rotates k, stores k and v
@@ -73,10 +78,26 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
     int gt = (int)blockIdx.x * p.tiles_per_cta;
     const int gt_end = min(gt + p.tiles_per_cta, p.total_tiles);
     unsigned pc = 0;  // tiles pushed through the stage ring so far: stage and phase follow from it
+    const unsigned spins = p.wait_spins ? p.wait_spins : (1u << 22);
+    bool abandoned = false;  // a bounded wait ran out, or an item failed its checks: no further loads, tickets only
+    int seg_no = 0;
+    trace_phase(p, 0);
     while (gt < gt_end) {
     const Located L = locate_tile<KV_TILE>(p, gt, gt_end, s_begin);
     const GqaItem &it = L.it;
     const int group = p.group;
+    if (L.bad && !abandoned) {
+        if (tid == 0) atomicOr(p.status, STATUS_BAD_ITEM);
+        abandoned = true;
+    }
+    if (abandoned) {  // take the unit's tickets so that the counters return to zero, touch nothing else
+        float o0[8][4] = {};
+        float m0[2] = {-INFINITY, -INFINITY}, l0[2] = {0.0f, 0.0f};
+        finish_unit(p, L, o0, m0, l0, s_w, s_M, s_L, &s_flag, reinterpret_cast<float *>(stages), true);
+        gt += L.seg;
+        __syncthreads();
+        continue;
+    }
 
     const int c0 = L.t0 * KV_TILE;
     const int c1 = min(c0 + L.seg * KV_TILE, it.local_len);
@@ -84,11 +105,13 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
     const int row_base = (it.kv_slot * p.Hkv + L.kvh) * p.cap_rows;
     const bool appender = it.append_row >= c0 && it.append_row < c0 + L.seg * KV_TILE;
 
+    const bool lose_load = p.inject_lost_load && blockIdx.x == 0 && seg_no == 0;
     auto issue_tile = [&](int tile) {
         const int st = (int)((pc + (unsigned)tile) % BF16_STAGES);
         uint8_t *kdst = stages + (size_t)st * 2 * TILE_BYTES_BF16;
         uint8_t *vdst = kdst + TILE_BYTES_BF16;
         mbar_expect_tx(&full[st], 2 * TILE_BYTES_BF16);
+        if (lose_load && tile == 0) return;  // diagnostic: the barrier is armed and nothing will ever arrive
         const int y = row_base + c0 + tile * KV_TILE;
 #pragma unroll
         for (int b = 0; b < 4; b++) {
@@ -170,6 +193,7 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
     fence_proxy_async();  // the Q staging area goes back to the ring
     __syncthreads();
     if (tid == 0 && ntiles >= BF16_STAGES) issue_tile(BF16_STAGES - 1);
+    if (seg_no == 0) trace_phase(p, 1);
 
     float o[8][4];
 #pragma unroll
@@ -177,12 +201,12 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
     float m_r[2] = {-INFINITY, -INFINITY};
     float l_r[2] = {0.0f, 0.0f};
     const float sl2 = p.scale * LOG2E;
-    bool failed = false;
+    int failed_at = -1;
 
     for (int i = 0; i < ntiles; i++) {
         const int st = (int)((pc + (unsigned)i) % BF16_STAGES);
         const unsigned par = ((pc + (unsigned)i) / BF16_STAGES) & 1u;
-        const bool ok = mbar_wait_bounded(&full[st], par);
+        const bool ok = mbar_wait_bounded(&full[st], par, spins);
         const uint32_t kst = smem_u32(stages + (size_t)st * 2 * TILE_BYTES_BF16);
         const uint32_t vst = kst + TILE_BYTES_BF16;
 
@@ -207,7 +231,7 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
         *reinterpret_cast<float2 *>(sx + (g + 8) * SX_STRIDE + 8 * warp + 2 * t) =
             make_float2(sacc[2], sacc[3]);
         if (!__syncthreads_and(ok ? 1 : 0)) {
-            failed = true;
+            failed_at = i;
             break;
         }
         // every warp is past its reads of tile i-1: refill that stage
@@ -261,6 +285,16 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
             o[nt][2] *= corr[1];
             o[nt][3] *= corr[1];
         }
+        if (tile_row0 + KV_TILE > c1) {
+            // Rows of the tile past the end of the sequence carry weight zero, but 0 * NaN is NaN: whatever the
+            // cache holds there (a caller's uninitialised memory) must not reach the product.  Each warp clears
+            // those rows of the 64-column box it reads.
+            const int first_bad = c1 - tile_row0;
+            uint8_t *vbox = stages + (size_t)st * 2 * TILE_BYTES_BF16 + TILE_BYTES_BF16 + warp * 4096;
+            for (int idx = first_bad * 8 + lane; idx < KV_TILE * 8; idx += 32)
+                *reinterpret_cast<uint4 *>(vbox + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+            __syncwarp();
+        }
         // O[:, 64w..64w+63] += P (16x32) * V (32 x 64)
 #pragma unroll
         for (int kk = 0; kk < 2; kk++) {
@@ -282,17 +316,28 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
             }
         }
     }
-    if (failed) {
+    if (failed_at >= 0) {
+        // A load did not arrive within the limit.  The loads that are still in flight write into this CTA's shared
+        // memory: wait for them (bounded again) before anything else, then stop streaming for good.
         if (tid == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);
-        return;
+        const int last_issued = min(ntiles - 1, max(BF16_STAGES - 1, failed_at + 1));
+        for (int j = failed_at + 1; j <= last_issued; j++)
+            mbar_wait_bounded(&full[(pc + (unsigned)j) % BF16_STAGES], ((pc + (unsigned)j) / BF16_STAGES) & 1u, spins);
+        abandoned = true;
+        __syncthreads();
     }
+    if (seg_no == 0) trace_phase(p, 2);
 
-    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag, reinterpret_cast<float *>(stages));  // the stage ring is idle here: scratch for the merge
+    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag, reinterpret_cast<float *>(stages), abandoned);  // the stage ring is idle here: scratch for the merge
+    if (seg_no == 0) trace_phase(p, 3);
     pc += (unsigned)ntiles;
     gt += L.seg;
+    seg_no++;
     fence_proxy_async();  // the next segment's TMA loads overwrite memory this segment touched
     __syncthreads();  // shared scratch (RoPE table, score exchange, merge weights) is reused by the next segment
     }
+    trace_phase(p, 4);
+    publish_exchange_flags(p, &s_flag);
 }
 
 constexpr size_t BF16_SMEM = 1024 + (size_t)BF16_STAGES * 2 * TILE_BYTES_BF16 +
@@ -303,11 +348,35 @@ constexpr size_t BF16_SMEM = 1024 + (size_t)BF16_STAGES * 2 * TILE_BYTES_BF16 +
 __global__ void __launch_bounds__(128)
 lse_merge_gate_kernel(int n_parts, int n, int H, const float *o_parts, const float *m_parts,
                       const float *l_parts, size_t stride_o, size_t stride_ml, size_t item_o, size_t item_ml,
-                      const float *gate, float *out) {
+                      const float *gate, float *out, const unsigned *flags, unsigned flag_value, unsigned spins,
+                      unsigned *status) {
     // one CTA per (item, head); 128 threads x 2 dims.  Part r, item i, head h:
     // o at o_parts + r*stride_o + i*item_o + h*256, m/l at + r*stride_ml + i*item_ml + h.
     const int item = blockIdx.x / H, head = blockIdx.x % H;
     const int tid = threadIdx.x;
+    if (flags) {
+        // Fused exchange: part r was stored into this buffer by rank r's decode kernel over NVLink; rank r publishes
+        // flags[r] = flag_value (a step number that only grows) once all its stores are visible.  The wait is
+        // bounded: when it runs out the CTA reports through the status word and leaves.
+        __shared__ int s_ok;
+        if (tid == 0) s_ok = 1;
+        __syncthreads();
+        if (tid < n_parts) {
+            bool seen = false;
+            for (unsigned i = 0; i < spins && !seen; i++) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + tid) : "memory");
+                seen = (int)(v - flag_value) >= 0;
+                if (!seen) __nanosleep(64);
+            }
+            if (!seen) s_ok = 0;
+        }
+        __syncthreads();
+        if (!s_ok) {
+            if (tid == 0) atomicOr(status, STATUS_PEER_TIMEOUT);
+            return;
+        }
+    }
     const size_t oo = (size_t)item * item_o + (size_t)head * HEAD_DIM, mo = (size_t)item * item_ml + head;
     float M = -INFINITY;
     for (int r = 0; r < n_parts; r++) M = fmaxf(M, m_parts[r * stride_ml + mo]);
@@ -403,14 +472,16 @@ cudaError_t launch_gqa_decode_bf16(const CUtensorMap &kmap, const CUtensorMap &v
 cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
                                   const float *m_parts, const float *l_parts, size_t part_stride,
                                   const float *gate, float *out, cudaStream_t stream, size_t o_item_stride,
-                                  size_t ml_item_stride) {
+                                  size_t ml_item_stride, const unsigned *flags, unsigned flag_value, unsigned spins,
+                                  unsigned *status) {
     if (n <= 0) return cudaSuccess;
+    if (flags && n_parts > 128) return cudaErrorInvalidValue;
     const size_t io = o_item_stride ? o_item_stride : (size_t)H * HEAD_DIM;
     const size_t iml = ml_item_stride ? ml_item_stride : (size_t)H;
     const size_t so = part_stride ? part_stride : (size_t)n * io;
     const size_t sml = part_stride ? part_stride : (size_t)n * iml;
     lse_merge_gate_kernel<<<n * H, 128, 0, stream>>>(n_parts, n, H, o_parts, m_parts, l_parts, so, sml, io, iml, gate,
-                                                     out);
+                                                     out, flags, flag_value, spins ? spins : (1u << 20), status);
     return cudaGetLastError();
 }
 

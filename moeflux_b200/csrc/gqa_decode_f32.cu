@@ -72,10 +72,26 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     int gt = (int)blockIdx.x * p.tiles_per_cta;
     const int gt_end = min(gt + p.tiles_per_cta, p.total_tiles);
     unsigned pc = 0;  // tiles pushed through the stage ring so far: stage and phase follow from it
+    const unsigned spins = p.wait_spins ? p.wait_spins : (1u << 22);
+    bool abandoned = false;  // a bounded wait ran out, or an item failed its checks: no further loads, tickets only
+    int seg_no = 0;
+    trace_phase(p, 0);
     while (gt < gt_end) {
     const Located L = locate_tile<F32_TILE>(p, gt, gt_end, s_begin);
     const GqaItem &it = L.it;
     const int group = p.group;
+    if (L.bad && !abandoned) {
+        if (tid == 0) atomicOr(p.status, STATUS_BAD_ITEM);
+        abandoned = true;
+    }
+    if (abandoned) {  // take the unit's tickets so that the counters return to zero, touch nothing else
+        float o0[8][4] = {};
+        float m0[2] = {-INFINITY, -INFINITY}, l0[2] = {0.0f, 0.0f};
+        finish_unit(p, L, o0, m0, l0, s_w, s_M, s_L, &s_flag, s_L + 16, true);
+        gt += L.seg;
+        __syncthreads();
+        continue;
+    }
 
     const int c0 = L.t0 * F32_TILE;
     const int c1 = min(c0 + L.seg * F32_TILE, it.local_len);
@@ -83,11 +99,13 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     const int row_base = (it.kv_slot * p.Hkv + L.kvh) * p.cap_rows;
     const bool appender = it.append_row >= c0 && it.append_row < c0 + L.seg * F32_TILE;
 
+    const bool lose_load = p.inject_lost_load && blockIdx.x == 0 && seg_no == 0;
     auto issue_tile = [&](int tile) {
         const int st = (int)((pc + (unsigned)tile) % F32_STAGES);
         uint8_t *kdst = stages + (size_t)st * 2 * TILE_BYTES_F32;
         uint8_t *vdst = kdst + TILE_BYTES_F32;
         mbar_expect_tx(&full[st], 2 * TILE_BYTES_F32);
+        if (lose_load && tile == 0) return;  // diagnostic: the barrier is armed and nothing will ever arrive
         const int y = row_base + c0 + tile * F32_TILE;
 #pragma unroll
         for (int b = 0; b < 8; b++) {
@@ -180,6 +198,7 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     fence_proxy_async();  // the Q staging area goes back to the ring
     __syncthreads();
     if (tid == 0 && ntiles >= F32_STAGES) issue_tile(F32_STAGES - 1);
+    if (seg_no == 0) trace_phase(p, 1);
 
     float o[8][4];
 #pragma unroll
@@ -187,12 +206,12 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
     float m_r[2] = {-INFINITY, -INFINITY};
     float l_r[2] = {0.0f, 0.0f};
     const float sl2 = p.scale * LOG2E;
-    bool failed = false;
+    int failed_at = -1;
 
     for (int i = 0; i < ntiles; i++) {
         const int st = (int)((pc + (unsigned)i) % F32_STAGES);
         const unsigned par = ((pc + (unsigned)i) / F32_STAGES) & 1u;
-        const bool ok = mbar_wait_bounded(&full[st], par);
+        const bool ok = mbar_wait_bounded(&full[st], par, spins);
         const uint8_t *kgen = stages + (size_t)st * 2 * TILE_BYTES_F32;
         const uint32_t kst = smem_u32(kgen);
         const uint8_t *vgen = kgen + TILE_BYTES_F32;
@@ -230,7 +249,7 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
                 make_float2(sp[nt][2], sp[nt][3]);
         }
         if (!__syncthreads_and(ok ? 1 : 0)) {
-            failed = true;
+            failed_at = i;
             break;
         }
         if (tid == 0 && i >= 1 && (i - 1 + F32_STAGES) < ntiles) issue_tile(i - 1 + F32_STAGES);
@@ -287,6 +306,17 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
             o[nt][2] *= corr[1];
             o[nt][3] *= corr[1];
         }
+        if (tile_row0 + F32_TILE > c1) {
+            // Rows of the tile past the end of the sequence carry weight zero, but 0 * NaN is NaN: whatever the
+            // cache holds there (a caller's uninitialised memory) must not reach the product.  Each warp clears
+            // those rows of the two 32-column boxes it reads.
+            const int first_bad = c1 - tile_row0;
+            uint8_t *vbox = stages + (size_t)st * 2 * TILE_BYTES_F32 + TILE_BYTES_F32 + 2 * warp * BOX_BYTES;
+            for (int b = 0; b < 2; b++)
+                for (int idx = first_bad * 8 + lane; idx < F32_TILE * 8; idx += 32)
+                    *reinterpret_cast<uint4 *>(vbox + b * BOX_BYTES + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+            __syncwarp();
+        }
         // O[:, 64w..64w+63] += P (16x16) * V (16 x 64): one k-step of 16 tile rows; the score
         // fragment (columns 2t, 2t+1 of each 8-column block) is already in A-operand order.
         {
@@ -311,16 +341,27 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
             }
         }
     }
-    if (failed) {
+    if (failed_at >= 0) {
+        // A load did not arrive within the limit.  The loads that are still in flight write into this CTA's shared
+        // memory: wait for them (bounded again) before anything else, then stop streaming for good.
         if (tid == 0) atomicOr(p.status, STATUS_TMA_TIMEOUT);
-        return;
+        const int last_issued = min(ntiles - 1, max(F32_STAGES - 1, failed_at + 1));
+        for (int j = failed_at + 1; j <= last_issued; j++)
+            mbar_wait_bounded(&full[(pc + (unsigned)j) % F32_STAGES], ((pc + (unsigned)j) / F32_STAGES) & 1u, spins);
+        abandoned = true;
+        __syncthreads();
     }
-    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag, s_L + 16);  // the stage ring is idle here: scratch for the merge
+    if (seg_no == 0) trace_phase(p, 2);
+    finish_unit(p, L, o, m_r, l_r, s_w, s_M, s_L, &s_flag, s_L + 16, abandoned);  // the stage ring is idle here: scratch for the merge
+    if (seg_no == 0) trace_phase(p, 3);
     pc += (unsigned)ntiles;
     gt += L.seg;
+    seg_no++;
     fence_proxy_async();  // the next segment's TMA loads overwrite memory this segment touched
     __syncthreads();  // shared scratch (RoPE table, score exchange, merge weights) is reused by the next segment
     }
+    trace_phase(p, 4);
+    publish_exchange_flags(p, &s_flag);
 }
 
 constexpr size_t F32_SMEM = 1024 + (size_t)F32_STAGES * 2 * TILE_BYTES_F32 +

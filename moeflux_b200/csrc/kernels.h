@@ -15,7 +15,10 @@ constexpr int HEAD_DIM = 256;      // full-attention head dim
 constexpr int GDN_DIM = 128;       // GatedDeltaNet key dim == value dim
 constexpr int KV_TILE = 32;        // cache rows per pipeline stage (bf16 cache)
 constexpr int KV_TILE_F32 = 16;    // same for the fp32 cache
-constexpr int MAX_SPLITS = 64;     // most KV chunks one (item, kv head) is split into
+constexpr int MERGE_GROUP = 8;     // partials merged by one CTA at the first level of a unit's merge
+constexpr int MAX_SPLITS = 64;     // most first-level groups of one unit (second-level fan-in)
+constexpr int MAX_UNIT_PARTS = MERGE_GROUP * MAX_SPLITS;  // most CTAs that may share one (item, kv head) unit
+constexpr int PHASE_TRACE_WORDS = 8;  // timestamps per CTA of the optional phase trace
 constexpr int CONV_TAPS = 4;
 
 // ---------------------------------------------------------------- GatedDeltaNet
@@ -79,6 +82,7 @@ struct GqaParams {
     size_t pml_item_stride;  //   [o | m | l] = H*256 + 2H for both
     float *sc_o, *sc_m, *sc_l;  // split-K scratch, one slot per CTA
     unsigned *tickets;       // [n][Hkv], zero between launches
+    unsigned *group_tickets; // one per scratch slot, zero between launches: arrivals of a first-level merge group
     const float *inv_freq;   // [rotary_dim/2]
     unsigned *status;
     int H, Hkv, group;       // group = H / Hkv <= 16
@@ -93,6 +97,22 @@ struct GqaParams {
     const uint16_t *knorm_w; // same for k
     int n_seqs;              // kv_slot / n_seqs = full-layer index of an item
     float norm_eps;
+    int n_kv_slots;          // items are checked against it (kv_slot) and against cap_rows (local_len, append_row)
+    // Diagnostics (all off by default):
+    unsigned wait_spins;     // poll limit of the bounded mbarrier waits; 0 = default
+    int inject_lost_load;    // 1: CTA 0 arms the barrier of its first tile and issues no load for it, so that its
+                             //    bounded wait runs out with nothing in flight (exercises the failure path)
+    unsigned long long *phase_trace;  // [total_ctas][PHASE_TRACE_WORDS] globaltimer stamps, or nullptr
+    // Fused exchange of the KV-sequence split (partial_mode only): when peer_recv != nullptr the merged partial of
+    // item i goes, instead of po/pm/pl, to the receive buffer of the rank that finishes the item,
+    //   peer_recv[i / items_per_dest] + ((size_t)my_rank * items_per_dest + i % items_per_dest) * po_item_stride
+    // as one block [o | m | l], through peer-mapped pointers (plain stores over NVLink, no multicast); the last CTA
+    // of the launch then publishes `flag_value` in slot my_rank of every peer's flag array.
+    float *const *peer_recv;             // device array [world] of device pointers
+    unsigned *const *peer_flags;         // device array [world] of device pointers to [world] flags
+    unsigned *done_counter;              // zero between launches
+    int items_per_dest, my_rank, world;
+    unsigned flag_value;
 };
 
 cudaError_t launch_gqa_decode_bf16(const CUtensorMap &kmap, const CUtensorMap &vmap,
@@ -105,10 +125,15 @@ cudaError_t gqa_decode_f32_configure();
 
 // Merge of gathered partials.  Part r of o/m/l starts part_stride floats after
 // part r-1; part_stride 0 means densely packed [n_parts][n][H][256] / [n_parts][n][H].
+// flags != nullptr (n_parts <= 128): every CTA first waits, bounded by `spins` polls, until flags[r] has reached
+// flag_value for every part r (the fused exchange's "rank r's stores have landed"); a wait that runs out sets
+// STATUS_PEER_TIMEOUT in *status.
 cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
                                   const float *m_parts, const float *l_parts, size_t part_stride,
                                   const float *gate, float *out, cudaStream_t stream,
-                                  size_t o_item_stride = 0, size_t ml_item_stride = 0);
+                                  size_t o_item_stride = 0, size_t ml_item_stride = 0,
+                                  const unsigned *flags = nullptr, unsigned flag_value = 0, unsigned spins = 0,
+                                  unsigned *status = nullptr);
 
 // RoPE on packed q [H][256], k [Hkv][256] in place (parity hook).
 // out[i] *= sigmoid(gate[i]) for n floats (n a multiple of 4): the gate applied after the fact, with the arithmetic

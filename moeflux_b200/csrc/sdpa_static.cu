@@ -35,17 +35,30 @@ constexpr int STATIC_SLOTS = 256;
 constexpr size_t OFF_TICKETS = 0;                                       // [MAX_KV_HEADS] unsigned
 constexpr size_t OFF_STATUS = 256;                                      // 1 unsigned
 constexpr size_t OFF_ITEM = 512;                                        // 1 GqaItem
-constexpr size_t OFF_M = 1024;                                          // [SLOTS][16] float
+constexpr size_t OFF_GROUP_TICKETS = 1024;                              // [SLOTS] unsigned
+constexpr size_t OFF_M = 2048;                                          // [SLOTS][16] float
 constexpr size_t OFF_L = OFF_M + sizeof(float) * STATIC_SLOTS * 16;     // [SLOTS][16] float
 constexpr size_t OFF_O = OFF_L + sizeof(float) * STATIC_SLOTS * 16;     // [SLOTS][16][256] float
 constexpr size_t SCRATCH_BYTES = OFF_O + sizeof(float) * STATIC_SLOTS * 16 * HEAD_DIM;  // ~4.03 MiB
 static_assert(OFF_O % 256 == 0, "partials must stay 256-byte aligned");
 static_assert(MFC_STATIC_MAX_KV_HEADS * sizeof(unsigned) <= 256, "ticket area too small");
+static_assert(OFF_GROUP_TICKETS + STATIC_SLOTS * sizeof(unsigned) <= OFF_M, "group ticket area too small");
 
 // Lives in the device image of every GPU that loads the library, until exit.
 // In host code this name is only a handle for cudaGetSymbolAddress: it is NOT a
 // device address and must never be handed to a kernel as one.
 static __device__ __align__(256) unsigned char g_static_scratch[SCRATCH_BYTES];
+
+// Start of a call, on the caller's stream: the item descriptor arrives by value (nothing is read from host memory
+// when the kernel runs), the chunk counters start at zero, and the status word keeps only what earlier calls
+// reported (mfc_sdpa_static_status reads and clears it).
+__global__ void static_begin_kernel(unsigned char *scratch, GqaItem it) {
+    unsigned *tickets = reinterpret_cast<unsigned *>(scratch + OFF_TICKETS);
+    unsigned *group_tickets = reinterpret_cast<unsigned *>(scratch + OFF_GROUP_TICKETS);
+    for (int i = threadIdx.x; i < MFC_STATIC_MAX_KV_HEADS; i += blockDim.x) tickets[i] = 0u;
+    for (int i = threadIdx.x; i < STATIC_SLOTS; i += blockDim.x) group_tickets[i] = 0u;
+    if (threadIdx.x == 0) *reinterpret_cast<GqaItem *>(scratch + OFF_ITEM) = it;
+}
 
 constexpr int MAX_DEVICES = 64;
 std::mutex g_setup_mutex;
@@ -135,13 +148,13 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
     if (encode_map(&kmap, k_cache, rows, bf16) || encode_map(&vmap, v_cache, rows, bf16)) return -1;
 
     // split: runs of equal tile counts over the heads' tiles, at most STATIC_SLOTS - num_kv_heads CTAs
-    // (a slot per (head, CTA) pair) and at most MAX_SPLITS partials per head
+    // (a slot per (head, CTA) pair) and at most MAX_UNIT_PARTS partials per head
     const int tile = bf16 ? KV_TILE : KV_TILE_F32;
     const int nt = (kv_len + tile - 1) / tile;
     const int total_tiles = nt * num_kv_heads;
     int w = (total_tiles + (STATIC_SLOTS - num_kv_heads) - 1) / (STATIC_SLOTS - num_kv_heads);
     if (w < 256 / tile) w = 256 / tile;
-    const int w_split = (nt + (MAX_SPLITS - 2) - 1) / (MAX_SPLITS - 2);
+    const int w_split = (nt + (MAX_UNIT_PARTS - 2) - 1) / (MAX_UNIT_PARTS - 2);
     if (w < w_split) w = w_split;
     const int n_ctas = (total_tiles + w - 1) / w;
     GqaItem it;
@@ -157,10 +170,9 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
     // The array keeps whatever the previous call left: the chunk counters and the
     // status word must start at zero.  (The partial slots are fully written before
     // they are read, so they need no clearing.)
-    e = cudaMemsetAsync(scratch, 0, OFF_ITEM, stream);
-    if (e != cudaSuccess) return fail(std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
-    e = cudaMemcpyAsync(scratch + OFF_ITEM, &it, sizeof(it), cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return fail(std::string("cudaMemcpyAsync(item): ") + cudaGetErrorString(e));
+    static_begin_kernel<<<1, 256, 0, stream>>>(scratch, it);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(std::string("kernel launch: ") + cudaGetErrorString(e));
 
     GqaParams p;
     memset(&p, 0, sizeof(p));
@@ -180,6 +192,8 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
     p.sc_m = reinterpret_cast<float *>(scratch + OFF_M);
     p.sc_l = reinterpret_cast<float *>(scratch + OFF_L);
     p.tickets = reinterpret_cast<unsigned *>(scratch + OFF_TICKETS);
+    p.group_tickets = reinterpret_cast<unsigned *>(scratch + OFF_GROUP_TICKETS);
+    p.n_kv_slots = 1;
     p.inv_freq = nullptr;
     p.status = reinterpret_cast<unsigned *>(scratch + OFF_STATUS);
     p.H = num_attn_heads;
@@ -196,6 +210,23 @@ int mfc_sdpa_static_dev(int32_t num_attn_heads, int32_t num_kv_heads, int32_t kv
     p.n_seqs = 1;
     e = bf16 ? launch_gqa_decode_bf16(kmap, vmap, p, stream) : launch_gqa_decode_f32(kmap, vmap, p, stream);
     if (e != cudaSuccess) return fail(std::string("kernel launch: ") + cudaGetErrorString(e));
+    return 0;
+}
+
+int mfc_sdpa_static_status(void *stream_v) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return fail("no current CUDA device");
+    unsigned char *scratch = nullptr;
+    if (setup_device(dev, &scratch)) return -1;
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    unsigned st = 0;
+    cudaError_t e = cudaMemcpyAsync(&st, scratch + OFF_STATUS, sizeof(st), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(scratch + OFF_STATUS, 0, sizeof(st), stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(std::string("reading the status word: ") + cudaGetErrorString(e));
+    if (st)
+        return fail("a kernel of mfc_sdpa_static_dev gave up on a bounded wait or refused its work descriptor (device "
+                    "status " + std::to_string(st) + "): outputs written since the last status call are not valid");
     return 0;
 }
 

@@ -7,6 +7,7 @@ host, or raw device pointers (ints, e.g. ``tensor.data_ptr()``) for ``*_dev``.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Optional, Sequence
 
 import numpy as np
@@ -41,6 +42,14 @@ def _u16(a, n: int, name: str):
     return a
 
 
+_LIVE = weakref.WeakSet()
+
+
+def live_contexts():
+    """The contexts of this process that are open (e.g. to verify their guard bands after a test)."""
+    return [c for c in list(_LIVE) if getattr(c, "_h", None)]
+
+
 class Ctx:
     """One attention backend context on one GPU."""
 
@@ -68,6 +77,7 @@ class Ctx:
         self.total_value = g.linear_num_v_heads * g.linear_value_dim
         self.conv_dim = 2 * g.linear_num_k_heads * g.linear_key_dim + self.total_value
         self.ssm_elems = g.linear_num_v_heads * g.linear_value_dim * g.linear_key_dim
+        _LIVE.add(self)
 
     # -- lifetime -------------------------------------------------------
     def close(self):
@@ -98,6 +108,11 @@ class Ctx:
     def stream(self) -> int:
         return int(self._lib.mfc_stream(self._h) or 0)
 
+    @property
+    def side_stream(self) -> int:
+        """The context's second queue (GatedDeltaNet launches with the tuning "gdn_side_queue")."""
+        return int(self._lib.mfc_side_stream(self._h) or 0)
+
     def set_stream(self, stream: int):
         """Issue all further work on the caller's stream (e.g. ``torch.cuda.Stream().cuda_stream``)."""
         self._check(self._lib.mfc_set_stream(self._h, stream or None), "mfc_set_stream")
@@ -115,6 +130,47 @@ class Ctx:
     @property
     def launch_count(self) -> int:
         return int(self._lib.mfc_launch_count(self._h))
+
+    def check_guards(self):
+        """Raises when a kernel wrote into the guard bands around one of the context's device allocations."""
+        self._check(self._lib.mfc_check_guards(self._h), "mfc_check_guards")
+
+    def read_phase_trace(self, max_ctas: int = 1024) -> np.ndarray:
+        """[ctas][8] uint64 nanosecond stamps of the last decode launch made with the tuning "gqa_phase_trace"."""
+        out = np.zeros((max_ctas, 8), np.uint64)
+        n = self._lib.mfc_read_phase_trace(self._h, out.ctypes.data, max_ctas)
+        if n < 0:
+            raise MfcError("mfc_read_phase_trace: " + self._lib.mfc_last_error(self._h).decode())
+        return out[:n]
+
+    # -- KV-sequence split: exchange fused into the decode kernel ---------------------
+    def exchange_create(self, items_per_rank: int) -> bytes:
+        """Allocates this rank's receive buffers; returns the 64-byte CUDA IPC handle the other ranks need."""
+        h = (C.c_ubyte * 64)()
+        self._check(self._lib.mfc_exchange_create(self._h, items_per_rank, h), "mfc_exchange_create")
+        return bytes(h)
+
+    def exchange_connect(self, handles: Sequence[bytes]):
+        """``handles``: the IPC handles of all ranks, in rank order (this rank's own entry is ignored)."""
+        blob = b"".join(bytes(h) for h in handles)
+        buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+        self._check(self._lib.mfc_exchange_connect(self._h, buf), "mfc_exchange_connect")
+
+    def exchange_connect_local(self, peers: Sequence["Ctx"]):
+        """Same, for contexts that live in this process (one per rank, in rank order)."""
+        tab = (C.c_void_p * len(peers))(*[p._h for p in peers])
+        self._check(self._lib.mfc_exchange_connect_local(self._h, tab), "mfc_exchange_connect_local")
+
+    def full_attn_partial_exchange_dev(self, layers, seq_ids, pos, q_ptr, k_ptr, v_ptr):
+        la, lp = _i32(layers)
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos)
+        rc = self._lib.mfc_full_attn_partial_exchange_dev(self._h, la.size, lp, sp, pp, q_ptr, k_ptr, v_ptr)
+        self._check(rc, "mfc_full_attn_partial_exchange_dev")
+
+    def lse_merge_gate_exchange_dev(self, gate_ptr, out_ptr):
+        self._check(self._lib.mfc_lse_merge_gate_exchange_dev(self._h, gate_ptr or None, out_ptr),
+                    "mfc_lse_merge_gate_exchange_dev")
 
     # -- weights --------------------------------------------------------
     def set_linear_weights(self, layer: int, conv_w_bf16, a_log, dt_bias_bf16, norm_w_bf16=None):
@@ -440,3 +496,11 @@ def sdpa_static_dev(num_attn_heads: int, num_kv_heads: int, kv_dtype: int, kv_le
                                k_cache_ptr, v_cache_ptr, out_ptr, stream or None)
     if rc != 0:
         raise MfcError("mfc_sdpa_static_dev: " + L.mfc_last_error(None).decode())
+
+
+def sdpa_static_status(stream: int = 0):
+    """``mfc_sdpa_static_status``: waits for ``stream`` and raises when a kernel of the calls since the previous
+    status call gave up (its outputs are then not valid).  Allocates nothing."""
+    L = lib()
+    if L.mfc_sdpa_static_status(stream or None) != 0:
+        raise MfcError("mfc_sdpa_static_status: " + L.mfc_last_error(None).decode())

@@ -18,3 +18,16 @@ def oracle_lib():
 
     oracle.build()
     return oracle
+
+
+@pytest.fixture(autouse=True)
+def guard_bands_intact(request):
+    """After every GPU test: no kernel wrote into the bands of 0xFF bytes around the device allocations of the
+    contexts that are still open (the stand-in for a memory checker)."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    import moeflux_b200 as M
+
+    for ctx in M.live_contexts():
+        ctx.check_guards()

@@ -125,3 +125,42 @@ def test_a3b_head_geometry():
         got = ctx.full_attn_step(3, 0, pos, *ins)
         assert I.rel_err(got, orc.full_attn_step(3, 0, pos, *ins)) <= TOL_F32
     ctx.close()
+
+
+def test_side_queue_step_then_snapshot_without_join():
+    """With the tuning "gdn_side_queue" the step's kernel runs on the context's second queue; a snapshot taken right
+    after it, with no explicit mfc_join, still sees the finished step (every call that reads or writes the
+    GatedDeltaNet state joins first)."""
+    import torch
+
+    from oracle import snapshot as snap
+
+    dev = torch.device("cuda:0")
+    ctx, orc = make_pair(max_seq=64, n_seqs=2, linear_layers=[0, 1, 2])
+    ctx.set_tuning("gdn_side_queue", 1)
+    r = I.rng(140)
+    items = [(0, 0), (1, 0), (2, 1)]
+    for step in range(5):
+        ins = [I.gdn_step_inputs(r) for _ in items]
+        d = [torch.tensor(np.stack([i[k] for i in ins]), device=dev) for k in range(4)]
+        out = torch.empty(len(items), G.total_value, device=dev)
+        torch.cuda.synchronize()
+        ctx.linear_attn_step_batched_dev([l for l, _ in items], [s for _, s in items], d[0].data_ptr(), d[1].data_ptr(),
+                                         d[2].data_ptr(), d[3].data_ptr(), out.data_ptr())
+        blob = ctx.state_save(0)  # no join in between
+        for j, (l, s) in enumerate(items):
+            orc.linear_attn_step(l, s, *ins[j])
+        a, b = snap.state_load(G, blob), snap.state_load(G, orc.state_save(0))
+        for layer in (0, 1):
+            assert np.array_equal(a[layer][1], b[layer][1]), step       # conv history
+            assert I.rel_err(a[layer][2], b[layer][2]) <= TOL_F32, step  # ssm state
+    # truncation resets the states: it must not race the step either
+    ins = [I.gdn_step_inputs(r) for _ in items]
+    d = [torch.tensor(np.stack([i[k] for i in ins]), device=dev) for k in range(4)]
+    torch.cuda.synchronize()
+    ctx.linear_attn_step_batched_dev([l for l, _ in items], [s for _, s in items], d[0].data_ptr(), d[1].data_ptr(),
+                                     d[2].data_ptr(), d[3].data_ptr(), out.data_ptr())
+    assert ctx.memory_seq_rm(0, 0, -1)
+    z = snap.state_load(G, ctx.state_save(0))
+    assert not z[0][2].any() and not z[1][1].any()
+    ctx.close()

@@ -292,3 +292,61 @@ def test_step_from_projection_outputs(bf16):
             ref = orc.full_attn_step(l, s, pos, qn, gate, kn, v[j])
             assert I.rel_err(got[j], ref) <= tol, (pos, j)
     ctx.close()
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_kv_split_fused_exchange_on_one_gpu(bf16):
+    """The exchange fused into the decode kernel: two contexts hold the block-cyclic halves of every sequence, each
+    stores the partial blocks of an item straight into the receive buffer of the context that finishes it and
+    publishes its step number; the finishing context's merge checks the step numbers, merges and gates.  Both
+    contexts live on one GPU here, so the two decode launches of a step are complete before the merges are issued
+    (kernels that wait on one another must not share a GPU); the receive buffers alternate by step parity."""
+    import torch
+
+    dev = torch.device("cuda:0")
+    kw = dict(max_seq=512, n_seqs=2, kv_bf16=bf16, linear_layers=[])
+    _, orc = make_pair(**kw)
+    parts = [make_pair(kv_rank=rk, kv_world=2, kv_block=32, **kw)[0] for rk in range(2)]
+    npr = 2
+    for c in parts:
+        c.exchange_create(npr)
+    for c in parts:
+        c.exchange_connect_local(parts)
+    r = I.rng(81)
+    items = [(3, 0), (7, 0), (3, 1), (7, 1)]  # sorted by finishing rank: sequence 0 on rank 0, sequence 1 on rank 1
+    layers, seqs = [i[0] for i in items], [i[1] for i in items]
+    n = len(items)
+    tol = TOL_BF16 if bf16 else TOL_F32
+    for pos in range(70):
+        ins = [I.gqa_step_inputs(r) for _ in items]
+        q = torch.tensor(np.stack([i[0] for i in ins]), device=dev)
+        gate = torch.tensor(np.stack([i[1] for i in ins]), device=dev)
+        k = torch.tensor(np.stack([i[2] for i in ins]), device=dev)
+        v = torch.tensor(np.stack([i[3] for i in ins]), device=dev)
+        torch.cuda.synchronize()
+        for c in parts:
+            c.full_attn_partial_exchange_dev(layers, seqs, [pos] * n, q.data_ptr(), k.data_ptr(), v.data_ptr())
+        for c in parts:
+            c.synchronize()
+        outs = []
+        for rk, c in enumerate(parts):
+            out = torch.empty(npr, G.q_dim, device=dev)
+            c.lse_merge_gate_exchange_dev(gate[rk * npr:(rk + 1) * npr].data_ptr(), out.data_ptr())
+            c.synchronize()
+            outs.append(out.cpu().numpy())
+        got = np.concatenate(outs)
+        for j, (layer, seq) in enumerate(items):
+            ref = orc.full_attn_step(layer, seq, pos, *ins[j])
+            assert I.rel_err(got[j], ref) <= tol, (pos, j)
+    # a merge whose peers never published the step: the bounded wait runs out and the call reports it
+    parts[0].set_tuning("gqa_wait_spins", 200)
+    parts[0].full_attn_partial_exchange_dev(layers, seqs, [70] * n, q.data_ptr(), k.data_ptr(), v.data_ptr())
+    out = torch.empty(npr, G.q_dim, device=dev)
+    parts[0].lse_merge_gate_exchange_dev(gate.data_ptr(), out.data_ptr())
+    with pytest.raises(M.MfcError, match="peer's partials did not arrive"):
+        parts[0].synchronize()
+    with pytest.raises(M.MfcError, match="exchange"):
+        parts[0].exchange_create(npr)  # already created
+    for c in parts:
+        c.check_guards()
+        c.close()
