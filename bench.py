@@ -65,6 +65,7 @@ def parse_args():
     ap.add_argument("--kv", default="bf16", choices=["bf16", "f32"], help="KV cache storage type")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-single-step", action="store_true", help="skip the batch-1 single-step latencies (N=1, stack)")
     return ap.parse_args()
 
 
@@ -663,6 +664,92 @@ def run_ours(args, rank, world, local_rank):
     return line
 
 
+# --------------------------------------------------------------------------- batch-1 single steps
+def single_step_latencies(local_rank=0, calls=1000):
+    """Configurations 0 and 1 as stated (one sequence, one layer-step per call) and the 32k target shape: microseconds
+    per step by CUDA events over `calls` pipelined device-pointer calls that rotate over enough sequences to exceed
+    the 126 MB L2 several times, so that every step streams its cache or state from HBM."""
+    import torch
+
+    import moeflux_b200 as M
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    out = {}
+
+    def timed(ctx, st, call, n_seqs, n_calls):
+        with torch.cuda.stream(st):
+            for i in range(n_seqs):
+                call(i)
+            st.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n = n_calls - n_calls % n_seqs
+            e0.record(st)
+            for i in range(n):
+                call(i)
+            e1.record(st)
+            st.synchronize()
+        ctx.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    def gqa(ctx_len, bf16, n_seqs, n_calls):
+        c = M.Ctx(num_layers=4, max_seq=ctx_len + n_calls // n_seqs + 8, n_seqs=n_seqs,
+                  kv_dtype=M.KV_BF16 if bf16 else M.KV_F32, device=local_rank, max_batch=4)
+        st = torch.cuda.Stream(device=dev)
+        c.set_stream(st.cuda_stream)
+        g = torch.Generator(device=dev)
+        g.manual_seed(5)
+        kr, vr = torch.randn(8192, KV_DIM, device=dev, generator=g), torch.randn(8192, KV_DIM, device=dev, generator=g)
+        L0 = ctx_len - 1
+        with torch.cuda.stream(st):
+            for s in range(n_seqs):
+                for p0 in range(0, L0, 8192):
+                    n = min(8192, L0 - p0)
+                    c.kv_append_rows_dev(3, s, p0, n, kr.data_ptr(), vr.data_ptr())
+        q, gt = torch.randn(Q_DIM, device=dev, generator=g), torch.randn(Q_DIM, device=dev, generator=g)
+        k, v = torch.randn(KV_DIM, device=dev, generator=g), torch.randn(KV_DIM, device=dev, generator=g)
+        o = torch.empty(Q_DIM, device=dev)
+        torch.cuda.synchronize(dev)
+        pos = [L0] * n_seqs
+
+        def call(i):
+            s = i % n_seqs
+            c.full_attn_step_batched_dev([3], [s], [pos[s]], q.data_ptr(), gt.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                         o.data_ptr())
+            pos[s] += 1
+
+        us = timed(c, st, call, n_seqs, n_calls)
+        c.close()
+        by = gqa_bytes_per_item(ctx_len, 2 if bf16 else 4)
+        return {"us_per_step": us, "algorithmic_bytes": by, "GBps": by / us / 1e3, "frac_of_8TBps": by / us / 1e3 / 8000.0,
+                "sequences_rotated": n_seqs}
+
+    out["gqa_ctx4096_f32 (configuration 0)"] = gqa(4096, False, 32, calls)
+    out["gqa_ctx32768_bf16"] = gqa(32768, True, 8, calls)
+    out["gqa_ctx32768_f32"] = gqa(32768, False, 8, calls)
+    # GatedDeltaNet single step (configuration 1)
+    n_seqs = 64
+    c = M.Ctx(num_layers=4, max_seq=64, n_seqs=n_seqs, device=local_rank, max_batch=4)
+    st = torch.cuda.Stream(device=dev)
+    c.set_stream(st.cuda_stream)
+    r = np.random.Generator(np.random.Philox(6))
+    bits = lambda a: torch.tensor(np.asarray(a, np.float32)).bfloat16().view(torch.int16).numpy().astype(np.uint16)
+    c.set_linear_weights(0, bits(r.standard_normal((CONV_DIM, 4)) * 0.5), r.uniform(0, 2.7, HV).astype(np.float32),
+                         bits(r.standard_normal(HV)), bits(1 + 0.1 * r.standard_normal(DK)))
+    qkv, z = torch.randn(CONV_DIM, device=dev), torch.randn(V_DIM, device=dev)
+    a, b, o = torch.randn(HV, device=dev), torch.randn(HV, device=dev), torch.empty(V_DIM, device=dev)
+    torch.cuda.synchronize(dev)
+    us = timed(c, st, lambda i: c.linear_attn_step_batched_dev([0], [i % n_seqs], qkv.data_ptr(), z.data_ptr(),
+                                                                 a.data_ptr(), b.data_ptr(), o.data_ptr()), n_seqs, 1024)
+    c.close()
+    by = gdn_bytes_per_item()
+    out["gdn_single_step (configuration 1)"] = {"us_per_step": us, "algorithmic_bytes": by, "GBps": by / us / 1e3,
+                                                "frac_of_8TBps": by / us / 1e3 / 8000.0, "sequences_rotated": n_seqs}
+    out["how"] = (f"CUDA events over {calls} pipelined device-pointer calls, one (layer, sequence) item each, rotating over "
+                  f"sequences whose caches or states together exceed the L2 several times")
+    return out
+
+
 # --------------------------------------------------------------------------- ragged batch, sharded by sequence
 RAGGED_SEQS = 64
 RAGGED_LO, RAGGED_HI = 1024, 32768
@@ -1188,6 +1275,8 @@ def main():
             else:
                 v, cores, desc, kind = cpu_sample(args.ctx, args.batch, kind=kind)
             line["cpu_baseline"] = {"value": v, "unit": "layer-steps/s", "cores": cores, "kind": kind, "sample": desc}
+        if world == 1 and args.workload == "stack" and not args.no_single_step:
+            line["roofline"]["single_step"] = single_step_latencies(local_rank)
         print(json.dumps(line), flush=True)
         failed = bool(line.get("parity")) and not line["parity"]["ok"]
     if world > 1:

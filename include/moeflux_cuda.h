@@ -77,8 +77,8 @@ void mfc_default_config(mfc_config *cfg);
  * crates/moeflux/src/riir/mod.rs:270).  Allocates the KV caches, the
  * GatedDeltaNet states (zeroed) and all working memory up front.  No entry
  * point of the hot path allocates device memory afterwards; the exceptions are
- * mfc_exchange_create (once, at set-up) and the host-pointer test hook
- * mfc_dequant_matvec_4bit (a temporary allocation per call).  Every allocation
+ * mfc_exchange_create (once, at set-up) and the host-pointer test hooks
+ * mfc_dequant_matvec_4bit and mfc_mla_sdpa_folded (a temporary allocation per call).  Every allocation
  * of the context sits between two bands of 0xFF bytes that no kernel may touch
  * (mfc_check_guards).  NULL on failure (mfc_last_error(NULL)). */
 mfc_ctx *mfc_open(const mfc_config *cfg);
@@ -418,6 +418,29 @@ int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *ctx, int32_t n_mat, const uint32_
                                       const uint16_t *const *scales, const uint16_t *const *biases,
                                       int32_t in_dim, const int32_t *out_dims, const float *x, int32_t n_vec,
                                       float *const *outs);
+
+/* ---- Folded MLA attention (the third attention flavour: Cogito-V2 / DeepSeek-V3 style latent KV) ----
+ * Replaces mla_sdpa_folded and its tiled form mla_sdpa_tile_accumulate / _finalize
+ * (crates/moeflux/shaders/shaders.metal:1717-1987) as dispatched by encode_mla_sdpa_folded[_tiled]
+ * (crates/moeflux/src/riir/gpu_mla.rs:146-274; CPU statement crates/moeflux/src/riir/mla_attn_cpu.rs:297-340):
+ *   s[h][t] = (q_prime[h] . latent[t] + q_pe[h] . rope_k[t]) * softmax_scale;  p = softmax_t(s[h]);
+ *   v_combine[h] = sum_t p[t] * latent[t]
+ * for num_heads heads over a caller-held compressed cache of cache_len positions:
+ *   q_prime [num_heads][512] (the query folded through kv_b_proj), q_pe [num_heads][64] (post-RoPE),
+ *   latent_cache [cache_len][512], rope_k_cache [cache_len][64], v_combine [num_heads][512], all fp32.
+ * kv_lora_rank 512 and qk_rope_head_dim 64 are the only supported sizes (MFC_MLA_RANK, MFC_MLA_ROPE).  The
+ * reference caps its single-dispatch kernel at 4096 positions and tiles beyond that; here every length is one call
+ * (split over the positions, merged by log-sum-exp: the algebra of the reference's tile merge).
+ * _dev: device pointers, 16-byte aligned, asynchronous on mfc_stream(ctx); the split's partials live in the
+ * context's scratch.  The host-pointer form stages its operands in device memory for the call (a test hook, like
+ * mfc_sdpa).  0 on success, -1 on error. */
+#define MFC_MLA_RANK 512
+#define MFC_MLA_ROPE 64
+int mfc_mla_sdpa_folded_dev(mfc_ctx *ctx, int32_t num_heads, int32_t cache_len, float softmax_scale,
+                            const float *q_prime, const float *q_pe, const float *latent_cache,
+                            const float *rope_k_cache, float *v_combine);
+int mfc_mla_sdpa_folded(mfc_ctx *ctx, int32_t num_heads, int32_t cache_len, float softmax_scale, const float *q_prime,
+                        const float *q_pe, const float *latent_cache, const float *rope_k_cache, float *v_combine);
 
 /* Tuning knobs (tests and sweeps): "gdn_rows" in {0,32,64,128} state rows per
  * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a decode launch aims for when it cuts the launch's

@@ -16,7 +16,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmoeflux_cuda.so")
-SOURCES = ["ctx.cu", "gdn_decode.cu", "gqa_decode.cu", "gqa_decode_f32.cu", "sdpa_static.cu", "gqa_prefill.cu", "gdn_prefill.cu", "matvec.cu"]
+SOURCES = ["ctx.cu", "gdn_decode.cu", "gqa_decode.cu", "gqa_decode_f32.cu", "sdpa_static.cu", "gqa_prefill.cu", "gdn_prefill.cu", "matvec.cu", "mla_decode.cu"]
 HEADERS = ["common.cuh", "kernels.h", "gqa_common.cuh", "tcgen05.cuh", os.path.join("..", "..", "include", "moeflux_cuda.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -800,7 +800,9 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
         ok = make_tensor_map(c, &c->kmap_pf, c->k_cache, kv_rows, 64) && make_tensor_map(c, &c->vmap_pf, c->v_cache, kv_rows, 64);
     if (ok && gdn_prefill_configure() != cudaSuccess) ok = fail(c, "cannot opt in to the prefill kernel's shared memory size");
     if (ok && gqa_prefill_configure() != cudaSuccess) ok = fail(c, "cannot opt in to the prefill kernel's shared memory size");
-    if (ok && (gqa_decode_configure() != cudaSuccess || gqa_decode_f32_configure() != cudaSuccess)) ok = fail(c, "cannot opt in to the kernels' shared memory size");
+    if (ok && (gqa_decode_configure() != cudaSuccess || gqa_decode_f32_configure() != cudaSuccess ||
+               mla_decode_configure() != cudaSuccess))
+        ok = fail(c, "cannot opt in to the kernels' shared memory size");
     if (!ok) {
         g_open_error = c->err;
         free_all(c);
@@ -1166,6 +1168,107 @@ int mfc_dequant_matvec_4bit(mfc_ctx *c, const uint32_t *w_packed, const uint16_t
             break;
         }
         rc = 0;
+    } while (0);
+    cudaStreamSynchronize(c->stream);
+    cudaFree(d);
+    return rc;
+}
+
+// ---------------------------------------------------------------- folded MLA attention
+
+int mfc_mla_sdpa_folded_dev(mfc_ctx *c, int32_t num_heads, int32_t cache_len, float softmax_scale, const float *q_prime,
+                            const float *q_pe, const float *latent_cache, const float *rope_k_cache, float *v_combine) {
+    if (!c) return -1;
+    if (!q_prime || !q_pe || !latent_cache || !rope_k_cache || !v_combine) {
+        fail(c, "NULL argument");
+        return -1;
+    }
+    if (num_heads <= 0 || num_heads > 1024 || cache_len <= 0) {
+        fail(c, "num_heads must be in [1, 1024] and cache_len positive");
+        return -1;
+    }
+    if (((uintptr_t)latent_cache & 15) || ((uintptr_t)rope_k_cache & 15) || ((uintptr_t)q_prime & 15) ||
+        ((uintptr_t)q_pe & 15) || ((uintptr_t)v_combine & 15)) {
+        fail(c, "all arrays must be 16-byte aligned");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    MlaParams p;
+    memset(&p, 0, sizeof(p));
+    p.H = num_heads;
+    p.cache_len = cache_len;
+    p.n_head_blocks = (num_heads + 15) / 16;
+    // chunks: one wave of CTAs (two per SM) over head blocks x chunks, at least 256 positions per chunk
+    int n_chunks = c->gqa_slots / p.n_head_blocks;
+    if (c->gqa_forced_chunk > 0) n_chunks = (cache_len + c->gqa_forced_chunk - 1) / c->gqa_forced_chunk;
+    const int max_by_len = (cache_len + 255) / 256;
+    if (n_chunks > max_by_len && c->gqa_forced_chunk <= 0) n_chunks = max_by_len;
+    if (n_chunks < 1) n_chunks = 1;
+    int rows = (cache_len + n_chunks - 1) / n_chunks;
+    rows = (rows + 15) / 16 * 16;
+    n_chunks = (cache_len + rows - 1) / rows;
+    p.n_chunks = n_chunks;
+    p.rows_per_chunk = rows;
+    // partials in the split-K scratch: [n_chunks][H][512] floats, m and l behind them in their own arrays
+    const size_t need_o = (size_t)n_chunks * num_heads * MLA_RANK;
+    if (need_o > (size_t)c->max_parts * 16 * HEAD_DIM || (size_t)n_chunks * num_heads > (size_t)c->max_parts * 16) {
+        fail(c, "split plan exceeds the scratch reserved at open");
+        return -1;
+    }
+    p.q_prime = q_prime;
+    p.q_pe = q_pe;
+    p.out = v_combine;
+    p.part_o = c->sc_o;
+    p.part_m = c->sc_m;
+    p.part_l = c->sc_l;
+    p.status = c->status;
+    p.scale = softmax_scale;
+    p.wait_spins = c->gqa_wait_spins;
+    CUtensorMap lat_map, rope_map;
+    if (!make_map_2d(c, &lat_map, const_cast<float *>(latent_cache), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, MLA_RANK,
+                     (uint64_t)cache_len, 32, 16) ||
+        !make_map_2d(c, &rope_map, const_cast<float *>(rope_k_cache), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, MLA_ROPE,
+                     (uint64_t)cache_len, 32, 16))
+        return -1;
+    CK(launch_mla_decode(lat_map, rope_map, p, c->stream));
+    c->launches += n_chunks > 1 ? 2 : 1;
+    return 0;
+}
+
+int mfc_mla_sdpa_folded(mfc_ctx *c, int32_t num_heads, int32_t cache_len, float softmax_scale, const float *q_prime,
+                        const float *q_pe, const float *latent_cache, const float *rope_k_cache, float *v_combine) {
+    if (!c) return -1;
+    if (!q_prime || !q_pe || !latent_cache || !rope_k_cache || !v_combine || num_heads <= 0 || cache_len <= 0) {
+        fail(c, "NULL argument, or num_heads / cache_len not positive");
+        return -1;
+    }
+    cudaSetDevice(c->cfg.device);
+    // a hook for tests and bring-up: the operands are staged in device memory for this call only
+    const size_t qb = sizeof(float) * (size_t)num_heads * MLA_RANK, pb = sizeof(float) * (size_t)num_heads * MLA_ROPE;
+    const size_t lb = sizeof(float) * (size_t)cache_len * MLA_RANK, rb = sizeof(float) * (size_t)cache_len * MLA_ROPE;
+    const size_t al = 255;
+    const size_t o_q = 0, o_p = (o_q + qb + al) & ~al, o_l = (o_p + pb + al) & ~al, o_r = (o_l + lb + al) & ~al,
+                 o_o = (o_r + rb + al) & ~al;
+    uint8_t *d = nullptr;
+    CK(cudaMalloc(&d, o_o + qb));
+    int rc = -1;
+    do {
+        if (cudaMemcpyAsync(d + o_q, q_prime, qb, cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+            cudaMemcpyAsync(d + o_p, q_pe, pb, cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+            cudaMemcpyAsync(d + o_l, latent_cache, lb, cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+            cudaMemcpyAsync(d + o_r, rope_k_cache, rb, cudaMemcpyHostToDevice, c->stream) != cudaSuccess) {
+            fail(c, "host to device copy failed");
+            break;
+        }
+        if (mfc_mla_sdpa_folded_dev(c, num_heads, cache_len, softmax_scale, (const float *)(d + o_q),
+                                    (const float *)(d + o_p), (const float *)(d + o_l), (const float *)(d + o_r),
+                                    (float *)(d + o_o)))
+            break;
+        if (cudaMemcpyAsync(v_combine, d + o_o, qb, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess) {
+            fail(c, "device to host copy failed");
+            break;
+        }
+        rc = check_status(c);
     } while (0);
     cudaStreamSynchronize(c->stream);
     cudaFree(d);

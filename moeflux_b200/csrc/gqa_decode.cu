@@ -367,7 +367,7 @@ lse_merge_gate_kernel(int n_parts, int n, int H, const float *o_parts, const flo
                 unsigned v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + tid) : "memory");
                 seen = (int)(v - flag_value) >= 0;
-                if (!seen) __nanosleep(64);
+                if (!seen) __nanosleep(1000);  // about a microsecond per poll: the limit is a time, give or take
             }
             if (!seen) s_ok = 0;
         }
@@ -481,7 +481,7 @@ cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_part
     const size_t so = part_stride ? part_stride : (size_t)n * io;
     const size_t sml = part_stride ? part_stride : (size_t)n * iml;
     lse_merge_gate_kernel<<<n * H, 128, 0, stream>>>(n_parts, n, H, o_parts, m_parts, l_parts, so, sml, io, iml, gate,
-                                                     out, flags, flag_value, spins ? spins : (1u << 20), status);
+                                                     out, flags, flag_value, spins ? spins : (1u << 21), status);
     return cudaGetLastError();
 }
 

@@ -125,7 +125,8 @@ cudaError_t gqa_decode_f32_configure();
 
 // Merge of gathered partials.  Part r of o/m/l starts part_stride floats after
 // part r-1; part_stride 0 means densely packed [n_parts][n][H][256] / [n_parts][n][H].
-// flags != nullptr (n_parts <= 128): every CTA first waits, bounded by `spins` polls, until flags[r] has reached
+// flags != nullptr (n_parts <= 128): every CTA first waits, bounded by `spins` polls of about a microsecond each (0: about
+// two seconds, enough for ranks that are out of step by a host hiccup), until flags[r] has reached
 // flag_value for every part r (the fused exchange's "rank r's stores have landed"); a wait that runs out sets
 // STATUS_PEER_TIMEOUT in *status.
 cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_parts,
@@ -201,6 +202,28 @@ struct GdnPrefillMaps {
     CUtensorMap wt, q, k, wm, ut;
 };
 cudaError_t launch_gdn_prefill(const GdnPrefillParams &p, const GdnPrefillMaps &m, cudaStream_t stream);
+
+// ---------------------------------------------------------------- folded MLA attention (mla_decode.cu)
+constexpr int MLA_RANK = 512;  // kv_lora_rank: latent dims of a cached row, and dims of an output row
+constexpr int MLA_ROPE = 64;   // qk_rope_head_dim
+struct MlaParams {
+    const float *q_prime;   // [H][512]
+    const float *q_pe;      // [H][64]
+    float *out;             // [H][512]
+    float *part_o;          // [n_chunks][H][512] un-normalised partials (n_chunks > 1)
+    float *part_m, *part_l; // [n_chunks][H]
+    unsigned *status;
+    int H, cache_len;
+    int n_head_blocks;      // ceil(H / 16)
+    int n_chunks;           // chunks of rows_per_chunk positions (a multiple of 16)
+    int rows_per_chunk;
+    float scale;            // softmax scale
+    unsigned wait_spins;    // poll limit of the bounded waits; 0 = default
+};
+cudaError_t mla_decode_configure();
+// lat_map: [cache_len][512] fp32, rope_map: [cache_len][64] fp32, boxes of 32 floats x 16 rows, 128-byte swizzle.
+cudaError_t launch_mla_decode(const CUtensorMap &lat_map, const CUtensorMap &rope_map, const MlaParams &p,
+                              cudaStream_t stream);
 
 // 4-bit group-64 dequant matvec (matvec.cu): for every matrix m of the batch and vector v,
 // out[m][v][r] = sum_c (nibble * scale + bias)(m; r, c) * x[v][c]; the matrices share in_dim and x; n_vec in 1..8.

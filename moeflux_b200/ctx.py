@@ -298,6 +298,32 @@ class Ctx:
         self._check(rc, "mfc_eval_token_attn")
         return fo, lo
 
+    def eval_token_attn_split(self, full_items, pos, q, gate_own, k, v, lin_items, qkv, z, alpha, beta, n_own: int):
+        """``eval_token_attn`` on a context of a KV split with its exchange connected: ``full_items`` is the whole
+        step's item list sorted by finishing rank, ``gate_own`` holds the gate rows of the ``n_own`` items this rank
+        finishes, and the returned full-attention outputs are those items' ([n_own, q_dim])."""
+        nf, nl = len(full_items), len(lin_items)
+        fl, flp = _i32([l for l, _ in full_items])
+        fs, fsp = _i32([s for _, s in full_items])
+        pa, pp = _i32(list(pos))
+        ll, llp = _i32([l for l, _ in lin_items] or [0])
+        ls, lsp = _i32([s for _, s in lin_items] or [0])
+        q, gate_own = _f32(q, nf * self.q_dim, "q"), _f32(gate_own, n_own * self.q_dim, "gate_own")
+        k, v = _f32(k, nf * self.kv_dim, "k"), _f32(v, nf * self.kv_dim, "v")
+        fo = np.empty((n_own, self.q_dim), np.float32)
+        lo = np.empty((nl, self.total_value), np.float32)
+        if nl:
+            qkv = _f32(qkv, nl * self.conv_dim, "qkv")
+            z = None if z is None else _f32(z, nl * self.total_value, "z")
+            alpha, beta = _f32(alpha, nl * self.v_heads, "alpha"), _f32(beta, nl * self.v_heads, "beta")
+        P = lambda a: _fp(a) if a is not None else None
+        rc = self._lib.mfc_eval_token_attn(
+            self._h, nf, flp, fsp, pp, _fp(q), _fp(gate_own), _fp(k), _fp(v), _fp(fo), nl, llp, lsp,
+            P(qkv) if nl else None, P(z) if nl else None, P(alpha) if nl else None, P(beta) if nl else None,
+            _fp(lo) if nl else None)
+        self._check(rc, "mfc_eval_token_attn")
+        return fo, lo
+
     def eval_token_attn_ptr(self, nf, fl_p, fs_p, pos_p, q_p, gate_p, k_p, v_p, fo_p, nl, ll_p, ls_p, qkv_p, z_p,
                             alpha_p, beta_p, lo_p):
         """Raw-pointer form (pinned host buffers, no numpy work per call)."""
@@ -466,6 +492,30 @@ class Ctx:
         rc = self._lib.mfc_dequant_matvec_4bit_multi_dev(self._h, n, tab(packed_ptrs), tab(scales_ptrs), tab(biases_ptrs),
                                                          in_dim, dims, x_ptr, n_vec, tab(out_ptrs))
         self._check(rc, "mfc_dequant_matvec_4bit_multi_dev")
+
+    # -- folded MLA attention (shaders.metal:1717-1987, gpu_mla.rs:146-274) -------------------------
+    def mla_sdpa_folded(self, cache_len: int, softmax_scale: float, q_prime, q_pe, latent_cache, rope_k_cache) -> np.ndarray:
+        """v_combine [num_heads, 512] for q_prime [num_heads, 512], q_pe [num_heads, 64] over the first cache_len rows
+        of latent_cache [., 512] and rope_k_cache [., 64] (host arrays)."""
+        qp = np.ascontiguousarray(q_prime, np.float32)
+        H = qp.size // 512
+        qp = _f32(qp, H * 512, "q_prime")
+        pe = _f32(q_pe, H * 64, "q_pe")
+        lat = _f32(latent_cache)
+        rk = _f32(rope_k_cache)
+        if cache_len > 0 and (lat.size < cache_len * 512 or rk.size < cache_len * 64):
+            raise ValueError("mla_sdpa_folded: cache shorter than cache_len rows")
+        out = np.empty((H, 512), np.float32)
+        rc = self._lib.mfc_mla_sdpa_folded(self._h, H, cache_len, softmax_scale, _fp(qp), _fp(pe), _fp(lat), _fp(rk),
+                                           _fp(out))
+        self._check(rc, "mfc_mla_sdpa_folded")
+        return out
+
+    def mla_sdpa_folded_dev(self, num_heads, cache_len, softmax_scale, q_prime_ptr, q_pe_ptr, latent_ptr, rope_k_ptr,
+                            out_ptr):
+        rc = self._lib.mfc_mla_sdpa_folded_dev(self._h, num_heads, cache_len, softmax_scale, q_prime_ptr, q_pe_ptr,
+                                               latent_ptr, rope_k_ptr, out_ptr)
+        self._check(rc, "mfc_mla_sdpa_folded_dev")
 
     def linear_attn_step_stateless(self, layer: int, qkv, z, alpha, beta, conv_state, ssm_state):
         """Returns (out, new_conv_state, new_ssm_state); inputs are not modified."""

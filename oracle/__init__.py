@@ -400,3 +400,25 @@ def lse_merge_gate(o_parts, m_parts, l_parts, gate, g: Geometry = A17B):
                                 g.num_attn_heads, g.head_dim):
         raise ValueError("lse_merge_gate: bad arguments")
     return out
+
+
+def mla_sdpa_folded(cache_len: int, softmax_scale: float, q_prime, q_pe, latent, rope_k, kv_lora_rank: int = 512,
+                    rope_dim: int = 64, tile: int = 0) -> np.ndarray:
+    """shaders.metal:1717-1822 (tile == 0) or the tiled online-softmax form :1845-1987 with tiles of `tile` positions.
+    Returns v_combine [num_heads, kv_lora_rank]."""
+    qp, qpp = _f(q_prime)
+    pe, pep = _f(q_pe)
+    lat, lp = _f(latent)
+    rk, rp = _f(rope_k)
+    H = qp.size // kv_lora_rank
+    out = np.zeros((H, kv_lora_rank), np.float32)
+    op = out.ctypes.data_as(C.POINTER(C.c_float))
+    if tile:
+        rc = lib().mfo_mla_sdpa_folded_tiled(H, kv_lora_rank, rope_dim, int(cache_len), int(tile), C.c_float(softmax_scale),
+                                             qpp, pep, lp, rp, op)
+    else:
+        rc = lib().mfo_mla_sdpa_folded(H, kv_lora_rank, rope_dim, int(cache_len), C.c_float(softmax_scale), qpp, pep, lp,
+                                       rp, op)
+    if rc:
+        raise ValueError("mla_sdpa_folded: bad arguments")
+    return out

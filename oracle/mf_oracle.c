@@ -604,3 +604,106 @@ MFO_API int mfo_lse_merge_gate(int n_parts, const float *o_parts, const float *m
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------
+ * Folded MLA attention.  crates/moeflux/shaders/shaders.metal:1717-1822
+ * (mla_sdpa_folded; the same sums per head as the CPU layer's SDPA loop,
+ * crates/moeflux/src/riir/mla_attn_cpu.rs:297-340, with K and V folded into the
+ * latent): scores by an fma chain over the latent then the rope dims, scaled;
+ * softmax as max / exp / sum / normalise; v_combine by an fma chain over the
+ * positions.  Threads split heads only.
+ * ---------------------------------------------------------------------- */
+MFO_API int mfo_mla_sdpa_folded(int num_heads, int kv_lora_rank, int rope_dim, int cache_len, float softmax_scale,
+                                const float *q_prime, const float *q_pe, const float *latent,
+                                const float *rope_k, float *v_combine) {
+    if (num_heads <= 0 || kv_lora_rank <= 0 || rope_dim < 0 || cache_len <= 0) return -1;
+    int err = 0;
+#pragma omp parallel for schedule(static)
+    for (int h = 0; h < num_heads; h++) {
+        float *scores = (float *)malloc(sizeof(float) * (size_t)cache_len);
+        if (!scores) {
+            err = 1;
+            continue;
+        }
+        const float *qh = q_prime + (size_t)h * kv_lora_rank, *ph = q_pe + (size_t)h * rope_dim;
+        for (int t = 0; t < cache_len; t++) {
+            const float *lt = latent + (size_t)t * kv_lora_rank, *rt = rope_k + (size_t)t * rope_dim;
+            float s = 0.0f;
+            for (int c = 0; c < kv_lora_rank; c++) s = fmaf(qh[c], lt[c], s);
+            for (int r = 0; r < rope_dim; r++) s = fmaf(ph[r], rt[r], s);
+            scores[t] = s * softmax_scale;
+        }
+        float mx = -INFINITY;
+        for (int t = 0; t < cache_len; t++) mx = scores[t] > mx ? scores[t] : mx;
+        float sum = 0.0f;
+        for (int t = 0; t < cache_len; t++) {
+            scores[t] = expf(scores[t] - mx);
+            sum += scores[t];
+        }
+        const float inv = 1.0f / sum;
+        for (int t = 0; t < cache_len; t++) scores[t] *= inv;
+        float *out = v_combine + (size_t)h * kv_lora_rank;
+        for (int c = 0; c < kv_lora_rank; c++) {
+            float acc = 0.0f;
+            for (int t = 0; t < cache_len; t++) acc = fmaf(scores[t], latent[(size_t)t * kv_lora_rank + c], acc);
+            out[c] = acc;
+        }
+        free(scores);
+    }
+    return err ? -1 : 0;
+}
+
+/* The tiled form: tiles of `tile` positions merged by the online softmax of
+ * mla_sdpa_tile_accumulate (shaders.metal:1845-1966), finished by
+ * mla_sdpa_tile_finalize (:1971-1987); the tile loop of
+ * encode_mla_sdpa_folded_tiled (crates/moeflux/src/riir/gpu_mla.rs:226-274). */
+MFO_API int mfo_mla_sdpa_folded_tiled(int num_heads, int kv_lora_rank, int rope_dim, int cache_len, int tile,
+                                      float softmax_scale, const float *q_prime, const float *q_pe,
+                                      const float *latent, const float *rope_k, float *v_combine) {
+    if (num_heads <= 0 || kv_lora_rank <= 0 || rope_dim < 0 || cache_len <= 0 || tile <= 0) return -1;
+    int err = 0;
+#pragma omp parallel for schedule(static)
+    for (int h = 0; h < num_heads; h++) {
+        float *scores = (float *)malloc(sizeof(float) * (size_t)tile);
+        float *vp = (float *)calloc((size_t)kv_lora_rank, sizeof(float));
+        if (!scores || !vp) {
+            err = 1;
+            free(scores);
+            free(vp);
+            continue;
+        }
+        const float *qh = q_prime + (size_t)h * kv_lora_rank, *ph = q_pe + (size_t)h * rope_dim;
+        float run_max = -INFINITY, run_den = 0.0f;
+        for (int t0 = 0; t0 < cache_len; t0 += tile) {
+            const int n = cache_len - t0 < tile ? cache_len - t0 : tile;
+            float tmax = -INFINITY;
+            for (int i = 0; i < n; i++) {
+                const float *lt = latent + (size_t)(t0 + i) * kv_lora_rank, *rt = rope_k + (size_t)(t0 + i) * rope_dim;
+                float s = 0.0f;
+                for (int c = 0; c < kv_lora_rank; c++) s = fmaf(qh[c], lt[c], s);
+                for (int r = 0; r < rope_dim; r++) s = fmaf(ph[r], rt[r], s);
+                scores[i] = s * softmax_scale;
+                tmax = scores[i] > tmax ? scores[i] : tmax;
+            }
+            float tsum = 0.0f;
+            for (int i = 0; i < n; i++) {
+                scores[i] = expf(scores[i] - tmax);
+                tsum += scores[i];
+            }
+            const float new_max = run_max > tmax ? run_max : tmax;
+            const float scale_old = expf(run_max - new_max), scale_new = expf(tmax - new_max);
+            run_den = run_den * scale_old + tsum * scale_new;
+            for (int c = 0; c < kv_lora_rank; c++) {
+                float part = 0.0f;
+                for (int i = 0; i < n; i++) part = fmaf(scores[i], latent[(size_t)(t0 + i) * kv_lora_rank + c], part);
+                vp[c] = vp[c] * scale_old + part * scale_new;
+            }
+            run_max = new_max;
+        }
+        const float inv = run_den > 0.0f ? 1.0f / run_den : 0.0f;
+        for (int c = 0; c < kv_lora_rank; c++) v_combine[(size_t)h * kv_lora_rank + c] = vp[c] * inv;
+        free(scores);
+        free(vp);
+    }
+    return err ? -1 : 0;
+}
