@@ -149,6 +149,8 @@ struct mfc_ctx {
     int n_sms = 148;
     size_t smem_optin = 227 * 1024;
     int gqa_forced_chunk = 0;
+    int gqa_min_rows = 128;        // least cache rows per CTA
+    bool gqa_unit_aligned = true;  // one CTA per unit when equal-length units nearly fill the wave
     long long launches = 0;
     std::string err;
 };
@@ -309,10 +311,10 @@ int check_status(mfc_ctx *c) {
 // head) units form one sequence; it is cut into equal runs of `tiles_per_cta` tiles,
 // one CTA each, across unit boundaries, so that one wave of CTAs (2 per SM) carries
 // the whole launch with equal work per CTA.  A unit cut by a run boundary is merged
-// from the partials of the CTAs that share it.  Constraints: at least 256 rows per
-// CTA (a CTA's start-up and epilogue cost about as much as streaming that), at most
-// MAX_UNIT_PARTS partials per unit.
-int plan_tiles_per_cta(const mfc_ctx *c, long long total_tiles, int max_unit_tiles) {
+// from the partials of the CTAs that share it.  Constraints: at least gqa_min_rows
+// rows per CTA, at most MAX_UNIT_PARTS partials per unit.
+int plan_tiles_per_cta(const mfc_ctx *c, long long total_tiles, int max_unit_tiles, int min_unit_tiles = 0,
+                       long long n_units = 0) {
     const int tile = c->cfg.kv_dtype == MFC_KV_BF16 ? KV_TILE : KV_TILE_F32;
     long long w;
     if (c->gqa_forced_chunk > 0) {
@@ -320,8 +322,16 @@ int plan_tiles_per_cta(const mfc_ctx *c, long long total_tiles, int max_unit_til
     } else {
         const long long ctas = c->gqa_target_ctas > 0 ? c->gqa_target_ctas : c->gqa_slots;
         w = (total_tiles + ctas - 1) / ctas;
-        const long long w_min = 256 / tile;
+        // A launch too small to give every CTA of the wave a long run (a single sequence, a few short ones) is bound
+        // by latency, not by bandwidth: it is spread over as many SMs as runs of gqa_min_rows rows allow.
+        const long long w_min = c->gqa_min_rows / tile;
         if (w < w_min) w = w_min;
+        // Units of equal length that nearly fill the wave by themselves: one CTA per unit.  No unit is shared, so
+        // no partial is parked or merged and every CTA builds its query fragments once; the few idle CTA slots cost
+        // less than that (the launch is bound by HBM, not by the number of CTAs that stream).
+        if (c->gqa_target_ctas == 0 && c->gqa_unit_aligned && n_units > 0 && min_unit_tiles == max_unit_tiles &&
+            n_units <= ctas && n_units * 10 >= ctas * 7 && max_unit_tiles >= w)
+            w = max_unit_tiles;
     }
     const long long w_split = (max_unit_tiles + (MAX_UNIT_PARTS - 2) - 1) / (MAX_UNIT_PARTS - 2);
     if (w < w_split) w = w_split;
@@ -375,7 +385,7 @@ int build_gqa_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq
     }
     const int tile = g.kv_dtype == MFC_KV_BF16 ? KV_TILE : KV_TILE_F32;
     long long total_tiles = 0;
-    int max_unit_tiles = 1;
+    int max_unit_tiles = 1, min_unit_tiles = 1 << 30;
     for (int i = 0; i < n; i++) {
         GqaItem &it = c->h_gqa_items[i];
         const int nt = it.local_len > 0 ? (it.local_len + tile - 1) / tile : 1;
@@ -383,12 +393,13 @@ int build_gqa_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq
         it.pad0 = it.pad1 = 0;
         total_tiles += (long long)nt * g.num_kv_heads;
         if (nt > max_unit_tiles) max_unit_tiles = nt;
+        if (nt < min_unit_tiles) min_unit_tiles = nt;
     }
     if (total_tiles >= (1ll << 31)) {
         fail(c, "too many KV tiles in one launch");
         return -1;
     }
-    c->plan_tiles_per_cta = plan_tiles_per_cta(c, total_tiles, max_unit_tiles);
+    c->plan_tiles_per_cta = plan_tiles_per_cta(c, total_tiles, max_unit_tiles, min_unit_tiles, (long long)n * g.num_kv_heads);
     c->plan_total_tiles = (int)total_tiles;
     const int cta = (int)((total_tiles + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta);
     if (cta + n * g.num_kv_heads > c->max_parts) {
@@ -436,8 +447,13 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
     p.norm_eps = g.rms_norm_eps;
 }
 
-int launch_gqa(mfc_ctx *c, const GqaParams &p) {
-    if (upload_items(c, c->d_gqa_items, c->h_gqa_items.data(), sizeof(GqaItem) * p.n_items, c->stream)) return -1;
+int launch_gqa(mfc_ctx *c, GqaParams &p) {
+    if (p.n_items <= INLINE_ITEMS) {  // a handful of items travel as kernel parameters: no copy before the launch
+        p.items = nullptr;
+        for (int i = 0; i < p.n_items; i++) p.inline_items[i] = c->h_gqa_items[i];
+    } else if (upload_items(c, c->d_gqa_items, c->h_gqa_items.data(), sizeof(GqaItem) * p.n_items, c->stream)) {
+        return -1;
+    }
     if (c->cfg.kv_dtype == MFC_KV_BF16) CK(launch_gqa_decode_bf16(c->kmap, c->vmap, p, c->stream));
     else CK(launch_gqa_decode_f32(c->kmap, c->vmap, p, c->stream));
     c->launches += 1;
@@ -505,7 +521,12 @@ int launch_gdn(mfc_ctx *c, int n, const float *qkv, const float *z, const float 
     p.Hk = g.linear_num_k_heads;
     p.conv_dim = c->conv_dim;
     p.eps = g.rms_norm_eps;
-    if (upload_items(c, c->d_gdn_items, c->h_gdn_items.data(), sizeof(GdnItem) * n, c->stream)) return -1;
+    if (n <= INLINE_ITEMS) {  // a handful of items travel as kernel parameters: no copy before the launch
+        p.items = nullptr;
+        for (int i = 0; i < n; i++) p.inline_items[i] = c->h_gdn_items[i];
+    } else if (upload_items(c, c->d_gdn_items, c->h_gdn_items.data(), sizeof(GdnItem) * n, c->stream)) {
+        return -1;
+    }
     // Whole heads per CTA (128 rows) amortise the conv/norm prologue best; smaller
     // blocks only when the launch would otherwise leave SMs without work.
     int rows = c->gdn_rows;
@@ -1289,6 +1310,11 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
     } else if (!strcmp(key, "gqa_chunk")) {
         if (value < 0) return -1;
         c->gqa_forced_chunk = value;
+    } else if (!strcmp(key, "gqa_min_rows")) {
+        if (value < 32 || value % 32) return -1;
+        c->gqa_min_rows = value;
+    } else if (!strcmp(key, "gqa_unit_aligned")) {
+        c->gqa_unit_aligned = value != 0;
     } else if (!strcmp(key, "gqa_wait_spins")) {
         if (value < 0) return -1;
         c->gqa_wait_spins = (unsigned)value;

@@ -56,7 +56,7 @@ __device__ __forceinline__ float conv_channel(const float *ring, const float *x,
 }
 
 template <int ROWS>
-__global__ void __launch_bounds__(256) gdn_decode_kernel(const GdnParams p) {
+__global__ void __launch_bounds__(256) gdn_decode_kernel(const __grid_constant__ GdnParams p) {
     constexpr int CS = GDN_DIM / ROWS;  // CTAs per head (cluster size)
     constexpr int RPW = ROWS / 8;       // rows per warp
     constexpr int NB = RPW / 4;         // batches of four rows per warp
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(const GdnParams p) {
     const int rb = bid % CS;
     const int h = (bid / CS) % p.Hv;
     const int item = bid / (CS * p.Hv);
-    const GdnItem it = p.items[item];
+    const GdnItem it = p.items ? p.items[item] : p.inline_items[item];
     const int vpk = p.Hv / p.Hk;
     const int j = h / vpk;
     const int total_key = p.Hk * GDN_DIM;

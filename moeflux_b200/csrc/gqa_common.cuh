@@ -90,9 +90,11 @@ struct Located {
 constexpr int LOCATE_SMEM_ITEMS = 512;
 // Stages the items' first-tile indices in shared memory (one round of global
 // loads instead of a dependent chain per lookup).  Contains a __syncthreads.
+__device__ __forceinline__ const GqaItem *item_list(const GqaParams &p) { return p.items ? p.items : p.inline_items; }
 __device__ __forceinline__ void stage_tile_begins(const GqaParams &p, int *s_begin) {
+    const GqaItem *items = item_list(p);
     if (p.n_items <= LOCATE_SMEM_ITEMS)
-        for (int i = threadIdx.x; i < p.n_items; i += blockDim.x) s_begin[i] = p.items[i].tile_begin;
+        for (int i = threadIdx.x; i < p.n_items; i += blockDim.x) s_begin[i] = items[i].tile_begin;
     __syncthreads();
 }
 // Segment that starts at tile `gt` of the launch-wide sequence and ends at the
@@ -101,14 +103,15 @@ template <int TILE_ROWS>
 __device__ __forceinline__ Located locate_tile(const GqaParams &p, int gt, int gt_end, const int *s_begin) {
     int lo = 0, hi = p.n_items - 1;
     const bool in_smem = p.n_items <= LOCATE_SMEM_ITEMS;
+    const GqaItem *items = item_list(p);
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
-        const int tb = in_smem ? s_begin[mid] : p.items[mid].tile_begin;
+        const int tb = in_smem ? s_begin[mid] : items[mid].tile_begin;
         if (tb <= gt) lo = mid;
         else hi = mid - 1;
     }
     Located L;
-    L.it = p.items[lo];
+    L.it = items[lo];
     L.item_idx = lo;
     const int nt = L.it.local_len > 0 ? (L.it.local_len + TILE_ROWS - 1) / TILE_ROWS : 1;
     const int local = gt - L.it.tile_begin;

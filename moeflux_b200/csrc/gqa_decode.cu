@@ -45,7 +45,7 @@ constexpr int SX_STRIDE = 40;                            // padded row stride of
 
 __global__ void __launch_bounds__(128, 2)
 gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
-                       const __grid_constant__ CUtensorMap vmap, const GqaParams p) {
+                       const __grid_constant__ CUtensorMap vmap, const __grid_constant__ GqaParams p) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the 128-byte swizzle atoms
     uint8_t *smem = reinterpret_cast<uint8_t *>(

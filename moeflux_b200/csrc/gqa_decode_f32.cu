@@ -39,7 +39,7 @@ __device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t &hi, u
 
 __global__ void __launch_bounds__(128, 2)
 gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
-                      const __grid_constant__ CUtensorMap vmap, const GqaParams p) {
+                      const __grid_constant__ CUtensorMap vmap, const __grid_constant__ GqaParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);

@@ -29,6 +29,8 @@ struct GdnItem {
     int32_t pad;
 };
 
+constexpr int INLINE_ITEMS = 4;  // launches of at most this many items carry them in the kernel's parameters
+
 struct GdnParams {
     float *ssm_base;          // [state][Hv][128 value][128 key]
     float *conv_base;         // [state][4 slots][conv_dim]
@@ -36,7 +38,8 @@ struct GdnParams {
     const float *a_log;       // [w_layer][Hv]
     const uint16_t *dt_bias;  // [w_layer][Hv] bf16
     const uint16_t *norm_w;   // [w_layer][128] bf16
-    const GdnItem *items;     // device
+    const GdnItem *items;     // device; nullptr: the items are `inline_items` (no copy precedes the launch)
+    GdnItem inline_items[INLINE_ITEMS];
     const float *qkv;         // [n][conv_dim]
     const float *z;           // [n][Hv*128] or nullptr
     const float *alpha;       // [n][Hv]
@@ -65,7 +68,8 @@ struct GqaItem {
 struct GqaParams {
     void *k_base;            // cache base pointers (for the append)
     void *v_base;
-    const GqaItem *items;    // device
+    const GqaItem *items;    // device; nullptr: the items are `inline_items` (no copy precedes the launch)
+    GqaItem inline_items[INLINE_ITEMS];
     int n_items;
     int total_ctas;
     // The tiles of all (item, kv head) units form one sequence; CTA c works on tiles

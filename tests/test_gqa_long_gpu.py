@@ -83,7 +83,7 @@ def test_ragged_batch_of_16_automatic_plan(bf16):
     """Sixteen sequences with ragged contexts between 8k and 32k in one launch under the automatic plan: one wave of
     CTAs with equal tile runs that cross unit boundaries, every unit shared by several CTAs."""
     n = 16
-    ctx, orc = make_pair(G4, max_seq=32768, n_seqs=n, kv_bf16=bf16, linear_layers=[])
+    ctx, orc = make_pair(G4, max_seq=32768 + 8, n_seqs=n, kv_bf16=bf16, linear_layers=[])
     r = I.rng(1600 + bf16)
     lens = [int(x) for x in r.integers(8192, 32768, n)]
     lens[0], lens[1] = 32767, 8192
@@ -108,7 +108,7 @@ def test_units_shared_by_many_ctas(lens):
     """Few long sequences: every (item, kv head) unit is shared by far more than sixteen CTAs, the last merge group
     of a unit is partly filled, and run boundaries fall inside units."""
     n = len(lens)
-    ctx, orc = make_pair(G4, max_seq=32768, n_seqs=n, kv_bf16=True, linear_layers=[])
+    ctx, orc = make_pair(G4, max_seq=32768 + 8, n_seqs=n, kv_bf16=True, linear_layers=[])
     r = I.rng(1700 + n)
     for s, ln in enumerate(lens):
         install_kv(ctx, orc, FULL, s, I.normal(r, (ln, G4.kv_dim)), I.normal(r, (ln, G4.kv_dim)))
