@@ -91,3 +91,58 @@ def test_kv_split_two_ranks_gloo(tmp_path, ctx_len):
     mp.spawn(_worker, args=(_free_port(), ctx_len, 70, path), nprocs=WORLD, join=True)
     worst = float(open(path).read())
     assert worst <= 1e-5, worst
+
+
+def _ragged_worker(rank, port, result_path):
+    """Sharding by sequence (bench.py --workload ragged) on CPU ranks: each rank computes the layer-steps of its shard
+    with the oracle, the padded outputs are all-gathered, and every sequence's output is found where the plan says."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    import bench
+
+    lens = [1 + (x % 97) for x in bench.ragged_lengths()]  # the benchmark's seeded lengths, scaled down for the CPU
+    shards, load = bench.ragged_shards(lens, WORLD)
+    n_max = max(len(s) for s in shards)
+    mine = shards[rank]
+    out = torch.zeros(n_max, G.q_dim)
+    refs = {}
+    for s in range(len(lens)):
+        r = I.rng(7000 + s)  # per-sequence stream: every rank can form any sequence's reference
+        K, V = I.normal(r, (lens[s], G.kv_dim)), I.normal(r, (lens[s], G.kv_dim))
+        q, gate = I.normal(r, G.q_dim), I.normal(r, G.q_dim)
+        o = O.sdpa(lens[s], q, gate, K, V)
+        if s in mine:
+            out[mine.index(s)] = torch.tensor(o)
+        refs[s] = o
+    gathered = torch.empty(WORLD * n_max, G.q_dim)
+    dist.all_gather_into_tensor(gathered, out)
+    ok = all(np.array_equal(gathered[rk * n_max + j].numpy(), refs[s]) for rk in range(WORLD) for j, s in enumerate(shards[rk]))
+    flag = torch.tensor([1.0 if ok else 0.0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        with open(result_path, "w") as f:
+            f.write(repr((float(flag[0]), load)))
+    dist.destroy_process_group()
+
+
+def test_ragged_sequence_sharding_two_ranks_gloo(tmp_path):
+    O.build()
+    path = str(tmp_path / "ragged.txt")
+    mp.spawn(_ragged_worker, args=(_free_port(), path), nprocs=WORLD, join=True)
+    ok, load = eval(open(path).read())
+    assert ok == 1.0
+
+
+def test_ragged_shards_are_a_balanced_partition():
+    import bench
+
+    lens = bench.ragged_lengths()
+    assert len(lens) == 64 and min(lens) >= 1024 and max(lens) <= 32768
+    assert lens == bench.ragged_lengths()  # seeded
+    for world in (1, 2, 4, 8):
+        shards, load = bench.ragged_shards(lens, world)
+        assert sorted(s for sh in shards for s in sh) == list(range(64))      # every sequence exactly once
+        assert [sum(lens[s] for s in sh) for sh in shards] == load
+        assert max(load) - min(load) <= max(lens)                             # greedy longest-first bound
+        assert max(load) <= 1.05 * sum(lens) / world + 1                      # and close to even for these lengths
