@@ -64,6 +64,7 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "f32"], help="KV cache storage type")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--repeats", type=int, default=0, help="timed blocks of --steps steps (0: at least 7 and about a second)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-single-step", action="store_true", help="skip the batch-1 single-step latencies (N=1, stack)")
     return ap.parse_args()
@@ -306,7 +307,7 @@ def run_ours(args, rank, world, local_rank):
     W, K = args.warmup, args.steps
     do_e2e = not args.no_e2e
     fused = world > 1 and args.exchange == "fused"
-    R = repeats_for(K, 4.9 * (CTX / 131072.0) * (B / 8.0) / world)
+    R = args.repeats or repeats_for(K, 4.9 * (CTX / 131072.0) * (B / 8.0) / world)
     We, Re = (min(W, 3), min(R, 7)) if do_e2e else (0, 0)
     total_steps = W + R * K + We + Re * K + 1  # + the step whose outputs are checked against the oracle
     L0 = CTX - total_steps  # the checked step brings every cache to exactly CTX rows
@@ -489,7 +490,14 @@ def run_ours(args, rank, world, local_rank):
     gqa_ms = sum(a.elapsed_time(b) for a, b in gqa_events) / len(gqa_events)
     gdn_ms = sum(a.elapsed_time(b) for a, b in gdn_events) / len(gdn_events) if nl else 0.0
     blocks_t = torch.tensor(blocks + [gqa_ms, gdn_ms], device=dev, dtype=torch.float64)
+    per_rank = None
     if world > 1:
+        mine_t = torch.tensor([statistics.median(blocks) / K, gqa_ms, gdn_ms], device=dev, dtype=torch.float64)
+        all_t = torch.empty(world * 3, device=dev, dtype=torch.float64)
+        dist.all_gather_into_tensor(all_t, mine_t)
+        per_rank = {"ms_per_step": [round(float(x), 4) for x in all_t[0::3]],
+                    "gqa_ms_per_launch": [round(float(x), 4) for x in all_t[1::3]],
+                    "gdn_ms_per_launch": [round(float(x), 4) for x in all_t[2::3]]}
         dist.all_reduce(blocks_t, op=dist.ReduceOp.MAX)  # every block: the slowest rank
     blocks = [float(x) for x in blocks_t[:R]]
     gqa_ms, gdn_ms = float(blocks_t[R]), float(blocks_t[R + 1])
@@ -660,6 +668,8 @@ def run_ours(args, rank, world, local_rank):
                 "min": N_LAYERS * B * K / (max(blocks) * 1e-3), "max": N_LAYERS * B * K / (min(blocks) * 1e-3),
                 "value_is": f"median of {R} timed blocks of {K} steps (CUDA events, slowest rank per block)",
                 "roofline": roofline, "e2e": e2e, "parity": parity, "gpu_launches": int(launches), "clocks": clocks}
+        if per_rank:
+            line["per_rank"] = per_rank  # device-timed, every rank's own median: the ranks run in lock step
     ctx.close()
     return line
 
@@ -850,7 +860,7 @@ def run_ragged(args, rank, world, local_rank):
     mine = shards[rank]
     n = len(mine)
     n_max = max(len(x) for x in shards)
-    R = repeats_for(K, 0.33 * max(load) / sum(lens))
+    R = args.repeats or repeats_for(K, 0.33 * max(load) / sum(lens))
     do_e2e = not args.no_e2e
     We, Re = (min(W, 3), min(R, 7)) if do_e2e else (0, 0)
     total_steps = W + R * K + We + Re * K + 1

@@ -445,8 +445,10 @@ int mfc_mla_sdpa_folded(mfc_ctx *ctx, int32_t num_heads, int32_t cache_len, floa
 /* Tuning knobs (tests and sweeps): "gdn_rows" in {0,32,64,128} state rows per
  * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a decode launch aims for when it cuts the launch's
  * KV tiles into equal runs (0 = one wave: two CTAs per SM); "gqa_chunk" forces the rows per CTA (0 = automatic); "gqa_min_rows" least rows per CTA under the automatic
- * plan (a multiple of 32, default 128); "gqa_unit_aligned" 0 = never give every (item, kv head) unit a CTA of its own
- * (default 1: done when equal-length units nearly fill the wave);
+ * plan (a multiple of 32, default 128); "gqa_unit_aligned" 1 = give every (item, kv head) unit a CTA of its own when
+ * equal-length units nearly fill the wave (default 0); "gqa_coop_merge" 0 = never launch cooperatively (default 1: a
+ * launch in which more than eight CTAs share a unit, i.e. a lone long sequence, is launched cooperatively when it
+ * fits the device, and the CTAs that share a unit merge it together);
  * "gdn_side_queue" (see mfc_join); "gqa_wait_spins" poll limit of the kernels' bounded waits (0 = default);
  * "gqa_inject_lost_load" 1 = the first CTA of the next decode launches arms the barrier of its first KV tile and
  * issues no load for it, so that its bounded wait runs out with nothing in flight (exercises the failure path

@@ -15,6 +15,7 @@ enum : unsigned {
     STATUS_TMA_TIMEOUT = 1u,
     STATUS_BAD_ITEM = 2u,
     STATUS_PEER_TIMEOUT = 4u,
+    STATUS_MERGE_TIMEOUT = 8u,
 };
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) {

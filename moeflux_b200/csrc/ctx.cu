@@ -129,6 +129,9 @@ struct mfc_ctx {
         bool connected = false;
     } xc;
     int plan_tiles_per_cta = 1, plan_total_tiles = 0;  // split of the launch being built
+    int plan_max_parts = 1;                            // most CTAs that share one unit in it
+    int coop_capacity = 0;                             // CTAs of the decode kernel the device holds at once
+    bool gqa_coop = true;                              // merge widely shared units cooperatively when possible
 
     // device staging for the host-pointer entry points (max_batch items)
     float *st_q = nullptr, *st_gate = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
@@ -150,7 +153,7 @@ struct mfc_ctx {
     size_t smem_optin = 227 * 1024;
     int gqa_forced_chunk = 0;
     int gqa_min_rows = 128;        // least cache rows per CTA
-    bool gqa_unit_aligned = true;  // one CTA per unit when equal-length units nearly fill the wave
+    bool gqa_unit_aligned = false;  // one CTA per unit when equal-length units nearly fill the wave (off: see the planner)
     long long launches = 0;
     std::string err;
 };
@@ -298,6 +301,7 @@ int check_status(mfc_ctx *c) {
         if (st & 1u) what += " a load did not arrive within the wait limit;";
         if (st & 2u) what += " an item failed its range checks;";
         if (st & 4u) what += " a peer's partials did not arrive within the wait limit;";
+        if (st & 8u) what += " the CTAs that share a unit did not all arrive within the wait limit;";
         fail(c, "a kernel gave up (device status " + std::to_string(st) + ":" + what +
                     ") the results since the last synchronisation are not valid");
         return -1;
@@ -326,9 +330,10 @@ int plan_tiles_per_cta(const mfc_ctx *c, long long total_tiles, int max_unit_til
         // by latency, not by bandwidth: it is spread over as many SMs as runs of gqa_min_rows rows allow.
         const long long w_min = c->gqa_min_rows / tile;
         if (w < w_min) w = w_min;
-        // Units of equal length that nearly fill the wave by themselves: one CTA per unit.  No unit is shared, so
-        // no partial is parked or merged and every CTA builds its query fragments once; the few idle CTA slots cost
-        // less than that (the launch is bound by HBM, not by the number of CTAs that stream).
+        // Optional (tuning "gqa_unit_aligned", off by default): units of equal length that nearly fill the wave by
+        // themselves get one CTA each.  No unit is shared, so nothing is parked or merged and every CTA builds its
+        // query fragments once.  Measured: 2 % faster on short bursts of 0.6 ms launches, 7-15 % slower on sustained
+        // 4.7 ms launches, where the SMs that hold two CTAs set the pace and fewer, longer runs lose.
         if (c->gqa_target_ctas == 0 && c->gqa_unit_aligned && n_units > 0 && min_unit_tiles == max_unit_tiles &&
             n_units <= ctas && n_units * 10 >= ctas * 7 && max_unit_tiles >= w)
             w = max_unit_tiles;
@@ -401,6 +406,7 @@ int build_gqa_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq
     }
     c->plan_tiles_per_cta = plan_tiles_per_cta(c, total_tiles, max_unit_tiles, min_unit_tiles, (long long)n * g.num_kv_heads);
     c->plan_total_tiles = (int)total_tiles;
+    c->plan_max_parts = (max_unit_tiles + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta + 1;
     const int cta = (int)((total_tiles + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta);
     if (cta + n * g.num_kv_heads > c->max_parts) {
         fail(c, "internal: split plan exceeds the scratch reserved at open");
@@ -427,6 +433,9 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
     p.tickets = c->tickets;
     p.group_tickets = c->group_tickets;
     p.n_kv_slots = c->n_kv_slots;
+    // a unit shared by many CTAs (a lone long sequence) is merged by its sharers together, which needs every CTA of
+    // the grid resident: a cooperative launch, when the grid fits the device
+    p.coop_merge = c->gqa_coop && c->plan_max_parts > MERGE_GROUP && total_ctas <= c->coop_capacity;
     p.wait_spins = c->gqa_wait_spins;
     p.inject_lost_load = c->gqa_inject_lost_load;
     p.phase_trace = (c->phase_trace_on && total_ctas <= mfc_ctx::MAX_TRACE_CTAS) ? c->phase_trace : nullptr;
@@ -824,6 +833,7 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
     if (ok && (gqa_decode_configure() != cudaSuccess || gqa_decode_f32_configure() != cudaSuccess ||
                mla_decode_configure() != cudaSuccess))
         ok = fail(c, "cannot opt in to the kernels' shared memory size");
+    if (ok) c->coop_capacity = g.kv_dtype == MFC_KV_BF16 ? gqa_decode_bf16_coop_capacity() : gqa_decode_f32_coop_capacity();
     if (!ok) {
         g_open_error = c->err;
         free_all(c);
@@ -1313,6 +1323,8 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
     } else if (!strcmp(key, "gqa_min_rows")) {
         if (value < 32 || value % 32) return -1;
         c->gqa_min_rows = value;
+    } else if (!strcmp(key, "gqa_coop_merge")) {
+        c->gqa_coop = value != 0;
     } else if (!strcmp(key, "gqa_unit_aligned")) {
         c->gqa_unit_aligned = value != 0;
     } else if (!strcmp(key, "gqa_wait_spins")) {
@@ -2317,6 +2329,7 @@ int mfc_sdpa(mfc_ctx *c, int32_t kv_len, const float *q, const float *q_gate, co
         const int nt = (kv_len + tile - 1) / tile;
         c->plan_total_tiles = nt * g.num_kv_heads;
         c->plan_tiles_per_cta = plan_tiles_per_cta(c, c->plan_total_tiles, nt);
+        c->plan_max_parts = (nt + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta + 1;
     }
     GqaParams p;
     fill_gqa_params(c, p, 1, (c->plan_total_tiles + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta);

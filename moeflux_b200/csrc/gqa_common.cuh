@@ -85,6 +85,8 @@ struct Located {
     int part_idx;  // this CTA's rank among them
     int slot0;     // scratch slot of the unit's first partial
     bool bad;      // the item failed its range checks: the unit is skipped (its tickets are still taken)
+    bool last_goes_on;  // the unit's last sharer continues with another unit after it (it takes no part in a
+                        //   cooperative merge: it must not wait in the middle of its run)
 };
 
 constexpr int LOCATE_SMEM_ITEMS = 512;
@@ -122,6 +124,7 @@ __device__ __forceinline__ Located locate_tile(const GqaParams &p, int gt, int g
     const int first_cta = tb_u / p.tiles_per_cta, last_cta = (tb_u + nt - 1) / p.tiles_per_cta;
     L.n_parts = last_cta - first_cta + 1;
     L.part_idx = (int)blockIdx.x - first_cta;
+    L.last_goes_on = tb_u + nt < min((last_cta + 1) * p.tiles_per_cta, p.total_tiles);
     // (unit index + CTA index) grows strictly along the tile sequence: a unique slot per pair
     L.slot0 = lo * p.Hkv + L.kvh + first_cta;
     // what the kernel indexes memory with must lie inside the caches and the input arrays
@@ -264,6 +267,102 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
     }
 }
 
+// Cooperative merge of a unit shared by many CTAs (a lone long sequence: up to MAX_UNIT_PARTS partials per unit).
+// Launched cooperatively, so every CTA of the grid is resident and a CTA may wait for the others.  Each sharer
+// parks its partial and takes the unit's ticket; the sharers whose segment ends their run (all but a last sharer
+// that goes on to another unit) wait until all tickets are taken and then each merges a slice of the output: slice
+// unit = (head, 64 output dims), dealt round-robin over the merging CTAs.  Per slice unit the 128 threads are 8 rows
+// of partials x 16 lanes of four dims; the loads of all partials of the slice are in flight together with the loads
+// of their (m, l), so the whole merge is one round trip to L2 instead of one per group of partials.
+//   s_w: 2 * MAX_UNIT_PARTS floats (m, then l), s_tmp: 8 * 64 floats.
+__device__ __forceinline__ void merge_unit_slices(const GqaParams &p, const Located &L, size_t slot0, int n_parts,
+                                                  int n_mergers, int my_idx, float *s_w, float *s_tmp) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int l16 = tid & 15, prow = tid >> 4;
+    const int group = p.group;
+    const size_t head0 = (size_t)L.it.in_idx * p.H + (size_t)L.kvh * group;
+    float *s_m = s_w, *s_l = s_w + MAX_UNIT_PARTS;
+    PartialDst pd;
+    if (p.partial_mode) pd = partial_dst(p, L.it.in_idx);
+    constexpr int ROWS_PER_THREAD = 16;  // partial rows a thread holds per batch (8 rows of threads: 128 partials)
+    for (int su = my_idx; su < group * 4; su += n_mergers) {
+        const int hr = su >> 2, j = su & 3;
+        float4 o4[ROWS_PER_THREAD];
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_THREAD; i++) {
+            const int c = prow + 8 * i;
+            o4[i] = c < n_parts ? *reinterpret_cast<const float4 *>(p.sc_o + ((slot0 + c) * 16 + hr) * HEAD_DIM + 64 * j + 4 * l16)
+                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        for (int c = tid; c < n_parts; c += 128) {
+            s_m[c] = p.sc_m[(slot0 + c) * 16 + hr];
+            s_l[c] = p.sc_l[(slot0 + c) * 16 + hr];
+        }
+        float2 gt2 = make_float2(0.0f, 0.0f);  // gate logits of the dims this thread finishes (threads 0..31: 2 each)
+        if (!p.partial_mode && p.gate && tid < 32)
+            gt2 = *reinterpret_cast<const float2 *>(p.gate + (head0 + hr) * (size_t)p.gate_row_stride + 64 * j + 2 * tid);
+        __syncthreads();
+        // every warp forms M and L for the head (the same values in all four)
+        float M = -INFINITY;
+        for (int c = lane; c < n_parts; c += 32) M = fmaxf(M, s_m[c]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float Ls = 0.0f;
+        for (int c = lane; c < n_parts; c += 32) Ls += (s_m[c] == -INFINITY ? 0.0f : expf(s_m[c] - M)) * s_l[c];
+        Ls = warp_sum(Ls);
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int b0 = 0; b0 < n_parts; b0 += 8 * ROWS_PER_THREAD) {
+            if (b0 > 0) {  // further batches of 128 partials (units shared by more than 128 CTAs)
+#pragma unroll
+                for (int i = 0; i < ROWS_PER_THREAD; i++) {
+                    const int c = b0 + prow + 8 * i;
+                    o4[i] = c < n_parts ? *reinterpret_cast<const float4 *>(p.sc_o + ((slot0 + c) * 16 + hr) * HEAD_DIM + 64 * j + 4 * l16)
+                                        : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < ROWS_PER_THREAD; i++) {
+                const int c = b0 + prow + 8 * i;
+                if (c >= n_parts) break;
+                const float w = s_m[c] == -INFINITY ? 0.0f : expf(s_m[c] - M);
+                acc.x = fmaf(w, o4[i].x, acc.x);
+                acc.y = fmaf(w, o4[i].y, acc.y);
+                acc.z = fmaf(w, o4[i].z, acc.z);
+                acc.w = fmaf(w, o4[i].w, acc.w);
+            }
+        }
+        *reinterpret_cast<float4 *>(s_tmp + prow * 64 + 4 * l16) = acc;
+        __syncthreads();
+        if (tid < 32) {  // two dims per thread: sum over the 8 rows of threads, in row order
+            float2 r = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const float2 v = *reinterpret_cast<const float2 *>(s_tmp + k * 64 + 2 * tid);
+                r.x += v.x;
+                r.y += v.y;
+            }
+            if (p.partial_mode) {
+                const int hl = L.kvh * group + hr;
+                *reinterpret_cast<float2 *>(pd.o + (size_t)hl * HEAD_DIM + 64 * j + 2 * tid) = r;
+                if (tid == 0 && j == 0) {
+                    pd.m[hl] = M;
+                    pd.l[hl] = Ls;
+                }
+            } else {
+                const float inv = 1.0f / Ls;
+                r.x *= inv;
+                r.y *= inv;
+                if (p.gate) {
+                    r.x *= 1.0f / (1.0f + expf(-gt2.x));
+                    r.y *= 1.0f / (1.0f + expf(-gt2.y));
+                }
+                *reinterpret_cast<float2 *>(p.out + (head0 + hr) * HEAD_DIM + 64 * j + 2 * tid) = r;
+            }
+        }
+        __syncthreads();  // s_m / s_l / s_tmp are reused by the next slice unit
+    }
+}
+
 // Epilogue shared by both kernels.  The warp layout of the accumulators is:
 // o[nt][2x + e] = row (g + 8x), dim 64*warp + 8*nt + 2t + e;  m_r / l_r per row
 // (l_r still split over the four lanes of a row).
@@ -319,10 +418,11 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
     }
 
     // The unit is shared: park the partial; the last CTA to arrive merges.  Up to MERGE_GROUP partials are merged in
-    // one level.  Beyond that the partials form groups of MERGE_GROUP consecutive ones: the last arriver of a group
+    // one level.  Beyond that, in a cooperative launch, the sharers merge together (merge_unit_slices); in an
+    // ordinary launch the partials form groups of MERGE_GROUP consecutive ones: the last arriver of a group
     // merges it into the group's first slot (many groups merge side by side on different SMs), then arrives at the
-    // unit's ticket, and the last group to arrive merges the group results.  Nothing ever spins: a CTA that is not
-    // last simply leaves.  A CTA that gave up on its loads still takes its tickets, so that the counters return to
+    // unit's ticket, and the last group to arrive merges the group results.  In an ordinary launch nothing ever
+    // spins: a CTA that is not last simply leaves.  A CTA that gave up on its loads still takes its tickets, so that the counters return to
     // zero for the next launch; what it would have merged is not merged (the status word says so to the host).
     const size_t slot0 = (size_t)L.slot0;  // first slot of the unit
     const size_t slot = slot0 + L.part_idx;
@@ -341,10 +441,45 @@ __device__ __forceinline__ void finish_unit(const GqaParams &p, const Located &L
             }
         }
     }
+    unsigned *unit_ticket = p.tickets + (size_t)L.item_idx * p.Hkv + L.kvh;
+    if (p.coop_merge && L.n_parts > MERGE_GROUP) {
+        // cooperative launch: the sharers that are at the end of their run merge the unit together (see above)
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) atomicAdd(unit_ticket, 1u);
+        const bool merger = !(L.last_goes_on && L.part_idx == L.n_parts - 1);
+        if (!merger) return;
+        const int n_mergers = L.n_parts - (L.last_goes_on ? 1 : 0);
+        if (tid == 0) {
+            bool seen = false;
+            const unsigned limit = p.wait_spins ? p.wait_spins : (1u << 22);
+            for (unsigned i = 0; i < limit && !seen; i++) {
+                unsigned v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(unit_ticket) : "memory");
+                seen = v >= (unsigned)L.n_parts;
+                if (!seen) __nanosleep(200);
+            }
+            *s_flag_p = seen;
+            if (!seen) atomicOr(p.status, STATUS_MERGE_TIMEOUT);
+        }
+        __syncthreads();
+        if (!*s_flag_p) return;  // the host clears the counters when it reads the status
+        __threadfence();
+        if (!abandoned) merge_unit_slices(p, L, slot0, L.n_parts, n_mergers, L.part_idx, s_w, s_tmp);
+        __syncthreads();
+        if (tid == 0) {  // the last merger to finish puts both counters back to zero for the next launch
+            unsigned *done = p.group_tickets + slot0;
+            const unsigned prev = atomicAdd(done, 1u);
+            if (prev == (unsigned)(n_mergers - 1)) {
+                *done = 0u;
+                *unit_ticket = 0u;
+            }
+        }
+        return;
+    }
     const bool two_level = L.n_parts > MERGE_GROUP;
     const int gi = L.part_idx / MERGE_GROUP;
     const int n_groups = (L.n_parts + MERGE_GROUP - 1) / MERGE_GROUP;
-    unsigned *unit_ticket = p.tickets + (size_t)L.item_idx * p.Hkv + L.kvh;
     __threadfence();
     __syncthreads();
     if (two_level) {

@@ -378,8 +378,23 @@ cudaError_t gqa_decode_f32_configure() {
 cudaError_t launch_gqa_decode_f32(const CUtensorMap &kmap, const CUtensorMap &vmap,
                                   const GqaParams &p, cudaStream_t stream) {
     if (p.total_ctas <= 0) return cudaSuccess;
+    if (p.coop_merge) {
+        // every CTA resident at once: CTAs that share a unit may wait for one another (merge_unit_slices)
+        void *args[] = {const_cast<CUtensorMap *>(&kmap), const_cast<CUtensorMap *>(&vmap), const_cast<GqaParams *>(&p)};
+        return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(gqa_decode_f32_kernel), dim3(p.total_ctas), dim3(128), args, F32_SMEM, stream);
+    }
     gqa_decode_f32_kernel<<<p.total_ctas, 128, F32_SMEM, stream>>>(kmap, vmap, p);
     return cudaGetLastError();
+}
+
+int gqa_decode_f32_coop_capacity() {
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gqa_decode_f32_kernel, 128, F32_SMEM) != cudaSuccess)
+        return 0;
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    return coop ? sms * per_sm : 0;
 }
 
 }  // namespace mfc

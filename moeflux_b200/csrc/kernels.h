@@ -102,6 +102,8 @@ struct GqaParams {
     int n_seqs;              // kv_slot / n_seqs = full-layer index of an item
     float norm_eps;
     int n_kv_slots;          // items are checked against it (kv_slot) and against cap_rows (local_len, append_row)
+    int coop_merge;          // 1: the launch is cooperative (every CTA resident): units shared by more than
+                             //    MERGE_GROUP CTAs are merged by their sharers together (they wait for one another)
     // Diagnostics (all off by default):
     unsigned wait_spins;     // poll limit of the bounded mbarrier waits; 0 = default
     int inject_lost_load;    // 1: CTA 0 arms the barrier of its first tile and issues no load for it, so that its
@@ -126,6 +128,10 @@ cudaError_t launch_gqa_decode_f32(const CUtensorMap &kmap, const CUtensorMap &vm
 // one-time opt-in to large dynamic shared memory
 cudaError_t gqa_decode_configure();
 cudaError_t gqa_decode_f32_configure();
+// CTAs of the decode kernel that the current device holds at once (0 when it cannot launch cooperatively): the
+// largest grid that may be launched with GqaParams::coop_merge.  Call after the configure function.
+int gqa_decode_bf16_coop_capacity();
+int gqa_decode_f32_coop_capacity();
 
 // Merge of gathered partials.  Part r of o/m/l starts part_stride floats after
 // part r-1; part_stride 0 means densely packed [n_parts][n][H][256] / [n_parts][n][H].

@@ -56,14 +56,18 @@ def test_config0_fp32_ctx4096_single_step():
     ctx.close()
 
 
+@pytest.mark.parametrize("coop", [1, 0])
 @pytest.mark.parametrize("bf16", [False, True])
-def test_ctx32768_single_step(bf16):
-    """The target shape: one sequence at context 32768.  A lone sequence is cut into 128 partials per kv head
-    (two-level merge: sixteen groups of eight)."""
-    ctx, orc = make_pair(G4, max_seq=32768, kv_bf16=bf16, linear_layers=[])
+def test_ctx32768_single_step(bf16, coop):
+    """The target shape: one sequence at context 32768.  A lone sequence is cut into well over a hundred partials per
+    kv head: merged by the CTAs that share the unit together in a cooperative launch (coop=1), or in two levels of
+    last-arriver merges in an ordinary one (coop=0)."""
+    ctx, orc = make_pair(G4, max_seq=32768 + 4, kv_bf16=bf16, linear_layers=[])
+    ctx.set_tuning("gqa_coop_merge", coop)
     r = I.rng(32768 + bf16)
     install_kv(ctx, orc, FULL, 0, I.normal(r, (32767, G4.kv_dim)), I.normal(r, (32767, G4.kv_dim)))
-    one_step(ctx, orc, 0, 32768, r, TOL_BF16 if bf16 else TOL_F32)
+    for step in range(3):  # three launches in a row: the merge counters of one are back at zero for the next
+        one_step(ctx, orc, 0, 32768 + step, r, TOL_BF16 if bf16 else TOL_F32)
     ctx.check_guards()
     ctx.close()
 
@@ -103,16 +107,19 @@ def test_ragged_batch_of_16_automatic_plan(bf16):
     ctx.close()
 
 
-@pytest.mark.parametrize("lens", [(20000, 9000, 31000), (5000,), (300, 32000)])
-def test_units_shared_by_many_ctas(lens):
-    """Few long sequences: every (item, kv head) unit is shared by far more than sixteen CTAs, the last merge group
-    of a unit is partly filled, and run boundaries fall inside units."""
+@pytest.mark.parametrize("coop", [1, 0])
+@pytest.mark.parametrize("lens", [(20000, 9000, 31000), (5000,), (300, 32000), (2500, 40, 2500, 7)])
+def test_units_shared_by_many_ctas(lens, coop):
+    """Few long sequences: every (item, kv head) unit is shared by far more than sixteen CTAs, run boundaries fall
+    inside units (a unit's last sharer goes on to the next unit and takes no part in a cooperative merge), short
+    units sit between long ones, and the last merge group of a unit is partly filled."""
     n = len(lens)
     ctx, orc = make_pair(G4, max_seq=32768 + 8, n_seqs=n, kv_bf16=True, linear_layers=[])
+    ctx.set_tuning("gqa_coop_merge", coop)
     r = I.rng(1700 + n)
     for s, ln in enumerate(lens):
         install_kv(ctx, orc, FULL, s, I.normal(r, (ln, G4.kv_dim)), I.normal(r, (ln, G4.kv_dim)))
-    for step in range(2):
+    for step in range(3):
         ins = [I.gqa_step_inputs(r, G4) for _ in range(n)]
         pos = [ln + step for ln in lens]
         got = ctx.full_attn_step_batched([FULL] * n, list(range(n)), pos, np.stack([i[0] for i in ins]),
