@@ -53,7 +53,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")
     ap.add_argument("--batch", type=int, default=8, help="sequences")
-    ap.add_argument("--workload", default="stack", choices=["stack", "ragged", "prefill", "matvec"],
+    ap.add_argument("--trace-world", type=int, default=8, help="--workload trace: the KV split whose per-rank launch is traced")
+    ap.add_argument("--workload", default="stack", choices=["stack", "ragged", "prefill", "matvec", "trace"],
                     help="stack: the decode stack (headline); ragged: 64 sequences of ragged context, one full-attention "
                          "layer-step each, sharded by sequence; prefill: 8192-token chunked prefill of one hybrid block; "
                          "matvec: the 4-bit projections around the attention sub-blocks of one hybrid block")
@@ -67,6 +68,9 @@ def parse_args():
     ap.add_argument("--repeats", type=int, default=0, help="timed blocks of --steps steps (0: at least 7 and about a second)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-single-step", action="store_true", help="skip the batch-1 single-step latencies (N=1, stack)")
+    ap.add_argument("--other-configs", type=int, default=0,
+                    help="1: the stack line also carries compact lines of the ragged workload (every N) and of the "
+                         "prefill workload (N=1), each run with --steps")
     return ap.parse_args()
 
 
@@ -670,6 +674,8 @@ def run_ours(args, rank, world, local_rank):
                 "roofline": roofline, "e2e": e2e, "parity": parity, "gpu_launches": int(launches), "clocks": clocks}
         if per_rank:
             line["per_rank"] = per_rank  # device-timed, every rank's own median: the ranks run in lock step
+    if world > 1:
+        dist.barrier()  # no rank unmaps its peers' buffers while another may still use them
     ctx.close()
     return line
 
@@ -758,6 +764,121 @@ def single_step_latencies(local_rank=0, calls=1000):
     out["how"] = (f"CUDA events over {calls} pipelined device-pointer calls, one (layer, sequence) item each, rotating over "
                   f"sequences whose caches or states together exceed the L2 several times")
     return out
+
+
+# --------------------------------------------------------------------------- per-CTA phase trace of the decode launch
+def run_trace(args):
+    """Where a decode launch spends its time, from the kernel's own per-CTA time stamps (tuning "gqa_phase_trace":
+    %globaltimer at kernel start, first segment's query fragments ready, its last KV tile consumed, its epilogue done,
+    CTA done).  Cases: the stack's full-attention launch as one rank of an N-way KV split sees it (--trace-world N,
+    emulated on this GPU by a context that holds rank 0's rows), and a lone sequence at ctx 4096 (fp32) and 32768
+    (bf16, fp32).  Prints one JSON line."""
+    import torch
+
+    import moeflux_b200 as M
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cases = []
+
+    def summarise(name, ctx, us_per_launch, alg_bytes):
+        tr = ctx.read_phase_trace().astype(np.int64)
+        d = (tr[:, :5] - tr[:, 0].min()) / 1e3
+        med = lambda x: float(np.median(x))
+        cases.append({"case": name, "ctas": int(len(tr)), "us_per_launch_events": us_per_launch,
+                      "GBps": alg_bytes / us_per_launch / 1e3 if us_per_launch else None,
+                      "span_us": float(d[:, 4].max()), "start_spread_us": float(d[:, 0].max()),
+                      "prologue_us": {"median": med(d[:, 1] - d[:, 0]), "max": float((d[:, 1] - d[:, 0]).max())},
+                      "first_segment_stream_us": {"median": med(d[:, 2] - d[:, 1]), "max": float((d[:, 2] - d[:, 1]).max())},
+                      "first_segment_epilogue_us": {"median": med(d[:, 3] - d[:, 2]), "max": float((d[:, 3] - d[:, 2]).max())},
+                      "cta_total_us": {"median": med(d[:, 4] - d[:, 0]), "min": float((d[:, 4] - d[:, 0]).min()),
+                                       "max": float((d[:, 4] - d[:, 0]).max())},
+                      "last_stream_end_us": float(d[:, 2].max())})
+
+    # (a) the stack's launch as one rank of a --trace-world split sees it
+    world, B, CTX = args.trace_world, args.batch, args.ctx
+    ctx = M.Ctx(max_seq=CTX, n_seqs=B, kv_dtype=M.KV_BF16, kv_rank=0, kv_world=world, kv_block=256, max_batch=N_LAYERS * B)
+    st = torch.cuda.Stream(device=dev)
+    ctx.set_stream(st.cuda_stream)
+    L0 = CTX - 64
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    with torch.cuda.stream(st):
+        kr, vr = torch.randn(8192, KV_DIM, device=dev, generator=g), torch.randn(8192, KV_DIM, device=dev, generator=g)
+        for layer in FULL_LAYERS:
+            for s_ in range(B):
+                for p0 in range(0, L0, 8192):
+                    ctx.kv_append_rows_dev(layer, s_, p0, min(8192, L0 - p0), kr.data_ptr(), vr.data_ptr())
+        st.synchronize()
+    items = [(l, s_) for s_ in range(B) for l in FULL_LAYERS]
+    ng = len(items)
+    layers, seqs = np.array([l for l, _ in items], np.int32), np.array([s_ for _, s_ in items], np.int32)
+    q, kk, vv = (torch.randn(ng, n, device=dev, generator=g) for n in (Q_DIM, KV_DIM, KV_DIM))
+    gate, out = torch.randn(ng, Q_DIM, device=dev, generator=g), torch.empty(ng, Q_DIM, device=dev)
+    send = torch.empty(ng * (H * D + 2 * H), device=dev)
+    pos = [L0]
+
+    def step():
+        p_ = np.full(ng, pos[0], np.int32)
+        if world > 1:
+            ctx.full_attn_partial_packed_dev(layers, seqs, p_, q.data_ptr(), kk.data_ptr(), vv.data_ptr(), send.data_ptr())
+        else:
+            ctx.full_attn_step_batched_dev(layers, seqs, p_, q.data_ptr(), gate.data_ptr(), kk.data_ptr(), vv.data_ptr(),
+                                           out.data_ptr())
+        pos[0] += 1
+
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(20):
+            step()
+        e1.record(st)
+        st.synchronize()
+        ctx.set_tuning("gqa_phase_trace", 1)
+        step()
+        st.synchronize()
+    summarise(f"stack launch, 120 items, one rank of a {world}-way KV split (ctx {CTX}, bf16)", ctx,
+              e0.elapsed_time(e1) / 20 * 1e3, ng * gqa_bytes_per_item(pos[0] / world, 2))
+    ctx.close()
+
+    # (b) a lone sequence: the launch is a latency problem
+    for ctx_len, bf16, n_seqs in ((4096, False, 32), (32768, True, 8), (32768, False, 8)):
+        c = M.Ctx(num_layers=4, max_seq=ctx_len + 200, n_seqs=n_seqs, kv_dtype=M.KV_BF16 if bf16 else M.KV_F32, max_batch=4)
+        st = torch.cuda.Stream(device=dev)
+        c.set_stream(st.cuda_stream)
+        with torch.cuda.stream(st):
+            for s_ in range(n_seqs):
+                for p0 in range(0, ctx_len - 1, 8192):
+                    c.kv_append_rows_dev(3, s_, p0, min(8192, ctx_len - 1 - p0), kr.data_ptr(), vr.data_ptr())
+            st.synchronize()
+        lens = [ctx_len - 1] * n_seqs
+
+        def call(i):
+            s_ = i % n_seqs
+            c.full_attn_step_batched_dev([3], [s_], [lens[s_]], q.data_ptr(), gate.data_ptr(), kk.data_ptr(),
+                                         vv.data_ptr(), out.data_ptr())
+            lens[s_] += 1
+
+        with torch.cuda.stream(st):
+            for i in range(n_seqs):
+                call(i)
+            st.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n = 64 * n_seqs
+            e0.record(st)
+            for i in range(n):
+                call(i)
+            e1.record(st)
+            st.synchronize()
+            c.set_tuning("gqa_phase_trace", 1)
+            call(0)
+            st.synchronize()
+        summarise(f"one sequence, ctx {ctx_len}, {'bf16' if bf16 else 'fp32'} KV", c, e0.elapsed_time(e1) / n * 1e3,
+                  gqa_bytes_per_item(ctx_len, 2 if bf16 else 4))
+        c.close()
+    return {"workload": "phase trace of the decode launch (%globaltimer stamps written by the kernel)", "cases": cases}
 
 
 # --------------------------------------------------------------------------- ragged batch, sharded by sequence
@@ -1248,6 +1369,17 @@ def run_matvec(args):
     return line
 
 
+def compact(line):
+    """The fields of a workload's line that matter when it rides along in another line."""
+    if not line:
+        return None
+    r = line.get("roofline") or {}
+    return {"metric": line["metric"], "value": line["value"], "unit": line["unit"], "ms_per_step": line["ms_per_step"],
+            "steps": line["steps"], "repeats": line.get("repeats"), "config": line["config"].get("workload"),
+            "roofline": {k: r.get(k) for k in ("bound", "kernel", "achieved", "peak", "unit", "frac", "ms_per_launch")},
+            "e2e": (line.get("e2e") or {}).get("value"), "parity": line.get("parity")}
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -1275,7 +1407,16 @@ def main():
         if rank == 0:
             print(json.dumps(run_matvec(args)), flush=True)
         return
+    if args.workload == "trace":
+        if rank == 0:
+            print(json.dumps(run_trace(args)), flush=True)
+        return
     line = run_ragged(args, rank, world, local_rank) if args.workload == "ragged" else run_ours(args, rank, world, local_rank)
+    others = {}
+    if args.workload == "stack" and args.other_configs:
+        others["ragged (configuration 2)"] = compact(run_ragged(args, rank, world, local_rank))
+        if world == 1:
+            others["prefill (configuration 3)"] = compact(run_prefill(args))
     failed = False
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
@@ -1287,8 +1428,11 @@ def main():
             line["cpu_baseline"] = {"value": v, "unit": "layer-steps/s", "cores": cores, "kind": kind, "sample": desc}
         if world == 1 and args.workload == "stack" and not args.no_single_step:
             line["roofline"]["single_step"] = single_step_latencies(local_rank)
+        if others:
+            line["other_configs"] = others
         print(json.dumps(line), flush=True)
-        failed = bool(line.get("parity")) and not line["parity"]["ok"]
+        failed = (bool(line.get("parity")) and not line["parity"]["ok"]) or any(
+            o and o.get("parity") and not o["parity"]["ok"] for o in others.values())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

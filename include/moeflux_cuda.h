@@ -445,7 +445,7 @@ int mfc_mla_sdpa_folded(mfc_ctx *ctx, int32_t num_heads, int32_t cache_len, floa
 /* Tuning knobs (tests and sweeps): "gdn_rows" in {0,32,64,128} state rows per
  * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a decode launch aims for when it cuts the launch's
  * KV tiles into equal runs (0 = one wave: two CTAs per SM); "gqa_chunk" forces the rows per CTA (0 = automatic); "gqa_min_rows" least rows per CTA under the automatic
- * plan (a multiple of 32, default 128); "gqa_unit_aligned" 1 = give every (item, kv head) unit a CTA of its own when
+ * plan (a multiple of 32, default 64); "gqa_unit_aligned" 1 = give every (item, kv head) unit a CTA of its own when
  * equal-length units nearly fill the wave (default 0); "gqa_coop_merge" 0 = never launch cooperatively (default 1: a
  * launch in which more than eight CTAs share a unit, i.e. a lone long sequence, is launched cooperatively when it
  * fits the device, and the CTAs that share a unit merge it together);
@@ -483,7 +483,7 @@ int mfc_read_phase_trace(mfc_ctx *ctx, unsigned long long *out, int32_t max_ctas
  * per GPU, each context computes un-normalised partials for all items and every item is finished on one rank (the
  * owner of its sequence).  Instead of writing the partials locally and handing them to a collective, the decode
  * kernel stores each merged partial block [o | m | l] straight into the receive buffer of the owner through a
- * peer-mapped pointer (plain stores over NVLink; no multicast, no TMA from or to peer memory), and its last CTA
+ * peer-mapped pointer (plain stores over NVLink: nothing else touches peer memory), and its last CTA
  * publishes a step number in every peer's flag array once the stores are visible.  The owner's merge kernel waits
  * (bounded) for the step number of every rank, merges by log-sum-exp and applies the gate.  Receive buffers are
  * double-buffered by step parity, which is enough: a rank cannot start step s+2 before every peer has merged step s.

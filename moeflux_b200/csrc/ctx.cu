@@ -152,7 +152,7 @@ struct mfc_ctx {
     int n_sms = 148;
     size_t smem_optin = 227 * 1024;
     int gqa_forced_chunk = 0;
-    int gqa_min_rows = 128;        // least cache rows per CTA
+    int gqa_min_rows = 64;         // least cache rows per CTA
     bool gqa_unit_aligned = false;  // one CTA per unit when equal-length units nearly fill the wave (off: see the planner)
     long long launches = 0;
     std::string err;

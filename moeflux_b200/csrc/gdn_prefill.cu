@@ -44,15 +44,15 @@ constexpr int DVC = 64;         // value rows per CTA
 constexpr int LDK = GDN_DIM + 8;  // padded leading dim (bf16) of [.][128] operand tiles
 
 // ------------------------------------------------------------------ 1. conv / norm / gates
-// grid (ceil(T / CONV_TT), conv_dim / 2048), 256 threads: a thread owns 8 consecutive channels of
-// CONV_TT consecutive tokens (16-byte loads of the input rows of the sliding window and of the
-// weights).  A q or k head is 128 channels = 16 neighbouring lanes, reduced by shuffles.
-// Block y == 0 also computes the per-head gates.  The kernel is bound by instruction issue
-// (SiLU) about as much as by memory, so SiLU uses ex2.approx and an approximate division
-// (the results feed bf16 operands), and one token per thread wins over input reuse: four
-// tokens per thread halved the threads in flight and took 319 us against 225 us.
-constexpr int CONV_TT = 1;
-__global__ void __launch_bounds__(256)
+// grid (ceil(T / CONV_TT), conv_dim / 2048), 256 threads: a thread owns 8 consecutive channels and walks CONV_TT
+// consecutive tokens with the three previous input rows in registers, so every input row is loaded once (one
+// 16-byte load per token and thread, eight of them in flight) and the taps once per CONV_TT tokens.  (The first
+// version gave every thread one token: four row loads and a re-read of the taps per token, 225 us for 8192 tokens.)
+// A q or k head is 128 channels = 16 neighbouring lanes, reduced by shuffles.  Block y == 0 also computes the
+// per-head gates.  SiLU uses ex2.approx and an approximate division (the results feed bf16 operands).
+constexpr int CONV_TT = 32;
+constexpr int CONV_UNROLL = 8;
+__global__ void __launch_bounds__(256, 2)
 gdn_prefill_conv_kernel(const __nv_bfloat16 *x, const __nv_bfloat16 *alpha, const __nv_bfloat16 *beta,
                         float *ring, int slot0, const uint16_t *conv_w, const float *a_log,
                         const uint16_t *dt_bias, __nv_bfloat16 *q_hat, __nv_bfloat16 *k_hat, float *v_out,
@@ -61,26 +61,29 @@ gdn_prefill_conv_kernel(const __nv_bfloat16 *x, const __nv_bfloat16 *alpha, cons
     const int c0 = (blockIdx.y * 256 + tid) * 8;
     const int total_key = Hk * GDN_DIM;
     const bool in_c = c0 < conv_dim;
-    float xr[CONV_TT + 3][8];  // rows t0-3 .. t0+3
-    float wf[8][4];            // taps of the 8 channels
+    const int t_end = min(t0 + CONV_TT, T);
+    float win[3][8];  // the rows before the current token: win[0] is the oldest
+    float wf[8][4];   // taps of the 8 channels
+    auto unpack = [](const uint4 &raw, float (&dst)[8]) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int k = 0; k < CONV_TT + 3; k++) {
+        for (int e = 0; e < 4; e++) {
+            dst[2 * e] = bf16_bits_to_f32((uint16_t)(w[e] & 0xffffu));
+            dst[2 * e + 1] = bf16_bits_to_f32((uint16_t)(w[e] >> 16));
+        }
+    };
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
         const int tt = t0 - 3 + k;
 #pragma unroll
-        for (int e = 0; e < 8; e++) xr[k][e] = 0.0f;
-        if (in_c && tt < T) {
+        for (int e = 0; e < 8; e++) win[k][e] = 0.0f;
+        if (in_c) {
             if (tt >= 0) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(x + (size_t)tt * conv_dim + c0);
-                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    xr[k][2 * e] = bf16_bits_to_f32((uint16_t)(w[e] & 0xffffu));
-                    xr[k][2 * e + 1] = bf16_bits_to_f32((uint16_t)(w[e] >> 16));
-                }
+                unpack(*reinterpret_cast<const uint4 *>(x + (size_t)tt * conv_dim + c0), win[k]);
             } else {  // history row from the ring: token -1 sits in slot0-1, etc.
                 const float *hr = ring + (size_t)((slot0 + tt) & 3) * conv_dim + c0;
 #pragma unroll
-                for (int e = 0; e < 8; e++) xr[k][e] = hr[e];
+                for (int e = 0; e < 8; e++) win[k][e] = hr[e];
             }
         }
     }
@@ -98,48 +101,60 @@ gdn_prefill_conv_kernel(const __nv_bfloat16 *x, const __nv_bfloat16 *alpha, cons
         }
     }
     const bool is_qk = c0 < 2 * total_key, is_q = c0 < total_key;
+    const float inv_scale = 1.0f / sqrtf((float)GDN_DIM);
+    for (int tb = t0; tb < t_end; tb += CONV_UNROLL) {  // uniform over the block
+        uint4 raw[CONV_UNROLL];
 #pragma unroll
-    for (int tt = 0; tt < CONV_TT; tt++) {
-        const int t = t0 + tt;
-        if (t >= T) break;  // uniform over the block
-        float y[8];
-        float ss = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 8; e++) {
-            float acc = fmaf(xr[tt][e], wf[e][0], 0.0f);
-            acc = fmaf(xr[tt + 1][e], wf[e][1], acc);
-            acc = fmaf(xr[tt + 2][e], wf[e][2], acc);
-            acc = fmaf(xr[tt + 3][e], wf[e][3], acc);
-            y[e] = __fdividef(acc, 1.0f + __expf(-acc));
-            ss += y[e] * y[e];
+        for (int u = 0; u < CONV_UNROLL; u++) {
+            raw[u] = make_uint4(0, 0, 0, 0);
+            if (in_c && tb + u < t_end) raw[u] = *reinterpret_cast<const uint4 *>(x + (size_t)(tb + u) * conv_dim + c0);
         }
-        // q or k: normalise over the head (16 lanes x 8 channels); every lane takes part in the shuffles
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (!in_c) continue;
-        if (is_qk) {
-            const float inv_scale = 1.0f / sqrtf((float)GDN_DIM);
-            const float inv = 1.0f / sqrtf(ss / (float)GDN_DIM + 1e-6f);
-            const int cc = is_q ? c0 : c0 - total_key;
-            uint32_t pk[4];
+        for (int u = 0; u < CONV_UNROLL; u++) {
+            const int t = tb + u;
+            if (t >= t_end) break;
+            float cur[8], y[8];
+            unpack(raw[u], cur);
+            float ss = 0.0f;
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float a0 = is_q ? y[2 * e] * inv * inv_scale * inv_scale : y[2 * e] * inv * inv_scale;
-                const float a1 = is_q ? y[2 * e + 1] * inv * inv_scale * inv_scale : y[2 * e + 1] * inv * inv_scale;
-                pk[e] = pack_bf16x2(a0, a1);
+            for (int e = 0; e < 8; e++) {
+                float acc = fmaf(win[0][e], wf[e][0], 0.0f);
+                acc = fmaf(win[1][e], wf[e][1], acc);
+                acc = fmaf(win[2][e], wf[e][2], acc);
+                acc = fmaf(cur[e], wf[e][3], acc);
+                y[e] = __fdividef(acc, 1.0f + __expf(-acc));
+                ss += y[e] * y[e];
+                win[0][e] = win[1][e];
+                win[1][e] = win[2][e];
+                win[2][e] = cur[e];
             }
-            __nv_bfloat16 *dst = (is_q ? q_hat : k_hat) + (size_t)t * total_key + cc;
-            *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        } else {
-            float *dst = v_out + (size_t)t * Hv * GDN_DIM + (c0 - 2 * total_key);
-            *reinterpret_cast<float4 *>(dst) = make_float4(y[0], y[1], y[2], y[3]);
-            *reinterpret_cast<float4 *>(dst + 4) = make_float4(y[4], y[5], y[6], y[7]);
+            // q or k: normalise over the head (16 lanes x 8 channels); every lane takes part in the shuffles
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (!in_c) continue;
+            if (is_qk) {
+                const float inv = 1.0f / sqrtf(ss / (float)GDN_DIM + 1e-6f);
+                const int cc = is_q ? c0 : c0 - total_key;
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float a0 = is_q ? y[2 * e] * inv * inv_scale * inv_scale : y[2 * e] * inv * inv_scale;
+                    const float a1 = is_q ? y[2 * e + 1] * inv * inv_scale * inv_scale : y[2 * e + 1] * inv * inv_scale;
+                    pk[e] = pack_bf16x2(a0, a1);
+                }
+                __nv_bfloat16 *dst = (is_q ? q_hat : k_hat) + (size_t)t * total_key + cc;
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            } else {
+                float *dst = v_out + (size_t)t * Hv * GDN_DIM + (c0 - 2 * total_key);
+                *reinterpret_cast<float4 *>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+                *reinterpret_cast<float4 *>(dst + 4) = make_float4(y[4], y[5], y[6], y[7]);
+            }
         }
     }
     if (blockIdx.y == 0 && tid < Hv) {
         const float dt_b = bf16_bits_to_f32(dt_bias[tid]);
         const float neg_a = -expf(a_log[tid]);
-        for (int t = t0; t < min(t0 + CONV_TT, T); t++) {
+        for (int t = t0; t < t_end; t++) {
             const float a_val = __bfloat162float(alpha[(size_t)t * Hv + tid]);
             const float softplus = logf(1.0f + expf(a_val + dt_b));
             lg_out[(size_t)t * Hv + tid] = neg_a * softplus * 1.4426950408889634f;  // log2 of the decay g

@@ -284,7 +284,8 @@ __device__ __forceinline__ void merge_unit_slices(const GqaParams &p, const Loca
     float *s_m = s_w, *s_l = s_w + MAX_UNIT_PARTS;
     PartialDst pd;
     if (p.partial_mode) pd = partial_dst(p, L.it.in_idx);
-    constexpr int ROWS_PER_THREAD = 16;  // partial rows a thread holds per batch (8 rows of threads: 128 partials)
+    constexpr int ROWS_PER_THREAD = 20;  // partial rows a thread holds per batch (8 rows of threads: 160 partials, so
+                                         // that one wave of CTAs over two units is a single batch)
     for (int su = my_idx; su < group * 4; su += n_mergers) {
         const int hr = su >> 2, j = su & 3;
         float4 o4[ROWS_PER_THREAD];

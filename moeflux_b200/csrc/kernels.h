@@ -112,7 +112,7 @@ struct GqaParams {
     // Fused exchange of the KV-sequence split (partial_mode only): when peer_recv != nullptr the merged partial of
     // item i goes, instead of po/pm/pl, to the receive buffer of the rank that finishes the item,
     //   peer_recv[i / items_per_dest] + ((size_t)my_rank * items_per_dest + i % items_per_dest) * po_item_stride
-    // as one block [o | m | l], through peer-mapped pointers (plain stores over NVLink, no multicast); the last CTA
+    // as one block [o | m | l], through peer-mapped pointers (plain stores over NVLink); the last CTA
     // of the launch then publishes `flag_value` in slot my_rank of every peer's flag array.
     float *const *peer_recv;             // device array [world] of device pointers
     unsigned *const *peer_flags;         // device array [world] of device pointers to [world] flags

@@ -13,7 +13,7 @@
 // The reference runs one threadgroup per head with the scores of up to 4096 positions in threadgroup memory and,
 // beyond that, one dispatch per 4096-position tile merged by an online softmax in device memory.  Here a CTA owns
 // 16 heads (the M rows of mma.sync m16n8k16) and a chunk of positions; tiles of 16 positions arrive by TMA
-// (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a two-stage ring with bounded mbarrier waits; fp32
+// (cp.async.bulk.tensor, 128-byte swizzle) into a two-stage ring with bounded mbarrier waits; fp32
 // operands enter the tensor cores as two-piece bf16 expansions (hi + mid, three products, fp32 accumulate: about
 // 2^-16 relative, inside the reference's 1e-3 bound).  Each warp owns a quarter of the 576 key dims for the scores
 // (partial score blocks are summed through shared memory) and a quarter of the 512 value dims for the output.  The

@@ -172,10 +172,11 @@ def test_linear_attn_prefill_8192_tokens_against_sequential_steps():
     """8192 tokens = 128 chunks of the delta rule: every token's output and the final state against 8192 sequential
     steps of the oracle.  The chunked form runs its contractions on bf16 operands, so a token's error is a sample of a
     distribution (mean 3.6e-3 on B200, the same at token 100 and at token 8000: nothing accumulates, the state ends
-    3e-3 from the oracle's).  Its tail is the gated RMSNorm dividing by the norm of a head's raw read-out: the rare
-    head whose read-out nearly cancels has its rounding error magnified.  Over 200 tokens the largest sample stays
-    below the stated 2e-2; over 8192 tokens x 64 heads the 99.9th percentile does, and the largest sample is held
-    to 5e-2."""
+    3e-3 from the oracle's).  The raw read-out (no gated norm) stays inside the stated 2e-2 at every token (largest
+    1.2e-2).  With the gated RMSNorm the distribution grows a tail, because the norm divides by the size of a head's
+    raw read-out: the rare head whose read-out nearly cancels has its rounding error magnified.  Over 200 tokens the
+    largest sample stays below 2e-2; over 8192 tokens x 64 heads the 99.9th percentile does (1.6e-2), and the largest
+    sample (2.7e-2) is held to 5e-2."""
     import torch
 
     dev = torch.device("cuda:0")
@@ -190,4 +191,9 @@ def test_linear_attn_prefill_8192_tokens_against_sequential_steps():
     a, b = snap.state_load(G, ctx.state_save(0)), snap.state_load(G, orc.state_save(0))
     assert np.array_equal(a[0][1], b[0][1])
     assert I.rel_err(a[0][2], b[0][2]) <= TOL_BF16
+    # the same tokens without the gated norm: every token inside the stated tolerance
+    ctx.memory_clear(0)
+    orc.memory_clear(0)
+    raw = _prefill_linear(ctx, orc, 0, 0, T, I.rng(550), dev, use_z=False, per_token=True)
+    assert raw.max() <= TOL_BF16, raw.max()
     ctx.close()
