@@ -54,7 +54,7 @@ def parse_args():
     ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")
     ap.add_argument("--batch", type=int, default=8, help="sequences")
     ap.add_argument("--trace-world", type=int, default=8, help="--workload trace: the KV split whose per-rank launch is traced")
-    ap.add_argument("--workload", default="stack", choices=["stack", "ragged", "prefill", "matvec", "trace"],
+    ap.add_argument("--workload", default="stack", choices=["stack", "ragged", "prefill", "matvec", "trace", "mla"],
                     help="stack: the decode stack (headline); ragged: 64 sequences of ragged context, one full-attention "
                          "layer-step each, sharded by sequence; prefill: 8192-token chunked prefill of one hybrid block; "
                          "matvec: the 4-bit projections around the attention sub-blocks of one hybrid block")
@@ -789,6 +789,9 @@ def run_trace(args):
                       "GBps": alg_bytes / us_per_launch / 1e3 if us_per_launch else None,
                       "span_us": float(d[:, 4].max()), "start_spread_us": float(d[:, 0].max()),
                       "prologue_us": {"median": med(d[:, 1] - d[:, 0]), "max": float((d[:, 1] - d[:, 0]).max())},
+                      "prologue_split_us (bf16 cache)": None if not tr[:, 5].any() else {
+                          "rows_staged": med((tr[:, 5] - tr[:, 0]) / 1e3), "rotated": med((tr[:, 6] - tr[:, 5]) / 1e3),
+                          "fragments_and_third_tile": med((tr[:, 1] - tr[:, 6]) / 1e3)},
                       "first_segment_stream_us": {"median": med(d[:, 2] - d[:, 1]), "max": float((d[:, 2] - d[:, 1]).max())},
                       "first_segment_epilogue_us": {"median": med(d[:, 3] - d[:, 2]), "max": float((d[:, 3] - d[:, 2]).max())},
                       "cta_total_us": {"median": med(d[:, 4] - d[:, 0]), "min": float((d[:, 4] - d[:, 0]).min()),
@@ -911,7 +914,8 @@ def ragged_config(args, n):
                         f"fp32 accumulate",
             "layer_steps_per_step": RAGGED_SEQS, "rows_total": sum(lens), "kv_dtype": "bf16",
             "parallelism": (f"sequences dealt over {n} ranks greedily, longest first; no exchange in the data path, the "
-                            f"outputs are gathered (one NCCL all-gather of 32 KiB per sequence)") if n > 1 else "single GPU",
+                            f"outputs are gathered (one NCCL all-gather of 32 KiB per sequence per step, running under the "
+                            f"next step's kernel)") if n > 1 else "single GPU",
             "l2": "the KV rows of a step (2.2 GB in all) exceed the 126 MB L2; no flush needed"}
 
 
@@ -1010,8 +1014,11 @@ def run_ragged(args, rank, world, local_rank):
         v_all = torch.randn(RAGGED_SEQS, KV_DIM, device=dev, generator=gen)
         idx = torch.tensor(mine, device=dev, dtype=torch.long)
         q, gate, kk, vv = (t[idx].contiguous() for t in (q_all, gate_all, k_all, v_all))
-        out_pad = torch.zeros(n_max, Q_DIM, device=dev)      # this rank's outputs, padded to the largest shard
-        gathered = torch.empty(world * n_max, Q_DIM, device=dev) if world > 1 else None
+        # this rank's outputs, padded to the largest shard; two buffers, so that the gather of one step runs under
+        # the kernel of the next (the next step does not depend on the gathered outputs)
+        out_bufs = [torch.zeros(n_max, Q_DIM, device=dev) for _ in range(2)]
+        gath_bufs = [torch.empty(world * n_max, Q_DIM, device=dev) for _ in range(2)] if world > 1 else None
+        out_pad, gathered = out_bufs[0], (gath_bufs[0] if world > 1 else None)
     stream.synchronize()
     layers = np.full(n, RAGGED_LAYER, np.int32)
     seqs = np.arange(n, dtype=np.int32)
@@ -1019,21 +1026,31 @@ def run_ragged(args, rank, world, local_rank):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     k_events = []
 
+    pending = [None, None]  # the gather that last used each buffer pair
+
     def device_step(timed):
+        b = step_no[0] & 1
         pos = np.array([lens[s] + step_no[0] for s in mine], np.int32)
+        if pending[b] is not None:
+            pending[b].wait()  # the stream waits for the gather that still reads this output buffer
+            pending[b] = None
         if timed:
             e0, e1 = ev(), ev()
             e0.record(stream)
         ctx.full_attn_step_batched_dev(layers, seqs, pos, q.data_ptr(), gate.data_ptr(), kk.data_ptr(), vv.data_ptr(),
-                                       out_pad.data_ptr())
+                                       out_bufs[b].data_ptr())
         if timed:
             e1.record(stream)
             k_events.append((e0, e1))
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out_pad)
+            pending[b] = dist.all_gather_into_tensor(gath_bufs[b], out_bufs[b], async_op=True)
         step_no[0] += 1
 
     def barrier():
+        for b in range(2):  # a block ends when its last gathers have landed
+            if pending[b] is not None:
+                pending[b].wait()
+                pending[b] = None
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
@@ -1107,7 +1124,8 @@ def run_ragged(args, rank, world, local_rank):
     with torch.cuda.stream(stream):
         final = step_no[0]
         device_step(False)
-        stream.synchronize()
+        out_pad, gathered = out_bufs[final & 1], (gath_bufs[final & 1] if world > 1 else None)
+        barrier()
     ctx.synchronize()
     if rank == 0 and n:
         import oracle as O
@@ -1369,6 +1387,116 @@ def run_matvec(args):
     return line
 
 
+# --------------------------------------------------------------------------- folded MLA attention
+def run_mla(args):
+    """Folded MLA SDPA of one decode token (the third attention flavour): 128 heads, latent rank 512 + 64 rope dims,
+    fp32 latent cache of --ctx positions (default 32768: 75 MB), seeded N(0,1) cache rows and N(0,0.3) queries.  A step
+    = one call; the calls rotate over four caches (together more than twice the L2).  Single GPU."""
+    import torch
+
+    import moeflux_b200 as M
+    import oracle as O
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Hm, RANK, ROPE = 128, 512, 64
+    n = args.ctx if args.ctx != 131072 else 32768
+    K, W = args.steps, args.warmup
+    scale = float(1.0 / np.sqrt(np.float32(192.0)))
+    ctx = M.Ctx(num_layers=4, max_seq=64)
+    st = torch.cuda.Stream(device=dev)
+    ctx.set_stream(st.cuda_stream)
+    g = torch.Generator(device=dev)
+    g.manual_seed(31)
+    n_caches = 4
+    with torch.cuda.stream(st):
+        lat = [torch.randn(n, RANK, device=dev, generator=g) for _ in range(n_caches)]
+        rk = [torch.randn(n, ROPE, device=dev, generator=g) for _ in range(n_caches)]
+        qp = torch.randn(Hm, RANK, device=dev, generator=g) * 0.3
+        pe = torch.randn(Hm, ROPE, device=dev, generator=g) * 0.3
+        out = torch.empty(Hm, RANK, device=dev)
+    st.synchronize()
+    call = lambda i: ctx.mla_sdpa_folded_dev(Hm, n, scale, qp.data_ptr(), pe.data_ptr(), lat[i % n_caches].data_ptr(),
+                                             rk[i % n_caches].data_ptr(), out.data_ptr())
+    R = args.repeats or 7
+    sampler = ClockSampler(0)
+    blocks = []
+    with torch.cuda.stream(st):
+        for i in range(max(W, n_caches)):
+            call(i)
+        st.synchronize()
+        sampler.start()
+        time.sleep(0.3)
+        t0 = time.time()
+        launches0 = ctx.launch_count
+        for _ in range(R):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for i in range(K):
+                call(i)
+            e1.record(st)
+            st.synchronize()
+            blocks.append(e0.elapsed_time(e1))
+        launches = (ctx.launch_count - launches0) // R
+    ctx.synchronize()
+    clocks = sampler.stop(t0, time.time())
+    ms = statistics.median(blocks) / K
+    # end to end: the query of the token from pinned host memory, the result back; the cache is model state
+    hq, hp, ho = (torch.empty(Hm, d).pin_memory() for d in (RANK, ROPE, RANK))
+    hq.copy_(qp.cpu())
+    hp.copy_(pe.cpu())
+
+    def e2e_step(i):
+        with torch.cuda.stream(st):
+            qp.copy_(hq, non_blocking=True)
+            pe.copy_(hp, non_blocking=True)
+            call(i)
+            ho.copy_(out, non_blocking=True)
+            st.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    t1 = time.perf_counter()
+    for i in range(K):
+        e2e_step(i)
+    dt = (time.perf_counter() - t1) / K
+    # parity: the last e2e result against the oracle on the same cache
+    last = (K - 1) % n_caches
+    ref = O.mla_sdpa_folded(n, scale, hq.numpy(), hp.numpy(), lat[last].cpu().numpy(), rk[last].cpu().numpy())
+    err = float(np.max(np.abs(ho.numpy() - ref)) / max(np.max(np.abs(ref)), 1e-30))
+    # CPU arm: the oracle (the reference's C engine has no MLA twin) on the full problem, once
+    O.use_all_cores()
+    tc = time.perf_counter()
+    O.mla_sdpa_folded(n, scale, hq.numpy(), hp.numpy(), lat[0].cpu().numpy(), rk[0].cpu().numpy())
+    tc = time.perf_counter() - tc
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+    alg = n * (RANK + ROPE) * 4 + Hm * (2 * RANK + ROPE) * 4
+    flops = 2.0 * Hm * n * (RANK + ROPE + RANK)
+    achieved = alg / (ms * 1e-3) / 1e9
+    line = {"metric": "folded MLA attention steps/sec (128 heads, one decode token)", "value": 1e3 / ms, "unit": "steps/s",
+            "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms, "repeats": R, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 cache, two-piece bf16 products, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": f"folded MLA SDPA, 128 heads, rank 512 + rope 64, fp32 latent cache of {n} positions "
+                                   f"({alg / 1e6:.0f} MB per call), four caches rotated (more than the 126 MB L2)", "context": n},
+            "roofline": {"bound": "hbm", "kernel": "mla_decode_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)",
+                         "algorithmic_bytes_per_launch": alg, "ms_per_launch": ms, "frac_of_8TBps": achieved / 8000.0,
+                         "tensor_TFLOPs_useful": flops / (ms * 1e-3) / 1e12,
+                         "note": "121 useful flop per cached byte (x3 with the two-piece expansion on mma.sync): bound by the "
+                                 "legacy tensor pipe before HBM; the tcgen05 form is the next step"},
+            "e2e": {"value": 1.0 / dt, "unit": "steps/s", "h2d_bytes_per_step": 4 * Hm * (RANK + ROPE),
+                    "d2h_bytes_per_step": 4 * Hm * RANK},
+            "parity": {"max_rel_err": err, "tol": 1e-3, "items": 1, "ok": bool(err <= 1e-3),
+                       "what": "one call's v_combine against the CPU oracle on the same cache (the reference's GPU-vs-CPU bound)"},
+            "cpu_baseline": {"value": 1.0 / tc, "unit": "steps/s", "cores": O.num_threads(), "kind": "port",
+                             "sample": f"one call at the full size with the C restatement (OpenMP over heads): {tc * 1e3:.0f} ms"},
+            "gpu_launches": int(launches), "clocks": clocks}
+    ctx.close()
+    return line
+
+
 def compact(line):
     """The fields of a workload's line that matter when it rides along in another line."""
     if not line:
@@ -1410,6 +1538,13 @@ def main():
     if args.workload == "trace":
         if rank == 0:
             print(json.dumps(run_trace(args)), flush=True)
+        return
+    if args.workload == "mla":
+        if rank == 0:
+            line = run_mla(args)
+            print(json.dumps(line), flush=True)
+            if not line["parity"]["ok"]:
+                raise SystemExit("parity check failed: " + json.dumps(line["parity"]))
         return
     line = run_ragged(args, rank, world, local_rank) if args.workload == "ragged" else run_ours(args, rank, world, local_rank)
     others = {}

@@ -475,7 +475,7 @@ long long mfc_launch_count(const mfc_ctx *ctx);
 int mfc_check_guards(mfc_ctx *ctx);
 /* Time stamps (nanoseconds, %globaltimer) of the CTAs of the last decode launch made with the tuning
  * "gqa_phase_trace" on: out[cta][8] = {start, first segment's Q fragments ready, its last KV tile consumed, its
- * epilogue done, CTA done, 0, 0, 0}.  Returns the number of CTAs written (at most max_ctas), or -1. */
+ * epilogue done, CTA done, (bf16 cache only:) query rows staged, query rows rotated, 0}.  Returns the number of CTAs written (at most max_ctas), or -1. */
 int mfc_read_phase_trace(mfc_ctx *ctx, unsigned long long *out, int32_t max_ctas);
 
 /* ---- KV-sequence split: the exchange fused into the decode kernel ----

@@ -136,6 +136,7 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
         s_sin[tid] = sn;
     }
     __syncthreads();
+    if (seg_no == 0) trace_phase(p, 5);  // query rows and the RoPE table are in shared memory
 
     if (appender) {
         // rotate k, store the new K and V rows (bf16), then let thread 0 start the loads
@@ -185,6 +186,7 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
             *reinterpret_cast<uint32_t *>(s_qb + row * QB_STRIDE + d) = pack_bf16x2(x.x, x.y);
         }
         __syncthreads();
+        if (seg_no == 0) trace_phase(p, 6);  // appended (if this CTA appends), normalised and rotated
 #pragma unroll
         for (int ks = 0; ks < 16; ks++)
             ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
