@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072, help="context length per sequence")
     ap.add_argument("--batch", type=int, default=8, help="sequences")
+    ap.add_argument("--mla-cache", default="f32", choices=["f32", "bf16"], help="--workload mla: storage type of the latent cache")
     ap.add_argument("--trace-world", type=int, default=8, help="--workload trace: the KV split whose per-rank launch is traced")
     ap.add_argument("--workload", default="stack", choices=["stack", "ragged", "prefill", "matvec", "trace", "mla"],
                     help="stack: the decode stack (headline); ragged: 64 sequences of ragged context, one full-attention "
@@ -1403,6 +1404,9 @@ def run_mla(args):
     n = args.ctx if args.ctx != 131072 else 32768
     K, W = args.steps, args.warmup
     scale = float(1.0 / np.sqrt(np.float32(192.0)))
+    bf16 = args.mla_cache == "bf16"
+    esize = 2 if bf16 else 4
+    tol = 2e-2 if bf16 else 1e-3
     ctx = M.Ctx(num_layers=4, max_seq=64)
     st = torch.cuda.Stream(device=dev)
     ctx.set_stream(st.cuda_stream)
@@ -1412,12 +1416,16 @@ def run_mla(args):
     with torch.cuda.stream(st):
         lat = [torch.randn(n, RANK, device=dev, generator=g) for _ in range(n_caches)]
         rk = [torch.randn(n, ROPE, device=dev, generator=g) for _ in range(n_caches)]
+        if bf16:
+            lat = [x.to(torch.bfloat16).contiguous() for x in lat]
+            rk = [x.to(torch.bfloat16).contiguous() for x in rk]
         qp = torch.randn(Hm, RANK, device=dev, generator=g) * 0.3
         pe = torch.randn(Hm, ROPE, device=dev, generator=g) * 0.3
         out = torch.empty(Hm, RANK, device=dev)
     st.synchronize()
-    call = lambda i: ctx.mla_sdpa_folded_dev(Hm, n, scale, qp.data_ptr(), pe.data_ptr(), lat[i % n_caches].data_ptr(),
-                                             rk[i % n_caches].data_ptr(), out.data_ptr())
+    fn = ctx.mla_sdpa_folded_bf16_dev if bf16 else ctx.mla_sdpa_folded_dev
+    call = lambda i: fn(Hm, n, scale, qp.data_ptr(), pe.data_ptr(), lat[i % n_caches].data_ptr(),
+                        rk[i % n_caches].data_ptr(), out.data_ptr())
     R = args.repeats or 7
     sampler = ClockSampler(0)
     blocks = []
@@ -1462,33 +1470,34 @@ def run_mla(args):
     dt = (time.perf_counter() - t1) / K
     # parity: the last e2e result against the oracle on the same cache
     last = (K - 1) % n_caches
-    ref = O.mla_sdpa_folded(n, scale, hq.numpy(), hp.numpy(), lat[last].cpu().numpy(), rk[last].cpu().numpy())
+    ref = O.mla_sdpa_folded(n, scale, hq.numpy(), hp.numpy(), lat[last].float().cpu().numpy(), rk[last].float().cpu().numpy())
     err = float(np.max(np.abs(ho.numpy() - ref)) / max(np.max(np.abs(ref)), 1e-30))
     # CPU arm: the oracle (the reference's C engine has no MLA twin) on the full problem, once
     O.use_all_cores()
     tc = time.perf_counter()
-    O.mla_sdpa_folded(n, scale, hq.numpy(), hp.numpy(), lat[0].cpu().numpy(), rk[0].cpu().numpy())
+    O.mla_sdpa_folded(n, scale, hq.numpy(), hp.numpy(), lat[0].float().cpu().numpy(), rk[0].float().cpu().numpy())
     tc = time.perf_counter() - tc
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
-    alg = n * (RANK + ROPE) * 4 + Hm * (2 * RANK + ROPE) * 4
+    alg = n * (RANK + ROPE) * esize + Hm * (2 * RANK + ROPE) * 4
     flops = 2.0 * Hm * n * (RANK + ROPE + RANK)
     achieved = alg / (ms * 1e-3) / 1e9
     line = {"metric": "folded MLA attention steps/sec (128 heads, one decode token)", "value": 1e3 / ms, "unit": "steps/s",
             "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms, "repeats": R, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32 cache, two-piece bf16 products, f32 accumulate",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 cache, bf16 products, f32 accumulate" if bf16 else "f32 cache, two-piece bf16 products, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": f"folded MLA SDPA, 128 heads, rank 512 + rope 64, fp32 latent cache of {n} positions "
+            "config": {"workload": f"folded MLA SDPA, 128 heads, rank 512 + rope 64, {args.mla_cache} latent cache of {n} positions "
                                    f"({alg / 1e6:.0f} MB per call), four caches rotated (more than the 126 MB L2)", "context": n},
-            "roofline": {"bound": "hbm", "kernel": "mla_decode_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "mla_decode_bf16_kernel" if bf16 else "mla_decode_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)",
                          "algorithmic_bytes_per_launch": alg, "ms_per_launch": ms, "frac_of_8TBps": achieved / 8000.0,
                          "tensor_TFLOPs_useful": flops / (ms * 1e-3) / 1e12,
-                         "note": "121 useful flop per cached byte (x3 with the two-piece expansion on mma.sync): bound by the "
-                                 "legacy tensor pipe before HBM; the tcgen05 form is the next step"},
+                         "note": "121 (fp32 cache; x3 with the two-piece expansion) or 242 (bf16 cache) useful flop per cached byte "
+                                 "on mma.sync: bound by the legacy tensor pipe before HBM; the tcgen05 form is the next step"},
             "e2e": {"value": 1.0 / dt, "unit": "steps/s", "h2d_bytes_per_step": 4 * Hm * (RANK + ROPE),
                     "d2h_bytes_per_step": 4 * Hm * RANK},
-            "parity": {"max_rel_err": err, "tol": 1e-3, "items": 1, "ok": bool(err <= 1e-3),
+            "parity": {"max_rel_err": err, "tol": tol, "items": 1, "ok": bool(err <= tol),
                        "what": "one call's v_combine against the CPU oracle on the same cache (the reference's GPU-vs-CPU bound)"},
             "cpu_baseline": {"value": 1.0 / tc, "unit": "steps/s", "cores": O.num_threads(), "kind": "port",
                              "sample": f"one call at the full size with the C restatement (OpenMP over heads): {tc * 1e3:.0f} ms"},

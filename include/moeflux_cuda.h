@@ -441,6 +441,12 @@ int mfc_mla_sdpa_folded_dev(mfc_ctx *ctx, int32_t num_heads, int32_t cache_len, 
                             const float *rope_k_cache, float *v_combine);
 int mfc_mla_sdpa_folded(mfc_ctx *ctx, int32_t num_heads, int32_t cache_len, float softmax_scale, const float *q_prime,
                         const float *q_pe, const float *latent_cache, const float *rope_k_cache, float *v_combine);
+/* The same for a cache stored as bf16 (latent [cache_len][512], rope_k [cache_len][64] bf16 bit patterns; not a format
+ * of the reference, which stores fp32): half the HBM bytes per position and single bf16 products, like the bf16 KV
+ * cache of the GQA path; results within 2e-2 of the fp32 statement on the rounded cache.  Device pointers. */
+int mfc_mla_sdpa_folded_bf16_dev(mfc_ctx *ctx, int32_t num_heads, int32_t cache_len, float softmax_scale,
+                                 const float *q_prime, const float *q_pe, const void *latent_cache_bf16,
+                                 const void *rope_k_cache_bf16, float *v_combine);
 
 /* Tuning knobs (tests and sweeps): "gdn_rows" in {0,32,64,128} state rows per
  * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a decode launch aims for when it cuts the launch's

@@ -112,6 +112,7 @@ SIGNATURES = {
     "mfc_dequant_matvec_4bit": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
     "mfc_dequant_matvec_4bit_multi_dev": (C.c_int, [_P, C.c_int32, _P, _P, _P, C.c_int32, _P, _P, C.c_int32, _P]),
     "mfc_mla_sdpa_folded_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_float, _P, _P, _P, _P, _P]),
+    "mfc_mla_sdpa_folded_bf16_dev": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_float, _P, _P, _P, _P, _P]),
     "mfc_mla_sdpa_folded": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_float, _F, _F, _F, _F, _F]),
     "mfc_set_tuning": (C.c_int, [_P, C.c_char_p, C.c_int]),
     "mfc_launch_count": (C.c_longlong, [_P]),

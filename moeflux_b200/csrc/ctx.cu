@@ -1207,8 +1207,10 @@ int mfc_dequant_matvec_4bit(mfc_ctx *c, const uint32_t *w_packed, const uint16_t
 
 // ---------------------------------------------------------------- folded MLA attention
 
-int mfc_mla_sdpa_folded_dev(mfc_ctx *c, int32_t num_heads, int32_t cache_len, float softmax_scale, const float *q_prime,
-                            const float *q_pe, const float *latent_cache, const float *rope_k_cache, float *v_combine) {
+namespace {
+int mla_sdpa_folded_dev(mfc_ctx *c, int32_t num_heads, int32_t cache_len, float softmax_scale, const float *q_prime,
+                        const float *q_pe, const void *latent_cache, const void *rope_k_cache, float *v_combine,
+                        bool cache_bf16) {
     if (!c) return -1;
     if (!q_prime || !q_pe || !latent_cache || !rope_k_cache || !v_combine) {
         fail(c, "NULL argument");
@@ -1255,15 +1257,30 @@ int mfc_mla_sdpa_folded_dev(mfc_ctx *c, int32_t num_heads, int32_t cache_len, fl
     p.status = c->status;
     p.scale = softmax_scale;
     p.wait_spins = c->gqa_wait_spins;
+    p.cache_bf16 = cache_bf16 ? 1 : 0;
     CUtensorMap lat_map, rope_map;
-    if (!make_map_2d(c, &lat_map, const_cast<float *>(latent_cache), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, MLA_RANK,
-                     (uint64_t)cache_len, 32, 16) ||
-        !make_map_2d(c, &rope_map, const_cast<float *>(rope_k_cache), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, MLA_ROPE,
-                     (uint64_t)cache_len, 32, 16))
+    const CUtensorMapDataType dt = cache_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const int es = cache_bf16 ? 2 : 4, box_cols = cache_bf16 ? 64 : 32, box_rows = cache_bf16 ? 32 : 16;
+    if (!make_map_2d(c, &lat_map, const_cast<void *>(latent_cache), dt, es, MLA_RANK, (uint64_t)cache_len, box_cols, box_rows) ||
+        !make_map_2d(c, &rope_map, const_cast<void *>(rope_k_cache), dt, es, MLA_ROPE, (uint64_t)cache_len, box_cols, box_rows))
         return -1;
     CK(launch_mla_decode(lat_map, rope_map, p, c->stream));
     c->launches += n_chunks > 1 ? 2 : 1;
     return 0;
+}
+}  // namespace
+
+int mfc_mla_sdpa_folded_dev(mfc_ctx *c, int32_t num_heads, int32_t cache_len, float softmax_scale, const float *q_prime,
+                            const float *q_pe, const float *latent_cache, const float *rope_k_cache, float *v_combine) {
+    return mla_sdpa_folded_dev(c, num_heads, cache_len, softmax_scale, q_prime, q_pe, latent_cache, rope_k_cache, v_combine,
+                               false);
+}
+
+int mfc_mla_sdpa_folded_bf16_dev(mfc_ctx *c, int32_t num_heads, int32_t cache_len, float softmax_scale,
+                                 const float *q_prime, const float *q_pe, const void *latent_cache_bf16,
+                                 const void *rope_k_cache_bf16, float *v_combine) {
+    return mla_sdpa_folded_dev(c, num_heads, cache_len, softmax_scale, q_prime, q_pe, latent_cache_bf16, rope_k_cache_bf16,
+                               v_combine, true);
 }
 
 int mfc_mla_sdpa_folded(mfc_ctx *c, int32_t num_heads, int32_t cache_len, float softmax_scale, const float *q_prime,

@@ -275,6 +275,7 @@ __device__ __forceinline__ void merge_unit(const GqaParams &p, const Located &L,
 // of partials x 16 lanes of four dims; the loads of all partials of the slice are in flight together with the loads
 // of their (m, l), so the whole merge is one round trip to L2 instead of one per group of partials.
 //   s_w: 2 * MAX_UNIT_PARTS floats (m, then l), s_tmp: 8 * 64 floats.
+static_assert(MAX_SPLITS * 16 >= 2 * MAX_UNIT_PARTS, "the merge weight area of the kernels must hold m and l of every partial");
 __device__ __forceinline__ void merge_unit_slices(const GqaParams &p, const Located &L, size_t slot0, int n_parts,
                                                   int n_mergers, int my_idx, float *s_w, float *s_tmp) {
     const int tid = threadIdx.x, lane = tid & 31;

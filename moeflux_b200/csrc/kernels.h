@@ -227,11 +227,13 @@ struct MlaParams {
     int n_head_blocks;      // ceil(H / 16)
     int n_chunks;           // chunks of rows_per_chunk positions (a multiple of 16)
     int rows_per_chunk;
+    int cache_bf16;         // 0: fp32 cache (the reference's storage), 1: bf16 cache
     float scale;            // softmax scale
     unsigned wait_spins;    // poll limit of the bounded waits; 0 = default
 };
 cudaError_t mla_decode_configure();
-// lat_map: [cache_len][512] fp32, rope_map: [cache_len][64] fp32, boxes of 32 floats x 16 rows, 128-byte swizzle.
+// fp32 cache: lat_map [cache_len][512], rope_map [cache_len][64], boxes of 32 floats x 16 rows, 128-byte swizzle;
+// bf16 cache (p.cache_bf16): the same arrays as bf16, boxes of 64 elements x 32 rows.
 cudaError_t launch_mla_decode(const CUtensorMap &lat_map, const CUtensorMap &rope_map, const MlaParams &p,
                               cudaStream_t stream);
 

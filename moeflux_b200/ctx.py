@@ -517,6 +517,12 @@ class Ctx:
                                                latent_ptr, rope_k_ptr, out_ptr)
         self._check(rc, "mfc_mla_sdpa_folded_dev")
 
+    def mla_sdpa_folded_bf16_dev(self, num_heads, cache_len, softmax_scale, q_prime_ptr, q_pe_ptr, latent_bf16_ptr,
+                                 rope_k_bf16_ptr, out_ptr):
+        rc = self._lib.mfc_mla_sdpa_folded_bf16_dev(self._h, num_heads, cache_len, softmax_scale, q_prime_ptr, q_pe_ptr,
+                                                    latent_bf16_ptr, rope_k_bf16_ptr, out_ptr)
+        self._check(rc, "mfc_mla_sdpa_folded_bf16_dev")
+
     def linear_attn_step_stateless(self, layer: int, qkv, z, alpha, beta, conv_state, ssm_state):
         """Returns (out, new_conv_state, new_ssm_state); inputs are not modified."""
         qkv = _f32(qkv, self.conv_dim, "qkv")

@@ -188,3 +188,25 @@ def test_bounded_wait_runs_out_and_the_context_survives():
             assert I.rel_err(got[s], orc.full_attn_step(FULL, s, pos[s], *ins[s])) <= TOL_BF16, (step, s)
     ctx.check_guards()
     ctx.close()
+
+
+def test_one_cta_per_unit_plan():
+    """Tuning "gqa_unit_aligned": 120 sequences of equal length give 240 equal units, which nearly fill the wave of 296
+    CTAs, so every unit gets a CTA of its own (no shared units, nothing parked or merged).  Off, the same launch is
+    cut into equal runs across unit boundaries; both must agree with the oracle."""
+    n = 120
+    ctx, orc = make_pair(G4, max_seq=512, n_seqs=n, kv_bf16=True, linear_layers=[], max_batch=n)
+    r = I.rng(2000)
+    for s in range(n):
+        install_kv(ctx, orc, FULL, s, I.normal(r, (300, G4.kv_dim)), I.normal(r, (300, G4.kv_dim)))
+    for step, aligned in enumerate((1, 0, 1)):
+        ctx.set_tuning("gqa_unit_aligned", aligned)
+        ins = [I.gqa_step_inputs(r, G4) for _ in range(n)]
+        pos = [300 + step] * n
+        got = ctx.full_attn_step_batched([FULL] * n, list(range(n)), pos, np.stack([i[0] for i in ins]),
+                                         np.stack([i[1] for i in ins]), np.stack([i[2] for i in ins]),
+                                         np.stack([i[3] for i in ins]))
+        worst = max(I.rel_err(got[s], orc.full_attn_step(FULL, s, pos[s], *ins[s])) for s in range(n))
+        assert worst <= TOL_BF16, (step, worst)
+    ctx.check_guards()
+    ctx.close()

@@ -98,3 +98,33 @@ def test_gpu_argument_errors():
     with pytest.raises(M.MfcError):
         ctx.mla_sdpa_folded(0, 1.0, z, np.zeros(16 * ROPE, np.float32), np.zeros(RANK, np.float32), np.zeros(ROPE, np.float32))
     ctx.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cache_len,heads", [(1, 128), (31, 16), (32, 128), (33, 128), (1000, 128), (5000, 40), (32768, 128)])
+def test_gpu_bf16_cache_matches_oracle_on_the_rounded_cache(cache_len, heads):
+    """The bf16 latent cache (not a reference format; the counterpart of the GQA path's bf16 KV cache): the oracle
+    runs in fp32 on the rounded cache values, tolerance 2e-2."""
+    import torch
+
+    import moeflux_b200 as M
+
+    dev = torch.device("cuda:0")
+    ctx = M.Ctx(num_layers=4, max_seq=64)
+    qp, pe, lat, rk = normal_inputs(cache_len, 800 + cache_len, heads=heads, qs=0.3)
+    ref = O.mla_sdpa_folded(cache_len, SCALE, qp, pe, O.round_bf16(lat), O.round_bf16(rk))
+    dq, dp = torch.tensor(qp, device=dev), torch.tensor(pe, device=dev)
+    dl = torch.tensor(lat, device=dev).to(torch.bfloat16).contiguous()
+    dr = torch.tensor(rk, device=dev).to(torch.bfloat16).contiguous()
+    out = torch.full((heads, RANK), float("nan"), device=dev)
+    torch.cuda.synchronize()
+    for chunk in (0, 64):  # the automatic split, then many small chunks through the merge kernel
+        ctx.set_tuning("gqa_chunk", chunk)
+        ctx.mla_sdpa_folded_bf16_dev(heads, cache_len, float(SCALE), dq.data_ptr(), dp.data_ptr(), dl.data_ptr(),
+                                     dr.data_ptr(), out.data_ptr())
+        ctx.synchronize()
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert I.rel_err(got, ref) <= 2e-2, chunk
+    ctx.check_guards()
+    ctx.close()
