@@ -69,9 +69,9 @@ def parse_args():
     ap.add_argument("--repeats", type=int, default=0, help="timed blocks of --steps steps (0: at least 7 and about a second)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-single-step", action="store_true", help="skip the batch-1 single-step latencies (N=1, stack)")
-    ap.add_argument("--other-configs", type=int, default=0,
-                    help="1: the stack line also carries compact lines of the ragged workload (every N) and of the "
-                         "prefill workload (N=1), each run with --steps")
+    ap.add_argument("--other-configs", type=int, default=1,
+                    help="1 (default): the stack line also carries compact lines of the ragged workload (every N) and of "
+                         "the prefill workload (N=1), each run with --steps; 0: the stack workload alone")
     return ap.parse_args()
 
 

@@ -132,6 +132,7 @@ struct mfc_ctx {
     int plan_max_parts = 1;                            // most CTAs that share one unit in it
     int coop_capacity = 0;                             // CTAs of the decode kernel the device holds at once
     bool gqa_coop = true;                              // merge widely shared units cooperatively when possible
+    int gqa_coop_min_parts = 32;                       // ... when some unit is shared by more CTAs than this
 
     // device staging for the host-pointer entry points (max_batch items)
     float *st_q = nullptr, *st_gate = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
@@ -433,9 +434,11 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
     p.tickets = c->tickets;
     p.group_tickets = c->group_tickets;
     p.n_kv_slots = c->n_kv_slots;
-    // a unit shared by many CTAs (a lone long sequence) is merged by its sharers together, which needs every CTA of
-    // the grid resident: a cooperative launch, when the grid fits the device
-    p.coop_merge = c->gqa_coop && c->plan_max_parts > MERGE_GROUP && total_ctas <= c->coop_capacity;
+    // a unit shared by very many CTAs (a lone long sequence) is merged by its sharers together, which needs every CTA
+    // of the grid resident: a cooperative launch, when the grid fits the device.  Moderately shared units (a ragged
+    // batch of a few sequences) keep the ordinary launch and the two-level merge: a cooperative launch cannot start
+    // while another kernel (a collective, the GatedDeltaNet launch on the second queue) holds part of an SM.
+    p.coop_merge = c->gqa_coop && c->plan_max_parts > c->gqa_coop_min_parts && total_ctas <= c->coop_capacity;
     p.wait_spins = c->gqa_wait_spins;
     p.inject_lost_load = c->gqa_inject_lost_load;
     p.phase_trace = (c->phase_trace_on && total_ctas <= mfc_ctx::MAX_TRACE_CTAS) ? c->phase_trace : nullptr;
@@ -1342,6 +1345,9 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
         c->gqa_min_rows = value;
     } else if (!strcmp(key, "gqa_coop_merge")) {
         c->gqa_coop = value != 0;
+    } else if (!strcmp(key, "gqa_coop_min_parts")) {
+        if (value < MERGE_GROUP) return -1;
+        c->gqa_coop_min_parts = value;
     } else if (!strcmp(key, "gqa_unit_aligned")) {
         c->gqa_unit_aligned = value != 0;
     } else if (!strcmp(key, "gqa_wait_spins")) {

@@ -116,6 +116,7 @@ def test_units_shared_by_many_ctas(lens, coop):
     n = len(lens)
     ctx, orc = make_pair(G4, max_seq=32768 + 8, n_seqs=n, kv_bf16=True, linear_layers=[])
     ctx.set_tuning("gqa_coop_merge", coop)
+    ctx.set_tuning("gqa_coop_min_parts", 8)  # also the moderately shared units of these launches
     r = I.rng(1700 + n)
     for s, ln in enumerate(lens):
         install_kv(ctx, orc, FULL, s, I.normal(r, (ln, G4.kv_dim)), I.normal(r, (ln, G4.kv_dim)))
