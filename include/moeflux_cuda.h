@@ -453,8 +453,9 @@ int mfc_mla_sdpa_folded_bf16_dev(mfc_ctx *ctx, int32_t num_heads, int32_t cache_
  * KV tiles into equal runs (0 = one wave: two CTAs per SM); "gqa_chunk" forces the rows per CTA (0 = automatic); "gqa_min_rows" least rows per CTA under the automatic
  * plan (a multiple of 32, default 64); "gqa_unit_aligned" 1 = give every (item, kv head) unit a CTA of its own when
  * equal-length units nearly fill the wave (default 0); "gqa_coop_merge" 0 = never launch cooperatively (default 1: a
- * launch in which more than "gqa_coop_min_parts" (default 32, at least 8) CTAs share a unit, i.e. a lone long
- * sequence, is launched cooperatively when it fits the device, and the CTAs that share a unit merge it together);
+ * launch in which more than "gqa_coop_min_parts" (default 32, at least 8) CTAs share a unit and that
+ * unit has at least a quarter of the launch's CTAs, i.e. a lone long sequence or two, is launched cooperatively when
+ * it fits the device, and the CTAs that share a unit merge it together);
  * "gdn_side_queue" (see mfc_join); "gqa_wait_spins" poll limit of the kernels' bounded waits (0 = default);
  * "gqa_inject_lost_load" 1 = the first CTA of the next decode launches arms the barrier of its first KV tile and
  * issues no load for it, so that its bounded wait runs out with nothing in flight (exercises the failure path

@@ -434,11 +434,13 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
     p.tickets = c->tickets;
     p.group_tickets = c->group_tickets;
     p.n_kv_slots = c->n_kv_slots;
-    // a unit shared by very many CTAs (a lone long sequence) is merged by its sharers together, which needs every CTA
-    // of the grid resident: a cooperative launch, when the grid fits the device.  Moderately shared units (a ragged
-    // batch of a few sequences) keep the ordinary launch and the two-level merge: a cooperative launch cannot start
+    // a unit shared by very many CTAs (a lone long sequence: the launch is at most four units' worth of CTAs) is merged
+    // by its sharers together, which needs every CTA of the grid resident: a cooperative launch, when the grid fits
+    // the device.  Moderately shared units (a ragged batch of several sequences) keep the ordinary launch and the
+    // two-level merge: a cooperative launch cannot start
     // while another kernel (a collective, the GatedDeltaNet launch on the second queue) holds part of an SM.
-    p.coop_merge = c->gqa_coop && c->plan_max_parts > c->gqa_coop_min_parts && total_ctas <= c->coop_capacity;
+    p.coop_merge = c->gqa_coop && c->plan_max_parts > c->gqa_coop_min_parts && c->plan_max_parts * 4 >= total_ctas &&
+                   total_ctas <= c->coop_capacity;
     p.wait_spins = c->gqa_wait_spins;
     p.inject_lost_load = c->gqa_inject_lost_load;
     p.phase_trace = (c->phase_trace_on && total_ctas <= mfc_ctx::MAX_TRACE_CTAS) ? c->phase_trace : nullptr;
