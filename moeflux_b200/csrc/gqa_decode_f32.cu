@@ -217,18 +217,22 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         const uint8_t *vgen = kgen + TILE_BYTES_F32;
 
         // partial scores over dims 64w..64w+63 for the 16 rows of the tile
-        float sp[2][4];
+        // (the three products of the expansion accumulate separately: six independent chains of MMAs per warp
+        // instead of two chains of twelve dependent ones)
+        float sp[2][4], sp_mid[2][4], sp_kmid[2][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++) sp[nt][0] = sp[nt][1] = sp[nt][2] = sp[nt][3] = 0.0f;
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) sp[nt][e] = sp_mid[nt][e] = sp_kmid[nt][e] = 0.0f;
         if (ok) {
             const int r = lane & 7, mi = lane >> 3;
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++) {
-                const int row = 8 * nt + r;
+            for (int jx = 0; jx < 4; jx++) {  // one 16-dim k-step per ldmatrix.x4
+                const int box = 2 * warp + (jx >> 1);
+                const int chunk = ((jx & 1) << 2) + mi;
 #pragma unroll
-                for (int jx = 0; jx < 4; jx++) {  // one 16-dim k-step per ldmatrix.x4
-                    const int box = 2 * warp + (jx >> 1);
-                    const int chunk = ((jx & 1) << 2) + mi;
+                for (int nt = 0; nt < 2; nt++) {
+                    const int row = 8 * nt + r;
                     const uint32_t addr = kst + box * BOX_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4);
                     uint32_t r0, r1, r2, r3;  // K[row g][16 jx + t, + 4, + 8, + 12] of this warp's dims
                     ldmatrix_x4(r0, r1, r2, r3, addr);
@@ -236,10 +240,14 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
                     split_bf16x2(__uint_as_float(r0), __uint_as_float(r1), h0, m0);
                     split_bf16x2(__uint_as_float(r2), __uint_as_float(r3), h1, m1);
                     mma_bf16_16816(sp[nt], qh[jx], h0, h1);
-                    mma_bf16_16816(sp[nt], qm[jx], h0, h1);
-                    mma_bf16_16816(sp[nt], qh[jx], m0, m1);
+                    mma_bf16_16816(sp_mid[nt], qm[jx], h0, h1);
+                    mma_bf16_16816(sp_kmid[nt], qh[jx], m0, m1);
                 }
             }
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) sp[nt][e] += sp_mid[nt][e] + sp_kmid[nt][e];
         }
         float *spw = s_sp + ((i & 1) * 4 + warp) * 16 * SP_STRIDE;
 #pragma unroll

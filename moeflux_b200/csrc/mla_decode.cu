@@ -136,18 +136,22 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const __grid_cons
         const uint32_t kst = smem_u32(gen);
 
         // partial scores of the 16 positions over this warp's 144 key dims
-        float sp[2][4];
+        // (the three products of the expansion accumulate separately: six independent chains of MMAs per warp
+        // instead of two)
+        float sp[2][4], sp_mid[2][4], sp_kmid[2][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++) sp[nt][0] = sp[nt][1] = sp[nt][2] = sp[nt][3] = 0.0f;
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) sp[nt][e] = sp_mid[nt][e] = sp_kmid[nt][e] = 0.0f;
         if (ok) {
             const int r = lane & 7, mi = lane >> 3;
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++) {
-                const int row = 8 * nt + r;
+            for (int j = 0; j < MLA_KSTEPS_PER_WARP; j++) {
+                const int ks = MLA_KSTEPS_PER_WARP * warp + j;
+                const int box = ks >> 1, chunk16 = ((ks & 1) << 2) + mi;
 #pragma unroll
-                for (int j = 0; j < MLA_KSTEPS_PER_WARP; j++) {
-                    const int ks = MLA_KSTEPS_PER_WARP * warp + j;
-                    const int box = ks >> 1, chunk16 = ((ks & 1) << 2) + mi;
+                for (int nt = 0; nt < 2; nt++) {
+                    const int row = 8 * nt + r;
                     const uint32_t addr = kst + box * MLA_BOX_BYTES + row * 128 + ((chunk16 ^ (row & 7)) << 4);
                     uint32_t r0, r1, r2, r3;  // K[row][16 ks + t, + 4, + 8, + 12]
                     ldmatrix_x4(r0, r1, r2, r3, addr);
@@ -155,10 +159,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const __grid_cons
                     split2(__uint_as_float(r0), __uint_as_float(r1), h0, m0);
                     split2(__uint_as_float(r2), __uint_as_float(r3), h1, m1);
                     mma_bf16_16816(sp[nt], qh[j], h0, h1);
-                    mma_bf16_16816(sp[nt], qm[j], h0, h1);
-                    mma_bf16_16816(sp[nt], qh[j], m0, m1);
+                    mma_bf16_16816(sp_mid[nt], qm[j], h0, h1);
+                    mma_bf16_16816(sp_kmid[nt], qh[j], m0, m1);
                 }
             }
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) sp[nt][e] += sp_mid[nt][e] + sp_kmid[nt][e];
         }
         float *spw = s_sp + ((i & 1) * 4 + warp) * 16 * MLA_SP_STRIDE;
 #pragma unroll
