@@ -462,7 +462,7 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
 }
 
 int launch_gqa(mfc_ctx *c, GqaParams &p) {
-    if (p.n_items <= INLINE_ITEMS) {  // a handful of items travel as kernel parameters: no copy before the launch
+    if (p.n_items <= INLINE_ITEMS) {  // up to 64 items travel as kernel parameters: no copy before the launch
         p.items = nullptr;
         for (int i = 0; i < p.n_items; i++) p.inline_items[i] = c->h_gqa_items[i];
     } else if (upload_items(c, c->d_gqa_items, c->h_gqa_items.data(), sizeof(GqaItem) * p.n_items, c->stream)) {
@@ -535,7 +535,7 @@ int launch_gdn(mfc_ctx *c, int n, const float *qkv, const float *z, const float 
     p.Hk = g.linear_num_k_heads;
     p.conv_dim = c->conv_dim;
     p.eps = g.rms_norm_eps;
-    if (n <= INLINE_ITEMS) {  // a handful of items travel as kernel parameters: no copy before the launch
+    if (n <= INLINE_ITEMS) {  // up to 64 items travel as kernel parameters: no copy before the launch
         p.items = nullptr;
         for (int i = 0; i < n; i++) p.inline_items[i] = c->h_gdn_items[i];
     } else if (upload_items(c, c->d_gdn_items, c->h_gdn_items.data(), sizeof(GdnItem) * n, c->stream)) {

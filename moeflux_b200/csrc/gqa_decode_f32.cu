@@ -25,6 +25,9 @@ namespace mfc {
 
 namespace {
 
+#ifndef F32_SCORE_CHAINS
+#define F32_SCORE_CHAINS 3  // 3: one accumulator per product of the two-piece expansion; 1: a single chain
+#endif
 constexpr int F32_TILE = KV_TILE_F32;
 constexpr int F32_STAGES = 3;
 constexpr int TILE_BYTES_F32 = F32_TILE * HEAD_DIM * 4;  // 16 KiB per tensor per stage
@@ -239,15 +242,23 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
                     uint32_t h0, m0, h1, m1;
                     split_bf16x2(__uint_as_float(r0), __uint_as_float(r1), h0, m0);
                     split_bf16x2(__uint_as_float(r2), __uint_as_float(r3), h1, m1);
+#if F32_SCORE_CHAINS == 3
                     mma_bf16_16816(sp[nt], qh[jx], h0, h1);
                     mma_bf16_16816(sp_mid[nt], qm[jx], h0, h1);
                     mma_bf16_16816(sp_kmid[nt], qh[jx], m0, m1);
+#else
+                    mma_bf16_16816(sp[nt], qh[jx], h0, h1);
+                    mma_bf16_16816(sp[nt], qm[jx], h0, h1);
+                    mma_bf16_16816(sp[nt], qh[jx], m0, m1);
+#endif
                 }
             }
+#if F32_SCORE_CHAINS == 3
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) sp[nt][e] += sp_mid[nt][e] + sp_kmid[nt][e];
+#endif
         }
         float *spw = s_sp + ((i & 1) * 4 + warp) * 16 * SP_STRIDE;
 #pragma unroll
@@ -307,13 +318,6 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
             }
             l_r[x] = l_r[x] * corr[x] + rs;
         }
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-            o[nt][0] *= corr[0];
-            o[nt][1] *= corr[0];
-            o[nt][2] *= corr[1];
-            o[nt][3] *= corr[1];
-        }
         if (tile_row0 + F32_TILE > c1) {
             // Rows of the tile past the end of the sequence carry weight zero, but 0 * NaN is NaN: whatever the
             // cache holds there (a caller's uninitialised memory) must not reach the product.  Each warp clears
@@ -325,8 +329,13 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
                     *reinterpret_cast<uint4 *>(vbox + b * BOX_BYTES + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
             __syncwarp();
         }
-        // O[:, 64w..64w+63] += P (16x16) * V (16 x 64): one k-step of 16 tile rows; the score
+        // O[:, 64w..64w+63] = corr * O + P (16x16) * V (16 x 64): one k-step of 16 tile rows; the score
         // fragment (columns 2t, 2t+1 of each 8-column block) is already in A-operand order.
+        // The tile's three products are summed by the tensor core starting from zero (smallest terms first) and
+        // joined to the running output by one fused multiply-add per element.  The tensor core truncates its
+        // accumulator after every instruction; run through thousands of tiles, an accumulator kept there shrinks
+        // by half a unit in the last place each time (1e-4 of its size after 13000 rows), which the fp32 contract
+        // has no room for.  Here the long sum rounds to nearest, once per tile.
         {
             uint32_t ph[4], pm[4];
             split_bf16x2(sv[0][0], sv[0][1], ph[0], pm[0]);  // (g,   rows 2t, 2t+1)
@@ -343,9 +352,14 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
                 uint32_t h0, m0, h1, m1;
                 split_bf16x2(v_at(bx, 2 * t, col), v_at(bx, 2 * t + 1, col), h0, m0);
                 split_bf16x2(v_at(bx, 2 * t + 8, col), v_at(bx, 2 * t + 9, col), h1, m1);
-                mma_bf16_16816(o[nt], ph, h0, h1);
-                mma_bf16_16816(o[nt], pm, h0, h1);
-                mma_bf16_16816(o[nt], ph, m0, m1);
+                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                mma_bf16_16816(d, pm, h0, h1);
+                mma_bf16_16816(d, ph, m0, m1);
+                mma_bf16_16816(d, ph, h0, h1);
+                o[nt][0] = fmaf(o[nt][0], corr[0], d[0]);
+                o[nt][1] = fmaf(o[nt][1], corr[0], d[1]);
+                o[nt][2] = fmaf(o[nt][2], corr[1], d[2]);
+                o[nt][3] = fmaf(o[nt][3], corr[1], d[3]);
             }
         }
     }

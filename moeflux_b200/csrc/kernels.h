@@ -29,7 +29,7 @@ struct GdnItem {
     int32_t pad;
 };
 
-constexpr int INLINE_ITEMS = 4;  // launches of at most this many items carry them in the kernel's parameters
+constexpr int INLINE_ITEMS = 64;  // launches of at most this many items carry them in the kernel's parameters (2 KiB)
 
 struct GdnParams {
     float *ssm_base;          // [state][Hv][128 value][128 key]

@@ -225,15 +225,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const __grid_cons
             }
             l_r[x] = l_r[x] * corr[x] + rs;
         }
-#pragma unroll
-        for (int nt = 0; nt < 16; nt++) {
-            o[nt][0] *= corr[0];
-            o[nt][1] *= corr[0];
-            o[nt][2] *= corr[1];
-            o[nt][3] *= corr[1];
-        }
-        // O[:, 128w .. 128w+127] += P (16 x 16) * latent (16 x 128): the same tile, as the value operand.  Rows past
-        // the end of the cache were filled with zeros by the copy and carry weight zero.
+        // O[:, 128w .. 128w+127] = corr * O + P (16 x 16) * latent (16 x 128): the same tile, as the value operand.
+        // Rows past the end of the cache were filled with zeros by the copy and carry weight zero.  The tile's
+        // products are summed by the tensor core from zero and joined to the running output by a fused multiply-add
+        // that rounds to nearest: an accumulator kept in the tensor core is truncated after every instruction and
+        // drifts towards zero over thousands of tiles.
         {
             uint32_t ph[4], pm[4];
             split2(sv[0][0], sv[0][1], ph[0], pm[0]);  // (g,   rows 2t, 2t+1)
@@ -250,9 +246,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const __grid_cons
                 uint32_t h0, m0, h1, m1;
                 split2(v_at(bx, 2 * t, col), v_at(bx, 2 * t + 1, col), h0, m0);
                 split2(v_at(bx, 2 * t + 8, col), v_at(bx, 2 * t + 9, col), h1, m1);
-                mma_bf16_16816(o[nt], ph, h0, h1);
-                mma_bf16_16816(o[nt], pm, h0, h1);
-                mma_bf16_16816(o[nt], ph, m0, m1);
+                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                mma_bf16_16816(d, pm, h0, h1);
+                mma_bf16_16816(d, ph, m0, m1);
+                mma_bf16_16816(d, ph, h0, h1);
+                o[nt][0] = fmaf(o[nt][0], corr[0], d[0]);
+                o[nt][1] = fmaf(o[nt][1], corr[0], d[1]);
+                o[nt][2] = fmaf(o[nt][2], corr[1], d[2]);
+                o[nt][3] = fmaf(o[nt][3], corr[1], d[3]);
             }
         }
     }

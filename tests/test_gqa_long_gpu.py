@@ -72,6 +72,33 @@ def test_ctx32768_single_step(bf16, coop):
     ctx.close()
 
 
+def test_fp32_long_run_per_cta_keeps_fp32_accuracy():
+    """A CTA that streams 16384 rows by itself (the benchmark's launches of 120 items give every CTA runs of this
+    length; here one sequence with the least run length raised to 16384 rows).  An output accumulator that lives in
+    the tensor core is truncated after each of its 3072 instructions and ends 1e-4 below the true sum; the kernel
+    joins each tile's products to the running output with a rounded fused multiply-add instead.  Checked against a
+    float64 evaluation of the definition: 2e-5, five times inside the fp32 contract."""
+    ctx, _ = make_pair(G4, max_seq=32768, linear_layers=[])
+    ctx.set_tuning("gqa_min_rows", 16384)
+    r = I.rng(777)
+    n = 32768
+    q, gate, _, _ = I.gqa_step_inputs(r, G4)
+    K, V = I.normal(r, (n, G4.kv_dim)), I.normal(r, (n, G4.kv_dim))
+    got = ctx.sdpa(n, q, gate, K, V)
+    H, Hkv, D = G4.num_attn_heads, G4.num_kv_heads, G4.head_dim
+    ref = np.empty(H * D)
+    for h in range(H):
+        kv = h // (H // Hkv)
+        s = K[:, kv * D:(kv + 1) * D].astype(np.float64) @ q[h * D:(h + 1) * D].astype(np.float64) / np.sqrt(D)
+        p = np.exp(s - s.max())
+        o = (p / p.sum()) @ V[:, kv * D:(kv + 1) * D].astype(np.float64)
+        ref[h * D:(h + 1) * D] = o / (1.0 + np.exp(-gate[h * D:(h + 1) * D].astype(np.float64)))
+    err = float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+    assert err <= 2e-5, err
+    assert I.rel_err(got, O.sdpa(n, q, gate, K, V)) <= TOL_F32
+    ctx.close()
+
+
 def test_ctx131072_bf16_single_step():
     """The benchmark's context: 131072 rows, bf16 cache."""
     ctx, orc = make_pair(G4, max_seq=131072, kv_bf16=True, linear_layers=[])
