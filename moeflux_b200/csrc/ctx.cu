@@ -96,6 +96,17 @@ struct mfc_ctx {
     unsigned pin_next = 0;
     float *sc_o = nullptr, *sc_m = nullptr, *sc_l = nullptr;
     unsigned *tickets = nullptr, *group_tickets = nullptr, *status = nullptr;
+    unsigned *mv_sched = nullptr;  // two pairs (tile counter, finished CTAs) of the one-vector projection kernel, used in turn
+    unsigned mv_launches = 0;
+    bool mv_overlap = true;        // tuning "matvec_overlap"
+    struct MvMap {
+        const uint32_t *w;
+        const uint16_t *scales, *biases;
+        int in_dim, out_dim;
+        CUtensorMap map, sc_map, bi_map;
+    };
+    static constexpr size_t MV_MAP_CACHE = 256;
+    std::vector<MvMap> mv_maps;  // tensor maps of the weight matrices seen last (one-vector projection kernel)
     int max_parts = 0;
     // every device allocation of the context, with a band of 0xFF bytes on either side (mfc_check_guards)
     struct Alloc {
@@ -213,9 +224,9 @@ bool dalloc(mfc_ctx *c, T **p, size_t n, bool zero, const char *name = "buffer")
     return true;
 }
 
-// 2-D map over a row-major [rows][cols] array, 128-byte swizzle; box_cols * esize must be 128.
+// 2-D map over a row-major [rows][cols] array; with the 128-byte swizzle box_cols * esize must be 128.
 bool make_map_2d(mfc_ctx *c, CUtensorMap *map, void *base, CUtensorMapDataType dtype, int esize, uint64_t cols,
-                 uint64_t rows, int box_cols, int box_rows) {
+                 uint64_t rows, int box_cols, int box_rows, bool swizzle128 = true) {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -226,8 +237,8 @@ bool make_map_2d(mfc_ctx *c, CUtensorMap *map, void *base, CUtensorMapDataType d
     cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = ((EncodeTiledFn)fn)(map, dtype, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                     swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(c, "cuTensorMapEncodeTiled failed, code " + std::to_string((int)r));
     return true;
 }
@@ -296,6 +307,7 @@ int check_status(mfc_ctx *c) {
         cudaMemsetAsync(c->status, 0, sizeof(unsigned), c->stream);
         cudaMemsetAsync(c->tickets, 0, sizeof(unsigned) * (size_t)c->cfg.max_batch * c->cfg.num_kv_heads, c->stream);
         cudaMemsetAsync(c->group_tickets, 0, sizeof(unsigned) * (size_t)c->max_parts, c->stream);
+        cudaMemsetAsync(c->mv_sched, 0, 4 * sizeof(unsigned), c->stream);
         if (c->xc.done_counter) cudaMemsetAsync(c->xc.done_counter, 0, sizeof(unsigned), c->stream);
         cudaStreamSynchronize(c->stream);
         std::string what;
@@ -799,7 +811,7 @@ mfc_ctx *mfc_open(const mfc_config *cfg) {
          DA(d_gqa_items, mb, false) && DA(d_gdn_items, mb, false) &&
          DA(sc_o, (size_t)c->max_parts * 16 * HEAD_DIM, false) && DA(sc_m, (size_t)c->max_parts * 16, false) &&
          DA(sc_l, (size_t)c->max_parts * 16, false) && DA(tickets, mb * g.num_kv_heads, true) &&
-         DA(group_tickets, c->max_parts, true) && DA(status, 1, true) &&
+         DA(group_tickets, c->max_parts, true) && DA(status, 1, true) && DA(mv_sched, 4, true) &&
          DA(phase_trace, (size_t)mfc_ctx::MAX_TRACE_CTAS * PHASE_TRACE_WORDS, true) && DA(st_q, mb * qd, false) &&
          DA(st_gate, mb * qd, false) && DA(st_k, mb * kvd, false) && DA(st_v, mb * kvd, false) &&
          DA(st_out, mb * qd, false) && DA(st_qkv, mb * c->conv_dim, false) && DA(st_z, mb * vd, false) &&
@@ -1101,6 +1113,44 @@ int mfc_lse_merge_gate_exchange_dev(mfc_ctx *c, const float *gate, float *out) {
 // ---------------------------------------------------------------- projections: 4-bit dequant matvec
 
 namespace {
+// Tensor map of a weight matrix as bytes [out_dim][in_dim / 2], boxes of 16 rows x 128 bytes.  Encoding one is a
+// driver call of a microsecond or two; the maps of the matrices seen last are kept (a model's projections recur every
+// token).
+bool matvec_map(mfc_ctx *c, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int in_dim, int out_dim,
+                MatvecMaps *out, int m) {
+    for (const mfc_ctx::MvMap &e : c->mv_maps)
+        if (e.w == w && e.scales == scales && e.biases == biases && e.in_dim == in_dim && e.out_dim == out_dim) {
+            out->w[m] = e.map;
+            out->sc[m] = e.sc_map;
+            out->bi[m] = e.bi_map;
+            return true;
+        }
+    mfc_ctx::MvMap e;
+    memset(&e, 0, sizeof(e));
+    e.w = w;
+    e.scales = scales;
+    e.biases = biases;
+    e.in_dim = in_dim;
+    e.out_dim = out_dim;
+    if (!make_map_2d(c, &e.map, const_cast<uint32_t *>(w), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)in_dim / 2,
+                     (uint64_t)out_dim, 128, 16))
+        return false;
+    // scales and biases travel as boxes only when their rows are multiples of 16 bytes and 16-byte aligned
+    if (in_dim % 512 == 0 && !(((uintptr_t)scales | (uintptr_t)biases) & 15)) {
+        if (!make_map_2d(c, &e.sc_map, const_cast<uint16_t *>(scales), CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+                         (uint64_t)in_dim / 64, (uint64_t)out_dim, 32, 16, false) ||
+            !make_map_2d(c, &e.bi_map, const_cast<uint16_t *>(biases), CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+                         (uint64_t)in_dim / 64, (uint64_t)out_dim, 32, 16, false))
+            return false;
+    }
+    if (c->mv_maps.size() >= mfc_ctx::MV_MAP_CACHE) c->mv_maps.erase(c->mv_maps.begin());
+    c->mv_maps.push_back(e);
+    out->w[m] = e.map;
+    out->sc[m] = e.sc_map;
+    out->bi[m] = e.bi_map;
+    return true;
+}
+
 int check_matvec_args(mfc_ctx *c, const void *w, const void *s, const void *b, int32_t in_dim, int32_t out_dim,
                       const float *x, int32_t n_vec, const float *out) {
     if (!w || !s || !b || !x || !out) {
@@ -1139,6 +1189,10 @@ int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *c, int32_t n_mat, const uint32_t 
     MatvecBatch mb;
     memset(&mb, 0, sizeof(mb));
     mb.n_mat = n_mat;
+    mb.overlap = c->mv_overlap ? 1 : 0;
+    mb.status = c->status;
+    mb.spins = (unsigned)c->gqa_wait_spins;
+    mb.trace = c->phase_trace_on ? c->phase_trace : nullptr;  // the grid never exceeds two CTAs per SM
     for (int m = 0; m < n_mat; m++) {
         if (check_matvec_args(c, w_packed[m], scales[m], biases[m], in_dim, out_dims[m], x, n_vec, outs[m])) return -1;
         mb.w[m] = w_packed[m];
@@ -1150,12 +1204,19 @@ int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *c, int32_t n_mat, const uint32_t 
     cudaSetDevice(c->cfg.device);
     // as many vectors per pass over the weights as the staging of x allows
     int per_pass = n_vec;
+    MatvecMaps maps;  // for the one-vector kernel (a pass of one vector: n_vec 1, or the remainder of several passes)
+    for (int m = 0; m < n_mat; m++)
+        if (!matvec_map(c, w_packed[m], scales[m], biases[m], in_dim, out_dims[m], &maps, m)) return -1;
     while (per_pass > 1 && dequant_matvec_4bit_smem(in_dim, per_pass) > c->smem_optin) per_pass--;
     for (int v0 = 0; v0 < n_vec; v0 += per_pass) {
         const int nv = n_vec - v0 < per_pass ? n_vec - v0 : per_pass;
         MatvecBatch pass = mb;
         for (int m = 0; m < n_mat; m++) pass.out[m] = outs[m] + (size_t)v0 * out_dims[m];
-        CK(launch_dequant_matvec_4bit(pass, x + (size_t)v0 * in_dim, in_dim, nv, c->n_sms, c->stream));
+        int grid = 0;
+        pass.sched = c->mv_sched + 2 * (c->mv_launches++ & 1u);  // a launch may overlap the one before it
+        CK(launch_dequant_matvec_4bit(pass, x + (size_t)v0 * in_dim, in_dim, nv, c->n_sms, c->stream,
+                                      nv == 1 ? &maps : nullptr, &grid));
+        if (pass.trace && grid > 0) c->last_launch_ctas = grid;
         c->launches += 1;
     }
     return 0;
@@ -1345,6 +1406,8 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
     } else if (!strcmp(key, "gqa_min_rows")) {
         if (value < 32 || value % 32) return -1;
         c->gqa_min_rows = value;
+    } else if (!strcmp(key, "matvec_overlap")) {
+        c->mv_overlap = value != 0;
     } else if (!strcmp(key, "gqa_coop_merge")) {
         c->gqa_coop = value != 0;
     } else if (!strcmp(key, "gqa_coop_min_parts")) {

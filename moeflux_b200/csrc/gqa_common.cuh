@@ -134,11 +134,6 @@ __device__ __forceinline__ Located locate_tile(const GqaParams &p, int gt, int g
     return L;
 }
 
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 // Optional per-CTA phase trace (thread 0 only): word w of this CTA's record.
 __device__ __forceinline__ void trace_phase(const GqaParams &p, int w) {
     if (p.phase_trace && threadIdx.x == 0 && w < PHASE_TRACE_WORDS)

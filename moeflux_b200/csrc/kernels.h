@@ -246,12 +246,27 @@ struct MatvecBatch {
     const uint16_t *scales[MATVEC_MAX_MATS], *biases[MATVEC_MAX_MATS];
     float *out[MATVEC_MAX_MATS];
     int out_dim[MATVEC_MAX_MATS];
-    int group_begin[MATVEC_MAX_MATS];  // filled by the launcher: first row group of each matrix
-    int total_groups;
+    int group_begin[MATVEC_MAX_MATS];  // filled by the launcher: first row tile of each matrix
+    int total_groups;                  // filled by the launcher: row tiles in all
+    unsigned *sched;                   // two zeroed words in device memory: next tile, finished CTAs (one-vector kernel);
+                                       // consecutive launches must not share them (they may overlap)
+    unsigned *status;                  // the context's status word
+    unsigned spins;                    // poll limit of the kernel's bounded waits
+    int sb_bulk;                       // filled by the launcher: scales and biases travel with the weight stages
+    unsigned long long *trace;         // optional [CTA][PHASE_TRACE_WORDS] nanosecond stamps of the one-vector kernel
+    int overlap;                       // launch as a programmatic dependent launch (the kernel waits by itself)
+};
+// Tensor maps of the batch's matrices for the one-vector kernel: the weights of matrix m as a 2-D byte array
+// [out_dim][in_dim / 2], boxes of 16 rows x 128 bytes, 128-byte swizzle; its scales and its biases as
+// [out_dim][in_dim / 64] 16-bit arrays, boxes of 16 rows x 32 groups, no swizzle (only when in_dim is a multiple of
+// 512: rows of 16-byte multiples).
+struct alignas(64) MatvecMaps {
+    CUtensorMap w[MATVEC_MAX_MATS], sc[MATVEC_MAX_MATS], bi[MATVEC_MAX_MATS];
 };
 size_t dequant_matvec_4bit_smem(int in_dim, int n_vec);
+// maps: needed when n_vec == 1; grid_out (optional): the grid of the one-vector kernel, for readers of its phase trace
 cudaError_t launch_dequant_matvec_4bit(MatvecBatch mb, const float *x, int in_dim, int n_vec, int n_sms,
-                                       cudaStream_t stream);
+                                       cudaStream_t stream, const MatvecMaps *maps = nullptr, int *grid_out = nullptr);
 
 // Per-thread message of the last failure that had no context (ctx.cu).
 std::string &no_ctx_error();

@@ -7,19 +7,11 @@
 //   consecutive input features; scales, biases bf16 [out_dim][in_dim/64];
 //   out[r] = sum_c (nibble(r,c) * scale[r][c/64] + bias[r][c/64]) * x[c].
 //
-// The product is bound by the weight bytes (0.5 B per multiply-add), so the kernel is built
-// around 16-byte weight loads and few instructions per nibble:
-//   * one launch takes up to eight matrices that share x (q/k/v_proj; in_proj_qkv/z/a/b): a launch costs
-//     ~10 us of fixed latency, several times what streaming a 20 MB matrix does;
-//   * x (all n_vec vectors) and the sums of x over each 32-feature half group are staged in
-//     shared memory once per CTA;
-//   * a lane owns 16-byte chunks (32 nibbles, half a group) lane, lane+32, ... of FOUR rows
-//     at a time, so a chunk of x read from shared memory serves four rows;
-//   * a nibble n becomes the float 1 + n/128 by byte surgery (three ALU operations per word of eight nibbles,
-//     then one PRMT per nibble), so per nibble there is about one ALU operation and one FMA;
-//     with D = sum (1 + n/128) x and X = sum x over the chunk,
-//     sum (n s + b) x = 128 s (D - X) + b X   (D - X cancels ~5 bits of the 24).
+// The product is bound by the weight bytes (0.5 B per multiply-add).  One launch takes up to eight matrices that
+// share x (q/k/v_proj; in_proj_qkv/z/a/b): a launch has microseconds of fixed latency, as much as streaming a
+// 20 MB matrix takes.  Two kernels: one vector (the decode step) below, two to eight vectors further down.
 #include <stdint.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -28,170 +20,453 @@ namespace mfc {
 
 namespace {
 
-constexpr int MV_ROWS = 4;      // rows a lane works on at a time
-constexpr int MV_WARPS = 8;     // warps per CTA
-constexpr int MV_THREADS = MV_WARPS * 32;
+// ------------------------------------------------------------------ one vector: streamed tiles, integer tensor cores
+// The product with one vector is the decode step's projection and is bound by the weight bytes, so the kernel is
+// organised around keeping HBM busy and spending next to nothing per nibble:
+//   * persistent CTAs take tiles of 16 rows from a counter in device memory (tiles of a launch cost the same, and the
+//     two CTAs of an SM share the queue, so the SMs finish together);
+//   * a producer warp streams each tile in stages of 16 rows x 1 KiB (32 groups) with cp.async.bulk into a ring of
+//     3-8 stages (64-128 KiB in flight per SM), completion on mbarriers; it starts before x is staged;
+//   * the nibbles go to the tensor core as they are: w & 0x0f0f0f0f and (w >> 4) & 0x0f0f0f0f are the u8 A operands
+//     of mma.sync m16n8k32 (three ALU operations per word of eight nibbles, no offset to cancel afterwards);
+//   * x enters as integers: per group of 64 features, q = rint(x / sx) with sx the power of two that puts the
+//     group's largest |x| below 2^30, written in four balanced base-256 digits (s8: the bytes of q + 0x808080 with
+//     the top bit of the three low bytes flipped).  The four digits of a group are four of the eight B columns, so
+//     two groups share one accumulator and every lane of a quad ends up owning one (group, digit pair):
+//     sum n x = sx * (D0 + 256 D1 + 256^2 D2 + 256^3 D3) is exact integer arithmetic, and the only roundings are
+//     those of x to 31 bits relative to its group's largest element, of the integers to fp32, and of the fp32 sums
+//     over groups (the reference's CPU product rounds every multiply-add);
+//   * scales and biases of a stage (16 rows x 64 bytes each) are two more boxes of the same stage when their rows
+//     are 16-byte aligned (in_dim a multiple of 512), otherwise the consumers read them from global memory;
+//   * the launch is a programmatic dependent launch: its CTAs may start while the kernel before it in the stream is
+//     still draining, and the producer warps request tensor maps and weights at once (the first box of a cold launch
+//     takes 2-3 us to arrive); only the consumers wait for the earlier kernel, before they read x or write results;
+//   * the eight consumer warps split the groups of a stage; their partial sums for a tile meet in shared memory, four
+//     tiles behind one rendezvous, and are added in a fixed order (results do not depend on timing).
+// A NaN or infinity in x makes every output NaN, as it does in the reference's product.
+constexpr int SV_WARPS = 8;                        // consumer warps
+constexpr int SV_THREADS = (SV_WARPS + 1) * 32;    // and the producer warp
+constexpr int SV_ROWS = 16;                        // rows per tile: M of the MMA
+constexpr int SV_CHUNK_GROUPS = 32;                // groups of 64 features per stage
+constexpr int SV_ROW_BYTES = SV_CHUNK_GROUPS * 32; // 1 KiB of a row per stage
+constexpr int SV_BOX_BYTES = SV_ROWS * 128;        // one TMA box: 16 rows x 128 bytes (4 groups), 128-byte swizzle
+constexpr int SV_BOXES = SV_ROW_BYTES / 128;       // 8 boxes per stage: box w holds the groups consumer warp w takes
+constexpr int SV_W_BYTES = SV_BOXES * SV_BOX_BYTES;  // weights of a stage: 16 KiB
+constexpr int SV_SB_ROW = SV_CHUNK_GROUPS * 2;     // scales (or biases) of a row in a stage: 64 bytes
+constexpr int SV_SB_BOX = SV_ROWS * SV_SB_ROW;     // one TMA box of scales (or of biases): 16 rows x 32 groups, 1 KiB
+constexpr int SV_STAGE_BYTES = SV_W_BYTES + 2 * SV_SB_BOX;  // 18 KiB: a multiple of the swizzle atom
+static_assert(SV_STAGE_BYTES % 1024 == 0, "stages keep the 1 KiB alignment of the swizzled boxes");
+constexpr int SV_MAX_STAGES = 8;
+constexpr int SV_BATCH = 4;                        // tiles combined behind one rendezvous
+constexpr int SV_OFF_HDR = 256;                    // after the mbarriers
+constexpr int SV_OFF_SLOT = SV_OFF_HDR + SV_MAX_STAGES * 16;
+constexpr int SV_OFF_RED = SV_OFF_SLOT + 2 * SV_BATCH * 8 + 64;
+constexpr int SV_OFF_XW = SV_OFF_RED + 2 * SV_BATCH * SV_WARPS * SV_ROWS * 4;
+static_assert(SV_OFF_XW % 16 == 0 && SV_OFF_RED % 16 == 0, "alignment of the shared-memory regions");
 
-// The eight nibbles of a packed word as the floats 1 + n/128: with the nibble in the low half of byte 2 and the
-// constant 0x80 in its high half, the bit pattern is 0x3F80'0000 | n << 16.  Two masks put 0x80 | n into every byte
-// (three ALU operations per word), then one PRMT per nibble assembles the float: byte 3 = 0x3F, byte 2 = 0x80 | n.
-__device__ __forceinline__ void nib_floats(uint32_t w, float (&f)[8]) {
-    const uint32_t lo = (w & 0x0f0f0f0fu) | 0x80808080u;         // nibbles 0, 2, 4, 6
-    const uint32_t hi = ((w >> 4) & 0x0f0f0f0fu) | 0x80808080u;  // nibbles 1, 3, 5, 7
-    constexpr uint32_t K = 0x0000003fu;                          // byte 4 of the PRMT pair = 0x3F, bytes 5-7 = 0
-    f[0] = __uint_as_float(__byte_perm(lo, K, 0x4055));
-    f[1] = __uint_as_float(__byte_perm(hi, K, 0x4055));
-    f[2] = __uint_as_float(__byte_perm(lo, K, 0x4155));
-    f[3] = __uint_as_float(__byte_perm(hi, K, 0x4155));
-    f[4] = __uint_as_float(__byte_perm(lo, K, 0x4255));
-    f[5] = __uint_as_float(__byte_perm(hi, K, 0x4255));
-    f[6] = __uint_as_float(__byte_perm(lo, K, 0x4355));
-    f[7] = __uint_as_float(__byte_perm(hi, K, 0x4355));
+__host__ __device__ inline size_t sv_fixed_bytes(int in_dim) {
+    const size_t n_groups = (size_t)(in_dim >> 6);
+    return ((size_t)SV_OFF_XW + n_groups * 16 + n_groups * 256 + 1023) & ~(size_t)1023;
 }
 
-template <int NV> struct MvDepth { static constexpr int value = NV <= 2 ? 2 : 1; };  // 16-byte chunks per row a lane has in flight
-
-template <int NV>
-__global__ void __launch_bounds__(MV_THREADS, NV <= 2 ? 2 : 1)
-dequant_matvec_4bit_kernel(const __grid_constant__ MatvecBatch mb, const float *__restrict__ x, int in_dim) {
-    extern __shared__ __align__(16) float smem_f[];
-    // [NV][in_dim / 32][36]: a chunk of 32 features padded to 36 floats, so that lanes reading consecutive chunks
-    // (128 bytes apart unpadded: one bank) spread over the banks
-    float *xs = smem_f;
-    const int in_dim_p = (in_dim >> 5) * 36;
-    float *xh = smem_f + NV * in_dim_p;    // [NV][in_dim / 32]: sums of x over half groups
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_chunks = in_dim >> 5;      // 16-byte chunks per row
-    const int n_groups = in_dim >> 6;
-    const int row_stride_w = in_dim >> 3;  // words per row
-
-    constexpr int MV_DEPTH = MvDepth<NV>::value;
-    struct Chunk {
-        uint4 w[MV_ROWS];
-        uint16_t sc[MV_ROWS], bi[MV_ROWS];
-    };
-    // row group rg (MV_ROWS rows of one matrix) -> matrix and first row; a group never straddles two matrices
-    auto locate = [&](int rg, int &m, int &row0) {
-        m = 0;
-#pragma unroll
-        for (int k = 1; k < MATVEC_MAX_MATS; k++)
-            if (k < mb.n_mat && rg >= mb.group_begin[k]) m = k;
-        row0 = (rg - mb.group_begin[m]) * MV_ROWS;
-    };
-    auto load_chunk = [&](int m, int row0, int c, Chunk &ch) {
-        const uint32_t *W = mb.w[m];
-        const uint16_t *scales = mb.scales[m], *biases = mb.biases[m];
-        const int out_dim = mb.out_dim[m];
-#pragma unroll
-        for (int r = 0; r < MV_ROWS; r++) {
-            const int row = min(row0 + r, out_dim - 1);  // rows past the end repeat the last one; not stored
-            ch.w[r] = __ldg(reinterpret_cast<const uint4 *>(W + (size_t)row * row_stride_w + 4 * c));
-            ch.sc[r] = __ldg(scales + (size_t)row * n_groups + (c >> 1));
-            ch.bi[r] = __ldg(biases + (size_t)row * n_groups + (c >> 1));
-        }
-    };
-    // the first weights are requested before x is staged, so that their latency runs under the staging
-    const int rg_first = blockIdx.x * MV_WARPS + warp;
-    Chunk first;
-    if (rg_first < mb.total_groups && lane < n_chunks) {
-        int m, row0;
-        locate(rg_first, m, row0);
-        load_chunk(m, row0, lane, first);
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D(16x8,s32) += A(16x32,u8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm(  // registers only: left to the compiler's scheduling
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// One poll of an mbarrier phase that lets the hardware park the thread for up to `ns` nanoseconds (it resumes when the
+// phase completes): a waiting warp then spends no issue slots, which the warps that have data need.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t *bar, unsigned parity, unsigned ns) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait (each poll parks for up to a microsecond) that also gives up when another warp of the CTA has.
+__device__ __forceinline__ bool sv_wait(uint64_t *bar, unsigned parity, unsigned spins, volatile int *abort_flag) {
+    for (unsigned i = 0; i < spins; i++) {
+        if (mbar_try_wait_parked(bar, parity, 1000u)) return true;
+        if ((i & 15u) == 15u && *abort_flag) return false;
     }
+    return false;
+}
 
-    // x and, from the same registers, the sums over 32-feature half groups (8 consecutive threads hold one)
-    const int n_f4 = NV * (in_dim >> 2);
-    for (int i0 = 0; i0 < n_f4; i0 += 4 * MV_THREADS) {  // four loads in flight per thread
-        float4 v[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int i = i0 + u * MV_THREADS + tid;
-            v[u] = i < n_f4 ? __ldg(reinterpret_cast<const float4 *>(x) + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+// Optional per-CTA phase stamps (nanoseconds): 0 entry, 1 barriers set up, 2 x staged (this thread), 3 x staged (all),
+// 4 first stage arrived, 5 last stage consumed, 6 results stored; 7 (producer) first ring of stages issued.
+__device__ __forceinline__ void sv_trace(const MatvecBatch &mb, int w) {
+    if (mb.trace) mb.trace[(size_t)blockIdx.x * PHASE_TRACE_WORDS + w] = global_timer_ns();
+}
+
+__global__ void __launch_bounds__(SV_THREADS, 2)
+dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const __grid_constant__ MatvecBatch mb,
+                                  const float *__restrict__ x, int in_dim, int n_stages) {
+    extern __shared__ __align__(16) uint8_t sv_smem_raw[];
+    uint8_t *sv_smem = sv_smem_raw + ((1024u - (smem_u32(sv_smem_raw) & 1023u)) & 1023u);  // swizzled boxes: 1 KiB alignment
+    uint64_t *full = reinterpret_cast<uint64_t *>(sv_smem);         // [SV_MAX_STAGES]
+    uint64_t *empty = full + SV_MAX_STAGES;                         // [SV_MAX_STAGES]
+    uint64_t *red_bar = empty + SV_MAX_STAGES;                      // rendezvous of the consumer warps
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(red_bar + 1);
+    int4 *hdr = reinterpret_cast<int4 *>(sv_smem + SV_OFF_HDR);     // per stage: {tile, matrix, first row, chunk}
+    int2 *slot_info = reinterpret_cast<int2 *>(sv_smem + SV_OFF_SLOT);  // [2][SV_BATCH]: {matrix, first row}
+    float *red = reinterpret_cast<float *>(sv_smem + SV_OFF_RED);   // [2][SV_BATCH][SV_WARPS][SV_ROWS]
+    float4 *xw = reinterpret_cast<float4 *>(sv_smem + SV_OFF_XW);   // per group: {sx, sx * 256^2, sum of x, -}
+    const int n_groups = in_dim >> 6;
+    uint8_t *xb = reinterpret_cast<uint8_t *>(xw + n_groups);       // per group [digit][t] x {b0, b1 of MMA 0; of MMA 1}
+    uint8_t *stages = sv_smem + sv_fixed_bytes(in_dim);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row_bytes = in_dim >> 1;
+    const int n_chunks = (n_groups + SV_CHUNK_GROUPS - 1) / SV_CHUNK_GROUPS;
+    const unsigned spins = mb.spins ? mb.spins : (1u << 21);  // polls of up to a microsecond each
+
+    if (tid == 0) sv_trace(mb, 0);
+    if (tid == 0) {
+        for (int s = 0; s < n_stages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], SV_WARPS);
         }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int i = i0 + u * MV_THREADS + tid;
-            if (i < n_f4) {
-                const int vec = i / (in_dim >> 2), f = (i - vec * (in_dim >> 2)) * 4;  // feature index of the first float
-                *reinterpret_cast<float4 *>(xs + (size_t)vec * in_dim_p + (f >> 5) * 36 + (f & 31)) = v[u];
-            }
-            float sm = (v[u].x + v[u].y) + (v[u].z + v[u].w);
-            sm += __shfl_xor_sync(0xffffffffu, sm, 1);
-            sm += __shfl_xor_sync(0xffffffffu, sm, 2);
-            sm += __shfl_xor_sync(0xffffffffu, sm, 4);
-            if ((tid & 7) == 0 && i < n_f4) xh[i >> 3] = sm;
-        }
+        mbar_init(red_bar, SV_WARPS);
+        *abort_flag = 0;
+        mbar_fence_init();
     }
     __syncthreads();
+    if (tid == 0) sv_trace(mb, 1);
 
-    // D = sum over the chunk of (1 + n/128) x, for MV_ROWS rows and NV vectors
-    auto chunk_dot = [&](const Chunk &ch, int c, float (&acc)[MV_ROWS][NV]) {
-        float d[MV_ROWS][NV];
-#pragma unroll
-        for (int r = 0; r < MV_ROWS; r++)
-#pragma unroll
-            for (int v = 0; v < NV; v++) d[r][v] = 0.0f;
-#pragma unroll
-        for (int q = 0; q < 4; q++) {  // one packed word = 8 features at a time
-            float xv[NV][8];
-#pragma unroll
-            for (int v = 0; v < NV; v++) {
-                const float4 a = *reinterpret_cast<const float4 *>(xs + (size_t)v * in_dim_p + 36 * c + 8 * q);
-                const float4 b = *reinterpret_cast<const float4 *>(xs + (size_t)v * in_dim_p + 36 * c + 8 * q + 4);
-                xv[v][0] = a.x; xv[v][1] = a.y; xv[v][2] = a.z; xv[v][3] = a.w;
-                xv[v][4] = b.x; xv[v][5] = b.y; xv[v][6] = b.z; xv[v][7] = b.w;
-            }
-#pragma unroll
-            for (int r = 0; r < MV_ROWS; r++) {
-                const uint32_t word = q == 0 ? ch.w[r].x : q == 1 ? ch.w[r].y : q == 2 ? ch.w[r].z : ch.w[r].w;
-                float f[8];
-                nib_floats(word, f);
-#pragma unroll
-                for (int v = 0; v < NV; v++)
-#pragma unroll
-                    for (int j = 0; j < 8; j++) d[r][v] = fmaf(f[j], xv[v][j], d[r][v]);
+    if (warp == SV_WARPS) {
+        // ---------------- producer: tiles from the launch-wide counter, stages into the ring
+        if (lane < mb.n_mat) {
+            prefetch_tmap(&maps.w[lane]);
+            if (mb.sb_bulk) {
+                prefetch_tmap(&maps.sc[lane]);
+                prefetch_tmap(&maps.bi[lane]);
             }
         }
+        unsigned it = 0;  // stages issued
+        int st = 0;       // it modulo the ring, and the parity of the ring's previous turn
+        unsigned prev_phase = 1;
+        bool ok = true;
+        int tile = blockIdx.x;  // the first tile is fixed; the rest come from the counter, asked for one tile ahead
+        int tile_next = 0;      // (the answer of an atomic takes a microsecond: as long as streaming a tile)
+        if (lane == 0) tile_next = (int)(gridDim.x + atomicAdd(mb.sched, 1u));
+        while (ok && tile < mb.total_groups) {
+            int m = 0;
 #pragma unroll
-        for (int v = 0; v < NV; v++) {
-            const float xsum = xh[v * n_chunks + c];
-#pragma unroll
-            for (int r = 0; r < MV_ROWS; r++)
-                acc[r][v] += fmaf(128.0f * bf16_bits_to_f32(ch.sc[r]), d[r][v] - xsum, bf16_bits_to_f32(ch.bi[r]) * xsum);
+            for (int k = 1; k < MATVEC_MAX_MATS; k++)
+                if (k < mb.n_mat && tile >= mb.group_begin[k]) m = k;
+            const int row0 = (tile - mb.group_begin[m]) * SV_ROWS;
+            for (int chunk = 0; chunk < n_chunks; chunk++) {
+                if (it >= (unsigned)n_stages) ok = sv_wait(&empty[st], prev_phase, spins, abort_flag);
+                if (!ok) break;
+                const int bytes = min(SV_ROW_BYTES, row_bytes - chunk * SV_ROW_BYTES);  // of a row in this stage
+                const int n_boxes = (bytes + 127) >> 7;
+                if (lane == 0) {
+                    hdr[st] = make_int4(tile, m, row0, chunk);
+                    mbar_expect_tx(&full[st], (unsigned)(n_boxes * SV_BOX_BYTES + (mb.sb_bulk ? 2 * SV_SB_BOX : 0)));
+                }
+                __syncwarp();
+                uint8_t *dst = stages + (size_t)st * SV_STAGE_BYTES;
+                // box b: bytes [128 b, 128 b + 128) of the stage's 1 KiB of rows row0 .. row0 + 15 (rows and bytes
+                // past the matrix arrive as zeros); then the rows' scales and biases of the stage's 32 groups
+                if (lane < n_boxes)
+                    tma_load_2d(dst + lane * SV_BOX_BYTES, &maps.w[m], chunk * SV_ROW_BYTES + lane * 128, row0, &full[st]);
+                else if (mb.sb_bulk && lane == 8)
+                    tma_load_2d(dst + SV_W_BYTES, &maps.sc[m], chunk * SV_CHUNK_GROUPS, row0, &full[st]);
+                else if (mb.sb_bulk && lane == 9)
+                    tma_load_2d(dst + SV_W_BYTES + SV_SB_BOX, &maps.bi[m], chunk * SV_CHUNK_GROUPS, row0, &full[st]);
+                it++;
+                if (++st == n_stages) {
+                    st = 0;
+                    prev_phase ^= 1u;
+                }
+            }
+            if (!ok) break;
+            tile = __shfl_sync(0xffffffffu, tile_next, 0);
+            if (lane == 0 && tile < mb.total_groups) tile_next = (int)(gridDim.x + atomicAdd(mb.sched, 1u));
         }
+        if (ok) {  // the stage after the last one carries "no more work"
+            if (it >= (unsigned)n_stages) ok = sv_wait(&empty[st], prev_phase, spins, abort_flag);
+            if (ok && lane == 0) {
+                hdr[st] = make_int4(-1, 0, 0, 0);
+                mbar_arrive(&full[st]);
+            }
+        }
+        if (!ok) {
+            // gave up (or a consumer did): no further copies are issued; the copies still in flight write into this
+            // CTA's shared memory, so they are waited for (bounded again) before the warp leaves
+            if (lane == 0) {
+                *abort_flag = 1;
+                atomicOr(mb.status, STATUS_TMA_TIMEOUT);
+            }
+            const unsigned first = it > (unsigned)n_stages ? it - (unsigned)n_stages : 0u;
+            for (unsigned k = first; k < it; k++)
+                mbar_wait_bounded(&full[k % (unsigned)n_stages], (k / (unsigned)n_stages) & 1u, spins);
+        }
+        // the last CTA to finish puts the counters back for the next launch
+        if (lane == 0) {
+            __threadfence();
+            if (atomicAdd(mb.sched + 1, 1u) == gridDim.x - 1) {
+                mb.sched[0] = 0u;
+                mb.sched[1] = 0u;
+                __threadfence();
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers: x as integer digits in B-fragment order, then the stream of stages
+    // x is an earlier kernel's result: wait for the kernels before this one to finish and their writes to be visible.
+    // Only then may the kernel after this one start (it uses the tile counters this kernel's predecessor used).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    {
+        const int n_words = in_dim >> 3;  // a thread handles the 8 features of one packed word; 8 threads hold a group
+        constexpr int XU = 4;             // words per thread whose loads are in flight together
+        for (int wq0 = 0; wq0 < n_words; wq0 += SV_WARPS * 32 * XU) {
+            float4 va[XU], vb[XU];
+#pragma unroll
+            for (int u = 0; u < XU; u++) {
+                const int wq = wq0 + u * SV_WARPS * 32 + tid;
+                const bool in = wq < n_words;
+                va[u] = in ? __ldg(reinterpret_cast<const float4 *>(x) + 2 * wq) : make_float4(0.f, 0.f, 0.f, 0.f);
+                vb[u] = in ? __ldg(reinterpret_cast<const float4 *>(x) + 2 * wq + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < XU; u++) {
+                const int wq = wq0 + u * SV_WARPS * 32 + tid;
+                if (wq0 + u * SV_WARPS * 32 >= n_words) break;  // uniform over the CTA
+                const bool in = wq < n_words;
+                const float v[8] = {va[u].x, va[u].y, va[u].z, va[u].w, vb[u].x, vb[u].y, vb[u].z, vb[u].w};
+                float sm = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+                uint32_t ebits = 0;  // largest exponent field of the group: the scale, and NaN / infinity (255)
+#pragma unroll
+                for (int j = 0; j < 8; j++) ebits = max(ebits, (__float_as_uint(v[j]) >> 23) & 0xffu);
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) {
+                    ebits = max(ebits, __shfl_xor_sync(0xffffffffu, ebits, o));
+                    sm += __shfl_xor_sync(0xffffffffu, sm, o);
+                }
+                const bool finite = ebits != 255u;
+                const uint32_t e = min(max(ebits, 30u), 254u);
+                const float inv = __uint_as_float((283u - e) << 23);  // 2^(29 - exponent): |x| * inv < 2^30
+                float sx = __uint_as_float((e - 29u) << 23);
+                if (!finite) sx = __uint_as_float(0x7fc00000u);
+                // the four s8 digits of an element are the bytes of this word
+                // (features 1, 3, 5, 7 of a word enter divided by 16: their nibbles go to the tensor core as 16 n)
+                const float inv_odd = inv * 0.0625f;
+                uint32_t dg[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    dg[j] = finite ? ((uint32_t)(__float2int_rn(v[j] * ((j & 1) ? inv_odd : inv)) + 0x00808080) ^ 0x00808080u) : 0u;
+                // 4 x 4 byte transposes: digit c of features 0, 2, 4, 6 (the word's low nibbles) and of 1, 3, 5, 7
+                uint32_t b0[4], b1[4];
+                {
+                    const uint32_t l01 = __byte_perm(dg[0], dg[2], 0x5140), h01 = __byte_perm(dg[0], dg[2], 0x7362);
+                    const uint32_t l23 = __byte_perm(dg[4], dg[6], 0x5140), h23 = __byte_perm(dg[4], dg[6], 0x7362);
+                    b0[0] = __byte_perm(l01, l23, 0x5410);
+                    b0[1] = __byte_perm(l01, l23, 0x7632);
+                    b0[2] = __byte_perm(h01, h23, 0x5410);
+                    b0[3] = __byte_perm(h01, h23, 0x7632);
+                }
+                {
+                    const uint32_t l01 = __byte_perm(dg[1], dg[3], 0x5140), h01 = __byte_perm(dg[1], dg[3], 0x7362);
+                    const uint32_t l23 = __byte_perm(dg[5], dg[7], 0x5140), h23 = __byte_perm(dg[5], dg[7], 0x7362);
+                    b1[0] = __byte_perm(l01, l23, 0x5410);
+                    b1[1] = __byte_perm(l01, l23, 0x7632);
+                    b1[2] = __byte_perm(h01, h23, 0x5410);
+                    b1[3] = __byte_perm(h01, h23, 0x7632);
+                }
+                if (in) {
+                    const int gi = wq >> 3, wl = wq & 7;
+                    uint8_t *dst = xb + (size_t)gi * 256 + (wl >> 1) * 16 + (wl & 1) * 8;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) *reinterpret_cast<uint2 *>(dst + c * 64) = make_uint2(b0[c], b1[c]);
+                    if (wl == 0) xw[gi] = make_float4(sx, sx * 65536.0f, sm, 0.0f);
+                }
+            }
+        }
+    }
+    if (tid == 0) sv_trace(mb, 2);
+    asm volatile("bar.sync 1, %0;" ::"n"(SV_WARPS * 32) : "memory");
+    if (tid == 0) sv_trace(mb, 3);
+
+    const int g = lane >> 2, t = lane & 3;
+    const int my_sel = t >> 1, my_h = t & 1;  // which group of a pair, and which digit pair, this lane finishes
+    const int b_sel = g >> 2, b_c = g & 3;    // which group and digit this lane's B column carries
+    constexpr uint32_t NIB = 0x0f0f0f0fu;
+    float tot0 = 0.0f, tot1 = 0.0f;           // rows g and g + 8 of the current tile
+    int slot = 0, buf = 0;
+    unsigned red_parity = 0;
+    bool failed = false;
+
+    auto flush = [&]() -> bool {
+        // partial sums of `slot` tiles are in red[buf]: meet, then add the eight warps' parts in a fixed order
+        __syncwarp();
+        if (lane == 0) mbar_arrive(red_bar);
+        if (!sv_wait(red_bar, red_parity, spins, abort_flag)) return false;
+        red_parity ^= 1u;
+        if (tid < slot * SV_ROWS) {
+            const int s = tid >> 4, r = tid & 15;
+            const int2 info = slot_info[buf * SV_BATCH + s];
+            const float *src = red + ((size_t)(buf * SV_BATCH + s) * SV_WARPS) * SV_ROWS + r;
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < SV_WARPS; w++) sum += src[w * SV_ROWS];
+            if (info.y + r < mb.out_dim[info.x]) mb.out[info.x][info.y + r] = sum;
+        }
+        buf ^= 1;
+        slot = 0;
+        return true;
     };
 
-    for (int rg = rg_first; rg < mb.total_groups; rg += gridDim.x * MV_WARPS) {
-        int m, row0;
-        locate(rg, m, row0);
-        float acc[MV_ROWS][NV];
+    // lane constants of the stage loop
+    // Row g of the MMA is row rho(g) = (g >> 1) | (g & 1) << 2 of the tile (and g + 8 is rho(g) + 8): the eight lanes
+    // that shared memory serves together (g = 2q, 2q + 1; t = 0..3) then read rows q and q + 4, whose 16-byte
+    // chunks the 128-byte swizzle stores in opposite halves of the row: no bank is asked twice.
+    const int rho = (g >> 1) | ((g & 1) << 2);
+    // Lane (g, t) reads chunk 4 u + t of row rho (16 bytes = four words = half a group) for pair u of the warp's box.
+    // MMA j of the pair takes word j of every lane: its k slots of lanes t = 0, 1 are features of the pair's first
+    // group, those of lanes t = 2, 3 features of the second; the B columns 0-3 hold the first group's digits of x and
+    // are zero on the second group's k slots, columns 4-7 the other way round.
+    int a_off[2];
 #pragma unroll
-        for (int r = 0; r < MV_ROWS; r++)
+    for (int u = 0; u < 2; u++) a_off[u] = warp * SV_BOX_BYTES + rho * 128 + (((4 * u + t) ^ rho) << 4);
+    // B operand of lane (g, t): column g = digit b_c of group b_sel of the pair, on the k slots of lane t: real
+    // for the lanes whose t belongs to that group, zero (never loaded) for the others
+    const bool b_real = b_sel == (t >> 1);
+    const uint8_t *xb_lane = xb + (4 * warp + b_sel) * 256 + b_c * 64 + (t & 1) * 32;
+    const int sb_lane = SV_W_BYTES + rho * SV_SB_ROW + 8 * warp;  // scales of row rho, the warp's four groups
+    const float *xw_lane = reinterpret_cast<const float *>(xw + 4 * warp + my_sel);
+    uint4 bb[2][2];  // [pair][MMAs 0-1 | 2-3]: {b0, b1} of two MMAs each; stays zero in the lanes that never load
 #pragma unroll
-            for (int v = 0; v < NV; v++) acc[r][v] = 0.0f;
-        // MV_DEPTH chunks per row in flight: the loads of a round are all issued before the first is used
-        for (int c0 = lane; c0 < n_chunks; c0 += 32 * MV_DEPTH) {
-            Chunk ch[MV_DEPTH];
+    for (int u = 0; u < 2; u++) bb[u][0] = bb[u][1] = make_uint4(0u, 0u, 0u, 0u);
+
+    int st = 0;
+    unsigned phase = 0;
+    long long wait_cycles = 0;
+    for (bool first = true;; first = false) {
+        const long long w0 = clock64();
+        if (!sv_wait(&full[st], phase, spins, abort_flag)) {
+            failed = true;
+            break;
+        }
+        wait_cycles += clock64() - w0;
+        const int4 h = hdr[st];
+        if (first && tid == 0) sv_trace(mb, 4);
+        if (h.x < 0) break;
+        const int m = h.y, row0 = h.z, chunk = h.w;
+        const int groups_here = min(SV_CHUNK_GROUPS, n_groups - chunk * SV_CHUNK_GROUPS);
+        const uint8_t *sbase = stages + (size_t)st * SV_STAGE_BYTES;
+        if (4 * warp < groups_here) {  // the warp's box was loaded (bytes of it past the row's end arrived as zeros)
+            // this lane's scale and bias of the two pairs
+            uint16_t s_lo[2], s_hi[2], c_lo[2], c_hi[2];
+            if (mb.sb_bulk) {
+                // the warp's four groups are 8 bytes of a row: one read per row and array, then this lane's two
+                const uint8_t *sb = sbase + sb_lane;
+                const uint2 a = *reinterpret_cast<const uint2 *>(sb);
+                const uint2 b = *reinterpret_cast<const uint2 *>(sb + 8 * SV_SB_ROW);
+                const uint2 c = *reinterpret_cast<const uint2 *>(sb + SV_SB_BOX);
+                const uint2 e8 = *reinterpret_cast<const uint2 *>(sb + SV_SB_BOX + 8 * SV_SB_ROW);
+                const int sh = 16 * my_sel;  // groups 4w + my_sel (low word) and 4w + 2 + my_sel (high word)
+                s_lo[0] = (uint16_t)(a.x >> sh);
+                s_lo[1] = (uint16_t)(a.y >> sh);
+                s_hi[0] = (uint16_t)(b.x >> sh);
+                s_hi[1] = (uint16_t)(b.y >> sh);
+                c_lo[0] = (uint16_t)(c.x >> sh);
+                c_lo[1] = (uint16_t)(c.y >> sh);
+                c_hi[0] = (uint16_t)(e8.x >> sh);
+                c_hi[1] = (uint16_t)(e8.y >> sh);
+            } else {
+                const int out_dim = mb.out_dim[m];
+                const int r_lo = min(row0 + rho, out_dim - 1), r_hi = min(row0 + rho + 8, out_dim - 1);
+                const size_t col = (size_t)chunk * SV_CHUNK_GROUPS + 4 * warp + my_sel;
 #pragma unroll
-            for (int k = 0; k < MV_DEPTH; k++) {
-                const int c = c0 + 32 * k;
-                if (c >= n_chunks) break;
-                if (k == 0 && c0 == lane && rg == rg_first) ch[0] = first;
-                else load_chunk(m, row0, c, ch[k]);
+                for (int u = 0; u < 2; u++) {
+                    const size_t cc = min(col + 2 * u, (size_t)n_groups - 1);
+                    s_lo[u] = __ldg(mb.scales[m] + (size_t)r_lo * n_groups + cc);
+                    s_hi[u] = __ldg(mb.scales[m] + (size_t)r_hi * n_groups + cc);
+                    c_lo[u] = __ldg(mb.biases[m] + (size_t)r_lo * n_groups + cc);
+                    c_hi[u] = __ldg(mb.biases[m] + (size_t)r_hi * n_groups + cc);
+                }
+            }
+            const uint8_t *xb_here = xb_lane + (size_t)chunk * (SV_CHUNK_GROUPS * 256);
+            int d[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}}, e[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};  // two chains per pair
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const uint4 wa = *reinterpret_cast<const uint4 *>(sbase + a_off[u]);
+                const uint4 wb = *reinterpret_cast<const uint4 *>(sbase + a_off[u] + 8 * 128);
+                if (b_real) {
+                    bb[u][0] = *reinterpret_cast<const uint4 *>(xb_here + u * 512);
+                    bb[u][1] = *reinterpret_cast<const uint4 *>(xb_here + u * 512 + 16);
+                }
+                mma_u8s8_16832(d[u], wa.x & NIB, wb.x & NIB, wa.x & ~NIB, wb.x & ~NIB, bb[u][0].x, bb[u][0].y);
+                mma_u8s8_16832(e[u], wa.y & NIB, wb.y & NIB, wa.y & ~NIB, wb.y & ~NIB, bb[u][0].z, bb[u][0].w);
+                mma_u8s8_16832(d[u], wa.z & NIB, wb.z & NIB, wa.z & ~NIB, wb.z & ~NIB, bb[u][1].x, bb[u][1].y);
+                mma_u8s8_16832(e[u], wa.w & NIB, wb.w & NIB, wa.w & ~NIB, wb.w & ~NIB, bb[u][1].z, bb[u][1].w);
             }
 #pragma unroll
-            for (int k = 0; k < MV_DEPTH; k++) {
-                const int c = c0 + 32 * k;
-                if (c < n_chunks) chunk_dot(ch[k], c, acc);
+            for (int u = 0; u < 2; u++)
+#pragma unroll
+                for (int k = 0; k < 4; k++) d[u][k] += e[u][k];
+            const float *xwv = xw_lane + (size_t)chunk * (SV_CHUNK_GROUPS * 4);
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                if (4 * warp + 2 * u + my_sel < groups_here) {  // (always, but for a ragged last stage)
+                    const float wgt = xwv[8 * u + my_h];
+                    const float f0 = (float)(d[u][0] + d[u][1] * 256) * wgt;  // row rho:     digits (2h, 2h+1) of the group
+                    const float f1 = (float)(d[u][2] + d[u][3] * 256) * wgt;  // row rho + 8
+                    tot0 = fmaf(bf16_bits_to_f32(s_lo[u]), f0, tot0);
+                    tot1 = fmaf(bf16_bits_to_f32(s_hi[u]), f1, tot1);
+                    if (my_h == 0) {
+                        const float xs = xwv[8 * u + 2];
+                        tot0 = fmaf(bf16_bits_to_f32(c_lo[u]), xs, tot0);
+                        tot1 = fmaf(bf16_bits_to_f32(c_hi[u]), xs, tot1);
+                    }
+                }
             }
         }
-#pragma unroll
-        for (int r = 0; r < MV_ROWS; r++)
-#pragma unroll
-            for (int v = 0; v < NV; v++) {
-                const float s = warp_sum(acc[r][v]);
-                if (lane == 0 && row0 + r < mb.out_dim[m]) mb.out[m][(size_t)v * mb.out_dim[m] + row0 + r] = s;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+        if (++st == n_stages) {
+            st = 0;
+            phase ^= 1u;
+        }
+        if (chunk == n_chunks - 1) {
+            tot0 += __shfl_xor_sync(0xffffffffu, tot0, 1);
+            tot1 += __shfl_xor_sync(0xffffffffu, tot1, 1);
+            tot0 += __shfl_xor_sync(0xffffffffu, tot0, 2);
+            tot1 += __shfl_xor_sync(0xffffffffu, tot1, 2);
+            float *dst = red + ((size_t)(buf * SV_BATCH + slot) * SV_WARPS + warp) * SV_ROWS;
+            if (t == 0) {
+                dst[rho] = tot0;
+                dst[rho + 8] = tot1;
             }
+            if (tid == 0) slot_info[buf * SV_BATCH + slot] = make_int2(m, row0);
+            tot0 = tot1 = 0.0f;
+            if (++slot == SV_BATCH && !flush()) {
+                failed = true;
+                break;
+            }
+        }
+    }
+    if (tid == 0) sv_trace(mb, 5);
+    if (tid == 0 && mb.trace) mb.trace[(size_t)blockIdx.x * PHASE_TRACE_WORDS + 7] = (unsigned long long)wait_cycles;
+    if (!failed && slot > 0 && !flush()) failed = true;
+    if (tid == 0) sv_trace(mb, 6);
+    if (failed && lane == 0) {
+        *abort_flag = 1;
+        atomicOr(mb.status, STATUS_TMA_TIMEOUT);
     }
 }
 
@@ -403,55 +678,77 @@ cudaError_t launch_mma(MatvecBatch mb, const float *x, int in_dim, int n_sms, cu
     return cudaGetLastError();
 }
 
-template <int NV>
-cudaError_t launch_nv(const MatvecBatch &mb, const float *x, int in_dim, int n_sms, cudaStream_t stream) {
-    const size_t smem = sizeof(float) * (size_t)NV * ((in_dim >> 5) * 36 + in_dim / 32);
-    // the shared-memory opt-in and the occupancy query are host calls of several microseconds: once per size
-    static thread_local size_t cfg_smem[16] = {0};
-    static thread_local int cfg_dev[16], cfg_per_sm[16];
+// Stages of the ring and CTAs per SM for a given in_dim: two CTAs per SM when each can still hold three stages.
+void sv_plan(int in_dim, size_t smem_optin, int &n_stages, int &ctas_per_sm) {
+    const size_t fixed = sv_fixed_bytes(in_dim) + 1024;  // with the alignment slack
+    const size_t half = smem_optin / 2 > 2048 ? smem_optin / 2 - 2048 : 0;  // room for the per-CTA reserve of the SM
+    ctas_per_sm = 2;
+    long long n = half > fixed ? (long long)((half - fixed) / SV_STAGE_BYTES) : 0;
+    if (n < 3) {
+        ctas_per_sm = 1;
+        n = smem_optin > fixed ? (long long)((smem_optin - fixed) / SV_STAGE_BYTES) : 0;
+    }
+    n_stages = (int)(n > SV_MAX_STAGES ? SV_MAX_STAGES : n);
+}
+
+cudaError_t launch_stream(MatvecBatch mb, const MatvecMaps *maps, const float *x, int in_dim, int n_sms, cudaStream_t stream,
+                          int *grid_out) {
+    if (!maps) return cudaErrorInvalidValue;
+    static thread_local bool configured[64] = {false};  // per device: the opt-in is a host call of several microseconds
+    static thread_local int optin[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    int slot = -1;
-    for (int i = 0; i < 16; i++)
-        if (cfg_smem[i] == smem && cfg_dev[i] == dev) slot = i;
-    if (slot < 0) {
-        cudaError_t e = cudaFuncSetAttribute(dequant_matvec_4bit_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(227 * 1024));
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        cudaError_t e = cudaDeviceGetAttribute(&optin[dev], cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         if (e != cudaSuccess) return e;
-        int per_sm = 1;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dequant_matvec_4bit_kernel<NV>, MV_THREADS, smem);
+        e = cudaFuncSetAttribute(dequant_matvec_4bit_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin[dev]);
         if (e != cudaSuccess) return e;
-        static thread_local int next = 0;
-        slot = next;
-        next = (next + 1) & 15;
-        cfg_smem[slot] = smem;
-        cfg_dev[slot] = dev;
-        cfg_per_sm[slot] = per_sm < 1 ? 1 : per_sm;
+        configured[dev] = true;
     }
-    int grid = (mb.total_groups + MV_WARPS - 1) / MV_WARPS;
-    if (grid > n_sms * cfg_per_sm[slot]) grid = n_sms * cfg_per_sm[slot];  // CTAs stride over the rows: x is staged once per CTA
-    dequant_matvec_4bit_kernel<NV><<<grid, MV_THREADS, smem, stream>>>(mb, x, in_dim);
-    return cudaGetLastError();
+    int n_stages = 0, ctas_per_sm = 1;
+    sv_plan(in_dim, (size_t)optin[dev], n_stages, ctas_per_sm);
+    if (n_stages < 2 || !mb.sched || !mb.status) return cudaErrorInvalidValue;
+    int tiles = 0;  // here group_begin counts tiles of 16 rows per matrix
+    for (int m = 0; m < mb.n_mat; m++) {
+        mb.group_begin[m] = tiles;
+        tiles += (mb.out_dim[m] + SV_ROWS - 1) / SV_ROWS;
+    }
+    mb.total_groups = tiles;
+    mb.sb_bulk = in_dim % 512 == 0;  // rows of scales are then multiples of 16 bytes
+    for (int m = 0; m < mb.n_mat; m++)
+        if (((uintptr_t)mb.scales[m] | (uintptr_t)mb.biases[m]) & 15) mb.sb_bulk = 0;
+    int grid = n_sms * ctas_per_sm;
+    if (grid > tiles) grid = tiles;
+    const size_t smem = 1024 + sv_fixed_bytes(in_dim) + (size_t)n_stages * SV_STAGE_BYTES;  // 1 KiB: alignment slack
+    if (grid_out) *grid_out = grid;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(SV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    memset(&attr, 0, sizeof(attr));
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start before the kernel ahead of it has drained
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = mb.overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, dequant_matvec_4bit_stream_kernel, *maps, mb, x, in_dim, n_stages);
 }
 
 }  // namespace
 
 size_t dequant_matvec_4bit_smem(int in_dim, int n_vec) {
-    if (n_vec == 1) return sizeof(float) * (size_t)((in_dim >> 5) * 36 + in_dim / 32);
+    if (n_vec == 1) return 1024 + sv_fixed_bytes(in_dim) + 2 * (size_t)SV_STAGE_BYTES;  // the least the ring works with
     return mma_smem(in_dim, n_vec);
 }
 
 cudaError_t launch_dequant_matvec_4bit(MatvecBatch mb, const float *x, int in_dim, int n_vec, int n_sms,
-                                       cudaStream_t stream) {
+                                       cudaStream_t stream, const MatvecMaps *maps, int *grid_out) {
     if (mb.n_mat < 1 || mb.n_mat > MATVEC_MAX_MATS) return cudaErrorInvalidValue;
-    int g = 0;
-    for (int m = 0; m < mb.n_mat; m++) {
-        mb.group_begin[m] = g;
-        g += (mb.out_dim[m] + MV_ROWS - 1) / MV_ROWS;
-    }
-    mb.total_groups = g;
     switch (n_vec) {
-        case 1: return launch_nv<1>(mb, x, in_dim, n_sms, stream);
+        case 1: return launch_stream(mb, maps, x, in_dim, n_sms, stream, grid_out);
         case 2: return launch_mma<2>(mb, x, in_dim, n_sms, stream);
         case 3: return launch_mma<3>(mb, x, in_dim, n_sms, stream);
         case 4: return launch_mma<4>(mb, x, in_dim, n_sms, stream);

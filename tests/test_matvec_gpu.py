@@ -42,6 +42,47 @@ def test_single_vector_parity(ctx, in_dim, out_dim):
     assert I.rel_err(got, ref) <= TOL_F32
 
 
+@pytest.mark.parametrize("in_dim,out_dim", [(192, 40), (2112, 100), (4096, 12288), (4160, 4100)])
+def test_single_vector_ragged_stages_and_many_tiles(ctx, in_dim, out_dim):
+    """Shapes that exercise the one-vector kernel's edges: an odd number of groups (the last pair of groups is half
+    empty), a last stage of one group (2112 = 33 groups), more tiles than CTAs (every CTA takes several, in batches of
+    four behind one rendezvous), a last tile of 4 rows.  Twice in a row: the tile counter is back at zero for the
+    second launch, and the result is the same to the bit (fixed summation order)."""
+    r = I.rng(3 * in_dim + out_dim)
+    packed, scales, biases = I.quant_weights(r, in_dim, out_dim)
+    x = I.normal(r, in_dim)
+    ref = O.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    got = ctx.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    assert I.rel_err(got, ref) <= 1e-5, I.rel_err(got, ref)  # integer products: ten times inside the 1e-4 contract
+    again = ctx.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    assert np.array_equal(got, again)
+
+
+def test_single_vector_wide_dynamic_range_and_nonfinite_inputs(ctx):
+    """x is turned into integers per group of 64 features, relative to the group's largest element: elements 2^20
+    times smaller than their neighbours keep their leading bits, a zero group stays zero, and a NaN or an infinity in
+    x makes every output NaN (every row multiplies every feature), as in the reference's product."""
+    r = I.rng(4242)
+    in_dim, out_dim = 4096, 300
+    packed, scales, biases = I.quant_weights(r, in_dim, out_dim)
+    x = I.normal(r, in_dim)
+    x[::7] *= 2.0 ** 20
+    x[64:128] = 0.0
+    x[130] = 1e-30
+    ref = O.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    got = ctx.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    assert I.rel_err(got, ref) <= 1e-5, I.rel_err(got, ref)
+    small = np.zeros(in_dim, np.float32)
+    small[5] = 3e-39  # a denormal on its own: below what the integer scale reaches, contributes nothing or its value
+    got = ctx.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, small)
+    assert np.all(np.abs(got) <= 3e-39 * 16 * 0.2)
+    for bad in (np.nan, np.inf):
+        xb = I.normal(r, in_dim)
+        xb[1000] = bad
+        got = ctx.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, xb)
+        assert np.isnan(got).all() or (bad == np.inf and not np.isfinite(got).any())
+
+
 @pytest.mark.parametrize("n_vec", [2, 3, 5, 8])
 def test_several_vectors_share_the_weights(ctx, n_vec):
     r = I.rng(70 + n_vec)
