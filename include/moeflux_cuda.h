@@ -394,9 +394,19 @@ int mfc_sdpa_static_status(void *stream);
  * for n_vec (1..8) input vectors x [n_vec][in_dim] -> out [n_vec][out_dim], fp32, the
  * weights read once per pass.  in_dim must be a positive multiple of 64 (the reference's
  * InDimNotMultiple error).  One pass takes as many vectors as fit in shared memory
- * (n_vec * in_dim * 4.125 bytes: all 8 at in_dim 4096, 6 at 8192, 3 at 16384); more
- * vectors take further passes; in_dim itself is limited to 55,000 or so.
+ * (n_vec * in_dim * 4.25 bytes beside 45 KB of staging: all 8 at in_dim 4096, 4 at 8192, 2 at
+ * 16384); more vectors take further passes; in_dim itself is limited to 40,000 or so.
+ * Arithmetic: the nibbles and a per-group integer form of x (31 bits relative to the group's
+ * largest |x|) are multiplied exactly on the integer tensor cores; scales, biases and the sums
+ * over groups are fp32.  Against the reference's fp32 product: 3e-6 (max-norm relative) on
+ * N(0,1) inputs; a NaN or an infinity in x makes every output NaN.
  * _dev: device pointers (w_packed and x 16-byte aligned), asynchronous on mfc_stream(ctx).
+ * The kernel is launched so that it may begin (fetching weights, scales and biases) before the
+ * kernel queued ahead of it on the stream has finished; it waits for that kernel by itself
+ * before it reads x or writes out.  The weights, scales and biases must therefore be complete
+ * when the call is made if a kernel produces them (data copied or loaded earlier, the usual
+ * case for model weights, needs nothing); the tuning "matvec_overlap" 0 restores plain
+ * stream order.
  * The host-pointer form stages the operands in device memory for the call (a hook for
  * tests and bring-up, like mfc_sdpa).  Return 0 on success, -1 on error. */
 #define MFC_MATVEC_GROUP_SIZE 64
@@ -460,7 +470,9 @@ int mfc_mla_sdpa_folded_bf16_dev(mfc_ctx *ctx, int32_t num_heads, int32_t cache_
  * "gqa_inject_lost_load" 1 = the first CTA of the next decode launches arms the barrier of its first KV tile and
  * issues no load for it, so that its bounded wait runs out with nothing in flight (exercises the failure path
  * without faulting the GPU: the kernel returns, mfc_synchronize reports -1, the context stays usable);
- * "gqa_phase_trace" 1 = decode launches of at most 1024 CTAs record per-CTA time stamps (mfc_read_phase_trace). */
+ * "gqa_phase_trace" 1 = decode launches of at most 1024 CTAs, and the projection launches, record per-CTA time
+ * stamps (mfc_read_phase_trace); "matvec_overlap" 0 = projection kernels start only when the kernel ahead of them on
+ * the stream has finished (default 1, see mfc_dequant_matvec_4bit_dev). */
 int mfc_set_tuning(mfc_ctx *ctx, const char *key, int value);
 /* With the tuning "gdn_side_queue" = 1, mfc_linear_attn_step_batched_dev issues
  * its kernel on a second queue of the context: it starts after everything
@@ -482,7 +494,10 @@ long long mfc_launch_count(const mfc_ctx *ctx);
 int mfc_check_guards(mfc_ctx *ctx);
 /* Time stamps (nanoseconds, %globaltimer) of the CTAs of the last decode launch made with the tuning
  * "gqa_phase_trace" on: out[cta][8] = {start, first segment's Q fragments ready, its last KV tile consumed, its
- * epilogue done, CTA done, (bf16 cache only:) query rows staged, query rows rotated, 0}.  Returns the number of CTAs written (at most max_ctas), or -1. */
+ * epilogue done, CTA done, (bf16 cache only:) query rows staged, query rows rotated, 0}.  After a projection launch
+ * (mfc_dequant_matvec_4bit*): {start, barriers set up, x staged by thread 0, x staged by all, first stage of weights
+ * arrived, last stage consumed, results stored, cycles warp 0 spent waiting for weights}.  Returns the number of CTAs
+ * written (at most max_ctas), or -1. */
 int mfc_read_phase_trace(mfc_ctx *ctx, unsigned long long *out, int32_t max_ctas);
 
 /* ---- KV-sequence split: the exchange fused into the decode kernel ----

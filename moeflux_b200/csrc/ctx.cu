@@ -1204,7 +1204,7 @@ int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *c, int32_t n_mat, const uint32_t 
     cudaSetDevice(c->cfg.device);
     // as many vectors per pass over the weights as the staging of x allows
     int per_pass = n_vec;
-    MatvecMaps maps;  // for the one-vector kernel (a pass of one vector: n_vec 1, or the remainder of several passes)
+    MatvecMaps maps;
     for (int m = 0; m < n_mat; m++)
         if (!matvec_map(c, w_packed[m], scales[m], biases[m], in_dim, out_dims[m], &maps, m)) return -1;
     while (per_pass > 1 && dequant_matvec_4bit_smem(in_dim, per_pass) > c->smem_optin) per_pass--;
@@ -1214,8 +1214,7 @@ int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *c, int32_t n_mat, const uint32_t 
         for (int m = 0; m < n_mat; m++) pass.out[m] = outs[m] + (size_t)v0 * out_dims[m];
         int grid = 0;
         pass.sched = c->mv_sched + 2 * (c->mv_launches++ & 1u);  // a launch may overlap the one before it
-        CK(launch_dequant_matvec_4bit(pass, x + (size_t)v0 * in_dim, in_dim, nv, c->n_sms, c->stream,
-                                      nv == 1 ? &maps : nullptr, &grid));
+        CK(launch_dequant_matvec_4bit(pass, x + (size_t)v0 * in_dim, in_dim, nv, c->n_sms, c->stream, &maps, &grid));
         if (pass.trace && grid > 0) c->last_launch_ctas = grid;
         c->launches += 1;
     }

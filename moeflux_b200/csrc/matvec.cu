@@ -9,7 +9,7 @@
 //
 // The product is bound by the weight bytes (0.5 B per multiply-add).  One launch takes up to eight matrices that
 // share x (q/k/v_proj; in_proj_qkv/z/a/b): a launch has microseconds of fixed latency, as much as streaming a
-// 20 MB matrix takes.  Two kernels: one vector (the decode step) below, two to eight vectors further down.
+// 20 MB matrix takes.  One kernel, instantiated for one to eight vectors.
 #include <stdint.h>
 #include <string.h>
 
@@ -20,21 +20,25 @@ namespace mfc {
 
 namespace {
 
-// ------------------------------------------------------------------ one vector: streamed tiles, integer tensor cores
+// ------------------------------------------------------------------ streamed tiles, integer tensor cores
 // The product with one vector is the decode step's projection and is bound by the weight bytes, so the kernel is
-// organised around keeping HBM busy and spending next to nothing per nibble:
+// organised around keeping HBM busy and spending next to nothing per nibble (what changes with two to eight vectors
+// is said where the consumer's two forms are):
 //   * persistent CTAs take tiles of 16 rows from a counter in device memory (tiles of a launch cost the same, and the
 //     two CTAs of an SM share the queue, so the SMs finish together);
-//   * a producer warp streams each tile in stages of 16 rows x 1 KiB (32 groups) with cp.async.bulk into a ring of
-//     3-8 stages (64-128 KiB in flight per SM), completion on mbarriers; it starts before x is staged;
-//   * the nibbles go to the tensor core as they are: w & 0x0f0f0f0f and (w >> 4) & 0x0f0f0f0f are the u8 A operands
-//     of mma.sync m16n8k32 (three ALU operations per word of eight nibbles, no offset to cancel afterwards);
+//   * a producer warp streams each tile in stages of 16 rows x 1 KiB (32 groups) into a ring of 3-8 stages
+//     (64-128 KiB in flight per SM): eight TMA boxes of 16 rows x 128 bytes with the 128-byte swizzle, completion on
+//     mbarriers (a row-by-row cp.async.bulk of the same bytes ran at a third of the rate); it starts before x is staged;
+//   * the nibbles go to the tensor core as they are: w & 0x0f0f0f0f and w & 0xf0f0f0f0 (16 n; the features they
+//     multiply enter divided by 16) are the u8 A operands of mma.sync m16n8k32: two ALU operations per word of eight
+//     nibbles, no offset to cancel afterwards;
 //   * x enters as integers: per group of 64 features, q = rint(x / sx) with sx the power of two that puts the
 //     group's largest |x| below 2^30, written in four balanced base-256 digits (s8: the bytes of q + 0x808080 with
 //     the top bit of the three low bytes flipped).  The four digits of a group are four of the eight B columns, so
 //     two groups share one accumulator and every lane of a quad ends up owning one (group, digit pair):
 //     sum n x = sx * (D0 + 256 D1 + 256^2 D2 + 256^3 D3) is exact integer arithmetic, and the only roundings are
-//     those of x to 31 bits relative to its group's largest element, of the integers to fp32, and of the fp32 sums
+//     those of x to 31 bits (27 for the features that enter divided by 16) relative to its group's largest element,
+//     of the integers to fp32, and of the fp32 sums
 //     over groups (the reference's CPU product rounds every multiply-add);
 //   * scales and biases of a stage (16 rows x 64 bytes each) are two more boxes of the same stage when their rows
 //     are 16-byte aligned (in_dim a multiple of 512), otherwise the consumers read them from global memory;
@@ -61,12 +65,15 @@ constexpr int SV_BATCH = 4;                        // tiles combined behind one 
 constexpr int SV_OFF_HDR = 256;                    // after the mbarriers
 constexpr int SV_OFF_SLOT = SV_OFF_HDR + SV_MAX_STAGES * 16;
 constexpr int SV_OFF_RED = SV_OFF_SLOT + 2 * SV_BATCH * 8 + 64;
-constexpr int SV_OFF_XW = SV_OFF_RED + 2 * SV_BATCH * SV_WARPS * SV_ROWS * 4;
-static_assert(SV_OFF_XW % 16 == 0 && SV_OFF_RED % 16 == 0, "alignment of the shared-memory regions");
-
-__host__ __device__ inline size_t sv_fixed_bytes(int in_dim) {
+static_assert(SV_OFF_RED % 16 == 0, "alignment of the shared-memory regions");
+// after the partial sums [2][SV_BATCH][SV_WARPS][n_vec][SV_ROWS]: per vector and group {sx, sx * 256^2, sum of x, -},
+// then per vector and group the 256 bytes of digits in B-fragment order
+__host__ __device__ constexpr size_t sv_off_xw(int n_vec) {
+    return (size_t)SV_OFF_RED + 2 * SV_BATCH * SV_WARPS * SV_ROWS * 4 * (size_t)n_vec;
+}
+__host__ __device__ inline size_t sv_fixed_bytes(int in_dim, int n_vec) {
     const size_t n_groups = (size_t)(in_dim >> 6);
-    return ((size_t)SV_OFF_XW + n_groups * 16 + n_groups * 256 + 1023) & ~(size_t)1023;
+    return (sv_off_xw(n_vec) + (size_t)n_vec * (n_groups * 16 + n_groups * 256) + 1023) & ~(size_t)1023;
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
@@ -109,7 +116,8 @@ __device__ __forceinline__ void sv_trace(const MatvecBatch &mb, int w) {
     if (mb.trace) mb.trace[(size_t)blockIdx.x * PHASE_TRACE_WORDS + w] = global_timer_ns();
 }
 
-__global__ void __launch_bounds__(SV_THREADS, 2)
+template <int NV>
+__global__ void __launch_bounds__(SV_THREADS, NV <= 2 ? 2 : 1)
 dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const __grid_constant__ MatvecBatch mb,
                                   const float *__restrict__ x, int in_dim, int n_stages) {
     extern __shared__ __align__(16) uint8_t sv_smem_raw[];
@@ -120,11 +128,11 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     volatile int *abort_flag = reinterpret_cast<volatile int *>(red_bar + 1);
     int4 *hdr = reinterpret_cast<int4 *>(sv_smem + SV_OFF_HDR);     // per stage: {tile, matrix, first row, chunk}
     int2 *slot_info = reinterpret_cast<int2 *>(sv_smem + SV_OFF_SLOT);  // [2][SV_BATCH]: {matrix, first row}
-    float *red = reinterpret_cast<float *>(sv_smem + SV_OFF_RED);   // [2][SV_BATCH][SV_WARPS][SV_ROWS]
-    float4 *xw = reinterpret_cast<float4 *>(sv_smem + SV_OFF_XW);   // per group: {sx, sx * 256^2, sum of x, -}
+    float *red = reinterpret_cast<float *>(sv_smem + SV_OFF_RED);   // [2][SV_BATCH][SV_WARPS][NV][SV_ROWS]
+    float4 *xw = reinterpret_cast<float4 *>(sv_smem + sv_off_xw(NV));  // [NV][group]: {sx, sx * 256^2, sum of x, -}
     const int n_groups = in_dim >> 6;
-    uint8_t *xb = reinterpret_cast<uint8_t *>(xw + n_groups);       // per group [digit][t] x {b0, b1 of MMA 0; of MMA 1}
-    uint8_t *stages = sv_smem + sv_fixed_bytes(in_dim);
+    uint8_t *xb = reinterpret_cast<uint8_t *>(xw + (size_t)NV * n_groups);  // [NV][group][digit][word] x {b0, b1}
+    uint8_t *stages = sv_smem + sv_fixed_bytes(in_dim, NV);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row_bytes = in_dim >> 1;
@@ -230,7 +238,10 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     // Only then may the kernel after this one start (it uses the tile counters this kernel's predecessor used).
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    {
+    for (int vec = 0; vec < NV; vec++) {
+        const float *xv_src = x + (size_t)vec * in_dim;
+        float4 *xw_v = xw + (size_t)vec * n_groups;
+        uint8_t *xb_v = xb + (size_t)vec * n_groups * 256;
         const int n_words = in_dim >> 3;  // a thread handles the 8 features of one packed word; 8 threads hold a group
         constexpr int XU = 4;             // words per thread whose loads are in flight together
         for (int wq0 = 0; wq0 < n_words; wq0 += SV_WARPS * 32 * XU) {
@@ -239,8 +250,8 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
             for (int u = 0; u < XU; u++) {
                 const int wq = wq0 + u * SV_WARPS * 32 + tid;
                 const bool in = wq < n_words;
-                va[u] = in ? __ldg(reinterpret_cast<const float4 *>(x) + 2 * wq) : make_float4(0.f, 0.f, 0.f, 0.f);
-                vb[u] = in ? __ldg(reinterpret_cast<const float4 *>(x) + 2 * wq + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                va[u] = in ? __ldg(reinterpret_cast<const float4 *>(xv_src) + 2 * wq) : make_float4(0.f, 0.f, 0.f, 0.f);
+                vb[u] = in ? __ldg(reinterpret_cast<const float4 *>(xv_src) + 2 * wq + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int u = 0; u < XU; u++) {
@@ -289,10 +300,10 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
                 }
                 if (in) {
                     const int gi = wq >> 3, wl = wq & 7;
-                    uint8_t *dst = xb + (size_t)gi * 256 + (wl >> 1) * 16 + (wl & 1) * 8;
+                    uint8_t *dst = xb_v + (size_t)gi * 256 + (wl >> 1) * 16 + (wl & 1) * 8;
 #pragma unroll
                     for (int c = 0; c < 4; c++) *reinterpret_cast<uint2 *>(dst + c * 64) = make_uint2(b0[c], b1[c]);
-                    if (wl == 0) xw[gi] = make_float4(sx, sx * 65536.0f, sm, 0.0f);
+                    if (wl == 0) xw_v[gi] = make_float4(sx, sx * 65536.0f, sm, 0.0f);
                 }
             }
         }
@@ -316,14 +327,15 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
         if (lane == 0) mbar_arrive(red_bar);
         if (!sv_wait(red_bar, red_parity, spins, abort_flag)) return false;
         red_parity ^= 1u;
-        if (tid < slot * SV_ROWS) {
-            const int s = tid >> 4, r = tid & 15;
+        for (int idx = tid; idx < slot * NV * SV_ROWS; idx += SV_WARPS * 32) {
+            const int s = idx / (NV * SV_ROWS), vr = idx - s * (NV * SV_ROWS);  // vr = vector * 16 + row
             const int2 info = slot_info[buf * SV_BATCH + s];
-            const float *src = red + ((size_t)(buf * SV_BATCH + s) * SV_WARPS) * SV_ROWS + r;
+            const float *src = red + ((size_t)(buf * SV_BATCH + s) * SV_WARPS) * (NV * SV_ROWS) + vr;
             float sum = 0.0f;
 #pragma unroll
-            for (int w = 0; w < SV_WARPS; w++) sum += src[w * SV_ROWS];
-            if (info.y + r < mb.out_dim[info.x]) mb.out[info.x][info.y + r] = sum;
+            for (int w = 0; w < SV_WARPS; w++) sum += src[w * (NV * SV_ROWS)];
+            const int out_dim = mb.out_dim[info.x], r = vr & (SV_ROWS - 1);
+            if (info.y + r < out_dim) mb.out[info.x][(size_t)(vr >> 4) * out_dim + info.y + r] = sum;
         }
         buf ^= 1;
         slot = 0;
@@ -352,23 +364,109 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
 #pragma unroll
     for (int u = 0; u < 2; u++) bb[u][0] = bb[u][1] = make_uint4(0u, 0u, 0u, 0u);
 
+    // ---- two to eight vectors: the B columns are (vector, digit), two vectors to an MMA, so the two groups of a pair
+    // can no longer share an accumulator.  The same A words go in twice, once with the k slots of the second group
+    // masked to zero (lanes t = 2, 3) and once with those of the first: twice the MMAs of the one-vector form per
+    // pair of vectors, the same loads and the same integer work per nibble.
+    constexpr int CB = (NV + 1) / 2;  // pairs of vectors
+    float totv[CB][2];                // rows rho and rho + 8 of the tile, vector 2 cb + (t >> 1), digit pair t & 1
+#pragma unroll
+    for (int cb = 0; cb < CB; cb++) totv[cb][0] = totv[cb][1] = 0.0f;
+    const uint32_t nib_a = t < 2 ? NIB : 0u, nibh_a = t < 2 ? ~NIB : 0u;  // first group's k slots
+    const uint32_t nib_b = t < 2 ? 0u : NIB, nibh_b = t < 2 ? 0u : ~NIB;  // second group's
+    auto several_vectors = [&](const uint8_t *sbase, int m, int row0, int chunk, int groups_here) {
+        uint16_t s_lo[4], s_hi[4], c_lo[4], c_hi[4];  // of the warp's four groups, rows rho and rho + 8
+        if (mb.sb_bulk) {
+            const uint8_t *sb = sbase + sb_lane;
+            const uint2 a = *reinterpret_cast<const uint2 *>(sb);
+            const uint2 b = *reinterpret_cast<const uint2 *>(sb + 8 * SV_SB_ROW);
+            const uint2 c = *reinterpret_cast<const uint2 *>(sb + SV_SB_BOX);
+            const uint2 e8 = *reinterpret_cast<const uint2 *>(sb + SV_SB_BOX + 8 * SV_SB_ROW);
+            s_lo[0] = (uint16_t)a.x, s_lo[1] = (uint16_t)(a.x >> 16), s_lo[2] = (uint16_t)a.y, s_lo[3] = (uint16_t)(a.y >> 16);
+            s_hi[0] = (uint16_t)b.x, s_hi[1] = (uint16_t)(b.x >> 16), s_hi[2] = (uint16_t)b.y, s_hi[3] = (uint16_t)(b.y >> 16);
+            c_lo[0] = (uint16_t)c.x, c_lo[1] = (uint16_t)(c.x >> 16), c_lo[2] = (uint16_t)c.y, c_lo[3] = (uint16_t)(c.y >> 16);
+            c_hi[0] = (uint16_t)e8.x, c_hi[1] = (uint16_t)(e8.x >> 16), c_hi[2] = (uint16_t)e8.y, c_hi[3] = (uint16_t)(e8.y >> 16);
+        } else {
+            const int out_dim = mb.out_dim[m];
+            const int r_lo = min(row0 + rho, out_dim - 1), r_hi = min(row0 + rho + 8, out_dim - 1);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const size_t cc = min((size_t)chunk * SV_CHUNK_GROUPS + 4 * warp + q, (size_t)n_groups - 1);
+                s_lo[q] = __ldg(mb.scales[m] + (size_t)r_lo * n_groups + cc);
+                s_hi[q] = __ldg(mb.scales[m] + (size_t)r_hi * n_groups + cc);
+                c_lo[q] = __ldg(mb.biases[m] + (size_t)r_lo * n_groups + cc);
+                c_hi[q] = __ldg(mb.biases[m] + (size_t)r_hi * n_groups + cc);
+            }
+        }
+        const size_t g_first = (size_t)chunk * SV_CHUNK_GROUPS + 4 * warp;  // the warp's first group
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const uint4 wa = *reinterpret_cast<const uint4 *>(sbase + a_off[u]);
+            const uint4 wb = *reinterpret_cast<const uint4 *>(sbase + a_off[u] + 8 * 128);
+#pragma unroll
+            for (int cb = 0; cb < CB; cb++) {
+                // this lane's B column: digit g & 3 of vector 2 cb + (g >> 2), on the k slots of lane t (words
+                // 4 (t & 1) .. + 3 of the pair's first group for t < 2, of its second for t >= 2)
+                const int vb = 2 * cb + (g >> 2);
+                uint4 b01 = make_uint4(0u, 0u, 0u, 0u), b23 = b01;
+                if (vb < NV) {
+                    const uint8_t *pb = xb + ((size_t)vb * n_groups + g_first + 2 * u + (t >> 1)) * 256 + (g & 3) * 64 + (t & 1) * 32;
+                    b01 = *reinterpret_cast<const uint4 *>(pb);
+                    b23 = *reinterpret_cast<const uint4 *>(pb + 16);
+                }
+                int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
+                mma_u8s8_16832(da, wa.x & nib_a, wb.x & nib_a, wa.x & nibh_a, wb.x & nibh_a, b01.x, b01.y);
+                mma_u8s8_16832(db, wa.x & nib_b, wb.x & nib_b, wa.x & nibh_b, wb.x & nibh_b, b01.x, b01.y);
+                mma_u8s8_16832(da, wa.y & nib_a, wb.y & nib_a, wa.y & nibh_a, wb.y & nibh_a, b01.z, b01.w);
+                mma_u8s8_16832(db, wa.y & nib_b, wb.y & nib_b, wa.y & nibh_b, wb.y & nibh_b, b01.z, b01.w);
+                mma_u8s8_16832(da, wa.z & nib_a, wb.z & nib_a, wa.z & nibh_a, wb.z & nibh_a, b23.x, b23.y);
+                mma_u8s8_16832(db, wa.z & nib_b, wb.z & nib_b, wa.z & nibh_b, wb.z & nibh_b, b23.x, b23.y);
+                mma_u8s8_16832(da, wa.w & nib_a, wb.w & nib_a, wa.w & nibh_a, wb.w & nibh_a, b23.z, b23.w);
+                mma_u8s8_16832(db, wa.w & nib_b, wb.w & nib_b, wa.w & nibh_b, wb.w & nibh_b, b23.z, b23.w);
+                const int v = 2 * cb + (t >> 1);  // the accumulator columns of this lane: digit pair t & 1 of vector v
+                if (v < NV) {
+#pragma unroll
+                    for (int grp = 0; grp < 2; grp++) {
+                        const int q = 2 * u + grp;
+                        if (4 * warp + q < groups_here) {
+                            const float4 wv = xw[(size_t)v * n_groups + g_first + q];
+                            const float wgt = my_h ? wv.y : wv.x;
+                            const int *d = grp ? db : da;
+                            const float f0 = (float)(d[0] + d[1] * 256) * wgt;  // row rho
+                            const float f1 = (float)(d[2] + d[3] * 256) * wgt;  // row rho + 8
+                            totv[cb][0] = fmaf(bf16_bits_to_f32(s_lo[q]), f0, totv[cb][0]);
+                            totv[cb][1] = fmaf(bf16_bits_to_f32(s_hi[q]), f1, totv[cb][1]);
+                            if (my_h == 0) {
+                                totv[cb][0] = fmaf(bf16_bits_to_f32(c_lo[q]), wv.z, totv[cb][0]);
+                                totv[cb][1] = fmaf(bf16_bits_to_f32(c_hi[q]), wv.z, totv[cb][1]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    };
+
     int st = 0;
     unsigned phase = 0;
     long long wait_cycles = 0;
     for (bool first = true;; first = false) {
-        const long long w0 = clock64();
+        const long long w0 = mb.trace ? clock64() : 0;
         if (!sv_wait(&full[st], phase, spins, abort_flag)) {
             failed = true;
             break;
         }
-        wait_cycles += clock64() - w0;
+        if (mb.trace) wait_cycles += clock64() - w0;
         const int4 h = hdr[st];
         if (first && tid == 0) sv_trace(mb, 4);
         if (h.x < 0) break;
         const int m = h.y, row0 = h.z, chunk = h.w;
         const int groups_here = min(SV_CHUNK_GROUPS, n_groups - chunk * SV_CHUNK_GROUPS);
         const uint8_t *sbase = stages + (size_t)st * SV_STAGE_BYTES;
-        if (4 * warp < groups_here) {  // the warp's box was loaded (bytes of it past the row's end arrived as zeros)
+        if (NV > 1) {
+            if (4 * warp < groups_here)
+                several_vectors(sbase, m, row0, chunk, groups_here);
+        } else if (4 * warp < groups_here) {  // the warp's box was loaded (bytes of it past the row's end arrived as zeros)
             // this lane's scale and bias of the two pairs
             uint16_t s_lo[2], s_hi[2], c_lo[2], c_hi[2];
             if (mb.sb_bulk) {
@@ -443,17 +541,31 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
             phase ^= 1u;
         }
         if (chunk == n_chunks - 1) {
-            tot0 += __shfl_xor_sync(0xffffffffu, tot0, 1);
-            tot1 += __shfl_xor_sync(0xffffffffu, tot1, 1);
-            tot0 += __shfl_xor_sync(0xffffffffu, tot0, 2);
-            tot1 += __shfl_xor_sync(0xffffffffu, tot1, 2);
-            float *dst = red + ((size_t)(buf * SV_BATCH + slot) * SV_WARPS + warp) * SV_ROWS;
-            if (t == 0) {
-                dst[rho] = tot0;
-                dst[rho + 8] = tot1;
+            float *dst = red + ((size_t)(buf * SV_BATCH + slot) * SV_WARPS + warp) * (NV * SV_ROWS);
+            if (NV == 1) {
+                tot0 += __shfl_xor_sync(0xffffffffu, tot0, 1);
+                tot1 += __shfl_xor_sync(0xffffffffu, tot1, 1);
+                tot0 += __shfl_xor_sync(0xffffffffu, tot0, 2);
+                tot1 += __shfl_xor_sync(0xffffffffu, tot1, 2);
+                if (t == 0) {
+                    dst[rho] = tot0;
+                    dst[rho + 8] = tot1;
+                }
+                tot0 = tot1 = 0.0f;
+            } else {
+#pragma unroll
+                for (int cb = 0; cb < CB; cb++) {  // lanes t and t ^ 1 hold the two digit pairs of the same vector
+                    const float a0 = totv[cb][0] + __shfl_xor_sync(0xffffffffu, totv[cb][0], 1);
+                    const float a1 = totv[cb][1] + __shfl_xor_sync(0xffffffffu, totv[cb][1], 1);
+                    const int v = 2 * cb + (t >> 1);
+                    if (my_h == 0 && v < NV) {
+                        dst[v * SV_ROWS + rho] = a0;
+                        dst[v * SV_ROWS + rho + 8] = a1;
+                    }
+                    totv[cb][0] = totv[cb][1] = 0.0f;
+                }
             }
             if (tid == 0) slot_info[buf * SV_BATCH + slot] = make_int2(m, row0);
-            tot0 = tot1 = 0.0f;
             if (++slot == SV_BATCH && !flush()) {
                 failed = true;
                 break;
@@ -470,220 +582,13 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     }
 }
 
-// ------------------------------------------------------------------ several vectors: tensor cores
-// With n_vec >= 2 the CUDA-core kernel above spends one FMA per nibble and vector and is bound by instruction
-// issue, so batching vectors buys nothing.  Here the vectors are the N = 8 columns of mma.sync m16n8k16 (unused
-// columns are zero), 16 rows of W are the M rows and 16 nibbles the K step:
-//   * a nibble n enters as the bf16 16 + n = 0x4180 | n << 3, which is exact: one shift and one LOP3 give the
-//     bf16x2 {16 + n_j, 16 + n_(j+4)} of a word (a larger offset, e.g. 128 + n, would cost accuracy below);
-//   * x enters as a two-piece bf16 expansion (hi + mid, two MMAs per step), staged once per CTA in shared
-//     memory in fragment order; the K index of the MMA is permuted to fit the nibble pairs above;
-//   * per group of 64 features the 16 x 8 accumulator D = sum (16 + n) x is folded into the result as
-//     s (D - 16 X) + b X with X = sum x over the group (cancels under 2 bits);
-//   * a lane reads 8 bytes per row and group (a quad reads one 32-byte sector), eight groups in flight.
-// The MMA sums over K, so every lane ends with finished outputs: rows g, g+8 x vectors 2t, 2t+1.
-constexpr int MM_WARPS = 8;
-constexpr int MM_THREADS = MM_WARPS * 32;
-constexpr int MM_DEPTH = 8;  // groups of 64 features a lane has in flight
-
-__device__ __forceinline__ void split_bf16x2_mv(float x0, float x1, uint32_t &hi, uint32_t &mid) {
-    hi = pack_bf16x2(x0, x1);
-    mid = pack_bf16x2(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xffff0000u));
-}
-
-// ks = 1, 2, 4 or 8 warps share a tile of 16 rows, each taking a contiguous range of groups (so that short
-// launches still fill every warp slot of the GPU); their partial results are added in a fixed order.
-template <int NV>
-__global__ void __launch_bounds__(MM_THREADS, NV <= 3 ? 2 : 1)
-dequant_matvec_4bit_mma_kernel(const __grid_constant__ MatvecBatch mb, const float *__restrict__ x, int in_dim, int ks) {
-    extern __shared__ __align__(16) uint8_t smem_b[];
-    // B fragments: [group][step 0/1][hi | mid][g < NV][t] x 16 bytes {m1b0, m1b1, m2b0, m2b1}: the lanes of a
-    // quarter warp read consecutive 16-byte words
-    uint4 *xb = reinterpret_cast<uint4 *>(smem_b);
-    const int n_groups = in_dim >> 6;
-    float *xg = reinterpret_cast<float *>(smem_b + (size_t)n_groups * 8 * NV * 32);  // [NV][n_groups] group sums
-    float4 *red = reinterpret_cast<float4 *>(xg + NV * n_groups);                     // [MM_WARPS][32] partial results
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int row_stride_w = in_dim >> 3;
-
-    // ---- stage x: entry e = (group, step, t) of vector v covers x[v][64 group + 16 t + 8 step + 0..7] ----
-    const int n_entries = n_groups * 8;
-    for (int i0 = 0; i0 < NV * n_entries; i0 += 2 * MM_THREADS) {
-        float4 a[2], b[2];
-        int vv[2], ee[2];
-        bool in[2];
-#pragma unroll
-        for (int u = 0; u < 2; u++) {  // two entries (four 16-byte loads) in flight per thread
-            const int i = i0 + u * MM_THREADS + tid;
-            in[u] = i < NV * n_entries;
-            vv[u] = in[u] ? i / n_entries : 0;
-            ee[u] = in[u] ? i - vv[u] * n_entries : 0;
-            const int gi = ee[u] >> 3, st = (ee[u] >> 2) & 1, tt = ee[u] & 3;
-            const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)vv[u] * in_dim + 64 * gi + 16 * tt + 8 * st);
-            a[u] = in[u] ? __ldg(src) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            b[u] = in[u] ? __ldg(src + 1) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        }
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            if (in[u]) {
-                uint32_t h[4], m[4];
-                split_bf16x2_mv(a[u].x, b[u].x, h[0], m[0]);  // MMA 1, b0: k slots (2t, 2t+1)   <- features 0, 4
-                split_bf16x2_mv(a[u].y, b[u].y, h[1], m[1]);  // MMA 1, b1: k slots (2t+8, 2t+9) <- features 1, 5
-                split_bf16x2_mv(a[u].z, b[u].z, h[2], m[2]);  // MMA 2, b0                        <- features 2, 6
-                split_bf16x2_mv(a[u].w, b[u].w, h[3], m[3]);  // MMA 2, b1                        <- features 3, 7
-                const int gs = ee[u] >> 2, tt = ee[u] & 3;  // (group, step), t
-                xb[((size_t)(gs * 2 + 0) * NV + vv[u]) * 4 + tt] = make_uint4(h[0], h[1], h[2], h[3]);
-                xb[((size_t)(gs * 2 + 1) * NV + vv[u]) * 4 + tt] = make_uint4(m[0], m[1], m[2], m[3]);
-            }
-            // the eight entries of a group sit in eight consecutive threads
-            float sm = ((a[u].x + a[u].y) + (a[u].z + a[u].w)) + ((b[u].x + b[u].y) + (b[u].z + b[u].w));
-            sm += __shfl_xor_sync(0xffffffffu, sm, 1);
-            sm += __shfl_xor_sync(0xffffffffu, sm, 2);
-            sm += __shfl_xor_sync(0xffffffffu, sm, 4);
-            if ((tid & 7) == 0 && in[u]) xg[vv[u] * n_groups + (ee[u] >> 3)] = sm;
-        }
-    }
-    __syncthreads();
-
-    const int tiles_total = mb.total_groups;  // here: tiles of 16 rows (see the launcher)
-    const int tiles_per_cta = MM_WARPS / ks;
-    const int tile_in_cta = warp / ks, split = warp - tile_in_cta * ks;
-    const int gps = (n_groups + ks - 1) / ks;
-    const int g_begin = split * gps, g_end = min(g_begin + gps, n_groups);
-    for (int tile0 = blockIdx.x * tiles_per_cta; tile0 < tiles_total; tile0 += gridDim.x * tiles_per_cta) {
-        const int tile = tile0 + tile_in_cta;
-        const bool active = tile < tiles_total;
-        // tile -> matrix (tiles never straddle two matrices: the launcher counts them per matrix)
-        int m = 0;
-#pragma unroll
-        for (int k = 1; k < MATVEC_MAX_MATS; k++)
-            if (k < mb.n_mat && tile >= mb.group_begin[k]) m = k;
-        const int row0 = active ? (tile - mb.group_begin[m]) * 16 : 0;
-        const int out_dim = mb.out_dim[m];
-        float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // (row g, vec 2t), (row g, vec 2t+1), (row g+8, ...), (row g+8, ...)
-        if (active) {
-            const int r_lo = min(row0 + g, out_dim - 1), r_hi = min(row0 + g + 8, out_dim - 1);  // clamped, not stored
-            const uint2 *w_lo = reinterpret_cast<const uint2 *>(mb.w[m] + (size_t)r_lo * row_stride_w) + t;
-            const uint2 *w_hi = reinterpret_cast<const uint2 *>(mb.w[m] + (size_t)r_hi * row_stride_w) + t;
-            const uint16_t *s_lo = mb.scales[m] + (size_t)r_lo * n_groups, *s_hi = mb.scales[m] + (size_t)r_hi * n_groups;
-            const uint16_t *b_lo = mb.biases[m] + (size_t)r_lo * n_groups, *b_hi = mb.biases[m] + (size_t)r_hi * n_groups;
-            for (int g0 = g_begin; g0 < g_end; g0 += MM_DEPTH) {
-                uint2 wl[MM_DEPTH], wh[MM_DEPTH];
-                uint16_t sl[MM_DEPTH], sh[MM_DEPTH], bl[MM_DEPTH], bh[MM_DEPTH];
-#pragma unroll
-                for (int k = 0; k < MM_DEPTH; k++) {
-                    const int gi = min(g0 + k, g_end - 1);
-                    wl[k] = __ldg(w_lo + 4 * gi);  // 8 words per row and group; this lane takes words 2t, 2t+1
-                    wh[k] = __ldg(w_hi + 4 * gi);
-                    sl[k] = __ldg(s_lo + gi);
-                    sh[k] = __ldg(s_hi + gi);
-                    bl[k] = __ldg(b_lo + gi);
-                    bh[k] = __ldg(b_hi + gi);
-                }
-#pragma unroll
-                for (int k = 0; k < MM_DEPTH; k++) {
-                    const int gi = g0 + k;
-                    if (gi >= g_end) break;
-                    float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                    for (int st = 0; st < 2; st++) {
-                        const uint32_t a_lo = st == 0 ? wl[k].x : wl[k].y, a_hi = st == 0 ? wh[k].x : wh[k].y;
-                        uint4 bh4 = make_uint4(0, 0, 0, 0), bm4 = make_uint4(0, 0, 0, 0);
-                        if (g < NV) {
-                            const int gs = gi * 2 + st;
-                            bh4 = xb[((size_t)(gs * 2 + 0) * NV + g) * 4 + t];
-                            bm4 = xb[((size_t)(gs * 2 + 1) * NV + g) * 4 + t];
-                        }
-                        // bf16 16 + n = 0x4180 | n << 3 (exact): nibble pairs (j, j + 4) of a word in one register
-                        constexpr uint32_t MASK = 0x00780078u, BASE = 0x41804180u;
-                        uint32_t a1[4] = {((a_lo << 3) & MASK) | BASE, ((a_hi << 3) & MASK) | BASE,
-                                          ((a_lo >> 1) & MASK) | BASE, ((a_hi >> 1) & MASK) | BASE};
-                        uint32_t a2[4] = {((a_lo >> 5) & MASK) | BASE, ((a_hi >> 5) & MASK) | BASE,
-                                          ((a_lo >> 9) & MASK) | BASE, ((a_hi >> 9) & MASK) | BASE};
-                        mma_bf16_16816(d, a1, bh4.x, bh4.y);
-                        mma_bf16_16816(d, a1, bm4.x, bm4.y);
-                        mma_bf16_16816(d, a2, bh4.z, bh4.w);
-                        mma_bf16_16816(d, a2, bm4.z, bm4.w);
-                    }
-                    const float x0 = (2 * t < NV) ? xg[(2 * t) * n_groups + gi] : 0.0f;
-                    const float x1 = (2 * t + 1 < NV) ? xg[(2 * t + 1) * n_groups + gi] : 0.0f;
-                    const float s0 = bf16_bits_to_f32(sl[k]), s1 = bf16_bits_to_f32(sh[k]);
-                    const float c0 = bf16_bits_to_f32(bl[k]), c1 = bf16_bits_to_f32(bh[k]);
-                    tot[0] += fmaf(s0, fmaf(-16.0f, x0, d[0]), c0 * x0);
-                    tot[1] += fmaf(s0, fmaf(-16.0f, x1, d[1]), c0 * x1);
-                    tot[2] += fmaf(s1, fmaf(-16.0f, x0, d[2]), c1 * x0);
-                    tot[3] += fmaf(s1, fmaf(-16.0f, x1, d[3]), c1 * x1);
-                }
-            }
-        }
-        if (ks > 1) {  // uniform over the CTA
-            red[warp * 32 + lane] = make_float4(tot[0], tot[1], tot[2], tot[3]);
-            __syncthreads();
-            if (split == 0)
-                for (int k = 1; k < ks; k++) {
-                    const float4 p = red[(warp + k) * 32 + lane];
-                    tot[0] += p.x;
-                    tot[1] += p.y;
-                    tot[2] += p.z;
-                    tot[3] += p.w;
-                }
-            __syncthreads();
-        }
-        if (active && split == 0) {
-            float *o = mb.out[m];
-            if (row0 + g < out_dim) {
-                if (2 * t < NV) o[(size_t)(2 * t) * out_dim + row0 + g] = tot[0];
-                if (2 * t + 1 < NV) o[(size_t)(2 * t + 1) * out_dim + row0 + g] = tot[1];
-            }
-            if (row0 + g + 8 < out_dim) {
-                if (2 * t < NV) o[(size_t)(2 * t) * out_dim + row0 + g + 8] = tot[2];
-                if (2 * t + 1 < NV) o[(size_t)(2 * t + 1) * out_dim + row0 + g + 8] = tot[3];
-            }
-        }
-    }
-}
-
-size_t mma_smem(int in_dim, int nv) {
-    return (size_t)(in_dim >> 6) * 8 * nv * 32 + sizeof(float) * (size_t)nv * (in_dim >> 6) + sizeof(float4) * MM_WARPS * 32;
-}
-
-template <int NV>
-cudaError_t launch_mma(MatvecBatch mb, const float *x, int in_dim, int n_sms, cudaStream_t stream) {
-    const size_t smem = mma_smem(in_dim, NV);
-    static thread_local bool configured[64] = {false};  // per device: the opt-in is a host call of several microseconds
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(dequant_matvec_4bit_mma_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(227 * 1024));
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
-    }
-    int tiles = 0;  // here group_begin counts tiles of 16 rows per matrix
-    for (int m = 0; m < mb.n_mat; m++) {
-        mb.group_begin[m] = tiles;
-        tiles += (mb.out_dim[m] + 15) / 16;
-    }
-    mb.total_groups = tiles;
-    // warps per tile: enough to give every warp slot of the GPU work, while a warp keeps at least 8 groups
-    const int ctas_per_sm = (NV <= 3 && smem <= 100 * 1024) ? 2 : 1;
-    const int slots = n_sms * ctas_per_sm * MM_WARPS;
-    int ks = 1;
-    while (ks < MM_WARPS && tiles * ks < slots && (in_dim >> 6) / (2 * ks) >= 8) ks *= 2;
-    const int tiles_per_cta = MM_WARPS / ks;
-    int grid = (tiles + tiles_per_cta - 1) / tiles_per_cta;
-    if (grid > n_sms * ctas_per_sm) grid = n_sms * ctas_per_sm;
-    dequant_matvec_4bit_mma_kernel<NV><<<grid, MM_THREADS, smem, stream>>>(mb, x, in_dim, ks);
-    return cudaGetLastError();
-}
-
-// Stages of the ring and CTAs per SM for a given in_dim: two CTAs per SM when each can still hold three stages.
-void sv_plan(int in_dim, size_t smem_optin, int &n_stages, int &ctas_per_sm) {
-    const size_t fixed = sv_fixed_bytes(in_dim) + 1024;  // with the alignment slack
+// Stages of the ring and CTAs per SM for a given in_dim and number of vectors: two CTAs per SM when each can still
+// hold three stages (and the kernel is built for two: one or two vectors).
+void sv_plan(int in_dim, int n_vec, size_t smem_optin, int &n_stages, int &ctas_per_sm) {
+    const size_t fixed = sv_fixed_bytes(in_dim, n_vec) + 1024;  // with the alignment slack
     const size_t half = smem_optin / 2 > 2048 ? smem_optin / 2 - 2048 : 0;  // room for the per-CTA reserve of the SM
     ctas_per_sm = 2;
-    long long n = half > fixed ? (long long)((half - fixed) / SV_STAGE_BYTES) : 0;
+    long long n = (n_vec <= 2 && half > fixed) ? (long long)((half - fixed) / SV_STAGE_BYTES) : 0;
     if (n < 3) {
         ctas_per_sm = 1;
         n = smem_optin > fixed ? (long long)((smem_optin - fixed) / SV_STAGE_BYTES) : 0;
@@ -691,6 +596,7 @@ void sv_plan(int in_dim, size_t smem_optin, int &n_stages, int &ctas_per_sm) {
     n_stages = (int)(n > SV_MAX_STAGES ? SV_MAX_STAGES : n);
 }
 
+template <int NV>
 cudaError_t launch_stream(MatvecBatch mb, const MatvecMaps *maps, const float *x, int in_dim, int n_sms, cudaStream_t stream,
                           int *grid_out) {
     if (!maps) return cudaErrorInvalidValue;
@@ -702,14 +608,14 @@ cudaError_t launch_stream(MatvecBatch mb, const MatvecMaps *maps, const float *x
     if (!configured[dev]) {
         cudaError_t e = cudaDeviceGetAttribute(&optin[dev], cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(dequant_matvec_4bit_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin[dev]);
+        e = cudaFuncSetAttribute(dequant_matvec_4bit_stream_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin[dev]);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
     int n_stages = 0, ctas_per_sm = 1;
-    sv_plan(in_dim, (size_t)optin[dev], n_stages, ctas_per_sm);
+    sv_plan(in_dim, NV, (size_t)optin[dev], n_stages, ctas_per_sm);
     if (n_stages < 2 || !mb.sched || !mb.status) return cudaErrorInvalidValue;
-    int tiles = 0;  // here group_begin counts tiles of 16 rows per matrix
+    int tiles = 0;  // group_begin counts tiles of 16 rows per matrix
     for (int m = 0; m < mb.n_mat; m++) {
         mb.group_begin[m] = tiles;
         tiles += (mb.out_dim[m] + SV_ROWS - 1) / SV_ROWS;
@@ -720,7 +626,7 @@ cudaError_t launch_stream(MatvecBatch mb, const MatvecMaps *maps, const float *x
         if (((uintptr_t)mb.scales[m] | (uintptr_t)mb.biases[m]) & 15) mb.sb_bulk = 0;
     int grid = n_sms * ctas_per_sm;
     if (grid > tiles) grid = tiles;
-    const size_t smem = 1024 + sv_fixed_bytes(in_dim) + (size_t)n_stages * SV_STAGE_BYTES;  // 1 KiB: alignment slack
+    const size_t smem = 1024 + sv_fixed_bytes(in_dim, NV) + (size_t)n_stages * SV_STAGE_BYTES;  // 1 KiB: alignment slack
     if (grid_out) *grid_out = grid;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -734,28 +640,27 @@ cudaError_t launch_stream(MatvecBatch mb, const MatvecMaps *maps, const float *x
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = mb.overlap ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, dequant_matvec_4bit_stream_kernel, *maps, mb, x, in_dim, n_stages);
+    return cudaLaunchKernelEx(&cfg, dequant_matvec_4bit_stream_kernel<NV>, *maps, mb, x, in_dim, n_stages);
 }
 
 }  // namespace
 
 size_t dequant_matvec_4bit_smem(int in_dim, int n_vec) {
-    if (n_vec == 1) return 1024 + sv_fixed_bytes(in_dim) + 2 * (size_t)SV_STAGE_BYTES;  // the least the ring works with
-    return mma_smem(in_dim, n_vec);
+    return 1024 + sv_fixed_bytes(in_dim, n_vec) + 2 * (size_t)SV_STAGE_BYTES;  // the least the ring works with
 }
 
 cudaError_t launch_dequant_matvec_4bit(MatvecBatch mb, const float *x, int in_dim, int n_vec, int n_sms,
                                        cudaStream_t stream, const MatvecMaps *maps, int *grid_out) {
     if (mb.n_mat < 1 || mb.n_mat > MATVEC_MAX_MATS) return cudaErrorInvalidValue;
     switch (n_vec) {
-        case 1: return launch_stream(mb, maps, x, in_dim, n_sms, stream, grid_out);
-        case 2: return launch_mma<2>(mb, x, in_dim, n_sms, stream);
-        case 3: return launch_mma<3>(mb, x, in_dim, n_sms, stream);
-        case 4: return launch_mma<4>(mb, x, in_dim, n_sms, stream);
-        case 5: return launch_mma<5>(mb, x, in_dim, n_sms, stream);
-        case 6: return launch_mma<6>(mb, x, in_dim, n_sms, stream);
-        case 7: return launch_mma<7>(mb, x, in_dim, n_sms, stream);
-        case 8: return launch_mma<8>(mb, x, in_dim, n_sms, stream);
+        case 1: return launch_stream<1>(mb, maps, x, in_dim, n_sms, stream, grid_out);
+        case 2: return launch_stream<2>(mb, maps, x, in_dim, n_sms, stream, grid_out);
+        case 3: return launch_stream<3>(mb, maps, x, in_dim, n_sms, stream, grid_out);
+        case 4: return launch_stream<4>(mb, maps, x, in_dim, n_sms, stream, grid_out);
+        case 5: return launch_stream<5>(mb, maps, x, in_dim, n_sms, stream, grid_out);
+        case 6: return launch_stream<6>(mb, maps, x, in_dim, n_sms, stream, grid_out);
+        case 7: return launch_stream<7>(mb, maps, x, in_dim, n_sms, stream, grid_out);
+        case 8: return launch_stream<8>(mb, maps, x, in_dim, n_sms, stream, grid_out);
         default: return cudaErrorInvalidValue;
     }
 }
