@@ -1286,7 +1286,7 @@ def run_matvec(args):
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    K, W, NV = args.steps, args.warmup, args.vecs
+    K, W, NV = max(args.steps, 200), args.warmup, args.vecs  # a step is under 0.1 ms: at least 200 of them are timed
     full = [(4096, 16384), (4096, 512), (4096, 512), (8192, 4096)]
     lin = [(4096, 12288), (4096, 8192), (4096, 64), (4096, 64), (8192, 4096)]
     shapes = lin * 3 + full
@@ -1585,6 +1585,8 @@ def main():
         others["ragged (configuration 2)"] = compact(run_ragged(args, rank, world, local_rank))
         if world == 1:
             others["prefill (configuration 3)"] = compact(run_prefill(args))
+            others["4-bit projections of a hybrid block"] = compact(run_matvec(args))
+            others["folded MLA attention, fp32 cache"] = compact(run_mla(args))
     failed = False
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

@@ -64,7 +64,7 @@ constexpr int SV_MAX_STAGES = 8;
 constexpr int SV_BATCH = 4;                        // tiles combined behind one rendezvous
 constexpr int SV_OFF_HDR = 256;                    // after the mbarriers
 constexpr int SV_OFF_SLOT = SV_OFF_HDR + SV_MAX_STAGES * 16;
-constexpr int SV_OFF_RED = SV_OFF_SLOT + 2 * SV_BATCH * 8 + 64;
+constexpr int SV_OFF_RED = SV_OFF_SLOT + 2 * SV_BATCH * 8 + 64;  // (64 spare bytes)
 static_assert(SV_OFF_RED % 16 == 0, "alignment of the shared-memory regions");
 // after the partial sums [2][SV_BATCH][SV_WARPS][n_vec][SV_ROWS]: per vector and group {sx, sx * 256^2, sum of x, -},
 // then per vector and group the 256 bytes of digits in B-fragment order
@@ -82,7 +82,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 // D(16x8,s32) += A(16x32,u8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
-    asm(  // registers only: left to the compiler's scheduling
+    asm volatile(  // volatile: the instruction needs the whole warp, so it must stay where it is written
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
@@ -238,11 +238,12 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     // Only then may the kernel after this one start (it uses the tile counters this kernel's predecessor used).
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    for (int vec = 0; vec < NV; vec++) {
-        const float *xv_src = x + (size_t)vec * in_dim;
-        float4 *xw_v = xw + (size_t)vec * n_groups;
-        uint8_t *xb_v = xb + (size_t)vec * n_groups * 256;
-        const int n_words = in_dim >> 3;  // a thread handles the 8 features of one packed word; 8 threads hold a group
+    {
+        // the NV vectors are contiguous in x, in xw and in xb: staged as one vector of NV * in_dim features
+        const float *xv_src = x;
+        float4 *xw_v = xw;
+        uint8_t *xb_v = xb;
+        const int n_words = NV * (in_dim >> 3);  // a thread handles the 8 features of one packed word; 8 threads hold a group
         constexpr int XU = 4;             // words per thread whose loads are in flight together
         for (int wq0 = 0; wq0 < n_words; wq0 += SV_WARPS * 32 * XU) {
             float4 va[XU], vb[XU];
@@ -365,15 +366,16 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     for (int u = 0; u < 2; u++) bb[u][0] = bb[u][1] = make_uint4(0u, 0u, 0u, 0u);
 
     // ---- two to eight vectors: the B columns are (vector, digit), two vectors to an MMA, so the two groups of a pair
-    // can no longer share an accumulator.  The same A words go in twice, once with the k slots of the second group
-    // masked to zero (lanes t = 2, 3) and once with those of the first: twice the MMAs of the one-vector form per
-    // pair of vectors, the same loads and the same integer work per nibble.
+    // can no longer share an accumulator and every MMA must take its k slots from one group.  A lane holds four words
+    // of one group (lanes t = 0, 1: the first group of the pair, t = 2, 3: the second); lanes t and t ^ 2 swap two
+    // words each, after which every lane holds words base, base + 1 (base = 4 (t & 1) + 2 (t >> 1)) of both groups:
+    // two MMAs per group and pair of vectors, the same loads and the same integer work per nibble as with one vector.
     constexpr int CB = (NV + 1) / 2;  // pairs of vectors
     float totv[CB][2];                // rows rho and rho + 8 of the tile, vector 2 cb + (t >> 1), digit pair t & 1
 #pragma unroll
     for (int cb = 0; cb < CB; cb++) totv[cb][0] = totv[cb][1] = 0.0f;
-    const uint32_t nib_a = t < 2 ? NIB : 0u, nibh_a = t < 2 ? ~NIB : 0u;  // first group's k slots
-    const uint32_t nib_b = t < 2 ? 0u : NIB, nibh_b = t < 2 ? 0u : ~NIB;  // second group's
+    const bool upper = t >= 2;
+    const int b_word = 4 * (t & 1) + 2 * (t >> 1);
     auto several_vectors = [&](const uint8_t *sbase, int m, int row0, int chunk, int groups_here) {
         uint16_t s_lo[4], s_hi[4], c_lo[4], c_hi[4];  // of the warp's four groups, rows rho and rho + 8
         if (mb.sb_bulk) {
@@ -403,26 +405,29 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
         for (int u = 0; u < 2; u++) {
             const uint4 wa = *reinterpret_cast<const uint4 *>(sbase + a_off[u]);
             const uint4 wb = *reinterpret_cast<const uint4 *>(sbase + a_off[u] + 8 * 128);
+            // rows rho (wa) and rho + 8 (wb): words w0, w1 of the pair's first group (ga, gb) and of its second (ha, hb)
+            const uint32_t ra0 = __shfl_xor_sync(0xffffffffu, upper ? wa.x : wa.z, 2);
+            const uint32_t ra1 = __shfl_xor_sync(0xffffffffu, upper ? wa.y : wa.w, 2);
+            const uint32_t rb0 = __shfl_xor_sync(0xffffffffu, upper ? wb.x : wb.z, 2);
+            const uint32_t rb1 = __shfl_xor_sync(0xffffffffu, upper ? wb.y : wb.w, 2);
+            const uint32_t ga0 = upper ? ra0 : wa.x, ga1 = upper ? ra1 : wa.y, gb0 = upper ? rb0 : wb.x, gb1 = upper ? rb1 : wb.y;
+            const uint32_t ha0 = upper ? wa.z : ra0, ha1 = upper ? wa.w : ra1, hb0 = upper ? wb.z : rb0, hb1 = upper ? wb.w : rb1;
 #pragma unroll
             for (int cb = 0; cb < CB; cb++) {
-                // this lane's B column: digit g & 3 of vector 2 cb + (g >> 2), on the k slots of lane t (words
-                // 4 (t & 1) .. + 3 of the pair's first group for t < 2, of its second for t >= 2)
+                // this lane's B column: digit g & 3 of vector 2 cb + (g >> 2), on this lane's k slots: words
+                // b_word, b_word + 1 of the group
                 const int vb = 2 * cb + (g >> 2);
-                uint4 b01 = make_uint4(0u, 0u, 0u, 0u), b23 = b01;
+                uint4 bg = make_uint4(0u, 0u, 0u, 0u), bh = bg;
                 if (vb < NV) {
-                    const uint8_t *pb = xb + ((size_t)vb * n_groups + g_first + 2 * u + (t >> 1)) * 256 + (g & 3) * 64 + (t & 1) * 32;
-                    b01 = *reinterpret_cast<const uint4 *>(pb);
-                    b23 = *reinterpret_cast<const uint4 *>(pb + 16);
+                    const uint8_t *pb = xb + ((size_t)vb * n_groups + g_first + 2 * u) * 256 + (g & 3) * 64 + b_word * 8;
+                    bg = *reinterpret_cast<const uint4 *>(pb);
+                    bh = *reinterpret_cast<const uint4 *>(pb + 256);
                 }
                 int da[4] = {0, 0, 0, 0}, db[4] = {0, 0, 0, 0};
-                mma_u8s8_16832(da, wa.x & nib_a, wb.x & nib_a, wa.x & nibh_a, wb.x & nibh_a, b01.x, b01.y);
-                mma_u8s8_16832(db, wa.x & nib_b, wb.x & nib_b, wa.x & nibh_b, wb.x & nibh_b, b01.x, b01.y);
-                mma_u8s8_16832(da, wa.y & nib_a, wb.y & nib_a, wa.y & nibh_a, wb.y & nibh_a, b01.z, b01.w);
-                mma_u8s8_16832(db, wa.y & nib_b, wb.y & nib_b, wa.y & nibh_b, wb.y & nibh_b, b01.z, b01.w);
-                mma_u8s8_16832(da, wa.z & nib_a, wb.z & nib_a, wa.z & nibh_a, wb.z & nibh_a, b23.x, b23.y);
-                mma_u8s8_16832(db, wa.z & nib_b, wb.z & nib_b, wa.z & nibh_b, wb.z & nibh_b, b23.x, b23.y);
-                mma_u8s8_16832(da, wa.w & nib_a, wb.w & nib_a, wa.w & nibh_a, wb.w & nibh_a, b23.z, b23.w);
-                mma_u8s8_16832(db, wa.w & nib_b, wb.w & nib_b, wa.w & nibh_b, wb.w & nibh_b, b23.z, b23.w);
+                mma_u8s8_16832(da, ga0 & NIB, gb0 & NIB, ga0 & ~NIB, gb0 & ~NIB, bg.x, bg.y);
+                mma_u8s8_16832(db, ha0 & NIB, hb0 & NIB, ha0 & ~NIB, hb0 & ~NIB, bh.x, bh.y);
+                mma_u8s8_16832(da, ga1 & NIB, gb1 & NIB, ga1 & ~NIB, gb1 & ~NIB, bg.z, bg.w);
+                mma_u8s8_16832(db, ha1 & NIB, hb1 & NIB, ha1 & ~NIB, hb1 & ~NIB, bh.z, bh.w);
                 const int v = 2 * cb + (t >> 1);  // the accumulator columns of this lane: digit pair t & 1 of vector v
                 if (v < NV) {
 #pragma unroll
@@ -628,14 +633,12 @@ cudaError_t launch_stream(MatvecBatch mb, const MatvecMaps *maps, const float *x
     if (grid > tiles) grid = tiles;
     const size_t smem = 1024 + sv_fixed_bytes(in_dim, NV) + (size_t)n_stages * SV_STAGE_BYTES;  // 1 KiB: alignment slack
     if (grid_out) *grid_out = grid;
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(SV_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    memset(&attr, 0, sizeof(attr));
+    cudaLaunchAttribute attr = {};
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start before the kernel ahead of it has drained
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
