@@ -472,7 +472,9 @@ int mfc_mla_sdpa_folded_bf16_dev(mfc_ctx *ctx, int32_t num_heads, int32_t cache_
  * without faulting the GPU: the kernel returns, mfc_synchronize reports -1, the context stays usable);
  * "gqa_phase_trace" 1 = decode launches of at most 1024 CTAs, and the projection launches, record per-CTA time
  * stamps (mfc_read_phase_trace); "matvec_overlap" 0 = projection kernels start only when the kernel ahead of them on
- * the stream has finished (default 1, see mfc_dequant_matvec_4bit_dev). */
+ * the stream has finished (default 1, see mfc_dequant_matvec_4bit_dev); "matvec_inject_lost_load" 1 = the same
+ * exercise as "gqa_inject_lost_load" for the projection kernel (its first CTA arms its first stage of weights and
+ * requests nothing for it). */
 int mfc_set_tuning(mfc_ctx *ctx, const char *key, int value);
 /* With the tuning "gdn_side_queue" = 1, mfc_linear_attn_step_batched_dev issues
  * its kernel on a second queue of the context: it starts after everything

@@ -72,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, unsigned parity
 
 // ---- TMA: 2-D tiled load global -> shared, completion on an mbarrier ------
 // c0 is the innermost coordinate (elements); c0 * element size must be a
-// multiple of 16 bytes.  No cluster multicast is used anywhere in this library.
+// multiple of 16 bytes.  Every load of this library lands in the shared memory of the issuing CTA only.
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tmap, int c0, int c1,
                                             uint64_t *bar) {
     asm volatile(

@@ -120,6 +120,7 @@ struct mfc_ctx {
     // diagnostics
     unsigned gqa_wait_spins = 0;
     int gqa_inject_lost_load = 0;
+    int mv_inject_lost_load = 0;
     unsigned long long *phase_trace = nullptr;  // [MAX_TRACE_CTAS][PHASE_TRACE_WORDS]
     static constexpr int MAX_TRACE_CTAS = 1024;
     bool phase_trace_on = false;
@@ -1190,6 +1191,7 @@ int mfc_dequant_matvec_4bit_multi_dev(mfc_ctx *c, int32_t n_mat, const uint32_t 
     memset(&mb, 0, sizeof(mb));
     mb.n_mat = n_mat;
     mb.overlap = c->mv_overlap ? 1 : 0;
+    mb.inject_lost_load = c->mv_inject_lost_load;
     mb.status = c->status;
     mb.spins = (unsigned)c->gqa_wait_spins;
     mb.trace = c->phase_trace_on ? c->phase_trace : nullptr;  // the grid never exceeds two CTAs per SM
@@ -1263,7 +1265,7 @@ int mfc_dequant_matvec_4bit(mfc_ctx *c, const uint32_t *w_packed, const uint16_t
             fail(c, "device to host copy failed");
             break;
         }
-        rc = 0;
+        rc = check_status(c);  // a kernel that gave up on a bounded wait reports here
     } while (0);
     cudaStreamSynchronize(c->stream);
     cudaFree(d);
@@ -1405,6 +1407,8 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
     } else if (!strcmp(key, "gqa_min_rows")) {
         if (value < 32 || value % 32) return -1;
         c->gqa_min_rows = value;
+    } else if (!strcmp(key, "matvec_inject_lost_load")) {
+        c->mv_inject_lost_load = value != 0;
     } else if (!strcmp(key, "matvec_overlap")) {
         c->mv_overlap = value != 0;
     } else if (!strcmp(key, "gqa_coop_merge")) {

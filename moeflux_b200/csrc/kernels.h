@@ -255,6 +255,7 @@ struct MatvecBatch {
     int sb_bulk;                       // filled by the launcher: scales and biases travel with the weight stages
     unsigned long long *trace;         // optional [CTA][PHASE_TRACE_WORDS] nanosecond stamps of the one-vector kernel
     int overlap;                       // launch as a programmatic dependent launch (the kernel waits by itself)
+    int inject_lost_load;              // test hook: CTA 0 arms its first stage and requests nothing for it
 };
 // Tensor maps of the batch's matrices for the one-vector kernel: the weights of matrix m as a 2-D byte array
 // [out_dim][in_dim / 2], boxes of 16 rows x 128 bytes, 128-byte swizzle; its scales and its biases as

@@ -187,7 +187,10 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
                 uint8_t *dst = stages + (size_t)st * SV_STAGE_BYTES;
                 // box b: bytes [128 b, 128 b + 128) of the stage's 1 KiB of rows row0 .. row0 + 15 (rows and bytes
                 // past the matrix arrive as zeros); then the rows' scales and biases of the stage's 32 groups
-                if (lane < n_boxes)
+                // (test hook: the first CTA arms its first stage and requests nothing, so that the consumers' bounded
+                // wait runs out with nothing in flight)
+                if (mb.inject_lost_load && blockIdx.x == 0 && it == 0) {
+                } else if (lane < n_boxes)
                     tma_load_2d(dst + lane * SV_BOX_BYTES, &maps.w[m], chunk * SV_ROW_BYTES + lane * 128, row0, &full[st]);
                 else if (mb.sb_bulk && lane == 8)
                     tma_load_2d(dst + SV_W_BYTES, &maps.sc[m], chunk * SV_CHUNK_GROUPS, row0, &full[st]);

@@ -165,3 +165,31 @@ def test_several_matrices_in_one_launch(ctx):
             assert I.rel_err(got[v], O.dequant_matvec_4bit(m[0], m[1], m[2], in_dim, got.shape[1], x[v])) <= TOL_F32
     with pytest.raises(M.MfcError):
         ctx.dequant_matvec_4bit_multi_dev([0] * 9, [0] * 9, [0] * 9, in_dim, [1] * 9, d_x.data_ptr(), 1, [0] * 9)
+
+
+def test_bounded_wait_runs_out_and_the_context_survives():
+    """The projection kernel's failure path: its first CTA arms the barrier of its first stage of weights and requests
+    nothing for it, with a low poll limit.  Nothing is in flight for that barrier, so the consumers' wait runs out:
+    the CTA gives up, the others finish, the call reports the failure, the tile counters are back at zero and the
+    same context goes on to compute correct products.  (No fault, trap or hang is involved anywhere.)"""
+    c, _ = make_pair(max_seq=64, n_seqs=1, linear_layers=[])
+    r = I.rng(31337)
+    in_dim, out_dim = 4096, 5000  # more tiles than CTAs: the other CTAs take over the tile counter meanwhile
+    packed, scales, biases = I.quant_weights(r, in_dim, out_dim)
+    x = I.normal(r, in_dim)
+    c.set_tuning("gqa_wait_spins", 200)
+    c.set_tuning("matvec_inject_lost_load", 1)
+    with pytest.raises(M.MfcError, match="did not arrive within the wait limit"):
+        c.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    c.set_tuning("matvec_inject_lost_load", 0)
+    c.set_tuning("gqa_wait_spins", 0)
+    c.synchronize()  # the report was cleared with the failed call
+    ref = O.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    for _ in range(2):
+        assert I.rel_err(c.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x), ref) <= 1e-5
+    x2 = I.normal(r, (3, in_dim))
+    got = c.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x2)
+    for v in range(3):
+        assert I.rel_err(got[v], O.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x2[v])) <= 1e-5
+    c.check_guards()
+    c.close()
