@@ -101,6 +101,22 @@ def test_several_vectors_share_the_weights(ctx, n_vec):
     assert I.rel_err(alone, got[n_vec - 1]) <= TOL_F32
 
 
+@pytest.mark.parametrize("n_vec,in_dim,out_dim", [(3, 2112, 100), (5, 192, 40), (2, 4160, 530), (8, 8192, 300), (7, 64, 3)])
+def test_several_vectors_ragged_shapes(ctx, n_vec, in_dim, out_dim):
+    """The several-vector form of the kernel at the shapes that take its other branches: scales and biases read from
+    global memory (in_dim not a multiple of 512), a last stage of one group, an odd number of groups, a last tile of a
+    few rows, an odd number of vectors (the last pair of columns half empty), 8192-wide rows (four passes' worth of
+    staging for 8 vectors)."""
+    r = I.rng(100 * n_vec + in_dim + out_dim)
+    packed, scales, biases = I.quant_weights(r, in_dim, out_dim)
+    x = I.normal(r, (n_vec, in_dim))
+    got = ctx.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x)
+    assert got.shape == (n_vec, out_dim)
+    for v in range(n_vec):
+        ref = O.dequant_matvec_4bit(packed, scales, biases, in_dim, out_dim, x[v])
+        assert I.rel_err(got[v], ref) <= 1e-5, (v, I.rel_err(got[v], ref))
+
+
 def test_device_pointer_entry_point(ctx):
     import torch
     r = I.rng(5)
