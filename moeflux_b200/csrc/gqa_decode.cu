@@ -120,11 +120,7 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
         }
     };
 
-    // the first tiles of the segment; the last stage of the ring first carries the Q rows (below)
-    if (tid == 0 && !appender) {
-        const int n0 = min(ntiles, BF16_STAGES - 1);
-        for (int i = 0; i < n0; i++) issue_tile(i);
-    }
+    // (the last stage of the ring first carries the Q rows)
     float *s_q = reinterpret_cast<float *>(stages + (size_t)((pc + BF16_STAGES - 1) % BF16_STAGES) * 2 * TILE_BYTES_BF16);
     stage_q_rows(p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * (size_t)p.q_row_stride, group, p.q_row_stride, s_q);
     // RoPE table for this token
@@ -136,6 +132,13 @@ gqa_decode_bf16_kernel(const __grid_constant__ CUtensorMap kmap,
         s_sin[tid] = sn;
     }
     __syncthreads();
+    // The first tiles of the segment are requested only now, with the query rows already in shared memory: every CTA
+    // of a launch starts at the same time, and query rows asked for behind 57 MB of first tiles came back after 8 us
+    // while the ring sat full and idle.  (The rows themselves take a microsecond; nothing can be computed before.)
+    if (tid == 0 && !appender) {
+        const int n0 = min(ntiles, BF16_STAGES - 1);
+        for (int i = 0; i < n0; i++) issue_tile(i);
+    }
     if (seg_no == 0) trace_phase(p, 5);  // query rows and the RoPE table are in shared memory
 
     if (appender) {

@@ -117,11 +117,7 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         }
     };
 
-    // the first tiles of the segment; the last stage of the ring first carries the Q rows (below)
-    if (tid == 0 && !appender) {
-        const int n0 = min(ntiles, F32_STAGES - 1);
-        for (int i = 0; i < n0; i++) issue_tile(i);
-    }
+    // (the last stage of the ring first carries the Q rows)
     float *s_q = reinterpret_cast<float *>(stages + (size_t)((pc + F32_STAGES - 1) % F32_STAGES) * 2 * TILE_BYTES_F32);
     stage_q_rows(p.q + ((size_t)it.in_idx * p.H + (size_t)L.kvh * group) * (size_t)p.q_row_stride, group, p.q_row_stride, s_q);
     const int half = p.rotary_dim >> 1;
@@ -132,6 +128,12 @@ gqa_decode_f32_kernel(const __grid_constant__ CUtensorMap kmap,
         s_sin[tid] = sn;
     }
     __syncthreads();
+    // the first tiles of the segment are requested only now, with the query rows already in shared memory (rows asked
+    // for behind the first tiles of every CTA of the launch came back after microseconds, with the ring full and idle)
+    if (tid == 0 && !appender) {
+        const int n0 = min(ntiles, F32_STAGES - 1);
+        for (int i = 0; i < n0; i++) issue_tile(i);
+    }
 
     if (appender) {
         const float *ksrc = p.k + ((size_t)it.in_idx * p.Hkv + L.kvh) * HEAD_DIM;
