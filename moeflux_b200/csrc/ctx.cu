@@ -475,7 +475,7 @@ void fill_gqa_params(mfc_ctx *c, GqaParams &p, int n, int total_ctas) {
 }
 
 int launch_gqa(mfc_ctx *c, GqaParams &p) {
-    if (p.n_items <= INLINE_ITEMS) {  // up to 64 items travel as kernel parameters: no copy before the launch
+    if (p.n_items <= GQA_INLINE_ITEMS) {  // up to 128 items travel as kernel parameters: no copy before the launch
         p.items = nullptr;
         for (int i = 0; i < p.n_items; i++) p.inline_items[i] = c->h_gqa_items[i];
     } else if (upload_items(c, c->d_gqa_items, c->h_gqa_items.data(), sizeof(GqaItem) * p.n_items, c->stream)) {

@@ -29,7 +29,9 @@ struct GdnItem {
     int32_t pad;
 };
 
-constexpr int INLINE_ITEMS = 64;  // launches of at most this many items carry them in the kernel's parameters (2 KiB)
+constexpr int INLINE_ITEMS = 64;       // GatedDeltaNet launches of at most this many items carry them in the kernel's parameters (1 KiB)
+constexpr int GQA_INLINE_ITEMS = 128;  // the same for the full-attention launches (4 KiB: the benchmark's 120 items; a
+                                       // table in device memory costs every CTA two more dependent reads at its start)
 
 struct GdnParams {
     float *ssm_base;          // [state][Hv][128 value][128 key]
@@ -69,7 +71,7 @@ struct GqaParams {
     void *k_base;            // cache base pointers (for the append)
     void *v_base;
     const GqaItem *items;    // device; nullptr: the items are `inline_items` (no copy precedes the launch)
-    GqaItem inline_items[INLINE_ITEMS];
+    GqaItem inline_items[GQA_INLINE_ITEMS];
     int n_items;
     int total_ctas;
     // The tiles of all (item, kv head) units form one sequence; CTA c works on tiles
