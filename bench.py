@@ -727,12 +727,15 @@ def single_step_latencies(local_rank=0, calls=1000):
         k, v = torch.randn(KV_DIM, device=dev, generator=g), torch.randn(KV_DIM, device=dev, generator=g)
         o = torch.empty(Q_DIM, device=dev)
         torch.cuda.synchronize(dev)
-        pos = [L0] * n_seqs
+        # the host side of a call is kept to one ctypes call on tables that are passed by address
+        lay_tab, seq_tab = np.full(1, 3, np.int32), np.arange(n_seqs, dtype=np.int32)
+        pos = np.full(n_seqs, L0, np.int32)
+        lay_p, seq_p, pos_p = lay_tab.ctypes.data, seq_tab.ctypes.data, pos.ctypes.data
+        ptrs = (q.data_ptr(), gt.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr())
 
         def call(i):
             s = i % n_seqs
-            c.full_attn_step_batched_dev([3], [s], [pos[s]], q.data_ptr(), gt.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                         o.data_ptr())
+            c.full_attn_step_batched_dev_ptr(1, lay_p, seq_p + 4 * s, pos_p + 4 * s, *ptrs)
             pos[s] += 1
 
         us = timed(c, st, call, n_seqs, n_calls)
@@ -756,8 +759,11 @@ def single_step_latencies(local_rank=0, calls=1000):
     qkv, z = torch.randn(CONV_DIM, device=dev), torch.randn(V_DIM, device=dev)
     a, b, o = torch.randn(HV, device=dev), torch.randn(HV, device=dev), torch.empty(V_DIM, device=dev)
     torch.cuda.synchronize(dev)
-    us = timed(c, st, lambda i: c.linear_attn_step_batched_dev([0], [i % n_seqs], qkv.data_ptr(), z.data_ptr(),
-                                                                 a.data_ptr(), b.data_ptr(), o.data_ptr()), n_seqs, 1024)
+    # (a call is under 10 us: the host side must not be the slower part, so the tables are kept and passed by address)
+    lay_tab, seq_tab = np.zeros(1, np.int32), np.arange(n_seqs, dtype=np.int32)
+    lay_p, seq_p = lay_tab.ctypes.data, seq_tab.ctypes.data
+    ptrs = (qkv.data_ptr(), z.data_ptr(), a.data_ptr(), b.data_ptr(), o.data_ptr())
+    us = timed(c, st, lambda i: c.linear_attn_step_batched_dev_ptr(1, lay_p, seq_p + 4 * (i % n_seqs), *ptrs), n_seqs, 1024)
     c.close()
     by = gdn_bytes_per_item()
     out["gdn_single_step (configuration 1)"] = {"us_per_step": us, "algorithmic_bytes": by, "GBps": by / us / 1e3,

@@ -272,6 +272,13 @@ class Ctx:
                                                       C.cast(pos_p, _I), q_ptr, gate_ptr, k_ptr, v_ptr, out_ptr)
         self._check(rc, "mfc_full_attn_step_batched_dev")
 
+    def linear_attn_step_batched_dev_ptr(self, n, layers_p, seqs_p, qkv_ptr, z_ptr, alpha_ptr, beta_ptr, out_ptr):
+        """``mfc_linear_attn_step_batched_dev`` with the two host tables given as addresses of int32 arrays the
+        caller keeps (no per-call conversions)."""
+        rc = self._lib.mfc_linear_attn_step_batched_dev(self._h, n, C.cast(layers_p, _I), C.cast(seqs_p, _I), qkv_ptr,
+                                                        z_ptr or None, alpha_ptr, beta_ptr, out_ptr)
+        self._check(rc, "mfc_linear_attn_step_batched_dev")
+
     def linear_attn_step_batched_ptr(self, n, layers_p, seqs_p, qkv_p, z_p, alpha_p, beta_p, out_p):
         rc = self._lib.mfc_linear_attn_step_batched(self._h, n, C.cast(layers_p, _I), C.cast(seqs_p, _I),
                                                     C.cast(qkv_p, _F), C.cast(z_p, _F) if z_p else None,
