@@ -48,8 +48,10 @@ namespace {
 //   * the eight consumer warps split the groups of a stage; their partial sums for a tile meet in shared memory, four
 //     tiles behind one rendezvous, and are added in a fixed order (results do not depend on timing).
 // A NaN or infinity in x makes every output NaN, as it does in the reference's product.
-constexpr int SV_WARPS = 8;                        // consumer warps
-constexpr int SV_THREADS = (SV_WARPS + 1) * 32;    // and the producer warp
+// Consumer warps (a producer warp comes on top): eight, one per box of a stage, for one or two vectors; sixteen, two
+// per box (one pair of groups each), from three vectors on, where the work per stage grows with the vectors and one
+// CTA per SM is all that fits: twice the warps hide the latencies that eight cannot.
+__host__ __device__ constexpr int sv_warps(int n_vec) { return n_vec >= 3 ? 16 : 8; }
 constexpr int SV_ROWS = 16;                        // rows per tile: M of the MMA
 constexpr int SV_CHUNK_GROUPS = 32;                // groups of 64 features per stage
 constexpr int SV_ROW_BYTES = SV_CHUNK_GROUPS * 32; // 1 KiB of a row per stage
@@ -61,15 +63,17 @@ constexpr int SV_SB_BOX = SV_ROWS * SV_SB_ROW;     // one TMA box of scales (or 
 constexpr int SV_STAGE_BYTES = SV_W_BYTES + 2 * SV_SB_BOX;  // 18 KiB: a multiple of the swizzle atom
 static_assert(SV_STAGE_BYTES % 1024 == 0, "stages keep the 1 KiB alignment of the swizzled boxes");
 constexpr int SV_MAX_STAGES = 8;
-constexpr int SV_BATCH = 4;                        // tiles combined behind one rendezvous
+constexpr int SV_BATCH = 4;                        // tiles combined behind one rendezvous (at most)
+// ... two with sixteen consumer warps, whose table of partial sums is twice as wide
+__host__ __device__ constexpr int sv_batch(int n_vec) { return n_vec >= 3 ? 2 : SV_BATCH; }
 constexpr int SV_OFF_HDR = 256;                    // after the mbarriers
 constexpr int SV_OFF_SLOT = SV_OFF_HDR + SV_MAX_STAGES * 16;
 constexpr int SV_OFF_RED = SV_OFF_SLOT + 2 * SV_BATCH * 8 + 64;  // (64 spare bytes)
 static_assert(SV_OFF_RED % 16 == 0, "alignment of the shared-memory regions");
-// after the partial sums [2][SV_BATCH][SV_WARPS][n_vec][SV_ROWS]: per vector and group {sx, sx * 256^2, sum of x, -},
+// after the partial sums [2][tiles of a batch][consumer warps][n_vec][SV_ROWS]: per vector and group {sx, sx * 256^2, sum of x, -},
 // then per vector and group the 256 bytes of digits in B-fragment order
 __host__ __device__ constexpr size_t sv_off_xw(int n_vec) {
-    return (size_t)SV_OFF_RED + 2 * SV_BATCH * SV_WARPS * SV_ROWS * 4 * (size_t)n_vec;
+    return (size_t)SV_OFF_RED + 2 * sv_batch(n_vec) * sv_warps(n_vec) * SV_ROWS * 4 * (size_t)n_vec;
 }
 __host__ __device__ inline size_t sv_fixed_bytes(int in_dim, int n_vec) {
     const size_t n_groups = (size_t)(in_dim >> 6);
@@ -117,7 +121,7 @@ __device__ __forceinline__ void sv_trace(const MatvecBatch &mb, int w) {
 }
 
 template <int NV>
-__global__ void __launch_bounds__(SV_THREADS, NV <= 2 ? 2 : 1)
+__global__ void __launch_bounds__((sv_warps(NV) + 1) * 32, NV <= 2 ? 2 : 1)
 dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const __grid_constant__ MatvecBatch mb,
                                   const float *__restrict__ x, int in_dim, int n_stages) {
     extern __shared__ __align__(16) uint8_t sv_smem_raw[];
@@ -128,7 +132,9 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     volatile int *abort_flag = reinterpret_cast<volatile int *>(red_bar + 1);
     int4 *hdr = reinterpret_cast<int4 *>(sv_smem + SV_OFF_HDR);     // per stage: {tile, matrix, first row, chunk}
     int2 *slot_info = reinterpret_cast<int2 *>(sv_smem + SV_OFF_SLOT);  // [2][SV_BATCH]: {matrix, first row}
-    float *red = reinterpret_cast<float *>(sv_smem + SV_OFF_RED);   // [2][SV_BATCH][SV_WARPS][NV][SV_ROWS]
+    constexpr int CW = sv_warps(NV);  // consumer warps
+    constexpr int BATCH = sv_batch(NV);
+    float *red = reinterpret_cast<float *>(sv_smem + SV_OFF_RED);   // [2][BATCH][CW][NV][SV_ROWS]
     float4 *xw = reinterpret_cast<float4 *>(sv_smem + sv_off_xw(NV));  // [NV][group]: {sx, sx * 256^2, sum of x, -}
     const int n_groups = in_dim >> 6;
     uint8_t *xb = reinterpret_cast<uint8_t *>(xw + (size_t)NV * n_groups);  // [NV][group][digit][word] x {b0, b1}
@@ -143,16 +149,16 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     if (tid == 0) {
         for (int s = 0; s < n_stages; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], SV_WARPS);
+            mbar_init(&empty[s], CW);
         }
-        mbar_init(red_bar, SV_WARPS);
+        mbar_init(red_bar, CW);
         *abort_flag = 0;
         mbar_fence_init();
     }
     __syncthreads();
     if (tid == 0) sv_trace(mb, 1);
 
-    if (warp == SV_WARPS) {
+    if (warp == CW) {
         // ---------------- producer: tiles from the launch-wide counter, stages into the ring
         if (lane < mb.n_mat) {
             prefetch_tmap(&maps.w[lane]);
@@ -248,19 +254,19 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
         uint8_t *xb_v = xb;
         const int n_words = NV * (in_dim >> 3);  // a thread handles the 8 features of one packed word; 8 threads hold a group
         constexpr int XU = 4;             // words per thread whose loads are in flight together
-        for (int wq0 = 0; wq0 < n_words; wq0 += SV_WARPS * 32 * XU) {
+        for (int wq0 = 0; wq0 < n_words; wq0 += CW * 32 * XU) {
             float4 va[XU], vb[XU];
 #pragma unroll
             for (int u = 0; u < XU; u++) {
-                const int wq = wq0 + u * SV_WARPS * 32 + tid;
+                const int wq = wq0 + u * CW * 32 + tid;
                 const bool in = wq < n_words;
                 va[u] = in ? __ldg(reinterpret_cast<const float4 *>(xv_src) + 2 * wq) : make_float4(0.f, 0.f, 0.f, 0.f);
                 vb[u] = in ? __ldg(reinterpret_cast<const float4 *>(xv_src) + 2 * wq + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int u = 0; u < XU; u++) {
-                const int wq = wq0 + u * SV_WARPS * 32 + tid;
-                if (wq0 + u * SV_WARPS * 32 >= n_words) break;  // uniform over the CTA
+                const int wq = wq0 + u * CW * 32 + tid;
+                if (wq0 + u * CW * 32 >= n_words) break;  // uniform over the CTA
                 const bool in = wq < n_words;
                 const float v[8] = {va[u].x, va[u].y, va[u].z, va[u].w, vb[u].x, vb[u].y, vb[u].z, vb[u].w};
                 float sm = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
@@ -313,7 +319,7 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
         }
     }
     if (tid == 0) sv_trace(mb, 2);
-    asm volatile("bar.sync 1, %0;" ::"n"(SV_WARPS * 32) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     if (tid == 0) sv_trace(mb, 3);
 
     const int g = lane >> 2, t = lane & 3;
@@ -331,13 +337,13 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
         if (lane == 0) mbar_arrive(red_bar);
         if (!sv_wait(red_bar, red_parity, spins, abort_flag)) return false;
         red_parity ^= 1u;
-        for (int idx = tid; idx < slot * NV * SV_ROWS; idx += SV_WARPS * 32) {
+        for (int idx = tid; idx < slot * NV * SV_ROWS; idx += CW * 32) {
             const int s = idx / (NV * SV_ROWS), vr = idx - s * (NV * SV_ROWS);  // vr = vector * 16 + row
             const int2 info = slot_info[buf * SV_BATCH + s];
-            const float *src = red + ((size_t)(buf * SV_BATCH + s) * SV_WARPS) * (NV * SV_ROWS) + vr;
+            const float *src = red + ((size_t)(buf * BATCH + s) * CW) * (NV * SV_ROWS) + vr;
             float sum = 0.0f;
 #pragma unroll
-            for (int w = 0; w < SV_WARPS; w++) sum += src[w * (NV * SV_ROWS)];
+            for (int w = 0; w < CW; w++) sum += src[w * (NV * SV_ROWS)];
             const int out_dim = mb.out_dim[info.x], r = vr & (SV_ROWS - 1);
             if (info.y + r < out_dim) mb.out[info.x][(size_t)(vr >> 4) * out_dim + info.y + r] = sum;
         }
@@ -351,19 +357,23 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     // that shared memory serves together (g = 2q, 2q + 1; t = 0..3) then read rows q and q + 4, whose 16-byte
     // chunks the 128-byte swizzle stores in opposite halves of the row: no bank is asked twice.
     const int rho = (g >> 1) | ((g & 1) << 2);
+    // the box of a stage this warp works on, and which of its two pairs of groups (both, with eight consumer warps)
+    const int box = CW == 16 ? warp >> 1 : warp;
+    const int u_first = CW == 16 ? (warp & 1) : 0;
+    constexpr int U_COUNT = CW == 16 ? 1 : 2;
     // Lane (g, t) reads chunk 4 u + t of row rho (16 bytes = four words = half a group) for pair u of the warp's box.
     // MMA j of the pair takes word j of every lane: its k slots of lanes t = 0, 1 are features of the pair's first
     // group, those of lanes t = 2, 3 features of the second; the B columns 0-3 hold the first group's digits of x and
     // are zero on the second group's k slots, columns 4-7 the other way round.
     int a_off[2];
 #pragma unroll
-    for (int u = 0; u < 2; u++) a_off[u] = warp * SV_BOX_BYTES + rho * 128 + (((4 * u + t) ^ rho) << 4);
+    for (int uu = 0; uu < 2; uu++) a_off[uu] = box * SV_BOX_BYTES + rho * 128 + (((4 * (u_first + uu) + t) ^ rho) << 4);
     // B operand of lane (g, t): column g = digit b_c of group b_sel of the pair, on the k slots of lane t: real
     // for the lanes whose t belongs to that group, zero (never loaded) for the others
     const bool b_real = b_sel == (t >> 1);
-    const uint8_t *xb_lane = xb + (4 * warp + b_sel) * 256 + b_c * 64 + (t & 1) * 32;
-    const int sb_lane = SV_W_BYTES + rho * SV_SB_ROW + 8 * warp;  // scales of row rho, the warp's four groups
-    const float *xw_lane = reinterpret_cast<const float *>(xw + 4 * warp + my_sel);
+    const uint8_t *xb_lane = xb + (4 * box + b_sel) * 256 + b_c * 64 + (t & 1) * 32;
+    const int sb_lane = SV_W_BYTES + rho * SV_SB_ROW + 8 * box;  // scales of row rho, the box's four groups
+    const float *xw_lane = reinterpret_cast<const float *>(xw + 4 * box + my_sel);
     uint4 bb[2][2];  // [pair][MMAs 0-1 | 2-3]: {b0, b1} of two MMAs each; stays zero in the lanes that never load
 #pragma unroll
     for (int u = 0; u < 2; u++) bb[u][0] = bb[u][1] = make_uint4(0u, 0u, 0u, 0u);
@@ -380,34 +390,39 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
     const bool upper = t >= 2;
     const int b_word = 4 * (t & 1) + 2 * (t >> 1);
     auto several_vectors = [&](const uint8_t *sbase, int m, int row0, int chunk, int groups_here) {
-        uint16_t s_lo[4], s_hi[4], c_lo[4], c_hi[4];  // of the warp's four groups, rows rho and rho + 8
+        // scales and biases of the box's four groups, rows rho and rho + 8: two bf16 per word (groups 0-1 | 2-3)
+        uint2 sc_lo, sc_hi, bi_lo, bi_hi;
         if (mb.sb_bulk) {
             const uint8_t *sb = sbase + sb_lane;
-            const uint2 a = *reinterpret_cast<const uint2 *>(sb);
-            const uint2 b = *reinterpret_cast<const uint2 *>(sb + 8 * SV_SB_ROW);
-            const uint2 c = *reinterpret_cast<const uint2 *>(sb + SV_SB_BOX);
-            const uint2 e8 = *reinterpret_cast<const uint2 *>(sb + SV_SB_BOX + 8 * SV_SB_ROW);
-            s_lo[0] = (uint16_t)a.x, s_lo[1] = (uint16_t)(a.x >> 16), s_lo[2] = (uint16_t)a.y, s_lo[3] = (uint16_t)(a.y >> 16);
-            s_hi[0] = (uint16_t)b.x, s_hi[1] = (uint16_t)(b.x >> 16), s_hi[2] = (uint16_t)b.y, s_hi[3] = (uint16_t)(b.y >> 16);
-            c_lo[0] = (uint16_t)c.x, c_lo[1] = (uint16_t)(c.x >> 16), c_lo[2] = (uint16_t)c.y, c_lo[3] = (uint16_t)(c.y >> 16);
-            c_hi[0] = (uint16_t)e8.x, c_hi[1] = (uint16_t)(e8.x >> 16), c_hi[2] = (uint16_t)e8.y, c_hi[3] = (uint16_t)(e8.y >> 16);
+            sc_lo = *reinterpret_cast<const uint2 *>(sb);
+            sc_hi = *reinterpret_cast<const uint2 *>(sb + 8 * SV_SB_ROW);
+            bi_lo = *reinterpret_cast<const uint2 *>(sb + SV_SB_BOX);
+            bi_hi = *reinterpret_cast<const uint2 *>(sb + SV_SB_BOX + 8 * SV_SB_ROW);
         } else {
             const int out_dim = mb.out_dim[m];
             const int r_lo = min(row0 + rho, out_dim - 1), r_hi = min(row0 + rho + 8, out_dim - 1);
+            uint32_t w4[4][4];
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                const size_t cc = min((size_t)chunk * SV_CHUNK_GROUPS + 4 * warp + q, (size_t)n_groups - 1);
-                s_lo[q] = __ldg(mb.scales[m] + (size_t)r_lo * n_groups + cc);
-                s_hi[q] = __ldg(mb.scales[m] + (size_t)r_hi * n_groups + cc);
-                c_lo[q] = __ldg(mb.biases[m] + (size_t)r_lo * n_groups + cc);
-                c_hi[q] = __ldg(mb.biases[m] + (size_t)r_hi * n_groups + cc);
+                const size_t cc = min((size_t)chunk * SV_CHUNK_GROUPS + 4 * box + q, (size_t)n_groups - 1);
+                w4[0][q] = __ldg(mb.scales[m] + (size_t)r_lo * n_groups + cc);
+                w4[1][q] = __ldg(mb.scales[m] + (size_t)r_hi * n_groups + cc);
+                w4[2][q] = __ldg(mb.biases[m] + (size_t)r_lo * n_groups + cc);
+                w4[3][q] = __ldg(mb.biases[m] + (size_t)r_hi * n_groups + cc);
             }
+            sc_lo = make_uint2(w4[0][0] | (w4[0][1] << 16), w4[0][2] | (w4[0][3] << 16));
+            sc_hi = make_uint2(w4[1][0] | (w4[1][1] << 16), w4[1][2] | (w4[1][3] << 16));
+            bi_lo = make_uint2(w4[2][0] | (w4[2][1] << 16), w4[2][2] | (w4[2][3] << 16));
+            bi_hi = make_uint2(w4[3][0] | (w4[3][1] << 16), w4[3][2] | (w4[3][3] << 16));
         }
-        const size_t g_first = (size_t)chunk * SV_CHUNK_GROUPS + 4 * warp;  // the warp's first group
+        const size_t g_first = (size_t)chunk * SV_CHUNK_GROUPS + 4 * box;  // the box's first group
 #pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const uint4 wa = *reinterpret_cast<const uint4 *>(sbase + a_off[u]);
-            const uint4 wb = *reinterpret_cast<const uint4 *>(sbase + a_off[u] + 8 * 128);
+        for (int uu = 0; uu < U_COUNT; uu++) {
+            const int u = u_first + uu;  // the pair of groups: both for a warp that has the box to itself
+            const uint32_t p_sc_lo = u ? sc_lo.y : sc_lo.x, p_sc_hi = u ? sc_hi.y : sc_hi.x;  // the pair's two groups
+            const uint32_t p_bi_lo = u ? bi_lo.y : bi_lo.x, p_bi_hi = u ? bi_hi.y : bi_hi.x;
+            const uint4 wa = *reinterpret_cast<const uint4 *>(sbase + a_off[uu]);
+            const uint4 wb = *reinterpret_cast<const uint4 *>(sbase + a_off[uu] + 8 * 128);
             // rows rho (wa) and rho + 8 (wb): words w0, w1 of the pair's first group (ga, gb) and of its second (ha, hb)
             const uint32_t ra0 = __shfl_xor_sync(0xffffffffu, upper ? wa.x : wa.z, 2);
             const uint32_t ra1 = __shfl_xor_sync(0xffffffffu, upper ? wa.y : wa.w, 2);
@@ -436,17 +451,17 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
 #pragma unroll
                     for (int grp = 0; grp < 2; grp++) {
                         const int q = 2 * u + grp;
-                        if (4 * warp + q < groups_here) {
+                        if (4 * box + q < groups_here) {
                             const float4 wv = xw[(size_t)v * n_groups + g_first + q];
                             const float wgt = my_h ? wv.y : wv.x;
                             const int *d = grp ? db : da;
                             const float f0 = (float)(d[0] + d[1] * 256) * wgt;  // row rho
                             const float f1 = (float)(d[2] + d[3] * 256) * wgt;  // row rho + 8
-                            totv[cb][0] = fmaf(bf16_bits_to_f32(s_lo[q]), f0, totv[cb][0]);
-                            totv[cb][1] = fmaf(bf16_bits_to_f32(s_hi[q]), f1, totv[cb][1]);
+                            totv[cb][0] = fmaf(bf16_bits_to_f32((uint16_t)(p_sc_lo >> (16 * grp))), f0, totv[cb][0]);
+                            totv[cb][1] = fmaf(bf16_bits_to_f32((uint16_t)(p_sc_hi >> (16 * grp))), f1, totv[cb][1]);
                             if (my_h == 0) {
-                                totv[cb][0] = fmaf(bf16_bits_to_f32(c_lo[q]), wv.z, totv[cb][0]);
-                                totv[cb][1] = fmaf(bf16_bits_to_f32(c_hi[q]), wv.z, totv[cb][1]);
+                                totv[cb][0] = fmaf(bf16_bits_to_f32((uint16_t)(p_bi_lo >> (16 * grp))), wv.z, totv[cb][0]);
+                                totv[cb][1] = fmaf(bf16_bits_to_f32((uint16_t)(p_bi_hi >> (16 * grp))), wv.z, totv[cb][1]);
                             }
                         }
                     }
@@ -472,9 +487,9 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
         const int groups_here = min(SV_CHUNK_GROUPS, n_groups - chunk * SV_CHUNK_GROUPS);
         const uint8_t *sbase = stages + (size_t)st * SV_STAGE_BYTES;
         if (NV > 1) {
-            if (4 * warp < groups_here)
+            if (4 * box < groups_here)
                 several_vectors(sbase, m, row0, chunk, groups_here);
-        } else if (4 * warp < groups_here) {  // the warp's box was loaded (bytes of it past the row's end arrived as zeros)
+        } else if (4 * box < groups_here) {  // the warp's box was loaded (bytes of it past the row's end arrived as zeros)
             // this lane's scale and bias of the two pairs
             uint16_t s_lo[2], s_hi[2], c_lo[2], c_hi[2];
             if (mb.sb_bulk) {
@@ -496,7 +511,7 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
             } else {
                 const int out_dim = mb.out_dim[m];
                 const int r_lo = min(row0 + rho, out_dim - 1), r_hi = min(row0 + rho + 8, out_dim - 1);
-                const size_t col = (size_t)chunk * SV_CHUNK_GROUPS + 4 * warp + my_sel;
+                const size_t col = (size_t)chunk * SV_CHUNK_GROUPS + 4 * box + my_sel;
 #pragma unroll
                 for (int u = 0; u < 2; u++) {
                     const size_t cc = min(col + 2 * u, (size_t)n_groups - 1);
@@ -528,7 +543,7 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
             const float *xwv = xw_lane + (size_t)chunk * (SV_CHUNK_GROUPS * 4);
 #pragma unroll
             for (int u = 0; u < 2; u++) {
-                if (4 * warp + 2 * u + my_sel < groups_here) {  // (always, but for a ragged last stage)
+                if (4 * box + 2 * u + my_sel < groups_here) {  // (always, but for a ragged last stage)
                     const float wgt = xwv[8 * u + my_h];
                     const float f0 = (float)(d[u][0] + d[u][1] * 256) * wgt;  // row rho:     digits (2h, 2h+1) of the group
                     const float f1 = (float)(d[u][2] + d[u][3] * 256) * wgt;  // row rho + 8
@@ -549,7 +564,7 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
             phase ^= 1u;
         }
         if (chunk == n_chunks - 1) {
-            float *dst = red + ((size_t)(buf * SV_BATCH + slot) * SV_WARPS + warp) * (NV * SV_ROWS);
+            float *dst = red + ((size_t)(buf * BATCH + slot) * CW + warp) * (NV * SV_ROWS);
             if (NV == 1) {
                 tot0 += __shfl_xor_sync(0xffffffffu, tot0, 1);
                 tot1 += __shfl_xor_sync(0xffffffffu, tot1, 1);
@@ -574,7 +589,7 @@ dequant_matvec_4bit_stream_kernel(const __grid_constant__ MatvecMaps maps, const
                 }
             }
             if (tid == 0) slot_info[buf * SV_BATCH + slot] = make_int2(m, row0);
-            if (++slot == SV_BATCH && !flush()) {
+            if (++slot == BATCH && !flush()) {
                 failed = true;
                 break;
             }
@@ -638,7 +653,7 @@ cudaError_t launch_stream(MatvecBatch mb, const MatvecMaps *maps, const float *x
     if (grid_out) *grid_out = grid;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(SV_THREADS);
+    cfg.blockDim = dim3((unsigned)((sv_warps(NV) + 1) * 32));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr = {};
