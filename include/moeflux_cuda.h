@@ -462,7 +462,9 @@ int mfc_mla_sdpa_folded_bf16_dev(mfc_ctx *ctx, int32_t num_heads, int32_t cache_
  * CTA (0 = chosen per launch); "gqa_target_ctas" CTAs a decode launch aims for when it cuts the launch's
  * KV tiles into equal runs (0 = one wave: two CTAs per SM); "gqa_chunk" forces the rows per CTA (0 = automatic); "gqa_min_rows" least rows per CTA under the automatic
  * plan (a multiple of 32, default 64); "gqa_unit_aligned" 1 = give every (item, kv head) unit a CTA of its own when
- * equal-length units nearly fill the wave (default 0); "gqa_coop_merge" 0 = never launch cooperatively (default 1: a
+ * equal-length units nearly fill the wave (default 0); "gqa_align_units" 0 = never pad units to whole CTA runs (default 1:
+ * a launch of few long units on a full wave, e.g. a ragged batch of 8-32 sequences, gives every unit whole CTAs, so
+ * that no CTA works on two units); "gqa_coop_merge" 0 = never launch cooperatively (default 1: a
  * launch in which more than "gqa_coop_min_parts" (default 32, at least 8) CTAs share a unit and that
  * unit has at least a quarter of the launch's CTAs, i.e. a lone long sequence or two, is launched cooperatively when
  * it fits the device, and the CTAs that share a unit merge it together);

@@ -167,6 +167,7 @@ struct mfc_ctx {
     int gqa_forced_chunk = 0;
     int gqa_min_rows = 64;         // least cache rows per CTA
     bool gqa_unit_aligned = false;  // one CTA per unit when equal-length units nearly fill the wave (off: see the planner)
+    bool gqa_align_units = true;    // few units on a full wave: whole CTA runs per unit (tuning "gqa_align_units")
     long long launches = 0;
     std::string err;
 };
@@ -421,6 +422,45 @@ int build_gqa_items(mfc_ctx *c, int n, const int32_t *layers, const int32_t *seq
     c->plan_tiles_per_cta = plan_tiles_per_cta(c, total_tiles, max_unit_tiles, min_unit_tiles, (long long)n * g.num_kv_heads);
     c->plan_total_tiles = (int)total_tiles;
     c->plan_max_parts = (max_unit_tiles + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta + 1;
+    // A few long units on a full wave (a ragged batch of 8-32 sequences): runs that cross unit boundaries give one
+    // CTA in ten a second segment -- a second prologue, a parked partial, a fence under full load -- and those CTAs
+    // finish 30-45 us after the rest.  With few units it is cheaper to give every unit whole CTAs: the run length T
+    // grows until sum ceil(tiles / T) fits the wave, every unit is padded to whole runs (half a run wasted per unit on
+    // average) and no CTA has a second segment.  Taken when that waste costs less than the tail it removes.
+    const long long n_units = (long long)n * g.num_kv_heads;
+    if (c->gqa_align_units && c->gqa_target_ctas == 0 && c->gqa_forced_chunk == 0 && n_units * 4 <= c->gqa_slots) {
+        const long long w_min = c->gqa_min_rows / tile;
+        long long T = (total_tiles + c->gqa_slots - 1) / c->gqa_slots;
+        if (T < w_min) T = w_min;
+        const long long w_split = (max_unit_tiles + (MAX_UNIT_PARTS - 2) - 1) / (MAX_UNIT_PARTS - 2);
+        if (T < w_split) T = w_split;
+        long long runs = 0;
+        for (;; T++) {
+            runs = 0;
+            for (int i = 0; i < n; i++) {
+                const GqaItem &it = c->h_gqa_items[i];
+                const long long nt = it.local_len > 0 ? (it.local_len + tile - 1) / tile : 1;
+                runs += ((nt + T - 1) / T) * g.num_kv_heads;
+            }
+            if (runs <= c->gqa_slots) break;
+        }
+        const long long tile_bytes = 2ll * tile * HEAD_DIM * c->kv_esize;
+        if (T * n_units * tile_bytes < 520000000ll) {  // waste (units / 2 runs) under 40 us of a CTA's stream at 22 GB/s
+            long long tb = 0;
+            for (int i = 0; i < n; i++) {
+                GqaItem &it = c->h_gqa_items[i];
+                const long long nt = it.local_len > 0 ? (it.local_len + tile - 1) / tile : 1;
+                const long long padded = ((nt + T - 1) / T) * T;
+                it.tile_begin = (int32_t)tb;
+                it.pad0 = (int32_t)padded;
+                tb += padded * g.num_kv_heads;
+            }
+            total_tiles = tb;
+            c->plan_tiles_per_cta = (int)T;
+            c->plan_total_tiles = (int)tb;
+            c->plan_max_parts = (int)((max_unit_tiles + T - 1) / T);
+        }
+    }
     const int cta = (int)((total_tiles + c->plan_tiles_per_cta - 1) / c->plan_tiles_per_cta);
     if (cta + n * g.num_kv_heads > c->max_parts) {
         fail(c, "internal: split plan exceeds the scratch reserved at open");
@@ -1411,6 +1451,8 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
         c->mv_inject_lost_load = value != 0;
     } else if (!strcmp(key, "matvec_overlap")) {
         c->mv_overlap = value != 0;
+    } else if (!strcmp(key, "gqa_align_units")) {
+        c->gqa_align_units = value != 0;
     } else if (!strcmp(key, "gqa_coop_merge")) {
         c->gqa_coop = value != 0;
     } else if (!strcmp(key, "gqa_coop_min_parts")) {

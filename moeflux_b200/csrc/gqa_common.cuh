@@ -115,7 +115,9 @@ __device__ __forceinline__ Located locate_tile(const GqaParams &p, int gt, int g
     Located L;
     L.it = items[lo];
     L.item_idx = lo;
-    const int nt = L.it.local_len > 0 ? (L.it.local_len + TILE_ROWS - 1) / TILE_ROWS : 1;
+    // tiles a kv head of the item takes in the launch-wide sequence: its own, or (pad0 > 0: a plan that keeps units
+    // and CTA runs aligned) that number rounded up to whole runs; the tiles past the item's rows are empty
+    const int nt = L.it.pad0 > 0 ? L.it.pad0 : (L.it.local_len > 0 ? (L.it.local_len + TILE_ROWS - 1) / TILE_ROWS : 1);
     const int local = gt - L.it.tile_begin;
     L.kvh = local / nt;
     L.t0 = local - L.kvh * nt;

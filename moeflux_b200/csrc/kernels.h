@@ -63,7 +63,9 @@ struct GqaItem {
     int32_t append_row;  // local row that receives k,v, or -1 when another context owns it
     int32_t tile_begin;  // index, in the launch-wide tile sequence, of the first tile of kv head 0;
                          //   every kv head of the item has max(1, ceil(local_len / tile rows)) tiles
-    int32_t pad0, pad1;
+    int32_t pad0;        // 0, or the tiles every kv head of the item occupies in the tile sequence when the plan pads
+                         //   units to whole CTA runs (a multiple of tiles_per_cta, >= the head's own tiles)
+    int32_t pad1;
     int32_t in_idx;      // index of the item's q/gate/k/v/out rows
 };
 
