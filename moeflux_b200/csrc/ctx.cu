@@ -1825,39 +1825,59 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
         return -1;
     }
     cudaSetDevice(g.device);
-    // validate both groups before anything is queued; a failure leaves every state as it was
-    if (n_lin) {
-        if (build_gdn_items(c, n_lin, lin_layers, lin_seqs)) return -1;
-        if (z)
-            for (int i = 0; i < n_lin; i++)
-                if (c->lin_weights_set[c->h_gdn_items[i].w_layer] != 2) {
-                    for (int j = 0; j < n_lin; j++) c->conv_step[c->h_gdn_items[j].state_idx] -= 1;
-                    fail(c, "z given but no norm weight was set for layer " + std::to_string(lin_layers[i]));
-                    return -1;
-                }
-    }
-    int total = 0;
-    if (n_full && build_gqa_items(c, n_full, full_layers, full_seqs, pos, &total)) {
-        for (int j = 0; j < n_lin; j++) c->conv_step[c->h_gdn_items[j].state_idx] -= 1;
-        return -1;
-    }
     cudaStream_t main_stream = c->stream;
+    // The input copies into the staging buffers are queued before the host plans the launches, so that the planning
+    // (tens of microseconds for a hundred items) runs under them. They touch no cache and no state: a validation
+    // failure below still leaves every state as it was.
     // The attention group goes first: its inputs are small and its kernel is the long one, so the copy engine
     // should not make it wait behind the GatedDeltaNet inputs (3.5x larger), which then travel under that kernel.
+    const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)n_full;
+    const size_t kd = sizeof(float) * g.num_kv_heads * HEAD_DIM * (size_t)n_full;
+    // with a KV split, gate and full_out cover the items this rank finishes only
+    const size_t own_qd = split ? sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)c->xc.npr : qd;
+    const size_t vd = sizeof(float) * g.linear_num_v_heads * GDN_DIM * (size_t)n_lin;
+    const size_t hd = sizeof(float) * g.linear_num_v_heads * (size_t)n_lin;
     CK(cudaEventRecord(c->ev_fork, main_stream));
+    CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
     if (n_full) {
-        const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)n_full;
-        const size_t kd = sizeof(float) * g.num_kv_heads * HEAD_DIM * (size_t)n_full;
-        // with a KV split, gate and full_out cover the items this rank finishes only
-        const size_t own_qd = split ? sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)c->xc.npr : qd;
         // q, k, v first; the gate logits (as many bytes as q) are only needed after the attention kernel, so they
         // travel on the side queue under it and are applied by a separate elementwise pass (or by the merge)
         CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, main_stream));
         CK(cudaMemcpyAsync(c->st_k, k, kd, cudaMemcpyHostToDevice, main_stream));
         CK(cudaMemcpyAsync(c->st_v, v, kd, cudaMemcpyHostToDevice, main_stream));
-        CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
         CK(cudaMemcpyAsync(c->st_gate, gate, own_qd, cudaMemcpyHostToDevice, c->side_stream));
         CK(cudaEventRecord(c->ev_gate, c->side_stream));
+    }
+    if (n_lin) {
+        cudaStream_t s2 = c->side_stream;
+        CK(cudaMemcpyAsync(c->st_qkv, qkv, sizeof(float) * c->conv_dim * (size_t)n_lin, cudaMemcpyHostToDevice, s2));
+        if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, s2));
+        CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, s2));
+        CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, s2));
+    }
+    // validate both groups before a kernel is queued; a failure leaves every state as it was, and returns only
+    // after the queued copies have finished reading the caller's buffers
+    auto refuse = [&]() {
+        cudaStreamSynchronize(c->side_stream);
+        cudaStreamSynchronize(main_stream);
+        return -1;
+    };
+    if (n_lin) {
+        if (build_gdn_items(c, n_lin, lin_layers, lin_seqs)) return refuse();
+        if (z)
+            for (int i = 0; i < n_lin; i++)
+                if (c->lin_weights_set[c->h_gdn_items[i].w_layer] != 2) {
+                    for (int j = 0; j < n_lin; j++) c->conv_step[c->h_gdn_items[j].state_idx] -= 1;
+                    fail(c, "z given but no norm weight was set for layer " + std::to_string(lin_layers[i]));
+                    return refuse();
+                }
+    }
+    int total = 0;
+    if (n_full && build_gqa_items(c, n_full, full_layers, full_seqs, pos, &total)) {
+        for (int j = 0; j < n_lin; j++) c->conv_step[c->h_gdn_items[j].state_idx] -= 1;
+        return refuse();
+    }
+    if (n_full) {
         GqaParams p;
         fill_gqa_params(c, p, n_full, total);
         p.q = c->st_q;
@@ -1890,15 +1910,8 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
         CK(cudaMemcpyAsync(full_out, c->st_out, own_qd, cudaMemcpyDeviceToHost, main_stream));
     }
     if (n_lin) {
-        // GatedDeltaNet group on the side queue: its copies and kernel overlap the attention kernel
-        CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
+        // GatedDeltaNet group on the side queue: its copies (queued above) and kernel overlap the attention kernel
         cudaStream_t s2 = c->side_stream;
-        const size_t vd = sizeof(float) * g.linear_num_v_heads * GDN_DIM * (size_t)n_lin;
-        const size_t hd = sizeof(float) * g.linear_num_v_heads * (size_t)n_lin;
-        CK(cudaMemcpyAsync(c->st_qkv, qkv, sizeof(float) * c->conv_dim * (size_t)n_lin, cudaMemcpyHostToDevice, s2));
-        if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, s2));
-        CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, s2));
-        CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, s2));
         c->stream = s2;
         const int rc = launch_gdn(c, n_lin, c->st_qkv, z ? c->st_z : nullptr, c->st_alpha, c->st_beta, c->st_gout);
         c->stream = main_stream;
