@@ -277,7 +277,7 @@ def run_reference(args, rank):
         "e2e": {"value": value, "unit": "layer-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(args, n):
@@ -514,13 +514,16 @@ def run_ours(args, rank, world, local_rank):
     if do_e2e:
         pin = lambda *shape: torch.empty(*shape, dtype=torch.float32).pin_memory()
         n_gate = ng if world == 1 else npr  # gate rows and outputs are needed only where an item is finished
-        hq, hgate, hk, hv, hout = pin(ng, Q_DIM), pin(n_gate, Q_DIM), pin(ng, KV_DIM), pin(ng, KV_DIM), pin(n_gate, Q_DIM)
+        # fused exchange: every rank's host sends the query rows of the items it finishes, the rest cross the links
+        gather_q = world > 1 and fused
+        n_q = npr if gather_q else ng
+        hq, hgate, hk, hv, hout = pin(n_q, Q_DIM), pin(n_gate, Q_DIM), pin(ng, KV_DIM), pin(ng, KV_DIM), pin(n_gate, Q_DIM)
         hqkv, hz, ha, hb, hlo = pin(max(nl, 1), CONV_DIM), pin(max(nl, 1), V_DIM), pin(max(nl, 1), HV), pin(
             max(nl, 1), HV), pin(max(nl, 1), V_DIM)
-        for h, d_ in ((hq, q), (hgate, gate if world == 1 else gate[own]), (hk, kk), (hv, vv), (hqkv, qkv), (hz, z),
+        for h, d_ in ((hq, q[own] if gather_q else q), (hgate, gate if world == 1 else gate[own]), (hk, kk), (hv, vv), (hqkv, qkv), (hz, z),
                       (ha, alpha), (hb, beta)):
             h.copy_(d_.cpu())
-        h2d = 4 * ((ng + n_gate) * Q_DIM + 2 * ng * KV_DIM + nl * (CONV_DIM + V_DIM + 2 * HV))
+        h2d = 4 * ((n_q + n_gate) * Q_DIM + 2 * ng * KV_DIM + nl * (CONV_DIM + V_DIM + 2 * HV))
         d2h = 4 * (n_gate * Q_DIM + nl * V_DIM)
         use_abi = world == 1 or fused
 
@@ -551,6 +554,7 @@ def run_ours(args, rank, world, local_rank):
 
         if use_abi and world > 1:
             ctx.set_tuning("gdn_side_queue", 0)  # the call runs its two groups on its two queues itself
+            ctx.set_tuning("exchange_gather_q", int(gather_q))
         for _ in range(We):
             e2e_step()
         e_blocks = []
@@ -569,7 +573,9 @@ def run_ours(args, rank, world, local_rank):
         e2e = {"value": N_LAYERS * B * K / dt, "unit": "layer-steps/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * dt / K, "steps": K, "repeats": Re,
                "min": N_LAYERS * B * K / max(e_blocks), "max": N_LAYERS * B * K / min(e_blocks),
-               "api": "mfc_eval_token_attn (host pointers; copies, kernels and exchange inside the call)" if use_abi
+               "api": ("mfc_eval_token_attn (host pointers; copies, kernels and exchange inside the call" +
+                       ("; each host sends the query rows of its own items, gathered over NVLink)" if gather_q else ")"))
+               if use_abi
                else "torch copies around the _dev calls and one NCCL all-to-all"}
         ctx.synchronize()
         if use_abi and world > 1:
@@ -1555,7 +1561,26 @@ def compact(line):
             "e2e": (line.get("e2e") or {}).get("value"), "parity": line.get("parity")}
 
 
+_LINE_FD = None
+
+
+def emit(line):
+    """The one JSON line, to the process's real standard output."""
+    data = (json.dumps(line) + "\n").encode()
+    if _LINE_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_LINE_FD, data)
+
+
 def main():
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1 behind Python's back: everything but the
+    # JSON line goes to standard error, so that standard output carries that line alone.
+    global _LINE_FD
+    sys.stdout.flush()
+    _LINE_FD = os.dup(1)
+    os.dup2(2, 1)
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -1576,23 +1601,23 @@ def main():
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
     if args.workload == "prefill":
         if rank == 0:
-            print(json.dumps(run_prefill(args)), flush=True)
+            emit(run_prefill(args))
         return
     if args.workload == "matvec":
         if rank == 0:
             line = run_matvec(args)
-            print(json.dumps(line), flush=True)
+            emit(line)
             if not line["parity"]["ok"]:
                 raise SystemExit("parity check failed: " + json.dumps(line["parity"]))
         return
     if args.workload == "trace":
         if rank == 0:
-            print(json.dumps(run_trace(args)), flush=True)
+            emit(run_trace(args))
         return
     if args.workload == "mla":
         if rank == 0:
             line = run_mla(args)
-            print(json.dumps(line), flush=True)
+            emit(line)
             if not line["parity"]["ok"]:
                 raise SystemExit("parity check failed: " + json.dumps(line["parity"]))
         return
@@ -1617,7 +1642,7 @@ def main():
             line["roofline"]["single_step"] = single_step_latencies(local_rank)
         if others:
             line["other_configs"] = others
-        print(json.dumps(line), flush=True)
+        emit(line)
         failed = (bool(line.get("parity")) and not line["parity"]["ok"]) or any(
             o and o.get("parity") and not o["parity"]["ok"] for o in others.values())
     if world > 1:

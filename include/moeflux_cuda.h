@@ -179,11 +179,18 @@ int mfc_full_attn_step_qproj_batched_dev(mfc_ctx *ctx, int32_t n, const int32_t 
  * RsCtx::eval_token (crates/moeflux/src/riir/mod.rs:1218) does across its layer
  * loop for this path, for layers whose inputs do not depend on one another's
  * outputs; the two groups run on two queues so that the host<->device copies of
- * one overlap the kernel of the other.  All arguments are validated before
- * anything is queued: on -1 no state has changed.  On a context of a KV split
+ * one overlap the kernel of the other.  The input copies into staging buffers
+ * are queued first and the arguments validated under them, before any kernel:
+ * on -1 no cache or state has changed.  On a context of a KV split
  * (kv_world > 1, exchange connected) the full-attention group is the whole
  * step's item list sorted by finishing rank, and gate / full_out cover the
- * items_per_rank items this rank finishes (see mfc_exchange_create). */
+ * items_per_rank items this rank finishes (see mfc_exchange_create).  With the
+ * tuning "exchange_gather_q" 1 (set alike on every rank) q, too, holds only the
+ * rows of the items this rank finishes, [items_per_rank][num_attn_heads*head_dim]:
+ * every rank stores its rows into the peers' memory over the links instead of
+ * every rank's host sending all rows over PCIe (an eighth of the bytes at
+ * kv_world 8); the flags that order it are step numbers, and the waits bounded
+ * like the merge's. */
 int mfc_eval_token_attn(mfc_ctx *ctx, int32_t n_full, const int32_t *full_layers,
                         const int32_t *full_seqs, const int32_t *pos, const float *q,
                         const float *gate, const float *k, const float *v, float *full_out,
@@ -468,6 +475,7 @@ int mfc_mla_sdpa_folded_bf16_dev(mfc_ctx *ctx, int32_t num_heads, int32_t cache_
  * launch in which more than "gqa_coop_min_parts" (default 32, at least 8) CTAs share a unit and that
  * unit has at least a quarter of the launch's CTAs, i.e. a lone long sequence or two, is launched cooperatively when
  * it fits the device, and the CTAs that share a unit merge it together);
+ * "exchange_gather_q" (see mfc_eval_token_attn; default 0);
  * "gdn_side_queue" (see mfc_join); "gqa_wait_spins" poll limit of the kernels' bounded waits (0 = default);
  * "gqa_inject_lost_load" 1 = the first CTA of the next decode launches arms the barrier of its first KV tile and
  * issues no load for it, so that its bounded wait runs out with nothing in flight (exercises the failure path

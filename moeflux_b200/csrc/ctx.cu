@@ -139,7 +139,17 @@ struct mfc_ctx {
         unsigned *done_counter = nullptr;
         unsigned step = 0;              // steps issued so far (flag value of the latest one)
         bool connected = false;
+        // gather of the query rows over the links (tuning "exchange_gather_q"): every rank receives from the host the
+        // rows of the items it finishes only and stores them into every peer's copy of the step's row table
+        float *q_rows = nullptr;            // [2][world * npr][q_dim], in the shared allocation after the flags
+        unsigned *q_flags = nullptr;        // [world], written by the peers: rows of step n have landed
+        float **d_peer_q = nullptr;         // device [2][world]: every rank's two row tables
+        unsigned **d_peer_q_flags = nullptr;  // device [world]
+        unsigned *q_done_counter = nullptr;
+        bool gather_q = false;
+        bool shares_device = false;         // a peer context lives on this context's GPU (tests in one process)
     } xc;
+    static constexpr size_t XC_FLAG_BYTES = 512;  // one flag array: up to 128 ranks
     int plan_tiles_per_cta = 1, plan_total_tiles = 0;  // split of the launch being built
     int plan_max_parts = 1;                            // most CTAs that share one unit in it
     int coop_capacity = 0;                             // CTAs of the decode kernel the device holds at once
@@ -311,6 +321,7 @@ int check_status(mfc_ctx *c) {
         cudaMemsetAsync(c->group_tickets, 0, sizeof(unsigned) * (size_t)c->max_parts, c->stream);
         cudaMemsetAsync(c->mv_sched, 0, 4 * sizeof(unsigned), c->stream);
         if (c->xc.done_counter) cudaMemsetAsync(c->xc.done_counter, 0, sizeof(unsigned), c->stream);
+        if (c->xc.q_done_counter) cudaMemsetAsync(c->xc.q_done_counter, 0, sizeof(unsigned), c->stream);
         cudaStreamSynchronize(c->stream);
         std::string what;
         if (st & 1u) what += " a load did not arrive within the wait limit;";
@@ -984,16 +995,23 @@ size_t xc_item_floats(const mfc_ctx *c) { return (size_t)c->cfg.num_attn_heads *
 int xc_finish_connect(mfc_ctx *c) {
     const int W = c->cfg.kv_world;
     std::vector<float *> recv(2 * (size_t)W);
-    std::vector<unsigned *> flags(W);
+    std::vector<unsigned *> flags(W), q_flags(W);
+    std::vector<float *> q_rows(2 * (size_t)W);
     const size_t half = (size_t)W * c->xc.npr * xc_item_floats(c);  // floats of one receive buffer
+    const size_t q_half = (size_t)W * c->xc.npr * c->cfg.num_attn_heads * HEAD_DIM;  // floats of one row table
     for (int r = 0; r < W; r++) {
         uint8_t *b = c->xc.peer_base[r];
         recv[r] = reinterpret_cast<float *>(b);
         recv[W + r] = reinterpret_cast<float *>(b) + half;
         flags[r] = reinterpret_cast<unsigned *>(b + c->xc.recv_bytes);
+        q_flags[r] = reinterpret_cast<unsigned *>(b + c->xc.recv_bytes + mfc_ctx::XC_FLAG_BYTES);
+        q_rows[r] = reinterpret_cast<float *>(b + c->xc.recv_bytes + 2 * mfc_ctx::XC_FLAG_BYTES);
+        q_rows[W + r] = q_rows[r] + q_half;
     }
     CK(cudaMemcpy(c->xc.d_peer_recv, recv.data(), sizeof(float *) * recv.size(), cudaMemcpyHostToDevice));
     CK(cudaMemcpy(c->xc.d_peer_flags, flags.data(), sizeof(unsigned *) * flags.size(), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(c->xc.d_peer_q, q_rows.data(), sizeof(float *) * q_rows.size(), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(c->xc.d_peer_q_flags, q_flags.data(), sizeof(unsigned *) * q_flags.size(), cudaMemcpyHostToDevice));
     c->xc.connected = true;
     return 0;
 }
@@ -1017,15 +1035,21 @@ int mfc_exchange_create(mfc_ctx *c, int32_t items_per_rank, void *ipc_handle_out
     cudaSetDevice(g.device);
     c->xc.npr = items_per_rank;
     c->xc.recv_bytes = (2 * (size_t)g.kv_world * items_per_rank * xc_item_floats(c) * sizeof(float) + 255) & ~(size_t)255;
-    c->xc.bytes = c->xc.recv_bytes + 256;
+    const size_t q_bytes = 2 * sizeof(float) * (size_t)g.kv_world * items_per_rank * g.num_attn_heads * HEAD_DIM;
+    c->xc.bytes = c->xc.recv_bytes + 2 * mfc_ctx::XC_FLAG_BYTES + q_bytes;
     // its own cudaMalloc (no guard bands): an IPC handle names a whole allocation, from its base
     CK(cudaMalloc((void **)&c->xc.base, c->xc.bytes));
     c->allocs.push_back({c->xc.base, c->xc.bytes, "exchange", false});  // freed with the rest; not band-checked
     CK(cudaMemset(c->xc.base, 0, c->xc.bytes));
     c->xc.recv = reinterpret_cast<float *>(c->xc.base);
     c->xc.flags = reinterpret_cast<unsigned *>(c->xc.base + c->xc.recv_bytes);
+    c->xc.q_flags = reinterpret_cast<unsigned *>(c->xc.base + c->xc.recv_bytes + mfc_ctx::XC_FLAG_BYTES);
+    c->xc.q_rows = reinterpret_cast<float *>(c->xc.base + c->xc.recv_bytes + 2 * mfc_ctx::XC_FLAG_BYTES);
     if (!dalloc(c, &c->xc.d_peer_recv, 2 * (size_t)g.kv_world, true, "xc.d_peer_recv") ||
         !dalloc(c, &c->xc.d_peer_flags, (size_t)g.kv_world, true, "xc.d_peer_flags") ||
+        !dalloc(c, &c->xc.d_peer_q, 2 * (size_t)g.kv_world, true, "xc.d_peer_q") ||
+        !dalloc(c, &c->xc.d_peer_q_flags, (size_t)g.kv_world, true, "xc.d_peer_q_flags") ||
+        !dalloc(c, &c->xc.q_done_counter, 1, true, "xc.q_done_counter") ||
         !dalloc(c, &c->xc.done_counter, 1, true, "xc.done_counter"))
         return -1;
     c->xc.peer_base.assign(g.kv_world, nullptr);
@@ -1078,6 +1102,7 @@ int mfc_exchange_connect_local(mfc_ctx *c, mfc_ctx *const *peers) {
             fail(c, "peer " + std::to_string(r) + " is not the matching context of this split with its exchange created");
             return -1;
         }
+        if (o->cfg.device == c->cfg.device) c->xc.shares_device = true;
         if (o->cfg.device != c->cfg.device) {
             cudaError_t e = cudaDeviceEnablePeerAccess(o->cfg.device, 0);
             if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
@@ -1451,6 +1476,8 @@ int mfc_set_tuning(mfc_ctx *c, const char *key, int value) {
         c->mv_inject_lost_load = value != 0;
     } else if (!strcmp(key, "matvec_overlap")) {
         c->mv_overlap = value != 0;
+    } else if (!strcmp(key, "exchange_gather_q")) {
+        c->xc.gather_q = value != 0;
     } else if (!strcmp(key, "gqa_align_units")) {
         c->gqa_align_units = value != 0;
     } else if (!strcmp(key, "gqa_coop_merge")) {
@@ -1824,41 +1851,46 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
                 "pass items_per_rank * kv_world full-attention items sorted by the rank that finishes them");
         return -1;
     }
+    if (split && n_full && c->xc.gather_q && c->xc.shares_device) {
+        // its kernel waits for the peers' kernels, and kernels on one GPU are not guaranteed to run at the same time
+        fail(c, "exchange_gather_q needs every rank of the split on a GPU of its own");
+        return -1;
+    }
     cudaSetDevice(g.device);
     cudaStream_t main_stream = c->stream;
-    // The input copies into the staging buffers are queued before the host plans the launches, so that the planning
-    // (tens of microseconds for a hundred items) runs under them. They touch no cache and no state: a validation
-    // failure below still leaves every state as it was.
-    // The attention group goes first: its inputs are small and its kernel is the long one, so the copy engine
-    // should not make it wait behind the GatedDeltaNet inputs (3.5x larger), which then travel under that kernel.
+    // Order of the host's work, chosen for the time until the attention kernel starts (the long one): the copies of
+    // its inputs are queued first, the launches are planned under them (tens of microseconds for a hundred items),
+    // its kernel is queued, and only then the gate logits, the GatedDeltaNet inputs (3.5x larger) and that group's
+    // kernel, all of which travel under the attention kernel.  The early copies go to staging buffers and touch no
+    // cache and no state: a validation failure still leaves every state as it was.
     const size_t qd = sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)n_full;
     const size_t kd = sizeof(float) * g.num_kv_heads * HEAD_DIM * (size_t)n_full;
     // with a KV split, gate and full_out cover the items this rank finishes only
     const size_t own_qd = split ? sizeof(float) * g.num_attn_heads * HEAD_DIM * (size_t)c->xc.npr : qd;
     const size_t vd = sizeof(float) * g.linear_num_v_heads * GDN_DIM * (size_t)n_lin;
     const size_t hd = sizeof(float) * g.linear_num_v_heads * (size_t)n_lin;
+    const bool gather = split && n_full && c->xc.gather_q;  // q: own rows only, the rest over the links
+    const unsigned next_step = c->xc.step + 1;              // the exchange's step number of this call
+    const float *q_dev = c->st_q;
     CK(cudaEventRecord(c->ev_fork, main_stream));
     CK(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
     if (n_full) {
-        // q, k, v first; the gate logits (as many bytes as q) are only needed after the attention kernel, so they
-        // travel on the side queue under it and are applied by a separate elementwise pass (or by the merge)
-        CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, main_stream));
+        if (gather) {
+            // q holds the rows of this rank's own items: they land in their slot of this step's row table; the other
+            // slots arrive over the links
+            const size_t own_floats = own_qd / sizeof(float);
+            float *table = c->xc.q_rows + (size_t)(next_step & 1u) * g.kv_world * own_floats;
+            CK(cudaMemcpyAsync(table + (size_t)g.kv_rank * own_floats, q, own_qd, cudaMemcpyHostToDevice, main_stream));
+            q_dev = table;
+        } else {
+            CK(cudaMemcpyAsync(c->st_q, q, qd, cudaMemcpyHostToDevice, main_stream));
+        }
         CK(cudaMemcpyAsync(c->st_k, k, kd, cudaMemcpyHostToDevice, main_stream));
         CK(cudaMemcpyAsync(c->st_v, v, kd, cudaMemcpyHostToDevice, main_stream));
-        CK(cudaMemcpyAsync(c->st_gate, gate, own_qd, cudaMemcpyHostToDevice, c->side_stream));
-        CK(cudaEventRecord(c->ev_gate, c->side_stream));
     }
-    if (n_lin) {
-        cudaStream_t s2 = c->side_stream;
-        CK(cudaMemcpyAsync(c->st_qkv, qkv, sizeof(float) * c->conv_dim * (size_t)n_lin, cudaMemcpyHostToDevice, s2));
-        if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, s2));
-        CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, s2));
-        CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, s2));
-    }
-    // validate both groups before a kernel is queued; a failure leaves every state as it was, and returns only
-    // after the queued copies have finished reading the caller's buffers
+    // validate both groups before any kernel is queued; a refusal returns only after the queued copies have finished
+    // reading the caller's buffers
     auto refuse = [&]() {
-        cudaStreamSynchronize(c->side_stream);
         cudaStreamSynchronize(main_stream);
         return -1;
     };
@@ -1880,15 +1912,21 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
     if (n_full) {
         GqaParams p;
         fill_gqa_params(c, p, n_full, total);
-        p.q = c->st_q;
+        p.q = q_dev;
         p.gate = nullptr;
         p.k = c->st_k;
         p.v = c->st_v;
         p.out = c->st_out;
         p.partial_mode = 0;
         if (split) {
+            c->xc.step = next_step;
+            if (gather) {
+                CK(launch_q_rows_gather(c->xc.d_peer_q + (size_t)(next_step & 1u) * g.kv_world, c->xc.d_peer_q_flags,
+                                        c->xc.q_flags, c->xc.q_done_counter, own_qd / sizeof(float), g.kv_rank,
+                                        g.kv_world, next_step, c->gqa_wait_spins, c->status, main_stream));
+                c->launches += 1;
+            }
             // partials straight into the owners' receive buffers; the merge below waits for the peers' flags
-            c->xc.step += 1;
             p.partial_mode = 1;
             p.po_item_stride = p.pml_item_stride = (size_t)g.num_attn_heads * (HEAD_DIM + 2);
             p.peer_recv = c->xc.d_peer_recv + (size_t)(c->xc.step & 1u) * g.kv_world;
@@ -1900,6 +1938,26 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
             p.flag_value = c->xc.step;
         }
         if (launch_gqa(c, p)) return -1;
+        // the gate logits (as many bytes as q) are only needed after the attention kernel: they travel on the side
+        // queue under it and are applied by a separate elementwise pass (or by the merge)
+        CK(cudaMemcpyAsync(c->st_gate, gate, own_qd, cudaMemcpyHostToDevice, c->side_stream));
+        CK(cudaEventRecord(c->ev_gate, c->side_stream));
+    }
+    if (n_lin) {
+        // GatedDeltaNet group on the side queue: its copies and kernel overlap the attention kernel
+        cudaStream_t s2 = c->side_stream;
+        CK(cudaMemcpyAsync(c->st_qkv, qkv, sizeof(float) * c->conv_dim * (size_t)n_lin, cudaMemcpyHostToDevice, s2));
+        if (z) CK(cudaMemcpyAsync(c->st_z, z, vd, cudaMemcpyHostToDevice, s2));
+        CK(cudaMemcpyAsync(c->st_alpha, alpha, hd, cudaMemcpyHostToDevice, s2));
+        CK(cudaMemcpyAsync(c->st_beta, beta, hd, cudaMemcpyHostToDevice, s2));
+        c->stream = s2;
+        const int rc = launch_gdn(c, n_lin, c->st_qkv, z ? c->st_z : nullptr, c->st_alpha, c->st_beta, c->st_gout);
+        c->stream = main_stream;
+        if (rc) return -1;
+        CK(cudaMemcpyAsync(lin_out, c->st_gout, vd, cudaMemcpyDeviceToHost, s2));
+        CK(cudaEventRecord(c->ev_join, s2));
+    }
+    if (n_full) {
         CK(cudaStreamWaitEvent(main_stream, c->ev_gate, 0));
         if (split) {
             if (mfc_lse_merge_gate_exchange_dev(c, c->st_gate, c->st_out)) return -1;
@@ -1908,16 +1966,6 @@ int mfc_eval_token_attn(mfc_ctx *c, int32_t n_full, const int32_t *full_layers, 
             c->launches += 1;
         }
         CK(cudaMemcpyAsync(full_out, c->st_out, own_qd, cudaMemcpyDeviceToHost, main_stream));
-    }
-    if (n_lin) {
-        // GatedDeltaNet group on the side queue: its copies (queued above) and kernel overlap the attention kernel
-        cudaStream_t s2 = c->side_stream;
-        c->stream = s2;
-        const int rc = launch_gdn(c, n_lin, c->st_qkv, z ? c->st_z : nullptr, c->st_alpha, c->st_beta, c->st_gout);
-        c->stream = main_stream;
-        if (rc) return -1;
-        CK(cudaMemcpyAsync(lin_out, c->st_gout, vd, cudaMemcpyDeviceToHost, s2));
-        CK(cudaEventRecord(c->ev_join, s2));
     }
     if (n_lin) CK(cudaStreamWaitEvent(main_stream, c->ev_join, 0));
     return check_status(c);

@@ -505,6 +505,63 @@ cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_part
     return cudaGetLastError();
 }
 
+// ---- gather of the step's query rows over the links (cross-GPU KV split) ----------
+// Every rank holds, in its own copy of the step's row table, the rows of the items it finishes (they came from its
+// host).  The kernel stores them into the same slot of every peer's table with plain peer stores, then the CTA that
+// finishes last publishes flags[my_rank] = flag_value on every peer and waits, bounded, until every peer's flag has
+// reached flag_value in this rank's own array: when the kernel ends, the whole table is in this GPU's memory and the
+// decode kernel queued behind it reads it like any other device buffer.  The waits are on other GPUs' kernels only.
+static __global__ void __launch_bounds__(256)
+q_rows_gather_kernel(float *const *peer_rows, unsigned *const *peer_flags, const unsigned *my_flags,
+                     unsigned *done_counter, size_t own_floats, int my_rank, int world, unsigned flag_value,
+                     unsigned spins, unsigned *status) {
+    const int tid = threadIdx.x;
+    const size_t n4 = own_floats / 4;
+    const float4 *src = reinterpret_cast<const float4 *>(peer_rows[my_rank] + (size_t)my_rank * own_floats);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = src[i];
+        for (int d = 1; d < world; d++) {
+            const int r = (my_rank + d) % world;  // every rank starts at another peer
+            reinterpret_cast<float4 *>(peer_rows[r] + (size_t)my_rank * own_floats)[i] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_last;
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(done_counter, 1u);
+        s_last = (prev == gridDim.x - 1);
+        if (s_last) *done_counter = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence_system();
+    if (tid < world && tid != my_rank) {
+        unsigned *dst = peer_flags[tid] + my_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(flag_value) : "memory");
+        bool seen = false;
+        for (unsigned i = 0; i < spins && !seen; i++) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + tid) : "memory");
+            seen = (int)(v - flag_value) >= 0;
+            if (!seen) __nanosleep(500);
+        }
+        if (!seen) atomicOr(status, STATUS_PEER_TIMEOUT);
+    }
+}
+
+cudaError_t launch_q_rows_gather(float *const *peer_rows, unsigned *const *peer_flags, const unsigned *my_flags,
+                                 unsigned *done_counter, size_t own_floats, int my_rank, int world,
+                                 unsigned flag_value, unsigned spins, unsigned *status, cudaStream_t stream) {
+    if (world < 2 || world > 128 || own_floats == 0 || own_floats % 4) return cudaErrorInvalidValue;
+    const size_t n4 = own_floats / 4;
+    int grid = (int)((n4 + 511) / 512);  // two 16-byte chunks per thread and peer
+    if (grid > 64) grid = 64;
+    q_rows_gather_kernel<<<grid, 256, 0, stream>>>(peer_rows, peer_flags, my_flags, done_counter, own_floats, my_rank,
+                                                   world, flag_value, spins ? spins : (1u << 22), status);
+    return cudaGetLastError();
+}
+
 // out *= sigmoid(gate), four floats per thread: the gate applied after the fact with the fused epilogue's arithmetic
 static __global__ void sigmoid_gate_kernel(float *out, const float *gate, size_t n4) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;

@@ -150,6 +150,15 @@ cudaError_t launch_lse_merge_gate(int n_parts, int n, int H, const float *o_part
                                   const unsigned *flags = nullptr, unsigned flag_value = 0, unsigned spins = 0,
                                   unsigned *status = nullptr);
 
+// Gather of a step's query rows across the ranks of a KV split: rank my_rank's own_floats floats, at offset
+// my_rank * own_floats of its table peer_rows[my_rank], are stored at the same offset of every peer's table
+// peer_rows[r]; then flags are exchanged (peer_flags[r][my_rank] = flag_value; wait, at most `spins` polls of half a
+// microsecond, two seconds by default, for my_flags[r] >= flag_value from every peer).  When the kernel has ended the
+// whole table is in this GPU's memory.  A wait that runs out sets STATUS_PEER_TIMEOUT in *status.
+cudaError_t launch_q_rows_gather(float *const *peer_rows, unsigned *const *peer_flags, const unsigned *my_flags,
+                                 unsigned *done_counter, size_t own_floats, int my_rank, int world,
+                                 unsigned flag_value, unsigned spins, unsigned *status, cudaStream_t stream);
+
 // RoPE on packed q [H][256], k [Hkv][256] in place (parity hook).
 // out[i] *= sigmoid(gate[i]) for n floats (n a multiple of 4): the gate applied after the fact, with the arithmetic
 // of the fused epilogue, when the gate logits arrive later than q, k and v.

@@ -312,17 +312,19 @@ class Ctx:
         self._check(rc, "mfc_eval_token_attn")
         return fo, lo
 
-    def eval_token_attn_split(self, full_items, pos, q, gate_own, k, v, lin_items, qkv, z, alpha, beta, n_own: int):
+    def eval_token_attn_split(self, full_items, pos, q, gate_own, k, v, lin_items, qkv, z, alpha, beta, n_own: int,
+                              q_own: bool = False):
         """``eval_token_attn`` on a context of a KV split with its exchange connected: ``full_items`` is the whole
         step's item list sorted by finishing rank, ``gate_own`` holds the gate rows of the ``n_own`` items this rank
-        finishes, and the returned full-attention outputs are those items' ([n_own, q_dim])."""
+        finishes, and the returned full-attention outputs are those items' ([n_own, q_dim]).  ``q_own``: ``q`` holds
+        the query rows of those ``n_own`` items only (the tuning "exchange_gather_q" must be 1 on every rank)."""
         nf, nl = len(full_items), len(lin_items)
         fl, flp = _i32([l for l, _ in full_items])
         fs, fsp = _i32([s for _, s in full_items])
         pa, pp = _i32(list(pos))
         ll, llp = _i32([l for l, _ in lin_items] or [0])
         ls, lsp = _i32([s for _, s in lin_items] or [0])
-        q, gate_own = _f32(q, nf * self.q_dim, "q"), _f32(gate_own, n_own * self.q_dim, "gate_own")
+        q, gate_own = _f32(q, (n_own if q_own else nf) * self.q_dim, "q"), _f32(gate_own, n_own * self.q_dim, "gate_own")
         k, v = _f32(k, nf * self.kv_dim, "k"), _f32(v, nf * self.kv_dim, "v")
         fo = np.empty((n_own, self.q_dim), np.float32)
         lo = np.empty((nl, self.total_value), np.float32)

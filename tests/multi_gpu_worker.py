@@ -1,7 +1,8 @@
 """Worker of tests/test_multi_gpu.py: one process per GPU (launched by torch.distributed.run), the KV positions of
 every sequence split block-cyclically over the ranks.  Checks, against the CPU oracle on every rank, the exchange that
 is fused into the decode kernel (peer stores + step flags over CUDA IPC mappings) through the device-pointer calls and
-through the host-pointer step mfc_eval_token_attn.  Prints one line "rank R ok ..." per rank."""
+through the host-pointer step mfc_eval_token_attn, with every host sending all query rows and with the rows
+gathered over the links.  Prints one line "rank R ok ..." per rank."""
 import os
 import sys
 
@@ -47,7 +48,7 @@ def main():
             lin = [I.gdn_step_inputs(r) for _ in range(2 * world)][2 * rank:2 * rank + 2]
             refs = [orc.full_attn_step(layer, s, pos, *ins[j]) for j, (layer, s) in enumerate(items)]
             q, gate, k, v = (np.stack([i[c] for i in ins]) for c in range(4))
-            if pos % 2 == 0:  # device-pointer calls
+            if pos % 3 == 0:  # device-pointer calls
                 dq, dg, dk, dv = (torch.tensor(a, device=dev) for a in (q, gate, k, v))
                 out = torch.empty(npr, G.q_dim, device=dev)
                 torch.cuda.synchronize()
@@ -59,9 +60,12 @@ def main():
                     a, b = ctx.linear_attn_step(layer, s, *x), orc.linear_attn_step(layer, s, *x)
                     worst = max(worst, I.rel_err(a, b) * (tol / TOL_F32))
             else:             # the host-pointer step: both groups, copies and exchange inside one call
-                got, lo = ctx.eval_token_attn_split(items, [pos] * n, q, gate[own], k, v, lin_items,
+                q_own = pos % 3 == 2  # ... and the query rows gathered over the links, each host sending its own
+                ctx.set_tuning("exchange_gather_q", int(q_own))
+                got, lo = ctx.eval_token_attn_split(items, [pos] * n, q[own] if q_own else q, gate[own], k, v, lin_items,
                                                     np.stack([x[0] for x in lin]), np.stack([x[1] for x in lin]),
-                                                    np.stack([x[2] for x in lin]), np.stack([x[3] for x in lin]), npr)
+                                                    np.stack([x[2] for x in lin]), np.stack([x[3] for x in lin]), npr,
+                                                    q_own=q_own)
                 for j, ((layer, s), x) in enumerate(zip(lin_items, lin)):
                     worst = max(worst, I.rel_err(lo[j], orc.linear_attn_step(layer, s, *x)) * (tol / TOL_F32))
             for j in range(npr):
