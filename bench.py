@@ -68,6 +68,10 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--repeats", type=int, default=0, help="timed blocks of --steps steps (0: at least 7 and about a second)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gather-q", type=int, default=0, choices=[0, 1],
+                    help="N>1, fused exchange, end-to-end arm: 1 = every host sends the query rows of its own items and "
+                         "the ranks gather them over NVLink (an eighth of the PCIe bytes at 8 GPUs, the same step "
+                         "time); 0 = every host sends all rows")
     ap.add_argument("--no-single-step", action="store_true", help="skip the batch-1 single-step latencies (N=1, stack)")
     ap.add_argument("--other-configs", type=int, default=1,
                     help="1 (default): the stack line also carries compact lines of the ragged workload (every N) and of "
@@ -515,7 +519,7 @@ def run_ours(args, rank, world, local_rank):
         pin = lambda *shape: torch.empty(*shape, dtype=torch.float32).pin_memory()
         n_gate = ng if world == 1 else npr  # gate rows and outputs are needed only where an item is finished
         # fused exchange: every rank's host sends the query rows of the items it finishes, the rest cross the links
-        gather_q = world > 1 and fused
+        gather_q = world > 1 and fused and bool(args.gather_q)
         n_q = npr if gather_q else ng
         hq, hgate, hk, hv, hout = pin(n_q, Q_DIM), pin(n_gate, Q_DIM), pin(ng, KV_DIM), pin(ng, KV_DIM), pin(n_gate, Q_DIM)
         hqkv, hz, ha, hb, hlo = pin(max(nl, 1), CONV_DIM), pin(max(nl, 1), V_DIM), pin(max(nl, 1), HV), pin(
