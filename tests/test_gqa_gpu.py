@@ -347,6 +347,13 @@ def test_kv_split_fused_exchange_on_one_gpu(bf16):
         parts[0].synchronize()
     with pytest.raises(M.MfcError, match="exchange"):
         parts[0].exchange_create(npr)  # already created
+    # the gather of the query rows over the links waits for the peers' kernels: with a peer on the same GPU the
+    # host-pointer step refuses it before anything is queued
+    parts[1].set_tuning("exchange_gather_q", 1)
+    zq, zk = np.zeros((npr, G.q_dim), np.float32), np.zeros((n, G.kv_dim), np.float32)
+    with pytest.raises(M.MfcError, match="GPU of its own"):
+        parts[1].eval_token_attn_split(items, [0] * n, zq, zq, zk, zk, [], None, None, None, None, npr, q_own=True)
+    parts[1].set_tuning("exchange_gather_q", 0)
     for c in parts:
         c.check_guards()
         c.close()
